@@ -1,0 +1,286 @@
+/*
+ * rnb_b200 — C ABI of the sm_100a batch-1 decode/prefill operator library.
+ *
+ * Drop-in boundary: runNburn has no C ABI for its CUDA operators; what `rnb-runtime` and
+ * `rnb-llm` call is the set of Rust free functions that `rnb_backend_cuda` re-exports
+ * (crates/rnb-backend/cuda/src/lib.rs:44-175).  Each entry point below replaces one of
+ * those functions (cited per declaration, paths relative to the reference project):
+ * slices become (pointer, length), `Result<_, String>` becomes an int status plus
+ * rnb_b200_last_error(), and `Vec<f32>` results become caller-provided buffers.
+ *
+ * Conventions kept from the reference:
+ *  - weight slices are borrowed host memory (the GGUF mmap) that outlives the call; the
+ *    library owns every device copy and keys it by (host address, length);
+ *  - shape errors are reported before any CUDA call, with the reference's messages;
+ *  - host-returning calls synchronise their stream before returning; `_dev` calls do not;
+ *  - callable from any thread; calls are serialised on one process-wide lock;
+ *  - device selection by the RNB_CUDA_DEVICE environment variable (default 0);
+ *  - there is no CPU fallback: without a usable CUDA device every compute call fails.
+ */
+#ifndef RNB_B200_H
+#define RNB_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* status codes — DeviceOpStatus, crates/rnb-backend/api/src/lib.rs:205-211, plus CUDA errors */
+#define RNB_B200_OK 0
+#define RNB_B200_UNSUPPORTED 1
+#define RNB_B200_VALIDATION_FAILED 2
+#define RNB_B200_OUT_OF_MEMORY 3
+#define RNB_B200_CUDA_ERROR 4
+#define RNB_B200_DEVICE_FAULT_FLAG 5 /* a kernel reported a bounded wait that gave up */
+
+/* GGML type ids used by `down_quant: u32` arguments */
+#define RNB_B200_TYPE_Q8_0 8u
+#define RNB_B200_TYPE_Q4_K 12u
+#define RNB_B200_TYPE_Q6_K 14u
+
+/* Message of the last failing call on this thread (never NULL). */
+const char *rnb_b200_last_error(void);
+
+/* CudaState::open — crates/rnb-backend/cuda/src/runtime/state/init.rs:86-139.  Every compute
+ * call opens the state lazily; calling this first only moves the cost. */
+int rnb_b200_open(void);
+/* Drop for CudaState — state/init.rs:446-857: frees every device allocation. */
+void rnb_b200_close(void);
+/* cuda_memory_info — api/cache_api.rs:97 */
+int rnb_b200_cuda_memory_info(size_t *free_bytes, size_t *total_bytes);
+int rnb_b200_device_sm_count(int *sm_count);
+
+/* ---- resident weight cache -------------------------------------------------------------- */
+/* cuda_cache_snapshot / cuda_weight_residency_counters — api/cache_api.rs:114,147;
+ * DeviceTransferCounters — crates/rnb-backend/api/src/lib.rs:213-242 */
+typedef struct {
+    uint64_t lookups, hits, misses, evictions, uploads, upload_bytes, transient_uploads;
+    uint64_t resident_entries, resident_bytes, resident_limit_bytes;
+    uint64_t h2d_bytes, d2h_bytes;
+} rnb_b200_cache_snapshot;
+int rnb_b200_cuda_cache_snapshot(rnb_b200_cache_snapshot *out);
+/* clear_q4k_cache — api/cache_api.rs:18 */
+int rnb_b200_clear_q4k_cache(void);
+/* reset_state_for_engine_init — api/cache_api.rs:83 */
+int rnb_b200_reset_state_for_engine_init(void);
+/* prewarm_q4k_weights(&[&[u8]]) -> usize — api/quant_api.rs:952-971 */
+int rnb_b200_prewarm_q4k_weights(const uint8_t *const *slices, const size_t *lens, size_t n,
+                                 size_t *n_resident);
+/* Residency budget override in bytes (0 = derive from free memory as
+ * DeviceResidencyPlan does — crates/rnb-memory/src/device_residency.rs:40-91). */
+int rnb_b200_set_resident_limit(size_t bytes);
+/* host_register.rs:45-190 — pin the page-aligned interior of a host range for async DMA;
+ * clear_host_registered_ranges — api/cache_api.rs */
+int rnb_b200_register_host_range(const void *ptr, size_t len);
+int rnb_b200_clear_host_registered_ranges(void);
+
+/* ---- Q8_K activation quantisation --------------------------------------------------------
+ * quantize_input_q8k_into — crates/rnb-cpu/src/gemm/activation_q8.rs:122-139 (the reference
+ * quantises activations on the host; this path does it on the device, bit-exactly).
+ * `blocks_out` receives n/256 blocks of 292 bytes (f32 d, i8 qs[256], i16 bsums[16]). */
+int rnb_b200_quantize_q8k(const float *input, size_t n, void *blocks_out);
+
+/* ---- quantised matvec -------------------------------------------------------------------- */
+/* q4k_gemv / q4k_gemv_into — api/quant_api.rs:183-218,220 */
+int rnb_b200_q4k_gemv(const uint8_t *weights, size_t weights_len, size_t rows, size_t cols,
+                      const float *input, size_t input_len, float *output, size_t output_len);
+/* q6k_gemv — api/quant_api.rs:2071-2106 */
+int rnb_b200_q6k_gemv(const uint8_t *weights, size_t weights_len, size_t rows, size_t cols,
+                      const float *input, size_t input_len, float *output, size_t output_len);
+/* q8_0_gemv — api/quant_api.rs:498-505 (f32 activations, as rnb-cpu's x86 path) */
+int rnb_b200_q8_0_gemv(const uint8_t *weights, size_t weights_len, size_t rows, size_t cols,
+                       const float *input, size_t input_len, float *output, size_t output_len);
+/* q4k_gemv_with_device_input — api/quant_api.rs:288; q6k_… — :242.  `input_dev` is a device
+ * address of `cols` f32 values. */
+int rnb_b200_q4k_gemv_with_device_input(const uint8_t *weights, size_t weights_len, size_t rows,
+                                        size_t cols, uint64_t input_dev, float *output,
+                                        size_t output_len);
+int rnb_b200_q6k_gemv_with_device_input(const uint8_t *weights, size_t weights_len, size_t rows,
+                                        size_t cols, uint64_t input_dev, float *output,
+                                        size_t output_len);
+/* q6k_gemv_argmax -> (u32, f32) — api/quant_api.rs:2170.  Ties resolve to the LAST index, the
+ * rule of the reference's CPU sampler (crates/rnb-llm/src/sampler/greedy.rs:4-11). */
+int rnb_b200_q6k_gemv_argmax(const uint8_t *weights, size_t weights_len, size_t rows, size_t cols,
+                             const float *input, size_t input_len, uint32_t *index_out,
+                             float *value_out);
+/* q4k_gemv_batch / q6k_gemv_batch — api/quant_api.rs:2283,3919: input [seq][cols], output
+ * seq-major [seq][rows]. */
+int rnb_b200_q4k_gemv_batch(const uint8_t *weights, size_t weights_len, size_t rows, size_t cols,
+                            const float *input, size_t input_len, float *output,
+                            size_t output_len);
+int rnb_b200_q6k_gemv_batch(const uint8_t *weights, size_t weights_len, size_t rows, size_t cols,
+                            const float *input, size_t input_len, float *output,
+                            size_t output_len);
+
+/* ---- attention ---------------------------------------------------------------------------- */
+/* attention_decode_hd128 — api/attention_api.rs:1943-1978.  q f32[heads*128]; k, v f16 bits
+ * [kv_len][kv_heads][128]; out f32[heads*128]. */
+int rnb_b200_attention_decode_hd128(const float *q, size_t q_len, const uint16_t *k,
+                                    const uint16_t *v, size_t kv_elems, size_t kv_len,
+                                    size_t num_heads, size_t num_kv_heads, float scale,
+                                    float *out, size_t out_len);
+/* attention_decode_cached — api/attention_api.rs:2055-2102 (runtime/attention.rs:3913-4291):
+ * per-layer device KV mirror keyed by the host K/V base addresses; only rows the mirror does
+ * not hold yet are uploaded. */
+int rnb_b200_attention_decode_cached(size_t layer_index, const float *q, size_t q_len,
+                                     const uint16_t *k, const uint16_t *v, size_t kv_elems,
+                                     size_t kv_len, size_t num_heads, size_t num_kv_heads,
+                                     size_t head_dim, float scale, float *out, size_t out_len);
+/* clear_decode_attention_kv_cache — api/cache_api.rs:136 */
+int rnb_b200_clear_decode_attention_kv_cache(void);
+/* attention_prefill_flash_hd128 — api/attention_api.rs:661-700: causal, query i sees keys
+ * 0..(kv_len - seq_len + i); q f32 [seq][heads][128]; k, v f32 [kv_len][kv_heads][128]. */
+int rnb_b200_attention_prefill_flash_hd128(const float *q, const float *k, const float *v,
+                                           size_t seq_len, size_t kv_len, size_t num_heads,
+                                           size_t num_kv_heads, float scale, float *out);
+/* dense_q4k_attention_qkv_rope_hd128_decode — api/dense_api.rs:988-1074: q/k/v matvec,
+ * adjacent-pair RoPE on q and k at position pos_start, K/V rounded to f16.  Weight types are
+ * given per matrix (the reference's name says Q4_K; Q4_K_M files carry Q6_K in attn_v). */
+int rnb_b200_dense_attention_qkv_rope_hd128_decode(
+    const uint8_t *q_w, size_t q_w_len, uint32_t q_type, const uint8_t *k_w, size_t k_w_len,
+    uint32_t k_type, const uint8_t *v_w, size_t v_w_len, uint32_t v_type, size_t q_rows,
+    size_t kv_rows, size_t n_embd, size_t num_heads, size_t num_kv_heads, float rope_theta,
+    size_t pos_start, const float *input, float *q_rope, uint16_t *k_bits, uint16_t *v_bits);
+/* dense_q4k_silu_ffn_batch — api/dense_api.rs:297-339: down(silu(gate x) * (up x)),
+ * seq-major [seq][n_embd] */
+int rnb_b200_dense_q4k_silu_ffn_batch(const uint8_t *gate, size_t gate_len, const uint8_t *up,
+                                      size_t up_len, const uint8_t *down, size_t down_len,
+                                      uint32_t down_quant, size_t n_ff, size_t n_embd,
+                                      size_t seq_len, const float *input, float *output);
+
+/* ---- MoE ---------------------------------------------------------------------------------- */
+/* moe_route_topk_f32 — api/dense_api.rs:1834 (kernel quant_batch_and_ops.cuh:4782-4912).
+ * Softmax mode only (sigmoid_mode != 0 → RNB_B200_UNSUPPORTED).  ids/weights: [seq][top_k],
+ * retained_counts: [seq]. */
+int rnb_b200_moe_route_topk_f32(const float *logits, size_t logits_len,
+                                const float *selection_bias, size_t seq_len, size_t n_expert,
+                                size_t top_k, int sigmoid_mode, int normalize_selected,
+                                float scale, float adaptive_top_p, uint32_t *ids_out,
+                                float *weights_out, uint32_t *retained_counts_out);
+/* Router logits f32 [n_expert][hidden] x h, in the summation order of the reference's host
+ * gemv_f32 (crates/rnb-cpu/src/gemm/f32_gemv.rs:215-237), bit-exact. */
+int rnb_b200_router_logits_f32(const float *router_w, size_t n_expert, size_t hidden,
+                               const float *h, float *logits_out);
+/* qwen35_sparse_experts — api/qwen_moe_api.rs:1712-1803: out = sum_e w_e * Down_e(silu(Gate_e
+ * x) * (Up_e x)) over the routed experts, summed in selection order.  gate/up are Q4_K,
+ * down is `down_quant`. */
+int rnb_b200_qwen35_sparse_experts(const uint8_t *const *gate, const uint8_t *const *up,
+                                   const uint8_t *const *down, size_t gate_slice_len,
+                                   size_t down_slice_len, const float *route_weights,
+                                   size_t n_selected, uint32_t down_quant, size_t n_ff,
+                                   size_t n_embd, const float *input, float *output);
+/* qwen35_register_moe_layer — api/qwen_moe_api.rs:1502-1553: uploads one layer's stacked
+ * expert tensors without evicting; *fitted = 0 when it did not fit. */
+int rnb_b200_qwen35_register_moe_layer(const uint8_t *gate_all, size_t gate_len,
+                                       const uint8_t *up_all, size_t up_len,
+                                       const uint8_t *down_all, size_t down_len,
+                                       uint32_t down_quant, size_t n_ff, size_t n_embd,
+                                       int *fitted);
+
+/* ---- glue ops ------------------------------------------------------------------------------ */
+/* rms_norm_rows_f32 — api/dense_api.rs:2527 (CPU formula: f64 mean square, (x/rms)*w) */
+int rnb_b200_rms_norm_rows_f32(const float *input, const float *weight, size_t hidden,
+                               size_t rows, float eps, float *output);
+/* rope_f32_inplace — api/dense_api.rs:2001 (adjacent pairs; neox != 0 → half-split) */
+int rnb_b200_rope_f32_inplace(float *data, size_t n, size_t pos_start, size_t head_dim,
+                              size_t dim, float theta, int neox);
+/* activation_mul_f32_inplace — api/dense_api.rs:1331: gate = silu(gate) * up */
+int rnb_b200_activation_mul_f32_inplace(float *gate, const float *up, size_t n);
+
+/* ---- expert-cache bookkeeping (host only; crates/rnb-memory/src/sparse_expert_cache.rs) ---- */
+typedef struct {
+    uint64_t missing_bytes, eviction_reload_bytes;
+    uint32_t predicted_future_reuses, replaces_temp_upload;
+} rnb_b200_bundle_admission;
+/* evaluate_expert_bundle_admission — sparse_expert_cache.rs:221-245: 1 = admit */
+int rnb_b200_evaluate_expert_bundle_admission(const rnb_b200_bundle_admission *a);
+/* DeviceResidencyPlan::from_snapshot — crates/rnb-memory/src/device_residency.rs:40-91:
+ * resident_limit = free - reserve, reserve = clamp(ceil_256MiB(total/16), 512 MiB, 2 GiB) */
+uint64_t rnb_b200_resident_limit_for(uint64_t total_bytes, uint64_t free_bytes);
+
+/* ---- token-level decoder: the device-resident chain ------------------------------------------
+ * The reference drives one operator call (and usually one stream sync) per projection; its
+ * "carrier" variants (api/dense_api.rs:1176-1311, 2098-2400) were moving toward keeping
+ * activations on the device.  The decoder is that chain finished: weights are registered
+ * once, a decode step is one CUDA graph launch, and only the token id crosses PCIe.
+ * Mirrors Engine::forward_decode — crates/rnb-llm/src/engine/decode_inference.rs:175-208,
+ * decode.rs:199-564, decode_ffn.rs:294-366, logits.rs. */
+typedef struct {
+    int32_t n_layer, hidden, n_head, n_kv_head, head_dim, n_ff, vocab;
+    int32_t rope_neox;
+    float rms_eps, rope_theta;
+    int32_t n_expert, n_expert_used, n_ff_expert;
+    int32_t max_ctx;
+    /* row sharding across GPUs (1 = single GPU) */
+    int32_t world_size, rank;
+} rnb_b200_model_cfg;
+typedef struct {
+    uint32_t type;
+    const uint8_t *data; /* host bytes (copied to the device) */
+    size_t len;
+} rnb_b200_qweight;
+typedef struct {
+    const float *attn_norm, *ffn_norm;
+    rnb_b200_qweight wq, wk, wv, wo, gate, up, down;
+    const float *router;
+    rnb_b200_qweight gate_exps, up_exps, down_exps;
+} rnb_b200_layer_weights;
+typedef struct rnb_b200_decoder rnb_b200_decoder;
+
+int rnb_b200_decoder_create(const rnb_b200_model_cfg *cfg, rnb_b200_decoder **out);
+void rnb_b200_decoder_destroy(rnb_b200_decoder *d);
+/* Copies one layer's weights to the device (row-sharded when world_size > 1). */
+int rnb_b200_decoder_set_layer(rnb_b200_decoder *d, int layer, const rnb_b200_layer_weights *w);
+int rnb_b200_decoder_set_globals(rnb_b200_decoder *d, rnb_b200_qweight token_embd,
+                                 const float *out_norm, rnb_b200_qweight output);
+/* Fills every weight with synthetic data generated on the device (bench only): N(0, sigma)
+ * values quantised per block with a min/max fit; norms = 1. */
+int rnb_b200_decoder_fill_synthetic(rnb_b200_decoder *d, uint64_t seed, float sigma);
+/* Fills the KV cache rows [0, n_pos) with synthetic f16 values (bench only). */
+int rnb_b200_decoder_fill_kv_synthetic(rnb_b200_decoder *d, int n_pos, uint64_t seed);
+/* One decode step at position `pos`: token in, greedy next token out (host buffers).
+ * logits_out may be NULL; otherwise receives `vocab` floats. */
+int rnb_b200_decoder_step(rnb_b200_decoder *d, uint32_t token, int pos, uint32_t *next_token,
+                          float *logits_out);
+/* Enqueue-only variant for device-resident timing: consumes the token already on the device
+ * (the previous step's argmax when `chain` != 0), no host copy, no synchronisation.
+ * pos >= 0 sets the position; pos < 0 continues at the position after the previous step. */
+int rnb_b200_decoder_step_dev(rnb_b200_decoder *d, int pos, int chain);
+int rnb_b200_decoder_sync(rnb_b200_decoder *d);
+/* Device stream handle (cudaStream_t) the decoder launches on, for event timing. */
+void *rnb_b200_decoder_stream(rnb_b200_decoder *d);
+int rnb_b200_decoder_read_kv(rnb_b200_decoder *d, int layer, int n_pos, uint16_t *k_out,
+                             uint16_t *v_out);
+int rnb_b200_decoder_read_hidden(rnb_b200_decoder *d, float *hidden_out);
+int rnb_b200_decoder_read_expert_ids(rnb_b200_decoder *d, int layer, uint32_t *ids_out);
+/* kernels launched per decode step, bytes of weights resident, per-step algorithmic bytes */
+int rnb_b200_decoder_stats(rnb_b200_decoder *d, uint64_t *launches_per_step,
+                           uint64_t *weight_bytes, uint64_t *kv_bytes_per_pos);
+/* Multi-GPU: attach an NCCL communicator built from a 128-byte unique id that rank 0 made
+ * with rnb_b200_nccl_unique_id and the host side distributed to every rank. */
+int rnb_b200_nccl_unique_id(uint8_t id_out[128]);
+int rnb_b200_decoder_attach_nccl(rnb_b200_decoder *d, const uint8_t id[128]);
+
+/* ---- device-pointer tier (no host copies, no synchronisation; for callers that keep
+ * activations on the device and for kernel timing).  `stream` is a cudaStream_t or NULL. */
+int rnb_b200_dev_quantize_q8k(const float *x_dev, size_t cols, size_t seq, void *xq_dev,
+                              void *ref_blocks_dev, void *stream);
+size_t rnb_b200_dev_q8k_bytes(size_t cols);
+int rnb_b200_dev_gemv(uint32_t type, const uint8_t *w_dev, size_t rows, size_t cols,
+                      const void *x_dev /* Q8K-dev layout, or f32 for Q8_0 */, float *y_dev,
+                      int rows_per_tile /* 0 = auto */, void *stream);
+int rnb_b200_dev_flash_decode(const float *q_dev, const uint16_t *k_dev, const uint16_t *v_dev,
+                              size_t kv_len, size_t num_heads, size_t num_kv_heads, float scale,
+                              float *partials_dev, size_t partials_bytes, int n_chunks,
+                              float *out_dev, void *stream);
+size_t rnb_b200_flash_decode_scratch_bytes(size_t num_heads, int n_chunks);
+int rnb_b200_flash_decode_default_chunks(size_t kv_len, size_t num_kv_heads);
+/* Reads and clears the device error word set by kernels whose bounded waits gave up. */
+int rnb_b200_dev_error_flag(int *flag_out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* RNB_B200_H */

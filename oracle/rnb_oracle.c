@@ -1016,17 +1016,26 @@ size_t orc_moe_route_topk(const float *logits, size_t n_expert, size_t top_k, ui
     return sel;
 }
 
-/* Router logits: sequential f32 dot per expert row.  The reference computes these on the
- * host with gemv_f32 (crates/rnb-llm/src/engine/models/shared_expert_moe/moe_view.rs:146-157);
- * the summation order pinned here (one running sum, k ascending, no FMA) is the one the
- * device kernel reproduces so that expert ids match exactly. */
+/* Router logits: the reference computes them on the host with gemv_f32 → dot_f32_row
+ * (crates/rnb-llm/src/engine/models/shared_expert_moe/moe_view.rs:146-157,
+ *  crates/rnb-cpu/src/gemm/f32_gemv.rs:215-237,266-275): two 8-lane FMA accumulators walking
+ * the row 16 elements at a time, acc0+acc1, then (l+l4) → (+2) → (+1), then a scalar tail.
+ * Restated lane by lane with fmaf, which is bit-identical to the vector FMA. */
+static float dot_f32_row(const float *a, const float *b, size_t n) {
+    float acc[16] = {0};
+    size_t i = 0;
+    for (; i + 16 <= n; i += 16)
+        for (int l = 0; l < 16; l++) acc[l] = fmaf(a[i + l], b[i + l], acc[l]);
+    float s[8];
+    for (int l = 0; l < 8; l++) s[l] = acc[l] + acc[l + 8];
+    float r0 = s[0] + s[4], r1 = s[1] + s[5], r2 = s[2] + s[6], r3 = s[3] + s[7];
+    float t0 = r0 + r2, t1 = r1 + r3;
+    float out = t0 + t1;
+    for (; i < n; i++) out += a[i] * b[i];
+    return out;
+}
 void orc_gemv_f32(const float *w, const float *x, float *out, size_t rows, size_t cols) {
-    for (size_t r = 0; r < rows; r++) {
-        float acc = 0.0f;
-        const float *wr = w + r * cols;
-        for (size_t k = 0; k < cols; k++) acc += wr[k] * x[k];
-        out[r] = acc;
-    }
+    for (size_t r = 0; r < rows; r++) out[r] = dot_f32_row(w + r * cols, x, cols);
 }
 
 /* Expert FFN: per selected expert gate/up GEMV → SiLU·up → down GEMV → × route weight;

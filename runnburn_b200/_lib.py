@@ -1,0 +1,146 @@
+"""Loads librnb_b200.so and declares its C ABI (include/rnb_b200.h) for ctypes.
+
+The CUDA library is the product: if it is missing this module raises, there is no fallback.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+PKG = Path(__file__).resolve().parent
+LIB_PATH = PKG / "librnb_b200.so"
+HEADER = PKG.parent / "include" / "rnb_b200.h"
+
+OK, UNSUPPORTED, VALIDATION_FAILED, OUT_OF_MEMORY, CUDA_ERROR, DEVICE_FAULT_FLAG = range(6)
+TYPE_Q8_0, TYPE_Q4_K, TYPE_Q6_K = 8, 12, 14
+
+
+class RnbError(RuntimeError):
+    """A failing library call: `status` is the RNB_B200_* code, the message is the library's."""
+
+    def __init__(self, status: int, message: str):
+        super().__init__(message)
+        self.status = status
+
+
+class CacheSnapshot(C.Structure):
+    _fields_ = [(n, C.c_uint64) for n in (
+        "lookups", "hits", "misses", "evictions", "uploads", "upload_bytes", "transient_uploads",
+        "resident_entries", "resident_bytes", "resident_limit_bytes", "h2d_bytes", "d2h_bytes")]
+
+
+class BundleAdmission(C.Structure):
+    _fields_ = [("missing_bytes", C.c_uint64), ("eviction_reload_bytes", C.c_uint64),
+                ("predicted_future_reuses", C.c_uint32), ("replaces_temp_upload", C.c_uint32)]
+
+
+class ModelCfg(C.Structure):
+    _fields_ = [(n, C.c_int32) for n in ("n_layer", "hidden", "n_head", "n_kv_head", "head_dim",
+                                         "n_ff", "vocab", "rope_neox")] + \
+               [("rms_eps", C.c_float), ("rope_theta", C.c_float)] + \
+               [(n, C.c_int32) for n in ("n_expert", "n_expert_used", "n_ff_expert", "max_ctx",
+                                         "world_size", "rank")]
+
+
+class QWeight(C.Structure):
+    _fields_ = [("type", C.c_uint32), ("data", C.c_void_p), ("len", C.c_size_t)]
+
+
+class LayerWeights(C.Structure):
+    _fields_ = [("attn_norm", C.c_void_p), ("ffn_norm", C.c_void_p)] + \
+               [(n, QWeight) for n in ("wq", "wk", "wv", "wo", "gate", "up", "down")] + \
+               [("router", C.c_void_p)] + \
+               [(n, QWeight) for n in ("gate_exps", "up_exps", "down_exps")]
+
+
+_lib = None
+
+
+def load() -> C.CDLL:
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not LIB_PATH.exists():
+        raise ImportError(
+            f"{LIB_PATH} is missing: build it with `python -m runnburn_b200.build` "
+            "(nvcc, sm_100a). There is no CPU or PyTorch fallback for this library.")
+    L = C.CDLL(str(LIB_PATH))
+    sz, vp, i32, u32, f32, u64 = C.c_size_t, C.c_void_p, C.c_int, C.c_uint32, C.c_float, C.c_uint64
+    L.rnb_b200_last_error.restype = C.c_char_p
+    L.rnb_b200_close.restype = None
+    sig = {
+        "rnb_b200_open": [],
+        "rnb_b200_cuda_memory_info": [vp, vp],
+        "rnb_b200_device_sm_count": [vp],
+        "rnb_b200_cuda_cache_snapshot": [vp],
+        "rnb_b200_clear_q4k_cache": [],
+        "rnb_b200_reset_state_for_engine_init": [],
+        "rnb_b200_prewarm_q4k_weights": [vp, vp, sz, vp],
+        "rnb_b200_set_resident_limit": [sz],
+        "rnb_b200_register_host_range": [vp, sz],
+        "rnb_b200_clear_host_registered_ranges": [],
+        "rnb_b200_quantize_q8k": [vp, sz, vp],
+        "rnb_b200_q4k_gemv": [vp, sz, sz, sz, vp, sz, vp, sz],
+        "rnb_b200_q6k_gemv": [vp, sz, sz, sz, vp, sz, vp, sz],
+        "rnb_b200_q8_0_gemv": [vp, sz, sz, sz, vp, sz, vp, sz],
+        "rnb_b200_q4k_gemv_with_device_input": [vp, sz, sz, sz, u64, vp, sz],
+        "rnb_b200_q6k_gemv_with_device_input": [vp, sz, sz, sz, u64, vp, sz],
+        "rnb_b200_q6k_gemv_argmax": [vp, sz, sz, sz, vp, sz, vp, vp],
+        "rnb_b200_q4k_gemv_batch": [vp, sz, sz, sz, vp, sz, vp, sz],
+        "rnb_b200_q6k_gemv_batch": [vp, sz, sz, sz, vp, sz, vp, sz],
+        "rnb_b200_attention_decode_hd128": [vp, sz, vp, vp, sz, sz, sz, sz, f32, vp, sz],
+        "rnb_b200_attention_decode_cached": [sz, vp, sz, vp, vp, sz, sz, sz, sz, sz, f32, vp, sz],
+        "rnb_b200_clear_decode_attention_kv_cache": [],
+        "rnb_b200_attention_prefill_flash_hd128": [vp, vp, vp, sz, sz, sz, sz, f32, vp],
+        "rnb_b200_dense_attention_qkv_rope_hd128_decode": [
+            vp, sz, u32, vp, sz, u32, vp, sz, u32, sz, sz, sz, sz, sz, f32, sz, vp, vp, vp, vp],
+        "rnb_b200_dense_q4k_silu_ffn_batch": [vp, sz, vp, sz, vp, sz, u32, sz, sz, sz, vp, vp],
+        "rnb_b200_moe_route_topk_f32": [vp, sz, vp, sz, sz, sz, i32, i32, f32, f32, vp, vp, vp],
+        "rnb_b200_router_logits_f32": [vp, sz, sz, vp, vp],
+        "rnb_b200_qwen35_sparse_experts": [vp, vp, vp, sz, sz, vp, sz, u32, sz, sz, vp, vp],
+        "rnb_b200_qwen35_register_moe_layer": [vp, sz, vp, sz, vp, sz, u32, sz, sz, vp],
+        "rnb_b200_rms_norm_rows_f32": [vp, vp, sz, sz, f32, vp],
+        "rnb_b200_rope_f32_inplace": [vp, sz, sz, sz, sz, f32, i32],
+        "rnb_b200_activation_mul_f32_inplace": [vp, vp, sz],
+        "rnb_b200_evaluate_expert_bundle_admission": [vp],
+        "rnb_b200_decoder_create": [vp, vp],
+        "rnb_b200_decoder_set_layer": [vp, i32, vp],
+        "rnb_b200_decoder_set_globals": [vp, QWeight, vp, QWeight],
+        "rnb_b200_decoder_fill_synthetic": [vp, u64, f32],
+        "rnb_b200_decoder_fill_kv_synthetic": [vp, i32, u64],
+        "rnb_b200_decoder_step": [vp, u32, i32, vp, vp],
+        "rnb_b200_decoder_step_dev": [vp, i32, i32],
+        "rnb_b200_decoder_sync": [vp],
+        "rnb_b200_decoder_read_kv": [vp, i32, i32, vp, vp],
+        "rnb_b200_decoder_read_hidden": [vp, vp],
+        "rnb_b200_decoder_read_expert_ids": [vp, i32, vp],
+        "rnb_b200_decoder_stats": [vp, vp, vp, vp],
+        "rnb_b200_nccl_unique_id": [vp],
+        "rnb_b200_decoder_attach_nccl": [vp, vp],
+        "rnb_b200_dev_quantize_q8k": [vp, sz, sz, vp, vp, vp],
+        "rnb_b200_dev_gemv": [u32, vp, sz, sz, vp, vp, i32, vp],
+        "rnb_b200_dev_flash_decode": [vp, vp, vp, sz, sz, sz, f32, vp, sz, i32, vp, vp],
+        "rnb_b200_flash_decode_default_chunks": [sz, sz],
+        "rnb_b200_dev_error_flag": [vp],
+    }
+    for name, args in sig.items():
+        fn = getattr(L, name)
+        fn.argtypes = args
+        fn.restype = i32
+    L.rnb_b200_decoder_destroy.argtypes = [vp]
+    L.rnb_b200_decoder_destroy.restype = None
+    L.rnb_b200_decoder_stream.argtypes = [vp]
+    L.rnb_b200_decoder_stream.restype = vp
+    L.rnb_b200_resident_limit_for.argtypes = [u64, u64]
+    L.rnb_b200_resident_limit_for.restype = u64
+    L.rnb_b200_dev_q8k_bytes.argtypes = [sz]
+    L.rnb_b200_dev_q8k_bytes.restype = sz
+    L.rnb_b200_flash_decode_scratch_bytes.argtypes = [sz, i32]
+    L.rnb_b200_flash_decode_scratch_bytes.restype = sz
+    _lib = L
+    return L
+
+
+def check(status: int) -> None:
+    if status != OK:
+        raise RnbError(status, load().rnb_b200_last_error().decode("utf-8", "replace"))

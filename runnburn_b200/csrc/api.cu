@@ -1,0 +1,983 @@
+// C ABI of the operator library (declarations and reference citations: include/rnb_b200.h).
+// Host logic only: validation with the reference's messages, residency, staging, launches.
+#include <math.h>
+
+#include <algorithm>
+
+#include "launch.hpp"
+#include "prefill.cuh"
+
+namespace rnb {
+
+thread_local std::string g_last_error;
+
+State &state() {
+    static State s;
+    return s;
+}
+std::mutex &state_mutex() {
+    static std::mutex m;
+    return m;
+}
+bool use_pdl() {
+    static int v = -1;
+    if (v < 0) {
+        const char *e = getenv("RNB_B200_PDL");
+        v = (e && *e && strcmp(e, "0") != 0) ? 1 : 0;
+    }
+    return v == 1;
+}
+int gemv_kernel_setup() {
+    static bool done = false;
+    if (done) return RNB_B200_OK;
+    RNB_CU(cudaFuncSetAttribute(gemv_tile_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+    RNB_CU(cudaFuncSetAttribute(gemv_tile_kernel_1, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+    done = true;
+    return RNB_B200_OK;
+}
+
+// ---------------------------------------------------------------------------------------------
+// State
+// ---------------------------------------------------------------------------------------------
+int State::open() {
+    if (is_open) return RNB_B200_OK;
+    int n = 0;
+    cudaError_t e = cudaGetDeviceCount(&n);
+    if (e != cudaSuccess || n == 0) {
+        cudaGetLastError();
+        return fail(RNB_B200_CUDA_ERROR, "no usable CUDA device (%s); this library has no CPU fallback",
+                    e == cudaSuccess ? "device count is 0" : cudaGetErrorString(e));
+    }
+    const char *env = getenv("RNB_CUDA_DEVICE");
+    device = env ? atoi(env) : 0;
+    if (device < 0 || device >= n) return fail(RNB_B200_VALIDATION_FAILED, "RNB_CUDA_DEVICE=%d out of range (%d devices)", device, n);
+    RNB_CU(cudaSetDevice(device));
+    cudaDeviceProp prop;
+    RNB_CU(cudaGetDeviceProperties(&prop, device));
+    sm_count = prop.multiProcessorCount;
+    if (prop.major < 10)
+        return fail(RNB_B200_UNSUPPORTED, "device %d is sm_%d%d; this library is built for sm_100a only", device,
+                    prop.major, prop.minor);
+    size_t free_b = 0;
+    RNB_CU(cudaMemGetInfo(&free_b, &total));
+    resident_limit = limit_override ? limit_override : (size_t)resident_limit_for(total, free_b);
+    RNB_CU(cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking));
+    RNB_CU(cudaMalloc((void **)&dev_error, sizeof(int)));
+    RNB_CU(cudaMemsetAsync(dev_error, 0, sizeof(int), stream));
+    memset(&ctr, 0, sizeof(ctr));
+    is_open = true;
+    return RNB_B200_OK;
+}
+
+void State::evict_all(bool include_pinned) {
+    for (auto it = resident.begin(); it != resident.end();) {
+        if (include_pinned || !it->second.pinned) {
+            cudaFree(it->second.dev);
+            resident_bytes -= it->second.bytes;
+            ctr.evictions++;
+            it = resident.erase(it);
+        } else {
+            ++it;
+        }
+    }
+}
+
+void State::close() {
+    if (!is_open) return;
+    cudaSetDevice(device);
+    cudaStreamSynchronize(stream);
+    evict_all(true);
+    for (auto &kv : kv_mirrors) {
+        cudaFree(kv.second.dk);
+        cudaFree(kv.second.dv);
+    }
+    kv_mirrors.clear();
+    for (auto &r : registered) cudaHostUnregister(r.first);
+    registered.clear();
+    DevBuf *bufs[] = {&in_f32, &xq, &xq2, &out_f32, &mid_a, &mid_b, &mid_c, &jobs, &partials, &misc, &transient};
+    for (DevBuf *b : bufs) b->release();
+    pin_in.release();
+    pin_out.release();
+    pin_jobs.release();
+    cudaFree(dev_error);
+    dev_error = nullptr;
+    cudaStreamDestroy(stream);
+    stream = nullptr;
+    is_open = false;
+}
+
+// Resident lookup: exact (ptr,len) hit, or a slice of a larger resident range (stacked expert
+// tensors registered once); miss -> budget check, LRU eviction, allocate, upload.  Over-budget
+// weights are uploaded into a transient buffer that the next transient upload overwrites
+// (crates/rnb-backend/cuda/src/runtime/state/q4k_cache.rs:757-851).
+int State::resident_ptr(const uint8_t *host, size_t len, bool pin, const uint8_t **dev_out) {
+    ctr.lookups++;
+    epoch++;
+    auto it = resident.upper_bound(std::make_pair((const void *)host, (size_t)-1));
+    if (it != resident.begin()) {
+        --it;
+        const uint8_t *base = (const uint8_t *)it->first.first;
+        if (host >= base && host + len <= base + it->first.second) {
+            it->second.epoch = epoch;
+            if (pin) it->second.pinned = true;
+            ctr.hits++;
+            *dev_out = it->second.dev + (host - base);
+            return RNB_B200_OK;
+        }
+    }
+    ctr.misses++;
+    if (len > resident_limit) {
+        if (pin) return fail(RNB_B200_OUT_OF_MEMORY, "resident weight of %zu bytes exceeds the residency limit %zu", len, resident_limit);
+        RNB_TRY(transient.ensure(len + 16));
+        RNB_CU(cudaMemcpyAsync(transient.p, host, len, cudaMemcpyHostToDevice, stream));
+        ctr.transient_uploads++;
+        ctr.h2d_bytes += len;
+        *dev_out = transient.as<uint8_t>();
+        return RNB_B200_OK;
+    }
+    auto evict_lru = [&]() -> bool {
+        auto victim = resident.end();
+        for (auto j = resident.begin(); j != resident.end(); ++j)
+            if (!j->second.pinned && (victim == resident.end() || j->second.epoch < victim->second.epoch)) victim = j;
+        if (victim == resident.end()) return false;
+        cudaFree(victim->second.dev);
+        resident_bytes -= victim->second.bytes;
+        ctr.evictions++;
+        resident.erase(victim);
+        return true;
+    };
+    while (resident_bytes + len > resident_limit)
+        if (!evict_lru()) break;
+    if (resident_bytes + len > resident_limit) {
+        if (pin) return fail(RNB_B200_OUT_OF_MEMORY, "no room to pin %zu bytes (resident %zu, limit %zu)", len, resident_bytes, resident_limit);
+        RNB_TRY(transient.ensure(len + 16));
+        RNB_CU(cudaMemcpyAsync(transient.p, host, len, cudaMemcpyHostToDevice, stream));
+        ctr.transient_uploads++;
+        ctr.h2d_bytes += len;
+        *dev_out = transient.as<uint8_t>();
+        return RNB_B200_OK;
+    }
+    uint8_t *dev = nullptr;
+    for (;;) {
+        cudaError_t e = cudaSuccess;
+        if (fail_next_allocs > 0) {  // host-side fault injection: behave as if the driver said OOM
+            fail_next_allocs--;
+            e = cudaErrorMemoryAllocation;
+        } else {
+            e = cudaMalloc((void **)&dev, len + 16);  // +16: slack for the unaligned tile readers
+        }
+        if (e == cudaSuccess) break;
+        cudaGetLastError();
+        if (e != cudaErrorMemoryAllocation || !evict_lru()) return fail_cuda(e, "cudaMalloc(resident weight)");
+    }
+    cudaError_t e = cudaMemcpyAsync(dev, host, len, cudaMemcpyHostToDevice, stream);
+    if (e != cudaSuccess) {
+        cudaFree(dev);
+        return fail_cuda(e, "cudaMemcpyAsync(resident weight)");
+    }
+    Resident r;
+    r.dev = dev;
+    r.bytes = len;
+    r.epoch = epoch;
+    r.pinned = pin;
+    resident[std::make_pair((const void *)host, len)] = r;
+    resident_bytes += len;
+    ctr.uploads++;
+    ctr.upload_bytes += len;
+    ctr.h2d_bytes += len;
+    *dev_out = dev;
+    return RNB_B200_OK;
+}
+
+int State::h2d(void *dst, const void *src, size_t n, PinnedBuf &stage, size_t stage_off) {
+    if (n == 0) return RNB_B200_OK;
+    RNB_TRY(stage.ensure(stage_off + n));
+    memcpy(stage.as<uint8_t>() + stage_off, src, n);
+    RNB_CU(cudaMemcpyAsync(dst, stage.as<uint8_t>() + stage_off, n, cudaMemcpyHostToDevice, stream));
+    ctr.h2d_bytes += n;
+    return RNB_B200_OK;
+}
+
+int State::check_dev_error() {
+    int flag = 0;
+    RNB_CU(cudaMemcpyAsync(&flag, dev_error, sizeof(int), cudaMemcpyDeviceToHost, stream));
+    RNB_CU(cudaStreamSynchronize(stream));
+    if (flag != 0) {
+        cudaMemsetAsync(dev_error, 0, sizeof(int), stream);
+        return fail(RNB_B200_DEVICE_FAULT_FLAG, "device kernel reported error flag %d (%s)", flag,
+                    flag == DEV_ERR_MBAR_TIMEOUT ? "bounded mbarrier wait gave up" : "inconsistent job table");
+    }
+    return RNB_B200_OK;
+}
+
+// D2H of results through pinned staging, then synchronise and surface device error flags.
+static int finish_to_host(State &st, const void *dev_src, void *host_dst, size_t n) {
+    RNB_TRY(st.pin_out.ensure(n + 16));
+    RNB_CU(cudaMemcpyAsync(st.pin_out.p, dev_src, n, cudaMemcpyDeviceToHost, st.stream));
+    int *flag = reinterpret_cast<int *>(st.pin_out.as<uint8_t>() + ((n + 3) & ~(size_t)3));
+    RNB_CU(cudaMemcpyAsync(flag, st.dev_error, sizeof(int), cudaMemcpyDeviceToHost, st.stream));
+    RNB_CU(cudaStreamSynchronize(st.stream));
+    st.ctr.d2h_bytes += n;
+    if (*flag != 0) {
+        cudaMemsetAsync(st.dev_error, 0, sizeof(int), st.stream);
+        return fail(RNB_B200_DEVICE_FAULT_FLAG, "device kernel reported error flag %d", *flag);
+    }
+    memcpy(host_dst, st.pin_out.p, n);
+    return RNB_B200_OK;
+}
+
+struct Locked {
+    std::lock_guard<std::mutex> g;
+    State &st;
+    Locked() : g(state_mutex()), st(state()) {}
+};
+
+static const char *type_name(int t) {
+    return t == TYPE_Q4_K ? "Q4_K" : t == TYPE_Q6_K ? "Q6_K" : t == TYPE_Q8_0 ? "Q8_0" : "?";
+}
+
+// Shape checks with the reference's wording (api/quant_api.rs:189-206).
+static int validate_gemv(int type, size_t weights_len, size_t rows, size_t cols, size_t input_len,
+                         size_t seq, size_t output_len, bool check_input) {
+    const size_t blk = type == TYPE_Q8_0 ? 32 : 256;
+    if (cols == 0 || cols % blk != 0)
+        return fail(RNB_B200_VALIDATION_FAILED, "%s cols must be divisible by %zu, got %zu", type_name(type), blk, cols);
+    const size_t expect = rows * row_bytes_of(type, cols);
+    if (weights_len != expect)
+        return fail(RNB_B200_VALIDATION_FAILED, "%s weight byte mismatch: got %zu, expected %zu", type_name(type), weights_len, expect);
+    if (check_input && input_len != cols * seq)
+        return fail(RNB_B200_VALIDATION_FAILED, "%s input length mismatch: got %zu, expected %zu", type_name(type), input_len, cols * seq);
+    if (output_len < rows * seq)
+        return fail(RNB_B200_VALIDATION_FAILED, "%s output too small: got %zu, expected >= %zu", type_name(type), output_len, rows * seq);
+    if (rows == 0) return fail(RNB_B200_VALIDATION_FAILED, "%s rows must be non-zero", type_name(type));
+    return RNB_B200_OK;
+}
+
+// Shared body of the host-buffer matvec entry points.
+static int gemv_host(int type, const uint8_t *weights, size_t weights_len, size_t rows, size_t cols,
+                     const float *input, size_t input_len, uint64_t input_dev, size_t seq,
+                     float *output, size_t output_len, uint32_t *argmax_idx, float *argmax_val) {
+    RNB_TRY(validate_gemv(type, weights_len, rows, cols, input_len, seq, argmax_idx ? rows * seq : output_len,
+                          input_dev == 0));
+    if (!weights || (!input && !input_dev)) return fail(RNB_B200_VALIDATION_FAILED, "null pointer argument");
+    Locked L;
+    State &st = L.st;
+    RNB_TRY(st.open());
+    RNB_CU(cudaSetDevice(st.device));
+    const uint8_t *w_dev = nullptr;
+    RNB_TRY(st.resident_ptr(weights, weights_len, false, &w_dev));
+    const float *x_dev = reinterpret_cast<const float *>(input_dev);
+    if (!input_dev) {
+        RNB_TRY(st.in_f32.ensure(cols * seq * sizeof(float)));
+        RNB_TRY(st.h2d(st.in_f32.p, input, cols * seq * sizeof(float), st.pin_in));
+        x_dev = st.in_f32.as<float>();
+    }
+    const void *act = x_dev;
+    size_t x_stride = cols * sizeof(float);
+    if (type != TYPE_Q8_0) {
+        RNB_TRY(st.xq.ensure(q8k_dev_bytes(cols) * seq));
+        RNB_TRY(launch_quantize_q8k(st.stream, x_dev, cols, seq, st.xq.as<uint8_t>(), nullptr));
+        act = st.xq.p;
+        x_stride = q8k_dev_bytes(cols);
+    }
+    RNB_TRY(st.out_f32.ensure(rows * seq * sizeof(float) + 16));
+    GemvJob job = make_job(type, w_dev, act, st.out_f32.as<float>(), nullptr, rows, cols, 0, st.sm_count,
+                           (int)seq, x_stride);
+    RNB_TRY(launch_gemv_one(st.stream, job, cols, st.dev_error));
+    if (argmax_idx) {
+        RNB_TRY(st.misc.ensure(16));
+        RNB_CU(launch_k(argmax_last_kernel, dim3(1), dim3(1024), 0, st.stream, (const float *)st.out_f32.p,
+                        (int)rows, st.misc.as<uint32_t>(), st.misc.as<float>() + 1));
+        uint32_t pair[2];
+        RNB_TRY(finish_to_host(st, st.misc.p, pair, 8));
+        *argmax_idx = pair[0];
+        if (argmax_val) memcpy(argmax_val, &pair[1], 4);
+        return RNB_B200_OK;
+    }
+    return finish_to_host(st, st.out_f32.p, output, rows * seq * sizeof(float));
+}
+
+// Batched (prefill) matvec: each weight tile is staged once and applied to every token's
+// Q8_K activations, so results are the ones rnb-cpu's gemv_quantized gives for seq_len > 1
+// (crates/rnb-cpu/src/gemm/quant_gemv.rs:1145-1182), seq-major.
+static int prefill_gemm_host(int type, const uint8_t *w, size_t wl, size_t rows, size_t cols, const float *in,
+                             size_t seq, float *out, size_t ol) {
+    if (seq == 0) return fail(RNB_B200_VALIDATION_FAILED, "%s batch needs at least one token", type_name(type));
+    return gemv_host(type, w, wl, rows, cols, in, seq * cols, 0, seq, out, ol, nullptr, nullptr);
+}
+
+}  // namespace rnb
+
+using namespace rnb;
+
+// =============================================================================================
+// extern "C"
+// =============================================================================================
+extern "C" {
+
+const char *rnb_b200_last_error(void) { return g_last_error.c_str(); }
+
+int rnb_b200_open(void) {
+    Locked L;
+    return L.st.open();
+}
+void rnb_b200_close(void) {
+    Locked L;
+    L.st.close();
+}
+int rnb_b200_cuda_memory_info(size_t *free_bytes, size_t *total_bytes) {
+    Locked L;
+    RNB_TRY(L.st.open());
+    RNB_CU(cudaSetDevice(L.st.device));
+    size_t f = 0, t = 0;
+    RNB_CU(cudaMemGetInfo(&f, &t));
+    if (free_bytes) *free_bytes = f;
+    if (total_bytes) *total_bytes = t;
+    return RNB_B200_OK;
+}
+int rnb_b200_device_sm_count(int *sm_count) {
+    Locked L;
+    RNB_TRY(L.st.open());
+    if (sm_count) *sm_count = L.st.sm_count;
+    return RNB_B200_OK;
+}
+int rnb_b200_cuda_cache_snapshot(rnb_b200_cache_snapshot *out) {
+    if (!out) return fail(RNB_B200_VALIDATION_FAILED, "null snapshot pointer");
+    Locked L;
+    *out = L.st.ctr;
+    out->resident_entries = L.st.resident.size();
+    out->resident_bytes = L.st.resident_bytes;
+    out->resident_limit_bytes = L.st.resident_limit;
+    return RNB_B200_OK;
+}
+int rnb_b200_clear_q4k_cache(void) {
+    Locked L;
+    if (!L.st.is_open) return RNB_B200_OK;
+    RNB_CU(cudaSetDevice(L.st.device));
+    RNB_CU(cudaStreamSynchronize(L.st.stream));
+    L.st.evict_all(true);
+    return RNB_B200_OK;
+}
+int rnb_b200_reset_state_for_engine_init(void) {
+    Locked L;
+    if (!L.st.is_open) return RNB_B200_OK;
+    RNB_CU(cudaSetDevice(L.st.device));
+    RNB_CU(cudaStreamSynchronize(L.st.stream));
+    L.st.evict_all(true);
+    for (auto &kv : L.st.kv_mirrors) {
+        cudaFree(kv.second.dk);
+        cudaFree(kv.second.dv);
+    }
+    L.st.kv_mirrors.clear();
+    memset(&L.st.ctr, 0, sizeof(L.st.ctr));
+    return RNB_B200_OK;
+}
+int rnb_b200_prewarm_q4k_weights(const uint8_t *const *slices, const size_t *lens, size_t n, size_t *n_resident) {
+    if (n && (!slices || !lens)) return fail(RNB_B200_VALIDATION_FAILED, "null slice table");
+    Locked L;
+    RNB_TRY(L.st.open());
+    RNB_CU(cudaSetDevice(L.st.device));
+    size_t ok = 0;
+    for (size_t i = 0; i < n; i++) {
+        const uint8_t *dev = nullptr;
+        const uint64_t before = L.st.ctr.transient_uploads;
+        RNB_TRY(L.st.resident_ptr(slices[i], lens[i], false, &dev));
+        if (L.st.ctr.transient_uploads == before) ok++;
+    }
+    RNB_CU(cudaStreamSynchronize(L.st.stream));
+    if (n_resident) *n_resident = ok;
+    return RNB_B200_OK;
+}
+int rnb_b200_set_resident_limit(size_t bytes) {
+    Locked L;
+    L.st.limit_override = bytes;
+    if (L.st.is_open) {
+        if (bytes) {
+            L.st.resident_limit = bytes;
+        } else {
+            size_t f = 0, t = 0;
+            RNB_CU(cudaMemGetInfo(&f, &t));
+            L.st.resident_limit = (size_t)resident_limit_for(t, f + L.st.resident_bytes);
+        }
+    }
+    return RNB_B200_OK;
+}
+int rnb_b200_register_host_range(const void *ptr, size_t len) {
+    if (!ptr || !len) return fail(RNB_B200_VALIDATION_FAILED, "empty host range");
+    Locked L;
+    RNB_TRY(L.st.open());
+    RNB_CU(cudaSetDevice(L.st.device));
+    // only whole pages strictly inside the range can be pinned
+    const uintptr_t page = 4096, b = ((uintptr_t)ptr + page - 1) & ~(page - 1), e = ((uintptr_t)ptr + len) & ~(page - 1);
+    if (e <= b) return RNB_B200_OK;
+    cudaError_t err = cudaHostRegister((void *)b, e - b, cudaHostRegisterReadOnly);
+    if (err == cudaErrorNotSupported || err == cudaErrorInvalidValue) {
+        cudaGetLastError();
+        err = cudaHostRegister((void *)b, e - b, cudaHostRegisterDefault);
+    }
+    if (err == cudaErrorHostMemoryAlreadyRegistered) {
+        cudaGetLastError();
+        return RNB_B200_OK;
+    }
+    if (err != cudaSuccess) return fail_cuda(err, "cudaHostRegister");
+    L.st.registered.push_back(std::make_pair((void *)b, (size_t)(e - b)));
+    return RNB_B200_OK;
+}
+int rnb_b200_clear_host_registered_ranges(void) {
+    Locked L;
+    if (!L.st.is_open) return RNB_B200_OK;
+    RNB_CU(cudaSetDevice(L.st.device));
+    RNB_CU(cudaStreamSynchronize(L.st.stream));
+    for (auto &r : L.st.registered) cudaHostUnregister(r.first);
+    L.st.registered.clear();
+    return RNB_B200_OK;
+}
+
+int rnb_b200_quantize_q8k(const float *input, size_t n, void *blocks_out) {
+    if (n % 256 != 0) return fail(RNB_B200_VALIDATION_FAILED, "Q8_K input length must be divisible by 256, got %zu", n);
+    if (n == 0) return RNB_B200_OK;
+    if (!input || !blocks_out) return fail(RNB_B200_VALIDATION_FAILED, "null pointer argument");
+    Locked L;
+    State &st = L.st;
+    RNB_TRY(st.open());
+    RNB_CU(cudaSetDevice(st.device));
+    RNB_TRY(st.in_f32.ensure(n * sizeof(float)));
+    RNB_TRY(st.h2d(st.in_f32.p, input, n * sizeof(float), st.pin_in));
+    const size_t out_bytes = n / 256 * Q8K_BYTES;
+    RNB_TRY(st.out_f32.ensure(out_bytes));
+    RNB_TRY(launch_quantize_q8k(st.stream, st.in_f32.as<float>(), n, 1, nullptr, st.out_f32.as<uint8_t>()));
+    return finish_to_host(st, st.out_f32.p, blocks_out, out_bytes);
+}
+
+int rnb_b200_q4k_gemv(const uint8_t *w, size_t wl, size_t rows, size_t cols, const float *in, size_t il, float *out, size_t ol) {
+    return gemv_host(TYPE_Q4_K, w, wl, rows, cols, in, il, 0, 1, out, ol, nullptr, nullptr);
+}
+int rnb_b200_q6k_gemv(const uint8_t *w, size_t wl, size_t rows, size_t cols, const float *in, size_t il, float *out, size_t ol) {
+    return gemv_host(TYPE_Q6_K, w, wl, rows, cols, in, il, 0, 1, out, ol, nullptr, nullptr);
+}
+int rnb_b200_q8_0_gemv(const uint8_t *w, size_t wl, size_t rows, size_t cols, const float *in, size_t il, float *out, size_t ol) {
+    return gemv_host(TYPE_Q8_0, w, wl, rows, cols, in, il, 0, 1, out, ol, nullptr, nullptr);
+}
+int rnb_b200_q4k_gemv_with_device_input(const uint8_t *w, size_t wl, size_t rows, size_t cols, uint64_t in_dev, float *out, size_t ol) {
+    if (!in_dev) return fail(RNB_B200_VALIDATION_FAILED, "Q4_K device input pointer is null");
+    return gemv_host(TYPE_Q4_K, w, wl, rows, cols, nullptr, 0, in_dev, 1, out, ol, nullptr, nullptr);
+}
+int rnb_b200_q6k_gemv_with_device_input(const uint8_t *w, size_t wl, size_t rows, size_t cols, uint64_t in_dev, float *out, size_t ol) {
+    if (!in_dev) return fail(RNB_B200_VALIDATION_FAILED, "Q6_K device input pointer is null");
+    return gemv_host(TYPE_Q6_K, w, wl, rows, cols, nullptr, 0, in_dev, 1, out, ol, nullptr, nullptr);
+}
+int rnb_b200_q6k_gemv_argmax(const uint8_t *w, size_t wl, size_t rows, size_t cols, const float *in, size_t il, uint32_t *idx, float *val) {
+    if (!idx) return fail(RNB_B200_VALIDATION_FAILED, "null index output");
+    return gemv_host(TYPE_Q6_K, w, wl, rows, cols, in, il, 0, 1, nullptr, 0, idx, val);
+}
+int rnb_b200_q4k_gemv_batch(const uint8_t *w, size_t wl, size_t rows, size_t cols, const float *in, size_t il, float *out, size_t ol) {
+    if (cols == 0 || il % cols != 0) return fail(RNB_B200_VALIDATION_FAILED, "Q4_K batch input length %zu is not a multiple of cols %zu", il, cols);
+    return prefill_gemm_host(TYPE_Q4_K, w, wl, rows, cols, in, il / cols, out, ol);
+}
+int rnb_b200_q6k_gemv_batch(const uint8_t *w, size_t wl, size_t rows, size_t cols, const float *in, size_t il, float *out, size_t ol) {
+    if (cols == 0 || il % cols != 0) return fail(RNB_B200_VALIDATION_FAILED, "Q6_K batch input length %zu is not a multiple of cols %zu", il, cols);
+    return prefill_gemm_host(TYPE_Q6_K, w, wl, rows, cols, in, il / cols, out, ol);
+}
+
+// ---- attention --------------------------------------------------------------------------------
+static int validate_attn(size_t q_len, size_t kv_elems, size_t kv_len, size_t heads, size_t kv_heads, size_t head_dim, size_t out_len) {
+    if (head_dim != 128) return fail(RNB_B200_UNSUPPORTED, "decode attention supports head_dim 128 only, got %zu", head_dim);
+    if (kv_heads == 0 || heads == 0 || heads % kv_heads != 0)
+        return fail(RNB_B200_VALIDATION_FAILED, "attention: num_heads(%zu) must be a multiple of num_kv_heads(%zu)", heads, kv_heads);
+    if (q_len != heads * head_dim) return fail(RNB_B200_VALIDATION_FAILED, "attention q length mismatch: got %zu, expected %zu", q_len, heads * head_dim);
+    if (kv_elems < kv_len * kv_heads * head_dim)
+        return fail(RNB_B200_VALIDATION_FAILED, "attention kv length mismatch: got %zu, expected >= %zu", kv_elems, kv_len * kv_heads * head_dim);
+    if (out_len < heads * head_dim) return fail(RNB_B200_VALIDATION_FAILED, "attention output too small: got %zu, expected >= %zu", out_len, heads * head_dim);
+    if (kv_len == 0) return fail(RNB_B200_VALIDATION_FAILED, "attention kv_len must be non-zero");
+    return RNB_B200_OK;
+}
+
+static int attention_run(State &st, const uint16_t *k_dev, const uint16_t *v_dev, const float *q, size_t kv_len,
+                         size_t heads, size_t kv_heads, float scale, float *out) {
+    RNB_TRY(st.in_f32.ensure(heads * HD * sizeof(float)));
+    RNB_TRY(st.h2d(st.in_f32.p, q, heads * HD * sizeof(float), st.pin_in));
+    const int n_chunks = flash_decode_default_chunks(kv_len, kv_heads, st.sm_count);
+    RNB_TRY(st.partials.ensure(flash_decode_scratch_bytes(heads, n_chunks)));
+    RNB_TRY(st.out_f32.ensure(heads * HD * sizeof(float)));
+    RNB_TRY(launch_flash_decode(st.stream, st.in_f32.as<float>(), k_dev, v_dev, nullptr, (int)kv_len, (int)heads,
+                                (int)kv_heads, scale, st.partials.as<float>(), n_chunks, st.out_f32.as<float>()));
+    return finish_to_host(st, st.out_f32.p, out, heads * HD * sizeof(float));
+}
+
+int rnb_b200_attention_decode_hd128(const float *q, size_t q_len, const uint16_t *k, const uint16_t *v, size_t kv_elems,
+                                    size_t kv_len, size_t heads, size_t kv_heads, float scale, float *out, size_t out_len) {
+    RNB_TRY(validate_attn(q_len, kv_elems, kv_len, heads, kv_heads, 128, out_len));
+    if (!q || !k || !v || !out) return fail(RNB_B200_VALIDATION_FAILED, "null pointer argument");
+    Locked L;
+    State &st = L.st;
+    RNB_TRY(st.open());
+    RNB_CU(cudaSetDevice(st.device));
+    const size_t bytes = kv_len * kv_heads * HD * sizeof(uint16_t);
+    RNB_TRY(st.mid_a.ensure(bytes));
+    RNB_TRY(st.mid_b.ensure(bytes));
+    RNB_CU(cudaMemcpyAsync(st.mid_a.p, k, bytes, cudaMemcpyHostToDevice, st.stream));
+    RNB_CU(cudaMemcpyAsync(st.mid_b.p, v, bytes, cudaMemcpyHostToDevice, st.stream));
+    st.ctr.h2d_bytes += 2 * bytes;
+    return attention_run(st, st.mid_a.as<uint16_t>(), st.mid_b.as<uint16_t>(), q, kv_len, heads, kv_heads, scale, out);
+}
+
+int rnb_b200_attention_decode_cached(size_t layer, const float *q, size_t q_len, const uint16_t *k, const uint16_t *v,
+                                     size_t kv_elems, size_t kv_len, size_t heads, size_t kv_heads, size_t head_dim,
+                                     float scale, float *out, size_t out_len) {
+    RNB_TRY(validate_attn(q_len, kv_elems, kv_len, heads, kv_heads, head_dim, out_len));
+    if (!q || !k || !v || !out) return fail(RNB_B200_VALIDATION_FAILED, "null pointer argument");
+    Locked L;
+    State &st = L.st;
+    RNB_TRY(st.open());
+    RNB_CU(cudaSetDevice(st.device));
+    KvMirror &m = st.kv_mirrors[layer];
+    const size_t kv_dim = kv_heads * HD;
+    const bool same = m.host_k == k && m.host_v == v && m.kv_dim == kv_dim && m.rows_have <= kv_len;
+    if (!same) m.rows_have = 0;
+    if (m.rows_cap < kv_len || m.kv_dim != kv_dim) {
+        // grow geometrically; old rows are re-uploaded from the host copy (the cache is
+        // append-only and re-uploadable: runtime/attention.rs:3973-3990)
+        size_t cap = std::max<size_t>(kv_len, m.rows_cap * 2);
+        cap = std::max<size_t>(cap, 256);
+        uint16_t *nk = nullptr, *nv = nullptr;
+        RNB_CU(cudaMalloc((void **)&nk, cap * kv_dim * 2));
+        cudaError_t e = cudaMalloc((void **)&nv, cap * kv_dim * 2);
+        if (e != cudaSuccess) {
+            cudaFree(nk);
+            return fail_cuda(e, "cudaMalloc(kv mirror)");
+        }
+        if (m.rows_have && m.kv_dim == kv_dim) {
+            RNB_CU(cudaMemcpyAsync(nk, m.dk, m.rows_have * kv_dim * 2, cudaMemcpyDeviceToDevice, st.stream));
+            RNB_CU(cudaMemcpyAsync(nv, m.dv, m.rows_have * kv_dim * 2, cudaMemcpyDeviceToDevice, st.stream));
+            RNB_CU(cudaStreamSynchronize(st.stream));
+        } else {
+            m.rows_have = 0;
+        }
+        cudaFree(m.dk);
+        cudaFree(m.dv);
+        m.dk = nk;
+        m.dv = nv;
+        m.rows_cap = cap;
+        m.kv_dim = kv_dim;
+    }
+    m.host_k = k;
+    m.host_v = v;
+    if (kv_len > m.rows_have) {
+        const size_t off = m.rows_have * kv_dim, n = (kv_len - m.rows_have) * kv_dim * 2;
+        RNB_CU(cudaMemcpyAsync(m.dk + off, k + off, n, cudaMemcpyHostToDevice, st.stream));
+        RNB_CU(cudaMemcpyAsync(m.dv + off, v + off, n, cudaMemcpyHostToDevice, st.stream));
+        st.ctr.h2d_bytes += 2 * n;
+        m.rows_have = kv_len;
+    }
+    return attention_run(st, m.dk, m.dv, q, kv_len, heads, kv_heads, scale, out);
+}
+
+int rnb_b200_clear_decode_attention_kv_cache(void) {
+    Locked L;
+    if (!L.st.is_open) return RNB_B200_OK;
+    RNB_CU(cudaSetDevice(L.st.device));
+    RNB_CU(cudaStreamSynchronize(L.st.stream));
+    for (auto &kv : L.st.kv_mirrors) {
+        cudaFree(kv.second.dk);
+        cudaFree(kv.second.dv);
+    }
+    L.st.kv_mirrors.clear();
+    return RNB_B200_OK;
+}
+
+int rnb_b200_attention_prefill_flash_hd128(const float *q, const float *k, const float *v, size_t seq_len, size_t kv_len,
+                                           size_t heads, size_t kv_heads, float scale, float *out) {
+    if (kv_heads == 0 || heads == 0 || heads % kv_heads != 0)
+        return fail(RNB_B200_VALIDATION_FAILED, "attention: num_heads(%zu) must be a multiple of num_kv_heads(%zu)", heads, kv_heads);
+    if (seq_len == 0 || kv_len < seq_len) return fail(RNB_B200_VALIDATION_FAILED, "prefill attention needs 0 < seq_len <= kv_len, got %zu / %zu", seq_len, kv_len);
+    if (!q || !k || !v || !out) return fail(RNB_B200_VALIDATION_FAILED, "null pointer argument");
+    Locked L;
+    State &st = L.st;
+    RNB_TRY(st.open());
+    RNB_CU(cudaSetDevice(st.device));
+    const size_t qb = seq_len * heads * HD * 4, kb = kv_len * kv_heads * HD * 4;
+    RNB_TRY(st.in_f32.ensure(qb));
+    RNB_TRY(st.mid_a.ensure(kb));
+    RNB_TRY(st.mid_b.ensure(kb));
+    RNB_TRY(st.out_f32.ensure(qb));
+    RNB_CU(cudaMemcpyAsync(st.in_f32.p, q, qb, cudaMemcpyHostToDevice, st.stream));
+    RNB_CU(cudaMemcpyAsync(st.mid_a.p, k, kb, cudaMemcpyHostToDevice, st.stream));
+    RNB_CU(cudaMemcpyAsync(st.mid_b.p, v, kb, cudaMemcpyHostToDevice, st.stream));
+    st.ctr.h2d_bytes += qb + 2 * kb;
+    RNB_TRY(launch_prefill_attention_f32kv(st.stream, st.in_f32.as<float>(), st.mid_a.as<float>(), st.mid_b.as<float>(),
+                                           (int)seq_len, (int)kv_len, (int)heads, (int)kv_heads, scale, st.out_f32.as<float>()));
+    return finish_to_host(st, st.out_f32.p, out, qb);
+}
+
+// ---- glue ops -----------------------------------------------------------------------------------
+static void host_rope_row(size_t pos, size_t head_dim, float theta, float *row /* [2][head_dim/2] */) {
+    // CPU angle chain: crates/rnb-cpu/src/kernels/rope.rs:267-293
+    const float theta_scale = powf(theta, -2.0f / (float)head_dim);
+    float angle = (float)pos;
+    for (size_t i = 0; i < head_dim / 2; i++) {
+        row[i] = cosf(angle);
+        row[head_dim / 2 + i] = sinf(angle);
+        angle *= theta_scale;
+    }
+}
+
+int rnb_b200_rms_norm_rows_f32(const float *input, const float *weight, size_t hidden, size_t rows, float eps, float *output) {
+    if (hidden == 0 || hidden % 256 != 0) return fail(RNB_B200_VALIDATION_FAILED, "rms_norm hidden must be divisible by 256, got %zu", hidden);
+    if (!input || !weight || !output) return fail(RNB_B200_VALIDATION_FAILED, "null pointer argument");
+    if (rows == 0) return RNB_B200_OK;
+    Locked L;
+    State &st = L.st;
+    RNB_TRY(st.open());
+    RNB_CU(cudaSetDevice(st.device));
+    RNB_TRY(st.in_f32.ensure(rows * hidden * 4));
+    RNB_TRY(st.mid_a.ensure(hidden * 4));
+    RNB_TRY(st.out_f32.ensure(rows * hidden * 4));
+    RNB_TRY(st.h2d(st.in_f32.p, input, rows * hidden * 4, st.pin_in));
+    RNB_CU(cudaMemcpyAsync(st.mid_a.p, weight, hidden * 4, cudaMemcpyHostToDevice, st.stream));
+    RNB_CU(launch_k(rmsnorm_q8k_kernel<512>, dim3((unsigned)rows), dim3(512), 0, st.stream, (const float *)st.in_f32.p,
+                    (const float *)st.mid_a.p, eps, (int)hidden, st.out_f32.as<float>(), (uint8_t *)nullptr));
+    return finish_to_host(st, st.out_f32.p, output, rows * hidden * 4);
+}
+
+int rnb_b200_rope_f32_inplace(float *data, size_t n, size_t pos_start, size_t head_dim, size_t dim, float theta, int neox) {
+    if (head_dim != 128) return fail(RNB_B200_UNSUPPORTED, "rope supports head_dim 128 only, got %zu", head_dim);
+    if (dim == 0 || dim % head_dim != 0 || n % dim != 0) return fail(RNB_B200_VALIDATION_FAILED, "rope shape mismatch: n=%zu dim=%zu head_dim=%zu", n, dim, head_dim);
+    if (n == 0) return RNB_B200_OK;
+    if (!data) return fail(RNB_B200_VALIDATION_FAILED, "null pointer argument");
+    Locked L;
+    State &st = L.st;
+    RNB_TRY(st.open());
+    RNB_CU(cudaSetDevice(st.device));
+    const size_t seq = n / dim, heads = dim / head_dim;
+    RNB_TRY(st.in_f32.ensure(n * 4));
+    RNB_TRY(st.mid_a.ensure(seq * 128 * 4));
+    RNB_TRY(st.pin_jobs.ensure(seq * 128 * 4));
+    for (size_t t = 0; t < seq; t++) host_rope_row(pos_start + t, 128, theta, st.pin_jobs.as<float>() + t * 128);
+    RNB_CU(cudaMemcpyAsync(st.mid_a.p, st.pin_jobs.p, seq * 128 * 4, cudaMemcpyHostToDevice, st.stream));
+    RNB_TRY(st.h2d(st.in_f32.p, data, n * 4, st.pin_in));
+    for (size_t t = 0; t < seq; t++)  // rotate "q" heads only; no cache writes
+        RNB_CU(launch_k(rope_kv_append_kernel, dim3((unsigned)heads), dim3(64), 0, st.stream, st.in_f32.as<float>() + t * dim,
+                        (const float *)nullptr, (const float *)nullptr, (const float *)st.mid_a.p, (const int *)nullptr, (int)t, 1,
+                        (int)heads, 0, neox, (uint16_t *)nullptr, (uint16_t *)nullptr, (uint16_t *)nullptr, (uint16_t *)nullptr));
+    return finish_to_host(st, st.in_f32.p, data, n * 4);
+}
+
+int rnb_b200_activation_mul_f32_inplace(float *gate, const float *up, size_t n) {
+    if (n % 256 != 0) return fail(RNB_B200_VALIDATION_FAILED, "activation length must be divisible by 256, got %zu", n);
+    if (n == 0) return RNB_B200_OK;
+    if (!gate || !up) return fail(RNB_B200_VALIDATION_FAILED, "null pointer argument");
+    Locked L;
+    State &st = L.st;
+    RNB_TRY(st.open());
+    RNB_CU(cudaSetDevice(st.device));
+    RNB_TRY(st.in_f32.ensure(2 * n * 4));
+    RNB_TRY(st.out_f32.ensure(n * 4));
+    RNB_TRY(st.pin_in.ensure(2 * n * 4));
+    memcpy(st.pin_in.p, gate, n * 4);
+    memcpy(st.pin_in.as<float>() + n, up, n * 4);
+    RNB_CU(cudaMemcpyAsync(st.in_f32.p, st.pin_in.p, 2 * n * 4, cudaMemcpyHostToDevice, st.stream));
+    RNB_CU(launch_k(silu_mul_q8k_kernel, dim3((unsigned)((n / 256 + 3) / 4)), dim3(128), 0, st.stream, (const float *)st.in_f32.p,
+                    (const float *)(st.in_f32.as<float>() + n), (int)n, 1, st.out_f32.as<float>(), (uint8_t *)nullptr));
+    return finish_to_host(st, st.out_f32.p, gate, n * 4);
+}
+
+// ---- fused decode front half ---------------------------------------------------------------------
+int rnb_b200_dense_attention_qkv_rope_hd128_decode(const uint8_t *q_w, size_t q_w_len, uint32_t q_type, const uint8_t *k_w,
+                                                   size_t k_w_len, uint32_t k_type, const uint8_t *v_w, size_t v_w_len,
+                                                   uint32_t v_type, size_t q_rows, size_t kv_rows, size_t n_embd,
+                                                   size_t num_heads, size_t num_kv_heads, float rope_theta, size_t pos_start,
+                                                   const float *input, float *q_rope, uint16_t *k_bits, uint16_t *v_bits) {
+    if (q_rows != num_heads * 128 || kv_rows != num_kv_heads * 128)
+        return fail(RNB_B200_VALIDATION_FAILED, "qkv rope hd128: rows (%zu, %zu) do not match heads (%zu, %zu) x 128", q_rows, kv_rows, num_heads, num_kv_heads);
+    const uint32_t types[3] = {q_type, k_type, v_type};
+    const size_t lens[3] = {q_w_len, k_w_len, v_w_len}, rows[3] = {q_rows, kv_rows, kv_rows};
+    for (int i = 0; i < 3; i++) {
+        if (types[i] != TYPE_Q4_K && types[i] != TYPE_Q6_K) return fail(RNB_B200_UNSUPPORTED, "qkv rope hd128: weight type %u not supported", types[i]);
+        RNB_TRY(validate_gemv((int)types[i], lens[i], rows[i], n_embd, n_embd, 1, rows[i], true));
+    }
+    if (!q_w || !k_w || !v_w || !input || !q_rope || !k_bits || !v_bits) return fail(RNB_B200_VALIDATION_FAILED, "null pointer argument");
+    Locked L;
+    State &st = L.st;
+    RNB_TRY(st.open());
+    RNB_CU(cudaSetDevice(st.device));
+    const uint8_t *wd[3];
+    const uint8_t *wh[3] = {q_w, k_w, v_w};
+    for (int i = 0; i < 3; i++) RNB_TRY(st.resident_ptr(wh[i], lens[i], false, &wd[i]));
+    RNB_TRY(st.in_f32.ensure(n_embd * 4));
+    RNB_TRY(st.h2d(st.in_f32.p, input, n_embd * 4, st.pin_in));
+    RNB_TRY(st.xq.ensure(q8k_dev_bytes(n_embd)));
+    RNB_TRY(launch_quantize_q8k(st.stream, st.in_f32.as<float>(), n_embd, 1, st.xq.as<uint8_t>(), nullptr));
+    const size_t out_floats = q_rows + 2 * kv_rows;
+    RNB_TRY(st.out_f32.ensure(out_floats * 4 + 2 * kv_rows * 2));
+    float *qd = st.out_f32.as<float>(), *kd = qd + q_rows, *vd = kd + kv_rows;
+    uint16_t *kb = reinterpret_cast<uint16_t *>(vd + kv_rows), *vb = kb + kv_rows;
+    GemvJob jobs[3];
+    float *outs[3] = {qd, kd, vd};
+    int tile0 = 0;
+    for (int i = 0; i < 3; i++) {
+        jobs[i] = make_job((int)types[i], wd[i], st.xq.p, outs[i], nullptr, rows[i], n_embd, 0, st.sm_count);
+        jobs[i].tile0 = tile0;
+        tile0 += (jobs[i].rows + jobs[i].rows_per_tile - 1) / jobs[i].rows_per_tile;
+    }
+    RNB_TRY(st.jobs.ensure(sizeof(jobs)));
+    RNB_TRY(st.h2d(st.jobs.p, jobs, sizeof(jobs), st.pin_jobs));
+    RNB_TRY(launch_gemv_jobs(st.stream, jobs, st.jobs.as<GemvJob>(), 3, n_embd, st.dev_error));
+    RNB_TRY(st.mid_a.ensure(128 * 4));
+    host_rope_row(pos_start, 128, rope_theta, st.pin_jobs.as<float>() + 256);
+    RNB_CU(cudaMemcpyAsync(st.mid_a.p, st.pin_jobs.as<float>() + 256, 128 * 4, cudaMemcpyHostToDevice, st.stream));
+    RNB_CU(launch_k(rope_kv_append_kernel, dim3((unsigned)(num_heads + 2 * num_kv_heads)), dim3(64), 0, st.stream, qd,
+                    (const float *)kd, (const float *)vd, (const float *)st.mid_a.p, (const int *)nullptr, 0, 0, (int)num_heads,
+                    (int)num_kv_heads, 0, (uint16_t *)nullptr, (uint16_t *)nullptr, kb, vb));
+    RNB_TRY(st.pin_out.ensure(out_floats * 4 + 2 * kv_rows * 2 + 16));
+    std::vector<uint8_t> tmp(out_floats * 4 + 2 * kv_rows * 2);
+    RNB_TRY(finish_to_host(st, st.out_f32.p, tmp.data(), tmp.size()));
+    memcpy(q_rope, tmp.data(), q_rows * 4);
+    memcpy(k_bits, tmp.data() + out_floats * 4, kv_rows * 2);
+    memcpy(v_bits, tmp.data() + out_floats * 4 + kv_rows * 2, kv_rows * 2);
+    return RNB_B200_OK;
+}
+
+int rnb_b200_dense_q4k_silu_ffn_batch(const uint8_t *gate, size_t gate_len, const uint8_t *up, size_t up_len, const uint8_t *down,
+                                      size_t down_len, uint32_t down_quant, size_t n_ff, size_t n_embd, size_t seq_len,
+                                      const float *input, float *output) {
+    if (down_quant != TYPE_Q4_K && down_quant != TYPE_Q6_K) return fail(RNB_B200_UNSUPPORTED, "dense FFN: down quant %u not supported", down_quant);
+    if (seq_len == 0) return fail(RNB_B200_VALIDATION_FAILED, "dense FFN: seq_len must be non-zero");
+    RNB_TRY(validate_gemv(TYPE_Q4_K, gate_len, n_ff, n_embd, n_embd * seq_len, seq_len, n_ff * seq_len, true));
+    RNB_TRY(validate_gemv(TYPE_Q4_K, up_len, n_ff, n_embd, n_embd * seq_len, seq_len, n_ff * seq_len, true));
+    RNB_TRY(validate_gemv((int)down_quant, down_len, n_embd, n_ff, n_ff * seq_len, seq_len, n_embd * seq_len, true));
+    if (!gate || !up || !down || !input || !output) return fail(RNB_B200_VALIDATION_FAILED, "null pointer argument");
+    Locked L;
+    State &st = L.st;
+    RNB_TRY(st.open());
+    RNB_CU(cudaSetDevice(st.device));
+    const uint8_t *gd, *ud, *dd;
+    RNB_TRY(st.resident_ptr(gate, gate_len, false, &gd));
+    RNB_TRY(st.resident_ptr(up, up_len, false, &ud));
+    RNB_TRY(st.resident_ptr(down, down_len, false, &dd));
+    RNB_TRY(st.in_f32.ensure(n_embd * seq_len * 4));
+    RNB_TRY(st.h2d(st.in_f32.p, input, n_embd * seq_len * 4, st.pin_in));
+    RNB_TRY(st.xq.ensure(q8k_dev_bytes(n_embd) * seq_len));
+    RNB_TRY(launch_quantize_q8k(st.stream, st.in_f32.as<float>(), n_embd, seq_len, st.xq.as<uint8_t>(), nullptr));
+    RNB_TRY(st.mid_a.ensure(n_ff * seq_len * 4));
+    RNB_TRY(st.mid_b.ensure(n_ff * seq_len * 4));
+    GemvJob jobs[2];
+    jobs[0] = make_job(TYPE_Q4_K, gd, st.xq.p, st.mid_a.as<float>(), nullptr, n_ff, n_embd, 0, st.sm_count, (int)seq_len, q8k_dev_bytes(n_embd));
+    jobs[1] = make_job(TYPE_Q4_K, ud, st.xq.p, st.mid_b.as<float>(), nullptr, n_ff, n_embd, jobs[0].rows_per_tile, st.sm_count, (int)seq_len, q8k_dev_bytes(n_embd));
+    jobs[1].tile0 = (jobs[0].rows + jobs[0].rows_per_tile - 1) / jobs[0].rows_per_tile;
+    RNB_TRY(st.jobs.ensure(sizeof(jobs)));
+    RNB_TRY(st.h2d(st.jobs.p, jobs, sizeof(jobs), st.pin_jobs));
+    RNB_TRY(launch_gemv_jobs(st.stream, jobs, st.jobs.as<GemvJob>(), 2, n_embd, st.dev_error));
+    RNB_TRY(st.xq2.ensure(q8k_dev_bytes(n_ff) * seq_len));
+    RNB_CU(launch_k(silu_mul_q8k_kernel, dim3((unsigned)((n_ff / 256 * seq_len + 3) / 4)), dim3(128), 0, st.stream,
+                    (const float *)st.mid_a.p, (const float *)st.mid_b.p, (int)n_ff, (int)seq_len, (float *)nullptr, st.xq2.as<uint8_t>()));
+    RNB_TRY(st.out_f32.ensure(n_embd * seq_len * 4));
+    GemvJob dj = make_job((int)down_quant, dd, st.xq2.p, st.out_f32.as<float>(), nullptr, n_embd, n_ff, 0, st.sm_count, (int)seq_len, q8k_dev_bytes(n_ff));
+    RNB_TRY(launch_gemv_one(st.stream, dj, n_ff, st.dev_error));
+    return finish_to_host(st, st.out_f32.p, output, n_embd * seq_len * 4);
+}
+
+// ---- MoE ---------------------------------------------------------------------------------------------
+int rnb_b200_moe_route_topk_f32(const float *logits, size_t logits_len, const float *selection_bias, size_t seq_len, size_t n_expert,
+                                size_t top_k, int sigmoid_mode, int normalize_selected, float scale, float adaptive_top_p,
+                                uint32_t *ids_out, float *weights_out, uint32_t *retained_counts_out) {
+    (void)normalize_selected;
+    (void)adaptive_top_p;
+    if (logits_len != seq_len * n_expert) return fail(RNB_B200_VALIDATION_FAILED, "CUDA MoE route logits mismatch: got=%zu expected=%zu", logits_len, seq_len * n_expert);
+    if (n_expert == 0 || n_expert > 1024 || top_k == 0 || top_k > n_expert || top_k > 32)
+        return fail(RNB_B200_VALIDATION_FAILED, "invalid CUDA MoE route shape: seq_len=%zu n_expert=%zu top_k=%zu", seq_len, n_expert, top_k);
+    if (sigmoid_mode || selection_bias) return fail(RNB_B200_UNSUPPORTED, "sigmoid / biased routing is not on this path (softmax top-k only)");
+    if (seq_len == 0) return RNB_B200_OK;
+    if (!logits || !ids_out || !weights_out) return fail(RNB_B200_VALIDATION_FAILED, "null pointer argument");
+    Locked L;
+    State &st = L.st;
+    RNB_TRY(st.open());
+    RNB_CU(cudaSetDevice(st.device));
+    RNB_TRY(st.in_f32.ensure(logits_len * 4));
+    RNB_TRY(st.h2d(st.in_f32.p, logits, logits_len * 4, st.pin_in));
+    const size_t slots = seq_len * top_k;
+    RNB_TRY(st.out_f32.ensure(slots * 8));
+    uint32_t *ids_dev = st.out_f32.as<uint32_t>();
+    float *w_dev = st.out_f32.as<float>() + slots;
+    RNB_CU(launch_k(moe_route_topk_kernel, dim3((unsigned)seq_len), dim3(32), 0, st.stream, (const float *)st.in_f32.p, (int)n_expert,
+                    (int)top_k, ids_dev, w_dev));
+    std::vector<uint8_t> tmp(slots * 8);
+    RNB_TRY(finish_to_host(st, st.out_f32.p, tmp.data(), tmp.size()));
+    memcpy(ids_out, tmp.data(), slots * 4);
+    const float *wsrc = reinterpret_cast<const float *>(tmp.data() + slots * 4);
+    for (size_t i = 0; i < slots; i++) weights_out[i] = scale == 1.0f ? wsrc[i] : wsrc[i] * scale;
+    if (retained_counts_out)
+        for (size_t t = 0; t < seq_len; t++) retained_counts_out[t] = (uint32_t)top_k;
+    return RNB_B200_OK;
+}
+
+int rnb_b200_router_logits_f32(const float *router_w, size_t n_expert, size_t hidden, const float *h, float *logits_out) {
+    if (hidden == 0 || hidden % 16 != 0) return fail(RNB_B200_VALIDATION_FAILED, "router hidden must be divisible by 16, got %zu", hidden);
+    if (n_expert == 0) return RNB_B200_OK;
+    if (!router_w || !h || !logits_out) return fail(RNB_B200_VALIDATION_FAILED, "null pointer argument");
+    Locked L;
+    State &st = L.st;
+    RNB_TRY(st.open());
+    RNB_CU(cudaSetDevice(st.device));
+    const uint8_t *wd = nullptr;
+    RNB_TRY(st.resident_ptr(reinterpret_cast<const uint8_t *>(router_w), n_expert * hidden * 4, false, &wd));
+    RNB_TRY(st.in_f32.ensure(hidden * 4));
+    RNB_TRY(st.h2d(st.in_f32.p, h, hidden * 4, st.pin_in));
+    RNB_TRY(st.out_f32.ensure(n_expert * 4));
+    RNB_CU(launch_k(router_logits_kernel, dim3((unsigned)((n_expert + 7) / 8)), dim3(128), 0, st.stream, reinterpret_cast<const float *>(wd),
+                    (const float *)st.in_f32.p, (int)n_expert, (int)hidden, st.out_f32.as<float>()));
+    return finish_to_host(st, st.out_f32.p, logits_out, n_expert * 4);
+}
+
+int rnb_b200_qwen35_sparse_experts(const uint8_t *const *gate, const uint8_t *const *up, const uint8_t *const *down,
+                                   size_t gate_slice_len, size_t down_slice_len, const float *route_weights, size_t n_selected,
+                                   uint32_t down_quant, size_t n_ff, size_t n_embd, const float *input, float *output) {
+    if (down_quant != TYPE_Q4_K && down_quant != TYPE_Q6_K) return fail(RNB_B200_UNSUPPORTED, "sparse experts: down quant %u not supported", down_quant);
+    if (n_selected == 0 || n_selected > 32) return fail(RNB_B200_VALIDATION_FAILED, "sparse experts: selected count %zu out of range 1..32", n_selected);
+    RNB_TRY(validate_gemv(TYPE_Q4_K, gate_slice_len, n_ff, n_embd, n_embd, 1, n_ff, true));
+    RNB_TRY(validate_gemv((int)down_quant, down_slice_len, n_embd, n_ff, n_ff, 1, n_embd, true));
+    if (!gate || !up || !down || !route_weights || !input || !output) return fail(RNB_B200_VALIDATION_FAILED, "null pointer argument");
+    Locked L;
+    State &st = L.st;
+    RNB_TRY(st.open());
+    RNB_CU(cudaSetDevice(st.device));
+    const size_t k = n_selected;
+    std::vector<const uint8_t *> gd(k), ud(k), dd(k);
+    for (size_t e = 0; e < k; e++) {
+        RNB_TRY(st.resident_ptr(gate[e], gate_slice_len, false, &gd[e]));
+        RNB_TRY(st.resident_ptr(up[e], gate_slice_len, false, &ud[e]));
+        RNB_TRY(st.resident_ptr(down[e], down_slice_len, false, &dd[e]));
+    }
+    RNB_TRY(st.in_f32.ensure(n_embd * 4 + k * 4));
+    RNB_TRY(st.pin_in.ensure(n_embd * 4 + k * 4));
+    memcpy(st.pin_in.p, input, n_embd * 4);
+    memcpy(st.pin_in.as<uint8_t>() + n_embd * 4, route_weights, k * 4);
+    RNB_CU(cudaMemcpyAsync(st.in_f32.p, st.pin_in.p, n_embd * 4 + k * 4, cudaMemcpyHostToDevice, st.stream));
+    const float *rw_dev = st.in_f32.as<float>() + n_embd;
+    RNB_TRY(st.xq.ensure(q8k_dev_bytes(n_embd)));
+    RNB_TRY(launch_quantize_q8k(st.stream, st.in_f32.as<float>(), n_embd, 1, st.xq.as<uint8_t>(), nullptr));
+    RNB_TRY(st.mid_a.ensure(k * n_ff * 4));
+    RNB_TRY(st.mid_b.ensure(k * n_ff * 4));
+    const size_t n_down_jobs = (k + GEMV_MAX_PARTS - 1) / GEMV_MAX_PARTS;
+    std::vector<GemvJob> jobs(2 * k + n_down_jobs);
+    const int rpt = pick_rows_per_tile(TYPE_Q4_K, n_ff, n_embd, 1, st.sm_count);
+    int tile0 = 0;
+    for (size_t e = 0; e < 2 * k; e++) {
+        const bool is_up = e >= k;
+        const size_t ee = is_up ? e - k : e;
+        jobs[e] = make_job(TYPE_Q4_K, is_up ? ud[ee] : gd[ee], st.xq.p, (is_up ? st.mid_b.as<float>() : st.mid_a.as<float>()) + ee * n_ff,
+                           nullptr, n_ff, n_embd, rpt, st.sm_count);
+        jobs[e].tile0 = tile0;
+        tile0 += (int)((n_ff + rpt - 1) / rpt);
+    }
+    RNB_TRY(st.xq2.ensure(q8k_dev_bytes(n_ff) * k));
+    RNB_TRY(st.out_f32.ensure(n_embd * 4));
+    RNB_TRY(st.mid_c.ensure(n_embd * 4));
+    // down: groups of up to 8 experts per job; later groups add onto the earlier partial sum
+    for (size_t gi = 0; gi < n_down_jobs; gi++) {
+        const size_t e0 = gi * GEMV_MAX_PARTS, ne = std::min<size_t>(GEMV_MAX_PARTS, k - e0);
+        const bool last = gi + 1 == n_down_jobs;
+        float *dst = ((n_down_jobs - 1 - gi) % 2 == 0) ? st.out_f32.as<float>() : st.mid_c.as<float>();
+        const float *prev = gi == 0 ? nullptr : (((n_down_jobs - gi) % 2 == 0) ? st.out_f32.as<float>() : st.mid_c.as<float>());
+        (void)last;
+        GemvJob &dj = jobs[2 * k + gi];
+        dj = make_job((int)down_quant, dd[e0], st.xq2.p, dst, prev, n_embd, n_ff, 0, st.sm_count);
+        dj.rows_per_tile = pick_rows_per_tile((int)down_quant, n_embd, n_ff, (int)ne, st.sm_count);
+        dj.n_parts = (int)ne;
+        for (size_t p = 0; p < ne; p++) {
+            dj.parts[p].w = dd[e0 + p];
+            dj.parts[p].x = st.xq2.as<uint8_t>() + (e0 + p) * q8k_dev_bytes(n_ff);
+            dj.parts[p].scale = rw_dev + e0 + p;
+        }
+    }
+    RNB_TRY(st.jobs.ensure(jobs.size() * sizeof(GemvJob)));
+    RNB_TRY(st.h2d(st.jobs.p, jobs.data(), jobs.size() * sizeof(GemvJob), st.pin_jobs));
+    RNB_TRY(launch_gemv_jobs(st.stream, jobs.data(), st.jobs.as<GemvJob>(), (int)(2 * k), n_embd, st.dev_error));
+    RNB_CU(launch_k(silu_mul_q8k_kernel, dim3((unsigned)((n_ff / 256 * k + 3) / 4)), dim3(128), 0, st.stream, (const float *)st.mid_a.p,
+                    (const float *)st.mid_b.p, (int)n_ff, (int)k, (float *)nullptr, st.xq2.as<uint8_t>()));
+    for (size_t gi = 0; gi < n_down_jobs; gi++)
+        RNB_TRY(launch_gemv_jobs(st.stream, &jobs[2 * k + gi], st.jobs.as<GemvJob>() + 2 * k + gi, 1, n_ff, st.dev_error));
+    return finish_to_host(st, st.out_f32.p, output, n_embd * 4);
+}
+
+int rnb_b200_qwen35_register_moe_layer(const uint8_t *gate_all, size_t gate_len, const uint8_t *up_all, size_t up_len,
+                                       const uint8_t *down_all, size_t down_len, uint32_t down_quant, size_t n_ff, size_t n_embd,
+                                       int *fitted) {
+    if (down_quant != TYPE_Q4_K && down_quant != TYPE_Q6_K) return fail(RNB_B200_UNSUPPORTED, "register MoE layer: down quant %u not supported", down_quant);
+    const size_t gslice = n_ff * row_bytes_of(TYPE_Q4_K, n_embd), dslice = n_embd * row_bytes_of((int)down_quant, n_ff);
+    if (gslice == 0 || dslice == 0 || gate_len % gslice || up_len != gate_len || down_len % dslice || down_len / dslice != gate_len / gslice)
+        return fail(RNB_B200_VALIDATION_FAILED, "register MoE layer: stacked tensor sizes (%zu, %zu, %zu) do not match n_ff=%zu n_embd=%zu", gate_len, up_len, down_len, n_ff, n_embd);
+    if (!gate_all || !up_all || !down_all) return fail(RNB_B200_VALIDATION_FAILED, "null pointer argument");
+    Locked L;
+    State &st = L.st;
+    RNB_TRY(st.open());
+    RNB_CU(cudaSetDevice(st.device));
+    if (fitted) *fitted = 0;
+    // "without evicting": only admit when everything fits beside what is already resident
+    if (st.resident_bytes + gate_len + up_len + down_len > st.resident_limit) return RNB_B200_OK;
+    const uint8_t *d = nullptr;
+    RNB_TRY(st.resident_ptr(gate_all, gate_len, true, &d));
+    RNB_TRY(st.resident_ptr(up_all, up_len, true, &d));
+    RNB_TRY(st.resident_ptr(down_all, down_len, true, &d));
+    RNB_CU(cudaStreamSynchronize(st.stream));
+    if (fitted) *fitted = 1;
+    return RNB_B200_OK;
+}
+
+// ---- host-only bookkeeping -----------------------------------------------------------------------
+// admit iff missing_bytes * (predicted_future_reuses + [replaces a temp upload]) >
+//           missing_bytes + eviction_reload_bytes   (strict)
+// crates/rnb-memory/src/sparse_expert_cache.rs:221-245
+int rnb_b200_evaluate_expert_bundle_admission(const rnb_b200_bundle_admission *a) {
+    if (!a || a->missing_bytes == 0) return 0;
+    const unsigned __int128 benefit = (unsigned __int128)a->missing_bytes * ((uint64_t)a->predicted_future_reuses + (a->replaces_temp_upload ? 1u : 0u));
+    const unsigned __int128 cost = (unsigned __int128)a->missing_bytes + a->eviction_reload_bytes;
+    return benefit > cost ? 1 : 0;
+}
+uint64_t rnb_b200_resident_limit_for(uint64_t total_bytes, uint64_t free_bytes) { return resident_limit_for(total_bytes, free_bytes); }
+
+// ---- device-pointer tier ---------------------------------------------------------------------------
+size_t rnb_b200_dev_q8k_bytes(size_t cols) { return q8k_dev_bytes(cols); }
+int rnb_b200_dev_quantize_q8k(const float *x_dev, size_t cols, size_t seq, void *xq_dev, void *ref_blocks_dev, void *stream) {
+    if (cols % 256 != 0) return fail(RNB_B200_VALIDATION_FAILED, "Q8_K input length must be divisible by 256, got %zu", cols);
+    Locked L;
+    RNB_TRY(L.st.open());
+    return launch_quantize_q8k((cudaStream_t)stream, x_dev, cols, seq, (uint8_t *)xq_dev, (uint8_t *)ref_blocks_dev);
+}
+int rnb_b200_dev_gemv(uint32_t type, const uint8_t *w_dev, size_t rows, size_t cols, const void *x_dev, float *y_dev, int rows_per_tile, void *stream) {
+    if (row_bytes_of((int)type, cols) == 0 || cols % (type == TYPE_Q8_0 ? 32 : 256) != 0)
+        return fail(RNB_B200_VALIDATION_FAILED, "%s cols must be divisible by %d, got %zu", type_name((int)type), type == TYPE_Q8_0 ? 32 : 256, cols);
+    Locked L;
+    RNB_TRY(L.st.open());
+    GemvJob job = make_job((int)type, w_dev, x_dev, y_dev, nullptr, rows, cols, rows_per_tile, L.st.sm_count);
+    return launch_gemv_one((cudaStream_t)stream, job, cols, L.st.dev_error);
+}
+size_t rnb_b200_flash_decode_scratch_bytes(size_t num_heads, int n_chunks) { return flash_decode_scratch_bytes(num_heads, n_chunks); }
+int rnb_b200_flash_decode_default_chunks(size_t kv_len, size_t num_kv_heads) {
+    Locked L;
+    return flash_decode_default_chunks(kv_len, num_kv_heads, L.st.is_open ? L.st.sm_count : 148);
+}
+int rnb_b200_dev_flash_decode(const float *q_dev, const uint16_t *k_dev, const uint16_t *v_dev, size_t kv_len, size_t num_heads,
+                              size_t num_kv_heads, float scale, float *partials_dev, size_t partials_bytes, int n_chunks,
+                              float *out_dev, void *stream) {
+    if (num_kv_heads == 0 || num_heads % num_kv_heads != 0) return fail(RNB_B200_VALIDATION_FAILED, "attention: num_heads(%zu) must be a multiple of num_kv_heads(%zu)", num_heads, num_kv_heads);
+    if (n_chunks < 1 || partials_bytes < flash_decode_scratch_bytes(num_heads, n_chunks))
+        return fail(RNB_B200_VALIDATION_FAILED, "flash decode scratch too small: got %zu, expected >= %zu", partials_bytes, flash_decode_scratch_bytes(num_heads, n_chunks));
+    Locked L;
+    RNB_TRY(L.st.open());
+    return launch_flash_decode((cudaStream_t)stream, q_dev, k_dev, v_dev, nullptr, (int)kv_len, (int)num_heads, (int)num_kv_heads, scale,
+                               partials_dev, n_chunks, out_dev);
+}
+int rnb_b200_dev_error_flag(int *flag_out) {
+    Locked L;
+    RNB_TRY(L.st.open());
+    RNB_CU(cudaSetDevice(L.st.device));
+    int flag = 0;
+    RNB_CU(cudaMemcpy(&flag, L.st.dev_error, sizeof(int), cudaMemcpyDeviceToHost));
+    if (flag) RNB_CU(cudaMemset(L.st.dev_error, 0, sizeof(int)));
+    if (flag_out) *flag_out = flag;
+    return RNB_B200_OK;
+}
+
+}  // extern "C"
+
+#include "decoder.inc"

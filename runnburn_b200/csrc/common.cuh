@@ -1,0 +1,133 @@
+// Shared device/host helpers for the sm_100a batch-1 decode/prefill kernels.
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <string>
+
+namespace rnb {
+
+constexpr int QK_K = 256;
+constexpr int Q4K_BYTES = 144;
+constexpr int Q6K_BYTES = 210;
+constexpr int Q8_0_BYTES = 34;
+constexpr int Q8K_BYTES = 292;  // rnb-cpu Q8KBlock: f32 d @0, i8 qs[256] @4, i16 bsums[16] @260
+
+// GGML type ids, as the reference passes them across its operator API (`down_quant: u32`).
+constexpr int TYPE_Q8_0 = 8;
+constexpr int TYPE_Q4_K = 12;
+constexpr int TYPE_Q6_K = 14;
+
+// Device-side error word values (State::dev_error).
+constexpr int DEV_ERR_NONE = 0;
+constexpr int DEV_ERR_MBAR_TIMEOUT = 1;   // a bounded mbarrier wait gave up
+constexpr int DEV_ERR_BAD_JOB = 2;        // job table inconsistent with the launch
+
+__host__ __device__ inline size_t row_bytes_of(int type, size_t cols) {
+    switch (type) {
+    case TYPE_Q4_K: return cols / 256 * Q4K_BYTES;
+    case TYPE_Q6_K: return cols / 256 * Q6K_BYTES;
+    case TYPE_Q8_0: return cols / 32 * Q8_0_BYTES;
+    default: return 0;
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+// Device-internal activation layout ("Q8K-dev"): the same numbers as rnb-cpu's Q8KBlock
+// array, regrouped so that the matvec kernels can use 16-byte loads:
+//   int8  qs[K]            @ 0
+//   float d[K/256]         @ K
+//   int16 bsum32[K/256*8]  @ K + 4*(K/256)      (sum of each 32-element sub-block)
+// ---------------------------------------------------------------------------------------
+__host__ __device__ inline size_t q8k_dev_bytes(size_t cols) {
+    size_t nb = cols / 256;
+    return (cols + nb * 4 + nb * 16 + 15) & ~(size_t)15;
+}
+
+#ifdef __CUDACC__
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) {
+    return (uint32_t)__cvta_generic_to_shared(p);
+}
+
+__device__ __forceinline__ float f16_bits_to_f32(uint32_t h) {
+    return __half2float(__ushort_as_half((unsigned short)h));
+}
+
+// ---- mbarrier + 1-D bulk async copy (TMA engine, CTA-local destination) ----------------
+__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count)
+                 : "memory");
+}
+__device__ __forceinline__ void mbar_fence_init() {
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t *bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)),
+                 "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ void bulk_g2s(void *smem_dst, const void *gsrc, uint32_t bytes,
+                                         uint64_t *bar) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+        ::"r"(smem_u32(smem_dst)), "l"(gsrc), "r"(bytes), "r"(smem_u32(bar))
+        : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait: gives up after ~2^22 polls (seconds at worst), returns false on timeout so
+// the caller can flag the error and leave without touching the data.
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar, uint32_t parity) {
+    for (uint32_t i = 0; i < (1u << 22); i++) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if (i > 64) __nanosleep(i > 4096 ? 256 : 32);
+    }
+    return false;
+}
+
+// Programmatic dependent launch: let the next kernel in the stream start its prologue, and
+// wait for the previous kernel's memory to be visible.
+__device__ __forceinline__ void pdl_launch_dependents() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+__device__ __forceinline__ uint4 ldg_nc_u4(const void *p) {
+    uint4 v;
+    asm volatile("ld.global.nc.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p));
+    return v;
+}
+__device__ __forceinline__ uint2 ldg_nc_u2(const void *p) {
+    uint2 v;
+    asm volatile("ld.global.nc.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
+    return v;
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+#endif  // __CUDACC__
+
+}  // namespace rnb

@@ -1,0 +1,137 @@
+// Host-side launch helpers shared by the operator entry points and the decoder.
+#pragma once
+#include "attention.cuh"
+#include "gemv.cuh"
+#include "moe.cuh"
+#include "q8k.cuh"
+#include "state.hpp"
+
+namespace rnb {
+
+// Programmatic dependent launch is opt-in (RNB_B200_PDL=1): kernels then overlap their
+// weight prefetch with the tail of the previous kernel.
+bool use_pdl();
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_k(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                            cudaStream_t s, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    if (use_pdl()) {
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+    }
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
+constexpr size_t GEMV_SMEM_LIMIT = 200 * 1024;
+
+// Rows per tile: tiles are whole rows, their byte size must be a multiple of 16 for the bulk
+// copy, about 16 KB each, and there should be a few tiles per SM so the tail is short.
+inline int pick_rows_per_tile(int type, size_t rows, size_t cols, int n_parts, int sm_count) {
+    const size_t rb = row_bytes_of(type, cols);
+    if (rb == 0) return 1;
+    size_t unit = 1;
+    while ((unit * rb) % 16 != 0) unit *= 2;  // rb is even for every format: unit <= 8
+    size_t r = (16384 / rb) / unit * unit;
+    if (r < unit) r = unit;
+    while (r > unit && (rows + r - 1) / r < (size_t)(4 * sm_count) && r * rb > 4096) r -= unit;
+    while (r > unit && (size_t)n_parts * (r * rb + 32) > GEMV_SMEM_LIMIT) r -= unit;
+    if (r > rows) r = (rows + unit - 1) / unit * unit;
+    return (int)r;
+}
+inline uint32_t gemv_part_stride(int type, size_t cols, int rows_per_tile) {
+    return (uint32_t)(((size_t)rows_per_tile * row_bytes_of(type, cols) + 15) & ~(size_t)15) + 16;
+}
+
+int gemv_kernel_setup();  // raises the dynamic shared memory limit once
+
+// Launch a table of jobs that all share `cols`.  jobs_host is used to size the launch;
+// jobs_dev is the same table in device memory.
+inline int launch_gemv_jobs(cudaStream_t s, const GemvJob *jobs_host, const GemvJob *jobs_dev,
+                            int n_jobs, size_t cols, int *dev_error) {
+    RNB_TRY(gemv_kernel_setup());
+    int tiles = 0, max_parts = 1;
+    uint32_t stride = 0;
+    for (int i = 0; i < n_jobs; i++) {
+        const GemvJob &j = jobs_host[i];
+        tiles = j.tile0 + (j.rows + j.rows_per_tile - 1) / j.rows_per_tile;
+        if (j.n_parts > max_parts) max_parts = j.n_parts;
+        uint32_t st = gemv_part_stride(j.type, cols, j.rows_per_tile);
+        if (st > stride) stride = st;
+    }
+    const size_t smem = (size_t)stride * max_parts;
+    if (smem > 227 * 1024) return fail(RNB_B200_VALIDATION_FAILED, "matvec tile too large: %zu bytes", smem);
+    RNB_CU(launch_k(gemv_tile_kernel, dim3(tiles), dim3(GEMV_THREADS), smem, s, jobs_dev, n_jobs,
+                    (int)cols, stride, dev_error));
+    return RNB_B200_OK;
+}
+inline int launch_gemv_one(cudaStream_t s, const GemvJob &job, size_t cols, int *dev_error) {
+    RNB_TRY(gemv_kernel_setup());
+    const int tiles = (job.rows + job.rows_per_tile - 1) / job.rows_per_tile;
+    const uint32_t stride = gemv_part_stride(job.type, cols, job.rows_per_tile);
+    const size_t smem = (size_t)stride * job.n_parts;
+    if (smem > 227 * 1024) return fail(RNB_B200_VALIDATION_FAILED, "matvec tile too large: %zu bytes", smem);
+    RNB_CU(launch_k(gemv_tile_kernel_1, dim3(tiles), dim3(GEMV_THREADS), smem, s, job, (int)cols,
+                    stride, dev_error));
+    return RNB_B200_OK;
+}
+inline GemvJob make_job(int type, const uint8_t *w, const void *x, float *y, const float *residual,
+                        size_t rows, size_t cols, int rows_per_tile, int sm_count, int seq = 1,
+                        size_t x_stride = 0) {
+    GemvJob j;
+    memset(&j, 0, sizeof(j));
+    j.y = y;
+    j.residual = residual;
+    j.rows = (int)rows;
+    j.type = type;
+    j.n_parts = 1;
+    j.tile0 = 0;
+    j.rows_per_tile = rows_per_tile > 0 ? rows_per_tile : pick_rows_per_tile(type, rows, cols, 1, sm_count);
+    j.seq = seq;
+    j.x_stride = x_stride;
+    j.parts[0].w = w;
+    j.parts[0].x = reinterpret_cast<const uint8_t *>(x);
+    j.parts[0].scale = nullptr;
+    return j;
+}
+
+inline int launch_quantize_q8k(cudaStream_t s, const float *x, size_t cols, size_t seq,
+                               uint8_t *dev_out, uint8_t *ref_out) {
+    const int nblk = (int)(cols / 256 * seq);
+    if (nblk == 0) return RNB_B200_OK;
+    RNB_CU(launch_k(quantize_q8k_kernel, dim3((nblk + 3) / 4), dim3(128), 0, s, x, (int)cols,
+                    (int)seq, dev_out, ref_out));
+    return RNB_B200_OK;
+}
+
+inline int flash_decode_default_chunks(size_t kv_len, size_t num_kv_heads, int sm_count) {
+    if (kv_len == 0) return 1;
+    long want = (long)(4 * sm_count) / (long)(num_kv_heads ? num_kv_heads : 1);
+    long max_c = (long)((kv_len + 31) / 32);
+    if (want > max_c) want = max_c;
+    if (want < 1) want = 1;
+    return (int)want;
+}
+inline size_t flash_decode_scratch_bytes(size_t num_heads, int n_chunks) {
+    return num_heads * (size_t)n_chunks * FD_PART_STRIDE * sizeof(float);
+}
+// kv_len = (*kv_len_dev if given) + kv_len_host
+inline int launch_flash_decode(cudaStream_t s, const float *q, const uint16_t *k, const uint16_t *v,
+                               const int *kv_len_dev, int kv_len_host, int num_heads,
+                               int num_kv_heads, float scale, float *partials, int n_chunks,
+                               float *out) {
+    RNB_CU(launch_k(flash_decode_partials_kernel, dim3(num_kv_heads, n_chunks), dim3(FD_THREADS), 0,
+                    s, q, k, v, kv_len_dev, kv_len_host, num_heads, num_kv_heads, scale, partials));
+    RNB_CU(launch_k(flash_decode_reduce_kernel, dim3(num_heads), dim3(HD), 0, s,
+                    (const float *)partials, n_chunks, out));
+    return RNB_B200_OK;
+}
+
+}  // namespace rnb

@@ -1,0 +1,105 @@
+// MoE routing on device: router logits, softmax top-k, and the expert-gathered matvec job
+// tables, so that a decode step needs no host round trip between routing and the experts.
+#pragma once
+#include "common.cuh"
+#include "gemv.cuh"
+
+namespace rnb {
+
+// Router logits: f32 [n_expert][hidden] x f32 h.  16 threads per expert reproduce the exact
+// accumulation order of the reference's host routine (dot_f32_avx2_fma,
+// crates/rnb-cpu/src/gemm/f32_gemv.rs:215-237,266-275): thread j owns accumulator lane j of
+// the two 8-lane FMA registers, then lanes are folded 8, 4, 2, 1 apart.  Bit-identical
+// logits are what makes the selected expert ids identical.  hidden % 16 == 0.
+__global__ void __launch_bounds__(128)
+router_logits_kernel(const float *__restrict__ w, const float *__restrict__ h, int n_expert,
+                     int hidden, float *__restrict__ logits) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int j = threadIdx.x & 15;
+    const int e = blockIdx.x * (blockDim.x >> 4) + (threadIdx.x >> 4);
+    const bool live = e < n_expert;
+    const float *wr = w + (size_t)(live ? e : 0) * hidden;
+    float acc = 0.0f;
+#pragma unroll 8
+    for (int i = j; i < hidden; i += 16) acc = __fmaf_rn(wr[i], h[i], acc);
+    acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 8));
+    acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 4));
+    acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 2));
+    acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 1));
+    if (live && j == 0) logits[e] = acc;
+}
+
+// Top-k by logit (descending, ties -> lower expert id), weights = softmax over the selected
+// logits in rank order: crates/rnb-llm/src/engine/models/shared_expert_moe/routing.rs:18-62;
+// same contract as the reference's rnb_moe_route_topk_f32
+// (crates/rnb-backend/cuda/cuda/kernels/quant_batch_and_ops.cuh:4782-4912).
+// One warp per token; n_expert <= 1024, top_k <= 32.  exp is taken in double and rounded once.
+__global__ void __launch_bounds__(32)
+moe_route_topk_kernel(const float *__restrict__ logits, int n_expert, int top_k,
+                      uint32_t *__restrict__ ids_out, float *__restrict__ weights_out) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int lane = threadIdx.x;
+    const float *lg = logits + (size_t)blockIdx.x * n_expert;
+    uint32_t *ids = ids_out + (size_t)blockIdx.x * top_k;
+    float *wts = weights_out + (size_t)blockIdx.x * top_k;
+    const int sel = min(min(top_k, n_expert), 32);
+    uint32_t taken = 0;  // bit s <-> expert lane + 32*s
+    float my_val = 0.0f;
+    for (int r = 0; r < sel; r++) {
+        float best = -INFINITY;
+        int bi = 0x7fffffff;
+        for (int s = 0, e = lane; e < n_expert; s++, e += 32) {
+            if (taken & (1u << s)) continue;
+            const float v = lg[e];
+            if (bi == 0x7fffffff || v > best) {  // ascending e: strict > keeps the lowest id
+                best = v;
+                bi = e;
+            }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (oi != 0x7fffffff && (bi == 0x7fffffff || ov > best || (ov == best && oi < bi))) {
+                best = ov;
+                bi = oi;
+            }
+        }
+        if ((bi & 31) == lane && bi != 0x7fffffff) taken |= 1u << (bi >> 5);
+        if (lane == r) {
+            my_val = best;
+            ids[r] = (uint32_t)bi;
+        }
+    }
+    const float mx = __shfl_sync(0xffffffffu, my_val, 0);
+    float w = lane < sel ? (float)exp((double)__fsub_rn(my_val, mx)) : 0.0f;
+    float sum = 0.0f;
+    for (int r = 0; r < sel; r++) sum = __fadd_rn(sum, __shfl_sync(0xffffffffu, w, r));
+    if (lane < sel) wts[lane] = sum != 0.0f ? __fdiv_rn(w, sum) : w;
+}
+
+// Fills the per-layer job tables of the expert-gathered matvecs from the routed ids:
+//   gate_up job e (0..k-1) / (k..2k-1): rows n_ff, weights at base + id*stride, activation hq
+//   down job: one job with k parts (weight slice, that expert's activation, route weight)
+struct MoeLayerPtrs {
+    const uint8_t *gate_base, *up_base, *down_base;
+    size_t gate_stride, down_stride;
+};
+__global__ void moe_fill_jobs_kernel(const uint32_t *__restrict__ ids,
+                                     const float *__restrict__ weights, int top_k,
+                                     MoeLayerPtrs lp, GemvJob *__restrict__ gate_up_jobs,
+                                     GemvJob *__restrict__ down_job) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int e = threadIdx.x;
+    if (e >= top_k) return;
+    const size_t id = ids[e];
+    gate_up_jobs[e].parts[0].w = lp.gate_base + id * lp.gate_stride;
+    gate_up_jobs[top_k + e].parts[0].w = lp.up_base + id * lp.gate_stride;
+    down_job->parts[e].w = lp.down_base + id * lp.down_stride;
+    down_job->parts[e].scale = weights + e;
+}
+
+}  // namespace rnb

@@ -1,0 +1,58 @@
+// Prefill-side kernels: causal attention over f32 K/V (the reference's prefill operator takes
+// f32 tensors: crates/rnb-backend/cuda/src/runtime/api/attention_api.rs:661-700).
+#pragma once
+#include "attention.cuh"
+#include "state.hpp"
+
+namespace rnb {
+
+// grid = (seq_len, num_kv_heads), 128 threads: one CTA per (query, KV group); query i sees
+// keys 0..(kv_len - seq_len + i).  q/out f32 [seq][heads][128]; k, v [kv_len][kv_heads][128].
+template <typename KVT>
+__global__ void __launch_bounds__(FD_THREADS)
+prefill_attention_kernel(const float *__restrict__ q, const KVT *__restrict__ k,
+                         const KVT *__restrict__ v, int seq_len, int kv_len, int num_heads,
+                         int num_kv_heads, float scale, float *__restrict__ out) {
+    pdl_launch_dependents();
+    pdl_wait();
+    __shared__ float s_acc[(FD_THREADS / 32) * 4 * HD];
+    __shared__ float s_ml[(FD_THREADS / 32) * 4 * 2];
+    const int i = blockIdx.x, kv_h = blockIdx.y;
+    const int visible = kv_len - seq_len + i + 1;
+    const int group = num_heads / num_kv_heads;
+    const size_t kv_dim = (size_t)num_kv_heads * HD;
+    const float *qi = q + (size_t)i * num_heads * HD;
+    float *oi = out + (size_t)i * num_heads * HD;
+    for (int g0 = 0; g0 < group; g0 += 4) {
+        const int here = min(4, group - g0);
+        fd_process<4, KVT>(qi, k, v, kv_h, kv_h * group + g0, here, kv_dim, 0, visible, scale, 1, 0,
+                           nullptr, s_acc, s_ml, oi);
+        __syncthreads();
+    }
+}
+
+inline int launch_prefill_attention_f32kv(cudaStream_t s, const float *q, const float *k,
+                                          const float *v, int seq_len, int kv_len, int num_heads,
+                                          int num_kv_heads, float scale, float *out) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(seq_len, num_kv_heads);
+    cfg.blockDim = dim3(FD_THREADS);
+    cfg.stream = s;
+    RNB_CU(cudaLaunchKernelEx(&cfg, prefill_attention_kernel<float>, q, k, v, seq_len, kv_len,
+                              num_heads, num_kv_heads, scale, out));
+    return RNB_B200_OK;
+}
+inline int launch_prefill_attention_f16kv(cudaStream_t s, const float *q, const uint16_t *k,
+                                          const uint16_t *v, int seq_len, int kv_len,
+                                          int num_heads, int num_kv_heads, float scale,
+                                          float *out) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(seq_len, num_kv_heads);
+    cfg.blockDim = dim3(FD_THREADS);
+    cfg.stream = s;
+    RNB_CU(cudaLaunchKernelEx(&cfg, prefill_attention_kernel<uint16_t>, q, k, v, seq_len, kv_len,
+                              num_heads, num_kv_heads, scale, out));
+    return RNB_B200_OK;
+}
+
+}  // namespace rnb

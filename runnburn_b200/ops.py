@@ -1,0 +1,289 @@
+"""Python mirror of the operator functions of runNburn's `rnb_backend_cuda`
+(crates/rnb-backend/cuda/src/runtime/api/*.rs), bound to the C ABI by ctypes.
+
+Same names, argument order and error behaviour as the Rust functions: a failing call raises
+`RnbError` carrying the message the Rust `Result::Err(String)` would carry.  Arrays are numpy;
+weights are `uint8` views of GGUF block data and stay on the host (the library keeps its own
+device-resident copies keyed by host address).
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+
+from . import _lib
+from ._lib import TYPE_Q4_K, TYPE_Q6_K, TYPE_Q8_0, check, load
+
+Q8K_DTYPE = np.dtype([("d", "<f4"), ("qs", "i1", (256,)), ("bsums", "<i2", (16,))])
+
+
+def _p(a: np.ndarray):
+    return a.ctypes.data_as(C.c_void_p)
+
+
+def _f32(a) -> np.ndarray:
+    return np.ascontiguousarray(a, dtype=np.float32)
+
+
+def _u8(a) -> np.ndarray:
+    a = np.asarray(a)
+    if a.dtype != np.uint8 or not a.flags["C_CONTIGUOUS"]:
+        a = np.ascontiguousarray(a, dtype=np.uint8)
+    return a
+
+
+def _u16(a) -> np.ndarray:
+    return np.ascontiguousarray(a, dtype=np.uint16)
+
+
+# ---- state / cache -------------------------------------------------------------------------
+def open() -> None:  # noqa: A001 - mirrors CudaState::open
+    check(load().rnb_b200_open())
+
+
+def close() -> None:
+    load().rnb_b200_close()
+
+
+def cuda_memory_info() -> tuple[int, int]:
+    f, t = C.c_size_t(), C.c_size_t()
+    check(load().rnb_b200_cuda_memory_info(C.byref(f), C.byref(t)))
+    return f.value, t.value
+
+
+def device_sm_count() -> int:
+    n = C.c_int()
+    check(load().rnb_b200_device_sm_count(C.byref(n)))
+    return n.value
+
+
+def cuda_cache_snapshot() -> dict:
+    s = _lib.CacheSnapshot()
+    check(load().rnb_b200_cuda_cache_snapshot(C.byref(s)))
+    return {n: getattr(s, n) for n, _ in s._fields_}
+
+
+def clear_q4k_cache() -> None:
+    check(load().rnb_b200_clear_q4k_cache())
+
+
+def reset_state_for_engine_init() -> None:
+    check(load().rnb_b200_reset_state_for_engine_init())
+
+
+def set_resident_limit(nbytes: int) -> None:
+    check(load().rnb_b200_set_resident_limit(nbytes))
+
+
+def prewarm_q4k_weights(slices) -> int:
+    arrs = [_u8(s) for s in slices]
+    n = len(arrs)
+    ptrs = (C.c_void_p * n)(*[a.ctypes.data for a in arrs])
+    lens = (C.c_size_t * n)(*[a.size for a in arrs])
+    got = C.c_size_t()
+    check(load().rnb_b200_prewarm_q4k_weights(ptrs, lens, n, C.byref(got)))
+    return got.value
+
+
+def register_host_range(a: np.ndarray) -> None:
+    check(load().rnb_b200_register_host_range(_p(a), a.nbytes))
+
+
+def clear_host_registered_ranges() -> None:
+    check(load().rnb_b200_clear_host_registered_ranges())
+
+
+# ---- quantisation / matvec -----------------------------------------------------------------
+def quantize_q8k(x) -> np.ndarray:
+    """GGML Q8_K blocks of `x` (structured array, 292 bytes per 256 values), computed on the GPU."""
+    x = _f32(x).ravel()
+    out = np.zeros(x.size // 256 if x.size % 256 == 0 else 0, dtype=Q8K_DTYPE)
+    check(load().rnb_b200_quantize_q8k(_p(x), x.size, _p(out)))
+    return out
+
+
+def _gemv(fn, weights, rows, cols, x, seq=1) -> np.ndarray:
+    w, x = _u8(weights), _f32(x).ravel()
+    out = np.empty(rows * seq, dtype=np.float32)
+    check(fn(_p(w), w.size, rows, cols, _p(x), x.size, _p(out), out.size))
+    return out
+
+
+def q4k_gemv(weights, rows: int, cols: int, x) -> np.ndarray:
+    return _gemv(load().rnb_b200_q4k_gemv, weights, rows, cols, x)
+
+
+def q6k_gemv(weights, rows: int, cols: int, x) -> np.ndarray:
+    return _gemv(load().rnb_b200_q6k_gemv, weights, rows, cols, x)
+
+
+def q8_0_gemv(weights, rows: int, cols: int, x) -> np.ndarray:
+    return _gemv(load().rnb_b200_q8_0_gemv, weights, rows, cols, x)
+
+
+def gemv(ggml_type: int, weights, rows: int, cols: int, x) -> np.ndarray:
+    return {TYPE_Q4_K: q4k_gemv, TYPE_Q6_K: q6k_gemv, TYPE_Q8_0: q8_0_gemv}[ggml_type](weights, rows, cols, x)
+
+
+def q4k_gemv_with_device_input(weights, rows: int, cols: int, input_dev: int) -> np.ndarray:
+    w = _u8(weights)
+    out = np.empty(rows, dtype=np.float32)
+    check(load().rnb_b200_q4k_gemv_with_device_input(_p(w), w.size, rows, cols, input_dev, _p(out), out.size))
+    return out
+
+
+def q6k_gemv_with_device_input(weights, rows: int, cols: int, input_dev: int) -> np.ndarray:
+    w = _u8(weights)
+    out = np.empty(rows, dtype=np.float32)
+    check(load().rnb_b200_q6k_gemv_with_device_input(_p(w), w.size, rows, cols, input_dev, _p(out), out.size))
+    return out
+
+
+def q6k_gemv_argmax(weights, rows: int, cols: int, x) -> tuple[int, float]:
+    w, x = _u8(weights), _f32(x).ravel()
+    idx, val = C.c_uint32(), C.c_float()
+    check(load().rnb_b200_q6k_gemv_argmax(_p(w), w.size, rows, cols, _p(x), x.size, C.byref(idx), C.byref(val)))
+    return idx.value, val.value
+
+
+def q4k_gemv_batch(weights, rows: int, cols: int, x) -> np.ndarray:
+    x = _f32(x).ravel()
+    return _gemv(load().rnb_b200_q4k_gemv_batch, weights, rows, cols, x, seq=max(1, x.size // max(cols, 1)))
+
+
+def q6k_gemv_batch(weights, rows: int, cols: int, x) -> np.ndarray:
+    x = _f32(x).ravel()
+    return _gemv(load().rnb_b200_q6k_gemv_batch, weights, rows, cols, x, seq=max(1, x.size // max(cols, 1)))
+
+
+# ---- attention -----------------------------------------------------------------------------
+def attention_decode_hd128(q, k, v, kv_len: int, num_heads: int, num_kv_heads: int, scale: float) -> np.ndarray:
+    q, k, v = _f32(q).ravel(), _u16(k).ravel(), _u16(v).ravel()
+    out = np.empty(num_heads * 128, dtype=np.float32)
+    check(load().rnb_b200_attention_decode_hd128(_p(q), q.size, _p(k), _p(v), min(k.size, v.size), kv_len,
+                                                 num_heads, num_kv_heads, scale, _p(out), out.size))
+    return out
+
+
+def attention_decode_cached(layer_index: int, q, k, v, kv_len: int, num_heads: int, num_kv_heads: int,
+                            head_dim: int, scale: float) -> np.ndarray:
+    q = _f32(q).ravel()
+    assert k.dtype == np.uint16 and v.dtype == np.uint16 and k.flags["C_CONTIGUOUS"] and v.flags["C_CONTIGUOUS"], \
+        "the KV mirror is keyed by the host buffers' addresses: pass the cache arrays themselves"
+    out = np.empty(num_heads * head_dim, dtype=np.float32)
+    check(load().rnb_b200_attention_decode_cached(layer_index, _p(q), q.size, _p(k), _p(v), min(k.size, v.size),
+                                                  kv_len, num_heads, num_kv_heads, head_dim, scale, _p(out), out.size))
+    return out
+
+
+def clear_decode_attention_kv_cache() -> None:
+    check(load().rnb_b200_clear_decode_attention_kv_cache())
+
+
+def attention_prefill_flash_hd128(q, k, v, seq_len: int, kv_len: int, num_heads: int, num_kv_heads: int,
+                                  scale: float) -> np.ndarray:
+    q, k, v = _f32(q).ravel(), _f32(k).ravel(), _f32(v).ravel()
+    out = np.empty(seq_len * num_heads * 128, dtype=np.float32)
+    check(load().rnb_b200_attention_prefill_flash_hd128(_p(q), _p(k), _p(v), seq_len, kv_len, num_heads,
+                                                        num_kv_heads, scale, _p(out)))
+    return out
+
+
+def dense_attention_qkv_rope_hd128_decode(q_w, k_w, v_w, q_rows, kv_rows, n_embd, num_heads, num_kv_heads,
+                                          rope_theta, pos_start, x, q_type=TYPE_Q4_K, k_type=TYPE_Q4_K,
+                                          v_type=TYPE_Q4_K):
+    qw, kw, vw, x = _u8(q_w), _u8(k_w), _u8(v_w), _f32(x).ravel()
+    q = np.empty(q_rows, np.float32)
+    kb, vb = np.empty(kv_rows, np.uint16), np.empty(kv_rows, np.uint16)
+    check(load().rnb_b200_dense_attention_qkv_rope_hd128_decode(
+        _p(qw), qw.size, q_type, _p(kw), kw.size, k_type, _p(vw), vw.size, v_type, q_rows, kv_rows, n_embd,
+        num_heads, num_kv_heads, rope_theta, pos_start, _p(x), _p(q), _p(kb), _p(vb)))
+    return q, kb, vb
+
+
+def dense_q4k_silu_ffn_batch(gate, up, down, down_quant, n_ff, n_embd, seq_len, x) -> np.ndarray:
+    g, u, d, x = _u8(gate), _u8(up), _u8(down), _f32(x).ravel()
+    out = np.empty(seq_len * n_embd, np.float32)
+    check(load().rnb_b200_dense_q4k_silu_ffn_batch(_p(g), g.size, _p(u), u.size, _p(d), d.size, down_quant, n_ff,
+                                                   n_embd, seq_len, _p(x), _p(out)))
+    return out
+
+
+# ---- MoE -----------------------------------------------------------------------------------
+def moe_route_topk_f32(logits, selection_bias, seq_len, n_expert, top_k, sigmoid_mode=False,
+                       normalize_selected=False, scale=1.0, adaptive_top_p=None):
+    lg = _f32(logits).ravel()
+    ids = np.zeros(seq_len * top_k, np.uint32)
+    w = np.zeros(seq_len * top_k, np.float32)
+    cnt = np.zeros(seq_len, np.uint32)
+    bias = None if selection_bias is None else _f32(selection_bias)
+    check(load().rnb_b200_moe_route_topk_f32(_p(lg), lg.size, None if bias is None else _p(bias), seq_len, n_expert,
+                                             top_k, int(sigmoid_mode), int(normalize_selected), scale,
+                                             0.0 if adaptive_top_p is None else adaptive_top_p, _p(ids), _p(w), _p(cnt)))
+    return ids, w, cnt
+
+
+def router_logits_f32(router_w, h) -> np.ndarray:
+    w, h = _f32(router_w), _f32(h).ravel()
+    out = np.empty(w.shape[0], np.float32)
+    check(load().rnb_b200_router_logits_f32(_p(w), w.shape[0], w.shape[1], _p(h), _p(out)))
+    return out
+
+
+def qwen35_sparse_experts(gate, up, down, route_weights, down_quant, n_ff, n_embd, x) -> np.ndarray:
+    n = len(gate)
+    keep = [_u8(a) for a in list(gate) + list(up) + list(down)]
+    arr = C.c_void_p * n
+    g = arr(*[a.ctypes.data for a in keep[:n]])
+    u = arr(*[a.ctypes.data for a in keep[n:2 * n]])
+    d = arr(*[a.ctypes.data for a in keep[2 * n:]])
+    rw, x = _f32(route_weights).ravel(), _f32(x).ravel()
+    out = np.empty(n_embd, np.float32)
+    check(load().rnb_b200_qwen35_sparse_experts(g, u, d, keep[0].size if n else 0, keep[2 * n].size if n else 0, _p(rw), n,
+                                                down_quant, n_ff, n_embd, _p(x), _p(out)))
+    return out
+
+
+def qwen35_register_moe_layer(gate_all, up_all, down_all, down_quant, n_ff, n_embd) -> bool:
+    g, u, d = _u8(gate_all), _u8(up_all), _u8(down_all)
+    fitted = C.c_int()
+    check(load().rnb_b200_qwen35_register_moe_layer(_p(g), g.size, _p(u), u.size, _p(d), d.size, down_quant, n_ff,
+                                                    n_embd, C.byref(fitted)))
+    return bool(fitted.value)
+
+
+# ---- glue ----------------------------------------------------------------------------------
+def rms_norm_rows_f32(x, weight, eps: float) -> np.ndarray:
+    x, w = _f32(x), _f32(weight).ravel()
+    out = np.empty_like(x)
+    check(load().rnb_b200_rms_norm_rows_f32(_p(x), _p(w), w.size, x.size // max(w.size, 1), eps, _p(out)))
+    return out
+
+
+def rope_f32_inplace(data: np.ndarray, pos_start: int, head_dim: int, dim: int, theta: float, neox=False) -> None:
+    assert data.dtype == np.float32 and data.flags["C_CONTIGUOUS"]
+    check(load().rnb_b200_rope_f32_inplace(_p(data), data.size, pos_start, head_dim, dim, theta, int(neox)))
+
+
+def activation_mul_f32_inplace(gate: np.ndarray, up) -> None:
+    assert gate.dtype == np.float32 and gate.flags["C_CONTIGUOUS"]
+    up = _f32(up).ravel()
+    check(load().rnb_b200_activation_mul_f32_inplace(_p(gate), _p(up), gate.size))
+
+
+# ---- expert-cache bookkeeping --------------------------------------------------------------
+def evaluate_expert_bundle_admission(missing_bytes, eviction_reload_bytes, predicted_future_reuses,
+                                     replaces_temp_upload) -> bool:
+    a = _lib.BundleAdmission(missing_bytes, eviction_reload_bytes, predicted_future_reuses, int(replaces_temp_upload))
+    return bool(load().rnb_b200_evaluate_expert_bundle_admission(C.byref(a)))
+
+
+def resident_limit_for(total_bytes: int, free_bytes: int) -> int:
+    return int(load().rnb_b200_resident_limit_for(total_bytes, free_bytes))
+
+
+def dev_error_flag() -> int:
+    f = C.c_int()
+    check(load().rnb_b200_dev_error_flag(C.byref(f)))
+    return f.value

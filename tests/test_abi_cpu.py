@@ -1,0 +1,103 @@
+"""CPU-side checks of the drop-in boundary: the library loads, exports every symbol the
+header declares, validates shapes with the reference's messages before touching CUDA, and
+fails loudly (no fallback) when no GPU is present.  No compute runs here."""
+import ctypes as C
+import re
+import subprocess
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+@pytest.fixture(scope="module")
+def lib():
+    from runnburn_b200 import build
+    build.build_library()
+    import runnburn_b200
+    return runnburn_b200.load()
+
+
+def test_library_exports_every_declared_symbol(lib):
+    header = (ROOT / "include" / "rnb_b200.h").read_text()
+    header = re.sub(r"/\*.*?\*/", "", header, flags=re.S)
+    declared = sorted(set(re.findall(r"\b(rnb_b200_[a-z0-9_]+)\s*\(", header)))
+    assert len(declared) >= 50
+    exported = subprocess.run(["nm", "-D", "--defined-only", str(ROOT / "runnburn_b200" / "librnb_b200.so")],
+                              capture_output=True, text=True, check=True).stdout
+    have = set(re.findall(r" T (rnb_b200_[a-z0-9_]+)", exported))
+    missing = [s for s in declared if s not in have]
+    assert not missing, f"declared in include/rnb_b200.h but not exported: {missing}"
+    for s in declared:
+        assert hasattr(lib, s)
+
+
+def test_library_does_not_link_the_oracle(lib):
+    deps = subprocess.run(["ldd", str(ROOT / "runnburn_b200" / "librnb_b200.so")], capture_output=True, text=True).stdout
+    assert "oracle" not in deps
+    for f in (ROOT / "runnburn_b200").rglob("*"):
+        if f.suffix in (".py", ".cu", ".cuh", ".hpp", ".inc"):
+            text = f.read_text()
+            assert "import oracle" not in text and "rnb_oracle" not in text, f
+
+
+def test_shape_errors_use_the_reference_messages(lib):
+    import runnburn_b200 as r
+    from runnburn_b200 import ops
+    z = np.zeros
+    cases = [
+        (lambda: ops.q4k_gemv(z(144, np.uint8), 1, 255, z(255, np.float32)), "Q4_K cols must be divisible by 256, got 255"),
+        (lambda: ops.q4k_gemv(z(100, np.uint8), 1, 256, z(256, np.float32)), "Q4_K weight byte mismatch: got 100, expected 144"),
+        (lambda: ops.q4k_gemv(z(144, np.uint8), 1, 256, z(128, np.float32)), "Q4_K input length mismatch: got 128, expected 256"),
+        (lambda: ops.q6k_gemv(z(209, np.uint8), 1, 256, z(256, np.float32)), "Q6_K weight byte mismatch: got 209, expected 210"),
+        (lambda: ops.q8_0_gemv(z(34, np.uint8), 1, 33, z(33, np.float32)), "Q8_0 cols must be divisible by 32, got 33"),
+        (lambda: ops.moe_route_topk_f32(z(7, np.float32), None, 1, 8, 2), "CUDA MoE route logits mismatch: got=7 expected=8"),
+        (lambda: ops.moe_route_topk_f32(z(8, np.float32), None, 1, 8, 9), "invalid CUDA MoE route shape: seq_len=1 n_expert=8 top_k=9"),
+        (lambda: ops.attention_decode_hd128(z(256, np.float32), z(128, np.uint16), z(128, np.uint16), 1, 3, 2, 1.0),
+         "attention: num_heads(3) must be a multiple of num_kv_heads(2)"),
+    ]
+    for call, msg in cases:
+        with pytest.raises(r.RnbError) as e:
+            call()
+        assert e.value.status == 2 and str(e.value) == msg
+
+
+def test_residency_budget_rule(lib):
+    """DeviceResidencyPlan / default_device_dynamic_reserve_bytes
+    (crates/rnb-memory/src/device_residency.rs:40-96)."""
+    from runnburn_b200 import ops
+    MiB, GiB = 1 << 20, 1 << 30
+    assert ops.resident_limit_for(24 * GiB, 23 * GiB) == 23 * GiB - 1536 * MiB    # 24/16 = 1.5 GiB
+    assert ops.resident_limit_for(4 * GiB, 4 * GiB) == 4 * GiB - 512 * MiB         # floor 512 MiB
+    assert ops.resident_limit_for(192 * GiB, 180 * GiB) == 178 * GiB               # cap 2 GiB
+    assert ops.resident_limit_for(8 * GiB, 256 * MiB) == 0                         # saturating
+    assert ops.resident_limit_for(17 * GiB, 17 * GiB) == 17 * GiB - 1280 * MiB     # 1.0625 GiB -> 1.25 GiB
+
+
+def test_expert_bundle_admission_rule(lib):
+    """admit iff missing*(reuses + [replaces temp upload]) > missing + eviction_reload, strictly
+    (crates/rnb-memory/src/sparse_expert_cache.rs:221-245)."""
+    from runnburn_b200 import ops
+    adm = ops.evaluate_expert_bundle_admission
+    assert not adm(100, 0, 1, False)      # 100 > 100 is false: strict
+    assert adm(100, 0, 2, False)
+    assert adm(100, 0, 1, True)           # the current lookup's temp upload counts as one reuse
+    assert not adm(100, 100, 1, True)     # 200 > 200 false
+    assert adm(100, 99, 1, True)
+    assert not adm(0, 0, 10, True)        # nothing missing: nothing to admit
+    assert adm(2 ** 63, 2 ** 63, 4, False)  # 128-bit arithmetic, no wrap
+
+
+def test_compute_fails_loudly_without_a_gpu(lib):
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("a GPU is present")
+    import runnburn_b200 as r
+    from runnburn_b200 import ops
+    with pytest.raises(r.RnbError) as e:
+        ops.q4k_gemv(np.zeros(144, np.uint8), 1, 256, np.zeros(256, np.float32))
+    assert e.value.status == 4 and "no CPU fallback" in str(e.value)
+    with pytest.raises(r.RnbError):
+        r.Decoder(r.ModelConfig(n_layer=1, hidden=256, n_head=2, n_kv_head=1, n_ff=256, vocab=32, max_ctx=8))

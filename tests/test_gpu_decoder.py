@@ -1,0 +1,135 @@
+"""Token-level parity: the device-resident decoder against the oracle's model loop on small
+random-init stacks (the oracle takes seconds at these sizes), 64 greedy steps."""
+import numpy as np
+import pytest
+
+import oracle as orc
+from synth import llama_description, max_rel_err, moe_description
+
+pytestmark = pytest.mark.gpu
+
+
+def _run(desc, prompt, n_steps, max_ctx):
+    import runnburn_b200 as r
+    cfg = {k: v for k, v in desc["cfg"].items()}
+    dec = r.Decoder(r.ModelConfig(max_ctx=max_ctx, **cfg))
+    dec.load_description(desc)
+    ref = orc.Model(desc, max_ctx)
+    return dec, ref
+
+
+def _greedy(dec, ref, prompt, n_steps):
+    """Feeds the prompt token by token, then n_steps greedy tokens; returns per-step records."""
+    gpu_ids, cpu_ids, margins, errs = [], [], [], []
+    tok_g = tok_c = None
+    pos = 0
+    for t in prompt:
+        tok_g, lg = dec.step(t, pos, want_logits=True)
+        lc = ref.decode(t, pos)
+        tok_c = orc.argmax_last(lc)
+        errs.append(max_rel_err(lg, lc))
+        pos += 1
+    for _ in range(n_steps):
+        gpu_ids.append(tok_g)
+        cpu_ids.append(tok_c)
+        ng, lg = dec.step(tok_g, pos, want_logits=True)
+        lc = ref.decode(tok_c, pos)
+        top2 = np.partition(lc, -2)[-2:]
+        margins.append(float(top2[1] - top2[0]))
+        if tok_g == tok_c:
+            errs.append(max_rel_err(lg, lc))
+        assert ng == orc.argmax_last(lg)            # device argmax follows the last-maximum rule
+        tok_g, tok_c = ng, orc.argmax_last(lc)
+        pos += 1
+    return gpu_ids, cpu_ids, margins, errs
+
+
+def test_llama_greedy_64_steps_identical(tmp_path):
+    desc = llama_description(seed=0, n_layer=3, hidden=512, n_head=4, n_kv_head=2, n_ff=1024, vocab=2048)
+    rng = np.random.default_rng(0)
+    prompt = rng.integers(0, 2048, 24).tolist()
+    dec, ref = _run(desc, prompt, 64, 128)
+    gpu_ids, cpu_ids, margins, errs = _greedy(dec, ref, prompt, 64)
+    first = next((i for i, (a, b) in enumerate(zip(gpu_ids, cpu_ids)) if a != b), None)
+    assert first is None, f"greedy ids diverge at step {first}: gpu={gpu_ids[first]} cpu={cpu_ids[first]} " \
+                          f"logit margin there={margins[max(first - 1, 0)]:.3e}"
+    assert max(errs) <= 5e-3      # logits after a whole stack: looser than one matvec (1e-3)
+    # KV cache: K/V rows are f16 roundings of nearly identical f32 values
+    n_pos = len(prompt) + 64
+    for layer in range(3):
+        kg, vg = dec.read_kv(layer, n_pos)
+        kc, vc = ref.kv_cache(layer, n_pos)
+        for g, c in ((kg, kc), (vg, vc)):
+            gf, cf = g.view(np.float16).astype(np.float32), c.view(np.float16).astype(np.float32)
+            assert max_rel_err(gf, cf) <= 5e-3
+        if layer == 0:
+            assert np.mean(kg == kc) > 0.999 and np.mean(vg == vc) > 0.999
+    st = dec.stats()
+    assert st["launches_per_step"] == 1 + 3 * 11 + 3
+    dec.close()
+    ref.close()
+
+
+def test_llama_first_layer_kv_bits_and_embedding_exact():
+    desc = llama_description(seed=5, n_layer=1, hidden=256, n_head=2, n_kv_head=1, n_ff=512, vocab=512)
+    dec, ref = _run(desc, [], 0, 16)
+    for pos, tok in enumerate([3, 500, 17, 17]):
+        dec.step(tok, pos)
+        ref.decode(tok, pos)
+    kg, vg = dec.read_kv(0, 4)
+    kc, vc = ref.kv_cache(0, 4)
+    assert np.mean(kg == kc) > 0.995 and np.mean(vg == vc) > 0.995
+    dec.close()
+    ref.close()
+
+
+def test_moe_decoder_expert_ids_and_tokens():
+    desc = moe_description(seed=1, n_layer=2, hidden=512, n_head=4, n_kv_head=2, vocab=1024, n_expert=16,
+                           n_expert_used=4, n_ff_expert=256)
+    rng = np.random.default_rng(1)
+    prompt = rng.integers(0, 1024, 8).tolist()
+    dec, ref = _run(desc, prompt, 16, 64)
+    pos, tok_g, tok_c = 0, None, None
+    mismatched_layers = 0
+    for t in prompt + [None] * 16:
+        if t is None:
+            assert tok_g == tok_c
+            t = tok_g
+        tok_g, lg = dec.step(t, pos, want_logits=True)
+        lc = ref.decode(t, pos)
+        tok_c = orc.argmax_last(lc)
+        for layer in range(2):
+            if not np.array_equal(dec.read_expert_ids(layer), ref.expert_ids(layer)):
+                mismatched_layers += 1
+        assert max_rel_err(lg, lc) <= 1e-2
+        pos += 1
+    # layer 0 sees bit-identical inputs; deeper layers can differ only through near-tied logits
+    assert mismatched_layers == 0
+    dec.close()
+    ref.close()
+
+
+def test_step_dev_chain_matches_host_steps():
+    desc = llama_description(seed=2, n_layer=2, hidden=256, n_head=2, n_kv_head=1, n_ff=512, vocab=512)
+    import runnburn_b200 as r
+    a = r.Decoder(r.ModelConfig(max_ctx=64, **desc["cfg"]))
+    a.load_description(desc)
+    b = r.Decoder(r.ModelConfig(max_ctx=64, **desc["cfg"]))
+    b.load_description(desc)
+    tok = a.step(7, 0)
+    ids_a = [tok]
+    for pos in range(1, 20):
+        tok = a.step(tok, pos)
+        ids_a.append(tok)
+    b.step(7, 0)                 # leaves the argmax on the device
+    b.step_dev(pos=1, chain=True)
+    for _ in range(18):
+        b.step_dev()
+    b.sync()
+    # the chained run consumed the same tokens: its KV cache equals the host-driven one
+    for layer in range(2):
+        ka, va = a.read_kv(layer, 20)
+        kb, vb = b.read_kv(layer, 20)
+        assert np.array_equal(ka, kb) and np.array_equal(va, vb)
+    a.close()
+    b.close()

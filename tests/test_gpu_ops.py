@@ -1,0 +1,331 @@
+"""Parity of the CUDA operators with the CPU oracle, through the C ABI, on seeded inputs.
+
+Bars (BASELINE north star): Q8_K activation quantisation and MoE routing bit-exact;
+matvec and attention within max relative error 1e-3 (fp32 accumulate).
+"""
+import numpy as np
+import pytest
+
+import oracle as orc
+from synth import Q4_K, Q6_K, Q8_0, max_rel_err, quantized, random_blocks
+
+pytestmark = pytest.mark.gpu
+
+TOL = 1e-3  # max relative error, matvec and attention
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from runnburn_b200 import build, ops
+    build.build_library()
+    ops.open()
+    return ops
+
+
+# ---- Q8_K -------------------------------------------------------------------------------------
+def _q8k_equal(a, b):
+    return a.tobytes() == b.tobytes()
+
+
+def test_q8k_reference_fixtures_on_device(ops):
+    x = np.zeros((5, 256), np.float32)
+    x[1, 0] = 127.0
+    x[1, 1:7] = [-0.5, -1.5, -2.5, 0.5, 1.5, 2.5]
+    x[2, 0], x[2, 1] = 127.0, -127.0
+    x[3, 0], x[3, 1] = -127.0, 127.0
+    x[4, 15], x[4, 16], x[4, 255] = -1.0, -2.0, 127.0
+    got = ops.quantize_q8k(x.ravel())
+    assert _q8k_equal(got, orc.quantize_q8k(x.ravel()))
+    assert got[0]["d"] == 0.0 and got[1]["d"] == -1.0 and got[1]["qs"][1:7].tolist() == [0, 2, 2, 0, -2, -2]
+    assert got[2]["qs"][:2].tolist() == [-127, 127] and got[3]["d"] == 1.0
+    assert got[4]["bsums"][0] == 1 and got[4]["bsums"][1] == 2 and got[4]["bsums"][15] == -127
+
+
+@pytest.mark.parametrize("n", [256, 4096, 14336, 28672])
+def test_q8k_bit_exact(ops, n):
+    rng = np.random.default_rng(n)
+    for scale in (1.0, 1e-6, 3e4):
+        x = (rng.standard_normal(n) * scale).astype(np.float32)
+        x[rng.integers(0, n, 16)] = 0.0
+        assert _q8k_equal(ops.quantize_q8k(x), orc.quantize_q8k(x))
+    idx = np.arange(n)
+    x = (((idx * 73 + 19) % 2001).astype(np.float32) - 1000.0)   # many ties and repeated maxima
+    assert _q8k_equal(ops.quantize_q8k(x), orc.quantize_q8k(x))
+    x = np.repeat(np.float32([2.5, -2.5]), n // 2)               # |x| all equal: first element decides the sign
+    assert _q8k_equal(ops.quantize_q8k(x), orc.quantize_q8k(x))
+
+
+def test_q8k_empty_and_ragged(ops):
+    import runnburn_b200 as r
+    assert ops.quantize_q8k(np.zeros(0, np.float32)).size == 0
+    with pytest.raises(r.RnbError, match="divisible by 256"):
+        ops.quantize_q8k(np.zeros(255, np.float32))
+
+
+# ---- matvec -------------------------------------------------------------------------------------
+CONFIG1 = [(4096, 4096), (1024, 4096), (14336, 4096), (4096, 14336)]
+
+
+@pytest.mark.parametrize("rows,cols", CONFIG1)
+def test_q4k_gemv_config1_shapes(ops, rows, cols):
+    """BASELINE config 1: Llama-3-8B layer shapes, uniform quants/scales, |N(0,1e-3)| d/dmin, seed 0."""
+    rng = np.random.default_rng(0)
+    w = random_blocks(rng, Q4_K, rows, cols)
+    x = rng.standard_normal(cols).astype(np.float32)
+    ref = orc.gemv(Q4_K, w, x, rows, cols)
+    got = ops.q4k_gemv(w, rows, cols, x)
+    assert max_rel_err(got, ref) <= TOL
+    # linearity in the activation scale is exact for powers of two (Q8_K d scales, qs unchanged)
+    got2 = ops.q4k_gemv(w, rows, cols, x * np.float32(4.0))
+    assert np.array_equal(got2, got * np.float32(4.0))
+
+
+@pytest.mark.parametrize("t,rows,cols", [
+    (Q4_K, 1, 256), (Q4_K, 3, 256), (Q4_K, 130, 512), (Q4_K, 257, 768), (Q4_K, 2048, 768), (Q4_K, 768, 2048),
+    (Q6_K, 1, 256), (Q6_K, 5, 256), (Q6_K, 7, 768), (Q6_K, 130, 512), (Q6_K, 1024, 4096), (Q6_K, 4096, 14336),
+    (Q6_K, 515, 2048),
+    (Q8_0, 1, 32), (Q8_0, 3, 96), (Q8_0, 129, 256), (Q8_0, 1000, 4096),
+])
+def test_gemv_shapes_and_ragged_tiles(ops, t, rows, cols):
+    rng = np.random.default_rng(rows * 131 + cols)
+    w = random_blocks(rng, t, rows, cols)
+    x = rng.standard_normal(cols).astype(np.float32)
+    ref = orc.gemv(t, w, x, rows, cols)
+    got = ops.gemv(t, w, rows, cols, x)
+    assert max_rel_err(got, ref) <= TOL
+
+
+@pytest.mark.parametrize("t", [Q4_K, Q6_K, Q8_0])
+def test_gemv_on_quantised_gaussian_weights(ops, t):
+    rng = np.random.default_rng(7)
+    rows, cols = 384, 1024
+    _, w = quantized(rng, t, rows, cols)
+    x = rng.standard_normal(cols).astype(np.float32)
+    assert max_rel_err(ops.gemv(t, w, rows, cols, x), orc.gemv(t, w, x, rows, cols)) <= TOL
+
+
+def test_gemv_misaligned_weight_slice_takes_the_plain_load_path(ops):
+    """Weights that start at an odd byte inside a resident range are not 16-byte aligned on the
+    device either; the kernel must fall back to plain loads (reference: odd-offset rows are
+    bit-identical, crates/rnb-cpu/src/gemm/quant_gemv.rs:1257-1296)."""
+    rng = np.random.default_rng(3)
+    rows, cols = 64, 512
+    for t in (Q4_K, Q6_K, Q8_0):
+        w = random_blocks(rng, t, rows, cols)
+        x = rng.standard_normal(cols).astype(np.float32)
+        aligned = ops.gemv(t, w, rows, cols, x)
+        backing = np.zeros(w.size + 64, np.uint8)
+        backing[2:2 + w.size] = w
+        ops.prewarm_q4k_weights([backing])            # one resident range; the slice below lives inside it
+        shifted = ops.gemv(t, backing[2:2 + w.size], rows, cols, x)
+        assert np.array_equal(aligned, shifted)
+
+
+def test_gemv_batch_is_seq_major_and_matches_single_token_bits(ops):
+    rng = np.random.default_rng(5)
+    rows, cols, seq = 300, 512, 5
+    for t, batch in ((Q4_K, ops.q4k_gemv_batch), (Q6_K, ops.q6k_gemv_batch)):
+        w = random_blocks(rng, t, rows, cols)
+        x = rng.standard_normal((seq, cols)).astype(np.float32)
+        got = batch(w, rows, cols, x)
+        ref = orc.gemv(t, w, x, rows, cols, seq_len=seq)
+        assert max_rel_err(got, ref) <= TOL
+        for s in range(seq):   # one accumulation order for decode and prefill-of-1
+            assert np.array_equal(got[s * rows:(s + 1) * rows], ops.gemv(t, w, rows, cols, x[s]))
+
+
+def test_q6k_gemv_argmax_tie_rule(ops):
+    rng = np.random.default_rng(11)
+    rows, cols = 1000, 512
+    w = random_blocks(rng, Q6_K, rows, cols).reshape(rows, -1)
+    w[777] = w[123]                      # two identical rows -> exact tie if they are the maximum
+    x = rng.standard_normal(cols).astype(np.float32)
+    y = orc.gemv(Q6_K, w.ravel(), x, rows, cols)
+    w[123] = w[int(np.argmax(y))]
+    w[777] = w[123]
+    y = ops.q6k_gemv(w.ravel(), rows, cols, x)
+    idx, val = ops.q6k_gemv_argmax(w.ravel(), rows, cols, x)
+    assert idx == orc.argmax_last(y) and val == y[idx]
+    assert idx == max(i for i in range(rows) if y[i] == y.max())
+
+
+def test_resident_cache_counters_and_eviction(ops):
+    ops.reset_state_for_engine_init()
+    rng = np.random.default_rng(1)
+    rows, cols = 256, 512
+    ws = [random_blocks(rng, Q4_K, rows, cols) for _ in range(3)]
+    x = rng.standard_normal(cols).astype(np.float32)
+    refs = [orc.gemv(Q4_K, w, x, rows, cols) for w in ws]
+    ops.set_resident_limit(2 * ws[0].size + 100)          # room for two of the three
+    try:
+        for rnd in range(2):
+            for w, ref in zip(ws, refs):
+                assert max_rel_err(ops.q4k_gemv(w, rows, cols, x), ref) <= TOL
+        s = ops.cuda_cache_snapshot()
+        assert s["lookups"] == 6 and s["hits"] == 0 and s["misses"] == 6 and s["evictions"] >= 4
+        assert s["resident_entries"] == 2 and s["resident_bytes"] == 2 * ws[0].size
+        ops.q4k_gemv(ws[2], rows, cols, x)
+        assert ops.cuda_cache_snapshot()["hits"] == 1
+        ops.set_resident_limit(100)                        # nothing fits: transient uploads still compute
+        ops.clear_q4k_cache()
+        assert max_rel_err(ops.q4k_gemv(ws[0], rows, cols, x), refs[0]) <= TOL
+        assert ops.cuda_cache_snapshot()["transient_uploads"] >= 1
+    finally:
+        ops.set_resident_limit(0)
+        ops.reset_state_for_engine_init()
+
+
+# ---- attention ----------------------------------------------------------------------------------
+@pytest.mark.parametrize("heads,kvh,kv_len", [(32, 8, 1), (32, 8, 7), (32, 8, 333), (32, 8, 4096), (32, 4, 1025),
+                                              (64, 8, 2000), (8, 8, 65), (6, 2, 100)])
+def test_attention_decode_hd128(ops, heads, kvh, kv_len):
+    rng = np.random.default_rng(heads * 1000 + kv_len)
+    q = rng.standard_normal(heads * 128).astype(np.float32)
+    k = orc.f32_to_f16_bits(rng.standard_normal(kv_len * kvh * 128))
+    v = orc.f32_to_f16_bits(rng.standard_normal(kv_len * kvh * 128))
+    scale = 1.0 / np.sqrt(128.0)
+    ref = orc.attention_decode(q, k, v, heads, kvh, 128, kv_len, scale)
+    got = ops.attention_decode_hd128(q, k, v, kv_len, heads, kvh, scale)
+    assert max_rel_err(got, ref) <= TOL
+    assert np.max(np.abs(got - ref)) < 1e-4        # the reference's own CUDA tests: max_diff < 1e-4
+
+
+def test_attention_decode_cached_appends_only_new_rows(ops):
+    rng = np.random.default_rng(21)
+    heads, kvh, cap = 8, 2, 600
+    k = orc.f32_to_f16_bits(rng.standard_normal(cap * kvh * 128))
+    v = orc.f32_to_f16_bits(rng.standard_normal(cap * kvh * 128))
+    scale = 1.0 / np.sqrt(128.0)
+    ops.clear_decode_attention_kv_cache()
+    before = ops.cuda_cache_snapshot()["h2d_bytes"]
+    for kv_len in (1, 2, 3, 300, 301, 600):
+        q = rng.standard_normal(heads * 128).astype(np.float32)
+        got = ops.attention_decode_cached(3, q, k, v, kv_len, heads, kvh, 128, scale)
+        ref = orc.attention_decode(q, k, v, heads, kvh, 128, kv_len, scale)
+        assert max_rel_err(got, ref) <= TOL
+    moved = ops.cuda_cache_snapshot()["h2d_bytes"] - before
+    assert moved == 2 * 600 * kvh * 128 * 2 + 6 * heads * 128 * 4   # each KV row crossed PCIe once
+    ops.clear_decode_attention_kv_cache()
+
+
+def test_attention_prefill_causal(ops):
+    rng = np.random.default_rng(8)
+    heads, kvh, seq, kv_len = 8, 2, 37, 50
+    q = rng.standard_normal(seq * heads * 128).astype(np.float32)
+    k = rng.standard_normal(kv_len * kvh * 128).astype(np.float32)
+    v = rng.standard_normal(kv_len * kvh * 128).astype(np.float32)
+    scale = 1.0 / np.sqrt(128.0)
+    ref = orc.attention_prefill(q, k, v, seq, kv_len, heads, kvh, 128, scale)
+    got = ops.attention_prefill_flash_hd128(q, k, v, seq, kv_len, heads, kvh, scale)
+    assert max_rel_err(got, ref) <= TOL
+
+
+# ---- glue ---------------------------------------------------------------------------------------
+def test_rms_norm_rope_silu(ops):
+    rng = np.random.default_rng(4)
+    x = rng.standard_normal((3, 4096)).astype(np.float32) * 3
+    w = rng.standard_normal(4096).astype(np.float32)
+    got = ops.rms_norm_rows_f32(x, w, 1e-5)
+    ref = orc.rms_norm(x, w, 1e-5)
+    assert np.max(np.abs(got - ref) / np.maximum(np.abs(ref), 1e-6)) <= 2e-7     # <= 1 ulp of the rms
+    for neox in (False, True):
+        d = rng.standard_normal(2 * 1024).astype(np.float32)
+        ref = orc.rope(d, 4095, 128, 1024, 5e5, neox=neox)
+        ops.rope_f32_inplace(d, 4095, 128, 1024, 5e5, neox=neox)
+        assert np.array_equal(d, ref)                                           # same table, same mul/add order
+    g = rng.standard_normal(1024).astype(np.float32) * 4
+    u = rng.standard_normal(1024).astype(np.float32)
+    ref = orc.silu_mul(g, u)
+    ops.activation_mul_f32_inplace(g, u)
+    assert np.max(np.abs(g - ref) / np.maximum(np.abs(ref), 1e-12)) <= 2.4e-7    # 2 ulp
+
+
+def test_fused_qkv_rope_decode(ops):
+    rng = np.random.default_rng(6)
+    n_embd, heads, kvh, pos = 1024, 8, 2, 77
+    tq, wq = quantized(rng, Q4_K, heads * 128, n_embd)
+    tk, wk = quantized(rng, Q4_K, kvh * 128, n_embd)
+    tv, wv = quantized(rng, Q6_K, kvh * 128, n_embd)
+    x = rng.standard_normal(n_embd).astype(np.float32)
+    q, kb, vb = ops.dense_attention_qkv_rope_hd128_decode(wq, wk, wv, heads * 128, kvh * 128, n_embd, heads, kvh,
+                                                          5e5, pos, x, tq, tk, tv)
+    q_ref = orc.rope(orc.gemv(Q4_K, wq, x, heads * 128, n_embd), pos, 128, heads * 128, 5e5)
+    k_ref = orc.rope(orc.gemv(Q4_K, wk, x, kvh * 128, n_embd), pos, 128, kvh * 128, 5e5)
+    v_ref = orc.gemv(Q6_K, wv, x, kvh * 128, n_embd)
+    assert max_rel_err(q, q_ref) <= TOL
+    assert max_rel_err(kb.view(np.float16).astype(np.float32), orc.f32_to_f16_bits(k_ref).view(np.float16).astype(np.float32)) <= 2e-3
+    assert max_rel_err(vb.view(np.float16).astype(np.float32), orc.f32_to_f16_bits(v_ref).view(np.float16).astype(np.float32)) <= 2e-3
+    # exactness of the rotation + rounding given the device's own matvec output
+    qd = ops.q4k_gemv(wq, heads * 128, n_embd, x)
+    assert np.array_equal(q, orc.rope(qd, pos, 128, heads * 128, 5e5))
+    kd = ops.q4k_gemv(wk, kvh * 128, n_embd, x)
+    assert np.array_equal(kb, orc.f32_to_f16_bits(orc.rope(kd, pos, 128, kvh * 128, 5e5)))
+    assert np.array_equal(vb, orc.f32_to_f16_bits(ops.q6k_gemv(wv, kvh * 128, n_embd, x)))
+
+
+def test_dense_silu_ffn(ops):
+    rng = np.random.default_rng(9)
+    n_embd, n_ff, seq = 512, 1024, 3
+    _, g = quantized(rng, Q4_K, n_ff, n_embd)
+    _, u = quantized(rng, Q4_K, n_ff, n_embd)
+    for dt in (Q4_K, Q6_K):
+        _, d = quantized(rng, dt, n_embd, n_ff)
+        x = rng.standard_normal((seq, n_embd)).astype(np.float32)
+        got = ops.dense_q4k_silu_ffn_batch(g, u, d, dt, n_ff, n_embd, seq, x)
+        for s in range(seq):
+            act = orc.silu_mul(orc.gemv(Q4_K, g, x[s], n_ff, n_embd), orc.gemv(Q4_K, u, x[s], n_ff, n_embd))
+            ref = orc.gemv(dt, d, act, n_embd, n_ff)
+            assert max_rel_err(got[s * n_embd:(s + 1) * n_embd], ref) <= 2 * TOL   # two chained matvecs
+
+
+# ---- MoE ----------------------------------------------------------------------------------------
+def test_moe_routing_bit_exact(ops):
+    ids, w, cnt = ops.moe_route_topk_f32(np.float32([1.0, 4.0, 4.0, -2.0, 3.0]), None, 1, 5, 3)
+    assert ids.tolist() == [1, 2, 4] and cnt.tolist() == [3]
+    rng = np.random.default_rng(12)
+    for n_expert, k, seq in ((128, 8, 9), (16, 4, 3), (256, 8, 2), (8, 8, 2), (60, 1, 4)):
+        lg = rng.standard_normal((seq, n_expert)).astype(np.float32)
+        lg[0, :] = np.round(lg[0, :] * 2) / 2                  # many exact ties
+        lg[-1, :] = 0.25                                        # all tied
+        ids, w, cnt = ops.moe_route_topk_f32(lg, None, seq, n_expert, k)
+        for s in range(seq):
+            rid, rw = orc.moe_route_topk(lg[s], k)
+            assert np.array_equal(ids[s * k:(s + 1) * k], rid)
+            assert np.array_equal(w[s * k:(s + 1) * k].view(np.uint32), rw.view(np.uint32))
+    import runnburn_b200 as r
+    with pytest.raises(r.RnbError) as e:
+        ops.moe_route_topk_f32(np.zeros(8, np.float32), None, 1, 8, 2, sigmoid_mode=True)
+    assert e.value.status == 1
+
+
+def test_router_logits_bit_exact(ops):
+    rng = np.random.default_rng(13)
+    for n_expert, hidden in ((128, 2048), (16, 512), (5, 256)):
+        w = rng.standard_normal((n_expert, hidden)).astype(np.float32)
+        h = rng.standard_normal(hidden).astype(np.float32)
+        assert np.array_equal(ops.router_logits_f32(w, h).view(np.uint32), orc.gemv_f32(w, h).view(np.uint32))
+
+
+def test_sparse_experts(ops):
+    rng = np.random.default_rng(14)
+    n_embd, n_ff, n_expert, k = 512, 256, 12, 4
+    _, gate_all = quantized(rng, Q4_K, n_expert * n_ff, n_embd)
+    _, up_all = quantized(rng, Q4_K, n_expert * n_ff, n_embd)
+    gs = n_ff * orc.row_bytes(Q4_K, n_embd)
+    x = rng.standard_normal(n_embd).astype(np.float32)
+    lg = rng.standard_normal(n_expert).astype(np.float32)
+    ids, rw = orc.moe_route_topk(lg, k)
+    for dt in (Q4_K, Q6_K):
+        _, down_all = quantized(rng, dt, n_expert * n_embd, n_ff)
+        ds = n_embd * orc.row_bytes(dt, n_ff)
+        assert ops.qwen35_register_moe_layer(gate_all, up_all, down_all, dt, n_ff, n_embd)
+        before = ops.cuda_cache_snapshot()
+        gate = [gate_all[e * gs:(e + 1) * gs] for e in ids]
+        up = [up_all[e * gs:(e + 1) * gs] for e in ids]
+        down = [down_all[e * ds:(e + 1) * ds] for e in ids]
+        ref = orc.moe_experts(gate, up, down, rw, dt, n_ff, n_embd, x)
+        got = ops.qwen35_sparse_experts(gate, up, down, rw, dt, n_ff, n_embd, x)
+        assert max_rel_err(got, ref) <= 2 * TOL
+        after = ops.cuda_cache_snapshot()
+        assert after["uploads"] == before["uploads"] and after["hits"] - before["hits"] == 3 * k   # slices of the registered layer
+    ops.reset_state_for_engine_init()
