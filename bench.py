@@ -1,0 +1,357 @@
+#!/usr/bin/env python
+"""Headline benchmark: batch-1 greedy decode tok/s of a random-init Q4_K_M Llama stack.
+
+    python bench.py --gpus N --steps K --warmup W [--impl reference] [--workload NAME]
+
+N = 1 runs BASELINE config 2 (Llama-3-8B shape, 4096-token context already in the fp16 KV
+cache); N > 1 runs BASELINE config 5 (Llama-3-70B shape, context 32768) row-sharded over N
+GPUs, one process per GPU, launched by torch.distributed.run.  A step is one decode token.
+One JSON line is printed by rank 0.  `--impl reference` times the CPU oracle (the
+restatement of the reference's rnb-cpu path; the Rust original cannot be built here) on a
+bounded sample of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+WORKLOADS = {
+    # name: (shape, context, description)
+    "llama3-8b-q4km-ctx4096": (dict(n_layer=32, hidden=4096, n_head=32, n_kv_head=8, n_ff=14336, vocab=128256), 4096),
+    "llama3-70b-q4km-ctx32768": (dict(n_layer=80, hidden=8192, n_head=64, n_kv_head=8, n_ff=28672, vocab=128256), 32768),
+    "tiny-llama-ctx256": (dict(n_layer=2, hidden=512, n_head=4, n_kv_head=2, n_ff=1024, vocab=2048), 256),
+}
+METRIC = "decode_tok_per_s_batch1"
+UNIT = "tok/s"
+
+
+def row_bytes(t: int, cols: int) -> int:
+    return {12: cols // 256 * 144, 14: cols // 256 * 210}[t]
+
+
+def q8k_bytes(cols: int) -> int:
+    return cols // 256 * 292
+
+
+def algorithmic_bytes_per_token(shape: dict, ctx: int) -> dict:
+    """Bytes one decode token must move (Q4_K_M convention: attn_v, ffn_down, LM head in
+    Q6_K): weights once, the visible KV rows once, activations (Q8_K in, f32 out)."""
+    H, qd, kvd, ff, V, L = shape["hidden"], shape["n_head"] * 128, shape["n_kv_head"] * 128, shape["n_ff"], shape["vocab"], shape["n_layer"]
+    mats = [(12, qd, H), (12, kvd, H), (14, kvd, H), (12, H, qd), (12, ff, H), (12, ff, H), (14, H, ff)]
+    w_layer = sum(r * row_bytes(t, c) for t, r, c in mats)
+    act_layer = sum(q8k_bytes(c) + r * 4 for t, r, c in mats)
+    w = L * w_layer + V * row_bytes(14, H) + row_bytes(12, H)   # + LM head + one embedding row
+    act = L * act_layer + q8k_bytes(H) + V * 4
+    kv = L * 2 * (ctx + 1) * kvd * 2
+    return {"weights": w, "kv": kv, "activations": act, "total": w + kv + act}
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks / throttle reasons while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu = gpu_index
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        try:
+            f = tempfile.NamedTemporaryFile("w", suffix=".csv", delete=False)
+            self.path = f.name
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-i", str(self.gpu), "-lms", "100"], stdout=f, stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        try:
+            for line in open(self.path):
+                p = [c.strip() for c in line.split(",")]
+                if len(p) < 9:
+                    continue
+                try:
+                    sm.append(float(p[1]))
+                    mx.append(float(p[2]))
+                except ValueError:
+                    continue
+                for n, v in zip(names, p[5:9]):
+                    if v.lower().startswith("active"):
+                        reasons.add(n)
+            os.unlink(self.path)
+        except Exception:
+            pass
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# ------------------------------------------------------------------------------------------------
+# CPU arm: the oracle (restatement of rnb-cpu's x86 path) on a bounded sample of the workload.
+# One "step" = the decode work of one layer (norms, Q8_K, q/k/v/o/gate/up/down matvecs, RoPE,
+# f16 KV append, decode attention over the context) plus 1/n_layer of the LM head; a token is
+# n_layer such steps, so tok/s = 1 / (n_layer * layer_time + lm_head_time).
+# ------------------------------------------------------------------------------------------------
+def _blocks(rng, t, rows, cols):
+    if t == 12:
+        w = rng.integers(0, 256, size=(rows, cols // 256, 144), dtype=np.uint8)
+        d = np.abs(rng.standard_normal((rows, cols // 256, 2)) * 1e-3).astype(np.float16)
+        w[:, :, 0:4] = d.view(np.uint8).reshape(rows, cols // 256, 4)
+    else:
+        w = rng.integers(0, 256, size=(rows, cols // 256, 210), dtype=np.uint8)
+        d = (rng.standard_normal((rows, cols // 256, 1)) * 1e-3).astype(np.float16)
+        w[:, :, 208:210] = d.view(np.uint8).reshape(rows, cols // 256, 2)
+    return np.ascontiguousarray(w.reshape(-1))
+
+
+class CpuSample:
+    def __init__(self, shape: dict, ctx: int, seed: int = 0):
+        import oracle as orc
+        self.orc = orc
+        orc.build()
+        self.shape, self.ctx = shape, ctx
+        self.threads = orc.n_threads()
+        rng = np.random.default_rng(seed)
+        H, qd, kvd, ff = shape["hidden"], shape["n_head"] * 128, shape["n_kv_head"] * 128, shape["n_ff"]
+        self.mats = {n: (t, _blocks(rng, t, r, c), r, c) for n, t, r, c in (
+            ("q", 12, qd, H), ("k", 12, kvd, H), ("v", 14, kvd, H), ("o", 12, H, qd),
+            ("gate", 12, ff, H), ("up", 12, ff, H), ("down", 14, H, ff))}
+        # LM head: a slice of the rows is timed and scaled (the full matrix is 0.4-0.9 GB)
+        self.head_rows = min(shape["vocab"], 16384)
+        self.head = _blocks(rng, 14, self.head_rows, H)
+        self.x = rng.standard_normal(H).astype(np.float32)
+        self.norm = np.ones(H, np.float32)
+        self.k = rng.integers(0, 0x3C00, size=(ctx + 1) * kvd, dtype=np.uint16)
+        self.v = rng.integers(0, 0x3C00, size=(ctx + 1) * kvd, dtype=np.uint16)
+
+    def layer(self) -> float:
+        orc, s, T = self.orc, self.shape, self.threads
+        H, qd, kvd, ff = s["hidden"], s["n_head"] * 128, s["n_kv_head"] * 128, s["n_ff"]
+        t0 = time.perf_counter()
+        h = orc.rms_norm(self.x, self.norm, 1e-5)
+        q = orc.gemv(*self.mats["q"][:2], h, qd, H, threads=T)
+        k = orc.gemv(*self.mats["k"][:2], h, kvd, H, threads=T)
+        v = orc.gemv(*self.mats["v"][:2], h, kvd, H, threads=T)
+        q = orc.rope(q, self.ctx, 128, qd, 5e5)
+        k = orc.rope(k, self.ctx, 128, kvd, 5e5)
+        self.k[self.ctx * kvd:] = orc.f32_to_f16_bits(k)
+        self.v[self.ctx * kvd:] = orc.f32_to_f16_bits(v)
+        a = orc.attention_decode(q, self.k, self.v, s["n_head"], s["n_kv_head"], 128, self.ctx + 1,
+                                 1.0 / np.sqrt(128.0), threads=T)
+        x = self.x + orc.gemv(*self.mats["o"][:2], a, H, qd, threads=T)
+        h = orc.rms_norm(x, self.norm, 1e-5)
+        g = orc.gemv(*self.mats["gate"][:2], h, ff, H, threads=T)
+        u = orc.gemv(*self.mats["up"][:2], h, ff, H, threads=T)
+        act = orc.silu_mul(g, u)
+        x = x + orc.gemv(*self.mats["down"][:2], act, H, ff, threads=T)
+        return time.perf_counter() - t0
+
+    def lm_head(self) -> float:
+        t0 = time.perf_counter()
+        self.orc.gemv(14, self.head, self.x, self.head_rows, self.shape["hidden"], threads=self.threads)
+        return (time.perf_counter() - t0) * self.shape["vocab"] / self.head_rows
+
+    def tok_per_s(self, layer_s: float, head_s: float) -> float:
+        return 1.0 / (self.shape["n_layer"] * layer_s + head_s)
+
+    def describe(self) -> str:
+        return (f"one layer's decode work (7 matvecs on seeded uniform-quant blocks, RoPE, KV append, "
+                f"attention over {self.ctx + 1} f16 KV rows) and {self.head_rows} LM-head rows, "
+                f"scaled to {self.shape['n_layer']} layers + {self.shape['vocab']} vocab rows")
+
+
+def cpu_baseline(shape, ctx, reps: int, warmup: int):
+    s = CpuSample(shape, ctx)
+    for _ in range(max(warmup, 1)):
+        s.layer()
+    s.lm_head()
+    layer = [s.layer() for _ in range(max(reps, 1))]
+    head = [s.lm_head() for _ in range(3)]
+    return s, layer, head
+
+
+def run_reference(args, shape, ctx, name, rank, world):
+    """`--impl reference`: rank 0 times the CPU path on all host threads; other ranks idle."""
+    if rank != 0:
+        return None
+    s, layer, head = cpu_baseline(shape, ctx, args.steps, args.warmup)
+    total = sum(layer)
+    value = s.tok_per_s(total / len(layer), min(head))
+    cb = {"value": value, "unit": UNIT, "cores": s.threads, "kind": "port", "sample": s.describe()}
+    return {"impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": 1000.0 * total / len(layer), "higher_is_better": True,
+            "scaling": "strong" if args.gpus > 1 else "weak", "vs_baseline": None, "dtype": "int8xint4->int32, f32 accumulate",
+            "data": "synthetic", "config": {"workload": name, "step": "one layer sample on the host CPU", "context": ctx},
+            "cpu_baseline": cb, "gpu_launches": 0,
+            "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+
+
+# ------------------------------------------------------------------------------------------------
+# GPU arm
+# ------------------------------------------------------------------------------------------------
+def load_peaks() -> dict:
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return {"hbm_gbs": float(d["hbm_gbs"]), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "source": "fallback"}
+
+
+def run_gpu(args, shape, ctx, name, rank, world, local_rank):
+    import torch
+
+    os.environ["RNB_CUDA_DEVICE"] = str(local_rank)
+    import runnburn_b200 as r
+    from runnburn_b200 import build, ops
+    from runnburn_b200.decoder import nccl_unique_id
+
+    if rank == 0:
+        build.build_library()
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        torch.cuda.set_device(local_rank)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        dist.barrier()
+    ops.open()
+    K, W = args.steps, args.warmup
+    max_ctx = ctx + 2 * (K + W) + 8
+    cfg = r.ModelConfig(max_ctx=max_ctx, world_size=world, rank=rank, **shape)
+    dec = r.Decoder(cfg)
+    if world > 1:
+        ids = [nccl_unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(ids, src=0)
+        dec.attach_nccl(ids[0])
+    dec.fill_synthetic(seed=0, sigma=0.02)
+    dec.fill_kv_synthetic(ctx, seed=0)
+    stats = dec.stats()
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        dec.sync()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(v: float) -> float:
+        if dist is None:
+            return v
+        t = torch.tensor([v], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # -- device-resident: token ids never leave the GPU; CUDA events on the decoder's stream
+    tok = dec.step(1, ctx)                       # seeds the device-side token with a real argmax
+    dec.time_steps(ctx + 1, max(W, 3))           # warm-up
+    barrier()
+    clocks = ClockSampler(local_rank)
+    if rank == 0:
+        clocks.start()
+    ms = dec.time_steps(ctx + 1 + max(W, 3), K)
+    barrier()
+    ms = max_over_ranks(ms)
+
+    # -- end to end through the host-facing call: token id H2D, next token id D2H, sync per step
+    pos0 = ctx + 1 + max(W, 3) + K
+    for i in range(max(W, 3)):
+        tok = dec.step(tok, pos0 + i)
+    barrier()
+    t0 = time.perf_counter()
+    for i in range(K):
+        tok = dec.step(tok, pos0 + max(W, 3) + i)
+    barrier()
+    e2e_s = max_over_ranks(time.perf_counter() - t0)
+    clk = clocks.stop() if rank == 0 else None
+
+    # -- dominant kernel: every matvec launch of a step, timed alone over the model's own weights
+    mv = dec.time_matvecs(iters=max(3, min(K, 16))) if shape.get("n_expert", 0) == 0 else None
+    barrier()
+    if rank != 0:
+        return None
+    peaks = load_peaks()
+    alg = algorithmic_bytes_per_token(shape, ctx)
+    value = K / (ms / 1000.0)
+    out = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": max(W, 3),
+        "ms_per_step": ms / K, "higher_is_better": True, "scaling": "strong" if world > 1 else "weak",
+        "vs_baseline": None, "dtype": "int8xint4->int32, f32 accumulate", "data": "synthetic",
+        "config": {"workload": name, "context": ctx, "kv_cache": "f16", "weights": "random-init N(0,0.02), Q4_K_M layout (attn_v/ffn_down/output Q6_K), generated on device",
+                   "parallelism": f"row-sharded x{world} + NCCL all-gather" if world > 1 else "single GPU",
+                   "l2": "each step streams the whole model (>= 4.9 GB), far larger than the 126 MB L2: no flush needed",
+                   "algorithmic_bytes_per_token": alg},
+        "e2e": {"value": K / e2e_s, "unit": UNIT, "h2d_bytes_per_step": 8, "d2h_bytes_per_step": 8},
+        "gpu_launches": int(stats["launches_per_step"]) * K,
+        "clocks": clk,
+        "whole_step_hbm": {"achieved_gbs": alg["total"] / world / (ms / K / 1000.0) / 1e9, "peak_gbs": peaks["hbm_gbs"],
+                           "frac": alg["total"] / world / (ms / K / 1000.0) / 1e9 / peaks["hbm_gbs"]},
+    }
+    if mv:
+        per_launch_bytes = mv["bytes_per_iter"] / mv["launches_per_iter"]
+        per_launch_s = mv["ms"] / 1000.0 / (mv["iters"] * mv["launches_per_iter"])
+        ach = per_launch_bytes / per_launch_s / 1e9
+        out["roofline"] = {"kernel": "gemv_tile_kernel", "bound": "hbm", "achieved": ach, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                           "frac": ach / peaks["hbm_gbs"], "frac_of_8TBs_nominal": ach / 8000.0, "peak_source": peaks["source"],
+                           "traffic": None, "launches_per_step": mv["launches_per_iter"],
+                           "algorithmic_bytes_per_launch": per_launch_bytes, "avg_launch_us": per_launch_s * 1e6,
+                           "how": "CUDA events around all matvec launches of a step on the decoder stream, model's own weights"}
+    dec.close()
+    return out
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS))
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus and world > 1:
+        args.gpus = world
+    name = args.workload or ("llama3-8b-q4km-ctx4096" if args.gpus == 1 else "llama3-70b-q4km-ctx32768")
+    shape, ctx = WORKLOADS[name]
+    if args.impl == "reference":
+        out = run_reference(args, shape, ctx, name, rank, world)
+        if out is not None:
+            print(json.dumps(out), flush=True)
+        return
+    if world == 1 and args.gpus > 1:
+        sys.stderr.write("bench.py --gpus N>1 must be launched with torch.distributed.run (one rank per GPU)\n")
+        sys.exit(2)
+    out = run_gpu(args, shape, ctx, name, rank, world, local_rank)
+    if out is None:
+        return
+    if world == 1 and not args.no_cpu_baseline:
+        s, layer, head = cpu_baseline(shape, ctx, reps=5, warmup=1)
+        out["cpu_baseline"] = {"value": s.tok_per_s(min(layer), min(head)), "unit": UNIT, "cores": s.threads, "kind": "port",
+                               "sample": s.describe()}
+    print(json.dumps(out), flush=True)
+
+
+if __name__ == "__main__":
+    main()

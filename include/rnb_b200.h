@@ -258,6 +258,12 @@ int rnb_b200_decoder_read_expert_ids(rnb_b200_decoder *d, int layer, uint32_t *i
 /* kernels launched per decode step, bytes of weights resident, per-step algorithmic bytes */
 int rnb_b200_decoder_stats(rnb_b200_decoder *d, uint64_t *launches_per_step,
                            uint64_t *weight_bytes, uint64_t *kv_bytes_per_pos);
+/* Measurement helpers (CUDA events on the decoder's stream).  time_steps: `steps` chained
+ * device-resident decode steps from position `pos`.  time_matvecs: only the weight-streaming
+ * matvec launches of a step, `iters` times, with their algorithmic bytes and launch count. */
+int rnb_b200_decoder_time_steps(rnb_b200_decoder *d, int pos, int steps, float *ms_out);
+int rnb_b200_decoder_time_matvecs(rnb_b200_decoder *d, int iters, float *ms_out,
+                                  uint64_t *bytes_per_iter, uint64_t *launches_per_iter);
 /* Multi-GPU: attach an NCCL communicator built from a 128-byte unique id that rank 0 made
  * with rnb_b200_nccl_unique_id and the host side distributed to every rank. */
 int rnb_b200_nccl_unique_id(uint8_t id_out[128]);

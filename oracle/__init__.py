@@ -74,6 +74,7 @@ def _declare(L):
     L.orc_row_bytes.argtypes = [i32, sz]
     L.orc_attention_decode.argtypes = [vp, vp, vp, vp, sz, sz, sz, sz, f32]
     L.orc_attention_decode_online.argtypes = [vp, vp, vp, vp, sz, sz, sz, sz, f32]
+    L.orc_attention_decode_mt.argtypes = [vp, vp, vp, vp, sz, sz, sz, sz, f32, i32]
     L.orc_attention_prefill.argtypes = [vp, vp, vp, vp, sz, sz, sz, sz, sz, f32]
     L.orc_attention_prefill_f16kv.argtypes = [vp, vp, vp, vp, sz, sz, sz, sz, sz, f32]
     L.orc_moe_route_topk.restype = sz
@@ -197,11 +198,15 @@ def gemv(ggml_type: int, w, x, rows: int, cols: int, seq_len: int = 1,
 
 # ---- attention -----------------------------------------------------------------------------
 def attention_decode(q, k_bits, v_bits, num_heads, num_kv_heads, head_dim, kv_len, scale,
-                     online: bool = False) -> np.ndarray:
+                     online: bool = False, threads: int = 1) -> np.ndarray:
     q = _f32(q).ravel()
     k = np.ascontiguousarray(k_bits, dtype=np.uint16)
     v = np.ascontiguousarray(v_bits, dtype=np.uint16)
     out = np.empty(num_heads * head_dim, dtype=np.float32)
+    if threads > 1 and not online:
+        lib().orc_attention_decode_mt(_p(q), _p(k), _p(v), _p(out), num_heads, num_kv_heads,
+                                      head_dim, kv_len, scale, threads)
+        return out
     fn = lib().orc_attention_decode_online if online else lib().orc_attention_decode
     fn(_p(q), _p(k), _p(v), _p(out), num_heads, num_kv_heads, head_dim, kv_len, scale)
     return out

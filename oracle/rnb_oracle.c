@@ -822,7 +822,7 @@ int orc_gemv(int type, const uint8_t *w, const float *x, float *out, size_t rows
  * online: :245-297 (process_head).  f32·f16 dot: x86_helpers.rs:11-54 (two 8-lane
  * accumulators, mul then add, no FMA); scaled add: :58-80.
  * ---------------------------------------------------------------------------------------- */
-static float dot_f32_f16(const float *a, const uint16_t *b, size_t len) {
+static float dot_f32_f16_scalar(const float *a, const uint16_t *b, size_t len) {
     float acc0[8] = {0}, acc1[8] = {0};
     size_t i = 0;
     for (; i + 16 <= len; i += 16) {
@@ -841,20 +841,72 @@ static float dot_f32_f16(const float *a, const uint16_t *b, size_t len) {
     for (; i < len; i++) total += a[i] * orc_f16_to_f32(b[i]);
     return total;
 }
-static void scaled_add_f16(float *out, const uint16_t *v, float scale, size_t len) {
+static void scaled_add_f16_scalar(float *out, const uint16_t *v, float scale, size_t len) {
     for (size_t i = 0; i < len; i++) out[i] = out[i] + orc_f16_to_f32(v[i]) * scale;
 }
+/* The same two routines with F16C/AVX2, as the reference's x86 helpers are written
+ * (x86_helpers.rs:11-80): identical lane order, mul then add, so identical bits. */
+__attribute__((target("avx2,f16c"))) static float dot_f32_f16_avx2(const float *a,
+                                                                   const uint16_t *b,
+                                                                   size_t len) {
+    __m256 acc0 = _mm256_setzero_ps(), acc1 = _mm256_setzero_ps();
+    size_t i = 0;
+    for (; i + 16 <= len; i += 16) {
+        acc0 = _mm256_add_ps(acc0, _mm256_mul_ps(_mm256_loadu_ps(a + i),
+                                                 _mm256_cvtph_ps(_mm_loadu_si128((const __m128i *)(b + i)))));
+        acc1 = _mm256_add_ps(acc1, _mm256_mul_ps(_mm256_loadu_ps(a + i + 8),
+                                                 _mm256_cvtph_ps(_mm_loadu_si128((const __m128i *)(b + i + 8)))));
+    }
+    for (; i + 8 <= len; i += 8)
+        acc0 = _mm256_add_ps(acc0, _mm256_mul_ps(_mm256_loadu_ps(a + i),
+                                                 _mm256_cvtph_ps(_mm_loadu_si128((const __m128i *)(b + i)))));
+    __m256 acc = _mm256_add_ps(acc0, acc1);
+    __m128 sum128 = _mm_add_ps(_mm256_castps256_ps128(acc), _mm256_extractf128_ps(acc, 1));
+    __m128 shuf = _mm_movehdup_ps(sum128);
+    __m128 sums = _mm_add_ps(sum128, shuf);
+    shuf = _mm_movehl_ps(shuf, sums);
+    float total = _mm_cvtss_f32(_mm_add_ss(sums, shuf));
+    for (; i < len; i++) total += a[i] * orc_f16_to_f32(b[i]);
+    return total;
+}
+__attribute__((target("avx2,f16c"))) static void scaled_add_f16_avx2(float *out, const uint16_t *v,
+                                                                     float scale, size_t len) {
+    const __m256 s = _mm256_set1_ps(scale);
+    size_t i = 0;
+    for (; i + 8 <= len; i += 8) {
+        __m256 vf = _mm256_cvtph_ps(_mm_loadu_si128((const __m128i *)(v + i)));
+        _mm256_storeu_ps(out + i, _mm256_add_ps(_mm256_loadu_ps(out + i), _mm256_mul_ps(vf, s)));
+    }
+    for (; i < len; i++) out[i] = out[i] + orc_f16_to_f32(v[i]) * scale;
+}
+static int have_f16c(void) {
+    return !g_force_scalar && __builtin_cpu_supports("avx2") && __builtin_cpu_supports("f16c");
+}
+static float dot_f32_f16(const float *a, const uint16_t *b, size_t len) {
+    return have_f16c() ? dot_f32_f16_avx2(a, b, len) : dot_f32_f16_scalar(a, b, len);
+}
+static void scaled_add_f16(float *out, const uint16_t *v, float scale, size_t len) {
+    if (have_f16c()) scaled_add_f16_avx2(out, v, scale, len);
+    else scaled_add_f16_scalar(out, v, scale, len);
+}
 
-void orc_attention_decode(const float *q, const uint16_t *k, const uint16_t *v, float *out,
-                          size_t num_heads, size_t num_kv_heads, size_t head_dim, size_t kv_len,
-                          float scale) {
-    size_t group = num_heads / num_kv_heads, kv_dim = num_kv_heads * head_dim;
+typedef struct {
+    const float *q;
+    const uint16_t *k, *v;
+    float *out;
+    size_t num_heads, num_kv_heads, head_dim, kv_len;
+    float scale;
+} attn_ctx;
+static void attn_heads(size_t hb, size_t he, void *p) {
+    attn_ctx *c = (attn_ctx *)p;
+    size_t group = c->num_heads / c->num_kv_heads, kv_dim = c->num_kv_heads * c->head_dim;
+    size_t head_dim = c->head_dim, kv_len = c->kv_len;
     float *scores = (float *)malloc(sizeof(float) * (kv_len ? kv_len : 1));
-    for (size_t h = 0; h < num_heads; h++) {
+    for (size_t h = hb; h < he; h++) {
         size_t kv_h = h / group;
-        const float *qh = q + h * head_dim;
+        const float *qh = c->q + h * head_dim;
         for (size_t j = 0; j < kv_len; j++)
-            scores[j] = dot_f32_f16(qh, k + j * kv_dim + kv_h * head_dim, head_dim) * scale;
+            scores[j] = dot_f32_f16(qh, c->k + j * kv_dim + kv_h * head_dim, head_dim) * c->scale;
         float max_score = -INFINITY;
         for (size_t j = 0; j < kv_len; j++)
             if (scores[j] > max_score) max_score = scores[j];
@@ -864,12 +916,43 @@ void orc_attention_decode(const float *q, const uint16_t *k, const uint16_t *v, 
             sum += scores[j];
         }
         float inv_sum = sum > 0.0f ? 1.0f / sum : 0.0f;
-        float *o = out + h * head_dim;
+        float *o = c->out + h * head_dim;
         for (size_t d = 0; d < head_dim; d++) o[d] = 0.0f;
         for (size_t j = 0; j < kv_len; j++)
-            scaled_add_f16(o, v + j * kv_dim + kv_h * head_dim, scores[j] * inv_sum, head_dim);
+            scaled_add_f16(o, c->v + j * kv_dim + kv_h * head_dim, scores[j] * inv_sum, head_dim);
     }
     free(scores);
+}
+void orc_attention_decode(const float *q, const uint16_t *k, const uint16_t *v, float *out,
+                          size_t num_heads, size_t num_kv_heads, size_t head_dim, size_t kv_len,
+                          float scale) {
+    attn_ctx c = {q, k, v, out, num_heads, num_kv_heads, head_dim, kv_len, scale};
+    attn_heads(0, num_heads, &c);
+}
+/* Heads are independent; the reference runs them in parallel on its thread pool. */
+void orc_attention_decode_mt(const float *q, const uint16_t *k, const uint16_t *v, float *out,
+                             size_t num_heads, size_t num_kv_heads, size_t head_dim, size_t kv_len,
+                             float scale, int threads) {
+    attn_ctx c = {q, k, v, out, num_heads, num_kv_heads, head_dim, kv_len, scale};
+    if (threads <= 1) {
+        attn_heads(0, num_heads, &c);
+        return;
+    }
+    /* orc_parallel_for keeps n <= 64 on one thread; split heads by hand */
+    size_t nt = (size_t)threads < num_heads ? (size_t)threads : num_heads;
+    size_t chunk = (num_heads + nt - 1) / nt;
+    pthread_t tid[256];
+    orc_task task[256];
+    int n = 0;
+    for (size_t b = 0; b < num_heads && n < 256; b += chunk, n++) {
+        task[n].fn = attn_heads;
+        task[n].ctx = &c;
+        task[n].begin = b;
+        task[n].end = b + chunk < num_heads ? b + chunk : num_heads;
+    }
+    for (int i = 1; i < n; i++) pthread_create(&tid[i], NULL, orc_task_main, &task[i]);
+    orc_task_main(&task[0]);
+    for (int i = 1; i < n; i++) pthread_join(tid[i], NULL);
 }
 
 void orc_attention_decode_online(const float *q, const uint16_t *k, const uint16_t *v, float *out,

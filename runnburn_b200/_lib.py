@@ -115,6 +115,8 @@ def load() -> C.CDLL:
         "rnb_b200_decoder_read_hidden": [vp, vp],
         "rnb_b200_decoder_read_expert_ids": [vp, i32, vp],
         "rnb_b200_decoder_stats": [vp, vp, vp, vp],
+        "rnb_b200_decoder_time_steps": [vp, i32, i32, vp],
+        "rnb_b200_decoder_time_matvecs": [vp, i32, vp, vp, vp],
         "rnb_b200_nccl_unique_id": [vp],
         "rnb_b200_decoder_attach_nccl": [vp, vp],
         "rnb_b200_dev_quantize_q8k": [vp, sz, sz, vp, vp, vp],

@@ -27,11 +27,23 @@ bool use_pdl() {
     }
     return v == 1;
 }
+static size_t g_gemv_smem_max = 0;
+size_t gemv_smem_max() { return g_gemv_smem_max; }
 int gemv_kernel_setup() {
     static bool done = false;
     if (done) return RNB_B200_OK;
-    RNB_CU(cudaFuncSetAttribute(gemv_tile_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
-    RNB_CU(cudaFuncSetAttribute(gemv_tile_kernel_1, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+    int dev = 0, optin = 0;
+    RNB_CU(cudaGetDevice(&dev));
+    RNB_CU(cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
+    cudaFuncAttributes fa;
+    RNB_CU(cudaFuncGetAttributes(&fa, gemv_tile_kernel));
+    size_t stat = fa.sharedSizeBytes;
+    RNB_CU(cudaFuncGetAttributes(&fa, gemv_tile_kernel_1));
+    if (fa.sharedSizeBytes > stat) stat = fa.sharedSizeBytes;
+    const size_t dyn = (size_t)optin - ((stat + 1023) & ~(size_t)1023);
+    RNB_CU(cudaFuncSetAttribute(gemv_tile_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn));
+    RNB_CU(cudaFuncSetAttribute(gemv_tile_kernel_1, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn));
+    g_gemv_smem_max = dyn;
     done = true;
     return RNB_B200_OK;
 }

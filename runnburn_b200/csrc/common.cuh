@@ -38,12 +38,12 @@ __host__ __device__ inline size_t row_bytes_of(int type, size_t cols) {
 // Device-internal activation layout ("Q8K-dev"): the same numbers as rnb-cpu's Q8KBlock
 // array, regrouped so that the matvec kernels can use 16-byte loads:
 //   int8  qs[K]            @ 0
-//   float d[K/256]         @ K
-//   int16 bsum32[K/256*8]  @ K + 4*(K/256)      (sum of each 32-element sub-block)
+//   int16 bsum16[K/256*16] @ K                  (sum of each 16-element group, as Q8KBlock.bsums)
+//   float d[K/256]         @ K + 32*(K/256)
 // ---------------------------------------------------------------------------------------
 __host__ __device__ inline size_t q8k_dev_bytes(size_t cols) {
     size_t nb = cols / 256;
-    return (cols + nb * 4 + nb * 16 + 15) & ~(size_t)15;
+    return (cols + nb * 4 + nb * 32 + 15) & ~(size_t)15;
 }
 
 #ifdef __CUDACC__

@@ -51,11 +51,12 @@ inline uint32_t gemv_part_stride(int type, size_t cols, int rows_per_tile) {
 }
 
 int gemv_kernel_setup();  // raises the dynamic shared memory limit once
+size_t gemv_smem_max();    // dynamic shared memory a matvec launch may ask for
 
 // Launch a table of jobs that all share `cols`.  jobs_host is used to size the launch;
 // jobs_dev is the same table in device memory.
 inline int launch_gemv_jobs(cudaStream_t s, const GemvJob *jobs_host, const GemvJob *jobs_dev,
-                            int n_jobs, size_t cols, int *dev_error) {
+                            int n_jobs, size_t cols, int *dev_error, int dynamic_table = 0) {
     RNB_TRY(gemv_kernel_setup());
     int tiles = 0, max_parts = 1;
     uint32_t stride = 0;
@@ -67,9 +68,9 @@ inline int launch_gemv_jobs(cudaStream_t s, const GemvJob *jobs_host, const Gemv
         if (st > stride) stride = st;
     }
     const size_t smem = (size_t)stride * max_parts;
-    if (smem > 227 * 1024) return fail(RNB_B200_VALIDATION_FAILED, "matvec tile too large: %zu bytes", smem);
+    if (smem > gemv_smem_max()) return fail(RNB_B200_VALIDATION_FAILED, "matvec tile too large: %zu bytes", smem);
     RNB_CU(launch_k(gemv_tile_kernel, dim3(tiles), dim3(GEMV_THREADS), smem, s, jobs_dev, n_jobs,
-                    (int)cols, stride, dev_error));
+                    (int)cols, stride, dev_error, dynamic_table));
     return RNB_B200_OK;
 }
 inline int launch_gemv_one(cudaStream_t s, const GemvJob &job, size_t cols, int *dev_error) {
@@ -77,7 +78,7 @@ inline int launch_gemv_one(cudaStream_t s, const GemvJob &job, size_t cols, int 
     const int tiles = (job.rows + job.rows_per_tile - 1) / job.rows_per_tile;
     const uint32_t stride = gemv_part_stride(job.type, cols, job.rows_per_tile);
     const size_t smem = (size_t)stride * job.n_parts;
-    if (smem > 227 * 1024) return fail(RNB_B200_VALIDATION_FAILED, "matvec tile too large: %zu bytes", smem);
+    if (smem > gemv_smem_max()) return fail(RNB_B200_VALIDATION_FAILED, "matvec tile too large: %zu bytes", smem);
     RNB_CU(launch_k(gemv_tile_kernel_1, dim3(tiles), dim3(GEMV_THREADS), smem, s, job, (int)cols,
                     stride, dev_error));
     return RNB_B200_OK;

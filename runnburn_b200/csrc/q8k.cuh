@@ -7,11 +7,11 @@
 namespace rnb {
 
 // One warp quantises one 256-element block; lane holds elements 8*lane .. 8*lane+7.
-// Writes the device layout (qs / d / bsum32) and, when `ref_block` is given, the reference's
+// Writes the device layout (qs / d / bsum16) and, when `ref_block` is given, the reference's
 // 292-byte Q8KBlock as well.
 __device__ __forceinline__ void q8k_quantize_block_warp(const float (&v)[8], int lane,
                                                         int8_t *qs_out, float *d_out,
-                                                        int16_t *bsum32_out, uint8_t *ref_block) {
+                                                        int16_t *bsum16_out, uint8_t *ref_block) {
     // first element with the strictly largest |x|
     float amax = 0.0f, mval = 0.0f;
     int idx = 256;
@@ -53,7 +53,6 @@ __device__ __forceinline__ void q8k_quantize_block_warp(const float (&v)[8], int
 #pragma unroll
     for (int j = 0; j < 8; j++) s += q[j];
     const int s16 = s + __shfl_xor_sync(0xffffffffu, s, 1);      // 16-element sum
-    const int s32 = s16 + __shfl_xor_sync(0xffffffffu, s16, 2);  // 32-element sum
     const uint32_t w0 = (uint32_t)(q[0] & 0xff) | ((uint32_t)(q[1] & 0xff) << 8) |
                         ((uint32_t)(q[2] & 0xff) << 16) | ((uint32_t)(q[3] & 0xff) << 24);
     const uint32_t w1 = (uint32_t)(q[4] & 0xff) | ((uint32_t)(q[5] & 0xff) << 8) |
@@ -61,7 +60,7 @@ __device__ __forceinline__ void q8k_quantize_block_warp(const float (&v)[8], int
     if (qs_out) {
         *reinterpret_cast<uint2 *>(qs_out + lane * 8) = make_uint2(w0, w1);
         if (lane == 0) *d_out = d;
-        if ((lane & 3) == 0) bsum32_out[lane >> 2] = (int16_t)s32;
+        if ((lane & 1) == 0) bsum16_out[lane >> 1] = (int16_t)s16;
     }
     if (ref_block) {
         uint32_t *words = reinterpret_cast<uint32_t *>(ref_block);  // 292 = 4*73: 4-byte aligned
@@ -76,14 +75,14 @@ __device__ __forceinline__ void q8k_quantize_block_warp(const float (&v)[8], int
 struct Q8kDevView {
     int8_t *qs;
     float *d;
-    int16_t *bsum32;
+    int16_t *bsum16;
 };
 __device__ __forceinline__ Q8kDevView q8k_dev_view(uint8_t *base, int cols) {
     Q8kDevView v;
     const int nb = cols / 256;
     v.qs = reinterpret_cast<int8_t *>(base);
-    v.d = reinterpret_cast<float *>(base + cols);
-    v.bsum32 = reinterpret_cast<int16_t *>(base + cols + 4 * nb);
+    v.bsum16 = reinterpret_cast<int16_t *>(base + cols);
+    v.d = reinterpret_cast<float *>(base + cols + 32 * nb);
     return v;
 }
 
@@ -105,14 +104,13 @@ quantize_q8k_kernel(const float *__restrict__ x, int cols, int seq, uint8_t *dev
     Q8kDevView dv{nullptr, nullptr, nullptr};
     if (dev_out) dv = q8k_dev_view(dev_out + (size_t)s * q8k_dev_bytes(cols), cols);
     q8k_quantize_block_warp(v, lane, dev_out ? dv.qs + b * 256 : nullptr, dv.d + b,
-                            dv.bsum32 + b * 8,
+                            dv.bsum16 + b * 16,
                             ref_out ? ref_out + ((size_t)s * nb + b) * Q8K_BYTES : nullptr);
 }
 
 // RMSNorm with an f64 mean square and (x / rms) * w, as rnb-cpu's rms_norm_into_f64
 // (crates/rnb-cpu/src/kernels/norm.rs:177-196), fused with the Q8_K quantisation of the
 // result.  One CTA per token.  `h_out` (f32 normalised vector) is optional.
-// If `x_add` is given the input is x + x_add (residual add), and `x_sum_out` receives it.
 template <int THREADS>
 __global__ void __launch_bounds__(THREADS)
 rmsnorm_q8k_kernel(const float *__restrict__ x, const float *__restrict__ w, float eps, int hidden,
@@ -154,7 +152,7 @@ rmsnorm_q8k_kernel(const float *__restrict__ x, const float *__restrict__ w, flo
             *reinterpret_cast<float4 *>(ho) = make_float4(v[0], v[1], v[2], v[3]);
             *reinterpret_cast<float4 *>(ho + 4) = make_float4(v[4], v[5], v[6], v[7]);
         }
-        if (xq_out) q8k_quantize_block_warp(v, lane, dv.qs + b * 256, dv.d + b, dv.bsum32 + b * 8, nullptr);
+        if (xq_out) q8k_quantize_block_warp(v, lane, dv.qs + b * 256, dv.d + b, dv.bsum16 + b * 16, nullptr);
     }
 }
 
@@ -185,7 +183,7 @@ silu_mul_q8k_kernel(const float *__restrict__ gate, const float *__restrict__ up
     }
     if (xq_out) {
         Q8kDevView dv = q8k_dev_view(xq_out + (size_t)s * q8k_dev_bytes(n), n);
-        q8k_quantize_block_warp(v, lane, dv.qs + b * 256, dv.d + b, dv.bsum32 + b * 8, nullptr);
+        q8k_quantize_block_warp(v, lane, dv.qs + b * 256, dv.d + b, dv.bsum16 + b * 16, nullptr);
     }
 }
 

@@ -112,6 +112,17 @@ class Decoder:
     def sync(self) -> None:
         check(load().rnb_b200_decoder_sync(self._h))
 
+    def time_steps(self, pos: int, steps: int) -> float:
+        """Milliseconds (CUDA events) for `steps` chained device-resident steps from `pos`."""
+        ms = C.c_float()
+        check(load().rnb_b200_decoder_time_steps(self._h, pos, steps, C.byref(ms)))
+        return ms.value
+
+    def time_matvecs(self, iters: int = 1) -> dict:
+        ms, b, n = C.c_float(), C.c_uint64(), C.c_uint64()
+        check(load().rnb_b200_decoder_time_matvecs(self._h, iters, C.byref(ms), C.byref(b), C.byref(n)))
+        return {"ms": ms.value, "bytes_per_iter": b.value, "launches_per_iter": n.value, "iters": iters}
+
     @property
     def stream(self) -> int:
         return load().rnb_b200_decoder_stream(self._h) or 0

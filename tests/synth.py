@@ -40,6 +40,12 @@ def max_rel_err(got: np.ndarray, ref: np.ndarray) -> float:
     return float(np.max(np.abs(got - ref) / np.maximum(np.abs(ref), floor)))
 
 
+def max_err_vs_norm(got: np.ndarray, ref: np.ndarray) -> float:
+    """max |got - ref| / max |ref|: error of a whole vector (logits) relative to its scale."""
+    got, ref = np.asarray(got, np.float64), np.asarray(ref, np.float64)
+    return float(np.max(np.abs(got - ref)) / max(np.max(np.abs(ref)), 1e-30))
+
+
 def llama_description(seed: int, n_layer=2, hidden=512, n_head=4, n_kv_head=2, n_ff=1024, vocab=1024,
                       rope_theta=5e5, rms_eps=1e-5, sigma=0.02):
     """Random-init Llama-style stack in the Q4_K_M convention: attn_v, ffn_down and the LM

@@ -1,7 +1,9 @@
 """Parity of the CUDA operators with the CPU oracle, through the C ABI, on seeded inputs.
 
 Bars (BASELINE north star): Q8_K activation quantisation and MoE routing bit-exact;
-matvec and attention within max relative error 1e-3 (fp32 accumulate).
+matvec and attention within max relative error 1e-3 (fp32 accumulate).  The matvec kernels
+go further: they replay the accumulation order of rnb-cpu's AVX2 dots, so their outputs are
+compared bit for bit; the 1e-3 bar is kept for attention and for chains through exp().
 """
 import numpy as np
 import pytest
@@ -14,12 +16,26 @@ pytestmark = pytest.mark.gpu
 TOL = 1e-3  # max relative error, matvec and attention
 
 
+def bits_equal(a, b) -> bool:
+    a, b = np.ascontiguousarray(a, np.float32), np.ascontiguousarray(b, np.float32)
+    return a.shape == b.shape and np.array_equal(a.view(np.uint32), b.view(np.uint32))
+
+
 @pytest.fixture(scope="module")
 def ops():
     from runnburn_b200 import build, ops
     build.build_library()
     ops.open()
     return ops
+
+
+@pytest.fixture(autouse=True)
+def _fresh_weight_cache(ops):
+    """The resident cache is keyed by host address (weights are borrowed, immutable mmap pages
+    in the reference's contract).  numpy reuses freed addresses for new arrays, so every test
+    starts from an empty cache."""
+    ops.reset_state_for_engine_init()
+    yield
 
 
 # ---- Q8_K -------------------------------------------------------------------------------------
@@ -75,6 +91,7 @@ def test_q4k_gemv_config1_shapes(ops, rows, cols):
     ref = orc.gemv(Q4_K, w, x, rows, cols)
     got = ops.q4k_gemv(w, rows, cols, x)
     assert max_rel_err(got, ref) <= TOL
+    assert bits_equal(got, ref)
     # linearity in the activation scale is exact for powers of two (Q8_K d scales, qs unchanged)
     got2 = ops.q4k_gemv(w, rows, cols, x * np.float32(4.0))
     assert np.array_equal(got2, got * np.float32(4.0))
@@ -93,6 +110,7 @@ def test_gemv_shapes_and_ragged_tiles(ops, t, rows, cols):
     ref = orc.gemv(t, w, x, rows, cols)
     got = ops.gemv(t, w, rows, cols, x)
     assert max_rel_err(got, ref) <= TOL
+    assert bits_equal(got, ref)
 
 
 @pytest.mark.parametrize("t", [Q4_K, Q6_K, Q8_0])
@@ -101,7 +119,7 @@ def test_gemv_on_quantised_gaussian_weights(ops, t):
     rows, cols = 384, 1024
     _, w = quantized(rng, t, rows, cols)
     x = rng.standard_normal(cols).astype(np.float32)
-    assert max_rel_err(ops.gemv(t, w, rows, cols, x), orc.gemv(t, w, x, rows, cols)) <= TOL
+    assert bits_equal(ops.gemv(t, w, rows, cols, x), orc.gemv(t, w, x, rows, cols))
 
 
 def test_gemv_misaligned_weight_slice_takes_the_plain_load_path(ops):
@@ -114,6 +132,7 @@ def test_gemv_misaligned_weight_slice_takes_the_plain_load_path(ops):
         w = random_blocks(rng, t, rows, cols)
         x = rng.standard_normal(cols).astype(np.float32)
         aligned = ops.gemv(t, w, rows, cols, x)
+        ops.clear_q4k_cache()
         backing = np.zeros(w.size + 64, np.uint8)
         backing[2:2 + w.size] = w
         ops.prewarm_q4k_weights([backing])            # one resident range; the slice below lives inside it
@@ -129,7 +148,7 @@ def test_gemv_batch_is_seq_major_and_matches_single_token_bits(ops):
         x = rng.standard_normal((seq, cols)).astype(np.float32)
         got = batch(w, rows, cols, x)
         ref = orc.gemv(t, w, x, rows, cols, seq_len=seq)
-        assert max_rel_err(got, ref) <= TOL
+        assert bits_equal(got, ref)
         for s in range(seq):   # one accumulation order for decode and prefill-of-1
             assert np.array_equal(got[s * rows:(s + 1) * rows], ops.gemv(t, w, rows, cols, x[s]))
 
@@ -252,9 +271,8 @@ def test_fused_qkv_rope_decode(ops):
     q_ref = orc.rope(orc.gemv(Q4_K, wq, x, heads * 128, n_embd), pos, 128, heads * 128, 5e5)
     k_ref = orc.rope(orc.gemv(Q4_K, wk, x, kvh * 128, n_embd), pos, 128, kvh * 128, 5e5)
     v_ref = orc.gemv(Q6_K, wv, x, kvh * 128, n_embd)
-    assert max_rel_err(q, q_ref) <= TOL
-    assert max_rel_err(kb.view(np.float16).astype(np.float32), orc.f32_to_f16_bits(k_ref).view(np.float16).astype(np.float32)) <= 2e-3
-    assert max_rel_err(vb.view(np.float16).astype(np.float32), orc.f32_to_f16_bits(v_ref).view(np.float16).astype(np.float32)) <= 2e-3
+    assert bits_equal(q, q_ref)
+    assert np.array_equal(kb, orc.f32_to_f16_bits(k_ref)) and np.array_equal(vb, orc.f32_to_f16_bits(v_ref))
     # exactness of the rotation + rounding given the device's own matvec output
     qd = ops.q4k_gemv(wq, heads * 128, n_embd, x)
     assert np.array_equal(q, orc.rope(qd, pos, 128, heads * 128, 5e5))
@@ -316,6 +334,7 @@ def test_sparse_experts(ops):
     lg = rng.standard_normal(n_expert).astype(np.float32)
     ids, rw = orc.moe_route_topk(lg, k)
     for dt in (Q4_K, Q6_K):
+        ops.reset_state_for_engine_init()
         _, down_all = quantized(rng, dt, n_expert * n_embd, n_ff)
         ds = n_embd * orc.row_bytes(dt, n_ff)
         assert ops.qwen35_register_moe_layer(gate_all, up_all, down_all, dt, n_ff, n_embd)
