@@ -27,6 +27,22 @@ bool use_pdl() {
     }
     return v == 1;
 }
+const GemvTuning &gemv_tuning() {
+    static GemvTuning t = [] {
+        GemvTuning v{1, 8, 4};
+        auto env_int = [](const char *name, int dflt, int lo, int hi) {
+            const char *e = getenv(name);
+            if (!e || !*e) return dflt;
+            int x = atoi(e);
+            return x < lo ? lo : (x > hi ? hi : x);
+        };
+        v.warps = env_int("RNB_B200_GEMV_WARPS", v.warps, 1, 4);
+        v.chunk_blocks = env_int("RNB_B200_GEMV_CHUNK", v.chunk_blocks, 1, 64);
+        v.stages = env_int("RNB_B200_GEMV_STAGES", v.stages, 1, GS_MAX_STAGES);
+        return v;
+    }();
+    return t;
+}
 static size_t g_gemv_smem_max = 0;
 size_t gemv_smem_max() { return g_gemv_smem_max; }
 int gemv_kernel_setup() {
@@ -43,6 +59,8 @@ int gemv_kernel_setup() {
     const size_t dyn = (size_t)optin - ((stat + 1023) & ~(size_t)1023);
     RNB_CU(cudaFuncSetAttribute(gemv_tile_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn));
     RNB_CU(cudaFuncSetAttribute(gemv_tile_kernel_1, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn));
+    RNB_CU(cudaFuncSetAttribute(gemv_stream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn));
+    RNB_CU(cudaFuncSetAttribute(gemv_stream_kernel_1, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn));
     g_gemv_smem_max = dyn;
     done = true;
     return RNB_B200_OK;
@@ -871,15 +889,14 @@ int rnb_b200_qwen35_sparse_experts(const uint8_t *const *gate, const uint8_t *co
     RNB_TRY(st.mid_b.ensure(k * n_ff * 4));
     const size_t n_down_jobs = (k + GEMV_MAX_PARTS - 1) / GEMV_MAX_PARTS;
     std::vector<GemvJob> jobs(2 * k + n_down_jobs);
-    const int rpt = pick_rows_per_tile(TYPE_Q4_K, n_ff, n_embd, 1, st.sm_count);
     int tile0 = 0;
     for (size_t e = 0; e < 2 * k; e++) {
         const bool is_up = e >= k;
         const size_t ee = is_up ? e - k : e;
         jobs[e] = make_job(TYPE_Q4_K, is_up ? ud[ee] : gd[ee], st.xq.p, (is_up ? st.mid_b.as<float>() : st.mid_a.as<float>()) + ee * n_ff,
-                           nullptr, n_ff, n_embd, rpt, st.sm_count);
+                           nullptr, n_ff, n_embd, 0, st.sm_count);
         jobs[e].tile0 = tile0;
-        tile0 += (int)((n_ff + rpt - 1) / rpt);
+        tile0 += (int)((n_ff + jobs[e].rows_per_tile - 1) / jobs[e].rows_per_tile);
     }
     RNB_TRY(st.xq2.ensure(q8k_dev_bytes(n_ff) * k));
     RNB_TRY(st.out_f32.ensure(n_embd * 4));
@@ -892,9 +909,7 @@ int rnb_b200_qwen35_sparse_experts(const uint8_t *const *gate, const uint8_t *co
         const float *prev = gi == 0 ? nullptr : (((n_down_jobs - gi) % 2 == 0) ? st.out_f32.as<float>() : st.mid_c.as<float>());
         (void)last;
         GemvJob &dj = jobs[2 * k + gi];
-        dj = make_job((int)down_quant, dd[e0], st.xq2.p, dst, prev, n_embd, n_ff, 0, st.sm_count);
-        dj.rows_per_tile = pick_rows_per_tile((int)down_quant, n_embd, n_ff, (int)ne, st.sm_count);
-        dj.n_parts = (int)ne;
+        dj = make_job((int)down_quant, dd[e0], st.xq2.p, dst, prev, n_embd, n_ff, 0, st.sm_count, 1, 0, (int)ne);
         for (size_t p = 0; p < ne; p++) {
             dj.parts[p].w = dd[e0 + p];
             dj.parts[p].x = st.xq2.as<uint8_t>() + (e0 + p) * q8k_dev_bytes(n_ff);

@@ -2,6 +2,7 @@
 #pragma once
 #include "attention.cuh"
 #include "gemv.cuh"
+#include "gemv_stream.cuh"
 #include "moe.cuh"
 #include "q8k.cuh"
 #include "state.hpp"
@@ -53,11 +54,59 @@ inline uint32_t gemv_part_stride(int type, size_t cols, int rows_per_tile) {
 int gemv_kernel_setup();  // raises the dynamic shared memory limit once
 size_t gemv_smem_max();    // dynamic shared memory a matvec launch may ask for
 
+// Streaming (batch-1) kernel geometry: warps per CTA (4 rows each), super-blocks per stage and
+// pipeline depth; overridable by RNB_B200_GEMV_WARPS / _CHUNK / _STAGES for tuning.
+struct GemvTuning {
+    int warps, chunk_blocks, stages;
+};
+const GemvTuning &gemv_tuning();
+
+inline bool gemv_use_stream(int seq, size_t cols) { return seq <= 1 && cols % 256 == 0; }
+inline uint32_t gs_block_bytes(int type) {
+    return type == TYPE_Q4_K ? Q4K_BYTES : type == TYPE_Q6_K ? Q6K_BYTES : 8 * Q8_0_BYTES;
+}
+
+inline int launch_gemv_stream(cudaStream_t s, const GemvJob *jobs_host, const GemvJob *jobs_dev, int n_jobs,
+                              size_t cols, int *dev_error, int dynamic_table, bool by_value) {
+    const GemvTuning &tu = gemv_tuning();
+    const int rows_per_cta = jobs_host[0].rows_per_tile;
+    int tiles = 0, max_parts = 1;
+    uint32_t blk = 0;
+    for (int i = 0; i < n_jobs; i++) {
+        const GemvJob &j = jobs_host[i];
+        if (j.rows_per_tile != rows_per_cta || rows_per_cta % 4 != 0 || rows_per_cta > 16)
+            return fail(RNB_B200_VALIDATION_FAILED, "matvec jobs of one launch must share rows per CTA (4, 8, 12 or 16)");
+        tiles = j.tile0 + (j.rows + rows_per_cta - 1) / rows_per_cta;
+        if (j.n_parts > max_parts) max_parts = j.n_parts;
+        if (gs_block_bytes(j.type) > blk) blk = gs_block_bytes(j.type);
+    }
+    const int nb = (int)(cols / 256);
+    GsParams P;
+    P.cols = (int)cols;
+    P.chunk_blocks = tu.chunk_blocks < nb ? tu.chunk_blocks : nb;
+    if (P.chunk_blocks >= 8) P.chunk_blocks = P.chunk_blocks / 8 * 8;  // keeps Q6_K chunks 16-byte multiples
+    const int n_items = (nb + P.chunk_blocks - 1) / P.chunk_blocks * max_parts;
+    P.n_stages = n_items < tu.stages ? n_items : tu.stages;
+    P.row_stride = (((uint32_t)P.chunk_blocks * blk + 15u) & ~15u) + 16u;  // rows stay 16-byte aligned
+    P.dynamic_table = dynamic_table;
+    size_t smem = (size_t)P.n_stages * rows_per_cta * P.row_stride;
+    while (smem > gemv_smem_max() && P.n_stages > 1) smem = (size_t)(--P.n_stages) * rows_per_cta * P.row_stride;
+    if (smem > gemv_smem_max()) return fail(RNB_B200_VALIDATION_FAILED, "matvec stage too large: %zu bytes", smem);
+    const dim3 block(rows_per_cta / 4 * 32);
+    if (by_value)
+        RNB_CU(launch_k(gemv_stream_kernel_1, dim3(tiles), block, smem, s, jobs_host[0], P, dev_error));
+    else
+        RNB_CU(launch_k(gemv_stream_kernel, dim3(tiles), block, smem, s, jobs_dev, n_jobs, P, dev_error));
+    return RNB_B200_OK;
+}
+
 // Launch a table of jobs that all share `cols`.  jobs_host is used to size the launch;
 // jobs_dev is the same table in device memory.
 inline int launch_gemv_jobs(cudaStream_t s, const GemvJob *jobs_host, const GemvJob *jobs_dev,
                             int n_jobs, size_t cols, int *dev_error, int dynamic_table = 0) {
     RNB_TRY(gemv_kernel_setup());
+    if (gemv_use_stream(jobs_host[0].seq, cols))
+        return launch_gemv_stream(s, jobs_host, jobs_dev, n_jobs, cols, dev_error, dynamic_table, false);
     int tiles = 0, max_parts = 1;
     uint32_t stride = 0;
     for (int i = 0; i < n_jobs; i++) {
@@ -75,6 +124,7 @@ inline int launch_gemv_jobs(cudaStream_t s, const GemvJob *jobs_host, const Gemv
 }
 inline int launch_gemv_one(cudaStream_t s, const GemvJob &job, size_t cols, int *dev_error) {
     RNB_TRY(gemv_kernel_setup());
+    if (gemv_use_stream(job.seq, cols)) return launch_gemv_stream(s, &job, nullptr, 1, cols, dev_error, 0, true);
     const int tiles = (job.rows + job.rows_per_tile - 1) / job.rows_per_tile;
     const uint32_t stride = gemv_part_stride(job.type, cols, job.rows_per_tile);
     const size_t smem = (size_t)stride * job.n_parts;
@@ -83,18 +133,24 @@ inline int launch_gemv_one(cudaStream_t s, const GemvJob &job, size_t cols, int 
                     stride, dev_error));
     return RNB_B200_OK;
 }
+// rows_per_tile: 0 = automatic.  Batch-1 jobs (seq <= 1, cols % 256 == 0) run on the streaming
+// kernel, whose tiles are 4 rows per warp; batched jobs keep whole-row tiles in shared memory.
 inline GemvJob make_job(int type, const uint8_t *w, const void *x, float *y, const float *residual,
                         size_t rows, size_t cols, int rows_per_tile, int sm_count, int seq = 1,
-                        size_t x_stride = 0) {
+                        size_t x_stride = 0, int n_parts = 1) {
     GemvJob j;
     memset(&j, 0, sizeof(j));
     j.y = y;
     j.residual = residual;
     j.rows = (int)rows;
     j.type = type;
-    j.n_parts = 1;
+    j.n_parts = n_parts;
     j.tile0 = 0;
-    j.rows_per_tile = rows_per_tile > 0 ? rows_per_tile : pick_rows_per_tile(type, rows, cols, 1, sm_count);
+    if (gemv_use_stream(seq, cols))
+        j.rows_per_tile = rows_per_tile > 0 ? (rows_per_tile + 3) / 4 * 4 : 4 * gemv_tuning().warps;
+    else
+        j.rows_per_tile = rows_per_tile > 0 ? rows_per_tile : pick_rows_per_tile(type, rows, cols, n_parts, sm_count);
+    if (j.rows_per_tile > 16 && gemv_use_stream(seq, cols)) j.rows_per_tile = 16;
     j.seq = seq;
     j.x_stride = x_stride;
     j.parts[0].w = w;

@@ -131,5 +131,17 @@ def test_step_dev_chain_matches_host_steps():
         ka, va = a.read_kv(layer, 20)
         kb, vb = b.read_kv(layer, 20)
         assert np.array_equal(ka, kb) and np.array_equal(va, vb)
+    # the timing helpers run the same chained steps
+    c = r.Decoder(r.ModelConfig(max_ctx=64, **desc["cfg"]))
+    c.load_description(desc)
+    c.step(7, 0)
+    assert c.time_steps(1, 19) > 0.0
+    for layer in range(2):
+        ka, va = a.read_kv(layer, 20)
+        kc, vc = c.read_kv(layer, 20)
+        assert np.array_equal(ka, kc) and np.array_equal(va, vc)
+    mv = c.time_matvecs(2)
+    assert mv["launches_per_iter"] == 2 * 4 + 1 and mv["ms"] > 0.0
     a.close()
     b.close()
+    c.close()
