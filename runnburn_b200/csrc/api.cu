@@ -29,15 +29,15 @@ bool use_pdl() {
 }
 const GemvTuning &gemv_tuning() {
     static GemvTuning t = [] {
-        GemvTuning v{1, 8, 4};
+        GemvTuning v{0, 8, 4};
         auto env_int = [](const char *name, int dflt, int lo, int hi) {
             const char *e = getenv(name);
             if (!e || !*e) return dflt;
             int x = atoi(e);
             return x < lo ? lo : (x > hi ? hi : x);
         };
-        v.warps = env_int("RNB_B200_GEMV_WARPS", v.warps, 1, 4);
-        v.chunk_blocks = env_int("RNB_B200_GEMV_CHUNK", v.chunk_blocks, 1, 64);
+        v.rows = env_int("RNB_B200_GEMV_ROWS", v.rows, 0, 8);
+        v.chunk_blocks = env_int("RNB_B200_GEMV_CHUNK", v.chunk_blocks, 1, GS_MAX_CHUNK);
         v.stages = env_int("RNB_B200_GEMV_STAGES", v.stages, 1, GS_MAX_STAGES);
         return v;
     }();
@@ -55,6 +55,10 @@ int gemv_kernel_setup() {
     RNB_CU(cudaFuncGetAttributes(&fa, gemv_tile_kernel));
     size_t stat = fa.sharedSizeBytes;
     RNB_CU(cudaFuncGetAttributes(&fa, gemv_tile_kernel_1));
+    if (fa.sharedSizeBytes > stat) stat = fa.sharedSizeBytes;
+    RNB_CU(cudaFuncGetAttributes(&fa, gemv_stream_kernel));
+    if (fa.sharedSizeBytes > stat) stat = fa.sharedSizeBytes;
+    RNB_CU(cudaFuncGetAttributes(&fa, gemv_stream_kernel_1));
     if (fa.sharedSizeBytes > stat) stat = fa.sharedSizeBytes;
     const size_t dyn = (size_t)optin - ((stat + 1023) & ~(size_t)1023);
     RNB_CU(cudaFuncSetAttribute(gemv_tile_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn));
@@ -743,12 +747,8 @@ int rnb_b200_dense_attention_qkv_rope_hd128_decode(const uint8_t *q_w, size_t q_
     uint16_t *kb = reinterpret_cast<uint16_t *>(vd + kv_rows), *vb = kb + kv_rows;
     GemvJob jobs[3];
     float *outs[3] = {qd, kd, vd};
-    int tile0 = 0;
-    for (int i = 0; i < 3; i++) {
-        jobs[i] = make_job((int)types[i], wd[i], st.xq.p, outs[i], nullptr, rows[i], n_embd, 0, st.sm_count);
-        jobs[i].tile0 = tile0;
-        tile0 += (jobs[i].rows + jobs[i].rows_per_tile - 1) / jobs[i].rows_per_tile;
-    }
+    for (int i = 0; i < 3; i++) jobs[i] = make_job((int)types[i], wd[i], st.xq.p, outs[i], nullptr, rows[i], n_embd, 0, st.sm_count);
+    gemv_finalize_group(jobs, 3, n_embd, st.sm_count);
     RNB_TRY(st.jobs.ensure(sizeof(jobs)));
     RNB_TRY(st.h2d(st.jobs.p, jobs, sizeof(jobs), st.pin_jobs));
     RNB_TRY(launch_gemv_jobs(st.stream, jobs, st.jobs.as<GemvJob>(), 3, n_embd, st.dev_error));
@@ -793,7 +793,7 @@ int rnb_b200_dense_q4k_silu_ffn_batch(const uint8_t *gate, size_t gate_len, cons
     GemvJob jobs[2];
     jobs[0] = make_job(TYPE_Q4_K, gd, st.xq.p, st.mid_a.as<float>(), nullptr, n_ff, n_embd, 0, st.sm_count, (int)seq_len, q8k_dev_bytes(n_embd));
     jobs[1] = make_job(TYPE_Q4_K, ud, st.xq.p, st.mid_b.as<float>(), nullptr, n_ff, n_embd, jobs[0].rows_per_tile, st.sm_count, (int)seq_len, q8k_dev_bytes(n_embd));
-    jobs[1].tile0 = (jobs[0].rows + jobs[0].rows_per_tile - 1) / jobs[0].rows_per_tile;
+    gemv_finalize_group(jobs, 2, n_embd, st.sm_count);
     RNB_TRY(st.jobs.ensure(sizeof(jobs)));
     RNB_TRY(st.h2d(st.jobs.p, jobs, sizeof(jobs), st.pin_jobs));
     RNB_TRY(launch_gemv_jobs(st.stream, jobs, st.jobs.as<GemvJob>(), 2, n_embd, st.dev_error));
@@ -889,15 +889,13 @@ int rnb_b200_qwen35_sparse_experts(const uint8_t *const *gate, const uint8_t *co
     RNB_TRY(st.mid_b.ensure(k * n_ff * 4));
     const size_t n_down_jobs = (k + GEMV_MAX_PARTS - 1) / GEMV_MAX_PARTS;
     std::vector<GemvJob> jobs(2 * k + n_down_jobs);
-    int tile0 = 0;
     for (size_t e = 0; e < 2 * k; e++) {
         const bool is_up = e >= k;
         const size_t ee = is_up ? e - k : e;
         jobs[e] = make_job(TYPE_Q4_K, is_up ? ud[ee] : gd[ee], st.xq.p, (is_up ? st.mid_b.as<float>() : st.mid_a.as<float>()) + ee * n_ff,
                            nullptr, n_ff, n_embd, 0, st.sm_count);
-        jobs[e].tile0 = tile0;
-        tile0 += (int)((n_ff + jobs[e].rows_per_tile - 1) / jobs[e].rows_per_tile);
     }
+    gemv_finalize_group(jobs.data(), (int)(2 * k), n_embd, st.sm_count);
     RNB_TRY(st.xq2.ensure(q8k_dev_bytes(n_ff) * k));
     RNB_TRY(st.out_f32.ensure(n_embd * 4));
     RNB_TRY(st.mid_c.ensure(n_embd * 4));

@@ -7,6 +7,7 @@
 // shared by the `group` query heads that map to it; all arithmetic is fp32.
 #pragma once
 #include "common.cuh"
+#include "q8k.cuh"
 
 namespace rnb {
 
@@ -20,7 +21,7 @@ constexpr int HD = 128;
 // grid = num_heads + 2*num_kv_heads CTAs of 64 threads; thread i owns rotation pair i.
 // rope_table: [max_pos][2][64] (cos then sin) indexed by position when table_by_pos != 0,
 // else a single row.  Position = *pos_dev (optional device scalar) + pos_offset.
-__global__ void __launch_bounds__(64)
+RNB_GLOBAL void __launch_bounds__(64)
 rope_kv_append_kernel(float *__restrict__ q, const float *__restrict__ k,
                       const float *__restrict__ v, const float *__restrict__ rope_table,
                       const int *__restrict__ pos_dev, int pos_offset, int table_by_pos,
@@ -76,7 +77,7 @@ rope_kv_append_kernel(float *__restrict__ q, const float *__restrict__ k,
 }
 
 // Plain f32 -> f16 row append (no RoPE) for callers that rotate elsewhere.
-__global__ void kv_append_f16_kernel(const float *__restrict__ src, uint16_t *__restrict__ dst,
+RNB_GLOBAL void kv_append_f16_kernel(const float *__restrict__ src, uint16_t *__restrict__ dst,
                                      size_t n) {
     pdl_launch_dependents();
     pdl_wait();
@@ -198,7 +199,7 @@ __device__ __forceinline__ void fd_process(const float *__restrict__ q, const KV
     }
 }
 
-__global__ void __launch_bounds__(FD_THREADS)
+RNB_GLOBAL void __launch_bounds__(FD_THREADS)
 flash_decode_partials_kernel(const float *__restrict__ q, const uint16_t *__restrict__ k,
                              const uint16_t *__restrict__ v, const int *__restrict__ kv_len_dev,
                              int kv_len_host, int num_heads, int num_kv_heads, float scale,
@@ -223,7 +224,7 @@ flash_decode_partials_kernel(const float *__restrict__ q, const uint16_t *__rest
 }
 
 // grid = num_heads, 128 threads (one per output dim).
-__global__ void __launch_bounds__(HD)
+RNB_GLOBAL void __launch_bounds__(HD)
 flash_decode_reduce_kernel(const float *__restrict__ partials, int n_chunks,
                            float *__restrict__ out) {
     pdl_launch_dependents();
@@ -241,6 +242,40 @@ flash_decode_reduce_kernel(const float *__restrict__ partials, int n_chunks,
         L += pc[HD + 1] * f;
     }
     out[(size_t)h * HD + d] = L > 0.f ? a / L : 0.f;
+}
+
+// Chunk merge fused with the Q8_K quantisation of the attention output (the o_proj input):
+// grid = num_heads / 2, 256 threads; two heads are exactly one 256-element Q8_K block.
+RNB_GLOBAL void __launch_bounds__(2 * HD)
+flash_decode_reduce_q8k_kernel(const float *__restrict__ partials, int n_chunks, int num_heads,
+                               float *__restrict__ out, uint8_t *__restrict__ xq_out) {
+    pdl_launch_dependents();
+    pdl_wait();
+    __shared__ __align__(16) float s_out[2 * HD];
+    const int h = blockIdx.x * 2 + (threadIdx.x >> 7), d = threadIdx.x & (HD - 1);
+    const float *base = partials + (size_t)h * n_chunks * FD_PART_STRIDE;
+    float M = -INFINITY;
+    for (int c = 0; c < n_chunks; c++) M = fmaxf(M, base[(size_t)c * FD_PART_STRIDE + HD]);
+    float a = 0.f, L = 0.f;
+    for (int c = 0; c < n_chunks; c++) {
+        const float *pc = base + (size_t)c * FD_PART_STRIDE;
+        const float mc = pc[HD];
+        const float f = mc == -INFINITY ? 0.f : expf(mc - M);
+        a += pc[d] * f;
+        L += pc[HD + 1] * f;
+    }
+    const float o = L > 0.f ? a / L : 0.f;
+    if (out) out[(size_t)h * HD + d] = o;
+    s_out[threadIdx.x] = o;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        const int lane = threadIdx.x;
+        const float4 v0 = *reinterpret_cast<const float4 *>(s_out + lane * 8), v1 = *reinterpret_cast<const float4 *>(s_out + lane * 8 + 4);
+        const float v[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+        Q8kDevView dv = q8k_dev_view(xq_out, num_heads * HD);
+        const int b = blockIdx.x;
+        q8k_quantize_block_warp(v, lane, dv.qs + b * 256, dv.d + b, dv.bsum16 + b * 16, nullptr);
+    }
 }
 
 }  // namespace rnb

@@ -7,6 +7,10 @@
 
 #include <string>
 
+// Kernels live in headers shared by several translation units: internal linkage keeps each
+// unit's copy private.
+#define RNB_GLOBAL static __global__
+
 namespace rnb {
 
 constexpr int QK_K = 256;

@@ -350,13 +350,13 @@ __device__ __forceinline__ void gemv_tile_body(const GemvJob *__restrict__ jobs,
 }
 
 // Job table in global memory (multi-matrix launches: q/k/v, gate/up, routed experts).
-__global__ void __launch_bounds__(GEMV_THREADS)
+RNB_GLOBAL void __launch_bounds__(GEMV_THREADS)
 gemv_tile_kernel(const GemvJob *__restrict__ jobs, int n_jobs, int cols, uint32_t part_stride,
                  int *__restrict__ dev_error, int dynamic_table) {
     gemv_tile_body(jobs, n_jobs, cols, part_stride, dev_error, dynamic_table);
 }
 // Single job passed by value in kernel-parameter space (no table upload).
-__global__ void __launch_bounds__(GEMV_THREADS)
+RNB_GLOBAL void __launch_bounds__(GEMV_THREADS)
 gemv_tile_kernel_1(const __grid_constant__ GemvJob job, int cols, uint32_t part_stride,
                    int *__restrict__ dev_error) {
     gemv_tile_body(&job, 1, cols, part_stride, dev_error, 0);
@@ -364,7 +364,7 @@ gemv_tile_kernel_1(const __grid_constant__ GemvJob job, int cols, uint32_t part_
 
 // LM-head epilogue: greedy argmax with the reference CPU sampler's tie rule (the LAST of equal
 // maxima, crates/rnb-llm/src/sampler/greedy.rs:4-11).  Single CTA.
-__global__ void __launch_bounds__(1024)
+RNB_GLOBAL void __launch_bounds__(1024)
 argmax_last_kernel(const float *__restrict__ x, int n, uint32_t *__restrict__ idx_out,
                    float *__restrict__ val_out) {
     pdl_launch_dependents();

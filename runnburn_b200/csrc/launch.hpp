@@ -54,49 +54,59 @@ inline uint32_t gemv_part_stride(int type, size_t cols, int rows_per_tile) {
 int gemv_kernel_setup();  // raises the dynamic shared memory limit once
 size_t gemv_smem_max();    // dynamic shared memory a matvec launch may ask for
 
-// Streaming (batch-1) kernel geometry: warps per CTA (4 rows each), super-blocks per stage and
-// pipeline depth; overridable by RNB_B200_GEMV_WARPS / _CHUNK / _STAGES for tuning.
+// Streaming (batch-1) kernel geometry: rows per CTA (0 = choose per launch), super-blocks per
+// stage and pipeline depth; overridable by RNB_B200_GEMV_ROWS / _CHUNK / _STAGES for tuning.
 struct GemvTuning {
-    int warps, chunk_blocks, stages;
+    int rows, chunk_blocks, stages;
 };
 const GemvTuning &gemv_tuning();
 
-inline bool gemv_use_stream(int seq, size_t cols) { return seq <= 1 && cols % 256 == 0; }
-inline uint32_t gs_block_bytes(int type) {
-    return type == TYPE_Q4_K ? Q4K_BYTES : type == TYPE_Q6_K ? Q6K_BYTES : 8 * Q8_0_BYTES;
+inline bool gemv_use_stream(int type, int seq, size_t cols) {
+    return seq <= 1 && cols % 256 == 0 && (type == TYPE_Q4_K || type == TYPE_Q6_K);
+}
+// Rows per CTA for the streaming kernel: the largest of 8, 4, 2 that still gives about six
+// CTAs per SM, so that every SM holds enough warps to hide latency and the tail is short.
+inline int gs_pick_rows(size_t total_rows, int sm_count) {
+    const int forced = gemv_tuning().rows;
+    if (forced == 2 || forced == 4 || forced == 8) return forced;
+    for (int r = 8; r > 2; r /= 2)
+        if ((total_rows + r - 1) / r >= (size_t)(6 * sm_count)) return r;
+    return 2;
 }
 
 inline int launch_gemv_stream(cudaStream_t s, const GemvJob *jobs_host, const GemvJob *jobs_dev, int n_jobs,
                               size_t cols, int *dev_error, int dynamic_table, bool by_value) {
     const GemvTuning &tu = gemv_tuning();
-    const int rows_per_cta = jobs_host[0].rows_per_tile;
+    const int R = jobs_host[0].rows_per_tile;
     int tiles = 0, max_parts = 1;
     uint32_t blk = 0;
     for (int i = 0; i < n_jobs; i++) {
         const GemvJob &j = jobs_host[i];
-        if (j.rows_per_tile != rows_per_cta || rows_per_cta % 4 != 0 || rows_per_cta > 16)
-            return fail(RNB_B200_VALIDATION_FAILED, "matvec jobs of one launch must share rows per CTA (4, 8, 12 or 16)");
-        tiles = j.tile0 + (j.rows + rows_per_cta - 1) / rows_per_cta;
+        if (j.rows_per_tile != R || (R != 2 && R != 4 && R != 8) || !gemv_use_stream(j.type, j.seq, cols))
+            return fail(RNB_B200_VALIDATION_FAILED, "matvec jobs of one launch must share rows per CTA (2, 4 or 8) and be K-quants");
+        tiles = j.tile0 + (j.rows + R - 1) / R;
         if (j.n_parts > max_parts) max_parts = j.n_parts;
-        if (gs_block_bytes(j.type) > blk) blk = gs_block_bytes(j.type);
+        const uint32_t bb = j.type == TYPE_Q4_K ? Q4K_BYTES : Q6K_BYTES;
+        if (bb > blk) blk = bb;
     }
     const int nb = (int)(cols / 256);
     GsParams P;
     P.cols = (int)cols;
+    P.rows_per_cta = R;
     P.chunk_blocks = tu.chunk_blocks < nb ? tu.chunk_blocks : nb;
-    if (P.chunk_blocks >= 8) P.chunk_blocks = P.chunk_blocks / 8 * 8;  // keeps Q6_K chunks 16-byte multiples
     const int n_items = (nb + P.chunk_blocks - 1) / P.chunk_blocks * max_parts;
     P.n_stages = n_items < tu.stages ? n_items : tu.stages;
     P.row_stride = (((uint32_t)P.chunk_blocks * blk + 15u) & ~15u) + 16u;  // rows stay 16-byte aligned
+    P.act_off = (uint32_t)R * P.row_stride;
+    P.slot_bytes = P.act_off + (uint32_t)P.chunk_blocks * 288u;
     P.dynamic_table = dynamic_table;
-    size_t smem = (size_t)P.n_stages * rows_per_cta * P.row_stride;
-    while (smem > gemv_smem_max() && P.n_stages > 1) smem = (size_t)(--P.n_stages) * rows_per_cta * P.row_stride;
+    size_t smem = (size_t)P.n_stages * P.slot_bytes;
+    while (smem > gemv_smem_max() && P.n_stages > 1) smem = (size_t)(--P.n_stages) * P.slot_bytes;
     if (smem > gemv_smem_max()) return fail(RNB_B200_VALIDATION_FAILED, "matvec stage too large: %zu bytes", smem);
-    const dim3 block(rows_per_cta / 4 * 32);
     if (by_value)
-        RNB_CU(launch_k(gemv_stream_kernel_1, dim3(tiles), block, smem, s, jobs_host[0], P, dev_error));
+        RNB_CU(launch_k(gemv_stream_kernel_1, dim3(tiles), dim3(GS_THREADS), smem, s, jobs_host[0], P, dev_error));
     else
-        RNB_CU(launch_k(gemv_stream_kernel, dim3(tiles), block, smem, s, jobs_dev, n_jobs, P, dev_error));
+        RNB_CU(launch_k(gemv_stream_kernel, dim3(tiles), dim3(GS_THREADS), smem, s, jobs_dev, n_jobs, P, dev_error));
     return RNB_B200_OK;
 }
 
@@ -105,7 +115,7 @@ inline int launch_gemv_stream(cudaStream_t s, const GemvJob *jobs_host, const Ge
 inline int launch_gemv_jobs(cudaStream_t s, const GemvJob *jobs_host, const GemvJob *jobs_dev,
                             int n_jobs, size_t cols, int *dev_error, int dynamic_table = 0) {
     RNB_TRY(gemv_kernel_setup());
-    if (gemv_use_stream(jobs_host[0].seq, cols))
+    if (gemv_use_stream(jobs_host[0].type, jobs_host[0].seq, cols))
         return launch_gemv_stream(s, jobs_host, jobs_dev, n_jobs, cols, dev_error, dynamic_table, false);
     int tiles = 0, max_parts = 1;
     uint32_t stride = 0;
@@ -124,7 +134,7 @@ inline int launch_gemv_jobs(cudaStream_t s, const GemvJob *jobs_host, const Gemv
 }
 inline int launch_gemv_one(cudaStream_t s, const GemvJob &job, size_t cols, int *dev_error) {
     RNB_TRY(gemv_kernel_setup());
-    if (gemv_use_stream(job.seq, cols)) return launch_gemv_stream(s, &job, nullptr, 1, cols, dev_error, 0, true);
+    if (gemv_use_stream(job.type, job.seq, cols)) return launch_gemv_stream(s, &job, nullptr, 1, cols, dev_error, 0, true);
     const int tiles = (job.rows + job.rows_per_tile - 1) / job.rows_per_tile;
     const uint32_t stride = gemv_part_stride(job.type, cols, job.rows_per_tile);
     const size_t smem = (size_t)stride * job.n_parts;
@@ -133,8 +143,8 @@ inline int launch_gemv_one(cudaStream_t s, const GemvJob &job, size_t cols, int 
                     stride, dev_error));
     return RNB_B200_OK;
 }
-// rows_per_tile: 0 = automatic.  Batch-1 jobs (seq <= 1, cols % 256 == 0) run on the streaming
-// kernel, whose tiles are 4 rows per warp; batched jobs keep whole-row tiles in shared memory.
+// rows_per_tile: 0 = automatic.  Batch-1 K-quant jobs run on the streaming kernel (2, 4 or 8
+// rows per CTA); batched and Q8_0 jobs keep whole-row tiles in shared memory.
 inline GemvJob make_job(int type, const uint8_t *w, const void *x, float *y, const float *residual,
                         size_t rows, size_t cols, int rows_per_tile, int sm_count, int seq = 1,
                         size_t x_stride = 0, int n_parts = 1) {
@@ -146,17 +156,33 @@ inline GemvJob make_job(int type, const uint8_t *w, const void *x, float *y, con
     j.type = type;
     j.n_parts = n_parts;
     j.tile0 = 0;
-    if (gemv_use_stream(seq, cols))
-        j.rows_per_tile = rows_per_tile > 0 ? (rows_per_tile + 3) / 4 * 4 : 4 * gemv_tuning().warps;
+    if (gemv_use_stream(type, seq, cols))
+        j.rows_per_tile = (rows_per_tile == 2 || rows_per_tile == 4 || rows_per_tile == 8) ? rows_per_tile : gs_pick_rows(rows, sm_count);
     else
         j.rows_per_tile = rows_per_tile > 0 ? rows_per_tile : pick_rows_per_tile(type, rows, cols, n_parts, sm_count);
-    if (j.rows_per_tile > 16 && gemv_use_stream(seq, cols)) j.rows_per_tile = 16;
     j.seq = seq;
     j.x_stride = x_stride;
     j.parts[0].w = w;
     j.parts[0].x = reinterpret_cast<const uint8_t *>(x);
     j.parts[0].scale = nullptr;
     return j;
+}
+// Jobs that go out in one launch: pick the common rows-per-CTA (streaming kernel) and lay the
+// jobs' tiles end to end.
+inline void gemv_finalize_group(GemvJob *jobs, int n, size_t cols, int sm_count) {
+    bool stream = true;
+    size_t total_rows = 0;
+    for (int i = 0; i < n; i++) {
+        stream = stream && gemv_use_stream(jobs[i].type, jobs[i].seq, cols);
+        total_rows += (size_t)jobs[i].rows;
+    }
+    const int R = stream ? gs_pick_rows(total_rows, sm_count) : 0;
+    int tile0 = 0;
+    for (int i = 0; i < n; i++) {
+        if (stream) jobs[i].rows_per_tile = R;
+        jobs[i].tile0 = tile0;
+        tile0 += (jobs[i].rows + jobs[i].rows_per_tile - 1) / jobs[i].rows_per_tile;
+    }
 }
 
 inline int launch_quantize_q8k(cudaStream_t s, const float *x, size_t cols, size_t seq,

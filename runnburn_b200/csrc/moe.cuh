@@ -11,7 +11,7 @@ namespace rnb {
 // crates/rnb-cpu/src/gemm/f32_gemv.rs:215-237,266-275): thread j owns accumulator lane j of
 // the two 8-lane FMA registers, then lanes are folded 8, 4, 2, 1 apart.  Bit-identical
 // logits are what makes the selected expert ids identical.  hidden % 16 == 0.
-__global__ void __launch_bounds__(128)
+RNB_GLOBAL void __launch_bounds__(128)
 router_logits_kernel(const float *__restrict__ w, const float *__restrict__ h, int n_expert,
                      int hidden, float *__restrict__ logits) {
     pdl_launch_dependents();
@@ -35,7 +35,7 @@ router_logits_kernel(const float *__restrict__ w, const float *__restrict__ h, i
 // same contract as the reference's rnb_moe_route_topk_f32
 // (crates/rnb-backend/cuda/cuda/kernels/quant_batch_and_ops.cuh:4782-4912).
 // One warp per token; n_expert <= 1024, top_k <= 32.  exp is taken in double and rounded once.
-__global__ void __launch_bounds__(32)
+RNB_GLOBAL void __launch_bounds__(32)
 moe_route_topk_kernel(const float *__restrict__ logits, int n_expert, int top_k,
                       uint32_t *__restrict__ ids_out, float *__restrict__ weights_out) {
     pdl_launch_dependents();
@@ -87,7 +87,7 @@ struct MoeLayerPtrs {
     const uint8_t *gate_base, *up_base, *down_base;
     size_t gate_stride, down_stride;
 };
-__global__ void moe_fill_jobs_kernel(const uint32_t *__restrict__ ids,
+RNB_GLOBAL void moe_fill_jobs_kernel(const uint32_t *__restrict__ ids,
                                      const float *__restrict__ weights, int top_k,
                                      MoeLayerPtrs lp, GemvJob *__restrict__ gate_up_jobs,
                                      GemvJob *__restrict__ down_job) {

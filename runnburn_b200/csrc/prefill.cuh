@@ -9,7 +9,7 @@ namespace rnb {
 // grid = (seq_len, num_kv_heads), 128 threads: one CTA per (query, KV group); query i sees
 // keys 0..(kv_len - seq_len + i).  q/out f32 [seq][heads][128]; k, v [kv_len][kv_heads][128].
 template <typename KVT>
-__global__ void __launch_bounds__(FD_THREADS)
+RNB_GLOBAL void __launch_bounds__(FD_THREADS)
 prefill_attention_kernel(const float *__restrict__ q, const KVT *__restrict__ k,
                          const KVT *__restrict__ v, int seq_len, int kv_len, int num_heads,
                          int num_kv_heads, float scale, float *__restrict__ out) {

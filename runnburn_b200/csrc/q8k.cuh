@@ -88,7 +88,7 @@ __device__ __forceinline__ Q8kDevView q8k_dev_view(uint8_t *base, int cols) {
 
 // x: [seq][cols] f32.  dev_out: [seq] device-layout vectors (stride q8k_dev_bytes(cols)), may
 // be null.  ref_out: [seq][cols/256] reference 292-byte blocks, may be null.
-__global__ void __launch_bounds__(128)
+RNB_GLOBAL void __launch_bounds__(128)
 quantize_q8k_kernel(const float *__restrict__ x, int cols, int seq, uint8_t *dev_out,
                     uint8_t *ref_out) {
     pdl_launch_dependents();
@@ -112,7 +112,7 @@ quantize_q8k_kernel(const float *__restrict__ x, int cols, int seq, uint8_t *dev
 // (crates/rnb-cpu/src/kernels/norm.rs:177-196), fused with the Q8_K quantisation of the
 // result.  One CTA per token.  `h_out` (f32 normalised vector) is optional.
 template <int THREADS>
-__global__ void __launch_bounds__(THREADS)
+RNB_GLOBAL void __launch_bounds__(THREADS)
 rmsnorm_q8k_kernel(const float *__restrict__ x, const float *__restrict__ w, float eps, int hidden,
                    float *__restrict__ h_out, uint8_t *__restrict__ xq_out) {
     pdl_launch_dependents();
@@ -159,7 +159,7 @@ rmsnorm_q8k_kernel(const float *__restrict__ x, const float *__restrict__ w, flo
 // act = silu(gate) * up with g / (1 + exp(-g)) (crates/rnb-cpu/src/kernels/activation.rs:74-89),
 // fused with Q8_K quantisation.  exp is evaluated in double and rounded once so that the
 // value fed to the quantiser is the correctly rounded one.
-__global__ void __launch_bounds__(128)
+RNB_GLOBAL void __launch_bounds__(128)
 silu_mul_q8k_kernel(const float *__restrict__ gate, const float *__restrict__ up, int n, int seq,
                     float *__restrict__ act_out, uint8_t *__restrict__ xq_out) {
     pdl_launch_dependents();
