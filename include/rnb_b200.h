@@ -283,6 +283,26 @@ int rnb_b200_dev_flash_decode(const float *q_dev, const uint16_t *k_dev, const u
                               float *out_dev, void *stream);
 size_t rnb_b200_flash_decode_scratch_bytes(size_t num_heads, int n_chunks);
 int rnb_b200_flash_decode_default_chunks(size_t kv_len, size_t num_kv_heads);
+/* Decode attention for hosts that must not allocate device memory after start-up (a plug-in
+ * inside a server with a frozen memory pool, a sandbox whose allocator hooks abort on late
+ * allocations, a real-time loop that may not take the driver's allocation locks).  This entry
+ * point has no counterpart in the reference.  Same arithmetic as
+ * rnb_b200_dev_flash_decode, but the per-chunk partial results live in a fixed array inside
+ * the library (1 064 960 bytes per device that loads it, held until the process exits), so the
+ * call performs no cudaMalloc, cudaFree or allocating library call.  All pointers are device
+ * pointers owned by the caller; `stream` is a cudaStream_t or NULL; the call does not
+ * synchronise.  Limits: at most 64 query heads (more is rejected with
+ * RNB_B200_VALIDATION_FAILED); head_dim 128; long contexts are split into at most 32 chunks.
+ * The first call on each device looks up the array's device address (one
+ * cudaGetSymbolAddress); make that first call before starting any stream capture.
+ * Every call on a device uses the same array: calls that overlap on the GPU (different
+ * streams, or this entry point from two threads) race on it and must be serialised by the
+ * caller.  Nothing in the array needs clearing between calls: each call rewrites every record
+ * it later reads. */
+int rnb_b200_attention_decode_hd128_noalloc(const float *q_dev, const uint16_t *k_dev,
+                                            const uint16_t *v_dev, size_t kv_len,
+                                            size_t num_heads, size_t num_kv_heads, float scale,
+                                            float *out_dev, void *stream);
 /* Reads and clears the device error word set by kernels whose bounded waits gave up. */
 int rnb_b200_dev_error_flag(int *flag_out);
 
