@@ -29,14 +29,14 @@ bool use_pdl() {
 }
 const GemvTuning &gemv_tuning() {
     static GemvTuning t = [] {
-        GemvTuning v{0, 8, 4};
+        GemvTuning v{0, 8, 2};
         auto env_int = [](const char *name, int dflt, int lo, int hi) {
             const char *e = getenv(name);
             if (!e || !*e) return dflt;
             int x = atoi(e);
             return x < lo ? lo : (x > hi ? hi : x);
         };
-        v.rows = env_int("RNB_B200_GEMV_ROWS", v.rows, 0, 8);
+        v.rows = env_int("RNB_B200_GEMV_ROWS", v.rows, 0, 16);
         v.chunk_blocks = env_int("RNB_B200_GEMV_CHUNK", v.chunk_blocks, 1, GS_MAX_CHUNK);
         v.stages = env_int("RNB_B200_GEMV_STAGES", v.stages, 1, GS_MAX_STAGES);
         return v;

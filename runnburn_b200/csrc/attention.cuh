@@ -232,8 +232,10 @@ flash_decode_reduce_kernel(const float *__restrict__ partials, int n_chunks,
     const int h = blockIdx.x, d = threadIdx.x;
     const float *base = partials + (size_t)h * n_chunks * FD_PART_STRIDE;
     float M = -INFINITY;
+#pragma unroll 8
     for (int c = 0; c < n_chunks; c++) M = fmaxf(M, base[(size_t)c * FD_PART_STRIDE + HD]);
     float a = 0.f, L = 0.f;
+#pragma unroll 8
     for (int c = 0; c < n_chunks; c++) {
         const float *pc = base + (size_t)c * FD_PART_STRIDE;
         const float mc = pc[HD];
@@ -246,30 +248,46 @@ flash_decode_reduce_kernel(const float *__restrict__ partials, int n_chunks,
 
 // Chunk merge fused with the Q8_K quantisation of the attention output (the o_proj input):
 // grid = num_heads / 2, 256 threads; two heads are exactly one 256-element Q8_K block.
+// The 128 threads of a head first agree on the global max and the per-chunk rescale factors
+// (kept in shared memory), then each sums its output dimension over the chunks.
+constexpr int FD_MAX_CHUNKS = 1024;
 RNB_GLOBAL void __launch_bounds__(2 * HD)
 flash_decode_reduce_q8k_kernel(const float *__restrict__ partials, int n_chunks, int num_heads,
                                float *__restrict__ out, uint8_t *__restrict__ xq_out) {
     pdl_launch_dependents();
     pdl_wait();
     __shared__ __align__(16) float s_out[2 * HD];
-    const int h = blockIdx.x * 2 + (threadIdx.x >> 7), d = threadIdx.x & (HD - 1);
+    __shared__ float s_f[2][FD_MAX_CHUNKS];
+    __shared__ float s_red[2][4];
+    const int hs = threadIdx.x >> 7, d = threadIdx.x & (HD - 1), wq = d >> 5, lane = d & 31;
+    const int h = blockIdx.x * 2 + hs;
     const float *base = partials + (size_t)h * n_chunks * FD_PART_STRIDE;
-    float M = -INFINITY;
-    for (int c = 0; c < n_chunks; c++) M = fmaxf(M, base[(size_t)c * FD_PART_STRIDE + HD]);
-    float a = 0.f, L = 0.f;
-    for (int c = 0; c < n_chunks; c++) {
-        const float *pc = base + (size_t)c * FD_PART_STRIDE;
-        const float mc = pc[HD];
+    float m = -INFINITY;
+    for (int c = d; c < n_chunks; c += HD) m = fmaxf(m, base[(size_t)c * FD_PART_STRIDE + HD]);
+    m = warp_max(m);
+    if (lane == 0) s_red[hs][wq] = m;
+    __syncthreads();
+    const float M = fmaxf(fmaxf(s_red[hs][0], s_red[hs][1]), fmaxf(s_red[hs][2], s_red[hs][3]));
+    __syncthreads();
+    float l = 0.f;
+    for (int c = d; c < n_chunks; c += HD) {
+        const float mc = base[(size_t)c * FD_PART_STRIDE + HD];
         const float f = mc == -INFINITY ? 0.f : expf(mc - M);
-        a += pc[d] * f;
-        L += pc[HD + 1] * f;
+        s_f[hs][c] = f;
+        l += base[(size_t)c * FD_PART_STRIDE + HD + 1] * f;
     }
+    l = warp_sum(l);
+    if (lane == 0) s_red[hs][wq] = l;
+    __syncthreads();
+    const float L = (s_red[hs][0] + s_red[hs][1]) + (s_red[hs][2] + s_red[hs][3]);
+    float a = 0.f;
+#pragma unroll 8
+    for (int c = 0; c < n_chunks; c++) a += base[(size_t)c * FD_PART_STRIDE + d] * s_f[hs][c];
     const float o = L > 0.f ? a / L : 0.f;
     if (out) out[(size_t)h * HD + d] = o;
     s_out[threadIdx.x] = o;
     __syncthreads();
     if (threadIdx.x < 32) {
-        const int lane = threadIdx.x;
         const float4 v0 = *reinterpret_cast<const float4 *>(s_out + lane * 8), v1 = *reinterpret_cast<const float4 *>(s_out + lane * 8 + 4);
         const float v[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
         Q8kDevView dv = q8k_dev_view(xq_out, num_heads * HD);

@@ -405,4 +405,77 @@ argmax_last_kernel(const float *__restrict__ x, int n, uint32_t *__restrict__ id
     }
 }
 
+// Two-stage form for long vectors (the 128k-entry logits): stage 1 leaves one (value, index)
+// candidate per CTA of 1024 threads x 4 elements, stage 2 is argmax_last_pairs_kernel.
+RNB_GLOBAL void __launch_bounds__(1024)
+argmax_last_partial_kernel(const float *__restrict__ x, int n, float *__restrict__ vals, uint32_t *__restrict__ idxs) {
+    pdl_launch_dependents();
+    pdl_wait();
+    __shared__ float sv[32];
+    __shared__ int si[32];
+    float best = -INFINITY;
+    int bi = -1;
+    const int i0 = blockIdx.x * 4096;
+    for (int i = i0 + threadIdx.x; i < n && i < i0 + 4096; i += 1024) {
+        const float v = x[i];
+        if (bi < 0 || v >= best) {
+            best = v;
+            bi = i;
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (oi >= 0 && (bi < 0 || ov > best || (ov == best && oi > bi))) {
+            best = ov;
+            bi = oi;
+        }
+    }
+    if ((threadIdx.x & 31) == 0) {
+        sv[threadIdx.x >> 5] = best;
+        si[threadIdx.x >> 5] = bi;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 0; w < 32; w++)
+            if (si[w] >= 0 && (bi < 0 || sv[w] > best || (sv[w] == best && si[w] > bi))) {
+                best = sv[w];
+                bi = si[w];
+            }
+        vals[blockIdx.x] = best;
+        idxs[blockIdx.x] = (uint32_t)bi;
+    }
+}
+// one warp: last index of the maximum among n (value, index) candidates
+RNB_GLOBAL void __launch_bounds__(32)
+argmax_last_pairs_kernel(const float *__restrict__ vals, const uint32_t *__restrict__ idxs, int n, uint32_t *__restrict__ idx_out,
+                         float *__restrict__ val_out) {
+    pdl_launch_dependents();
+    pdl_wait();
+    float best = -INFINITY;
+    long long bi = -1;
+    for (int i = threadIdx.x; i < n; i += 32) {
+        const float v = vals[i];
+        const long long id = idxs[i];
+        if (bi < 0 || v > best || (v == best && id > bi)) {
+            best = v;
+            bi = id;
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const long long oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (oi >= 0 && (bi < 0 || ov > best || (ov == best && oi > bi))) {
+            best = ov;
+            bi = oi;
+        }
+    }
+    if (threadIdx.x == 0) {
+        *idx_out = (uint32_t)bi;
+        if (val_out) *val_out = best;
+    }
+}
+
 }  // namespace rnb

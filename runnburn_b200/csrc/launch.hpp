@@ -64,14 +64,12 @@ const GemvTuning &gemv_tuning();
 inline bool gemv_use_stream(int type, int seq, size_t cols) {
     return seq <= 1 && cols % 256 == 0 && (type == TYPE_Q4_K || type == TYPE_Q6_K);
 }
-// Rows per CTA for the streaming kernel: the largest of 8, 4, 2 that still gives about six
-// CTAs per SM, so that every SM holds enough warps to hide latency and the tail is short.
+// Rows per CTA for the streaming kernel (4 per warp): 8 when that still leaves eight CTAs
+// per SM, else 4 - row-poor matrices need every warp they can get.
 inline int gs_pick_rows(size_t total_rows, int sm_count) {
     const int forced = gemv_tuning().rows;
-    if (forced == 2 || forced == 4 || forced == 8) return forced;
-    for (int r = 8; r > 2; r /= 2)
-        if ((total_rows + r - 1) / r >= (size_t)(6 * sm_count)) return r;
-    return 2;
+    if (forced == 4 || forced == 8 || forced == 16) return forced;
+    return (total_rows + 7) / 8 >= (size_t)(8 * sm_count) ? 8 : 4;
 }
 
 inline int launch_gemv_stream(cudaStream_t s, const GemvJob *jobs_host, const GemvJob *jobs_dev, int n_jobs,
@@ -82,8 +80,8 @@ inline int launch_gemv_stream(cudaStream_t s, const GemvJob *jobs_host, const Ge
     uint32_t blk = 0;
     for (int i = 0; i < n_jobs; i++) {
         const GemvJob &j = jobs_host[i];
-        if (j.rows_per_tile != R || (R != 2 && R != 4 && R != 8) || !gemv_use_stream(j.type, j.seq, cols))
-            return fail(RNB_B200_VALIDATION_FAILED, "matvec jobs of one launch must share rows per CTA (2, 4 or 8) and be K-quants");
+        if (j.rows_per_tile != R || (R != 4 && R != 8 && R != 16) || !gemv_use_stream(j.type, j.seq, cols))
+            return fail(RNB_B200_VALIDATION_FAILED, "matvec jobs of one launch must share a valid rows-per-CTA and be K-quants");
         tiles = j.tile0 + (j.rows + R - 1) / R;
         if (j.n_parts > max_parts) max_parts = j.n_parts;
         const uint32_t bb = j.type == TYPE_Q4_K ? Q4K_BYTES : Q6K_BYTES;
@@ -104,9 +102,9 @@ inline int launch_gemv_stream(cudaStream_t s, const GemvJob *jobs_host, const Ge
     while (smem > gemv_smem_max() && P.n_stages > 1) smem = (size_t)(--P.n_stages) * P.slot_bytes;
     if (smem > gemv_smem_max()) return fail(RNB_B200_VALIDATION_FAILED, "matvec stage too large: %zu bytes", smem);
     if (by_value)
-        RNB_CU(launch_k(gemv_stream_kernel_1, dim3(tiles), dim3(GS_THREADS), smem, s, jobs_host[0], P, dev_error));
+        RNB_CU(launch_k(gemv_stream_kernel_1, dim3(tiles), dim3(R * 8), smem, s, jobs_host[0], P, dev_error));
     else
-        RNB_CU(launch_k(gemv_stream_kernel, dim3(tiles), dim3(GS_THREADS), smem, s, jobs_dev, n_jobs, P, dev_error));
+        RNB_CU(launch_k(gemv_stream_kernel, dim3(tiles), dim3(R * 8), smem, s, jobs_dev, n_jobs, P, dev_error));
     return RNB_B200_OK;
 }
 
@@ -143,7 +141,7 @@ inline int launch_gemv_one(cudaStream_t s, const GemvJob &job, size_t cols, int 
                     stride, dev_error));
     return RNB_B200_OK;
 }
-// rows_per_tile: 0 = automatic.  Batch-1 K-quant jobs run on the streaming kernel (2, 4 or 8
+// rows_per_tile: 0 = automatic.  Batch-1 K-quant jobs run on the streaming kernel (4, 8 or 16
 // rows per CTA); batched and Q8_0 jobs keep whole-row tiles in shared memory.
 inline GemvJob make_job(int type, const uint8_t *w, const void *x, float *y, const float *residual,
                         size_t rows, size_t cols, int rows_per_tile, int sm_count, int seq = 1,
@@ -157,7 +155,7 @@ inline GemvJob make_job(int type, const uint8_t *w, const void *x, float *y, con
     j.n_parts = n_parts;
     j.tile0 = 0;
     if (gemv_use_stream(type, seq, cols))
-        j.rows_per_tile = (rows_per_tile == 2 || rows_per_tile == 4 || rows_per_tile == 8) ? rows_per_tile : gs_pick_rows(rows, sm_count);
+        j.rows_per_tile = (rows_per_tile == 4 || rows_per_tile == 8 || rows_per_tile == 16) ? rows_per_tile : gs_pick_rows(rows, sm_count);
     else
         j.rows_per_tile = rows_per_tile > 0 ? rows_per_tile : pick_rows_per_tile(type, rows, cols, n_parts, sm_count);
     j.seq = seq;
@@ -199,6 +197,7 @@ inline int flash_decode_default_chunks(size_t kv_len, size_t num_kv_heads, int s
     long want = (long)(4 * sm_count) / (long)(num_kv_heads ? num_kv_heads : 1);
     long max_c = (long)((kv_len + 31) / 32);
     if (want > max_c) want = max_c;
+    if (want > FD_MAX_CHUNKS) want = FD_MAX_CHUNKS;
     if (want < 1) want = 1;
     return (int)want;
 }
