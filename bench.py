@@ -31,6 +31,8 @@ WORKLOADS = {
     # name: (shape, context, description)
     "llama3-8b-q4km-ctx4096": (dict(n_layer=32, hidden=4096, n_head=32, n_kv_head=8, n_ff=14336, vocab=128256), 4096),
     "llama3-70b-q4km-ctx32768": (dict(n_layer=80, hidden=8192, n_head=64, n_kv_head=8, n_ff=28672, vocab=128256), 32768),
+    # two layers of the 8B shapes + its LM head: the capture-sized case for ncu (about 1 GB resident)
+    "llama3-8b-2layers-ctx4096": (dict(n_layer=2, hidden=4096, n_head=32, n_kv_head=8, n_ff=14336, vocab=128256), 4096),
     "tiny-llama-ctx256": (dict(n_layer=2, hidden=512, n_head=4, n_kv_head=2, n_ff=1024, vocab=2048), 256),
 }
 METRIC = "decode_tok_per_s_batch1"
@@ -310,7 +312,7 @@ def run_gpu(args, shape, ctx, name, rank, world, local_rank):
         per_launch_bytes = mv["bytes_per_iter"] / mv["launches_per_iter"]
         per_launch_s = mv["ms"] / 1000.0 / (mv["iters"] * mv["launches_per_iter"])
         ach = per_launch_bytes / per_launch_s / 1e9
-        out["roofline"] = {"kernel": "gemv_tile_kernel", "bound": "hbm", "achieved": ach, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+        out["roofline"] = {"kernel": "gemv_stream_kernel", "bound": "hbm", "achieved": ach, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                            "frac": ach / peaks["hbm_gbs"], "frac_of_8TBs_nominal": ach / 8000.0, "peak_source": peaks["source"],
                            "traffic": None, "launches_per_step": mv["launches_per_iter"],
                            "algorithmic_bytes_per_launch": per_launch_bytes, "avg_launch_us": per_launch_s * 1e6,

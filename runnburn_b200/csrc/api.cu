@@ -534,7 +534,7 @@ static int attention_run(State &st, const uint16_t *k_dev, const uint16_t *v_dev
     RNB_TRY(st.partials.ensure(flash_decode_scratch_bytes(heads, n_chunks)));
     RNB_TRY(st.out_f32.ensure(heads * HD * sizeof(float)));
     RNB_TRY(launch_flash_decode(st.stream, st.in_f32.as<float>(), k_dev, v_dev, nullptr, (int)kv_len, (int)heads,
-                                (int)kv_heads, scale, st.partials.as<float>(), n_chunks, st.out_f32.as<float>()));
+                                (int)kv_heads, scale, st.partials.as<float>(), n_chunks, st.out_f32.as<float>(), st.dev_error));
     return finish_to_host(st, st.out_f32.p, out, heads * HD * sizeof(float));
 }
 
@@ -990,7 +990,7 @@ int rnb_b200_dev_flash_decode(const float *q_dev, const uint16_t *k_dev, const u
     Locked L;
     RNB_TRY(L.st.open());
     return launch_flash_decode((cudaStream_t)stream, q_dev, k_dev, v_dev, nullptr, (int)kv_len, (int)num_heads, (int)num_kv_heads, scale,
-                               partials_dev, n_chunks, out_dev);
+                               partials_dev, n_chunks, out_dev, L.st.dev_error);
 }
 int rnb_b200_dev_error_flag(int *flag_out) {
     Locked L;

@@ -223,6 +223,234 @@ flash_decode_partials_kernel(const float *__restrict__ q, const uint16_t *__rest
     }
 }
 
+// ---- split-KV flash decode on the tensor cores (f16 caches) ---------------------------------
+// Same grid, chunking and partial-record format as flash_decode_partials_kernel, but the K/V
+// rows of a chunk are staged in shared memory by 256-byte bulk copies (one per row, completing
+// on an mbarrier per 16-position block) and both products run as m16n8k16 MMAs with fp32
+// accumulators, with the (up to 8) query heads of a KV group as the N dimension:
+//   S^T[pos][head] = K[pos][dim] . Q^T[dim][head]     A = K rows as stored, B = query
+//   O^T[dim][head] += V^T[dim][pos] . P^T[pos][head]  A = V rows read transposed, B = P
+// K and V are exact f16 values; the pre-scaled f32 query and the f32 probabilities are each
+// split into two f16 terms (hi + lo), so the products keep ~22 mantissa bits.
+// Warp w owns positions [16w, 16w+16) of each 64-position staging pass and keeps its own
+// running (max, sum, O); the four warps are merged through shared memory at the end.
+constexpr int FDM_THREADS = 128;
+constexpr int FDM_SUPER = 64;             // positions staged per pass
+constexpr int FDM_ROW = 2 * HD + 16;      // padded row: ldmatrix without bank conflicts
+constexpr int FDM_KV_BYTES = 2 * FDM_SUPER * FDM_ROW;
+constexpr int FDM_ACC_STRIDE = HD + 4;    // merge scratch row (floats), padded against conflicts
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(addr)
+                 : "memory");
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(addr)
+                 : "memory");
+}
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
+    uint32_t d;
+    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(d) : "r"(a));
+    return d;
+}
+__device__ __forceinline__ void mma_f16_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+        "{%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+// (x, y) -> f16x2 "hi" and the f16x2 remainder "lo"
+__device__ __forceinline__ void split_f16x2(float x, float y, uint32_t &hi, uint32_t &lo) {
+    const __half2 h = __floats2half2_rn(x, y);
+    const float2 hf = __half22float2(h);
+    const __half2 l = __floats2half2_rn(x - hf.x, y - hf.y);
+    hi = *reinterpret_cast<const uint32_t *>(&h);
+    lo = *reinterpret_cast<const uint32_t *>(&l);
+}
+
+RNB_GLOBAL void __launch_bounds__(FDM_THREADS, 4)
+flash_decode_mma_kernel(const float *__restrict__ q, const uint16_t *__restrict__ k,
+                        const uint16_t *__restrict__ v, const int *__restrict__ kv_len_dev,
+                        int kv_len_host, int num_heads, int num_kv_heads, float scale,
+                        float *__restrict__ partials, int *__restrict__ err_flag) {
+    pdl_launch_dependents();
+    pdl_wait();
+    __shared__ __align__(128) uint8_t s_kv[FDM_KV_BYTES];   // K rows then V rows; merge scratch later
+    __shared__ __align__(8) uint64_t s_bar[FDM_SUPER / 16];
+    __shared__ float s_ml[(FDM_THREADS / 32) * 8 * 2];
+    static_assert((FDM_THREADS / 32) * 8 * FDM_ACC_STRIDE * 4 <= FDM_KV_BYTES, "merge scratch must fit the staging area");
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    const int kv_len = kv_len_dev ? *kv_len_dev + kv_len_host : kv_len_host;
+    const int n_chunks = gridDim.y, chunk = blockIdx.y, kv_h = blockIdx.x;
+    int chunk_len = (kv_len + n_chunks - 1) / n_chunks;
+    chunk_len = (chunk_len + 15) & ~15;
+    const int p_begin = min(kv_len, chunk * chunk_len), p_end = min(kv_len, p_begin + chunk_len);
+    const int group = num_heads / num_kv_heads;
+    const size_t kv_dim = (size_t)num_kv_heads * HD;
+    uint8_t *s_k = s_kv, *s_v = s_kv + FDM_SUPER * FDM_ROW;
+    if (tid < FDM_SUPER / 16) mbar_init(&s_bar[tid], 32);   // 16 K-row + 16 V-row issuers per block
+    mbar_fence_init();
+    uint32_t phase = 0;
+    const int my_row = tid & (FDM_SUPER - 1), my_is_v = tid >> 6;
+    const int mi = lane >> 3, mr = lane & 7;   // ldmatrix: this lane addresses row mr of matrix mi
+
+    for (int g0 = 0; g0 < group; g0 += 8) {
+        const int heads_here = min(8, group - g0), head0 = kv_h * group + g0;
+        // query B fragments: column (head) g, dims ks*16 + {2t, 2t+1} and + 8
+        uint32_t qh[8][2], ql[8][2];
+#pragma unroll
+        for (int ks = 0; ks < 8; ks++)
+#pragma unroll
+            for (int hf = 0; hf < 2; hf++) {
+                float2 qv = make_float2(0.f, 0.f);
+                if (g < heads_here)
+                    qv = *reinterpret_cast<const float2 *>(q + (size_t)(head0 + g) * HD + ks * 16 + hf * 8 + 2 * t);
+                split_f16x2(qv.x * scale, qv.y * scale, qh[ks][hf], ql[ks][hf]);
+            }
+        float o[8][4];   // O^T tile mt: (dim 16mt+g | +8, head 2t | 2t+1)
+#pragma unroll
+        for (int n = 0; n < 8; n++) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+        float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};   // heads 2t, 2t+1 (l: this thread's share)
+
+        for (int sp = p_begin; sp < p_end; sp += FDM_SUPER) {
+            const int n_here = min(FDM_SUPER, p_end - sp);
+            __syncthreads();   // everyone is done with the previous pass's rows (and barrier init)
+            {
+                uint64_t *bar = &s_bar[my_row >> 4];
+                if (my_row < n_here) {
+                    const uint16_t *src = (my_is_v ? v : k) + (size_t)(sp + my_row) * kv_dim + (size_t)kv_h * HD;
+                    mbar_arrive_expect_tx(bar, 2 * HD);
+                    bulk_g2s((my_is_v ? s_v : s_k) + my_row * FDM_ROW, src, 2 * HD, bar);
+                } else {
+                    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+                }
+            }
+            const int rows = min(16, n_here - 16 * warp);
+            if (rows > 0) {
+                // rows past the end of a ragged block hold stale bytes: zero them so that a
+                // masked probability (0) never meets a NaN/Inf pattern
+                if (rows < 16) {
+                    const int n_seg = (16 - rows) * 16;   // 16-byte segments per array
+                    for (int i = lane; i < 2 * n_seg; i += 32) {
+                        const int which = i / n_seg, j = i % n_seg;
+                        uint8_t *row = (which ? s_v : s_k) + (16 * warp + rows + j / 16) * FDM_ROW;
+                        *reinterpret_cast<uint4 *>(row + (j % 16) * 16) = make_uint4(0, 0, 0, 0);
+                    }
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    __syncwarp();
+                }
+                if (!mbar_wait_bounded(&s_bar[warp], phase)) {
+                    if (lane == 0 && err_flag) atomicExch(err_flag, DEV_ERR_MBAR_TIMEOUT);
+                } else {
+                    // ---- S^T = K Q^T for this warp's 16 positions ----
+                    float sc[4] = {0.f, 0.f, 0.f, 0.f};   // (pos g, head 2t) (g, 2t+1) (g+8, 2t) (g+8, 2t+1)
+                    const uint32_t k_base = smem_u32(s_k) + (16 * warp + (mi & 1) * 8 + mr) * FDM_ROW + (mi >> 1) * 16;
+#pragma unroll
+                    for (int ks = 0; ks < 8; ks++) {
+                        uint32_t a[4];
+                        ldmatrix_x4(a, k_base + ks * 32);
+                        mma_f16_16816(sc, a, qh[ks][0], qh[ks][1]);
+                        mma_f16_16816(sc, a, ql[ks][0], ql[ks][1]);
+                    }
+                    if (g >= rows) sc[0] = sc[1] = -INFINITY;
+                    if (g + 8 >= rows) sc[2] = sc[3] = -INFINITY;
+                    // ---- online softmax per head (column): max over the 16 positions ----
+                    float corr[2], pr[4];
+#pragma unroll
+                    for (int e = 0; e < 2; e++) {
+                        float mx = fmaxf(sc[e], sc[2 + e]);
+                        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+                        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
+                        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
+                        const float m_new = fmaxf(m_run[e], mx);
+                        corr[e] = m_run[e] == -INFINITY ? 0.f : expf(m_run[e] - m_new);
+                        pr[e] = sc[e] == -INFINITY ? 0.f : expf(sc[e] - m_new);
+                        pr[2 + e] = sc[2 + e] == -INFINITY ? 0.f : expf(sc[2 + e] - m_new);
+                        l_run[e] = l_run[e] * corr[e] + (pr[e] + pr[2 + e]);
+                        m_run[e] = m_new;
+                    }
+#pragma unroll
+                    for (int n = 0; n < 8; n++) {
+                        o[n][0] *= corr[0];
+                        o[n][1] *= corr[1];
+                        o[n][2] *= corr[0];
+                        o[n][3] *= corr[1];
+                    }
+                    // P^T as B fragments: transpose the two 8x8 (pos x head) tiles across the warp
+                    uint32_t p_lo_h, p_lo_l, p_hi_h, p_hi_l;
+                    split_f16x2(pr[0], pr[1], p_lo_h, p_lo_l);   // positions 0..7
+                    split_f16x2(pr[2], pr[3], p_hi_h, p_hi_l);   // positions 8..15
+                    const uint32_t b0h = movmatrix_trans(p_lo_h), b0l = movmatrix_trans(p_lo_l);
+                    const uint32_t b1h = movmatrix_trans(p_hi_h), b1l = movmatrix_trans(p_hi_l);
+                    // ---- O^T += V^T P^T: A tiles are V[pos][dim] read transposed ----
+                    const uint32_t v_base = smem_u32(s_v) + (16 * warp + (mi >> 1) * 8 + mr) * FDM_ROW + (mi & 1) * 16;
+#pragma unroll
+                    for (int mt = 0; mt < 8; mt++) {
+                        uint32_t a[4];
+                        ldmatrix_x4_trans(a, v_base + mt * 32);
+                        mma_f16_16816(o[mt], a, b0h, b1h);
+                        mma_f16_16816(o[mt], a, b0l, b1l);
+                    }
+                }
+            }
+            phase ^= 1;
+        }
+        // ---- merge the four warps (staging area reused as [warp][8 heads][128] f32) ----
+#pragma unroll
+        for (int e = 0; e < 2; e++) {
+            l_run[e] += __shfl_xor_sync(0xffffffffu, l_run[e], 4);
+            l_run[e] += __shfl_xor_sync(0xffffffffu, l_run[e], 8);
+            l_run[e] += __shfl_xor_sync(0xffffffffu, l_run[e], 16);
+        }
+        __syncthreads();
+        float *s_acc = reinterpret_cast<float *>(s_kv);
+#pragma unroll
+        for (int mt = 0; mt < 8; mt++) {
+            float *r0 = s_acc + (size_t)(warp * 8 + 2 * t) * FDM_ACC_STRIDE + mt * 16 + g;
+            r0[0] = o[mt][0];
+            r0[FDM_ACC_STRIDE] = o[mt][1];
+            r0[8] = o[mt][2];
+            r0[FDM_ACC_STRIDE + 8] = o[mt][3];
+        }
+        if (g == 0) {
+#pragma unroll
+            for (int e = 0; e < 2; e++) {
+                s_ml[(warp * 8 + 2 * t + e) * 2] = m_run[e];
+                s_ml[(warp * 8 + 2 * t + e) * 2 + 1] = l_run[e];
+            }
+        }
+        __syncthreads();
+        for (int hh = 0; hh < heads_here; hh++) {
+            const int d = tid;
+            float M = -INFINITY;
+#pragma unroll
+            for (int w = 0; w < FDM_THREADS / 32; w++) M = fmaxf(M, s_ml[(w * 8 + hh) * 2]);
+            float a = 0.f, L = 0.f;
+#pragma unroll
+            for (int w = 0; w < FDM_THREADS / 32; w++) {
+                const float mw = s_ml[(w * 8 + hh) * 2];
+                const float f = mw == -INFINITY ? 0.f : expf(mw - M);
+                a += s_acc[(size_t)(w * 8 + hh) * FDM_ACC_STRIDE + d] * f;
+                L += s_ml[(w * 8 + hh) * 2 + 1] * f;
+            }
+            float *out = partials + ((size_t)(head0 + hh) * n_chunks + chunk) * FD_PART_STRIDE;
+            out[d] = a;
+            if (d == 0) {
+                out[HD] = M;
+                out[HD + 1] = L;
+            }
+        }
+        // the next head pass overwrites s_kv through the async proxy after these generic reads
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+}
+
 // grid = num_heads, 128 threads (one per output dim).
 RNB_GLOBAL void __launch_bounds__(HD)
 flash_decode_reduce_kernel(const float *__restrict__ partials, int n_chunks,

@@ -204,13 +204,34 @@ inline int flash_decode_default_chunks(size_t kv_len, size_t num_kv_heads, int s
 inline size_t flash_decode_scratch_bytes(size_t num_heads, int n_chunks) {
     return num_heads * (size_t)n_chunks * FD_PART_STRIDE * sizeof(float);
 }
+// Partial records of every (head, chunk).  f16 caches on 16-byte boundaries take the
+// tensor-core kernel (its bulk copies need that alignment); anything else the CUDA-core one.
+inline bool flash_decode_force_simt() {
+    static const bool v = [] {
+        const char *e = getenv("RNB_B200_FD_SIMT");
+        return e && *e == '1';
+    }();
+    return v;
+}
+inline int launch_flash_decode_partials(cudaStream_t s, const float *q, const uint16_t *k, const uint16_t *v,
+                                        const int *kv_len_dev, int kv_len_host, int num_heads, int num_kv_heads,
+                                        float scale, float *partials, int n_chunks, int *dev_error) {
+    const bool aligned = (((uintptr_t)k | (uintptr_t)v) & 15) == 0;
+    if (aligned && !flash_decode_force_simt())
+        RNB_CU(launch_k(flash_decode_mma_kernel, dim3(num_kv_heads, n_chunks), dim3(FDM_THREADS), 0, s, q, k, v, kv_len_dev,
+                        kv_len_host, num_heads, num_kv_heads, scale, partials, dev_error));
+    else
+        RNB_CU(launch_k(flash_decode_partials_kernel, dim3(num_kv_heads, n_chunks), dim3(FD_THREADS), 0, s, q, k, v,
+                        kv_len_dev, kv_len_host, num_heads, num_kv_heads, scale, partials));
+    return RNB_B200_OK;
+}
 // kv_len = (*kv_len_dev if given) + kv_len_host
 inline int launch_flash_decode(cudaStream_t s, const float *q, const uint16_t *k, const uint16_t *v,
                                const int *kv_len_dev, int kv_len_host, int num_heads,
                                int num_kv_heads, float scale, float *partials, int n_chunks,
-                               float *out) {
-    RNB_CU(launch_k(flash_decode_partials_kernel, dim3(num_kv_heads, n_chunks), dim3(FD_THREADS), 0,
-                    s, q, k, v, kv_len_dev, kv_len_host, num_heads, num_kv_heads, scale, partials));
+                               float *out, int *dev_error = nullptr) {
+    RNB_TRY(launch_flash_decode_partials(s, q, k, v, kv_len_dev, kv_len_host, num_heads, num_kv_heads, scale, partials,
+                                         n_chunks, dev_error));
     RNB_CU(launch_k(flash_decode_reduce_kernel, dim3(num_heads), dim3(HD), 0, s,
                     (const float *)partials, n_chunks, out));
     return RNB_B200_OK;

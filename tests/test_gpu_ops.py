@@ -9,7 +9,7 @@ import numpy as np
 import pytest
 
 import oracle as orc
-from synth import Q4_K, Q6_K, Q8_0, max_rel_err, quantized, random_blocks
+from synth import Q4_K, Q6_K, Q8_0, max_rel_err, max_err_vs_norm, quantized, random_blocks
 
 pytestmark = pytest.mark.gpu
 
@@ -196,7 +196,7 @@ def test_resident_cache_counters_and_eviction(ops):
 
 # ---- attention ----------------------------------------------------------------------------------
 @pytest.mark.parametrize("heads,kvh,kv_len", [(32, 8, 1), (32, 8, 7), (32, 8, 333), (32, 8, 4096), (32, 4, 1025),
-                                              (64, 8, 2000), (8, 8, 65), (6, 2, 100)])
+                                              (64, 8, 2000), (8, 8, 65), (6, 2, 100), (32, 2, 300), (16, 8, 20000), (24, 2, 17)])
 def test_attention_decode_hd128(ops, heads, kvh, kv_len):
     rng = np.random.default_rng(heads * 1000 + kv_len)
     q = rng.standard_normal(heads * 128).astype(np.float32)
@@ -205,7 +205,13 @@ def test_attention_decode_hd128(ops, heads, kvh, kv_len):
     scale = 1.0 / np.sqrt(128.0)
     ref = orc.attention_decode(q, k, v, heads, kvh, 128, kv_len, scale)
     got = ops.attention_decode_hd128(q, k, v, kv_len, heads, kvh, scale)
-    assert max_rel_err(got, ref) <= TOL
+    if kv_len <= 4096:
+        assert max_rel_err(got, ref) <= TOL
+    else:
+        # Over 20000 positions the f32 running sums of either side carry ~1e-8 of absolute noise,
+        # which is more than 1e-3 of the few outputs that lie 1000x below the vector's scale:
+        # bound the error against the vector's scale instead, ten times tighter.
+        assert max_err_vs_norm(got, ref) <= TOL / 10
     assert np.max(np.abs(got - ref)) < 1e-4        # the reference's own CUDA tests: max_diff < 1e-4
 
 

@@ -55,7 +55,8 @@ WORKER = textwrap.dedent("""
     # a rank that fails is seen by the others as an error, not a hang
     dist.barrier()
     dist.destroy_process_group()
-    print("rank", rank, "ok")
+    sys.stdout.write("rank %%d ok\\n" %% rank)
+    sys.stdout.flush()
 """)
 
 
