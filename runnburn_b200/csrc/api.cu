@@ -23,7 +23,7 @@ bool use_pdl() {
     static int v = -1;
     if (v < 0) {
         const char *e = getenv("RNB_B200_PDL");
-        v = (e && *e && strcmp(e, "0") != 0) ? 1 : 0;
+        v = (e && *e && strcmp(e, "0") == 0) ? 0 : 1;   // on unless RNB_B200_PDL=0
     }
     return v == 1;
 }

@@ -312,9 +312,15 @@ RNB_GLOBAL void __launch_bounds__(128)
 gemv_stream_kernel(const GemvJob *__restrict__ jobs, int n_jobs, const GsParams P, int *__restrict__ dev_error) {
     gemv_stream_body(jobs, n_jobs, P, dev_error);
 }
+// Static job tables travel as a kernel parameter (constant bank): no dependent global loads
+// before the first copy can be issued.  Tables written on the device (MoE) use the kernel above.
+constexpr int GS_PACK = 3;
+struct GemvJobPack {
+    GemvJob j[GS_PACK];
+};
 RNB_GLOBAL void __launch_bounds__(128)
-gemv_stream_kernel_1(const __grid_constant__ GemvJob job, const GsParams P, int *__restrict__ dev_error) {
-    gemv_stream_body(&job, 1, P, dev_error);
+gemv_stream_kernel_1(const __grid_constant__ GemvJobPack jobs, int n_jobs, const GsParams P, int *__restrict__ dev_error) {
+    gemv_stream_body(jobs.j, n_jobs, P, dev_error);
 }
 
 }  // namespace rnb

@@ -9,9 +9,15 @@
 
 namespace rnb {
 
-// Programmatic dependent launch is opt-in (RNB_B200_PDL=1): kernels then overlap their
-// weight prefetch with the tail of the previous kernel.
+// Programmatic dependent launch (off with RNB_B200_PDL=0): kernels overlap their weight
+// prefetch and set-up with the tail of the previous kernel.
 bool use_pdl();
+
+// Kernels launched by this library so far (callers take differences).
+inline uint64_t &launch_count() {
+    static uint64_t n = 0;
+    return n;
+}
 
 template <typename... KArgs, typename... Args>
 inline cudaError_t launch_k(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
@@ -28,7 +34,9 @@ inline cudaError_t launch_k(void (*kernel)(KArgs...), dim3 grid, dim3 block, siz
         cfg.attrs = attr;
         cfg.numAttrs = 1;
     }
-    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+    if (e == cudaSuccess) launch_count()++;
+    return e;
 }
 
 constexpr size_t GEMV_SMEM_LIMIT = 200 * 1024;
@@ -101,10 +109,14 @@ inline int launch_gemv_stream(cudaStream_t s, const GemvJob *jobs_host, const Ge
     size_t smem = (size_t)P.n_stages * P.slot_bytes;
     while (smem > gemv_smem_max() && P.n_stages > 1) smem = (size_t)(--P.n_stages) * P.slot_bytes;
     if (smem > gemv_smem_max()) return fail(RNB_B200_VALIDATION_FAILED, "matvec stage too large: %zu bytes", smem);
-    if (by_value)
-        RNB_CU(launch_k(gemv_stream_kernel_1, dim3(tiles), dim3(R * 8), smem, s, jobs_host[0], P, dev_error));
-    else
+    if ((by_value || !dynamic_table) && n_jobs <= GS_PACK) {
+        GemvJobPack pack;
+        memset(&pack, 0, sizeof(pack));
+        for (int i = 0; i < n_jobs; i++) pack.j[i] = jobs_host[i];
+        RNB_CU(launch_k(gemv_stream_kernel_1, dim3(tiles), dim3(R * 8), smem, s, pack, n_jobs, P, dev_error));
+    } else {
         RNB_CU(launch_k(gemv_stream_kernel, dim3(tiles), dim3(R * 8), smem, s, jobs_dev, n_jobs, P, dev_error));
+    }
     return RNB_B200_OK;
 }
 
