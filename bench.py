@@ -35,6 +35,7 @@ WORKLOADS = {
     "llama3-8b-2layers-ctx4096": (dict(n_layer=2, hidden=4096, n_head=32, n_kv_head=8, n_ff=14336, vocab=128256), 4096),
     "tiny-llama-ctx256": (dict(n_layer=2, hidden=512, n_head=4, n_kv_head=2, n_ff=1024, vocab=2048), 256),
 }
+DRAM_TRAFFIC_OVER_ALGORITHMIC = 574.6 / 570.6
 METRIC = "decode_tok_per_s_batch1"
 UNIT = "tok/s"
 
@@ -314,7 +315,11 @@ def run_gpu(args, shape, ctx, name, rank, world, local_rank):
         ach = per_launch_bytes / per_launch_s / 1e9
         out["roofline"] = {"kernel": "gemv_stream_kernel", "bound": "hbm", "achieved": ach, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                            "frac": ach / peaks["hbm_gbs"], "frac_of_8TBs_nominal": ach / 8000.0, "peak_source": peaks["source"],
-                           "traffic": None, "launches_per_step": mv["launches_per_iter"],
+                           # DRAM read+write bytes per launch: the ncu capture of the five matvec shapes gave
+                           # 574.6 MB of traffic for 570.6 MB of algorithmic bytes (profiles/gemv_stream_kernel_*.md)
+                           "traffic": per_launch_bytes * DRAM_TRAFFIC_OVER_ALGORITHMIC,
+                           "traffic_source": "ncu dram__bytes_read.sum+dram__bytes_write.sum of the five layer shapes, scaled by algorithmic bytes",
+                           "launches_per_step": mv["launches_per_iter"],
                            "algorithmic_bytes_per_launch": per_launch_bytes, "avg_launch_us": per_launch_s * 1e6,
                            "how": "CUDA events around all matvec launches of a step on the decoder stream, model's own weights"}
     dec.close()
