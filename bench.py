@@ -291,6 +291,8 @@ def run_gpu(args, shape, ctx, name, rank, world, local_rank):
     mv = dec.time_matvecs(iters=max(3, min(K, 16))) if shape.get("n_expert", 0) == 0 else None
     barrier()
     if rank != 0:
+        dec.close()
+        dist.destroy_process_group()
         return None
     peaks = load_peaks()
     alg = algorithmic_bytes_per_token(shape, ctx)
@@ -323,6 +325,8 @@ def run_gpu(args, shape, ctx, name, rank, world, local_rank):
                            "algorithmic_bytes_per_launch": per_launch_bytes, "avg_launch_us": per_launch_s * 1e6,
                            "how": "CUDA events around all matvec launches of a step on the decoder stream, model's own weights"}
     dec.close()
+    if dist is not None:
+        dist.destroy_process_group()
     return out
 
 

@@ -10,7 +10,9 @@
 namespace rnb {
 
 // Programmatic dependent launch (off with RNB_B200_PDL=0): kernels overlap their weight
-// prefetch and set-up with the tail of the previous kernel.
+// prefetch and set-up with the tail of the previous kernel.  EVERY kernel launched through
+// launch_k must execute pdl_wait() before it touches memory another kernel wrote: a kernel
+// that skips it neither waits for its predecessor nor orders its successor behind it.
 bool use_pdl();
 
 // Kernels launched by this library so far (callers take differences).

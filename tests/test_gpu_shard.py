@@ -1,0 +1,75 @@
+"""Row-sharded decode on two GPUs: q/k/v by head, KV cache by KV head, NCCL all-gather of the
+f32 slices inside the per-token graph.  Greedy ids must equal the oracle's (and therefore the
+single-GPU decoder's).  Needs two devices; skipped otherwise."""
+import os
+import subprocess
+import sys
+import textwrap
+from pathlib import Path
+
+import pytest
+
+pytestmark = pytest.mark.gpu
+ROOT = Path(__file__).resolve().parent.parent
+
+WORKER = textwrap.dedent("""
+    import os, sys
+    sys.path.insert(0, %r); sys.path.insert(0, %r)
+    import numpy as np, torch, torch.distributed as dist
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    os.environ["RNB_CUDA_DEVICE"] = os.environ["LOCAL_RANK"]
+    torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
+    dist.init_process_group("nccl", device_id=torch.device("cuda", int(os.environ["LOCAL_RANK"])))
+    import oracle as orc
+    import runnburn_b200 as r
+    from runnburn_b200 import ops
+    from runnburn_b200.decoder import nccl_unique_id
+    from synth import llama_description
+    ops.open()
+    desc = llama_description(seed=0, n_layer=2, hidden=512, n_head=4, n_kv_head=2, n_ff=1024, vocab=2048)
+    dec = r.Decoder(r.ModelConfig(max_ctx=64, world_size=world, rank=rank, **desc["cfg"]))
+    ids = [nccl_unique_id() if rank == 0 else None]
+    dist.broadcast_object_list(ids, src=0)
+    dec.attach_nccl(ids[0])
+    dec.load_description(desc)
+    ref = orc.Model(desc, 64)
+    rng = np.random.default_rng(0)
+    prompt = rng.integers(0, 2048, 8).tolist()
+    pos, tg, tc = 0, None, None
+    for t in prompt:
+        tg = dec.step(t, pos)
+        tc = orc.argmax_last(ref.decode(t, pos))
+        pos += 1
+    got, want = [], []
+    for _ in range(24):
+        got.append(tg); want.append(tc)
+        tg = dec.step(tg, pos)
+        tc = orc.argmax_last(ref.decode(tc, pos))
+        pos += 1
+    assert got == want, (rank, got, want)
+    # each rank holds its own KV heads only
+    k, v = dec.read_kv(0, pos)
+    kc, vc = ref.kv_cache(0, pos)
+    kv_l = desc["cfg"]["n_kv_head"] // world * 128
+    kc = kc.reshape(pos, -1)[:, rank * kv_l:(rank + 1) * kv_l]
+    assert np.mean(k.reshape(pos, -1) == kc) > 0.999
+    dec.close(); ref.close()
+    dist.barrier()
+    dist.destroy_process_group()
+    sys.stdout.write("rank %%d ok\\\\n" %% rank)
+    sys.stdout.flush()
+""")
+
+
+def test_two_gpu_row_sharded_greedy_ids(tmp_path):
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    script = tmp_path / "worker.py"
+    script.write_text(WORKER % (str(ROOT), str(ROOT / "tests")))
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1")
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+                        "--master-addr", "127.0.0.1", "--master-port", "29741", str(script)],
+                       capture_output=True, text=True, env=env, timeout=600)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-4000:]
+    assert "rank 0 ok" in r.stdout and "rank 1 ok" in r.stdout
