@@ -1,0 +1,173 @@
+// Batch-1 Q4_K matvec for row-rich matrices: two threads per row, one warp per CTA.
+//
+// Same arithmetic as gemv_stream.cuh (bit-exact with rnb-cpu's AVX2 order), different split of
+// a row: thread h of a pair owns bytes 16h..16h+15 of every 32-byte qs group, which are exactly
+// accumulator lanes 4h..4h+3, so the integer lane sums need no exchange between threads and a
+// block's scales are decoded twice instead of eight times - about half the instructions per
+// block of the eight-thread form.  A warp therefore covers 16 rows; it is the whole CTA and
+// owns a private ring of stages (K-chunks of 2 super-blocks of every row + the matching
+// slices of the Q8_K activation), so refills need a warp-level sync only and ~20 such warps
+// fit on an SM.  Worth it when the matrix has rows to spare (gate/up, expert stacks): with few
+// rows the eight-thread kernel has more warps to hide latency with.
+#pragma once
+#include "gemv.cuh"
+#include "gemv_stream.cuh"
+
+namespace rnb {
+
+constexpr int GP_ROWS = 16;
+constexpr int GP_MAX_STAGES = 8;
+constexpr int GP_MAX_CHUNK = 8;
+
+struct GpParams {
+    int cols;
+    int chunk;            // super-blocks per stage
+    int n_stages;
+    uint32_t row_stride;  // 16-byte multiple, = 32 or 96 mod 128: the 16-byte loads of a quarter-warp hit 8 bank groups
+    uint32_t act_off;     // activation slice inside a stage: qs | bsum16 | d
+    uint32_t slot_bytes;
+};
+
+struct Q4kPairAcc {
+    float a[4], m[2];
+};
+// One block for thread h: lane sums of lanes 4h..4h+3 and of mins lanes 2h, 2h+1, then the
+// block's FMAs.  High nibbles stay in place (x16), the low scale is pre-multiplied by 16, one
+// exact shift per lane replaces the nibble shifts.
+__device__ __forceinline__ void gp_q4k_block(const uint8_t *blk, const uint8_t *act, const int16_t *bs16, float yd, int h,
+                                             Q4kPairAcc &A) {
+    const uint4 hdr = *reinterpret_cast<const uint4 *>(blk);
+    const uint32_t sc03 = hdr.y & 0x3f3f3f3fu, mn03 = hdr.z & 0x3f3f3f3fu;
+    const uint32_t sc47 = (hdr.w & 0x0f0f0f0fu) | (((hdr.y >> 6) & 0x03030303u) << 4);
+    const uint32_t mn47 = ((hdr.w >> 4) & 0x0f0f0f0fu) | (((hdr.z >> 6) & 0x03030303u) << 4);
+    int s0 = 0, s1 = 0, s2 = 0, s3 = 0;
+#pragma unroll
+    for (int g = 0; g < 4; g++) {
+        const uint4 q = *reinterpret_cast<const uint4 *>(blk + 16 + 32 * g + 16 * h);
+        const uint4 alo = *reinterpret_cast<const uint4 *>(act + 64 * g + 16 * h);
+        const uint4 ahi = *reinterpret_cast<const uint4 *>(act + 64 * g + 32 + 16 * h);
+        const uint32_t scw = g < 2 ? sc03 : sc47;
+        const int sl = (int)((scw >> (16 * (g & 1))) & 0xffu) << 4, sh = (int)((scw >> (16 * (g & 1) + 8)) & 0xffu);
+        s0 += sl * __dp4a((int)(q.x & 0x0f0f0f0fu), (int)alo.x, 0) + sh * dp4a_us(q.x & 0xf0f0f0f0u, ahi.x, 0);
+        s1 += sl * __dp4a((int)(q.y & 0x0f0f0f0fu), (int)alo.y, 0) + sh * dp4a_us(q.y & 0xf0f0f0f0u, ahi.y, 0);
+        s2 += sl * __dp4a((int)(q.z & 0x0f0f0f0fu), (int)alo.z, 0) + sh * dp4a_us(q.z & 0xf0f0f0f0u, ahi.z, 0);
+        s3 += sl * __dp4a((int)(q.w & 0x0f0f0f0fu), (int)alo.w, 0) + sh * dp4a_us(q.w & 0xf0f0f0f0u, ahi.w, 0);
+    }
+    const uint4 bs = *reinterpret_cast<const uint4 *>(bs16 + 8 * h);
+    const uint32_t mnw = h ? mn47 : mn03;
+    const int b0 = (short)((short)(bs.x & 0xffff) + (short)(bs.x >> 16)), b1 = (short)((short)(bs.y & 0xffff) + (short)(bs.y >> 16));
+    const int b2 = (short)((short)(bs.z & 0xffff) + (short)(bs.z >> 16)), b3 = (short)((short)(bs.w & 0xffff) + (short)(bs.w >> 16));
+    const int mp0 = (int)(mnw & 0xffu) * b0 + (int)((mnw >> 8) & 0xffu) * b1;
+    const int mp1 = (int)((mnw >> 16) & 0xffu) * b2 + (int)(mnw >> 24) * b3;
+    const float d = __fmul_rn(yd, f16_bits_to_f32(hdr.x & 0xffffu));
+    const float dmin = __fmul_rn(-yd, f16_bits_to_f32(hdr.x >> 16));
+    A.a[0] = __fmaf_rn(d, (float)(s0 >> 4), A.a[0]);
+    A.a[1] = __fmaf_rn(d, (float)(s1 >> 4), A.a[1]);
+    A.a[2] = __fmaf_rn(d, (float)(s2 >> 4), A.a[2]);
+    A.a[3] = __fmaf_rn(d, (float)(s3 >> 4), A.a[3]);
+    A.m[0] = __fmaf_rn(dmin, (float)mp0, A.m[0]);
+    A.m[1] = __fmaf_rn(dmin, (float)mp1, A.m[1]);
+}
+
+__device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+// grid = tiles of 16 rows, 32 threads.  Operands must be 16-byte aligned (the host checks).
+RNB_GLOBAL void __launch_bounds__(32)
+gemv_pair_q4k_kernel(const __grid_constant__ GemvJobPack jobs, int n_jobs, const GpParams P, int *__restrict__ dev_error) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    __shared__ __align__(8) uint64_t full[GP_MAX_STAGES];
+    const int lane = threadIdx.x, r = lane >> 1, h = lane & 1;
+    const int tile = blockIdx.x;
+    int jsel = 0;
+    for (int i = 1; i < n_jobs; i++)
+        if (tile >= jobs.j[i].tile0) jsel = i;
+    const GemvJob &job = jobs.j[jsel];
+    const int row0 = (tile - job.tile0) * GP_ROWS, nrows = min(GP_ROWS, job.rows - row0);
+    const int cols = P.cols, nb = cols >> 8, CB = P.chunk, S = P.n_stages;
+    if (nrows <= 0 || job.n_parts != 1 || job.type != TYPE_Q4_K || nb < 1 || CB < 1 || CB > GP_MAX_CHUNK || S < 1 || S > GP_MAX_STAGES ||
+        blockDim.x != 32 || (P.row_stride & 15u) || (uint32_t)CB * Q4K_BYTES > P.row_stride || (P.act_off & 15u) ||
+        (uint32_t)GP_ROWS * P.row_stride > P.act_off || P.act_off + (uint32_t)CB * 288u + 32u > P.slot_bytes) {
+        if (lane == 0) atomicExch(dev_error, DEV_ERR_BAD_JOB);
+        return;
+    }
+    pdl_launch_dependents();
+    const uint32_t rb = (uint32_t)nb * Q4K_BYTES;
+    const int n_chunks = (nb + CB - 1) / CB;
+    const uint8_t *w = job.parts[0].w, *x = job.parts[0].x;
+    // every row's first thread fetches that row's chunk; lane 1 fetches the activation slice
+    auto issue_w = [&](int c, int slot_idx) {
+        if (h != 0) return;
+        uint64_t *bar = &full[slot_idx];
+        if (r < nrows) {
+            const uint32_t bytes = (uint32_t)min(CB, nb - c * CB) * Q4K_BYTES;
+            mbar_arrive_expect_tx(bar, bytes);
+            bulk_g2s(smem + (uint32_t)slot_idx * P.slot_bytes + (uint32_t)r * P.row_stride, w + (size_t)(row0 + r) * rb + (uint32_t)(c * CB) * Q4K_BYTES,
+                     bytes, bar);
+        } else {
+            mbar_arrive(bar);
+        }
+    };
+    auto issue_a = [&](int c, int slot_idx) {
+        if (lane != 1) return;
+        uint64_t *bar = &full[slot_idx];
+        const uint32_t nblk = (uint32_t)min(CB, nb - c * CB);
+        // the block scales are 4 bytes each: copy the 16-byte groups that contain this chunk's
+        const uint32_t d_first = (uint32_t)(c * CB) * 4u, d_lo = d_first & ~15u, d_bytes = ((d_first + nblk * 4u + 15u) & ~15u) - d_lo;
+        uint8_t *dst = smem + (uint32_t)slot_idx * P.slot_bytes + P.act_off;
+        mbar_arrive_expect_tx(bar, nblk * 288u + d_bytes);
+        bulk_g2s(dst, x + (uint32_t)(c * CB) * 256u, nblk * 256u, bar);
+        bulk_g2s(dst + CB * 256, x + cols + (uint32_t)(c * CB) * 32u, nblk * 32u, bar);
+        bulk_g2s(dst + CB * 288, x + cols + 32 * nb + d_lo, d_bytes, bar);
+    };
+    if (lane == 0) {
+        for (int s = 0; s < S; s++) mbar_init(&full[s], GP_ROWS + 1);
+        mbar_fence_init();
+    }
+    __syncwarp();
+    for (int i = 0; i < S && i < n_chunks; i++) issue_w(i, i);
+    pdl_wait();   // the weights do not depend on the previous kernel; the activation does
+    for (int i = 0; i < S && i < n_chunks; i++) issue_a(i, i);
+    const uint32_t row_off = (uint32_t)(r < nrows ? r : 0) * P.row_stride + 0u;   // dead rows read row 0 and do not store
+    Q4kPairAcc A = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f}};
+    int slot_idx = 0;
+    uint32_t parity = 0;
+    for (int c = 0; c < n_chunks; c++) {
+        const int nblk = min(CB, nb - c * CB);
+        uint8_t *slot = smem + (uint32_t)slot_idx * P.slot_bytes;
+        if (!mbar_wait_bounded(&full[slot_idx], parity)) {
+            for (int k = c + 1; k < n_chunks && k < c + S; k++) mbar_wait_bounded(&full[k % S], (uint32_t)((k / S) & 1));
+            if (lane == 0) atomicExch(dev_error, DEV_ERR_MBAR_TIMEOUT);
+            return;
+        }
+        const uint8_t *rowp = slot + row_off;
+        const uint8_t *act = slot + P.act_off;
+        const int16_t *bs16 = reinterpret_cast<const int16_t *>(slot + P.act_off + CB * 256);
+        const float *xd = reinterpret_cast<const float *>(slot + P.act_off + CB * 288) + (((uint32_t)(c * CB) * 4u & 15u) >> 2);
+#pragma unroll 2
+        for (int j = 0; j < nblk; j++) gp_q4k_block(rowp + j * Q4K_BYTES, act + j * 256, bs16 + j * 16, xd[j], h, A);
+        __syncwarp();   // stage consumed by every row
+        if (c + S < n_chunks) {
+            issue_w(c + S, slot_idx);
+            issue_a(c + S, slot_idx);
+        }
+        if (++slot_idx == S) slot_idx = 0, parity ^= 1u;
+    }
+    // lanes 4h+w: (l + l4) across the pair, then (v0 + v2) + (v1 + v3); mins lanes 2h, 2h+1: (a0 + a2) + (a1 + a3)
+    const float v0 = __fadd_rn(A.a[0], __shfl_xor_sync(0xffffffffu, A.a[0], 1));
+    const float v1 = __fadd_rn(A.a[1], __shfl_xor_sync(0xffffffffu, A.a[1], 1));
+    const float v2 = __fadd_rn(A.a[2], __shfl_xor_sync(0xffffffffu, A.a[2], 1));
+    const float v3 = __fadd_rn(A.a[3], __shfl_xor_sync(0xffffffffu, A.a[3], 1));
+    const float hs = __fadd_rn(__fadd_rn(v0, v2), __fadd_rn(v1, v3));
+    const float x0 = __fadd_rn(A.m[0], __shfl_xor_sync(0xffffffffu, A.m[0], 1));
+    const float x1 = __fadd_rn(A.m[1], __shfl_xor_sync(0xffffffffu, A.m[1], 1));
+    float dot = __fadd_rn(hs, __fadd_rn(x0, x1));
+    if (job.parts[0].scale) dot = __fmul_rn(dot, __ldg(job.parts[0].scale));
+    if (r < nrows && h == 0) {
+        const size_t o = (size_t)row0 + r;
+        job.y[o] = job.residual ? __fadd_rn(job.residual[o], dot) : dot;
+    }
+}
+
+}  // namespace rnb

@@ -3,6 +3,7 @@
 #include "attention.cuh"
 #include "gemv.cuh"
 #include "gemv_stream.cuh"
+#include "gemv_pair.cuh"
 #include "moe.cuh"
 #include "q8k.cuh"
 #include "state.hpp"
@@ -82,8 +83,8 @@ inline int gs_pick_rows(size_t total_rows, int sm_count) {
     return (total_rows + 7) / 8 >= (size_t)(8 * sm_count) ? 8 : 4;
 }
 
-inline int launch_gemv_stream(cudaStream_t s, const GemvJob *jobs_host, const GemvJob *jobs_dev, int n_jobs,
-                              size_t cols, int *dev_error, int dynamic_table, bool by_value) {
+inline int launch_gemv_stream_rows(cudaStream_t s, const GemvJob *jobs_host, const GemvJob *jobs_dev, int n_jobs,
+                                   size_t cols, int *dev_error, int dynamic_table, bool by_value) {
     const GemvTuning &tu = gemv_tuning();
     const int R = jobs_host[0].rows_per_tile;
     int tiles = 0, max_parts = 1;
@@ -119,6 +120,67 @@ inline int launch_gemv_stream(cudaStream_t s, const GemvJob *jobs_host, const Ge
     } else {
         RNB_CU(launch_k(gemv_stream_kernel, dim3(tiles), dim3(R * 8), smem, s, jobs_dev, n_jobs, P, dev_error));
     }
+    return RNB_B200_OK;
+}
+
+// Tuning of the two-threads-per-row kernel: RNB_B200_PAIR=0 turns it off, _MIN_ROWS / _CHUNK /
+// _STAGES override when it is used and its pipeline shape.
+struct PairTuning {
+    int enabled, min_rows, chunk, stages;
+};
+inline const PairTuning &pair_tuning() {
+    static const PairTuning t = [] {
+        auto env_int = [](const char *name, int dflt, int lo, int hi) {
+            const char *e = getenv(name);
+            if (!e || !*e) return dflt;
+            const int x = atoi(e);
+            return x < lo ? lo : (x > hi ? hi : x);
+        };
+        PairTuning v;
+        v.enabled = env_int("RNB_B200_PAIR", 1, 0, 1);
+        v.min_rows = env_int("RNB_B200_PAIR_MIN_ROWS", 16384, 0, 1 << 30);
+        v.chunk = env_int("RNB_B200_PAIR_CHUNK", 2, 1, GP_MAX_CHUNK);
+        v.stages = env_int("RNB_B200_PAIR_STAGES", 3, 1, GP_MAX_STAGES);
+        return v;
+    }();
+    return t;
+}
+// Row-rich, all-Q4_K, single-part, 16-byte aligned static tables go to the two-threads-per-row
+// kernel; everything else to the eight-threads-per-row kernel.
+inline int launch_gemv_stream(cudaStream_t s, const GemvJob *jobs_host, const GemvJob *jobs_dev, int n_jobs,
+                              size_t cols, int *dev_error, int dynamic_table, bool by_value) {
+    const PairTuning &pt = pair_tuning();
+    bool pair = pt.enabled && !dynamic_table && n_jobs <= GS_PACK && cols % 256 == 0;
+    size_t total_rows = 0;
+    for (int i = 0; i < n_jobs && pair; i++) {
+        const GemvJob &j = jobs_host[i];
+        pair = j.type == TYPE_Q4_K && j.n_parts == 1 && j.seq <= 1 && ((((uintptr_t)j.parts[0].w | (uintptr_t)j.parts[0].x) & 15u) == 0);
+        total_rows += (size_t)j.rows;
+    }
+    if (!pair || total_rows < (size_t)pt.min_rows)
+        return launch_gemv_stream_rows(s, jobs_host, jobs_dev, n_jobs, cols, dev_error, dynamic_table, by_value);
+    GemvJobPack pack;
+    memset(&pack, 0, sizeof(pack));
+    int tiles = 0;
+    for (int i = 0; i < n_jobs; i++) {
+        pack.j[i] = jobs_host[i];
+        pack.j[i].rows_per_tile = GP_ROWS;
+        pack.j[i].tile0 = tiles;
+        tiles += (jobs_host[i].rows + GP_ROWS - 1) / GP_ROWS;
+    }
+    const int nb = (int)(cols / 256);
+    GpParams P;
+    P.cols = (int)cols;
+    P.chunk = pt.chunk < nb ? pt.chunk : nb;
+    const int n_chunks = (nb + P.chunk - 1) / P.chunk;
+    P.n_stages = n_chunks < pt.stages ? n_chunks : pt.stages;
+    P.row_stride = (uint32_t)P.chunk * Q4K_BYTES;
+    while ((P.row_stride & 127u) != 32u && (P.row_stride & 127u) != 96u) P.row_stride += 16u;
+    P.act_off = ((uint32_t)GP_ROWS * P.row_stride + 127u) & ~127u;
+    P.slot_bytes = (P.act_off + (uint32_t)P.chunk * 288u + 32u + 127u) & ~127u;
+    const size_t smem = (size_t)P.n_stages * P.slot_bytes;
+    if (smem > gemv_smem_max()) return launch_gemv_stream_rows(s, jobs_host, jobs_dev, n_jobs, cols, dev_error, dynamic_table, by_value);
+    RNB_CU(launch_k(gemv_pair_q4k_kernel, dim3(tiles), dim3(32), smem, s, pack, n_jobs, P, dev_error));
     return RNB_B200_OK;
 }
 
