@@ -113,6 +113,17 @@ int rnb_b200_q4k_gemv_batch(const uint8_t *weights, size_t weights_len, size_t r
 int rnb_b200_q6k_gemv_batch(const uint8_t *weights, size_t weights_len, size_t rows, size_t cols,
                             const float *input, size_t input_len, float *output,
                             size_t output_len);
+/* q4k_f16_gemm_batch — api/quant_api.rs:2364 (runtime/gemv.rs:2335-2421: dequant -> f16 +
+ * cublasGemmEx with f32 accumulation).  Here: weights dequantised tile-wise to bf16 inside a
+ * tcgen05 kernel, tokens rounded to bf16, f32 accumulators in tensor memory.  Same argument
+ * meaning and [seq][rows] output as the batch matvecs; a Q6_K twin for attn_v / ffn_down /
+ * output weights. */
+int rnb_b200_q4k_bf16_gemm_batch(const uint8_t *weights, size_t weights_len, size_t rows, size_t cols,
+                                 const float *input, size_t input_len, float *output,
+                                 size_t output_len);
+int rnb_b200_q6k_bf16_gemm_batch(const uint8_t *weights, size_t weights_len, size_t rows, size_t cols,
+                                 const float *input, size_t input_len, float *output,
+                                 size_t output_len);
 
 /* ---- attention ---------------------------------------------------------------------------- */
 /* attention_decode_hd128 — api/attention_api.rs:1943-1978.  q f32[heads*128]; k, v f16 bits
@@ -277,6 +288,11 @@ size_t rnb_b200_dev_q8k_bytes(size_t cols);
 int rnb_b200_dev_gemv(uint32_t type, const uint8_t *w_dev, size_t rows, size_t cols,
                       const void *x_dev /* Q8K-dev layout, or f32 for Q8_0 */, float *y_dev,
                       int rows_per_tile /* 0 = auto */, void *stream);
+/* Tensor-core prefill matmul on device-resident operands: x_dev f32 [seq][cols], xb_dev scratch
+ * of seq*cols bf16, y_dev f32 [seq][rows]; type = GGML type id (12 Q4_K, 14 Q6_K). */
+int rnb_b200_dev_prefill_gemm(int type, const uint8_t *w_dev, size_t rows, size_t cols,
+                              const float *x_dev, size_t seq, uint16_t *xb_dev, float *y_dev,
+                              void *stream);
 int rnb_b200_dev_flash_decode(const float *q_dev, const uint16_t *k_dev, const uint16_t *v_dev,
                               size_t kv_len, size_t num_heads, size_t num_kv_heads, float scale,
                               float *partials_dev, size_t partials_bytes, int n_chunks,

@@ -88,6 +88,8 @@ def load() -> C.CDLL:
         "rnb_b200_q6k_gemv_argmax": [vp, sz, sz, sz, vp, sz, vp, vp],
         "rnb_b200_q4k_gemv_batch": [vp, sz, sz, sz, vp, sz, vp, sz],
         "rnb_b200_q6k_gemv_batch": [vp, sz, sz, sz, vp, sz, vp, sz],
+        "rnb_b200_q4k_bf16_gemm_batch": [vp, sz, sz, sz, vp, sz, vp, sz],
+        "rnb_b200_q6k_bf16_gemm_batch": [vp, sz, sz, sz, vp, sz, vp, sz],
         "rnb_b200_attention_decode_hd128": [vp, sz, vp, vp, sz, sz, sz, sz, f32, vp, sz],
         "rnb_b200_attention_decode_cached": [sz, vp, sz, vp, vp, sz, sz, sz, sz, sz, f32, vp, sz],
         "rnb_b200_clear_decode_attention_kv_cache": [],
@@ -121,6 +123,7 @@ def load() -> C.CDLL:
         "rnb_b200_decoder_attach_nccl": [vp, vp],
         "rnb_b200_dev_quantize_q8k": [vp, sz, sz, vp, vp, vp],
         "rnb_b200_dev_gemv": [u32, vp, sz, sz, vp, vp, i32, vp],
+        "rnb_b200_dev_prefill_gemm": [i32, vp, sz, sz, vp, sz, vp, vp, vp],
         "rnb_b200_dev_flash_decode": [vp, vp, vp, sz, sz, sz, f32, vp, sz, i32, vp, vp],
         "rnb_b200_flash_decode_default_chunks": [sz, sz],
         "rnb_b200_attention_decode_hd128_noalloc": [vp, vp, vp, sz, sz, sz, f32, vp, vp],

@@ -341,6 +341,37 @@ static int prefill_gemm_host(int type, const uint8_t *w, size_t wl, size_t rows,
     return gemv_host(type, w, wl, rows, cols, in, seq * cols, 0, seq, out, ol, nullptr, nullptr);
 }
 
+int prefill_gemm_setup() {
+    static bool done = false;
+    if (done) return RNB_B200_OK;
+    RNB_CU(cudaFuncSetAttribute(prefill_gemm_kernel<TYPE_Q4_K>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PG_SMEM));
+    RNB_CU(cudaFuncSetAttribute(prefill_gemm_kernel<TYPE_Q6_K>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PG_SMEM));
+    done = true;
+    return RNB_B200_OK;
+}
+
+// Tensor-core prefill matmul from host buffers: bf16 x bf16 -> f32, weights dequantised in the
+// kernel (the reference's q4k_f16_gemm_batch dequantises to f16 and calls cuBLAS).
+static int prefill_tc_host(int type, const uint8_t *w, size_t wl, size_t rows, size_t cols, const float *in, size_t il, float *out, size_t ol) {
+    if (cols == 0 || il == 0 || il % cols != 0) return fail(RNB_B200_VALIDATION_FAILED, "%s batch input length %zu is not a multiple of cols %zu", type_name(type), il, cols);
+    const size_t seq = il / cols;
+    RNB_TRY(validate_gemv(type, wl, rows, cols, il, seq, ol, true));
+    if (!w || !in || !out) return fail(RNB_B200_VALIDATION_FAILED, "null pointer argument");
+    Locked L;
+    State &st = L.st;
+    RNB_TRY(st.open());
+    RNB_CU(cudaSetDevice(st.device));
+    const uint8_t *w_dev = nullptr;
+    RNB_TRY(st.resident_ptr(w, wl, false, &w_dev));
+    RNB_TRY(st.in_f32.ensure(il * sizeof(float)));
+    RNB_TRY(st.h2d(st.in_f32.p, in, il * sizeof(float), st.pin_in));
+    RNB_TRY(st.xb.ensure(il * 2));
+    RNB_TRY(st.out_f32.ensure(rows * seq * sizeof(float) + 16));
+    RNB_TRY(launch_prefill_gemm(st.stream, type, w_dev, rows, cols, st.in_f32.as<float>(), seq, st.xb.as<uint16_t>(), st.out_f32.as<float>(), st.dev_error));
+    RNB_TRY(finish_to_host(st, st.out_f32.p, out, rows * seq * sizeof(float)));
+    return st.check_dev_error();
+}
+
 }  // namespace rnb
 
 using namespace rnb;
@@ -512,6 +543,19 @@ int rnb_b200_q4k_gemv_batch(const uint8_t *w, size_t wl, size_t rows, size_t col
 int rnb_b200_q6k_gemv_batch(const uint8_t *w, size_t wl, size_t rows, size_t cols, const float *in, size_t il, float *out, size_t ol) {
     if (cols == 0 || il % cols != 0) return fail(RNB_B200_VALIDATION_FAILED, "Q6_K batch input length %zu is not a multiple of cols %zu", il, cols);
     return prefill_gemm_host(TYPE_Q6_K, w, wl, rows, cols, in, il / cols, out, ol);
+}
+int rnb_b200_q4k_bf16_gemm_batch(const uint8_t *w, size_t wl, size_t rows, size_t cols, const float *in, size_t il, float *out, size_t ol) {
+    return prefill_tc_host(TYPE_Q4_K, w, wl, rows, cols, in, il, out, ol);
+}
+int rnb_b200_q6k_bf16_gemm_batch(const uint8_t *w, size_t wl, size_t rows, size_t cols, const float *in, size_t il, float *out, size_t ol) {
+    return prefill_tc_host(TYPE_Q6_K, w, wl, rows, cols, in, il, out, ol);
+}
+int rnb_b200_dev_prefill_gemm(int type, const uint8_t *w_dev, size_t rows, size_t cols, const float *x_dev, size_t seq, uint16_t *xb_dev,
+                              float *y_dev, void *stream) {
+    if (!w_dev || !x_dev || !xb_dev || !y_dev) return fail(RNB_B200_VALIDATION_FAILED, "null pointer argument");
+    Locked L;
+    RNB_TRY(L.st.open());
+    return launch_prefill_gemm((cudaStream_t)stream, type, w_dev, rows, cols, x_dev, seq, xb_dev, y_dev, L.st.dev_error);
 }
 
 // ---- attention --------------------------------------------------------------------------------

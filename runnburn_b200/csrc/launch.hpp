@@ -5,6 +5,7 @@
 #include "gemv_stream.cuh"
 #include "gemv_pair.cuh"
 #include "moe.cuh"
+#include "prefill_gemm.cuh"
 #include "q8k.cuh"
 #include "state.hpp"
 
@@ -310,6 +311,29 @@ inline int launch_flash_decode(cudaStream_t s, const float *q, const uint16_t *k
                                          n_chunks, dev_error));
     RNB_CU(launch_k(flash_decode_reduce_kernel, dim3(num_heads), dim3(HD), 0, s,
                     (const float *)partials, n_chunks, out));
+    return RNB_B200_OK;
+}
+
+// Tensor-core prefill matmul: converts the f32 token rows to bf16 (scratch `xb`, seq*cols
+// elements) and runs the tcgen05 kernel.  y is [seq][rows] f32.
+int prefill_gemm_setup();   // raises the kernels' dynamic shared-memory limit once
+inline int launch_prefill_gemm(cudaStream_t s, int type, const uint8_t *w, size_t rows, size_t cols, const float *x, size_t seq,
+                               uint16_t *xb, float *y, int *dev_error) {
+    if (type != TYPE_Q4_K && type != TYPE_Q6_K) return fail(RNB_B200_UNSUPPORTED, "tensor-core prefill matmul supports Q4_K and Q6_K weights");
+    if (cols == 0 || cols % 256 != 0) return fail(RNB_B200_VALIDATION_FAILED, "cols(%zu) must be a non-zero multiple of 256", cols);
+    if (rows == 0 || seq == 0) return fail(RNB_B200_VALIDATION_FAILED, "prefill matmul needs rows and tokens");
+    if (((uintptr_t)w & 1u) || ((uintptr_t)x & 15u) || ((uintptr_t)xb & 15u) || ((uintptr_t)y & 15u) || (type == TYPE_Q4_K && ((uintptr_t)w & 15u)))
+        return fail(RNB_B200_VALIDATION_FAILED, "prefill matmul operands are not aligned");
+    RNB_TRY(prefill_gemm_setup());
+    const size_t n = seq * cols;
+    RNB_CU(launch_k(f32_to_bf16_kernel, dim3((unsigned)((n / 8 + 255) / 256)), dim3(256), 0, s, x, xb, n));
+    const dim3 grid((unsigned)((rows + PG_TILE_N - 1) / PG_TILE_N), (unsigned)((seq + PG_TILE_M - 1) / PG_TILE_M));
+    if (type == TYPE_Q4_K)
+        RNB_CU(launch_k(prefill_gemm_kernel<TYPE_Q4_K>, grid, dim3(PG_THREADS), PG_SMEM, s, w, (const uint16_t *)xb, y, (int)seq, (int)rows, (int)cols,
+                        dev_error));
+    else
+        RNB_CU(launch_k(prefill_gemm_kernel<TYPE_Q6_K>, grid, dim3(PG_THREADS), PG_SMEM, s, w, (const uint16_t *)xb, y, (int)seq, (int)rows, (int)cols,
+                        dev_error));
     return RNB_B200_OK;
 }
 

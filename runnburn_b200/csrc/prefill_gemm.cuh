@@ -1,0 +1,350 @@
+// Prefill matmul on the 5th-generation tensor cores: Y[t][row] = sum_k W[row][k] * X[t][k] for a
+// batch of tokens, W in GGUF Q4_K / Q6_K blocks, dequantised tile-wise to bf16 in shared
+// memory and multiplied with tcgen05.mma (bf16 x bf16 -> fp32 accumulators in tensor memory).
+// Replaces the reference's dequant -> f16 + cublasGemmEx path (q4k_f16_gemm_batch,
+// crates/rnb-backend/cuda/src/runtime/gemv.rs:2335-2421); the dequantisation follows
+// crates/rnb-cpu/src/quantize/dequant.rs:353-381 (Q4_K) and :780-807 (Q6_K) in f32 and rounds
+// once to bf16.
+//
+// One CTA owns a 256-token x 256-row output tile: two 128 x 256 fp32 accumulators = all 512
+// columns of the SM's tensor memory.  K advances 64 elements (one Q4_K group, a quarter of a
+// super-block) per pipeline stage; a stage holds the token tile (256 x 64 bf16) and the weight
+// tile (256 x 64 bf16), both K-major in the 128-byte swizzle the MMA descriptors expect:
+//   byte offset of (row r, 16-byte chunk c) = (r / 8) * 1024 + (r % 8) * 128 + ((c ^ (r % 8)) * 16).
+// Warp roles: 0-3 dequantise weights (one thread = two rows), 4-7 bring the token tile in with
+// cp.async, 8 allocates tensor memory and issues the MMAs (eight per stage: 2 token halves x 4
+// K-steps of 16); afterwards warps 0-7 read the accumulators back (tcgen05.ld, one TMEM lane
+// quarter per warp) and store f32 rows.  Every wait is bounded; a timeout sets the error flag
+// and all roles still meet at the final barrier, where the tensor memory is freed.
+#pragma once
+#include <cuda_bf16.h>
+
+#include <type_traits>
+
+#include "common.cuh"
+
+namespace rnb {
+
+constexpr int PG_TILE_M = 256;   // tokens per CTA
+constexpr int PG_TILE_N = 256;   // weight rows per CTA
+constexpr int PG_K = 64;         // elements per stage
+constexpr int PG_STAGES = 3;
+constexpr int PG_THREADS = 288;
+constexpr uint32_t PG_TILE_BYTES = 256 * 128;                      // one operand tile of a stage
+constexpr uint32_t PG_STAGE_BYTES = 2 * PG_TILE_BYTES;
+constexpr size_t PG_SMEM = (size_t)PG_STAGES * PG_STAGE_BYTES + 1024;   // + slack to align to 1024
+constexpr int DEV_ERR_GEMM_TIMEOUT = 3;
+
+__device__ __forceinline__ uint32_t pg_swz(int r, int c) { return (uint32_t)((r >> 3) * 1024 + (r & 7) * 128 + ((c ^ (r & 7)) << 4)); }
+
+// K-major, 128-byte swizzle, 8-row groups 1024 bytes apart; descriptor version 1 (sm_100)
+__device__ __forceinline__ uint64_t pg_smem_desc(uint32_t saddr) {
+    return (uint64_t)((saddr & 0x3ffffu) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+// D = f32, A = B = bf16, both K-major, N = 256, M = 128
+constexpr uint32_t PG_IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(PG_TILE_N >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+
+__device__ __forceinline__ void pg_mma(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(da), "l"(db), "r"(PG_IDESC), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void pg_commit(uint64_t *bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void pg_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void pg_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void pg_proxy_fence() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void pg_arrive(uint64_t *bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void pg_tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,"
+        "%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]),
+          "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]),
+          "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]),
+          "=r"(v[31])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+// q in 0..255 -> exact f32 without an int-to-float conversion: 2^23 + q, minus 2^23
+__device__ __forceinline__ float pg_byte_to_f32(uint32_t word, int byte) {
+    return __uint_as_float(__byte_perm(word, 0x4b000000u, 0x7650 + byte) ) - 8388608.0f;
+}
+__device__ __forceinline__ uint32_t pg_pack_bf16(float lo, float hi) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t *>(&v);
+}
+
+// ---- weight group (64 elements of one row) -> 8 chunks of 8 bf16 ------------------------------
+struct PgRawQ4 {
+    uint4 hdr;     // d, dmin, 12 scale bytes
+    uint4 q0, q1;  // 32 qs bytes of the group
+};
+__device__ __forceinline__ void pg_load_q4(PgRawQ4 &r, const uint8_t *blk, int g) {
+    r.hdr = ldg_nc_u4(blk);
+    r.q0 = ldg_nc_u4(blk + 16 + 32 * g);
+    r.q1 = ldg_nc_u4(blk + 32 + 32 * g);
+}
+// y = d*sc*q - dmin*m as (d*sc)*q - (dmin*m): crates/rnb-cpu/src/quantize/dequant.rs:353-381
+__device__ __forceinline__ void pg_dequant_q4(const PgRawQ4 &r, int g, uint8_t *row_base, int rr) {
+    const float d = f16_bits_to_f32(r.hdr.x & 0xffffu), dmin = f16_bits_to_f32(r.hdr.x >> 16);
+    const uint32_t sc03 = r.hdr.y & 0x3f3f3f3fu, mn03 = r.hdr.z & 0x3f3f3f3fu;
+    const uint32_t sc47 = (r.hdr.w & 0x0f0f0f0fu) | (((r.hdr.y >> 6) & 0x03030303u) << 4);
+    const uint32_t mn47 = ((r.hdr.w >> 4) & 0x0f0f0f0fu) | (((r.hdr.z >> 6) & 0x03030303u) << 4);
+    const uint32_t scw = g < 2 ? sc03 : sc47, mnw = g < 2 ? mn03 : mn47;
+    const int sh = 16 * (g & 1);
+    const float d_lo = __fmul_rn(d, (float)((scw >> sh) & 0xffu)), d_hi = __fmul_rn(d, (float)((scw >> (sh + 8)) & 0xffu));
+    const float m_lo = __fmul_rn(dmin, (float)((mnw >> sh) & 0xffu)), m_hi = __fmul_rn(dmin, (float)((mnw >> (sh + 8)) & 0xffu));
+    const uint32_t qw[8] = {r.q0.x, r.q0.y, r.q0.z, r.q0.w, r.q1.x, r.q1.y, r.q1.z, r.q1.w};
+#pragma unroll
+    for (int c = 0; c < 4; c++) {   // chunk c: low nibbles of bytes 8c..8c+7; chunk c+4: their high nibbles
+        uint32_t lo[4], hi[4];
+#pragma unroll
+        for (int w = 0; w < 2; w++) {
+            const uint32_t word = qw[2 * c + w], l4 = word & 0x0f0f0f0fu, h4 = (word >> 4) & 0x0f0f0f0fu;
+            lo[2 * w] = pg_pack_bf16(__fsub_rn(__fmul_rn(d_lo, pg_byte_to_f32(l4, 0)), m_lo), __fsub_rn(__fmul_rn(d_lo, pg_byte_to_f32(l4, 1)), m_lo));
+            lo[2 * w + 1] = pg_pack_bf16(__fsub_rn(__fmul_rn(d_lo, pg_byte_to_f32(l4, 2)), m_lo), __fsub_rn(__fmul_rn(d_lo, pg_byte_to_f32(l4, 3)), m_lo));
+            hi[2 * w] = pg_pack_bf16(__fsub_rn(__fmul_rn(d_hi, pg_byte_to_f32(h4, 0)), m_hi), __fsub_rn(__fmul_rn(d_hi, pg_byte_to_f32(h4, 1)), m_hi));
+            hi[2 * w + 1] = pg_pack_bf16(__fsub_rn(__fmul_rn(d_hi, pg_byte_to_f32(h4, 2)), m_hi), __fsub_rn(__fmul_rn(d_hi, pg_byte_to_f32(h4, 3)), m_hi));
+        }
+        *reinterpret_cast<uint4 *>(row_base + ((c ^ rr) << 4)) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+        *reinterpret_cast<uint4 *>(row_base + (((c + 4) ^ rr) << 4)) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+    }
+}
+
+// Q6_K: group g of a block = elements 64g..64g+63 = for half n = g/2 the pair (q1,q2) if g even,
+// (q3,q4) if g odd, l = 0..31 each; y = (d*sc)*(q-32): dequant.rs:780-807.  Blocks are 210 bytes,
+// so rows are only 2-byte aligned: bytes are fetched as aligned words and funnel-shifted.
+__device__ __forceinline__ uint32_t pg_ldg_u32_unaligned(const uint8_t *p) {
+    const uintptr_t a = reinterpret_cast<uintptr_t>(p);
+    const uint32_t *w = reinterpret_cast<const uint32_t *>(a & ~(uintptr_t)3);
+    const uint32_t sh = (uint32_t)(a & 3) * 8;
+    const uint32_t w0 = __ldg(w);
+    if (sh == 0) return w0;
+    return __funnelshift_r(w0, __ldg(w + 1), sh);
+}
+struct PgRawQ6 {
+    uint32_t ql_a[8], ql_b[8], qh[8];   // ql[64n + 0..31], ql[64n + 32..63], qh[32n + 0..31]
+    uint32_t sc;                         // the four scales this group uses, as bytes
+    float d;
+};
+__device__ __forceinline__ void pg_load_q6(PgRawQ6 &r, const uint8_t *blk, int g) {
+    const int n = g >> 1;
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        r.ql_a[i] = pg_ldg_u32_unaligned(blk + 64 * n + 4 * i);
+        r.ql_b[i] = pg_ldg_u32_unaligned(blk + 64 * n + 32 + 4 * i);
+        r.qh[i] = pg_ldg_u32_unaligned(blk + 128 + 32 * n + 4 * i);
+    }
+    // scales of (first 32, second 32) elements of the group: is = 8n + 4(g&1) + {0,1} and + 2
+    const uint8_t *s = blk + 192 + 8 * n + 4 * (g & 1);
+    r.sc = (uint32_t)s[0] | ((uint32_t)s[1] << 8) | ((uint32_t)s[2] << 16) | ((uint32_t)s[3] << 24);
+    r.d = f16_bits_to_f32(*reinterpret_cast<const uint16_t *>(blk + 208));
+}
+__device__ __forceinline__ void pg_dequant_q6(const PgRawQ6 &r, int g, uint8_t *row_base, int rr) {
+    const bool odd = g & 1;
+    // element e = 0..31 of the group: first kind (q1 or q3), scale byte e/16; e = 32..63: second kind, scale byte 2 + (e-32)/16
+    float ds[4];
+#pragma unroll
+    for (int i = 0; i < 4; i++) ds[i] = __fmul_rn(r.d, (float)(int)(int8_t)((r.sc >> (8 * i)) & 0xffu));
+#pragma unroll
+    for (int c = 0; c < 4; c++) {   // chunk c: elements 8c..8c+7 (first kind); chunk c+4: elements 32+8c.. (second kind)
+        uint32_t o1[4], o2[4];
+#pragma unroll
+        for (int w = 0; w < 2; w++) {
+            const int i = 2 * c + w;
+            const uint32_t la = r.ql_a[i], lb = r.ql_b[i], hh = r.qh[i];
+            const uint32_t qa = odd ? (((la >> 4) & 0x0f0f0f0fu) | (hh & 0x30303030u)) : ((la & 0x0f0f0f0fu) | ((hh << 4) & 0x30303030u));
+            const uint32_t qb = odd ? (((lb >> 4) & 0x0f0f0f0fu) | ((hh >> 2) & 0x30303030u)) : ((lb & 0x0f0f0f0fu) | ((hh << 2) & 0x30303030u));
+            const float sa = ds[c >> 1], sb = ds[2 + (c >> 1)];
+            o1[2 * w] = pg_pack_bf16(__fmul_rn(sa, pg_byte_to_f32(qa, 0) - 32.0f), __fmul_rn(sa, pg_byte_to_f32(qa, 1) - 32.0f));
+            o1[2 * w + 1] = pg_pack_bf16(__fmul_rn(sa, pg_byte_to_f32(qa, 2) - 32.0f), __fmul_rn(sa, pg_byte_to_f32(qa, 3) - 32.0f));
+            o2[2 * w] = pg_pack_bf16(__fmul_rn(sb, pg_byte_to_f32(qb, 0) - 32.0f), __fmul_rn(sb, pg_byte_to_f32(qb, 1) - 32.0f));
+            o2[2 * w + 1] = pg_pack_bf16(__fmul_rn(sb, pg_byte_to_f32(qb, 2) - 32.0f), __fmul_rn(sb, pg_byte_to_f32(qb, 3) - 32.0f));
+        }
+        *reinterpret_cast<uint4 *>(row_base + ((c ^ rr) << 4)) = make_uint4(o1[0], o1[1], o1[2], o1[3]);
+        *reinterpret_cast<uint4 *>(row_base + (((c + 4) ^ rr) << 4)) = make_uint4(o2[0], o2[1], o2[2], o2[3]);
+    }
+}
+
+// f32 -> bf16 rows (activation), padded to a multiple of 8 columns by construction (cols % 256 == 0)
+RNB_GLOBAL void __launch_bounds__(256)
+f32_to_bf16_kernel(const float *__restrict__ x, uint16_t *__restrict__ y, size_t n) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 8;
+    if (i >= n) return;
+    const float4 a = *reinterpret_cast<const float4 *>(x + i), b = *reinterpret_cast<const float4 *>(x + i + 4);
+    *reinterpret_cast<uint4 *>(y + i) = make_uint4(pg_pack_bf16(a.x, a.y), pg_pack_bf16(a.z, a.w), pg_pack_bf16(b.x, b.y), pg_pack_bf16(b.z, b.w));
+}
+
+// grid = (ceil(rows / 256), ceil(seq / 256)); 288 threads; dynamic shared memory PG_SMEM.
+template <int TYPE>
+RNB_GLOBAL void __launch_bounds__(PG_THREADS, 1)
+prefill_gemm_kernel(const uint8_t *__restrict__ w, const uint16_t *__restrict__ xb, float *__restrict__ y, int seq, int rows, int cols,
+                    int *__restrict__ err_flag) {
+    constexpr uint32_t BLK = TYPE == TYPE_Q4_K ? Q4K_BYTES : Q6K_BYTES;
+    extern __shared__ __align__(1024) uint8_t pg_smem_raw[];
+    __shared__ __align__(8) uint64_t full[PG_STAGES], empty[PG_STAGES], done_bar;
+    __shared__ uint32_t tmem_base_slot;
+    __shared__ int s_failed;
+    pdl_launch_dependents();
+    pdl_wait();
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(pg_smem_raw) + 1023) & ~(uintptr_t)1023);
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int n0 = blockIdx.x * PG_TILE_N, m0 = blockIdx.y * PG_TILE_M;
+    const int nb = cols >> 8, KT = cols / PG_K;
+    if (tid == 0) {
+        for (int s = 0; s < PG_STAGES; s++) {
+            mbar_init(&full[s], 8);    // one arrival per producer warp
+            mbar_init(&empty[s], 1);   // tcgen05.commit
+        }
+        mbar_init(&done_bar, 1);
+        mbar_fence_init();
+        s_failed = 0;
+    }
+    if (warp == 8) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)), "r"(512) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    pg_fence_before();
+    __syncthreads();
+    pg_fence_after();
+    const uint32_t tmem_base = tmem_base_slot;
+    bool ok = true;
+
+    if (warp < 4) {
+        // ---- weight producers: thread t dequantises rows t and t + 128 of the tile ----
+        const size_t rb = (size_t)nb * BLK;
+        const int ra = min(n0 + tid, rows - 1), rbw = min(n0 + tid + 128, rows - 1);   // rows past the end repeat the last one (never stored)
+        const uint8_t *wa = w + (size_t)ra * rb, *wb = w + (size_t)rbw * rb;
+        typename std::conditional<TYPE == TYPE_Q4_K, PgRawQ4, PgRawQ6>::type cur_a, cur_b, nxt_a, nxt_b;
+        auto load = [&](decltype(cur_a) &a, decltype(cur_b) &b, int kt) {
+            const int blk = kt >> 2, g = kt & 3;
+            if constexpr (TYPE == TYPE_Q4_K) {
+                pg_load_q4(a, wa + (size_t)blk * BLK, g);
+                pg_load_q4(b, wb + (size_t)blk * BLK, g);
+            } else {
+                pg_load_q6(a, wa + (size_t)blk * BLK, g);
+                pg_load_q6(b, wb + (size_t)blk * BLK, g);
+            }
+        };
+        load(cur_a, cur_b, 0);
+        for (int kt = 0; kt < KT && ok; kt++) {
+            const int s = kt % PG_STAGES;
+            if (kt + 1 < KT) load(nxt_a, nxt_b, kt + 1);
+            ok = mbar_wait_bounded(&empty[s], (uint32_t)(((kt / PG_STAGES) & 1) ^ 1));
+            if (!ok) break;
+            uint8_t *bt = smem + (uint32_t)s * PG_STAGE_BYTES + PG_TILE_BYTES;
+            const int r1 = tid, r2 = tid + 128, g = kt & 3;
+            if constexpr (TYPE == TYPE_Q4_K) {
+                pg_dequant_q4(cur_a, g, bt + (r1 >> 3) * 1024 + (r1 & 7) * 128, r1 & 7);
+                pg_dequant_q4(cur_b, g, bt + (r2 >> 3) * 1024 + (r2 & 7) * 128, r2 & 7);
+            } else {
+                pg_dequant_q6(cur_a, g, bt + (r1 >> 3) * 1024 + (r1 & 7) * 128, r1 & 7);
+                pg_dequant_q6(cur_b, g, bt + (r2 >> 3) * 1024 + (r2 & 7) * 128, r2 & 7);
+            }
+            pg_proxy_fence();
+            __syncwarp();
+            if (lane == 0) pg_arrive(&full[s]);
+            cur_a = nxt_a;
+            cur_b = nxt_b;
+        }
+    } else if (warp < 8) {
+        // ---- token producers: cp.async the 256 x 64 bf16 tile, one stage ahead ----
+        const int t = tid - 128;
+        auto issue = [&](int kt) {
+            const int s = kt % PG_STAGES;
+            uint8_t *at = smem + (uint32_t)s * PG_STAGE_BYTES;
+#pragma unroll
+            for (int i = 0; i < 16; i++) {
+                const int idx = i * 128 + t, r = idx >> 3, c = idx & 7;
+                const int tok = m0 + r;
+                const uint16_t *src = xb + (size_t)min(tok, seq - 1) * cols + (size_t)kt * PG_K + c * 8;
+                const uint32_t nbytes = tok < seq ? 16u : 0u;   // rows past the end are zero-filled
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(at) + pg_swz(r, c)), "l"(src), "r"(nbytes) : "memory");
+            }
+            asm volatile("cp.async.commit_group;" ::: "memory");
+        };
+        ok = mbar_wait_bounded(&empty[0], 1u);
+        if (ok) issue(0);
+        for (int kt = 0; kt < KT && ok; kt++) {
+            if (kt + 1 < KT) {
+                ok = mbar_wait_bounded(&empty[(kt + 1) % PG_STAGES], (uint32_t)((((kt + 1) / PG_STAGES) & 1) ^ 1));
+                if (!ok) break;
+                issue(kt + 1);
+                asm volatile("cp.async.wait_group 1;" ::: "memory");
+            } else {
+                asm volatile("cp.async.wait_group 0;" ::: "memory");
+            }
+            pg_proxy_fence();
+            __syncwarp();
+            if (lane == 0) pg_arrive(&full[kt % PG_STAGES]);
+        }
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+    } else {
+        // ---- MMA issuer ----
+        for (int kt = 0; kt < KT && ok; kt++) {
+            const int s = kt % PG_STAGES;
+            ok = mbar_wait_bounded(&full[s], (uint32_t)((kt / PG_STAGES) & 1));
+            if (!ok) break;
+            pg_fence_after();
+            if (lane == 0) {
+                const uint32_t a_addr = smem_u32(smem + (uint32_t)s * PG_STAGE_BYTES), b_addr = a_addr + PG_TILE_BYTES;
+#pragma unroll
+                for (int mh = 0; mh < 2; mh++)
+#pragma unroll
+                    for (int k = 0; k < 4; k++)
+                        pg_mma(tmem_base + (uint32_t)mh * 256u, pg_smem_desc(a_addr + (uint32_t)mh * 128u * 128u + (uint32_t)k * 32u),
+                               pg_smem_desc(b_addr + (uint32_t)k * 32u), (kt > 0 || k > 0) ? 1u : 0u);
+                pg_commit(&empty[s]);
+            }
+            __syncwarp();
+        }
+        if (ok && lane == 0) pg_commit(&done_bar);
+        __syncwarp();
+    }
+    if (!ok) atomicExch(&s_failed, 1);
+
+    // ---- epilogue: warps 0-7, accumulator = warp / 4, TMEM lane quarter = warp % 4 ----
+    if (warp < 8) {
+        bool fin = ok && mbar_wait_bounded(&done_bar, 0u);
+        if (!fin) atomicExch(&s_failed, 1);
+        pg_fence_after();
+        if (fin) {
+            const int acc = warp >> 2, q = warp & 3;
+            const int tok = m0 + acc * 128 + q * 32 + lane;
+#pragma unroll 1
+            for (int cc = 0; cc < PG_TILE_N / 32; cc++) {
+                uint32_t v[32];
+                pg_tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * 256 + cc * 32), v);
+                const int nn = n0 + cc * 32;
+                if (tok < seq) {
+                    float *dst = y + (size_t)tok * rows + nn;
+                    if (nn + 32 <= rows && (rows & 3) == 0) {   // 16-byte stores need rows % 4 == 0
+#pragma unroll
+                        for (int i = 0; i < 8; i++)
+                            *reinterpret_cast<float4 *>(dst + 4 * i) = make_float4(__uint_as_float(v[4 * i]), __uint_as_float(v[4 * i + 1]),
+                                                                                   __uint_as_float(v[4 * i + 2]), __uint_as_float(v[4 * i + 3]));
+                    } else {
+                        for (int i = 0; i < 32; i++)
+                            if (nn + i < rows) dst[i] = __uint_as_float(v[i]);
+                    }
+                }
+            }
+        }
+    }
+    pg_fence_before();
+    __syncthreads();
+    if (warp == 8) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
+        if (lane == 0 && s_failed && err_flag) atomicExch(err_flag, DEV_ERR_GEMM_TIMEOUT);
+    }
+}
+
+}  // namespace rnb

@@ -128,7 +128,7 @@ struct State {
     std::map<std::pair<const void *, size_t>, Resident> resident;
     uint64_t epoch = 0;
     rnb_b200_cache_snapshot ctr{};
-    DevBuf in_f32, xq, xq2, out_f32, mid_a, mid_b, mid_c, jobs, partials, misc, transient;
+    DevBuf in_f32, xq, xq2, out_f32, mid_a, mid_b, mid_c, jobs, partials, misc, transient, xb;
     PinnedBuf pin_in, pin_out, pin_jobs;
     int *dev_error = nullptr;
     std::map<size_t, KvMirror> kv_mirrors;

@@ -157,6 +157,18 @@ def q6k_gemv_batch(weights, rows: int, cols: int, x) -> np.ndarray:
     return _gemv(load().rnb_b200_q6k_gemv_batch, weights, rows, cols, x, seq=max(1, x.size // max(cols, 1)))
 
 
+def q4k_bf16_gemm_batch(weights, rows: int, cols: int, x) -> np.ndarray:
+    """Tensor-core prefill matmul (reference: q4k_f16_gemm_batch, api/quant_api.rs:2364): bf16
+    weights x bf16 tokens, f32 accumulate, output [seq][rows]."""
+    x = _f32(x).ravel()
+    return _gemv(load().rnb_b200_q4k_bf16_gemm_batch, weights, rows, cols, x, seq=max(1, x.size // max(cols, 1)))
+
+
+def q6k_bf16_gemm_batch(weights, rows: int, cols: int, x) -> np.ndarray:
+    x = _f32(x).ravel()
+    return _gemv(load().rnb_b200_q6k_bf16_gemm_batch, weights, rows, cols, x, seq=max(1, x.size // max(cols, 1)))
+
+
 # ---- attention -----------------------------------------------------------------------------
 def attention_decode_hd128(q, k, v, kv_len: int, num_heads: int, num_kv_heads: int, scale: float) -> np.ndarray:
     q, k, v = _f32(q).ravel(), _u16(k).ravel(), _u16(v).ravel()

@@ -1,0 +1,68 @@
+"""Tensor-core prefill matmul (tcgen05, bf16 x bf16 -> f32) against the oracle.
+
+The oracle side is rnb-cpu's dequantisation (f32) rounded once to bf16, tokens rounded to bf16,
+products summed in float64: the GPU result differs only by its f32 accumulation (a random walk
+of about sqrt(K) * 2^-24 of the partial sums, 1e-5 absolute at K = 4096), so errors are bounded
+relative to the size of a dot product, sqrt(sum (x*w)^2): 1e-4 of it, ten times tighter than
+the path's 1e-3.  A second check bounds the distance to the exact (unrounded) rnb-cpu matmul by
+what bf16 inputs allow."""
+import numpy as np
+import pytest
+
+import oracle as orc
+from synth import Q4_K, Q6_K, max_err_vs_norm, max_rel_err, quantized, random_blocks
+
+pytestmark = pytest.mark.gpu
+TOL = 1e-3
+
+
+def bf16_round(a: np.ndarray) -> np.ndarray:
+    u = np.ascontiguousarray(a, np.float32).view(np.uint32).astype(np.uint64)
+    r = ((u + 0x7FFF + ((u >> 16) & 1)) >> 16) << 16
+    return r.astype(np.uint32).view(np.float32)
+
+
+@pytest.fixture()
+def ops():
+    import runnburn_b200.ops as o
+    o.reset_state_for_engine_init()
+    return o
+
+
+@pytest.mark.parametrize("t,rows,cols,seq", [
+    (Q4_K, 256, 256, 1), (Q4_K, 256, 256, 256), (Q4_K, 300, 512, 37), (Q4_K, 1024, 4096, 273), (Q4_K, 4096, 4096, 512),
+    (Q6_K, 256, 256, 5), (Q6_K, 515, 1024, 100), (Q6_K, 1024, 4096, 300), (Q6_K, 4096, 2048, 512),
+])
+def test_bf16_gemm_matches_bf16_rounded_oracle(ops, t, rows, cols, seq):
+    rng = np.random.default_rng(rows * 31 + cols + seq)
+    _, w = quantized(rng, t, rows, cols)
+    x = rng.standard_normal((seq, cols)).astype(np.float32)
+    wd = orc.dequantize_matrix(t, w, rows, cols).reshape(rows, cols)
+    ref = bf16_round(x).astype(np.float64) @ bf16_round(wd).astype(np.float64).T
+    fn = ops.q4k_bf16_gemm_batch if t == Q4_K else ops.q6k_bf16_gemm_batch
+    got = fn(w, rows, cols, x).reshape(seq, rows)
+    scale = np.sqrt((x.astype(np.float64) ** 2) @ (wd.astype(np.float64) ** 2).T)
+    assert np.max(np.abs(got - ref) / np.maximum(scale, 1e-30)) <= TOL / 10
+    assert max_err_vs_norm(got, ref) <= TOL / 10
+    # distance to the exact matmul: two bf16 roundings per product, averaged over K terms
+    exact = x.astype(np.float64) @ wd.astype(np.float64).T
+    assert np.max(np.abs(got - exact) / np.maximum(scale, 1e-30)) <= 3e-2
+
+
+def test_bf16_gemm_uniform_quant_blocks_config1_shape(ops):
+    """BASELINE config 1 style blocks (uniform quants and scales) at a Llama layer shape."""
+    rng = np.random.default_rng(0)
+    rows, cols, seq = 4096, 4096, 256
+    w = random_blocks(rng, Q4_K, rows, cols)
+    x = rng.standard_normal((seq, cols)).astype(np.float32)
+    wd = orc.dequantize_matrix(Q4_K, w, rows, cols).reshape(rows, cols)
+    ref = bf16_round(x).astype(np.float64) @ bf16_round(wd).astype(np.float64).T
+    got = ops.q4k_bf16_gemm_batch(w, rows, cols, x).reshape(seq, rows)
+    assert max_err_vs_norm(got, ref) <= TOL / 10
+
+
+def test_bf16_gemm_rejects_bad_shapes(ops):
+    import runnburn_b200 as r
+    w = np.zeros(144, np.uint8)
+    with pytest.raises(r.RnbError):
+        ops.q4k_bf16_gemm_batch(w, 1, 256, np.zeros(255, np.float32))
