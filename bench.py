@@ -218,8 +218,74 @@ def load_peaks() -> dict:
     p = ROOT / "MEASURED_PEAKS.json"
     if p.exists():
         d = json.loads(p.read_text())
-        return {"hbm_gbs": float(d["hbm_gbs"]), "source": "measured"}
-    return {"hbm_gbs": 6650.0, "source": "fallback"}
+        return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d.get("bf16_tflops", 1590.0)),
+                "bf16_tflops_sustained": float(d.get("bf16_tflops_sustained", 1400.0)), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+def prefill_gemm_bench(shape: dict, seq: int, reps: int = 3) -> dict:
+    """Secondary measurement (BASELINE config 3): the seven matmuls of one 8B layer over `seq`
+    tokens on the tcgen05 kernel, device-resident operands, CUDA events on torch's current stream
+    (the kernel is launched on that stream).  Weights are random bytes with sane super-scales."""
+    import ctypes as C
+
+    import torch
+
+    import runnburn_b200 as r
+    L = r.load()
+    H, qd, kvd, ff = shape["hidden"], shape["n_head"] * 128, shape["n_kv_head"] * 128, shape["n_ff"]
+    # launches of a layer: (q, k, v) share the normed hidden state, (gate, up) likewise
+    groups = [[(12, qd, H), (12, kvd, H), (14, kvd, H)], [(12, H, qd)], [(12, ff, H), (12, ff, H)], [(14, H, ff)]]
+    g = torch.Generator(device="cuda").manual_seed(0)
+    stream = torch.cuda.current_stream().cuda_stream
+    peaks = load_peaks()
+    rows_out, flops_total, ms_total = [], 0.0, 0.0
+    for grp in groups:
+        cols = grp[0][2]
+        ws, ys = [], []
+        for t, rows, _ in grp:
+            blk = 144 if t == 12 else 210
+            w = torch.randint(0, 256, (rows, cols // 256, blk), dtype=torch.uint8, device="cuda", generator=g)
+            if t == 12:
+                w[..., 1] = 0x10; w[..., 3] = 0x10      # f16 d, dmin ~ 5e-4
+            else:
+                w[..., 209] = 0x10
+            ws.append(w)
+            ys.append(torch.empty(seq, rows, device="cuda"))
+        x = torch.randn(seq, cols, device="cuda", generator=g)
+        xb = torch.empty(seq * cols, dtype=torch.int16, device="cuda")
+        n = len(grp)
+        types = (C.c_int * n)(*[t for t, _, _ in grp])
+        wp = (C.c_void_p * n)(*[w.data_ptr() for w in ws])
+        rws = (C.c_size_t * n)(*[r_ for _, r_, _ in grp])
+        yp = (C.c_void_p * n)(*[y.data_ptr() for y in ys])
+
+        def run():
+            rc = L.rnb_b200_dev_prefill_gemm_multi(n, types, wp, rws, yp, cols, x.data_ptr(), seq, xb.data_ptr(), stream)
+            if rc != 0:
+                raise RuntimeError(L.rnb_b200_last_error().decode())
+        for _ in range(3):
+            run()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            run()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / reps
+        fl = sum(2.0 * r_ * cols * seq for _, r_, _ in grp)
+        flops_total += fl
+        ms_total += ms
+        rows_out.append({"matrices": ["%s %dx%d" % ("Q4_K" if t == 12 else "Q6_K", r_, c_) for t, r_, c_ in grp], "ms": ms, "tflops": fl / ms / 1e9})
+        del ws, ys, x, xb
+    if r.ops.dev_error_flag() != 0:
+        raise RuntimeError("device error flag set by the prefill matmul")
+    tf = flops_total / ms_total / 1e9
+    return {"workload": "llama3-8b layer matmuls, %d tokens" % seq, "tflops": tf, "peak_tflops": peaks["bf16_tflops"],
+            "frac_of_bf16_peak": tf / peaks["bf16_tflops"], "frac_of_sustained_bf16_peak": tf / peaks["bf16_tflops_sustained"],
+            "peak_source": peaks["source"], "ms_per_layer": ms_total, "includes": "f32->bf16 conversion of the tokens and in-kernel dequantisation",
+            "launches": rows_out}
 
 
 def run_gpu(args, shape, ctx, name, rank, world, local_rank):
@@ -338,6 +404,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-prefill", action="store_true", help="skip the secondary prefill-matmul measurement")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -357,6 +424,11 @@ def main():
     out = run_gpu(args, shape, ctx, name, rank, world, local_rank)
     if out is None:
         return
+    if world == 1 and shape.get("hidden") == 4096 and not args.no_prefill:
+        try:
+            out["prefill_gemm"] = prefill_gemm_bench(shape, 2048)
+        except Exception as e:   # a secondary figure must not lose the headline line
+            out["prefill_gemm"] = {"error": str(e)[:200]}
     if world == 1 and not args.no_cpu_baseline:
         s, layer, head = cpu_baseline(shape, ctx, reps=5, warmup=1)
         out["cpu_baseline"] = {"value": s.tok_per_s(min(layer), min(head)), "unit": UNIT, "cores": s.threads, "kind": "port",

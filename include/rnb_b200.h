@@ -293,6 +293,10 @@ int rnb_b200_dev_gemv(uint32_t type, const uint8_t *w_dev, size_t rows, size_t c
 int rnb_b200_dev_prefill_gemm(int type, const uint8_t *w_dev, size_t rows, size_t cols,
                               const float *x_dev, size_t seq, uint16_t *xb_dev, float *y_dev,
                               void *stream);
+/* Up to three matrices that share the tokens (q/k/v, gate/up) in one launch; arrays of length n. */
+int rnb_b200_dev_prefill_gemm_multi(int n, const int *types, const uint8_t *const *w_dev,
+                                    const size_t *rows, float *const *y_dev, size_t cols,
+                                    const float *x_dev, size_t seq, uint16_t *xb_dev, void *stream);
 int rnb_b200_dev_flash_decode(const float *q_dev, const uint16_t *k_dev, const uint16_t *v_dev,
                               size_t kv_len, size_t num_heads, size_t num_kv_heads, float scale,
                               float *partials_dev, size_t partials_bytes, int n_chunks,

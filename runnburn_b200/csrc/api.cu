@@ -344,8 +344,7 @@ static int prefill_gemm_host(int type, const uint8_t *w, size_t wl, size_t rows,
 int prefill_gemm_setup() {
     static bool done = false;
     if (done) return RNB_B200_OK;
-    RNB_CU(cudaFuncSetAttribute(prefill_gemm_kernel<TYPE_Q4_K>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PG_SMEM));
-    RNB_CU(cudaFuncSetAttribute(prefill_gemm_kernel<TYPE_Q6_K>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PG_SMEM));
+    RNB_CU(cudaFuncSetAttribute(prefill_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PG_SMEM));
     done = true;
     return RNB_B200_OK;
 }
@@ -556,6 +555,15 @@ int rnb_b200_dev_prefill_gemm(int type, const uint8_t *w_dev, size_t rows, size_
     Locked L;
     RNB_TRY(L.st.open());
     return launch_prefill_gemm((cudaStream_t)stream, type, w_dev, rows, cols, x_dev, seq, xb_dev, y_dev, L.st.dev_error);
+}
+int rnb_b200_dev_prefill_gemm_multi(int n, const int *types, const uint8_t *const *w_dev, const size_t *rows, float *const *y_dev, size_t cols,
+                                    const float *x_dev, size_t seq, uint16_t *xb_dev, void *stream) {
+    if (!types || !w_dev || !rows || !y_dev || !x_dev || !xb_dev) return fail(RNB_B200_VALIDATION_FAILED, "null pointer argument");
+    for (int i = 0; i < n && i < PG_MAX_JOBS; i++)
+        if (!w_dev[i] || !y_dev[i]) return fail(RNB_B200_VALIDATION_FAILED, "null pointer argument");
+    Locked L;
+    RNB_TRY(L.st.open());
+    return launch_prefill_gemm_multi((cudaStream_t)stream, n, types, w_dev, rows, y_dev, cols, x_dev, seq, xb_dev, L.st.dev_error);
 }
 
 // ---- attention --------------------------------------------------------------------------------

@@ -317,24 +317,38 @@ inline int launch_flash_decode(cudaStream_t s, const float *q, const uint16_t *k
 // Tensor-core prefill matmul: converts the f32 token rows to bf16 (scratch `xb`, seq*cols
 // elements) and runs the tcgen05 kernel.  y is [seq][rows] f32.
 int prefill_gemm_setup();   // raises the kernels' dynamic shared-memory limit once
+inline int launch_prefill_gemm_multi(cudaStream_t s, int n, const int *types, const uint8_t *const *w, const size_t *rows, float *const *y,
+                                     size_t cols, const float *x, size_t seq, uint16_t *xb, int *dev_error) {
+    if (n < 1 || n > PG_MAX_JOBS) return fail(RNB_B200_VALIDATION_FAILED, "prefill matmul takes 1..%d matrices per launch", PG_MAX_JOBS);
+    if (cols == 0 || cols % 256 != 0) return fail(RNB_B200_VALIDATION_FAILED, "cols(%zu) must be a non-zero multiple of 256", cols);
+    if (seq == 0) return fail(RNB_B200_VALIDATION_FAILED, "prefill matmul needs tokens");
+    if (((uintptr_t)x & 15u) || ((uintptr_t)xb & 15u)) return fail(RNB_B200_VALIDATION_FAILED, "prefill matmul operands are not aligned");
+    PgJobs jobs;
+    memset(&jobs, 0, sizeof(jobs));
+    jobs.n = n;
+    int tiles = 0;
+    for (int i = 0; i < n; i++) {
+        if (types[i] != TYPE_Q4_K && types[i] != TYPE_Q6_K) return fail(RNB_B200_UNSUPPORTED, "tensor-core prefill matmul supports Q4_K and Q6_K weights");
+        if (rows[i] == 0) return fail(RNB_B200_VALIDATION_FAILED, "prefill matmul needs rows");
+        if (((uintptr_t)w[i] & 1u) || ((uintptr_t)y[i] & 15u) || (types[i] == TYPE_Q4_K && ((uintptr_t)w[i] & 15u)))
+            return fail(RNB_B200_VALIDATION_FAILED, "prefill matmul operands are not aligned");
+        jobs.j[i].w = w[i];
+        jobs.j[i].y = y[i];
+        jobs.j[i].rows = (int)rows[i];
+        jobs.j[i].type = types[i];
+        jobs.j[i].tile0 = tiles;
+        tiles += (int)((rows[i] + PG_TILE_N - 1) / PG_TILE_N);
+    }
+    RNB_TRY(prefill_gemm_setup());
+    const size_t ne = seq * cols;
+    RNB_CU(launch_k(f32_to_bf16_kernel, dim3((unsigned)((ne / 8 + 255) / 256)), dim3(256), 0, s, x, xb, ne));
+    const dim3 grid((unsigned)tiles, (unsigned)((seq + PG_TILE_M - 1) / PG_TILE_M));
+    RNB_CU(launch_k(prefill_gemm_kernel, grid, dim3(PG_THREADS), PG_SMEM, s, jobs, (const uint16_t *)xb, (int)seq, (int)cols, dev_error));
+    return RNB_B200_OK;
+}
 inline int launch_prefill_gemm(cudaStream_t s, int type, const uint8_t *w, size_t rows, size_t cols, const float *x, size_t seq,
                                uint16_t *xb, float *y, int *dev_error) {
-    if (type != TYPE_Q4_K && type != TYPE_Q6_K) return fail(RNB_B200_UNSUPPORTED, "tensor-core prefill matmul supports Q4_K and Q6_K weights");
-    if (cols == 0 || cols % 256 != 0) return fail(RNB_B200_VALIDATION_FAILED, "cols(%zu) must be a non-zero multiple of 256", cols);
-    if (rows == 0 || seq == 0) return fail(RNB_B200_VALIDATION_FAILED, "prefill matmul needs rows and tokens");
-    if (((uintptr_t)w & 1u) || ((uintptr_t)x & 15u) || ((uintptr_t)xb & 15u) || ((uintptr_t)y & 15u) || (type == TYPE_Q4_K && ((uintptr_t)w & 15u)))
-        return fail(RNB_B200_VALIDATION_FAILED, "prefill matmul operands are not aligned");
-    RNB_TRY(prefill_gemm_setup());
-    const size_t n = seq * cols;
-    RNB_CU(launch_k(f32_to_bf16_kernel, dim3((unsigned)((n / 8 + 255) / 256)), dim3(256), 0, s, x, xb, n));
-    const dim3 grid((unsigned)((rows + PG_TILE_N - 1) / PG_TILE_N), (unsigned)((seq + PG_TILE_M - 1) / PG_TILE_M));
-    if (type == TYPE_Q4_K)
-        RNB_CU(launch_k(prefill_gemm_kernel<TYPE_Q4_K>, grid, dim3(PG_THREADS), PG_SMEM, s, w, (const uint16_t *)xb, y, (int)seq, (int)rows, (int)cols,
-                        dev_error));
-    else
-        RNB_CU(launch_k(prefill_gemm_kernel<TYPE_Q6_K>, grid, dim3(PG_THREADS), PG_SMEM, s, w, (const uint16_t *)xb, y, (int)seq, (int)rows, (int)cols,
-                        dev_error));
-    return RNB_B200_OK;
+    return launch_prefill_gemm_multi(s, 1, &type, &w, &rows, &y, cols, x, seq, xb, dev_error);
 }
 
 }  // namespace rnb

@@ -130,28 +130,29 @@ __device__ __forceinline__ uint32_t pg_ldg_u32_unaligned(const uint8_t *p) {
 }
 struct PgRawQ6 {
     uint32_t ql_a[8], ql_b[8], qh[8];   // ql[64n + 0..31], ql[64n + 32..63], qh[32n + 0..31]
-    uint32_t sc;                         // the four scales this group uses, as bytes
+    uint32_t sc[2];                      // scales 8n .. 8n+7 as bytes: word g&1 serves group g
     float d;
 };
-__device__ __forceinline__ void pg_load_q6(PgRawQ6 &r, const uint8_t *blk, int g) {
-    const int n = g >> 1;
+// One load serves both groups of half n (the even group reads low nibbles, the odd one high).
+__device__ __forceinline__ void pg_load_q6(PgRawQ6 &r, const uint8_t *blk, int n) {
 #pragma unroll
     for (int i = 0; i < 8; i++) {
         r.ql_a[i] = pg_ldg_u32_unaligned(blk + 64 * n + 4 * i);
         r.ql_b[i] = pg_ldg_u32_unaligned(blk + 64 * n + 32 + 4 * i);
         r.qh[i] = pg_ldg_u32_unaligned(blk + 128 + 32 * n + 4 * i);
     }
-    // scales of (first 32, second 32) elements of the group: is = 8n + 4(g&1) + {0,1} and + 2
-    const uint8_t *s = blk + 192 + 8 * n + 4 * (g & 1);
-    r.sc = (uint32_t)s[0] | ((uint32_t)s[1] << 8) | ((uint32_t)s[2] << 16) | ((uint32_t)s[3] << 24);
+    // scales of (first 32, second 32) elements of group g: is = 8n + 4(g&1) + {0,1} and + 2
+    r.sc[0] = pg_ldg_u32_unaligned(blk + 192 + 8 * n);
+    r.sc[1] = pg_ldg_u32_unaligned(blk + 196 + 8 * n);
     r.d = f16_bits_to_f32(*reinterpret_cast<const uint16_t *>(blk + 208));
 }
 __device__ __forceinline__ void pg_dequant_q6(const PgRawQ6 &r, int g, uint8_t *row_base, int rr) {
     const bool odd = g & 1;
     // element e = 0..31 of the group: first kind (q1 or q3), scale byte e/16; e = 32..63: second kind, scale byte 2 + (e-32)/16
     float ds[4];
+    const uint32_t scw = odd ? r.sc[1] : r.sc[0];
 #pragma unroll
-    for (int i = 0; i < 4; i++) ds[i] = __fmul_rn(r.d, (float)(int)(int8_t)((r.sc >> (8 * i)) & 0xffu));
+    for (int i = 0; i < 4; i++) ds[i] = __fmul_rn(r.d, (float)(int)(int8_t)((scw >> (8 * i)) & 0xffu));
 #pragma unroll
     for (int c = 0; c < 4; c++) {   // chunk c: elements 8c..8c+7 (first kind); chunk c+4: elements 32+8c.. (second kind)
         uint32_t o1[4], o2[4];
@@ -183,12 +184,22 @@ f32_to_bf16_kernel(const float *__restrict__ x, uint16_t *__restrict__ y, size_t
     *reinterpret_cast<uint4 *>(y + i) = make_uint4(pg_pack_bf16(a.x, a.y), pg_pack_bf16(a.z, a.w), pg_pack_bf16(b.x, b.y), pg_pack_bf16(b.z, b.w));
 }
 
-// grid = (ceil(rows / 256), ceil(seq / 256)); 288 threads; dynamic shared memory PG_SMEM.
-template <int TYPE>
+// Up to three matrices that share the token tile go out in one launch (q/k/v, gate/up): the
+// x dimension of the grid runs over the 256-row tiles of all of them.
+constexpr int PG_MAX_JOBS = 3;
+struct PgJob {
+    const uint8_t *w;
+    float *y;     // [seq][rows]
+    int rows, type, tile0, pad;
+};
+struct PgJobs {
+    PgJob j[PG_MAX_JOBS];
+    int n;
+};
+
+// grid = (sum over jobs of ceil(rows / 256), ceil(seq / 256)); 288 threads; dynamic shared memory PG_SMEM.
 RNB_GLOBAL void __launch_bounds__(PG_THREADS, 1)
-prefill_gemm_kernel(const uint8_t *__restrict__ w, const uint16_t *__restrict__ xb, float *__restrict__ y, int seq, int rows, int cols,
-                    int *__restrict__ err_flag) {
-    constexpr uint32_t BLK = TYPE == TYPE_Q4_K ? Q4K_BYTES : Q6K_BYTES;
+prefill_gemm_kernel(const __grid_constant__ PgJobs jobs, const uint16_t *__restrict__ xb, int seq, int cols, int *__restrict__ err_flag) {
     extern __shared__ __align__(1024) uint8_t pg_smem_raw[];
     __shared__ __align__(8) uint64_t full[PG_STAGES], empty[PG_STAGES], done_bar;
     __shared__ uint32_t tmem_base_slot;
@@ -197,7 +208,15 @@ prefill_gemm_kernel(const uint8_t *__restrict__ w, const uint16_t *__restrict__ 
     pdl_wait();
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(pg_smem_raw) + 1023) & ~(uintptr_t)1023);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int n0 = blockIdx.x * PG_TILE_N, m0 = blockIdx.y * PG_TILE_M;
+    int jsel = 0;
+    for (int i = 1; i < jobs.n; i++)
+        if ((int)blockIdx.x >= jobs.j[i].tile0) jsel = i;
+    const PgJob &job = jobs.j[jsel];
+    const int rows = job.rows, TYPE = job.type;
+    const uint8_t *__restrict__ w = job.w;
+    float *__restrict__ y = job.y;
+    const uint32_t BLK = TYPE == TYPE_Q4_K ? Q4K_BYTES : Q6K_BYTES;
+    const int n0 = ((int)blockIdx.x - job.tile0) * PG_TILE_N, m0 = blockIdx.y * PG_TILE_M;
     const int nb = cols >> 8, KT = cols / PG_K;
     if (tid == 0) {
         for (int s = 0; s < PG_STAGES; s++) {
@@ -223,37 +242,51 @@ prefill_gemm_kernel(const uint8_t *__restrict__ w, const uint16_t *__restrict__ 
         const size_t rb = (size_t)nb * BLK;
         const int ra = min(n0 + tid, rows - 1), rbw = min(n0 + tid + 128, rows - 1);   // rows past the end repeat the last one (never stored)
         const uint8_t *wa = w + (size_t)ra * rb, *wb = w + (size_t)rbw * rb;
-        typename std::conditional<TYPE == TYPE_Q4_K, PgRawQ4, PgRawQ6>::type cur_a, cur_b, nxt_a, nxt_b;
-        auto load = [&](decltype(cur_a) &a, decltype(cur_b) &b, int kt) {
-            const int blk = kt >> 2, g = kt & 3;
-            if constexpr (TYPE == TYPE_Q4_K) {
-                pg_load_q4(a, wa + (size_t)blk * BLK, g);
-                pg_load_q4(b, wb + (size_t)blk * BLK, g);
-            } else {
-                pg_load_q6(a, wa + (size_t)blk * BLK, g);
-                pg_load_q6(b, wb + (size_t)blk * BLK, g);
+        uint8_t *const row1 = smem + PG_TILE_BYTES + (tid >> 3) * 1024 + (tid & 7) * 128, *const row2 = row1 + 16 * 1024;   // rows t, t + 128
+        const int rr = tid & 7;
+        if (TYPE == TYPE_Q4_K) {
+            PgRawQ4 cur_a, cur_b, nxt_a, nxt_b;
+            pg_load_q4(cur_a, wa, 0);
+            pg_load_q4(cur_b, wb, 0);
+            for (int kt = 0; kt < KT && ok; kt++) {
+                const int s = kt % PG_STAGES;
+                if (kt + 1 < KT) {
+                    pg_load_q4(nxt_a, wa + (size_t)((kt + 1) >> 2) * BLK, (kt + 1) & 3);
+                    pg_load_q4(nxt_b, wb + (size_t)((kt + 1) >> 2) * BLK, (kt + 1) & 3);
+                }
+                ok = mbar_wait_bounded(&empty[s], (uint32_t)(((kt / PG_STAGES) & 1) ^ 1));
+                if (!ok) break;
+                pg_dequant_q4(cur_a, kt & 3, row1 + (uint32_t)s * PG_STAGE_BYTES, rr);
+                pg_dequant_q4(cur_b, kt & 3, row2 + (uint32_t)s * PG_STAGE_BYTES, rr);
+                pg_proxy_fence();
+                __syncwarp();
+                if (lane == 0) pg_arrive(&full[s]);
+                cur_a = nxt_a;
+                cur_b = nxt_b;
             }
-        };
-        load(cur_a, cur_b, 0);
-        for (int kt = 0; kt < KT && ok; kt++) {
-            const int s = kt % PG_STAGES;
-            if (kt + 1 < KT) load(nxt_a, nxt_b, kt + 1);
-            ok = mbar_wait_bounded(&empty[s], (uint32_t)(((kt / PG_STAGES) & 1) ^ 1));
-            if (!ok) break;
-            uint8_t *bt = smem + (uint32_t)s * PG_STAGE_BYTES + PG_TILE_BYTES;
-            const int r1 = tid, r2 = tid + 128, g = kt & 3;
-            if constexpr (TYPE == TYPE_Q4_K) {
-                pg_dequant_q4(cur_a, g, bt + (r1 >> 3) * 1024 + (r1 & 7) * 128, r1 & 7);
-                pg_dequant_q4(cur_b, g, bt + (r2 >> 3) * 1024 + (r2 & 7) * 128, r2 & 7);
-            } else {
-                pg_dequant_q6(cur_a, g, bt + (r1 >> 3) * 1024 + (r1 & 7) * 128, r1 & 7);
-                pg_dequant_q6(cur_b, g, bt + (r2 >> 3) * 1024 + (r2 & 7) * 128, r2 & 7);
+        } else {
+            PgRawQ6 cur_a, cur_b, nxt_a, nxt_b;
+            pg_load_q6(cur_a, wa, 0);
+            pg_load_q6(cur_b, wb, 0);
+            for (int kt = 0; kt < KT && ok; kt++) {
+                const int s = kt % PG_STAGES;
+                // a half block (128 elements) serves two stages: fetch the next half two stages ahead
+                if (!(kt & 1) && kt + 2 < KT) {
+                    pg_load_q6(nxt_a, wa + (size_t)((kt + 2) >> 2) * BLK, ((kt + 2) >> 1) & 1);
+                    pg_load_q6(nxt_b, wb + (size_t)((kt + 2) >> 2) * BLK, ((kt + 2) >> 1) & 1);
+                }
+                ok = mbar_wait_bounded(&empty[s], (uint32_t)(((kt / PG_STAGES) & 1) ^ 1));
+                if (!ok) break;
+                pg_dequant_q6(cur_a, kt & 3, row1 + (uint32_t)s * PG_STAGE_BYTES, rr);
+                pg_dequant_q6(cur_b, kt & 3, row2 + (uint32_t)s * PG_STAGE_BYTES, rr);
+                pg_proxy_fence();
+                __syncwarp();
+                if (lane == 0) pg_arrive(&full[s]);
+                if (kt & 1) {
+                    cur_a = nxt_a;
+                    cur_b = nxt_b;
+                }
             }
-            pg_proxy_fence();
-            __syncwarp();
-            if (lane == 0) pg_arrive(&full[s]);
-            cur_a = nxt_a;
-            cur_b = nxt_b;
         }
     } else if (warp < 8) {
         // ---- token producers: cp.async the 256 x 64 bf16 tile, one stage ahead ----

@@ -61,6 +61,36 @@ def test_bf16_gemm_uniform_quant_blocks_config1_shape(ops):
     assert max_err_vs_norm(got, ref) <= TOL / 10
 
 
+def test_bf16_gemm_three_matrices_one_launch(ops):
+    """q/k/v style: three matrices (mixed Q4_K / Q6_K, different row counts) behind one token tile."""
+    import ctypes as C
+
+    import torch
+
+    import runnburn_b200 as r
+    L = r.load()
+    rng = np.random.default_rng(11)
+    cols, seq = 1024, 70
+    specs = [(Q4_K, 512), (Q4_K, 130), (Q6_K, 256)]
+    ws = [quantized(rng, t, rows, cols)[1] for t, rows in specs]
+    x = rng.standard_normal((seq, cols)).astype(np.float32)
+    wt = [torch.from_numpy(np.ascontiguousarray(w)).cuda() for w in ws]
+    xt = torch.from_numpy(x).cuda()
+    xb = torch.empty(seq * cols, dtype=torch.int16, device="cuda")
+    ys = [torch.zeros(seq, rows, device="cuda") for _, rows in specs]
+    n = len(specs)
+    rc = L.rnb_b200_dev_prefill_gemm_multi(n, (C.c_int * n)(*[t for t, _ in specs]), (C.c_void_p * n)(*[w.data_ptr() for w in wt]),
+                                           (C.c_size_t * n)(*[rows for _, rows in specs]), (C.c_void_p * n)(*[y.data_ptr() for y in ys]),
+                                           cols, xt.data_ptr(), seq, xb.data_ptr(), torch.cuda.current_stream().cuda_stream)
+    assert rc == 0, L.rnb_b200_last_error()
+    torch.cuda.synchronize()
+    assert ops.dev_error_flag() == 0
+    for (t, rows), w, y in zip(specs, ws, ys):
+        wd = orc.dequantize_matrix(t, w, rows, cols).reshape(rows, cols)
+        ref = bf16_round(x).astype(np.float64) @ bf16_round(wd).astype(np.float64).T
+        assert max_err_vs_norm(y.cpu().numpy(), ref) <= TOL / 10
+
+
 def test_bf16_gemm_rejects_bad_shapes(ops):
     import runnburn_b200 as r
     w = np.zeros(144, np.uint8)
