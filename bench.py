@@ -33,6 +33,9 @@ WORKLOADS = {
     "llama3-70b-q4km-ctx32768": (dict(n_layer=80, hidden=8192, n_head=64, n_kv_head=8, n_ff=28672, vocab=128256), 32768),
     # two layers of the 8B shapes + its LM head: the capture-sized case for ncu (about 1 GB resident)
     "llama3-8b-2layers-ctx4096": (dict(n_layer=2, hidden=4096, n_head=32, n_kv_head=8, n_ff=14336, vocab=128256), 4096),
+    # BASELINE config 4: Qwen3-30B-A3B shape, 128 experts top-8 (Q4_K), attention in Q6_K
+    "qwen3-30b-a3b-moe-ctx8192": (dict(n_layer=48, hidden=2048, n_head=32, n_kv_head=4, n_ff=0, vocab=128256, n_expert=128, n_expert_used=8,
+                                       n_ff_expert=768, rope_neox=1), 8192),
     "tiny-llama-ctx256": (dict(n_layer=2, hidden=512, n_head=4, n_kv_head=2, n_ff=1024, vocab=2048), 256),
 }
 DRAM_TRAFFIC_OVER_ALGORITHMIC = 574.6 / 570.6
@@ -52,8 +55,14 @@ def algorithmic_bytes_per_token(shape: dict, ctx: int) -> dict:
     """Bytes one decode token must move (Q4_K_M convention: attn_v, ffn_down, LM head in
     Q6_K): weights once, the visible KV rows once, activations (Q8_K in, f32 out)."""
     H, qd, kvd, ff, V, L = shape["hidden"], shape["n_head"] * 128, shape["n_kv_head"] * 128, shape["n_ff"], shape["vocab"], shape["n_layer"]
-    mats = [(12, qd, H), (12, kvd, H), (14, kvd, H), (12, H, qd), (12, ff, H), (12, ff, H), (14, H, ff)]
-    w_layer = sum(r * row_bytes(t, c) for t, r, c in mats)
+    if shape.get("n_expert", 0):
+        # attention in Q6_K, f32 router, the k routed experts' gate/up/down in Q4_K
+        k, ffe = shape["n_expert_used"], shape["n_ff_expert"]
+        mats = [(14, qd, H), (14, kvd, H), (14, kvd, H), (14, H, qd)] + [(12, ffe, H)] * (2 * k) + [(12, H, ffe)] * k
+        w_layer = sum(r * row_bytes(t, c) for t, r, c in mats) + shape["n_expert"] * H * 4
+    else:
+        mats = [(12, qd, H), (12, kvd, H), (14, kvd, H), (12, H, qd), (12, ff, H), (12, ff, H), (14, H, ff)]
+        w_layer = sum(r * row_bytes(t, c) for t, r, c in mats)
     act_layer = sum(q8k_bytes(c) + r * 4 for t, r, c in mats)
     w = L * w_layer + V * row_bytes(14, H) + row_bytes(12, H)   # + LM head + one embedding row
     act = L * act_layer + q8k_bytes(H) + V * 4
@@ -309,10 +318,15 @@ def run_gpu(args, shape, ctx, name, rank, world, local_rank):
     max_ctx = ctx + 2 * (K + W) + 8
     cfg = r.ModelConfig(max_ctx=max_ctx, world_size=world, rank=rank, **shape)
     dec = r.Decoder(cfg)
-    if world > 1:
+    transport = os.environ.get("RNB_B200_TRANSPORT", "peer")   # "peer": peer-memory exchange kernels; "nccl": ncclAllGather
+    if world > 1 and transport == "nccl":
         ids = [nccl_unique_id() if rank == 0 else None]
         dist.broadcast_object_list(ids, src=0)
         dec.attach_nccl(ids[0])
+    elif world > 1:
+        handles = [None] * world
+        dist.all_gather_object(handles, dec.exchange_handle())
+        dec.attach_peers(handles)
     dec.fill_synthetic(seed=0, sigma=0.02)
     dec.fill_kv_synthetic(ctx, seed=0)
     stats = dec.stats()
@@ -367,9 +381,9 @@ def run_gpu(args, shape, ctx, name, rank, world, local_rank):
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": max(W, 3),
         "ms_per_step": ms / K, "higher_is_better": True, "scaling": "strong" if world > 1 else "weak",
         "vs_baseline": None, "dtype": "int8xint4->int32, f32 accumulate", "data": "synthetic",
-        "config": {"workload": name, "context": ctx, "kv_cache": "f16", "weights": "random-init N(0,0.02), Q4_K_M layout (attn_v/ffn_down/output Q6_K), generated on device",
-                   "parallelism": f"row-sharded x{world} + NCCL all-gather" if world > 1 else "single GPU",
-                   "l2": "each step streams the whole model (>= 4.9 GB), far larger than the 126 MB L2: no flush needed",
+        "config": {"workload": name, "context": ctx, "kv_cache": "f16", "weights": ("random-init N(0,0.02): attention and LM head Q6_K, f32 router, experts Q4_K, generated on device" if shape.get("n_expert", 0) else "random-init N(0,0.02), Q4_K_M layout (attn_v/ffn_down/output Q6_K), generated on device"),
+                   "parallelism": (f"row-sharded x{world}, all-gather by " + ("ncclAllGather" if transport == "nccl" else "peer-memory stores over NVLink (own kernel)")) if world > 1 else "single GPU",
+                   "l2": "each step streams its whole weight set and KV cache (GBs), far more than the 126 MB L2: no flush needed",
                    "algorithmic_bytes_per_token": alg},
         "e2e": {"value": K / e2e_s, "unit": UNIT, "h2d_bytes_per_step": 8, "d2h_bytes_per_step": 8},
         "gpu_launches": int(stats["launches_per_step"]) * K,

@@ -279,6 +279,14 @@ int rnb_b200_decoder_time_matvecs(rnb_b200_decoder *d, int iters, float *ms_out,
  * with rnb_b200_nccl_unique_id and the host side distributed to every rank. */
 int rnb_b200_nccl_unique_id(uint8_t id_out[128]);
 int rnb_b200_decoder_attach_nccl(rnb_b200_decoder *d, const uint8_t id[128]);
+/* Multi-GPU exchange over peer memory (the default transport; the NCCL communicator above is
+ * the fallback): every rank exports the CUDA IPC handle of its exchange arena, the host side
+ * all-gathers the 64-byte handles, every rank attaches the full list (rank order).  After
+ * that the slices of the four per-layer all-gathers travel as peer stores with a flag per
+ * exchange and rank; a slice that does not arrive within about a second sets the device error
+ * flag instead of hanging.  No counterpart in the reference (its CUDA path is single-GPU). */
+int rnb_b200_decoder_exchange_handle(rnb_b200_decoder *d, uint8_t handle_out[64]);
+int rnb_b200_decoder_attach_peers(rnb_b200_decoder *d, const uint8_t *handles /* world x 64 */);
 
 /* ---- device-pointer tier (no host copies, no synchronisation; for callers that keep
  * activations on the device and for kernel timing).  `stream` is a cudaStream_t or NULL. */

@@ -240,7 +240,10 @@ int State::check_dev_error() {
     if (flag != 0) {
         cudaMemsetAsync(dev_error, 0, sizeof(int), stream);
         return fail(RNB_B200_DEVICE_FAULT_FLAG, "device kernel reported error flag %d (%s)", flag,
-                    flag == DEV_ERR_MBAR_TIMEOUT ? "bounded mbarrier wait gave up" : "inconsistent job table");
+                    flag == DEV_ERR_MBAR_TIMEOUT   ? "bounded mbarrier wait gave up"
+                    : flag == DEV_ERR_GEMM_TIMEOUT ? "tensor-core matmul pipeline wait gave up"
+                    : flag == DEV_ERR_PEER_TIMEOUT ? "a peer GPU's slice did not arrive in time"
+                                                   : "inconsistent job table");
     }
     return RNB_B200_OK;
 }

@@ -28,6 +28,8 @@ constexpr int TYPE_Q6_K = 14;
 constexpr int DEV_ERR_NONE = 0;
 constexpr int DEV_ERR_MBAR_TIMEOUT = 1;   // a bounded mbarrier wait gave up
 constexpr int DEV_ERR_BAD_JOB = 2;        // job table inconsistent with the launch
+constexpr int DEV_ERR_GEMM_TIMEOUT = 3;   // tensor-core matmul: a pipeline wait gave up
+constexpr int DEV_ERR_PEER_TIMEOUT = 4;   // multi-GPU exchange: a peer's slice did not arrive in time
 
 __host__ __device__ inline size_t row_bytes_of(int type, size_t cols) {
     switch (type) {

@@ -33,7 +33,6 @@ constexpr int PG_THREADS = 288;
 constexpr uint32_t PG_TILE_BYTES = 256 * 128;                      // one operand tile of a stage
 constexpr uint32_t PG_STAGE_BYTES = 2 * PG_TILE_BYTES;
 constexpr size_t PG_SMEM = (size_t)PG_STAGES * PG_STAGE_BYTES + 1024;   // + slack to align to 1024
-constexpr int DEV_ERR_GEMM_TIMEOUT = 3;
 
 __device__ __forceinline__ uint32_t pg_swz(int r, int c) { return (uint32_t)((r >> 3) * 1024 + (r & 7) * 128 + ((c ^ (r & 7)) << 4)); }
 

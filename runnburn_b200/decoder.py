@@ -99,6 +99,18 @@ class Decoder:
         check(load().rnb_b200_decoder_attach_nccl(self._h, buf))
 
     # -- stepping --
+    def exchange_handle(self) -> bytes:
+        """CUDA IPC handle of this rank's exchange arena (64 bytes), to be all-gathered by the host."""
+        buf = (C.c_uint8 * 64)()
+        check(load().rnb_b200_decoder_exchange_handle(self._h, buf))
+        return bytes(buf)
+
+    def attach_peers(self, handles: list) -> None:
+        """`handles`: every rank's exchange handle in rank order; switches the all-gathers to peer stores."""
+        blob = b"".join(handles)
+        buf = (C.c_uint8 * len(blob)).from_buffer_copy(blob)
+        check(load().rnb_b200_decoder_attach_peers(self._h, buf))
+
     def step(self, token: int, pos: int, want_logits: bool = False):
         nxt = C.c_uint32()
         logits = np.empty(self.cfg.vocab, np.float32) if want_logits else None

@@ -100,7 +100,7 @@ def test_q4k_gemv_config1_shapes(ops, rows, cols):
 @pytest.mark.parametrize("t,rows,cols", [
     (Q4_K, 1, 256), (Q4_K, 3, 256), (Q4_K, 130, 512), (Q4_K, 257, 768), (Q4_K, 2048, 768), (Q4_K, 768, 2048),
     (Q6_K, 1, 256), (Q6_K, 5, 256), (Q6_K, 7, 768), (Q6_K, 130, 512), (Q6_K, 1024, 4096), (Q6_K, 4096, 14336),
-    (Q6_K, 515, 2048),
+    (Q6_K, 515, 2048), (Q4_K, 16400, 512), (Q4_K, 20000, 1024), (Q4_K, 16385, 256),   # >= 16384 rows: two-threads-per-row kernel
     (Q8_0, 1, 32), (Q8_0, 3, 96), (Q8_0, 129, 256), (Q8_0, 1000, 4096),
 ])
 def test_gemv_shapes_and_ragged_tiles(ops, t, rows, cols):

@@ -1,5 +1,5 @@
-"""Row-sharded decode on two GPUs: q/k/v by head, KV cache by KV head, NCCL all-gather of the
-f32 slices inside the per-token graph.  Greedy ids must equal the oracle's (and therefore the
+"""Row-sharded decode on two GPUs: q/k/v by head, KV cache by KV head, all-gather of the f32
+slices inside the per-token graph by peer-memory stores (default) or ncclAllGather.  Greedy ids must equal the oracle's (and therefore the
 single-GPU decoder's).  Needs two devices; skipped otherwise."""
 import os
 import subprocess
@@ -28,9 +28,14 @@ WORKER = textwrap.dedent("""
     ops.open()
     desc = llama_description(seed=0, n_layer=2, hidden=512, n_head=4, n_kv_head=2, n_ff=1024, vocab=2048)
     dec = r.Decoder(r.ModelConfig(max_ctx=64, world_size=world, rank=rank, **desc["cfg"]))
-    ids = [nccl_unique_id() if rank == 0 else None]
-    dist.broadcast_object_list(ids, src=0)
-    dec.attach_nccl(ids[0])
+    if os.environ.get("RNB_TEST_TRANSPORT", "peer") == "nccl":
+        ids = [nccl_unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(ids, src=0)
+        dec.attach_nccl(ids[0])
+    else:
+        handles = [None] * world
+        dist.all_gather_object(handles, dec.exchange_handle())
+        dec.attach_peers(handles)
     dec.load_description(desc)
     ref = orc.Model(desc, 64)
     rng = np.random.default_rng(0)
@@ -61,13 +66,14 @@ WORKER = textwrap.dedent("""
 """)
 
 
-def test_two_gpu_row_sharded_greedy_ids(tmp_path):
+@pytest.mark.parametrize("transport", ["peer", "nccl"])
+def test_two_gpu_row_sharded_greedy_ids(tmp_path, transport):
     import torch
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     script = tmp_path / "worker.py"
     script.write_text(WORKER % (str(ROOT), str(ROOT / "tests")))
-    env = dict(os.environ, MASTER_ADDR="127.0.0.1")
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", RNB_TEST_TRANSPORT=transport)
     r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
                         "--master-addr", "127.0.0.1", "--master-port", "29741", str(script)],
                        capture_output=True, text=True, env=env, timeout=600)
