@@ -4,7 +4,6 @@
 #include "gemv.cuh"
 #include "gemv_stream.cuh"
 #include "gemv_pair.cuh"
-#include "gemv_ksplit.cuh"
 #include "moe.cuh"
 #include "prefill_gemm.cuh"
 #include "q8k.cuh"
@@ -149,40 +148,8 @@ inline const PairTuning &pair_tuning() {
 }
 // Row-rich, all-Q4_K, single-part, 16-byte aligned static tables go to the two-threads-per-row
 // kernel; everything else to the eight-threads-per-row kernel.
-// K-split kernel: single static Q6_K job with long rows (RNB_B200_KSPLIT=0 turns it off,
-// RNB_B200_KSPLIT_MIN_COLS moves the threshold).
-struct KsplitTuning {
-    int enabled, min_cols, max_rows, stages;
-};
-inline const KsplitTuning &ksplit_tuning() {
-    static const KsplitTuning t = [] {
-        auto env_int = [](const char *name, int dflt) {
-            const char *e = getenv(name);
-            return (e && *e) ? atoi(e) : dflt;
-        };
-        KsplitTuning v;
-        v.enabled = env_int("RNB_B200_KSPLIT", 1);
-        v.min_cols = env_int("RNB_B200_KSPLIT_MIN_COLS", 8192);
-        v.max_rows = env_int("RNB_B200_KSPLIT_MAX_ROWS", 1 << 30);
-        v.stages = env_int("RNB_B200_KSPLIT_STAGES", 3);
-        if (v.stages < 1) v.stages = 1;
-        if (v.stages > GK_MAX_STAGES) v.stages = GK_MAX_STAGES;
-        return v;
-    }();
-    return t;
-}
 inline int launch_gemv_stream(cudaStream_t s, const GemvJob *jobs_host, const GemvJob *jobs_dev, int n_jobs,
                               size_t cols, int *dev_error, int dynamic_table, bool by_value) {
-    const KsplitTuning &kt = ksplit_tuning();
-    if (kt.enabled && !dynamic_table && n_jobs == 1 && jobs_host[0].type == TYPE_Q6_K && jobs_host[0].n_parts == 1 && jobs_host[0].seq <= 1 &&
-        cols % (256 * GK_CHUNK) == 0 && (int)cols >= kt.min_cols && jobs_host[0].rows <= kt.max_rows &&
-        ((((uintptr_t)jobs_host[0].parts[0].w | (uintptr_t)jobs_host[0].parts[0].x) & 15u) == 0) && gk_smem(kt.stages) <= gemv_smem_max()) {
-        const int tiles = (jobs_host[0].rows + GK_ROWS - 1) / GK_ROWS;
-        const int n_chunks = (int)(cols / (256 * GK_CHUNK));
-        const int S = kt.stages < n_chunks ? kt.stages : n_chunks;
-        RNB_CU(launch_k(gemv_ksplit_q6k_kernel, dim3(tiles), dim3(GK_THREADS), (size_t)gk_smem(S), s, jobs_host[0], (int)cols, S, dev_error));
-        return RNB_B200_OK;
-    }
     const PairTuning &pt = pair_tuning();
     bool pair = pt.enabled && !dynamic_table && n_jobs <= GS_PACK && cols % 256 == 0;
     size_t total_rows = 0;
