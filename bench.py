@@ -404,6 +404,19 @@ def run_gpu(args, shape, ctx, name, rank, world, local_rank):
                            "launches_per_step": mv["launches_per_iter"],
                            "algorithmic_bytes_per_launch": per_launch_bytes, "avg_launch_us": per_launch_s * 1e6,
                            "how": "CUDA events around all matvec launches of a step on the decoder stream, model's own weights"}
+    if world == 1 and shape.get("n_expert", 0) == 0 and not args.no_prefill:
+        # secondary measurement (BASELINE config 3): prefill of a 2048-token random prompt through the
+        # decoder's tensor-core path, device time between two events on the decoder's stream
+        try:
+            n_tok = min(2048, ctx)
+            ids = np.random.default_rng(0).integers(0, shape["vocab"], n_tok).astype(np.uint32)
+            dec.prefill(ids, 0, timed=True)
+            _, pms = dec.prefill(ids, 0, timed=True)
+            out["prefill"] = {"tokens": int(n_tok), "ms": pms, "tok_per_s": n_tok / (pms / 1000.0),
+                              "what": "embed, 32 x (RMSNorm, q/k/v matmul, RoPE + f16 KV append, causal attention, o_proj, RMSNorm, gate/up, SiLU*up, down), "
+                                      "final norm + LM head + argmax of the last token; matmuls on tcgen05 (bf16), attention on CUDA cores (fp32)"}
+        except Exception as e:   # a secondary figure must not lose the headline line
+            out["prefill"] = {"error": str(e)[:200]}
     dec.close()
     if dist is not None:
         dist.destroy_process_group()

@@ -279,6 +279,17 @@ int rnb_b200_decoder_time_matvecs(rnb_b200_decoder *d, int iters, float *ms_out,
  * with rnb_b200_nccl_unique_id and the host side distributed to every rank. */
 int rnb_b200_nccl_unique_id(uint8_t id_out[128]);
 int rnb_b200_decoder_attach_nccl(rnb_b200_decoder *d, const uint8_t id[128]);
+/* Prefill of n prompt tokens at positions pos0..pos0+n-1 (Engine::forward_prefill,
+ * crates/rnb-llm/src/engine/prefill.rs; CUDA path crates/rnb-runtime/src/cuda_inference/cuda/
+ * prefill.rs:1104-1166): all matmuls on the tcgen05 kernel (bf16 x bf16 -> f32), RoPE + f16 KV
+ * append for every position, causal attention over the cache, then the last token's logits ->
+ * greedy token.  Leaves the decoder ready to decode at position pos0+n.  ms_out (optional):
+ * device time between two events on the decoder's stream.  Single GPU, dense stacks. */
+int rnb_b200_decoder_prefill(rnb_b200_decoder *d, const uint32_t *tokens, int n, int pos0,
+                             uint32_t *next_token, float *ms_out);
+/* Logits of the last step or prefill (this rank's vocab slice), for tests. */
+int rnb_b200_decoder_read_logits(rnb_b200_decoder *d, float *out, size_t n);
+
 /* Multi-GPU exchange over peer memory (the default transport; the NCCL communicator above is
  * the fallback): every rank exports the CUDA IPC handle of its exchange arena, the host side
  * all-gathers the 64-byte handles, every rank attaches the full list (rank order).  After

@@ -121,6 +121,8 @@ def load() -> C.CDLL:
         "rnb_b200_decoder_time_matvecs": [vp, i32, vp, vp, vp],
         "rnb_b200_nccl_unique_id": [vp],
         "rnb_b200_decoder_attach_nccl": [vp, vp],
+        "rnb_b200_decoder_prefill": [vp, vp, i32, i32, vp, vp],
+        "rnb_b200_decoder_read_logits": [vp, vp, sz],
         "rnb_b200_decoder_exchange_handle": [vp, vp],
         "rnb_b200_decoder_attach_peers": [vp, vp],
         "rnb_b200_dev_quantize_q8k": [vp, sz, sz, vp, vp, vp],

@@ -66,6 +66,7 @@ int gemv_kernel_setup() {
     RNB_CU(cudaFuncSetAttribute(gemv_stream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn));
     RNB_CU(cudaFuncSetAttribute(gemv_stream_kernel_1, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn));
     RNB_CU(cudaFuncSetAttribute(gemv_pair_q4k_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn));
+    RNB_CU(cudaFuncSetAttribute(gemv_ksplit_q6k_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn));
     g_gemv_smem_max = dyn;
     done = true;
     return RNB_B200_OK;

@@ -30,7 +30,12 @@ rope_kv_append_kernel(float *__restrict__ q, const float *__restrict__ k,
                       uint16_t *__restrict__ v_row_out) {
     pdl_launch_dependents();
     pdl_wait();
-    const int pos = (pos_dev ? *pos_dev : 0) + pos_offset;
+    // gridDim.y > 1: a batch of consecutive tokens (prefill), token t = blockIdx.y at position base + t,
+    // its q/k/v rows t * (heads or kv heads) * 128 further on
+    q += (size_t)blockIdx.y * num_heads * HD;
+    k += (size_t)blockIdx.y * num_kv_heads * HD;
+    v += (size_t)blockIdx.y * num_kv_heads * HD;
+    const int pos = (pos_dev ? *pos_dev : 0) + pos_offset + (int)blockIdx.y;
     const int i = threadIdx.x;
     const float *cs = rope_table + (size_t)(table_by_pos ? pos : 0) * 128;
     const float c = cs[i], s = cs[64 + i];
@@ -94,6 +99,7 @@ RNB_GLOBAL void kv_append_f16_kernel(const float *__restrict__ src, uint16_t *__
 // merges chunks with the usual log-sum-exp rule.
 constexpr int FD_THREADS = 128;
 constexpr int FD_PART_STRIDE = HD + 2;
+constexpr int FD_MAX_CHUNKS = 1024;   // merge kernels keep one rescale factor per chunk in shared memory
 
 // four consecutive K/V elements as f32, from an f16 cache (decode) or f32 tensors (prefill API)
 __device__ __forceinline__ float4 kv_load4(const uint16_t *p) {
@@ -451,34 +457,58 @@ flash_decode_mma_kernel(const float *__restrict__ q, const uint16_t *__restrict_
     }
 }
 
-// grid = num_heads, 128 threads (one per output dim).
-RNB_GLOBAL void __launch_bounds__(HD)
+// Chunk merge: grid = num_heads, 512 threads.  The threads first agree on the global max and
+// the per-chunk rescale factors (shared memory), then thread (group g = tid / 128, dim d) sums
+// dimension d over the chunks c = g, g + 4, ...; the four groups are added at the end.  A head
+// sharded onto one GPU of eight has hundreds of chunks: a serial walk would take tens of us.
+RNB_GLOBAL void __launch_bounds__(4 * HD)
 flash_decode_reduce_kernel(const float *__restrict__ partials, int n_chunks,
                            float *__restrict__ out) {
     pdl_launch_dependents();
     pdl_wait();
-    const int h = blockIdx.x, d = threadIdx.x;
+    __shared__ float s_f[FD_MAX_CHUNKS];
+    __shared__ float s_red[16];
+    __shared__ float s_part[4][HD];
+    const int h = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const float *base = partials + (size_t)h * n_chunks * FD_PART_STRIDE;
+    float m = -INFINITY;
+    for (int c = tid; c < n_chunks; c += 4 * HD) m = fmaxf(m, base[(size_t)c * FD_PART_STRIDE + HD]);
+    m = warp_max(m);
+    if (lane == 0) s_red[warp] = m;
+    __syncthreads();
     float M = -INFINITY;
-#pragma unroll 8
-    for (int c = 0; c < n_chunks; c++) M = fmaxf(M, base[(size_t)c * FD_PART_STRIDE + HD]);
-    float a = 0.f, L = 0.f;
-#pragma unroll 8
-    for (int c = 0; c < n_chunks; c++) {
-        const float *pc = base + (size_t)c * FD_PART_STRIDE;
-        const float mc = pc[HD];
+#pragma unroll
+    for (int i = 0; i < 16; i++) M = fmaxf(M, s_red[i]);
+    __syncthreads();
+    float l = 0.f;
+    for (int c = tid; c < n_chunks; c += 4 * HD) {
+        const float mc = base[(size_t)c * FD_PART_STRIDE + HD];
         const float f = mc == -INFINITY ? 0.f : expf(mc - M);
-        a += pc[d] * f;
-        L += pc[HD + 1] * f;
+        s_f[c] = f;
+        l += base[(size_t)c * FD_PART_STRIDE + HD + 1] * f;
     }
-    out[(size_t)h * HD + d] = L > 0.f ? a / L : 0.f;
+    l = warp_sum(l);
+    if (lane == 0) s_red[warp] = l;
+    __syncthreads();
+    float L = 0.f;
+#pragma unroll
+    for (int i = 0; i < 16; i++) L += s_red[i];
+    const int g = tid >> 7, d = tid & (HD - 1);
+    float a = 0.f;
+#pragma unroll 8
+    for (int c = g; c < n_chunks; c += 4) a += base[(size_t)c * FD_PART_STRIDE + d] * s_f[c];
+    s_part[g][d] = a;
+    __syncthreads();
+    if (g == 0) {
+        const float t = (s_part[0][d] + s_part[1][d]) + (s_part[2][d] + s_part[3][d]);
+        out[(size_t)h * HD + d] = L > 0.f ? t / L : 0.f;
+    }
 }
 
 // Chunk merge fused with the Q8_K quantisation of the attention output (the o_proj input):
 // grid = num_heads / 2, 256 threads; two heads are exactly one 256-element Q8_K block.
 // The 128 threads of a head first agree on the global max and the per-chunk rescale factors
 // (kept in shared memory), then each sums its output dimension over the chunks.
-constexpr int FD_MAX_CHUNKS = 1024;
 RNB_GLOBAL void __launch_bounds__(2 * HD)
 flash_decode_reduce_q8k_kernel(const float *__restrict__ partials, int n_chunks, int num_heads,
                                float *__restrict__ out, uint8_t *__restrict__ xq_out) {

@@ -4,6 +4,7 @@
 #include "gemv.cuh"
 #include "gemv_stream.cuh"
 #include "gemv_pair.cuh"
+#include "gemv_ksplit.cuh"
 #include "moe.cuh"
 #include "prefill_gemm.cuh"
 #include "q8k.cuh"
@@ -146,10 +147,43 @@ inline const PairTuning &pair_tuning() {
     }();
     return t;
 }
+// K-split kernel: single static Q6_K job with long rows and few of them - the row-sharded
+// ffn_down slices of a multi-GPU run (1024 x 28672 on 8 GPUs); with 4096 rows it is faster alone
+// but not inside a decode step.  RNB_B200_KSPLIT=0 turns it off, _MIN_COLS / _MAX_ROWS move the limits.
+struct KsplitTuning {
+    int enabled, min_cols, max_rows, stages;
+};
+inline const KsplitTuning &ksplit_tuning() {
+    static const KsplitTuning t = [] {
+        auto env_int = [](const char *name, int dflt) {
+            const char *e = getenv(name);
+            return (e && *e) ? atoi(e) : dflt;
+        };
+        KsplitTuning v;
+        v.enabled = env_int("RNB_B200_KSPLIT", 1);
+        v.min_cols = env_int("RNB_B200_KSPLIT_MIN_COLS", 8192);
+        v.max_rows = env_int("RNB_B200_KSPLIT_MAX_ROWS", 2048);
+        v.stages = env_int("RNB_B200_KSPLIT_STAGES", 3);
+        if (v.stages < 1) v.stages = 1;
+        if (v.stages > GK_MAX_STAGES) v.stages = GK_MAX_STAGES;
+        return v;
+    }();
+    return t;
+}
 // Row-rich, all-Q4_K, single-part, 16-byte aligned static tables go to the two-threads-per-row
 // kernel; everything else to the eight-threads-per-row kernel.
 inline int launch_gemv_stream(cudaStream_t s, const GemvJob *jobs_host, const GemvJob *jobs_dev, int n_jobs,
                               size_t cols, int *dev_error, int dynamic_table, bool by_value) {
+    const KsplitTuning &kt = ksplit_tuning();
+    if (kt.enabled && !dynamic_table && n_jobs == 1 && jobs_host[0].type == TYPE_Q6_K && jobs_host[0].n_parts == 1 && jobs_host[0].seq <= 1 &&
+        cols % (256 * GK_CHUNK) == 0 && (int)cols >= kt.min_cols && jobs_host[0].rows <= kt.max_rows &&
+        ((((uintptr_t)jobs_host[0].parts[0].w | (uintptr_t)jobs_host[0].parts[0].x) & 15u) == 0) && gk_smem(kt.stages) <= gemv_smem_max()) {
+        const int tiles = (jobs_host[0].rows + GK_ROWS - 1) / GK_ROWS;
+        const int n_chunks = (int)(cols / (256 * GK_CHUNK));
+        const int S = kt.stages < n_chunks ? kt.stages : n_chunks;
+        RNB_CU(launch_k(gemv_ksplit_q6k_kernel, dim3(tiles), dim3(GK_THREADS), (size_t)gk_smem(S), s, jobs_host[0], (int)cols, S, dev_error));
+        return RNB_B200_OK;
+    }
     const PairTuning &pt = pair_tuning();
     bool pair = pt.enabled && !dynamic_table && n_jobs <= GS_PACK && cols % 256 == 0;
     size_t total_rows = 0;
@@ -309,7 +343,7 @@ inline int launch_flash_decode(cudaStream_t s, const float *q, const uint16_t *k
                                float *out, int *dev_error = nullptr) {
     RNB_TRY(launch_flash_decode_partials(s, q, k, v, kv_len_dev, kv_len_host, num_heads, num_kv_heads, scale, partials,
                                          n_chunks, dev_error));
-    RNB_CU(launch_k(flash_decode_reduce_kernel, dim3(num_heads), dim3(HD), 0, s,
+    RNB_CU(launch_k(flash_decode_reduce_kernel, dim3(num_heads), dim3(4 * HD), 0, s,
                     (const float *)partials, n_chunks, out));
     return RNB_B200_OK;
 }

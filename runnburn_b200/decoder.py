@@ -111,6 +111,20 @@ class Decoder:
         buf = (C.c_uint8 * len(blob)).from_buffer_copy(blob)
         check(load().rnb_b200_decoder_attach_peers(self._h, buf))
 
+    def prefill(self, tokens, pos0: int = 0, timed: bool = False):
+        """Runs the prompt through the tensor-core prefill path, appends its K/V rows and returns the
+        greedy next token (and the device milliseconds when `timed`)."""
+        t = np.ascontiguousarray(np.asarray(tokens, dtype=np.uint32))
+        nxt, ms = C.c_uint32(), C.c_float()
+        check(load().rnb_b200_decoder_prefill(self._h, t.ctypes.data_as(C.c_void_p), int(t.size), int(pos0), C.byref(nxt),
+                                              C.byref(ms) if timed else None))
+        return (nxt.value, ms.value) if timed else nxt.value
+
+    def read_logits(self) -> np.ndarray:
+        out = np.empty(self.cfg.vocab // self.cfg.world_size, np.float32)
+        check(load().rnb_b200_decoder_read_logits(self._h, out.ctypes.data_as(C.c_void_p), out.size))
+        return out
+
     def step(self, token: int, pos: int, want_logits: bool = False):
         nxt = C.c_uint32()
         logits = np.empty(self.cfg.vocab, np.float32) if want_logits else None

@@ -145,3 +145,36 @@ def test_step_dev_chain_matches_host_steps():
     a.close()
     b.close()
     c.close()
+
+
+def test_prefill_matches_token_by_token_decode():
+    """Tensor-core prefill (bf16 matmuls) against the oracle's token-by-token decode: logits of
+    the last prompt token within bf16's reach, K/V rows close, and decode continues from the
+    appended cache."""
+    desc = llama_description(seed=2, n_layer=3, hidden=512, n_head=4, n_kv_head=2, n_ff=1024, vocab=2048)
+    rng = np.random.default_rng(4)
+    prompt = rng.integers(0, 2048, 70).tolist()
+    dec, ref = _run(desc, prompt, 0, 128)
+    lc = None
+    for pos, t in enumerate(prompt):
+        lc = ref.decode(t, pos)
+    nxt = dec.prefill(prompt, 0)
+    lg = dec.read_logits()
+    assert max_err_vs_norm(lg, lc) <= 3e-2          # three layers of bf16-rounded matmuls
+    assert nxt == orc.argmax_last(lg)
+    for layer in range(3):
+        kg, vg = dec.read_kv(layer, len(prompt))
+        kc, vc = ref.kv_cache(layer, len(prompt))
+        for g, c in ((kg, kc), (vg, vc)):
+            gf, cf = g.view(np.float16).astype(np.float32), c.view(np.float16).astype(np.float32)
+            assert max_err_vs_norm(gf, cf) <= 3e-2
+    # layer 0's K/V come from one matmul of the embedding rows: tight
+    kg, _ = dec.read_kv(0, len(prompt))
+    kc, _ = ref.kv_cache(0, len(prompt))
+    assert max_err_vs_norm(kg.view(np.float16).astype(np.float32), kc.view(np.float16).astype(np.float32)) <= 1e-2
+    # decode goes on from the cache the prefill wrote
+    tok2, lg2 = dec.step(nxt, len(prompt), want_logits=True)
+    lc2 = ref.decode(nxt, len(prompt))
+    assert max_err_vs_norm(lg2, lc2) <= 3e-2
+    dec.close()
+    ref.close()
