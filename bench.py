@@ -414,7 +414,7 @@ def run_gpu(args, shape, ctx, name, rank, world, local_rank):
             _, pms = dec.prefill(ids, 0, timed=True)
             out["prefill"] = {"tokens": int(n_tok), "ms": pms, "tok_per_s": n_tok / (pms / 1000.0),
                               "what": "embed, 32 x (RMSNorm, q/k/v matmul, RoPE + f16 KV append, causal attention, o_proj, RMSNorm, gate/up, SiLU*up, down), "
-                                      "final norm + LM head + argmax of the last token; matmuls on tcgen05 (bf16), attention on CUDA cores (fp32)"}
+                                      "final norm + LM head + argmax of the last token; matmuls on tcgen05 (bf16), causal attention on mma.sync tensor cores (split-f16 operands, fp32 accumulate)"}
         except Exception as e:   # a secondary figure must not lose the headline line
             out["prefill"] = {"error": str(e)[:200]}
     dec.close()

@@ -279,11 +279,15 @@ __device__ __forceinline__ void split_f16x2(float x, float y, uint32_t &hi, uint
     lo = *reinterpret_cast<const uint32_t *>(&l);
 }
 
-RNB_GLOBAL void __launch_bounds__(FDM_THREADS, 4)
-flash_decode_mma_kernel(const float *__restrict__ q, const uint16_t *__restrict__ k,
-                        const uint16_t *__restrict__ v, const int *__restrict__ kv_len_dev,
-                        int kv_len_host, int num_heads, int num_kv_heads, float scale,
-                        float *__restrict__ partials, int *__restrict__ err_flag) {
+// PREFILL = false: decode, grid (kv heads, chunks), one query, partial records out.
+// PREFILL = true: causal prefill, grid (kv heads, query blocks); the 8 MMA columns are
+// (8 / group) consecutive queries x the group's heads, query i sees positions
+// 0 .. kv_len - seq_len + i, and the normalised result is written straight to `out`
+// ([seq][head][128]); no chunking, the CTA walks all visible positions.
+template <bool PREFILL>
+__device__ __forceinline__ void fdm_body(const float *__restrict__ q, const uint16_t *__restrict__ k, const uint16_t *__restrict__ v,
+                                         const int *__restrict__ kv_len_dev, int kv_len_host, int seq_len, int num_heads, int num_kv_heads,
+                                         float scale, float *__restrict__ partials, float *__restrict__ out, int *__restrict__ err_flag) {
     pdl_launch_dependents();
     pdl_wait();
     __shared__ __align__(128) uint8_t s_kv[FDM_KV_BYTES];   // K rows then V rows; merge scratch later
@@ -294,10 +298,19 @@ flash_decode_mma_kernel(const float *__restrict__ q, const uint16_t *__restrict_
     const int g = lane >> 2, t = lane & 3;
     const int kv_len = kv_len_dev ? *kv_len_dev + kv_len_host : kv_len_host;
     const int n_chunks = gridDim.y, chunk = blockIdx.y, kv_h = blockIdx.x;
-    int chunk_len = (kv_len + n_chunks - 1) / n_chunks;
-    chunk_len = (chunk_len + 15) & ~15;
-    const int p_begin = min(kv_len, chunk * chunk_len), p_end = min(kv_len, p_begin + chunk_len);
     const int group = num_heads / num_kv_heads;
+    const int qpc = PREFILL ? (group >= 8 ? 1 : 8 / group) : 1;   // queries per CTA
+    const int i0 = PREFILL ? (int)blockIdx.y * qpc : 0;
+    int p_begin, p_end;
+    if (PREFILL) {
+        p_begin = 0;
+        p_end = max(0, min(kv_len, kv_len - seq_len + min(i0 + qpc, seq_len)));   // what the CTA's last query sees
+    } else {
+        int chunk_len = (kv_len + n_chunks - 1) / n_chunks;
+        chunk_len = (chunk_len + 15) & ~15;
+        p_begin = min(kv_len, chunk * chunk_len);
+        p_end = min(kv_len, p_begin + chunk_len);
+    }
     const size_t kv_dim = (size_t)num_kv_heads * HD;
     uint8_t *s_k = s_kv, *s_v = s_kv + FDM_SUPER * FDM_ROW;
     if (tid < FDM_SUPER / 16) mbar_init(&s_bar[tid], 32);   // 16 K-row + 16 V-row issuers per block
@@ -308,17 +321,27 @@ flash_decode_mma_kernel(const float *__restrict__ q, const uint16_t *__restrict_
 
     for (int g0 = 0; g0 < group; g0 += 8) {
         const int heads_here = min(8, group - g0), head0 = kv_h * group + g0;
-        // query B fragments: column (head) g, dims ks*16 + {2t, 2t+1} and + 8
+        const int cols = PREFILL ? heads_here * qpc : heads_here;   // live MMA columns: (query, head) pairs
+        // column c -> (query c / heads_here, head c % heads_here); this thread's B-fragment column is g
+        const int my_qi = g / heads_here, my_hh = g % heads_here;
+        const bool col_live = g < cols && (!PREFILL || i0 + my_qi < seq_len);
+        // query B fragments: column g, dims ks*16 + {2t, 2t+1} and + 8
         uint32_t qh[8][2], ql[8][2];
+        const float *qrow = q + ((size_t)(PREFILL ? i0 + my_qi : 0) * num_heads + head0 + my_hh) * HD;
 #pragma unroll
         for (int ks = 0; ks < 8; ks++)
 #pragma unroll
             for (int hf = 0; hf < 2; hf++) {
                 float2 qv = make_float2(0.f, 0.f);
-                if (g < heads_here)
-                    qv = *reinterpret_cast<const float2 *>(q + (size_t)(head0 + g) * HD + ks * 16 + hf * 8 + 2 * t);
+                if (col_live) qv = *reinterpret_cast<const float2 *>(qrow + ks * 16 + hf * 8 + 2 * t);
                 split_f16x2(qv.x * scale, qv.y * scale, qh[ks][hf], ql[ks][hf]);
             }
+        // causal limit of the two columns this thread owns in the score tile (2t, 2t+1)
+        int lim[2] = {kv_len, kv_len};
+        if (PREFILL) {
+#pragma unroll
+            for (int e = 0; e < 2; e++) lim[e] = kv_len - seq_len + i0 + (2 * t + e) / heads_here + 1;
+        }
         float o[8][4];   // O^T tile mt: (dim 16mt+g | +8, head 2t | 2t+1)
 #pragma unroll
         for (int n = 0; n < 8; n++) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
@@ -366,6 +389,14 @@ flash_decode_mma_kernel(const float *__restrict__ q, const uint16_t *__restrict_
                     }
                     if (g >= rows) sc[0] = sc[1] = -INFINITY;
                     if (g + 8 >= rows) sc[2] = sc[3] = -INFINITY;
+                    if (PREFILL) {
+                        const int pa = sp + 16 * warp + g;   // absolute position of rows g and g + 8
+#pragma unroll
+                        for (int e = 0; e < 2; e++) {
+                            if (pa >= lim[e]) sc[e] = -INFINITY;
+                            if (pa + 8 >= lim[e]) sc[2 + e] = -INFINITY;
+                        }
+                    }
                     // ---- online softmax per head (column): max over the 16 positions ----
                     float corr[2], pr[4];
 #pragma unroll
@@ -374,7 +405,7 @@ flash_decode_mma_kernel(const float *__restrict__ q, const uint16_t *__restrict_
                         mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
                         mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
                         mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
-                        const float m_new = fmaxf(m_run[e], mx);
+                        const float m_new = fmaxf(m_run[e], mx);   // stays -inf while everything is masked
                         corr[e] = m_run[e] == -INFINITY ? 0.f : expf(m_run[e] - m_new);
                         pr[e] = sc[e] == -INFINITY ? 0.f : expf(sc[e] - m_new);
                         pr[2 + e] = sc[2 + e] == -INFINITY ? 0.f : expf(sc[2 + e] - m_new);
@@ -432,7 +463,7 @@ flash_decode_mma_kernel(const float *__restrict__ q, const uint16_t *__restrict_
             }
         }
         __syncthreads();
-        for (int hh = 0; hh < heads_here; hh++) {
+        for (int hh = 0; hh < cols; hh++) {
             const int d = tid;
             float M = -INFINITY;
 #pragma unroll
@@ -445,16 +476,35 @@ flash_decode_mma_kernel(const float *__restrict__ q, const uint16_t *__restrict_
                 a += s_acc[(size_t)(w * 8 + hh) * FDM_ACC_STRIDE + d] * f;
                 L += s_ml[(w * 8 + hh) * 2 + 1] * f;
             }
-            float *out = partials + ((size_t)(head0 + hh) * n_chunks + chunk) * FD_PART_STRIDE;
-            out[d] = a;
-            if (d == 0) {
-                out[HD] = M;
-                out[HD + 1] = L;
+            if (PREFILL) {
+                const int qi = hh / heads_here;
+                if (i0 + qi < seq_len) out[((size_t)(i0 + qi) * num_heads + head0 + hh % heads_here) * HD + d] = L > 0.f ? a / L : 0.f;
+            } else {
+                float *rec = partials + ((size_t)(head0 + hh) * n_chunks + chunk) * FD_PART_STRIDE;
+                rec[d] = a;
+                if (d == 0) {
+                    rec[HD] = M;
+                    rec[HD + 1] = L;
+                }
             }
         }
         // the next head pass overwrites s_kv through the async proxy after these generic reads
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
+}
+
+RNB_GLOBAL void __launch_bounds__(FDM_THREADS, 4)
+flash_decode_mma_kernel(const float *__restrict__ q, const uint16_t *__restrict__ k,
+                        const uint16_t *__restrict__ v, const int *__restrict__ kv_len_dev,
+                        int kv_len_host, int num_heads, int num_kv_heads, float scale,
+                        float *__restrict__ partials, int *__restrict__ err_flag) {
+    fdm_body<false>(q, k, v, kv_len_dev, kv_len_host, 1, num_heads, num_kv_heads, scale, partials, nullptr, err_flag);
+}
+// Causal prefill attention on the same machinery: grid (kv heads, ceil(seq / queries per CTA)).
+RNB_GLOBAL void __launch_bounds__(FDM_THREADS, 4)
+prefill_attention_mma_kernel(const float *__restrict__ q, const uint16_t *__restrict__ k, const uint16_t *__restrict__ v, int seq_len,
+                             int kv_len, int num_heads, int num_kv_heads, float scale, float *__restrict__ out, int *__restrict__ err_flag) {
+    fdm_body<true>(q, k, v, nullptr, kv_len, seq_len, num_heads, num_kv_heads, scale, nullptr, out, err_flag);
 }
 
 // Chunk merge: grid = num_heads, 512 threads.  The threads first agree on the global max and

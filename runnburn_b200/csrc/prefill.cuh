@@ -42,14 +42,26 @@ inline int launch_prefill_attention_f32kv(cudaStream_t s, const float *q, const 
                               num_heads, num_kv_heads, scale, out));
     return RNB_B200_OK;
 }
+// f16 caches on 16-byte boundaries take the tensor-core kernel, anything else the CUDA-core one.
 inline int launch_prefill_attention_f16kv(cudaStream_t s, const float *q, const uint16_t *k,
                                           const uint16_t *v, int seq_len, int kv_len,
                                           int num_heads, int num_kv_heads, float scale,
-                                          float *out) {
+                                          float *out, int *dev_error = nullptr) {
+    const int group = num_heads / num_kv_heads;
+    static const bool simt = [] {
+        const char *e = getenv("RNB_B200_FD_SIMT");
+        return e && *e == '1';
+    }();
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(seq_len, num_kv_heads);
-    cfg.blockDim = dim3(FD_THREADS);
     cfg.stream = s;
+    cfg.blockDim = dim3(FD_THREADS);
+    if (!simt && (((uintptr_t)k | (uintptr_t)v) & 15) == 0) {
+        const int qpc = group >= 8 ? 1 : 8 / group;
+        cfg.gridDim = dim3(num_kv_heads, (seq_len + qpc - 1) / qpc);
+        RNB_CU(cudaLaunchKernelEx(&cfg, prefill_attention_mma_kernel, q, k, v, seq_len, kv_len, num_heads, num_kv_heads, scale, out, dev_error));
+        return RNB_B200_OK;
+    }
+    cfg.gridDim = dim3(seq_len, num_kv_heads);
     RNB_CU(cudaLaunchKernelEx(&cfg, prefill_attention_kernel<uint16_t>, q, k, v, seq_len, kv_len,
                               num_heads, num_kv_heads, scale, out));
     return RNB_B200_OK;

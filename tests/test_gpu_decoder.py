@@ -147,13 +147,14 @@ def test_step_dev_chain_matches_host_steps():
     c.close()
 
 
-def test_prefill_matches_token_by_token_decode():
+@pytest.mark.parametrize("n_head,n_kv_head,n_prompt", [(4, 2, 70), (8, 1, 37), (2, 2, 81), (4, 1, 16)])
+def test_prefill_matches_token_by_token_decode(n_head, n_kv_head, n_prompt):
     """Tensor-core prefill (bf16 matmuls) against the oracle's token-by-token decode: logits of
     the last prompt token within bf16's reach, K/V rows close, and decode continues from the
     appended cache."""
-    desc = llama_description(seed=2, n_layer=3, hidden=512, n_head=4, n_kv_head=2, n_ff=1024, vocab=2048)
+    desc = llama_description(seed=2, n_layer=3, hidden=512, n_head=n_head, n_kv_head=n_kv_head, n_ff=1024, vocab=2048)
     rng = np.random.default_rng(4)
-    prompt = rng.integers(0, 2048, 70).tolist()
+    prompt = rng.integers(0, 2048, n_prompt).tolist()
     dec, ref = _run(desc, prompt, 0, 128)
     lc = None
     for pos, t in enumerate(prompt):
