@@ -37,7 +37,15 @@ struct GemvJob {
     int seq;          // tokens sharing the weight tile (1 for decode); outputs are seq-major
     size_t x_stride;  // bytes between consecutive tokens' activations
     GemvPart parts[GEMV_MAX_PARTS];
+    // Optional epilogue of the batch-1 streaming kernel (decode q/k/v): rotate adjacent row pairs
+    // with the cos/sin row of the current position and/or write the row as f16 into a KV cache.
+    int epi;                  // GEMV_EPI_*
+    int epi_kv_dim;           // elements per cache position
+    const float *epi_rope;    // [pos][cos 64 | sin 64]
+    const int *epi_pos;       // device scalar: position of this token
+    uint16_t *epi_cache;      // K or V cache of the layer
 };
+constexpr int GEMV_EPI_NONE = 0, GEMV_EPI_ROPE_F32 = 1, GEMV_EPI_ROPE_F16_CACHE = 2, GEMV_EPI_F16_CACHE = 3;
 
 __device__ __forceinline__ uint32_t lds32(uint32_t addr) {
     uint32_t v;

@@ -274,10 +274,30 @@ __device__ __forceinline__ void gr_run(const GemvJob *__restrict__ job, const Gs
         if (++cn == n_chunks) cn = 0, ++pn;
         if (++slot_idx == S) slot_idx = 0, parity ^= 1;
     }
-    if (live && t == 0) {
-        const size_t o = (size_t)row0 + r;
-        job->y[o] = job->residual ? __fadd_rn(job->residual[o], acc_total) : acc_total;
+    const size_t o = (size_t)row0 + r;
+    float val = acc_total;
+    if (live && t == 0 && job->residual) val = __fadd_rn(job->residual[o], acc_total);
+    const int epi = job->epi;
+    if (epi == GEMV_EPI_NONE) {
+        if (live && t == 0) job->y[o] = val;
+        return;
     }
+    // q/k/v epilogue: what rope_kv_append_kernel does, on the rows this CTA has just produced.
+    // Rows 2i and 2i+1 of a head are a rotation pair (adjacent-pair RoPE); they sit in
+    // neighbouring 8-lane groups of one warp (rows per CTA is a multiple of 4, row0 is even).
+    const float other = __shfl_xor_sync(0xffffffffu, val, 8);
+    if (!(live && t == 0)) return;
+    const int pos = *job->epi_pos;
+    float outv = val;
+    if (epi == GEMV_EPI_ROPE_F32 || epi == GEMV_EPI_ROPE_F16_CACHE) {
+        const int j = (int)(o & (size_t)127), i = j >> 1;
+        const float *cs = job->epi_rope + (size_t)pos * 128;
+        const float c = cs[i], sn = cs[64 + i];
+        const float x0 = (j & 1) ? other : val, x1 = (j & 1) ? val : other;
+        outv = (j & 1) ? __fadd_rn(__fmul_rn(x0, sn), __fmul_rn(x1, c)) : __fsub_rn(__fmul_rn(x0, c), __fmul_rn(x1, sn));
+    }
+    if (epi == GEMV_EPI_ROPE_F32) job->y[o] = outv;
+    else job->epi_cache[(size_t)pos * job->epi_kv_dim + o] = __half_as_ushort(__float2half_rn(outv));
 }
 
 __device__ __forceinline__ void gemv_stream_body(const GemvJob *__restrict__ jobs, int n_jobs, const GsParams &P,

@@ -175,7 +175,7 @@ inline const KsplitTuning &ksplit_tuning() {
 inline int launch_gemv_stream(cudaStream_t s, const GemvJob *jobs_host, const GemvJob *jobs_dev, int n_jobs,
                               size_t cols, int *dev_error, int dynamic_table, bool by_value) {
     const KsplitTuning &kt = ksplit_tuning();
-    if (kt.enabled && !dynamic_table && n_jobs == 1 && jobs_host[0].type == TYPE_Q6_K && jobs_host[0].n_parts == 1 && jobs_host[0].seq <= 1 &&
+    if (kt.enabled && !dynamic_table && n_jobs == 1 && jobs_host[0].type == TYPE_Q6_K && jobs_host[0].n_parts == 1 && jobs_host[0].seq <= 1 && jobs_host[0].epi == GEMV_EPI_NONE &&
         cols % (256 * GK_CHUNK) == 0 && (int)cols >= kt.min_cols && jobs_host[0].rows <= kt.max_rows &&
         ((((uintptr_t)jobs_host[0].parts[0].w | (uintptr_t)jobs_host[0].parts[0].x) & 15u) == 0) && gk_smem(kt.stages) <= gemv_smem_max()) {
         const int tiles = (jobs_host[0].rows + GK_ROWS - 1) / GK_ROWS;
@@ -189,7 +189,7 @@ inline int launch_gemv_stream(cudaStream_t s, const GemvJob *jobs_host, const Ge
     size_t total_rows = 0;
     for (int i = 0; i < n_jobs && pair; i++) {
         const GemvJob &j = jobs_host[i];
-        pair = j.type == TYPE_Q4_K && j.n_parts == 1 && j.seq <= 1 && ((((uintptr_t)j.parts[0].w | (uintptr_t)j.parts[0].x) & 15u) == 0);
+        pair = j.type == TYPE_Q4_K && j.n_parts == 1 && j.seq <= 1 && j.epi == GEMV_EPI_NONE && ((((uintptr_t)j.parts[0].w | (uintptr_t)j.parts[0].x) & 15u) == 0);
         total_rows += (size_t)j.rows;
     }
     if (!pair || total_rows < (size_t)pt.min_rows)

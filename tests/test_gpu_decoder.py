@@ -65,7 +65,7 @@ def test_llama_greedy_64_steps_identical(tmp_path):
         if layer == 0:
             assert np.mean(kg == kc) > 0.999 and np.mean(vg == vc) > 0.999
     st = dec.stats()
-    assert st["launches_per_step"] == 1 + 3 * 10 + 4
+    assert st["launches_per_step"] == 1 + 3 * 9 + 4   # RoPE and the KV append ride in the q/k/v matvec
     dec.close()
     ref.close()
 
