@@ -12,6 +12,7 @@
 #pragma once
 #include "gemv.cuh"
 #include "gemv_stream.cuh"
+#include "q8k.cuh"
 
 namespace rnb {
 
@@ -26,6 +27,18 @@ struct GpParams {
     uint32_t row_stride;  // 16-byte multiple, = 32 or 96 mod 128: the 16-byte loads of a quarter-warp hit 8 bank groups
     uint32_t act_off;     // activation slice inside a stage: qs | bsum16 | d
     uint32_t slot_bytes;
+};
+
+// Optional tail for a gate + up launch: the CTA that completes a 256-row block of both vectors
+// (16 gate tiles + 16 up tiles) computes silu(gate) * up for the block and quantises it to Q8_K -
+// the work of silu_mul_q8k_kernel, spread over the blocks as they finish, without a launch.
+// counters[block] is zero before the launch and re-armed by the block's last CTA.
+struct GpTail {
+    int kind;            // 0 = none, 1 = SiLU * up + Q8_K
+    int n;               // length of the gate / up vectors (multiple of 256)
+    const float *gate, *up;
+    uint8_t *xq_out;     // Q8K-dev layout of the n-vector
+    int *counters;       // n / 256 ints
 };
 
 struct Q4kPairAcc {
@@ -75,7 +88,8 @@ __device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
 
 // grid = tiles of 16 rows, 32 threads.  Operands must be 16-byte aligned (the host checks).
 RNB_GLOBAL void __launch_bounds__(32)
-gemv_pair_q4k_kernel(const __grid_constant__ GemvJobPack jobs, int n_jobs, const GpParams P, int *__restrict__ dev_error) {
+gemv_pair_q4k_kernel(const __grid_constant__ GemvJobPack jobs, int n_jobs, const GpParams P, int *__restrict__ dev_error,
+                     const __grid_constant__ GpTail tail) {
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ __align__(8) uint64_t full[GP_MAX_STAGES];
     const int lane = threadIdx.x, r = lane >> 1, h = lane & 1;
@@ -167,6 +181,29 @@ gemv_pair_q4k_kernel(const __grid_constant__ GemvJobPack jobs, int n_jobs, const
     if (r < nrows && h == 0) {
         const size_t o = (size_t)row0 + r;
         job.y[o] = job.residual ? __fadd_rn(job.residual[o], dot) : dot;
+    }
+    if (tail.kind == 1) {
+        const int blk = row0 >> 8;
+        __threadfence();   // this tile's 16 results are visible device-wide before the tile is counted
+        __syncwarp();
+        int last = 0;
+        if (lane == 0) last = atomicAdd(&tail.counters[blk], 1) == n_jobs * (256 / GP_ROWS) - 1;
+        last = __shfl_sync(0xffffffffu, last, 0);
+        if (!last) return;
+        __threadfence();
+        const size_t off = (size_t)blk * 256 + lane * 8;
+        const float4 g0 = __ldcg(reinterpret_cast<const float4 *>(tail.gate + off)), g1 = __ldcg(reinterpret_cast<const float4 *>(tail.gate + off + 4));
+        const float4 u0 = __ldcg(reinterpret_cast<const float4 *>(tail.up + off)), u1 = __ldcg(reinterpret_cast<const float4 *>(tail.up + off + 4));
+        const float gv[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w}, uv[8] = {u0.x, u0.y, u0.z, u0.w, u1.x, u1.y, u1.z, u1.w};
+        float v[8];
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            const float e = (float)exp((double)(-gv[j]));   // as silu_mul_q8k_kernel: exp in double, rounded once
+            v[j] = __fmul_rn(__fdiv_rn(gv[j], __fadd_rn(1.0f, e)), uv[j]);
+        }
+        Q8kDevView dv = q8k_dev_view(tail.xq_out, tail.n);
+        q8k_quantize_block_warp(v, lane, dv.qs + blk * 256, dv.d + blk, dv.bsum16 + blk * 16, nullptr);
+        if (lane == 0) tail.counters[blk] = 0;
     }
 }
 

@@ -173,7 +173,8 @@ inline const KsplitTuning &ksplit_tuning() {
 // Row-rich, all-Q4_K, single-part, 16-byte aligned static tables go to the two-threads-per-row
 // kernel; everything else to the eight-threads-per-row kernel.
 inline int launch_gemv_stream(cudaStream_t s, const GemvJob *jobs_host, const GemvJob *jobs_dev, int n_jobs,
-                              size_t cols, int *dev_error, int dynamic_table, bool by_value) {
+                              size_t cols, int *dev_error, int dynamic_table, bool by_value, const GpTail *tail = nullptr,
+                              bool *tail_done = nullptr) {
     const KsplitTuning &kt = ksplit_tuning();
     if (kt.enabled && !dynamic_table && n_jobs == 1 && jobs_host[0].type == TYPE_Q6_K && jobs_host[0].n_parts == 1 && jobs_host[0].seq <= 1 && jobs_host[0].epi == GEMV_EPI_NONE &&
         cols % (256 * GK_CHUNK) == 0 && (int)cols >= kt.min_cols && jobs_host[0].rows <= kt.max_rows &&
@@ -215,17 +216,25 @@ inline int launch_gemv_stream(cudaStream_t s, const GemvJob *jobs_host, const Ge
     P.slot_bytes = (P.act_off + (uint32_t)P.chunk * 288u + 32u + 127u) & ~127u;
     const size_t smem = (size_t)P.n_stages * P.slot_bytes;
     if (smem > gemv_smem_max()) return launch_gemv_stream_rows(s, jobs_host, jobs_dev, n_jobs, cols, dev_error, dynamic_table, by_value);
-    RNB_CU(launch_k(gemv_pair_q4k_kernel, dim3(tiles), dim3(32), smem, s, pack, n_jobs, P, dev_error));
+    GpTail t;
+    memset(&t, 0, sizeof(t));
+    // the tail needs whole 256-row blocks of both vectors in this launch
+    if (tail && tail->kind == 1 && n_jobs == 2 && jobs_host[0].rows == jobs_host[1].rows && jobs_host[0].rows % 256 == 0 && jobs_host[0].rows == tail->n) {
+        t = *tail;
+        if (tail_done) *tail_done = true;
+    }
+    RNB_CU(launch_k(gemv_pair_q4k_kernel, dim3(tiles), dim3(32), smem, s, pack, n_jobs, P, dev_error, t));
     return RNB_B200_OK;
 }
 
 // Launch a table of jobs that all share `cols`.  jobs_host is used to size the launch;
 // jobs_dev is the same table in device memory.
 inline int launch_gemv_jobs(cudaStream_t s, const GemvJob *jobs_host, const GemvJob *jobs_dev,
-                            int n_jobs, size_t cols, int *dev_error, int dynamic_table = 0) {
+                            int n_jobs, size_t cols, int *dev_error, int dynamic_table = 0, const GpTail *tail = nullptr,
+                            bool *tail_done = nullptr) {
     RNB_TRY(gemv_kernel_setup());
     if (gemv_use_stream(jobs_host[0].type, jobs_host[0].seq, cols))
-        return launch_gemv_stream(s, jobs_host, jobs_dev, n_jobs, cols, dev_error, dynamic_table, false);
+        return launch_gemv_stream(s, jobs_host, jobs_dev, n_jobs, cols, dev_error, dynamic_table, false, tail, tail_done);
     int tiles = 0, max_parts = 1;
     uint32_t stride = 0;
     for (int i = 0; i < n_jobs; i++) {

@@ -179,3 +179,19 @@ def test_prefill_matches_token_by_token_decode(n_head, n_kv_head, n_prompt):
     assert max_err_vs_norm(lg2, lc2) <= 3e-2
     dec.close()
     ref.close()
+
+
+def test_llama_wide_ffn_takes_the_fused_gate_up_path():
+    """n_ff = 8192: gate + up are 16384 rows, so the launch goes to the two-threads-per-row kernel and
+    SiLU * up + Q8_K run in its per-block tail; ids must still equal the oracle's."""
+    desc = llama_description(seed=9, n_layer=2, hidden=512, n_head=4, n_kv_head=2, n_ff=8192, vocab=2048)
+    rng = np.random.default_rng(3)
+    prompt = rng.integers(0, 2048, 12).tolist()
+    dec, ref = _run(desc, prompt, 32, 64)
+    gpu_ids, cpu_ids, margins, errs = _greedy(dec, ref, prompt, 32)
+    assert gpu_ids == cpu_ids
+    assert max(errs) <= 1e-3
+    st = dec.stats()
+    assert st["launches_per_step"] == 1 + 2 * 8 + 4   # per layer: norm, qkv, attention, merge, o, norm, gate/up, down
+    dec.close()
+    ref.close()
