@@ -401,7 +401,7 @@ def run_gpu(args, shape, ctx, name, rank, world, local_rank):
         out["roofline"] = {"kernel": "gemv_stream_kernel", "bound": "hbm", "achieved": ach, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                            "frac": ach / peaks["hbm_gbs"], "frac_of_8TBs_nominal": ach / 8000.0, "peak_source": peaks["source"],
                            # DRAM read+write bytes per launch: the ncu capture of the five matvec shapes gave
-                           # 574.6 MB of traffic for 570.6 MB of algorithmic bytes (profiles/gemv_stream_kernel_*.md)
+                           # 574.6 MB of traffic for 570.6 MB of algorithmic bytes (summary under profiles/)
                            "traffic": per_launch_bytes * DRAM_TRAFFIC_OVER_ALGORITHMIC,
                            "traffic_source": "ncu dram__bytes_read.sum+dram__bytes_write.sum of the five layer shapes, scaled by algorithmic bytes",
                            "launches_per_step": mv["launches_per_iter"],
