@@ -11,8 +11,8 @@
 // super-block) per pipeline stage; a stage holds the token tile (256 x 64 bf16) and the weight
 // tile (256 x 64 bf16), both K-major in the 128-byte swizzle the MMA descriptors expect:
 //   byte offset of (row r, 16-byte chunk c) = (r / 8) * 1024 + (r % 8) * 128 + ((c ^ (r % 8)) * 16).
-// Warp roles: 0-3 dequantise weights (one thread = two rows), 4-7 bring the token tile in with
-// cp.async, 8 allocates tensor memory and issues the MMAs (eight per stage: 2 token halves x 4
+// Warp roles: 0-7 produce a stage (thread t dequantises weight row t and copies 8 chunks of the
+// token tile with cp.async), 8 allocates tensor memory and issues the MMAs (eight per stage: 2 token halves x 4
 // K-steps of 16); afterwards warps 0-7 read the accumulators back (tcgen05.ld, one TMEM lane
 // quarter per warp) and store f32 rows.  Every wait is bounded; a timeout sets the error flag
 // and all roles still meet at the final barrier, where the tensor memory is freed.
@@ -74,6 +74,10 @@ __device__ __forceinline__ void pg_tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) 
 __device__ __forceinline__ float pg_byte_to_f32(uint32_t word, int byte) {
     return __uint_as_float(__byte_perm(word, 0x4b000000u, 0x7650 + byte) ) - 8388608.0f;
 }
+// same, minus 32 (Q6_K's offset): 2^23 + q - (2^23 + 32) is exact
+__device__ __forceinline__ float pg_byte_to_f32_m32(uint32_t word, int byte) {
+    return __uint_as_float(__byte_perm(word, 0x4b000000u, 0x7650 + byte)) - 8388640.0f;
+}
 __device__ __forceinline__ uint32_t pg_pack_bf16(float lo, float hi) {
     const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<const uint32_t *>(&v);
@@ -89,7 +93,9 @@ __device__ __forceinline__ void pg_load_q4(PgRawQ4 &r, const uint8_t *blk, int g
     r.q0 = ldg_nc_u4(blk + 16 + 32 * g);
     r.q1 = ldg_nc_u4(blk + 32 + 32 * g);
 }
-// y = d*sc*q - dmin*m as (d*sc)*q - (dmin*m): crates/rnb-cpu/src/quantize/dequant.rs:353-381
+// y = (d*sc)*q - (dmin*m) (crates/rnb-cpu/src/quantize/dequant.rs:353-381), evaluated with one fused
+// multiply-add per element: the f32 value can differ from the two-rounding form in its last bit,
+// which survives the rounding to bf16 only next to a tie.
 __device__ __forceinline__ void pg_dequant_q4(const PgRawQ4 &r, int g, uint8_t *row_base, int rr) {
     const float d = f16_bits_to_f32(r.hdr.x & 0xffffu), dmin = f16_bits_to_f32(r.hdr.x >> 16);
     const uint32_t sc03 = r.hdr.y & 0x3f3f3f3fu, mn03 = r.hdr.z & 0x3f3f3f3fu;
@@ -98,7 +104,7 @@ __device__ __forceinline__ void pg_dequant_q4(const PgRawQ4 &r, int g, uint8_t *
     const uint32_t scw = g < 2 ? sc03 : sc47, mnw = g < 2 ? mn03 : mn47;
     const int sh = 16 * (g & 1);
     const float d_lo = __fmul_rn(d, (float)((scw >> sh) & 0xffu)), d_hi = __fmul_rn(d, (float)((scw >> (sh + 8)) & 0xffu));
-    const float m_lo = __fmul_rn(dmin, (float)((mnw >> sh) & 0xffu)), m_hi = __fmul_rn(dmin, (float)((mnw >> (sh + 8)) & 0xffu));
+    const float nm_lo = -__fmul_rn(dmin, (float)((mnw >> sh) & 0xffu)), nm_hi = -__fmul_rn(dmin, (float)((mnw >> (sh + 8)) & 0xffu));
     const uint32_t qw[8] = {r.q0.x, r.q0.y, r.q0.z, r.q0.w, r.q1.x, r.q1.y, r.q1.z, r.q1.w};
 #pragma unroll
     for (int c = 0; c < 4; c++) {   // chunk c: low nibbles of bytes 8c..8c+7; chunk c+4: their high nibbles
@@ -106,10 +112,10 @@ __device__ __forceinline__ void pg_dequant_q4(const PgRawQ4 &r, int g, uint8_t *
 #pragma unroll
         for (int w = 0; w < 2; w++) {
             const uint32_t word = qw[2 * c + w], l4 = word & 0x0f0f0f0fu, h4 = (word >> 4) & 0x0f0f0f0fu;
-            lo[2 * w] = pg_pack_bf16(__fsub_rn(__fmul_rn(d_lo, pg_byte_to_f32(l4, 0)), m_lo), __fsub_rn(__fmul_rn(d_lo, pg_byte_to_f32(l4, 1)), m_lo));
-            lo[2 * w + 1] = pg_pack_bf16(__fsub_rn(__fmul_rn(d_lo, pg_byte_to_f32(l4, 2)), m_lo), __fsub_rn(__fmul_rn(d_lo, pg_byte_to_f32(l4, 3)), m_lo));
-            hi[2 * w] = pg_pack_bf16(__fsub_rn(__fmul_rn(d_hi, pg_byte_to_f32(h4, 0)), m_hi), __fsub_rn(__fmul_rn(d_hi, pg_byte_to_f32(h4, 1)), m_hi));
-            hi[2 * w + 1] = pg_pack_bf16(__fsub_rn(__fmul_rn(d_hi, pg_byte_to_f32(h4, 2)), m_hi), __fsub_rn(__fmul_rn(d_hi, pg_byte_to_f32(h4, 3)), m_hi));
+            lo[2 * w] = pg_pack_bf16(__fmaf_rn(d_lo, pg_byte_to_f32(l4, 0), nm_lo), __fmaf_rn(d_lo, pg_byte_to_f32(l4, 1), nm_lo));
+            lo[2 * w + 1] = pg_pack_bf16(__fmaf_rn(d_lo, pg_byte_to_f32(l4, 2), nm_lo), __fmaf_rn(d_lo, pg_byte_to_f32(l4, 3), nm_lo));
+            hi[2 * w] = pg_pack_bf16(__fmaf_rn(d_hi, pg_byte_to_f32(h4, 0), nm_hi), __fmaf_rn(d_hi, pg_byte_to_f32(h4, 1), nm_hi));
+            hi[2 * w + 1] = pg_pack_bf16(__fmaf_rn(d_hi, pg_byte_to_f32(h4, 2), nm_hi), __fmaf_rn(d_hi, pg_byte_to_f32(h4, 3), nm_hi));
         }
         *reinterpret_cast<uint4 *>(row_base + ((c ^ rr) << 4)) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
         *reinterpret_cast<uint4 *>(row_base + (((c + 4) ^ rr) << 4)) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
@@ -162,10 +168,10 @@ __device__ __forceinline__ void pg_dequant_q6(const PgRawQ6 &r, int g, uint8_t *
             const uint32_t qa = odd ? (((la >> 4) & 0x0f0f0f0fu) | (hh & 0x30303030u)) : ((la & 0x0f0f0f0fu) | ((hh << 4) & 0x30303030u));
             const uint32_t qb = odd ? (((lb >> 4) & 0x0f0f0f0fu) | ((hh >> 2) & 0x30303030u)) : ((lb & 0x0f0f0f0fu) | ((hh << 2) & 0x30303030u));
             const float sa = ds[c >> 1], sb = ds[2 + (c >> 1)];
-            o1[2 * w] = pg_pack_bf16(__fmul_rn(sa, pg_byte_to_f32(qa, 0) - 32.0f), __fmul_rn(sa, pg_byte_to_f32(qa, 1) - 32.0f));
-            o1[2 * w + 1] = pg_pack_bf16(__fmul_rn(sa, pg_byte_to_f32(qa, 2) - 32.0f), __fmul_rn(sa, pg_byte_to_f32(qa, 3) - 32.0f));
-            o2[2 * w] = pg_pack_bf16(__fmul_rn(sb, pg_byte_to_f32(qb, 0) - 32.0f), __fmul_rn(sb, pg_byte_to_f32(qb, 1) - 32.0f));
-            o2[2 * w + 1] = pg_pack_bf16(__fmul_rn(sb, pg_byte_to_f32(qb, 2) - 32.0f), __fmul_rn(sb, pg_byte_to_f32(qb, 3) - 32.0f));
+            o1[2 * w] = pg_pack_bf16(__fmul_rn(sa, pg_byte_to_f32_m32(qa, 0)), __fmul_rn(sa, pg_byte_to_f32_m32(qa, 1)));
+            o1[2 * w + 1] = pg_pack_bf16(__fmul_rn(sa, pg_byte_to_f32_m32(qa, 2)), __fmul_rn(sa, pg_byte_to_f32_m32(qa, 3)));
+            o2[2 * w] = pg_pack_bf16(__fmul_rn(sb, pg_byte_to_f32_m32(qb, 0)), __fmul_rn(sb, pg_byte_to_f32_m32(qb, 1)));
+            o2[2 * w + 1] = pg_pack_bf16(__fmul_rn(sb, pg_byte_to_f32_m32(qb, 2)), __fmul_rn(sb, pg_byte_to_f32_m32(qb, 3)));
         }
         *reinterpret_cast<uint4 *>(row_base + ((c ^ rr) << 4)) = make_uint4(o1[0], o1[1], o1[2], o1[3]);
         *reinterpret_cast<uint4 *>(row_base + (((c + 4) ^ rr) << 4)) = make_uint4(o2[0], o2[1], o2[2], o2[3]);
@@ -236,66 +242,18 @@ prefill_gemm_kernel(const __grid_constant__ PgJobs jobs, const uint16_t *__restr
     const uint32_t tmem_base = tmem_base_slot;
     bool ok = true;
 
-    if (warp < 4) {
-        // ---- weight producers: thread t dequantises rows t and t + 128 of the tile ----
+    if (warp < 8) {
+        // ---- producers: thread t dequantises weight row t of the tile and brings in 8 of the 2048
+        // 16-byte chunks of the token tile (cp.async, one stage ahead of the dequantisation) ----
         const size_t rb = (size_t)nb * BLK;
-        const int ra = min(n0 + tid, rows - 1), rbw = min(n0 + tid + 128, rows - 1);   // rows past the end repeat the last one (never stored)
-        const uint8_t *wa = w + (size_t)ra * rb, *wb = w + (size_t)rbw * rb;
-        uint8_t *const row1 = smem + PG_TILE_BYTES + (tid >> 3) * 1024 + (tid & 7) * 128, *const row2 = row1 + 16 * 1024;   // rows t, t + 128
+        const uint8_t *wr = w + (size_t)min(n0 + tid, rows - 1) * rb;   // rows past the end repeat the last one (never stored)
+        uint8_t *const brow = smem + PG_TILE_BYTES + (tid >> 3) * 1024 + (tid & 7) * 128;
         const int rr = tid & 7;
-        if (TYPE == TYPE_Q4_K) {
-            PgRawQ4 cur_a, cur_b, nxt_a, nxt_b;
-            pg_load_q4(cur_a, wa, 0);
-            pg_load_q4(cur_b, wb, 0);
-            for (int kt = 0; kt < KT && ok; kt++) {
-                const int s = kt % PG_STAGES;
-                if (kt + 1 < KT) {
-                    pg_load_q4(nxt_a, wa + (size_t)((kt + 1) >> 2) * BLK, (kt + 1) & 3);
-                    pg_load_q4(nxt_b, wb + (size_t)((kt + 1) >> 2) * BLK, (kt + 1) & 3);
-                }
-                ok = mbar_wait_bounded(&empty[s], (uint32_t)(((kt / PG_STAGES) & 1) ^ 1));
-                if (!ok) break;
-                pg_dequant_q4(cur_a, kt & 3, row1 + (uint32_t)s * PG_STAGE_BYTES, rr);
-                pg_dequant_q4(cur_b, kt & 3, row2 + (uint32_t)s * PG_STAGE_BYTES, rr);
-                pg_proxy_fence();
-                __syncwarp();
-                if (lane == 0) pg_arrive(&full[s]);
-                cur_a = nxt_a;
-                cur_b = nxt_b;
-            }
-        } else {
-            PgRawQ6 cur_a, cur_b, nxt_a, nxt_b;
-            pg_load_q6(cur_a, wa, 0);
-            pg_load_q6(cur_b, wb, 0);
-            for (int kt = 0; kt < KT && ok; kt++) {
-                const int s = kt % PG_STAGES;
-                // a half block (128 elements) serves two stages: fetch the next half two stages ahead
-                if (!(kt & 1) && kt + 2 < KT) {
-                    pg_load_q6(nxt_a, wa + (size_t)((kt + 2) >> 2) * BLK, ((kt + 2) >> 1) & 1);
-                    pg_load_q6(nxt_b, wb + (size_t)((kt + 2) >> 2) * BLK, ((kt + 2) >> 1) & 1);
-                }
-                ok = mbar_wait_bounded(&empty[s], (uint32_t)(((kt / PG_STAGES) & 1) ^ 1));
-                if (!ok) break;
-                pg_dequant_q6(cur_a, kt & 3, row1 + (uint32_t)s * PG_STAGE_BYTES, rr);
-                pg_dequant_q6(cur_b, kt & 3, row2 + (uint32_t)s * PG_STAGE_BYTES, rr);
-                pg_proxy_fence();
-                __syncwarp();
-                if (lane == 0) pg_arrive(&full[s]);
-                if (kt & 1) {
-                    cur_a = nxt_a;
-                    cur_b = nxt_b;
-                }
-            }
-        }
-    } else if (warp < 8) {
-        // ---- token producers: cp.async the 256 x 64 bf16 tile, one stage ahead ----
-        const int t = tid - 128;
-        auto issue = [&](int kt) {
-            const int s = kt % PG_STAGES;
-            uint8_t *at = smem + (uint32_t)s * PG_STAGE_BYTES;
+        auto issue_a = [&](int kt) {
+            uint8_t *at = smem + (uint32_t)(kt % PG_STAGES) * PG_STAGE_BYTES;
 #pragma unroll
-            for (int i = 0; i < 16; i++) {
-                const int idx = i * 128 + t, r = idx >> 3, c = idx & 7;
+            for (int i = 0; i < 8; i++) {
+                const int idx = i * 256 + tid, r = idx >> 3, c = idx & 7;
                 const int tok = m0 + r;
                 const uint16_t *src = xb + (size_t)min(tok, seq - 1) * cols + (size_t)kt * PG_K + c * 8;
                 const uint32_t nbytes = tok < seq ? 16u : 0u;   // rows past the end are zero-filled
@@ -303,20 +261,46 @@ prefill_gemm_kernel(const __grid_constant__ PgJobs jobs, const uint16_t *__restr
             }
             asm volatile("cp.async.commit_group;" ::: "memory");
         };
-        ok = mbar_wait_bounded(&empty[0], 1u);
-        if (ok) issue(0);
-        for (int kt = 0; kt < KT && ok; kt++) {
+        // stage kt: token tile of kt + 1 goes out first, then this stage's weights are dequantised
+        auto stage_head = [&](int kt) -> bool {
             if (kt + 1 < KT) {
-                ok = mbar_wait_bounded(&empty[(kt + 1) % PG_STAGES], (uint32_t)((((kt + 1) / PG_STAGES) & 1) ^ 1));
-                if (!ok) break;
-                issue(kt + 1);
-                asm volatile("cp.async.wait_group 1;" ::: "memory");
-            } else {
-                asm volatile("cp.async.wait_group 0;" ::: "memory");
+                if (!mbar_wait_bounded(&empty[(kt + 1) % PG_STAGES], (uint32_t)((((kt + 1) / PG_STAGES) & 1) ^ 1))) return false;
+                issue_a(kt + 1);
             }
+            return true;
+        };
+        auto stage_tail = [&](int kt) {
+            if (kt + 1 < KT) asm volatile("cp.async.wait_group 1;" ::: "memory");
+            else asm volatile("cp.async.wait_group 0;" ::: "memory");
             pg_proxy_fence();
             __syncwarp();
             if (lane == 0) pg_arrive(&full[kt % PG_STAGES]);
+        };
+        ok = mbar_wait_bounded(&empty[0], 1u);
+        if (ok) issue_a(0);
+        if (TYPE == TYPE_Q4_K) {
+            PgRawQ4 cur, nxt;
+            pg_load_q4(cur, wr, 0);
+            for (int kt = 0; kt < KT && ok; kt++) {
+                if (kt + 1 < KT) pg_load_q4(nxt, wr + (size_t)((kt + 1) >> 2) * BLK, (kt + 1) & 3);
+                ok = stage_head(kt);
+                if (!ok) break;
+                pg_dequant_q4(cur, kt & 3, brow + (uint32_t)(kt % PG_STAGES) * PG_STAGE_BYTES, rr);
+                stage_tail(kt);
+                cur = nxt;
+            }
+        } else {
+            PgRawQ6 cur, nxt;
+            pg_load_q6(cur, wr, 0);
+            for (int kt = 0; kt < KT && ok; kt++) {
+                // a half block (128 elements) serves two stages: fetch the next half two stages ahead
+                if (!(kt & 1) && kt + 2 < KT) pg_load_q6(nxt, wr + (size_t)((kt + 2) >> 2) * BLK, ((kt + 2) >> 1) & 1);
+                ok = stage_head(kt);
+                if (!ok) break;
+                pg_dequant_q6(cur, kt & 3, brow + (uint32_t)(kt % PG_STAGES) * PG_STAGE_BYTES, rr);
+                stage_tail(kt);
+                if (kt & 1) cur = nxt;
+            }
         }
         asm volatile("cp.async.wait_group 0;" ::: "memory");
     } else {
