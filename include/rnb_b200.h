@@ -298,6 +298,10 @@ int rnb_b200_decoder_read_logits(rnb_b200_decoder *d, float *out, size_t n);
  * flag instead of hanging.  No counterpart in the reference (its CUDA path is single-GPU). */
 int rnb_b200_decoder_exchange_handle(rnb_b200_decoder *d, uint8_t handle_out[64]);
 int rnb_b200_decoder_attach_peers(rnb_b200_decoder *d, const uint8_t *handles /* world x 64 */);
+/* Single-GPU check of the exchange's failure path: waits for a peer flag that nobody raises; the
+ * bounded wait gives up after about a second and *status_out receives the device error code
+ * (4 = peer timeout).  The context stays usable. */
+int rnb_b200_peer_exchange_timeout_selftest(int *status_out);
 
 /* ---- device-pointer tier (no host copies, no synchronisation; for callers that keep
  * activations on the device and for kernel timing).  `stream` is a cudaStream_t or NULL. */

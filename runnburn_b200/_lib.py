@@ -125,6 +125,7 @@ def load() -> C.CDLL:
         "rnb_b200_decoder_read_logits": [vp, vp, sz],
         "rnb_b200_decoder_exchange_handle": [vp, vp],
         "rnb_b200_decoder_attach_peers": [vp, vp],
+        "rnb_b200_peer_exchange_timeout_selftest": [vp],
         "rnb_b200_dev_quantize_q8k": [vp, sz, sz, vp, vp, vp],
         "rnb_b200_dev_gemv": [u32, vp, sz, sz, vp, vp, i32, vp],
         "rnb_b200_dev_prefill_gemm": [i32, vp, sz, sz, vp, sz, vp, vp, vp],

@@ -79,3 +79,23 @@ def test_two_gpu_row_sharded_greedy_ids(tmp_path, transport):
                        capture_output=True, text=True, env=env, timeout=600)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-4000:]
     assert "rank 0 ok" in r.stdout and "rank 1 ok" in r.stdout
+
+
+def test_peer_exchange_wait_gives_up_and_reports():
+    """Failure path without a second GPU or a fault: the exchange kernel waits for a flag nobody
+    raises; its bounded wait runs out, it reports error 4 through the status word and the library
+    keeps working afterwards."""
+    import ctypes as C
+
+    import numpy as np
+
+    import runnburn_b200 as r
+    from runnburn_b200 import ops
+    L = r.load()
+    ops.open()
+    status = C.c_int(-1)
+    assert L.rnb_b200_peer_exchange_timeout_selftest(C.byref(status)) == 0, L.rnb_b200_last_error()
+    assert status.value == 4
+    # the context is still usable
+    x = np.linspace(-1, 1, 256, dtype=np.float32)
+    assert ops.quantize_q8k(x).nbytes == 292
