@@ -195,3 +195,26 @@ def test_llama_wide_ffn_takes_the_fused_gate_up_path():
     assert st["launches_per_step"] == 1 + 2 * 8 + 4   # per layer: norm, qkv, attention, merge, o, norm, gate/up, down
     dec.close()
     ref.close()
+
+
+def test_prefill_in_two_pieces_equals_one_piece():
+    """A prompt prefilled as 40 + 30 tokens leaves the same K/V rows and the same logits as one
+    70-token prefill: every token's arithmetic is independent of how the prompt was cut."""
+    desc = llama_description(seed=6, n_layer=2, hidden=512, n_head=4, n_kv_head=2, n_ff=1024, vocab=2048)
+    prompt = np.random.default_rng(8).integers(0, 2048, 70).tolist()
+    import runnburn_b200 as r
+    cfg = r.ModelConfig(max_ctx=96, **desc["cfg"])
+    one, two = r.Decoder(cfg), r.Decoder(cfg)
+    one.load_description(desc)
+    two.load_description(desc)
+    n1 = one.prefill(prompt, 0)
+    two.prefill(prompt[:40], 0)
+    n2 = two.prefill(prompt[40:], 40)
+    assert n1 == n2
+    assert np.array_equal(one.read_logits().view(np.uint32), two.read_logits().view(np.uint32))
+    for layer in range(2):
+        k1, v1 = one.read_kv(layer, 70)
+        k2, v2 = two.read_kv(layer, 70)
+        assert np.array_equal(k1, k2) and np.array_equal(v1, v2)
+    one.close()
+    two.close()
