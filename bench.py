@@ -321,7 +321,7 @@ def run_gpu(args, shape, ctx, name, rank, world, local_rank):
     max_ctx = ctx + 2 * (K + W) + 8
     cfg = r.ModelConfig(max_ctx=max_ctx, world_size=world, rank=rank, **shape)
     dec = r.Decoder(cfg)
-    transport = os.environ.get("RNB_B200_TRANSPORT", "peer")   # "peer": peer-memory exchange kernels; "nccl": ncclAllGather
+    transport = os.environ.get("RNB_B200_TRANSPORT", "nccl")   # "nccl": ncclAllGather (measured faster); "peer": own peer-memory exchange kernels
     if world > 1 and transport == "nccl":
         ids = [nccl_unique_id() if rank == 0 else None]
         dist.broadcast_object_list(ids, src=0)
