@@ -1,5 +1,6 @@
 """Row-sharded decode on two GPUs: q/k/v by head, KV cache by KV head, all-gather of the f32
-slices inside the per-token graph by peer-memory stores (default) or ncclAllGather.  Greedy ids must equal the oracle's (and therefore the
+slices inside the per-token graph by ncclAllGather or by the library's own peer-memory exchange
+kernels (flag form and {value, tag} low-latency form).  Greedy ids must equal the oracle's (and therefore the
 single-GPU decoder's).  Needs two devices; skipped otherwise."""
 import os
 import subprocess
@@ -66,14 +67,15 @@ WORKER = textwrap.dedent("""
 """)
 
 
-@pytest.mark.parametrize("transport", ["peer", "nccl"])
+@pytest.mark.parametrize("transport", ["peer", "peer-ll", "nccl"])
 def test_two_gpu_row_sharded_greedy_ids(tmp_path, transport):
     import torch
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     script = tmp_path / "worker.py"
     script.write_text(WORKER % (str(ROOT), str(ROOT / "tests")))
-    env = dict(os.environ, MASTER_ADDR="127.0.0.1", RNB_TEST_TRANSPORT=transport)
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", RNB_TEST_TRANSPORT="nccl" if transport == "nccl" else "peer",
+               RNB_B200_PEER_LL="1" if transport == "peer-ll" else "0")
     r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
                         "--master-addr", "127.0.0.1", "--master-port", "29741", str(script)],
                        capture_output=True, text=True, env=env, timeout=600)
