@@ -35,11 +35,9 @@ router_logits_kernel(const float *__restrict__ w, const float *__restrict__ h, i
 // same contract as the reference's rnb_moe_route_topk_f32
 // (crates/rnb-backend/cuda/cuda/kernels/quant_batch_and_ops.cuh:4782-4912).
 // One warp per token; n_expert <= 1024, top_k <= 32.  exp is taken in double and rounded once.
-RNB_GLOBAL void __launch_bounds__(32)
-moe_route_topk_kernel(const float *__restrict__ logits, int n_expert, int top_k,
-                      uint32_t *__restrict__ ids_out, float *__restrict__ weights_out) {
-    pdl_launch_dependents();
-    pdl_wait();
+// Returns the id this lane selected (lane r holds rank r; other lanes return 0).
+__device__ __forceinline__ uint32_t moe_route_topk_warp(const float *__restrict__ logits, int n_expert, int top_k,
+                                                        uint32_t *__restrict__ ids_out, float *__restrict__ weights_out) {
     const int lane = threadIdx.x;
     const float *lg = logits + (size_t)blockIdx.x * n_expert;
     uint32_t *ids = ids_out + (size_t)blockIdx.x * top_k;
@@ -47,6 +45,7 @@ moe_route_topk_kernel(const float *__restrict__ logits, int n_expert, int top_k,
     const int sel = min(min(top_k, n_expert), 32);
     uint32_t taken = 0;  // bit s <-> expert lane + 32*s
     float my_val = 0.0f;
+    uint32_t my_id = 0;
     for (int r = 0; r < sel; r++) {
         float best = -INFINITY;
         int bi = 0x7fffffff;
@@ -70,7 +69,8 @@ moe_route_topk_kernel(const float *__restrict__ logits, int n_expert, int top_k,
         if ((bi & 31) == lane && bi != 0x7fffffff) taken |= 1u << (bi >> 5);
         if (lane == r) {
             my_val = best;
-            ids[r] = (uint32_t)bi;
+            my_id = (uint32_t)bi;
+            ids[r] = my_id;
         }
     }
     const float mx = __shfl_sync(0xffffffffu, my_val, 0);
@@ -78,6 +78,14 @@ moe_route_topk_kernel(const float *__restrict__ logits, int n_expert, int top_k,
     float sum = 0.0f;
     for (int r = 0; r < sel; r++) sum = __fadd_rn(sum, __shfl_sync(0xffffffffu, w, r));
     if (lane < sel) wts[lane] = sum != 0.0f ? __fdiv_rn(w, sum) : w;
+    return my_id;
+}
+RNB_GLOBAL void __launch_bounds__(32)
+moe_route_topk_kernel(const float *__restrict__ logits, int n_expert, int top_k,
+                      uint32_t *__restrict__ ids_out, float *__restrict__ weights_out) {
+    pdl_launch_dependents();
+    pdl_wait();
+    moe_route_topk_warp(logits, n_expert, top_k, ids_out, weights_out);
 }
 
 // Fills the per-layer job tables of the expert-gathered matvecs from the routed ids:
@@ -87,19 +95,24 @@ struct MoeLayerPtrs {
     const uint8_t *gate_base, *up_base, *down_base;
     size_t gate_stride, down_stride;
 };
-RNB_GLOBAL void moe_fill_jobs_kernel(const uint32_t *__restrict__ ids,
-                                     const float *__restrict__ weights, int top_k,
-                                     MoeLayerPtrs lp, GemvJob *__restrict__ gate_up_jobs,
-                                     GemvJob *__restrict__ down_job) {
-    pdl_launch_dependents();
-    pdl_wait();
+__device__ __forceinline__ void moe_fill_jobs_warp(size_t id, const float *__restrict__ weights, int top_k,
+                                                   const MoeLayerPtrs &lp, GemvJob *__restrict__ gate_up_jobs, GemvJob *__restrict__ down_job) {
     const int e = threadIdx.x;
     if (e >= top_k) return;
-    const size_t id = ids[e];
     gate_up_jobs[e].parts[0].w = lp.gate_base + id * lp.gate_stride;
     gate_up_jobs[top_k + e].parts[0].w = lp.up_base + id * lp.gate_stride;
     down_job->parts[e].w = lp.down_base + id * lp.down_stride;
     down_job->parts[e].scale = weights + e;
+}
+// Routing and the job tables in one launch (one token): the warp that selected the experts
+// also points the expert-gathered matvecs at them.
+RNB_GLOBAL void __launch_bounds__(32)
+moe_route_fill_kernel(const float *__restrict__ logits, int n_expert, int top_k, uint32_t *__restrict__ ids_out, float *__restrict__ weights_out,
+                      MoeLayerPtrs lp, GemvJob *__restrict__ gate_up_jobs, GemvJob *__restrict__ down_job) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const uint32_t id = moe_route_topk_warp(logits, n_expert, top_k, ids_out, weights_out);  // lane r: the expert of rank r
+    moe_fill_jobs_warp(id, weights_out, top_k, lp, gate_up_jobs, down_job);
 }
 
 }  // namespace rnb

@@ -363,4 +363,261 @@ prefill_gemm_kernel(const __grid_constant__ PgJobs jobs, const uint16_t *__restr
     }
 }
 
+// =================================================================================================
+// Wide-token form: one CTA owns a 512-token x 128-row output tile (four 128 x 128 fp32
+// accumulators = all 512 columns of tensor memory).  A dequantised weight tile now serves twice
+// as many tokens, which matters because the dequantising warps, not the tensor pipe, bound the
+// 256 x 256 form.  The token tile (512 x 64 bf16 = 64 KB per stage) is brought in by two tiled
+// TMA copies with the 128-byte swizzle (rows past the end of the batch read as zeros), so the
+// eight producer warps only dequantise: thread t owns weight row t / 2 and half t % 2 of the
+// 64-element group (Q4_K: low or high nibbles; Q6_K: the first or second 32 elements).  Two
+// stages of 80 KB; a stage is refilled as soon as the MMAs that read it have been committed.
+constexpr int PGW_TOK = 512;
+constexpr int PGW_ROWS = 128;
+constexpr int PGW_STAGES = 2;
+constexpr uint32_t PGW_A_BYTES = PGW_TOK * 128;    // token tile of a stage
+constexpr uint32_t PGW_B_BYTES = PGW_ROWS * 128;   // weight tile of a stage
+constexpr uint32_t PGW_STAGE_BYTES = PGW_A_BYTES + PGW_B_BYTES;
+constexpr size_t PGW_SMEM = (size_t)PGW_STAGES * PGW_STAGE_BYTES + 1024;
+constexpr int PGW_BOX_ROWS = 256;                  // tokens per TMA copy
+// D = f32, A = B = bf16, both K-major, N = 128, M = 128
+constexpr uint32_t PGW_IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(PGW_ROWS >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+
+__device__ __forceinline__ void pgw_mma(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(da), "l"(db), "r"(PGW_IDESC), "r"(accumulate)
+        : "memory");
+}
+// tiled 2-D copy global -> shared; x (elements of the inner dimension) * 2 bytes must be a multiple of 16
+__device__ __forceinline__ void pgw_tma_2d(uint32_t dst, const void *tmap, int x, int y, uint64_t *bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"(dst), "l"(tmap), "r"(x), "r"(y), "r"(smem_u32(bar))
+                 : "memory");
+}
+
+// Half h of a Q4_K group: h = 0 -> low nibbles (chunks 0-3), h = 1 -> high nibbles (chunks 4-7).
+__device__ __forceinline__ void pgw_dequant_q4(const PgRawQ4 &r, int g, int h, uint8_t *row_base, int rr) {
+    const float d = f16_bits_to_f32(r.hdr.x & 0xffffu), dmin = f16_bits_to_f32(r.hdr.x >> 16);
+    const uint32_t sc03 = r.hdr.y & 0x3f3f3f3fu, mn03 = r.hdr.z & 0x3f3f3f3fu;
+    const uint32_t sc47 = (r.hdr.w & 0x0f0f0f0fu) | (((r.hdr.y >> 6) & 0x03030303u) << 4);
+    const uint32_t mn47 = ((r.hdr.w >> 4) & 0x0f0f0f0fu) | (((r.hdr.z >> 6) & 0x03030303u) << 4);
+    const uint32_t scw = g < 2 ? sc03 : sc47, mnw = g < 2 ? mn03 : mn47;
+    const int sh = 16 * (g & 1) + 8 * h;
+    const float ds = __fmul_rn(d, (float)((scw >> sh) & 0xffu)), nm = -__fmul_rn(dmin, (float)((mnw >> sh) & 0xffu));
+    const uint32_t qw[8] = {r.q0.x, r.q0.y, r.q0.z, r.q0.w, r.q1.x, r.q1.y, r.q1.z, r.q1.w};
+    const int nsh = 4 * h;
+#pragma unroll
+    for (int c = 0; c < 4; c++) {
+        uint32_t o[4];
+#pragma unroll
+        for (int w = 0; w < 2; w++) {
+            const uint32_t n4 = (qw[2 * c + w] >> nsh) & 0x0f0f0f0fu;
+            o[2 * w] = pg_pack_bf16(__fmaf_rn(ds, pg_byte_to_f32(n4, 0), nm), __fmaf_rn(ds, pg_byte_to_f32(n4, 1), nm));
+            o[2 * w + 1] = pg_pack_bf16(__fmaf_rn(ds, pg_byte_to_f32(n4, 2), nm), __fmaf_rn(ds, pg_byte_to_f32(n4, 3), nm));
+        }
+        *reinterpret_cast<uint4 *>(row_base + (((c + 4 * h) ^ rr) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+}
+// Half h of the Q6_K groups of half-block n: h = 0 -> ql[64n .. 64n+31] (q1 / q3), h = 1 -> ql[64n+32 ..] (q2 / q4).
+struct PgwRawQ6 {
+    uint32_t ql[8], qh[8];
+    uint32_t sc[2];
+    float d;
+};
+__device__ __forceinline__ void pgw_load_q6(PgwRawQ6 &r, const uint8_t *blk, int n, int h) {
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        r.ql[i] = pg_ldg_u32_unaligned(blk + 64 * n + 32 * h + 4 * i);
+        r.qh[i] = pg_ldg_u32_unaligned(blk + 128 + 32 * n + 4 * i);
+    }
+    r.sc[0] = pg_ldg_u32_unaligned(blk + 192 + 8 * n);
+    r.sc[1] = pg_ldg_u32_unaligned(blk + 196 + 8 * n);
+    r.d = f16_bits_to_f32(*reinterpret_cast<const uint16_t *>(blk + 208));
+}
+__device__ __forceinline__ void pgw_dequant_q6(const PgwRawQ6 &r, int g, int h, uint8_t *row_base, int rr) {
+    const bool odd = g & 1;
+    const uint32_t scw = (odd ? r.sc[1] : r.sc[0]) >> (16 * h);   // this half's two scale bytes
+    const float ds0 = __fmul_rn(r.d, (float)(int)(int8_t)(scw & 0xffu)), ds1 = __fmul_rn(r.d, (float)(int)(int8_t)((scw >> 8) & 0xffu));
+    // the two high bits of this half's elements sit at bit 2h (even group) or 4 + 2h (odd group) of qh
+    const int hs = (odd ? 4 : 0) + 2 * h;
+#pragma unroll
+    for (int c = 0; c < 4; c++) {
+        uint32_t o[4];
+        const float sa = c < 2 ? ds0 : ds1;
+#pragma unroll
+        for (int w = 0; w < 2; w++) {
+            const int i = 2 * c + w;
+            const uint32_t lo = (odd ? (r.ql[i] >> 4) : r.ql[i]) & 0x0f0f0f0fu;
+            const uint32_t q = lo | (((r.qh[i] >> hs) << 4) & 0x30303030u);
+            o[2 * w] = pg_pack_bf16(__fmul_rn(sa, pg_byte_to_f32_m32(q, 0)), __fmul_rn(sa, pg_byte_to_f32_m32(q, 1)));
+            o[2 * w + 1] = pg_pack_bf16(__fmul_rn(sa, pg_byte_to_f32_m32(q, 2)), __fmul_rn(sa, pg_byte_to_f32_m32(q, 3)));
+        }
+        *reinterpret_cast<uint4 *>(row_base + (((c + 4 * h) ^ rr) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+}
+
+// 128-byte, 64-byte aligned descriptor of the bf16 token matrix [seq][cols] (a CUtensorMap, kept
+// opaque here): boxes of 64 columns x 256 tokens, 128-byte swizzle, zero fill past the end.
+struct alignas(64) PgTensorMap {
+    unsigned long long opaque[16];
+};
+
+// grid = (sum over jobs of ceil(rows / 128), ceil(seq / 512)); 288 threads; dynamic shared memory PGW_SMEM.
+RNB_GLOBAL void __launch_bounds__(PG_THREADS, 1)
+prefill_gemm_wide_kernel(const __grid_constant__ PgJobs jobs, const __grid_constant__ PgTensorMap tmap_x, int seq, int cols,
+                         int *__restrict__ err_flag) {
+    extern __shared__ __align__(1024) uint8_t pg_smem_raw[];
+    __shared__ __align__(8) uint64_t full[PGW_STAGES], empty[PGW_STAGES], done_bar;
+    __shared__ uint32_t tmem_base_slot;
+    __shared__ int s_failed;
+    pdl_launch_dependents();
+    pdl_wait();
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(pg_smem_raw) + 1023) & ~(uintptr_t)1023);
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    int jsel = 0;
+    for (int i = 1; i < jobs.n; i++)
+        if ((int)blockIdx.x >= jobs.j[i].tile0) jsel = i;
+    const PgJob &job = jobs.j[jsel];
+    const int rows = job.rows, TYPE = job.type;
+    const uint8_t *__restrict__ w = job.w;
+    float *__restrict__ y = job.y;
+    const uint32_t BLK = TYPE == TYPE_Q4_K ? Q4K_BYTES : Q6K_BYTES;
+    const int n0 = ((int)blockIdx.x - job.tile0) * PGW_ROWS, m0 = blockIdx.y * PGW_TOK;
+    const int nb = cols >> 8, KT = cols / PG_K;
+    if (tid == 0) {
+        for (int s = 0; s < PGW_STAGES; s++) {
+            mbar_init(&full[s], 9);    // one arrival per producer warp + the thread that issues the token copies
+            mbar_init(&empty[s], 1);   // tcgen05.commit
+        }
+        mbar_init(&done_bar, 1);
+        mbar_fence_init();
+        s_failed = 0;
+    }
+    if (warp == 8) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)), "r"(512) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    pg_fence_before();
+    __syncthreads();
+    pg_fence_after();
+    const uint32_t tmem_base = tmem_base_slot;
+    bool ok = true;
+
+    if (warp < 8) {
+        const int row = tid >> 1, h = tid & 1, rr = row & 7;
+        const size_t rb = (size_t)nb * BLK;
+        const uint8_t *wr = w + (size_t)min(n0 + row, rows - 1) * rb;   // rows past the end repeat the last one (never stored)
+        uint8_t *const brow = smem + PGW_A_BYTES + (row >> 3) * 1024 + rr * 128;
+        // token tile of stage kt: thread 0 announces the bytes and issues the two copies
+        auto issue_tokens = [&](int kt) {
+            if (tid != 0) return;
+            const int s = kt % PGW_STAGES;
+            const uint32_t dst = smem_u32(smem + (uint32_t)s * PGW_STAGE_BYTES);
+            mbar_arrive_expect_tx(&full[s], PGW_A_BYTES);
+#pragma unroll
+            for (int i = 0; i < PGW_TOK / PGW_BOX_ROWS; i++)
+                pgw_tma_2d(dst + (uint32_t)i * (PGW_BOX_ROWS * 128), &tmap_x, kt * PG_K, m0 + i * PGW_BOX_ROWS, &full[s]);
+        };
+        auto stage_tail = [&](int kt) -> bool {
+            pg_proxy_fence();
+            __syncwarp();
+            if (lane == 0) pg_arrive(&full[kt % PGW_STAGES]);
+            if (kt + 1 < KT) {
+                // the next stage may be written once the MMAs that read it have been committed
+                if (!mbar_wait_bounded(&empty[(kt + 1) % PGW_STAGES], (uint32_t)((((kt + 1) / PGW_STAGES) & 1) ^ 1))) return false;
+                issue_tokens(kt + 1);
+            }
+            return true;
+        };
+        ok = mbar_wait_bounded(&empty[0], 1u);
+        if (ok) issue_tokens(0);
+        if (TYPE == TYPE_Q4_K) {
+            PgRawQ4 cur, nxt;
+            pg_load_q4(cur, wr, 0);
+            for (int kt = 0; kt < KT && ok; kt++) {
+                if (kt + 1 < KT) pg_load_q4(nxt, wr + (size_t)((kt + 1) >> 2) * BLK, (kt + 1) & 3);
+                pgw_dequant_q4(cur, kt & 3, h, brow + (uint32_t)(kt % PGW_STAGES) * PGW_STAGE_BYTES, rr);
+                ok = stage_tail(kt);
+                cur = nxt;
+            }
+        } else {
+            PgwRawQ6 cur, nxt;
+            pgw_load_q6(cur, wr, 0, h);
+            for (int kt = 0; kt < KT && ok; kt++) {
+                // a half block (128 elements) serves two stages: fetch the next half two stages ahead
+                if (!(kt & 1) && kt + 2 < KT) pgw_load_q6(nxt, wr + (size_t)((kt + 2) >> 2) * BLK, ((kt + 2) >> 1) & 1, h);
+                pgw_dequant_q6(cur, kt & 3, h, brow + (uint32_t)(kt % PGW_STAGES) * PGW_STAGE_BYTES, rr);
+                ok = stage_tail(kt);
+                if (kt & 1) cur = nxt;
+            }
+        }
+    } else {
+        // ---- MMA issuer: 4 token quarters x 4 K-steps of 16 per stage ----
+        for (int kt = 0; kt < KT && ok; kt++) {
+            const int s = kt % PGW_STAGES;
+            ok = mbar_wait_bounded(&full[s], (uint32_t)((kt / PGW_STAGES) & 1));
+            if (!ok) break;
+            pg_fence_after();
+            if (lane == 0) {
+                const uint32_t a_addr = smem_u32(smem + (uint32_t)s * PGW_STAGE_BYTES), b_addr = a_addr + PGW_A_BYTES;
+#pragma unroll
+                for (int mq = 0; mq < 4; mq++)
+#pragma unroll
+                    for (int k = 0; k < 4; k++)
+                        pgw_mma(tmem_base + (uint32_t)mq * 128u, pg_smem_desc(a_addr + (uint32_t)mq * 128u * 128u + (uint32_t)k * 32u),
+                                pg_smem_desc(b_addr + (uint32_t)k * 32u), (kt > 0 || k > 0) ? 1u : 0u);
+                pg_commit(&empty[s]);
+            }
+            __syncwarp();
+        }
+        if (ok && lane == 0) pg_commit(&done_bar);
+        __syncwarp();
+    }
+    if (!ok) atomicExch(&s_failed, 1);
+
+    // ---- epilogue: warps 0-7, TMEM lane quarter = warp % 4, accumulators warp / 4 and warp / 4 + 2 ----
+    if (warp < 8) {
+        bool fin = ok && mbar_wait_bounded(&done_bar, 0u);
+        // token copies that were announced but never consumed must land before the CTA exits
+        if (!fin) {
+            atomicExch(&s_failed, 1);
+            for (int s = 0; s < PGW_STAGES; s++) mbar_wait_bounded(&full[s], 0u);
+        }
+        pg_fence_after();
+        if (fin) {
+            const int q = warp & 3;
+#pragma unroll 1
+            for (int a = warp >> 2; a < 4; a += 2) {
+                const int tok = m0 + a * 128 + q * 32 + lane;
+#pragma unroll 1
+                for (int cc = 0; cc < PGW_ROWS / 32; cc++) {
+                    uint32_t v[32];
+                    pg_tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(a * 128 + cc * 32), v);
+                    const int nn = n0 + cc * 32;
+                    if (tok < seq) {
+                        float *dst = y + (size_t)tok * rows + nn;
+                        if (nn + 32 <= rows && (rows & 3) == 0) {   // 16-byte stores need rows % 4 == 0
+#pragma unroll
+                            for (int i = 0; i < 8; i++)
+                                *reinterpret_cast<float4 *>(dst + 4 * i) = make_float4(__uint_as_float(v[4 * i]), __uint_as_float(v[4 * i + 1]),
+                                                                                       __uint_as_float(v[4 * i + 2]), __uint_as_float(v[4 * i + 3]));
+                        } else {
+                            for (int i = 0; i < 32; i++)
+                                if (nn + i < rows) dst[i] = __uint_as_float(v[i]);
+                        }
+                    }
+                }
+            }
+        }
+    }
+    pg_fence_before();
+    __syncthreads();
+    if (warp == 8) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
+        if (lane == 0 && s_failed && err_flag) atomicExch(err_flag, DEV_ERR_GEMM_TIMEOUT);
+    }
+}
+
 }  // namespace rnb
