@@ -364,8 +364,8 @@ prefill_gemm_kernel(const __grid_constant__ PgJobs jobs, const uint16_t *__restr
 }
 
 // =================================================================================================
-// Wide-token form: one CTA owns a 512-token x 128-row output tile (four 128 x 128 fp32
-// accumulators = all 512 columns of tensor memory).  A dequantised weight tile now serves twice
+// Wide-token form: one CTA owns a 512-token x 128-row output tile (two accumulators of 128 rows x
+// 256 tokens = all 512 columns of tensor memory; the weights are the M operand).  A dequantised weight tile now serves twice
 // as many tokens, which matters because the dequantising warps, not the tensor pipe, bound the
 // 256 x 256 form.  The token tile (512 x 64 bf16 = 64 KB per stage) is brought in by two tiled
 // TMA copies with the 128-byte swizzle (rows past the end of the batch read as zeros), so the
@@ -380,16 +380,6 @@ constexpr uint32_t PGW_B_BYTES = PGW_ROWS * 128;   // weight tile of a stage
 constexpr uint32_t PGW_STAGE_BYTES = PGW_A_BYTES + PGW_B_BYTES;
 constexpr size_t PGW_SMEM = (size_t)PGW_STAGES * PGW_STAGE_BYTES + 1024;
 constexpr int PGW_BOX_ROWS = 256;                  // tokens per TMA copy
-// D = f32, A = B = bf16, both K-major, N = 128, M = 128
-constexpr uint32_t PGW_IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(PGW_ROWS >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
-
-__device__ __forceinline__ void pgw_mma(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(tmem_d), "l"(da), "l"(db), "r"(PGW_IDESC), "r"(accumulate)
-        : "memory");
-}
 // tiled 2-D copy global -> shared; x (elements of the inner dimension) * 2 bytes must be a multiple of 16
 __device__ __forceinline__ void pgw_tma_2d(uint32_t dst, const void *tmap, int x, int y, uint64_t *bar) {
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
@@ -554,20 +544,22 @@ prefill_gemm_wide_kernel(const __grid_constant__ PgJobs jobs, const __grid_const
             }
         }
     } else {
-        // ---- MMA issuer: 4 token quarters x 4 K-steps of 16 per stage ----
+        // ---- MMA issuer: per stage 2 token halves x 4 K-steps of 16; the weight tile is the M operand (128 rows =
+        // 128 TMEM lanes), a token half the N operand (256 columns): fewer shared-memory reads per flop than four
+        // 128 x 128 products ----
         for (int kt = 0; kt < KT && ok; kt++) {
             const int s = kt % PGW_STAGES;
             ok = mbar_wait_bounded(&full[s], (uint32_t)((kt / PGW_STAGES) & 1));
             if (!ok) break;
             pg_fence_after();
             if (lane == 0) {
-                const uint32_t a_addr = smem_u32(smem + (uint32_t)s * PGW_STAGE_BYTES), b_addr = a_addr + PGW_A_BYTES;
+                const uint32_t x_addr = smem_u32(smem + (uint32_t)s * PGW_STAGE_BYTES), w_addr = x_addr + PGW_A_BYTES;
 #pragma unroll
-                for (int mq = 0; mq < 4; mq++)
+                for (int nh = 0; nh < 2; nh++)
 #pragma unroll
                     for (int k = 0; k < 4; k++)
-                        pgw_mma(tmem_base + (uint32_t)mq * 128u, pg_smem_desc(a_addr + (uint32_t)mq * 128u * 128u + (uint32_t)k * 32u),
-                                pg_smem_desc(b_addr + (uint32_t)k * 32u), (kt > 0 || k > 0) ? 1u : 0u);
+                        pg_mma(tmem_base + (uint32_t)nh * 256u, pg_smem_desc(w_addr + (uint32_t)k * 32u),
+                               pg_smem_desc(x_addr + (uint32_t)nh * 256u * 128u + (uint32_t)k * 32u), (kt > 0 || k > 0) ? 1u : 0u);
                 pg_commit(&empty[s]);
             }
             __syncwarp();
@@ -577,7 +569,8 @@ prefill_gemm_wide_kernel(const __grid_constant__ PgJobs jobs, const __grid_const
     }
     if (!ok) atomicExch(&s_failed, 1);
 
-    // ---- epilogue: warps 0-7, TMEM lane quarter = warp % 4, accumulators warp / 4 and warp / 4 + 2 ----
+    // ---- epilogue: warps 0-7; TMEM lane = weight row (lane quarter = warp % 4), column = token (half = warp / 4).
+    // A warp's 32 lanes hold 32 consecutive rows of one token: each store instruction writes 128 contiguous bytes ----
     if (warp < 8) {
         bool fin = ok && mbar_wait_bounded(&done_bar, 0u);
         // token copies that were announced but never consumed must land before the CTA exits
@@ -587,27 +580,18 @@ prefill_gemm_wide_kernel(const __grid_constant__ PgJobs jobs, const __grid_const
         }
         pg_fence_after();
         if (fin) {
-            const int q = warp & 3;
+            const int q = warp & 3, nh = warp >> 2;
+            const int row = n0 + q * 32 + lane;
 #pragma unroll 1
-            for (int a = warp >> 2; a < 4; a += 2) {
-                const int tok = m0 + a * 128 + q * 32 + lane;
-#pragma unroll 1
-                for (int cc = 0; cc < PGW_ROWS / 32; cc++) {
-                    uint32_t v[32];
-                    pg_tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(a * 128 + cc * 32), v);
-                    const int nn = n0 + cc * 32;
-                    if (tok < seq) {
-                        float *dst = y + (size_t)tok * rows + nn;
-                        if (nn + 32 <= rows && (rows & 3) == 0) {   // 16-byte stores need rows % 4 == 0
+            for (int cc = 0; cc < 256 / 32; cc++) {
+                uint32_t v[32];
+                pg_tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(nh * 256 + cc * 32), v);
+                const int tok0 = m0 + nh * 256 + cc * 32;
+                if (row < rows) {
+                    float *dst = y + (size_t)tok0 * rows + row;
 #pragma unroll
-                            for (int i = 0; i < 8; i++)
-                                *reinterpret_cast<float4 *>(dst + 4 * i) = make_float4(__uint_as_float(v[4 * i]), __uint_as_float(v[4 * i + 1]),
-                                                                                       __uint_as_float(v[4 * i + 2]), __uint_as_float(v[4 * i + 3]));
-                        } else {
-                            for (int i = 0; i < 32; i++)
-                                if (nn + i < rows) dst[i] = __uint_as_float(v[i]);
-                        }
-                    }
+                    for (int i = 0; i < 32; i++)
+                        if (tok0 + i < seq) dst[(size_t)i * rows] = __uint_as_float(v[i]);
                 }
             }
         }
