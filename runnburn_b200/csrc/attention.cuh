@@ -81,6 +81,37 @@ rope_kv_append_kernel(float *__restrict__ q, const float *__restrict__ k,
     }
 }
 
+// The same work for a batch of consecutive tokens (prefill): one CTA of 256 threads per token,
+// thread (g = tid / 64, i = tid % 64) owns rotation pair i of heads g, g + 4, ... - the cos/sin of
+// the pair is read once.  Same arithmetic and rounding as rope_kv_append_kernel.
+RNB_GLOBAL void __launch_bounds__(256)
+rope_kv_append_tokens_kernel(float *__restrict__ q, const float *__restrict__ k, const float *__restrict__ v, const float *__restrict__ rope_table,
+                             int pos0, int num_heads, int num_kv_heads, int neox, uint16_t *__restrict__ k_cache, uint16_t *__restrict__ v_cache) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x, pos = pos0 + t, i = threadIdx.x & 63, g = threadIdx.x >> 6;
+    const float *cs = rope_table + (size_t)pos * 128;
+    const float c = cs[i], s = cs[64 + i];
+    const int i0 = neox ? i : 2 * i, i1 = neox ? i + 64 : 2 * i + 1;
+    const size_t kv_dim = (size_t)num_kv_heads * HD;
+    float *qt = q + (size_t)t * num_heads * HD;
+    for (int h = g; h < num_heads; h += 4) {
+        float *qh = qt + (size_t)h * HD;
+        const float x0 = qh[i0], x1 = qh[i1];
+        qh[i0] = __fsub_rn(__fmul_rn(x0, c), __fmul_rn(x1, s));
+        qh[i1] = __fadd_rn(__fmul_rn(x0, s), __fmul_rn(x1, c));
+    }
+    const float *kt = k + (size_t)t * kv_dim, *vt = v + (size_t)t * kv_dim;
+    uint16_t *kd = k_cache + (size_t)pos * kv_dim, *vd = v_cache + (size_t)pos * kv_dim;
+    for (int h = g; h < num_kv_heads; h += 4) {
+        const float *kh = kt + (size_t)h * HD;
+        const float x0 = kh[i0], x1 = kh[i1];
+        kd[(size_t)h * HD + i0] = __half_as_ushort(__float2half_rn(__fsub_rn(__fmul_rn(x0, c), __fmul_rn(x1, s))));
+        kd[(size_t)h * HD + i1] = __half_as_ushort(__float2half_rn(__fadd_rn(__fmul_rn(x0, s), __fmul_rn(x1, c))));
+    }
+    for (size_t e = threadIdx.x; e < kv_dim; e += 256) vd[e] = __half_as_ushort(__float2half_rn(vt[e]));
+}
+
 // Plain f32 -> f16 row append (no RoPE) for callers that rotate elsewhere.
 RNB_GLOBAL void kv_append_f16_kernel(const float *__restrict__ src, uint16_t *__restrict__ dst,
                                      size_t n) {

@@ -405,6 +405,7 @@ inline int launch_prefill_gemm_multi(cudaStream_t s, int n, const int *types, co
     if (cols == 0 || cols % 256 != 0) return fail(RNB_B200_VALIDATION_FAILED, "cols(%zu) must be a non-zero multiple of 256", cols);
     if (seq == 0) return fail(RNB_B200_VALIDATION_FAILED, "prefill matmul needs tokens");
     if (((uintptr_t)x & 15u) || ((uintptr_t)xb & 15u)) return fail(RNB_B200_VALIDATION_FAILED, "prefill matmul operands are not aligned");
+    // x == nullptr: `xb` already holds the bf16 token matrix (written by the producer of the activation)
     PgJobs jobs;
     memset(&jobs, 0, sizeof(jobs));
     jobs.n = n;
@@ -423,7 +424,7 @@ inline int launch_prefill_gemm_multi(cudaStream_t s, int n, const int *types, co
     }
     RNB_TRY(prefill_gemm_setup());
     const size_t ne = seq * cols;
-    RNB_CU(launch_k(f32_to_bf16_kernel, dim3((unsigned)((ne / 8 + 255) / 256)), dim3(256), 0, s, x, xb, ne));
+    if (x) RNB_CU(launch_k(f32_to_bf16_kernel, dim3((unsigned)((ne / 8 + 255) / 256)), dim3(256), 0, s, x, xb, ne));
     if (prefill_gemm_wide()) {
         // tiles of 128 rows; the token matrix is read through a tiled TMA descriptor
         tiles = 0;

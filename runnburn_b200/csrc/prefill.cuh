@@ -2,6 +2,7 @@
 // f32 tensors: crates/rnb-backend/cuda/src/runtime/api/attention_api.rs:661-700).
 #pragma once
 #include "attention.cuh"
+#include "prefill_attention_tiled.cuh"
 #include "state.hpp"
 
 namespace rnb {
@@ -52,10 +53,30 @@ inline int launch_prefill_attention_f16kv(cudaStream_t s, const float *q, const 
         const char *e = getenv("RNB_B200_FD_SIMT");
         return e && *e == '1';
     }();
+    // RNB_B200_PF_ATTN=split keeps the split-KV decode machinery (8 columns per CTA) for prefill
+    static const bool tiled = [] {
+        const char *e = getenv("RNB_B200_PF_ATTN");
+        return !(e && !strcmp(e, "split"));
+    }();
     cudaLaunchConfig_t cfg = {};
     cfg.stream = s;
+    const bool aligned = (((uintptr_t)k | (uintptr_t)v) & 15) == 0;
+    if (!simt && tiled && aligned && group >= 1 && group <= PAT_ROWS && (group & (group - 1)) == 0 && num_heads == group * num_kv_heads &&
+        ((uintptr_t)q & 7) == 0 && ((uintptr_t)out & 7) == 0 && kv_len >= seq_len) {
+        static bool attr_set = false;
+        if (!attr_set) {
+            RNB_CU(cudaFuncSetAttribute(prefill_attention_tiled_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PAT_SMEM));
+            attr_set = true;
+        }
+        const int qpc = PAT_ROWS / group;
+        cfg.blockDim = dim3(PAT_THREADS);
+        cfg.gridDim = dim3((seq_len + qpc - 1) / qpc, num_kv_heads);
+        cfg.dynamicSmemBytes = PAT_SMEM;
+        RNB_CU(cudaLaunchKernelEx(&cfg, prefill_attention_tiled_kernel, q, k, v, seq_len, kv_len, num_heads, num_kv_heads, scale, out));
+        return RNB_B200_OK;
+    }
     cfg.blockDim = dim3(FD_THREADS);
-    if (!simt && (((uintptr_t)k | (uintptr_t)v) & 15) == 0) {
+    if (!simt && aligned) {
         const int qpc = group >= 8 ? 1 : 8 / group;
         cfg.gridDim = dim3(num_kv_heads, (seq_len + qpc - 1) / qpc);
         RNB_CU(cudaLaunchKernelEx(&cfg, prefill_attention_mma_kernel, q, k, v, seq_len, kv_len, num_heads, num_kv_heads, scale, out, dev_error));

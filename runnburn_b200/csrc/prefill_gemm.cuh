@@ -189,6 +189,27 @@ f32_to_bf16_kernel(const float *__restrict__ x, uint16_t *__restrict__ y, size_t
     *reinterpret_cast<uint4 *>(y + i) = make_uint4(pg_pack_bf16(a.x, a.y), pg_pack_bf16(a.z, a.w), pg_pack_bf16(b.x, b.y), pg_pack_bf16(b.z, b.w));
 }
 
+// silu(gate) * up (g / (1 + exp(-g)), crates/rnb-cpu/src/kernels/activation.rs:74-89, exp in double and
+// rounded once as in silu_mul_q8k_kernel) written straight as the bf16 token matrix of the down
+// matmul: the f32 value is rounded to bf16 exactly as f32_to_bf16_kernel would round it.
+RNB_GLOBAL void __launch_bounds__(256)
+silu_mul_bf16_kernel(const float *__restrict__ gate, const float *__restrict__ up, uint16_t *__restrict__ y, size_t n) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 8;
+    if (i >= n) return;
+    const float4 g0 = *reinterpret_cast<const float4 *>(gate + i), g1 = *reinterpret_cast<const float4 *>(gate + i + 4);
+    const float4 u0 = *reinterpret_cast<const float4 *>(up + i), u1 = *reinterpret_cast<const float4 *>(up + i + 4);
+    const float gv[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w}, uv[8] = {u0.x, u0.y, u0.z, u0.w, u1.x, u1.y, u1.z, u1.w};
+    float v[8];
+#pragma unroll
+    for (int j = 0; j < 8; j++) {
+        const float e = (float)exp((double)(-gv[j]));
+        v[j] = __fmul_rn(__fdiv_rn(gv[j], __fadd_rn(1.0f, e)), uv[j]);
+    }
+    *reinterpret_cast<uint4 *>(y + i) = make_uint4(pg_pack_bf16(v[0], v[1]), pg_pack_bf16(v[2], v[3]), pg_pack_bf16(v[4], v[5]), pg_pack_bf16(v[6], v[7]));
+}
+
 // Up to three matrices that share the token tile go out in one launch (q/k/v, gate/up): the
 // x dimension of the grid runs over the 256-row tiles of all of them.
 constexpr int PG_MAX_JOBS = 3;
