@@ -146,6 +146,12 @@ int rnb_b200_clear_decode_attention_kv_cache(void);
 int rnb_b200_attention_prefill_flash_hd128(const float *q, const float *k, const float *v,
                                            size_t seq_len, size_t kv_len, size_t num_heads,
                                            size_t num_kv_heads, float scale, float *out);
+/* The same with an f16 cache (bit patterns), k, v [kv_len][kv_heads][128] — the layout and
+ * argument order of the reference's f16-KV prefill operators (attention_prefill_flash_hd512_f16kv,
+ * api/attention_api.rs:43-89) at head dimension 128.  Runs the query-tiled tensor-core kernel. */
+int rnb_b200_attention_prefill_flash_hd128_f16kv(const float *q, const uint16_t *k, const uint16_t *v,
+                                                 size_t seq_len, size_t kv_len, size_t num_heads,
+                                                 size_t num_kv_heads, float scale, float *out);
 /* dense_q4k_attention_qkv_rope_hd128_decode — api/dense_api.rs:988-1074: q/k/v matvec,
  * adjacent-pair RoPE on q and k at position pos_start, K/V rounded to f16.  Weight types are
  * given per matrix (the reference's name says Q4_K; Q4_K_M files carry Q6_K in attn_v). */

@@ -94,6 +94,7 @@ def load() -> C.CDLL:
         "rnb_b200_attention_decode_cached": [sz, vp, sz, vp, vp, sz, sz, sz, sz, sz, f32, vp, sz],
         "rnb_b200_clear_decode_attention_kv_cache": [],
         "rnb_b200_attention_prefill_flash_hd128": [vp, vp, vp, sz, sz, sz, sz, f32, vp],
+        "rnb_b200_attention_prefill_flash_hd128_f16kv": [vp, vp, vp, sz, sz, sz, sz, f32, vp],
         "rnb_b200_dense_attention_qkv_rope_hd128_decode": [
             vp, sz, u32, vp, sz, u32, vp, sz, u32, sz, sz, sz, sz, sz, f32, sz, vp, vp, vp, vp],
         "rnb_b200_dense_q4k_silu_ffn_batch": [vp, sz, vp, sz, vp, sz, u32, sz, sz, sz, vp, vp],

@@ -701,6 +701,30 @@ int rnb_b200_attention_prefill_flash_hd128(const float *q, const float *k, const
     return finish_to_host(st, st.out_f32.p, out, qb);
 }
 
+int rnb_b200_attention_prefill_flash_hd128_f16kv(const float *q, const uint16_t *k, const uint16_t *v, size_t seq_len, size_t kv_len,
+                                                 size_t heads, size_t kv_heads, float scale, float *out) {
+    if (kv_heads == 0 || heads == 0 || heads % kv_heads != 0)
+        return fail(RNB_B200_VALIDATION_FAILED, "attention: num_heads(%zu) must be a multiple of num_kv_heads(%zu)", heads, kv_heads);
+    if (seq_len == 0 || kv_len < seq_len) return fail(RNB_B200_VALIDATION_FAILED, "prefill attention needs 0 < seq_len <= kv_len, got %zu / %zu", seq_len, kv_len);
+    if (!q || !k || !v || !out) return fail(RNB_B200_VALIDATION_FAILED, "null pointer argument");
+    Locked L;
+    State &st = L.st;
+    RNB_TRY(st.open());
+    RNB_CU(cudaSetDevice(st.device));
+    const size_t qb = seq_len * heads * HD * 4, kb = kv_len * kv_heads * HD * 2;
+    RNB_TRY(st.in_f32.ensure(qb));
+    RNB_TRY(st.mid_a.ensure(kb));
+    RNB_TRY(st.mid_b.ensure(kb));
+    RNB_TRY(st.out_f32.ensure(qb));
+    RNB_CU(cudaMemcpyAsync(st.in_f32.p, q, qb, cudaMemcpyHostToDevice, st.stream));
+    RNB_CU(cudaMemcpyAsync(st.mid_a.p, k, kb, cudaMemcpyHostToDevice, st.stream));
+    RNB_CU(cudaMemcpyAsync(st.mid_b.p, v, kb, cudaMemcpyHostToDevice, st.stream));
+    st.ctr.h2d_bytes += qb + 2 * kb;
+    RNB_TRY(launch_prefill_attention_f16kv(st.stream, st.in_f32.as<float>(), st.mid_a.as<uint16_t>(), st.mid_b.as<uint16_t>(), (int)seq_len, (int)kv_len,
+                                           (int)heads, (int)kv_heads, scale, st.out_f32.as<float>(), st.dev_error));
+    return finish_to_host(st, st.out_f32.p, out, qb);
+}
+
 // ---- glue ops -----------------------------------------------------------------------------------
 static void host_rope_row(size_t pos, size_t head_dim, float theta, float *row /* [2][head_dim/2] */) {
     // CPU angle chain: crates/rnb-cpu/src/kernels/rope.rs:267-293

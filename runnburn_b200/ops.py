@@ -202,6 +202,18 @@ def attention_prefill_flash_hd128(q, k, v, seq_len: int, kv_len: int, num_heads:
     return out
 
 
+def attention_prefill_flash_hd128_f16kv(q, k_bits, v_bits, seq_len: int, kv_len: int, num_heads: int, num_kv_heads: int,
+                                        scale: float) -> np.ndarray:
+    """Causal prefill attention against an f16 cache (uint16 bit patterns, [kv_len][kv_heads][128])."""
+    q = _f32(q).ravel()
+    k = np.ascontiguousarray(k_bits, dtype=np.uint16).ravel()
+    v = np.ascontiguousarray(v_bits, dtype=np.uint16).ravel()
+    out = np.empty(seq_len * num_heads * 128, dtype=np.float32)
+    check(load().rnb_b200_attention_prefill_flash_hd128_f16kv(_p(q), _p(k), _p(v), seq_len, kv_len, num_heads,
+                                                              num_kv_heads, scale, _p(out)))
+    return out
+
+
 def dense_attention_qkv_rope_hd128_decode(q_w, k_w, v_w, q_rows, kv_rows, n_embd, num_heads, num_kv_heads,
                                           rope_theta, pos_start, x, q_type=TYPE_Q4_K, k_type=TYPE_Q4_K,
                                           v_type=TYPE_Q4_K):

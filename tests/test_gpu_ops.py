@@ -245,6 +245,24 @@ def test_attention_prefill_causal(ops):
     assert max_rel_err(got, ref) <= TOL
 
 
+@pytest.mark.parametrize("heads,kvh,seq,kv_len", [
+    (32, 8, 300, 300),    # Llama-3-8B head layout, ragged last query block and key tile
+    (8, 1, 70, 1000),     # group 8, a cache much longer than the batch (later piece of a prompt)
+    (4, 4, 129, 129),     # no grouping: 128 queries per CTA + one more
+    (16, 4, 1, 65),       # a single query
+    (6, 2, 33, 64),       # group 3 does not divide 128: the split-KV kernel takes it
+])
+def test_attention_prefill_causal_f16_cache(ops, heads, kvh, seq, kv_len):
+    rng = np.random.default_rng(heads * 1000 + seq)
+    q = rng.standard_normal(seq * heads * 128).astype(np.float32)
+    k16 = rng.standard_normal(kv_len * kvh * 128).astype(np.float16)
+    v16 = rng.standard_normal(kv_len * kvh * 128).astype(np.float16)
+    scale = 1.0 / np.sqrt(128.0)
+    ref = orc.attention_prefill(q, k16.astype(np.float32), v16.astype(np.float32), seq, kv_len, heads, kvh, 128, scale)
+    got = ops.attention_prefill_flash_hd128_f16kv(q, k16.view(np.uint16), v16.view(np.uint16), seq, kv_len, heads, kvh, scale)
+    assert max_rel_err(got, ref) <= TOL
+
+
 # ---- glue ---------------------------------------------------------------------------------------
 def test_rms_norm_rope_silu(ops):
     rng = np.random.default_rng(4)
