@@ -349,7 +349,6 @@ int prefill_gemm_setup() {
     static bool done = false;
     if (done) return RNB_B200_OK;
     RNB_CU(cudaFuncSetAttribute(prefill_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PG_SMEM));
-    RNB_CU(cudaFuncSetAttribute(prefill_gemm_wide_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PGW_SMEM));
     done = true;
     return RNB_B200_OK;
 }

@@ -367,15 +367,7 @@ inline int launch_flash_decode(cudaStream_t s, const float *q, const uint16_t *k
 // Tensor-core prefill matmul: converts the f32 token rows to bf16 (scratch `xb`, seq*cols
 // elements) and runs the tcgen05 kernel.  y is [seq][rows] f32.
 int prefill_gemm_setup();   // raises the kernels' dynamic shared-memory limit once
-// RNB_B200_PG_TILE=256 selects the 256-token x 256-row kernel; default is 512 tokens x 128 rows.
-inline bool prefill_gemm_wide() {
-    static const bool v = [] {
-        const char *e = getenv("RNB_B200_PG_TILE");
-        return !(e && atoi(e) == 256);
-    }();
-    return v;
-}
-// Descriptor of the bf16 token matrix [seq][cols] for the wide kernel's tiled copies: boxes of
+// Descriptor of the bf16 token matrix [seq][cols] for the kernel's tiled copies: boxes of
 // 64 columns x 256 tokens, 128-byte swizzle, zeros past the last token.  The encoder is a driver
 // entry point, looked up once through the runtime.
 inline int encode_token_map(PgTensorMap *out, const uint16_t *xb, size_t seq, size_t cols) {
@@ -392,7 +384,7 @@ inline int encode_token_map(PgTensorMap *out, const uint16_t *xb, size_t seq, si
     }
     const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)seq};
     const cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
-    const cuuint32_t box[2] = {(cuuint32_t)PG_K, (cuuint32_t)PGW_BOX_ROWS};
+    const cuuint32_t box[2] = {(cuuint32_t)PG_K, (cuuint32_t)PG_BOX_ROWS};
     const cuuint32_t estr[2] = {1, 1};
     const CUresult r = encode(reinterpret_cast<CUtensorMap *>(out), CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<uint16_t *>(xb), dims, strides, box, estr,
                               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -420,26 +412,15 @@ inline int launch_prefill_gemm_multi(cudaStream_t s, int n, const int *types, co
         jobs.j[i].rows = (int)rows[i];
         jobs.j[i].type = types[i];
         jobs.j[i].tile0 = tiles;
-        tiles += (int)((rows[i] + PG_TILE_N - 1) / PG_TILE_N);
+        tiles += (int)((rows[i] + PG_ROWS - 1) / PG_ROWS);
     }
     RNB_TRY(prefill_gemm_setup());
     const size_t ne = seq * cols;
     if (x) RNB_CU(launch_k(f32_to_bf16_kernel, dim3((unsigned)((ne / 8 + 255) / 256)), dim3(256), 0, s, x, xb, ne));
-    if (prefill_gemm_wide()) {
-        // tiles of 128 rows; the token matrix is read through a tiled TMA descriptor
-        tiles = 0;
-        for (int i = 0; i < n; i++) {
-            jobs.j[i].tile0 = tiles;
-            tiles += (int)((rows[i] + PGW_ROWS - 1) / PGW_ROWS);
-        }
-        PgTensorMap tmap;
-        RNB_TRY(encode_token_map(&tmap, xb, seq, cols));
-        const dim3 grid((unsigned)tiles, (unsigned)((seq + PGW_TOK - 1) / PGW_TOK));
-        RNB_CU(launch_k(prefill_gemm_wide_kernel, grid, dim3(PG_THREADS), PGW_SMEM, s, jobs, tmap, (int)seq, (int)cols, dev_error));
-        return RNB_B200_OK;
-    }
-    const dim3 grid((unsigned)tiles, (unsigned)((seq + PG_TILE_M - 1) / PG_TILE_M));
-    RNB_CU(launch_k(prefill_gemm_kernel, grid, dim3(PG_THREADS), PG_SMEM, s, jobs, (const uint16_t *)xb, (int)seq, (int)cols, dev_error));
+    PgTensorMap tmap;
+    RNB_TRY(encode_token_map(&tmap, xb, seq, cols));
+    const dim3 grid((unsigned)tiles, (unsigned)((seq + PG_TOK - 1) / PG_TOK));
+    RNB_CU(launch_k(prefill_gemm_kernel, grid, dim3(PG_THREADS), PG_SMEM, s, jobs, tmap, (int)seq, (int)cols, dev_error));
     return RNB_B200_OK;
 }
 inline int launch_prefill_gemm(cudaStream_t s, int type, const uint8_t *w, size_t rows, size_t cols, const float *x, size_t seq,

@@ -6,16 +6,21 @@
 // crates/rnb-cpu/src/quantize/dequant.rs:353-381 (Q4_K) and :780-807 (Q6_K) in f32 and rounds
 // once to bf16.
 //
-// One CTA owns a 256-token x 256-row output tile: two 128 x 256 fp32 accumulators = all 512
-// columns of the SM's tensor memory.  K advances 64 elements (one Q4_K group, a quarter of a
-// super-block) per pipeline stage; a stage holds the token tile (256 x 64 bf16) and the weight
-// tile (256 x 64 bf16), both K-major in the 128-byte swizzle the MMA descriptors expect:
+// One CTA owns a 512-token x 128-row output tile: two fp32 accumulators of 128 rows x 256 tokens =
+// all 512 columns of the SM's tensor memory; the weight tile is the M operand (TMEM lane = weight
+// row), a token half the N operand.  A dequantised weight tile serves 512 tokens - the dequantising
+// warps, not the tensor pipe, bounded a 256 x 256 tile.  K advances 64 elements (one Q4_K group, a
+// quarter of a super-block) per pipeline stage; a stage holds the token tile (512 x 64 bf16 = 64 KB,
+// brought in by two tiled TMA copies; rows past the end of the batch read as zeros) and the weight
+// tile (128 x 64 bf16), both K-major in the 128-byte swizzle the MMA descriptors expect:
 //   byte offset of (row r, 16-byte chunk c) = (r / 8) * 1024 + (r % 8) * 128 + ((c ^ (r % 8)) * 16).
-// Warp roles: 0-7 produce a stage (thread t dequantises weight row t and copies 8 chunks of the
-// token tile with cp.async), 8 allocates tensor memory and issues the MMAs (eight per stage: 2 token halves x 4
-// K-steps of 16); afterwards warps 0-7 read the accumulators back (tcgen05.ld, one TMEM lane
-// quarter per warp) and store f32 rows.  Every wait is bounded; a timeout sets the error flag
-// and all roles still meet at the final barrier, where the tensor memory is freed.
+// Two stages of 80 KB; a stage is refilled as soon as the MMAs that read it have been committed.
+// Warp roles: 0-7 dequantise (thread t owns weight row t / 2 and half t % 2 of the 64-element group:
+// Q4_K low or high nibbles, Q6_K the first or second 32 elements), thread 0 also issues the token
+// copies; warp 8 allocates tensor memory and issues the MMAs (eight per stage: 2 token halves x 4
+// K-steps of 16); afterwards warps 0-7 read the accumulators back (tcgen05.ld, one TMEM lane quarter
+// per warp) and store f32 rows.  Every wait is bounded; a timeout sets the error flag and all roles
+// still meet at the final barrier, where the tensor memory is freed.
 #pragma once
 #include <cuda_bf16.h>
 
@@ -25,23 +30,23 @@
 
 namespace rnb {
 
-constexpr int PG_TILE_M = 256;   // tokens per CTA
-constexpr int PG_TILE_N = 256;   // weight rows per CTA
+constexpr int PG_TOK = 512;      // tokens per CTA
+constexpr int PG_ROWS = 128;     // weight rows per CTA
 constexpr int PG_K = 64;         // elements per stage
-constexpr int PG_STAGES = 3;
+constexpr int PG_STAGES = 2;
 constexpr int PG_THREADS = 288;
-constexpr uint32_t PG_TILE_BYTES = 256 * 128;                      // one operand tile of a stage
-constexpr uint32_t PG_STAGE_BYTES = 2 * PG_TILE_BYTES;
+constexpr uint32_t PG_A_BYTES = PG_TOK * 128;    // token tile of a stage
+constexpr uint32_t PG_B_BYTES = PG_ROWS * 128;   // weight tile of a stage
+constexpr uint32_t PG_STAGE_BYTES = PG_A_BYTES + PG_B_BYTES;
 constexpr size_t PG_SMEM = (size_t)PG_STAGES * PG_STAGE_BYTES + 1024;   // + slack to align to 1024
-
-__device__ __forceinline__ uint32_t pg_swz(int r, int c) { return (uint32_t)((r >> 3) * 1024 + (r & 7) * 128 + ((c ^ (r & 7)) << 4)); }
+constexpr int PG_BOX_ROWS = 256;                 // tokens per TMA copy
 
 // K-major, 128-byte swizzle, 8-row groups 1024 bytes apart; descriptor version 1 (sm_100)
 __device__ __forceinline__ uint64_t pg_smem_desc(uint32_t saddr) {
     return (uint64_t)((saddr & 0x3ffffu) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
 }
-// D = f32, A = B = bf16, both K-major, N = 256, M = 128
-constexpr uint32_t PG_IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(PG_TILE_N >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+// D = f32, A = B = bf16, both K-major, N = 256 (a token half), M = 128 (the weight rows)
+constexpr uint32_t PG_IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(256 >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
 
 __device__ __forceinline__ void pg_mma(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t accumulate) {
     asm volatile(
@@ -93,35 +98,6 @@ __device__ __forceinline__ void pg_load_q4(PgRawQ4 &r, const uint8_t *blk, int g
     r.q0 = ldg_nc_u4(blk + 16 + 32 * g);
     r.q1 = ldg_nc_u4(blk + 32 + 32 * g);
 }
-// y = (d*sc)*q - (dmin*m) (crates/rnb-cpu/src/quantize/dequant.rs:353-381), evaluated with one fused
-// multiply-add per element: the f32 value can differ from the two-rounding form in its last bit,
-// which survives the rounding to bf16 only next to a tie.
-__device__ __forceinline__ void pg_dequant_q4(const PgRawQ4 &r, int g, uint8_t *row_base, int rr) {
-    const float d = f16_bits_to_f32(r.hdr.x & 0xffffu), dmin = f16_bits_to_f32(r.hdr.x >> 16);
-    const uint32_t sc03 = r.hdr.y & 0x3f3f3f3fu, mn03 = r.hdr.z & 0x3f3f3f3fu;
-    const uint32_t sc47 = (r.hdr.w & 0x0f0f0f0fu) | (((r.hdr.y >> 6) & 0x03030303u) << 4);
-    const uint32_t mn47 = ((r.hdr.w >> 4) & 0x0f0f0f0fu) | (((r.hdr.z >> 6) & 0x03030303u) << 4);
-    const uint32_t scw = g < 2 ? sc03 : sc47, mnw = g < 2 ? mn03 : mn47;
-    const int sh = 16 * (g & 1);
-    const float d_lo = __fmul_rn(d, (float)((scw >> sh) & 0xffu)), d_hi = __fmul_rn(d, (float)((scw >> (sh + 8)) & 0xffu));
-    const float nm_lo = -__fmul_rn(dmin, (float)((mnw >> sh) & 0xffu)), nm_hi = -__fmul_rn(dmin, (float)((mnw >> (sh + 8)) & 0xffu));
-    const uint32_t qw[8] = {r.q0.x, r.q0.y, r.q0.z, r.q0.w, r.q1.x, r.q1.y, r.q1.z, r.q1.w};
-#pragma unroll
-    for (int c = 0; c < 4; c++) {   // chunk c: low nibbles of bytes 8c..8c+7; chunk c+4: their high nibbles
-        uint32_t lo[4], hi[4];
-#pragma unroll
-        for (int w = 0; w < 2; w++) {
-            const uint32_t word = qw[2 * c + w], l4 = word & 0x0f0f0f0fu, h4 = (word >> 4) & 0x0f0f0f0fu;
-            lo[2 * w] = pg_pack_bf16(__fmaf_rn(d_lo, pg_byte_to_f32(l4, 0), nm_lo), __fmaf_rn(d_lo, pg_byte_to_f32(l4, 1), nm_lo));
-            lo[2 * w + 1] = pg_pack_bf16(__fmaf_rn(d_lo, pg_byte_to_f32(l4, 2), nm_lo), __fmaf_rn(d_lo, pg_byte_to_f32(l4, 3), nm_lo));
-            hi[2 * w] = pg_pack_bf16(__fmaf_rn(d_hi, pg_byte_to_f32(h4, 0), nm_hi), __fmaf_rn(d_hi, pg_byte_to_f32(h4, 1), nm_hi));
-            hi[2 * w + 1] = pg_pack_bf16(__fmaf_rn(d_hi, pg_byte_to_f32(h4, 2), nm_hi), __fmaf_rn(d_hi, pg_byte_to_f32(h4, 3), nm_hi));
-        }
-        *reinterpret_cast<uint4 *>(row_base + ((c ^ rr) << 4)) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
-        *reinterpret_cast<uint4 *>(row_base + (((c + 4) ^ rr) << 4)) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
-    }
-}
-
 // Q6_K: group g of a block = elements 64g..64g+63 = for half n = g/2 the pair (q1,q2) if g even,
 // (q3,q4) if g odd, l = 0..31 each; y = (d*sc)*(q-32): dequant.rs:780-807.  Blocks are 210 bytes,
 // so rows are only 2-byte aligned: bytes are fetched as aligned words and funnel-shifted.
@@ -133,51 +109,6 @@ __device__ __forceinline__ uint32_t pg_ldg_u32_unaligned(const uint8_t *p) {
     if (sh == 0) return w0;
     return __funnelshift_r(w0, __ldg(w + 1), sh);
 }
-struct PgRawQ6 {
-    uint32_t ql_a[8], ql_b[8], qh[8];   // ql[64n + 0..31], ql[64n + 32..63], qh[32n + 0..31]
-    uint32_t sc[2];                      // scales 8n .. 8n+7 as bytes: word g&1 serves group g
-    float d;
-};
-// One load serves both groups of half n (the even group reads low nibbles, the odd one high).
-__device__ __forceinline__ void pg_load_q6(PgRawQ6 &r, const uint8_t *blk, int n) {
-#pragma unroll
-    for (int i = 0; i < 8; i++) {
-        r.ql_a[i] = pg_ldg_u32_unaligned(blk + 64 * n + 4 * i);
-        r.ql_b[i] = pg_ldg_u32_unaligned(blk + 64 * n + 32 + 4 * i);
-        r.qh[i] = pg_ldg_u32_unaligned(blk + 128 + 32 * n + 4 * i);
-    }
-    // scales of (first 32, second 32) elements of group g: is = 8n + 4(g&1) + {0,1} and + 2
-    r.sc[0] = pg_ldg_u32_unaligned(blk + 192 + 8 * n);
-    r.sc[1] = pg_ldg_u32_unaligned(blk + 196 + 8 * n);
-    r.d = f16_bits_to_f32(*reinterpret_cast<const uint16_t *>(blk + 208));
-}
-__device__ __forceinline__ void pg_dequant_q6(const PgRawQ6 &r, int g, uint8_t *row_base, int rr) {
-    const bool odd = g & 1;
-    // element e = 0..31 of the group: first kind (q1 or q3), scale byte e/16; e = 32..63: second kind, scale byte 2 + (e-32)/16
-    float ds[4];
-    const uint32_t scw = odd ? r.sc[1] : r.sc[0];
-#pragma unroll
-    for (int i = 0; i < 4; i++) ds[i] = __fmul_rn(r.d, (float)(int)(int8_t)((scw >> (8 * i)) & 0xffu));
-#pragma unroll
-    for (int c = 0; c < 4; c++) {   // chunk c: elements 8c..8c+7 (first kind); chunk c+4: elements 32+8c.. (second kind)
-        uint32_t o1[4], o2[4];
-#pragma unroll
-        for (int w = 0; w < 2; w++) {
-            const int i = 2 * c + w;
-            const uint32_t la = r.ql_a[i], lb = r.ql_b[i], hh = r.qh[i];
-            const uint32_t qa = odd ? (((la >> 4) & 0x0f0f0f0fu) | (hh & 0x30303030u)) : ((la & 0x0f0f0f0fu) | ((hh << 4) & 0x30303030u));
-            const uint32_t qb = odd ? (((lb >> 4) & 0x0f0f0f0fu) | ((hh >> 2) & 0x30303030u)) : ((lb & 0x0f0f0f0fu) | ((hh << 2) & 0x30303030u));
-            const float sa = ds[c >> 1], sb = ds[2 + (c >> 1)];
-            o1[2 * w] = pg_pack_bf16(__fmul_rn(sa, pg_byte_to_f32_m32(qa, 0)), __fmul_rn(sa, pg_byte_to_f32_m32(qa, 1)));
-            o1[2 * w + 1] = pg_pack_bf16(__fmul_rn(sa, pg_byte_to_f32_m32(qa, 2)), __fmul_rn(sa, pg_byte_to_f32_m32(qa, 3)));
-            o2[2 * w] = pg_pack_bf16(__fmul_rn(sb, pg_byte_to_f32_m32(qb, 0)), __fmul_rn(sb, pg_byte_to_f32_m32(qb, 1)));
-            o2[2 * w + 1] = pg_pack_bf16(__fmul_rn(sb, pg_byte_to_f32_m32(qb, 2)), __fmul_rn(sb, pg_byte_to_f32_m32(qb, 3)));
-        }
-        *reinterpret_cast<uint4 *>(row_base + ((c ^ rr) << 4)) = make_uint4(o1[0], o1[1], o1[2], o1[3]);
-        *reinterpret_cast<uint4 *>(row_base + (((c + 4) ^ rr) << 4)) = make_uint4(o2[0], o2[1], o2[2], o2[3]);
-    }
-}
-
 // f32 -> bf16 rows (activation), padded to a multiple of 8 columns by construction (cols % 256 == 0)
 RNB_GLOBAL void __launch_bounds__(256)
 f32_to_bf16_kernel(const float *__restrict__ x, uint16_t *__restrict__ y, size_t n) {
@@ -210,6 +141,18 @@ silu_mul_bf16_kernel(const float *__restrict__ gate, const float *__restrict__ u
     *reinterpret_cast<uint4 *>(y + i) = make_uint4(pg_pack_bf16(v[0], v[1]), pg_pack_bf16(v[2], v[3]), pg_pack_bf16(v[4], v[5]), pg_pack_bf16(v[6], v[7]));
 }
 
+// 128-byte, 64-byte aligned descriptor of the bf16 token matrix [seq][cols] (a CUtensorMap, kept
+// opaque here): boxes of 64 columns x 256 tokens, 128-byte swizzle, zero fill past the end.
+struct alignas(64) PgTensorMap {
+    unsigned long long opaque[16];
+};
+// tiled 2-D copy global -> shared; x (elements of the inner dimension) * 2 bytes must be a multiple of 16
+__device__ __forceinline__ void pg_tma_2d(uint32_t dst, const void *tmap, int x, int y, uint64_t *bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"(dst), "l"(tmap), "r"(x), "r"(y), "r"(smem_u32(bar))
+                 : "memory");
+}
+
 // Up to three matrices that share the token tile go out in one launch (q/k/v, gate/up): the
 // x dimension of the grid runs over the 256-row tiles of all of them.
 constexpr int PG_MAX_JOBS = 3;
@@ -223,193 +166,11 @@ struct PgJobs {
     int n;
 };
 
-// grid = (sum over jobs of ceil(rows / 256), ceil(seq / 256)); 288 threads; dynamic shared memory PG_SMEM.
-RNB_GLOBAL void __launch_bounds__(PG_THREADS, 1)
-prefill_gemm_kernel(const __grid_constant__ PgJobs jobs, const uint16_t *__restrict__ xb, int seq, int cols, int *__restrict__ err_flag) {
-    extern __shared__ __align__(1024) uint8_t pg_smem_raw[];
-    __shared__ __align__(8) uint64_t full[PG_STAGES], empty[PG_STAGES], done_bar;
-    __shared__ uint32_t tmem_base_slot;
-    __shared__ int s_failed;
-    pdl_launch_dependents();
-    pdl_wait();
-    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(pg_smem_raw) + 1023) & ~(uintptr_t)1023);
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    int jsel = 0;
-    for (int i = 1; i < jobs.n; i++)
-        if ((int)blockIdx.x >= jobs.j[i].tile0) jsel = i;
-    const PgJob &job = jobs.j[jsel];
-    const int rows = job.rows, TYPE = job.type;
-    const uint8_t *__restrict__ w = job.w;
-    float *__restrict__ y = job.y;
-    const uint32_t BLK = TYPE == TYPE_Q4_K ? Q4K_BYTES : Q6K_BYTES;
-    const int n0 = ((int)blockIdx.x - job.tile0) * PG_TILE_N, m0 = blockIdx.y * PG_TILE_M;
-    const int nb = cols >> 8, KT = cols / PG_K;
-    if (tid == 0) {
-        for (int s = 0; s < PG_STAGES; s++) {
-            mbar_init(&full[s], 8);    // one arrival per producer warp
-            mbar_init(&empty[s], 1);   // tcgen05.commit
-        }
-        mbar_init(&done_bar, 1);
-        mbar_fence_init();
-        s_failed = 0;
-    }
-    if (warp == 8) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)), "r"(512) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-    }
-    pg_fence_before();
-    __syncthreads();
-    pg_fence_after();
-    const uint32_t tmem_base = tmem_base_slot;
-    bool ok = true;
-
-    if (warp < 8) {
-        // ---- producers: thread t dequantises weight row t of the tile and brings in 8 of the 2048
-        // 16-byte chunks of the token tile (cp.async, one stage ahead of the dequantisation) ----
-        const size_t rb = (size_t)nb * BLK;
-        const uint8_t *wr = w + (size_t)min(n0 + tid, rows - 1) * rb;   // rows past the end repeat the last one (never stored)
-        uint8_t *const brow = smem + PG_TILE_BYTES + (tid >> 3) * 1024 + (tid & 7) * 128;
-        const int rr = tid & 7;
-        auto issue_a = [&](int kt) {
-            uint8_t *at = smem + (uint32_t)(kt % PG_STAGES) * PG_STAGE_BYTES;
-#pragma unroll
-            for (int i = 0; i < 8; i++) {
-                const int idx = i * 256 + tid, r = idx >> 3, c = idx & 7;
-                const int tok = m0 + r;
-                const uint16_t *src = xb + (size_t)min(tok, seq - 1) * cols + (size_t)kt * PG_K + c * 8;
-                const uint32_t nbytes = tok < seq ? 16u : 0u;   // rows past the end are zero-filled
-                asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(at) + pg_swz(r, c)), "l"(src), "r"(nbytes) : "memory");
-            }
-            asm volatile("cp.async.commit_group;" ::: "memory");
-        };
-        // stage kt: token tile of kt + 1 goes out first, then this stage's weights are dequantised
-        auto stage_head = [&](int kt) -> bool {
-            if (kt + 1 < KT) {
-                if (!mbar_wait_bounded(&empty[(kt + 1) % PG_STAGES], (uint32_t)((((kt + 1) / PG_STAGES) & 1) ^ 1))) return false;
-                issue_a(kt + 1);
-            }
-            return true;
-        };
-        auto stage_tail = [&](int kt) {
-            if (kt + 1 < KT) asm volatile("cp.async.wait_group 1;" ::: "memory");
-            else asm volatile("cp.async.wait_group 0;" ::: "memory");
-            pg_proxy_fence();
-            __syncwarp();
-            if (lane == 0) pg_arrive(&full[kt % PG_STAGES]);
-        };
-        ok = mbar_wait_bounded(&empty[0], 1u);
-        if (ok) issue_a(0);
-        if (TYPE == TYPE_Q4_K) {
-            PgRawQ4 cur, nxt;
-            pg_load_q4(cur, wr, 0);
-            for (int kt = 0; kt < KT && ok; kt++) {
-                if (kt + 1 < KT) pg_load_q4(nxt, wr + (size_t)((kt + 1) >> 2) * BLK, (kt + 1) & 3);
-                ok = stage_head(kt);
-                if (!ok) break;
-                pg_dequant_q4(cur, kt & 3, brow + (uint32_t)(kt % PG_STAGES) * PG_STAGE_BYTES, rr);
-                stage_tail(kt);
-                cur = nxt;
-            }
-        } else {
-            PgRawQ6 cur, nxt;
-            pg_load_q6(cur, wr, 0);
-            for (int kt = 0; kt < KT && ok; kt++) {
-                // a half block (128 elements) serves two stages: fetch the next half two stages ahead
-                if (!(kt & 1) && kt + 2 < KT) pg_load_q6(nxt, wr + (size_t)((kt + 2) >> 2) * BLK, ((kt + 2) >> 1) & 1);
-                ok = stage_head(kt);
-                if (!ok) break;
-                pg_dequant_q6(cur, kt & 3, brow + (uint32_t)(kt % PG_STAGES) * PG_STAGE_BYTES, rr);
-                stage_tail(kt);
-                if (kt & 1) cur = nxt;
-            }
-        }
-        asm volatile("cp.async.wait_group 0;" ::: "memory");
-    } else {
-        // ---- MMA issuer ----
-        for (int kt = 0; kt < KT && ok; kt++) {
-            const int s = kt % PG_STAGES;
-            ok = mbar_wait_bounded(&full[s], (uint32_t)((kt / PG_STAGES) & 1));
-            if (!ok) break;
-            pg_fence_after();
-            if (lane == 0) {
-                const uint32_t a_addr = smem_u32(smem + (uint32_t)s * PG_STAGE_BYTES), b_addr = a_addr + PG_TILE_BYTES;
-#pragma unroll
-                for (int mh = 0; mh < 2; mh++)
-#pragma unroll
-                    for (int k = 0; k < 4; k++)
-                        pg_mma(tmem_base + (uint32_t)mh * 256u, pg_smem_desc(a_addr + (uint32_t)mh * 128u * 128u + (uint32_t)k * 32u),
-                               pg_smem_desc(b_addr + (uint32_t)k * 32u), (kt > 0 || k > 0) ? 1u : 0u);
-                pg_commit(&empty[s]);
-            }
-            __syncwarp();
-        }
-        if (ok && lane == 0) pg_commit(&done_bar);
-        __syncwarp();
-    }
-    if (!ok) atomicExch(&s_failed, 1);
-
-    // ---- epilogue: warps 0-7, accumulator = warp / 4, TMEM lane quarter = warp % 4 ----
-    if (warp < 8) {
-        bool fin = ok && mbar_wait_bounded(&done_bar, 0u);
-        if (!fin) atomicExch(&s_failed, 1);
-        pg_fence_after();
-        if (fin) {
-            const int acc = warp >> 2, q = warp & 3;
-            const int tok = m0 + acc * 128 + q * 32 + lane;
-#pragma unroll 1
-            for (int cc = 0; cc < PG_TILE_N / 32; cc++) {
-                uint32_t v[32];
-                pg_tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * 256 + cc * 32), v);
-                const int nn = n0 + cc * 32;
-                if (tok < seq) {
-                    float *dst = y + (size_t)tok * rows + nn;
-                    if (nn + 32 <= rows && (rows & 3) == 0) {   // 16-byte stores need rows % 4 == 0
-#pragma unroll
-                        for (int i = 0; i < 8; i++)
-                            *reinterpret_cast<float4 *>(dst + 4 * i) = make_float4(__uint_as_float(v[4 * i]), __uint_as_float(v[4 * i + 1]),
-                                                                                   __uint_as_float(v[4 * i + 2]), __uint_as_float(v[4 * i + 3]));
-                    } else {
-                        for (int i = 0; i < 32; i++)
-                            if (nn + i < rows) dst[i] = __uint_as_float(v[i]);
-                    }
-                }
-            }
-        }
-    }
-    pg_fence_before();
-    __syncthreads();
-    if (warp == 8) {
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
-        if (lane == 0 && s_failed && err_flag) atomicExch(err_flag, DEV_ERR_GEMM_TIMEOUT);
-    }
-}
-
-// =================================================================================================
-// Wide-token form: one CTA owns a 512-token x 128-row output tile (two accumulators of 128 rows x
-// 256 tokens = all 512 columns of tensor memory; the weights are the M operand).  A dequantised weight tile now serves twice
-// as many tokens, which matters because the dequantising warps, not the tensor pipe, bound the
-// 256 x 256 form.  The token tile (512 x 64 bf16 = 64 KB per stage) is brought in by two tiled
-// TMA copies with the 128-byte swizzle (rows past the end of the batch read as zeros), so the
-// eight producer warps only dequantise: thread t owns weight row t / 2 and half t % 2 of the
-// 64-element group (Q4_K: low or high nibbles; Q6_K: the first or second 32 elements).  Two
-// stages of 80 KB; a stage is refilled as soon as the MMAs that read it have been committed.
-constexpr int PGW_TOK = 512;
-constexpr int PGW_ROWS = 128;
-constexpr int PGW_STAGES = 2;
-constexpr uint32_t PGW_A_BYTES = PGW_TOK * 128;    // token tile of a stage
-constexpr uint32_t PGW_B_BYTES = PGW_ROWS * 128;   // weight tile of a stage
-constexpr uint32_t PGW_STAGE_BYTES = PGW_A_BYTES + PGW_B_BYTES;
-constexpr size_t PGW_SMEM = (size_t)PGW_STAGES * PGW_STAGE_BYTES + 1024;
-constexpr int PGW_BOX_ROWS = 256;                  // tokens per TMA copy
-// tiled 2-D copy global -> shared; x (elements of the inner dimension) * 2 bytes must be a multiple of 16
-__device__ __forceinline__ void pgw_tma_2d(uint32_t dst, const void *tmap, int x, int y, uint64_t *bar) {
-    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-                 ::"r"(dst), "l"(tmap), "r"(x), "r"(y), "r"(smem_u32(bar))
-                 : "memory");
-}
-
 // Half h of a Q4_K group: h = 0 -> low nibbles (chunks 0-3), h = 1 -> high nibbles (chunks 4-7).
-__device__ __forceinline__ void pgw_dequant_q4(const PgRawQ4 &r, int g, int h, uint8_t *row_base, int rr) {
+// y = (d*sc)*q - (dmin*m) (crates/rnb-cpu/src/quantize/dequant.rs:353-381), evaluated with one fused
+// multiply-add per element: the f32 value can differ from the two-rounding form in its last bit,
+// which survives the rounding to bf16 only next to a tie.
+__device__ __forceinline__ void pg_dequant_q4(const PgRawQ4 &r, int g, int h, uint8_t *row_base, int rr) {
     const float d = f16_bits_to_f32(r.hdr.x & 0xffffu), dmin = f16_bits_to_f32(r.hdr.x >> 16);
     const uint32_t sc03 = r.hdr.y & 0x3f3f3f3fu, mn03 = r.hdr.z & 0x3f3f3f3fu;
     const uint32_t sc47 = (r.hdr.w & 0x0f0f0f0fu) | (((r.hdr.y >> 6) & 0x03030303u) << 4);
@@ -432,12 +193,12 @@ __device__ __forceinline__ void pgw_dequant_q4(const PgRawQ4 &r, int g, int h, u
     }
 }
 // Half h of the Q6_K groups of half-block n: h = 0 -> ql[64n .. 64n+31] (q1 / q3), h = 1 -> ql[64n+32 ..] (q2 / q4).
-struct PgwRawQ6 {
+struct PgRawQ6 {
     uint32_t ql[8], qh[8];
     uint32_t sc[2];
     float d;
 };
-__device__ __forceinline__ void pgw_load_q6(PgwRawQ6 &r, const uint8_t *blk, int n, int h) {
+__device__ __forceinline__ void pg_load_q6(PgRawQ6 &r, const uint8_t *blk, int n, int h) {
 #pragma unroll
     for (int i = 0; i < 8; i++) {
         r.ql[i] = pg_ldg_u32_unaligned(blk + 64 * n + 32 * h + 4 * i);
@@ -447,7 +208,7 @@ __device__ __forceinline__ void pgw_load_q6(PgwRawQ6 &r, const uint8_t *blk, int
     r.sc[1] = pg_ldg_u32_unaligned(blk + 196 + 8 * n);
     r.d = f16_bits_to_f32(*reinterpret_cast<const uint16_t *>(blk + 208));
 }
-__device__ __forceinline__ void pgw_dequant_q6(const PgwRawQ6 &r, int g, int h, uint8_t *row_base, int rr) {
+__device__ __forceinline__ void pg_dequant_q6(const PgRawQ6 &r, int g, int h, uint8_t *row_base, int rr) {
     const bool odd = g & 1;
     const uint32_t scw = (odd ? r.sc[1] : r.sc[0]) >> (16 * h);   // this half's two scale bytes
     const float ds0 = __fmul_rn(r.d, (float)(int)(int8_t)(scw & 0xffu)), ds1 = __fmul_rn(r.d, (float)(int)(int8_t)((scw >> 8) & 0xffu));
@@ -469,18 +230,13 @@ __device__ __forceinline__ void pgw_dequant_q6(const PgwRawQ6 &r, int g, int h, 
     }
 }
 
-// 128-byte, 64-byte aligned descriptor of the bf16 token matrix [seq][cols] (a CUtensorMap, kept
-// opaque here): boxes of 64 columns x 256 tokens, 128-byte swizzle, zero fill past the end.
-struct alignas(64) PgTensorMap {
-    unsigned long long opaque[16];
-};
 
-// grid = (sum over jobs of ceil(rows / 128), ceil(seq / 512)); 288 threads; dynamic shared memory PGW_SMEM.
+// grid = (sum over jobs of ceil(rows / 128), ceil(seq / 512)); 288 threads; dynamic shared memory PG_SMEM.
 RNB_GLOBAL void __launch_bounds__(PG_THREADS, 1)
-prefill_gemm_wide_kernel(const __grid_constant__ PgJobs jobs, const __grid_constant__ PgTensorMap tmap_x, int seq, int cols,
+prefill_gemm_kernel(const __grid_constant__ PgJobs jobs, const __grid_constant__ PgTensorMap tmap_x, int seq, int cols,
                          int *__restrict__ err_flag) {
     extern __shared__ __align__(1024) uint8_t pg_smem_raw[];
-    __shared__ __align__(8) uint64_t full[PGW_STAGES], empty[PGW_STAGES], done_bar;
+    __shared__ __align__(8) uint64_t full[PG_STAGES], empty[PG_STAGES], done_bar;
     __shared__ uint32_t tmem_base_slot;
     __shared__ int s_failed;
     pdl_launch_dependents();
@@ -495,10 +251,10 @@ prefill_gemm_wide_kernel(const __grid_constant__ PgJobs jobs, const __grid_const
     const uint8_t *__restrict__ w = job.w;
     float *__restrict__ y = job.y;
     const uint32_t BLK = TYPE == TYPE_Q4_K ? Q4K_BYTES : Q6K_BYTES;
-    const int n0 = ((int)blockIdx.x - job.tile0) * PGW_ROWS, m0 = blockIdx.y * PGW_TOK;
+    const int n0 = ((int)blockIdx.x - job.tile0) * PG_ROWS, m0 = blockIdx.y * PG_TOK;
     const int nb = cols >> 8, KT = cols / PG_K;
     if (tid == 0) {
-        for (int s = 0; s < PGW_STAGES; s++) {
+        for (int s = 0; s < PG_STAGES; s++) {
             mbar_init(&full[s], 9);    // one arrival per producer warp + the thread that issues the token copies
             mbar_init(&empty[s], 1);   // tcgen05.commit
         }
@@ -520,24 +276,24 @@ prefill_gemm_wide_kernel(const __grid_constant__ PgJobs jobs, const __grid_const
         const int row = tid >> 1, h = tid & 1, rr = row & 7;
         const size_t rb = (size_t)nb * BLK;
         const uint8_t *wr = w + (size_t)min(n0 + row, rows - 1) * rb;   // rows past the end repeat the last one (never stored)
-        uint8_t *const brow = smem + PGW_A_BYTES + (row >> 3) * 1024 + rr * 128;
+        uint8_t *const brow = smem + PG_A_BYTES + (row >> 3) * 1024 + rr * 128;
         // token tile of stage kt: thread 0 announces the bytes and issues the two copies
         auto issue_tokens = [&](int kt) {
             if (tid != 0) return;
-            const int s = kt % PGW_STAGES;
-            const uint32_t dst = smem_u32(smem + (uint32_t)s * PGW_STAGE_BYTES);
-            mbar_arrive_expect_tx(&full[s], PGW_A_BYTES);
+            const int s = kt % PG_STAGES;
+            const uint32_t dst = smem_u32(smem + (uint32_t)s * PG_STAGE_BYTES);
+            mbar_arrive_expect_tx(&full[s], PG_A_BYTES);
 #pragma unroll
-            for (int i = 0; i < PGW_TOK / PGW_BOX_ROWS; i++)
-                pgw_tma_2d(dst + (uint32_t)i * (PGW_BOX_ROWS * 128), &tmap_x, kt * PG_K, m0 + i * PGW_BOX_ROWS, &full[s]);
+            for (int i = 0; i < PG_TOK / PG_BOX_ROWS; i++)
+                pg_tma_2d(dst + (uint32_t)i * (PG_BOX_ROWS * 128), &tmap_x, kt * PG_K, m0 + i * PG_BOX_ROWS, &full[s]);
         };
         auto stage_tail = [&](int kt) -> bool {
             pg_proxy_fence();
             __syncwarp();
-            if (lane == 0) pg_arrive(&full[kt % PGW_STAGES]);
+            if (lane == 0) pg_arrive(&full[kt % PG_STAGES]);
             if (kt + 1 < KT) {
                 // the next stage may be written once the MMAs that read it have been committed
-                if (!mbar_wait_bounded(&empty[(kt + 1) % PGW_STAGES], (uint32_t)((((kt + 1) / PGW_STAGES) & 1) ^ 1))) return false;
+                if (!mbar_wait_bounded(&empty[(kt + 1) % PG_STAGES], (uint32_t)((((kt + 1) / PG_STAGES) & 1) ^ 1))) return false;
                 issue_tokens(kt + 1);
             }
             return true;
@@ -549,17 +305,17 @@ prefill_gemm_wide_kernel(const __grid_constant__ PgJobs jobs, const __grid_const
             pg_load_q4(cur, wr, 0);
             for (int kt = 0; kt < KT && ok; kt++) {
                 if (kt + 1 < KT) pg_load_q4(nxt, wr + (size_t)((kt + 1) >> 2) * BLK, (kt + 1) & 3);
-                pgw_dequant_q4(cur, kt & 3, h, brow + (uint32_t)(kt % PGW_STAGES) * PGW_STAGE_BYTES, rr);
+                pg_dequant_q4(cur, kt & 3, h, brow + (uint32_t)(kt % PG_STAGES) * PG_STAGE_BYTES, rr);
                 ok = stage_tail(kt);
                 cur = nxt;
             }
         } else {
-            PgwRawQ6 cur, nxt;
-            pgw_load_q6(cur, wr, 0, h);
+            PgRawQ6 cur, nxt;
+            pg_load_q6(cur, wr, 0, h);
             for (int kt = 0; kt < KT && ok; kt++) {
                 // a half block (128 elements) serves two stages: fetch the next half two stages ahead
-                if (!(kt & 1) && kt + 2 < KT) pgw_load_q6(nxt, wr + (size_t)((kt + 2) >> 2) * BLK, ((kt + 2) >> 1) & 1, h);
-                pgw_dequant_q6(cur, kt & 3, h, brow + (uint32_t)(kt % PGW_STAGES) * PGW_STAGE_BYTES, rr);
+                if (!(kt & 1) && kt + 2 < KT) pg_load_q6(nxt, wr + (size_t)((kt + 2) >> 2) * BLK, ((kt + 2) >> 1) & 1, h);
+                pg_dequant_q6(cur, kt & 3, h, brow + (uint32_t)(kt % PG_STAGES) * PG_STAGE_BYTES, rr);
                 ok = stage_tail(kt);
                 if (kt & 1) cur = nxt;
             }
@@ -569,12 +325,12 @@ prefill_gemm_wide_kernel(const __grid_constant__ PgJobs jobs, const __grid_const
         // 128 TMEM lanes), a token half the N operand (256 columns): fewer shared-memory reads per flop than four
         // 128 x 128 products ----
         for (int kt = 0; kt < KT && ok; kt++) {
-            const int s = kt % PGW_STAGES;
-            ok = mbar_wait_bounded(&full[s], (uint32_t)((kt / PGW_STAGES) & 1));
+            const int s = kt % PG_STAGES;
+            ok = mbar_wait_bounded(&full[s], (uint32_t)((kt / PG_STAGES) & 1));
             if (!ok) break;
             pg_fence_after();
             if (lane == 0) {
-                const uint32_t x_addr = smem_u32(smem + (uint32_t)s * PGW_STAGE_BYTES), w_addr = x_addr + PGW_A_BYTES;
+                const uint32_t x_addr = smem_u32(smem + (uint32_t)s * PG_STAGE_BYTES), w_addr = x_addr + PG_A_BYTES;
 #pragma unroll
                 for (int nh = 0; nh < 2; nh++)
 #pragma unroll
@@ -597,7 +353,7 @@ prefill_gemm_wide_kernel(const __grid_constant__ PgJobs jobs, const __grid_const
         // token copies that were announced but never consumed must land before the CTA exits
         if (!fin) {
             atomicExch(&s_failed, 1);
-            for (int s = 0; s < PGW_STAGES; s++) mbar_wait_bounded(&full[s], 0u);
+            for (int s = 0; s < PG_STAGES; s++) mbar_wait_bounded(&full[s], 0u);
         }
         pg_fence_after();
         if (fin) {
