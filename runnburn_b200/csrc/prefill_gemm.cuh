@@ -88,15 +88,21 @@ __device__ __forceinline__ uint32_t pg_pack_bf16(float lo, float hi) {
     return *reinterpret_cast<const uint32_t *>(&v);
 }
 
-// ---- weight group (64 elements of one row) -> 8 chunks of 8 bf16 ------------------------------
+// ---- raw bytes of a weight group (64 elements of one row) --------------------------------------
+// The two threads of a row fetch disjoint halves of what both need (the block header once per
+// block, the group's 32 qs bytes every stage) and exchange them by shuffle when the bytes are
+// used: every byte of a weight tile crosses the L2 -> SM path once.
 struct PgRawQ4 {
-    uint4 hdr;     // d, dmin, 12 scale bytes
-    uint4 q0, q1;  // 32 qs bytes of the group
+    uint2 hdr_half;   // bytes 8h .. 8h+7 of {d, dmin, 12 scale bytes}; valid for group 0 of a block
+    uint4 qm;         // qs bytes 16h .. 16h+15 of the group
 };
-__device__ __forceinline__ void pg_load_q4(PgRawQ4 &r, const uint8_t *blk, int g) {
-    r.hdr = ldg_nc_u4(blk);
-    r.q0 = ldg_nc_u4(blk + 16 + 32 * g);
-    r.q1 = ldg_nc_u4(blk + 32 + 32 * g);
+__device__ __forceinline__ void pg_load_q4(PgRawQ4 &r, const uint8_t *blk, int g, int h) {
+    if (g == 0) r.hdr_half = ldg_nc_u2(blk + 8 * h);
+    r.qm = ldg_nc_u4(blk + 16 + 32 * g + 16 * h);
+}
+__device__ __forceinline__ uint4 pg_pair_exchange(const uint4 &mine) {
+    return make_uint4(__shfl_xor_sync(0xffffffffu, mine.x, 1), __shfl_xor_sync(0xffffffffu, mine.y, 1), __shfl_xor_sync(0xffffffffu, mine.z, 1),
+                      __shfl_xor_sync(0xffffffffu, mine.w, 1));
 }
 // Q6_K: group g of a block = elements 64g..64g+63 = for half n = g/2 the pair (q1,q2) if g even,
 // (q3,q4) if g odd, l = 0..31 each; y = (d*sc)*(q-32): dequant.rs:780-807.  Blocks are 210 bytes,
@@ -170,15 +176,15 @@ struct PgJobs {
 // y = (d*sc)*q - (dmin*m) (crates/rnb-cpu/src/quantize/dequant.rs:353-381), evaluated with one fused
 // multiply-add per element: the f32 value can differ from the two-rounding form in its last bit,
 // which survives the rounding to bf16 only next to a tie.
-__device__ __forceinline__ void pg_dequant_q4(const PgRawQ4 &r, int g, int h, uint8_t *row_base, int rr) {
-    const float d = f16_bits_to_f32(r.hdr.x & 0xffffu), dmin = f16_bits_to_f32(r.hdr.x >> 16);
-    const uint32_t sc03 = r.hdr.y & 0x3f3f3f3fu, mn03 = r.hdr.z & 0x3f3f3f3fu;
-    const uint32_t sc47 = (r.hdr.w & 0x0f0f0f0fu) | (((r.hdr.y >> 6) & 0x03030303u) << 4);
-    const uint32_t mn47 = ((r.hdr.w >> 4) & 0x0f0f0f0fu) | (((r.hdr.z >> 6) & 0x03030303u) << 4);
+__device__ __forceinline__ void pg_dequant_q4(const uint4 &hdr, const uint4 &q0, const uint4 &q1, int g, int h, uint8_t *row_base, int rr) {
+    const float d = f16_bits_to_f32(hdr.x & 0xffffu), dmin = f16_bits_to_f32(hdr.x >> 16);
+    const uint32_t sc03 = hdr.y & 0x3f3f3f3fu, mn03 = hdr.z & 0x3f3f3f3fu;
+    const uint32_t sc47 = (hdr.w & 0x0f0f0f0fu) | (((hdr.y >> 6) & 0x03030303u) << 4);
+    const uint32_t mn47 = ((hdr.w >> 4) & 0x0f0f0f0fu) | (((hdr.z >> 6) & 0x03030303u) << 4);
     const uint32_t scw = g < 2 ? sc03 : sc47, mnw = g < 2 ? mn03 : mn47;
     const int sh = 16 * (g & 1) + 8 * h;
     const float ds = __fmul_rn(d, (float)((scw >> sh) & 0xffu)), nm = -__fmul_rn(dmin, (float)((mnw >> sh) & 0xffu));
-    const uint32_t qw[8] = {r.q0.x, r.q0.y, r.q0.z, r.q0.w, r.q1.x, r.q1.y, r.q1.z, r.q1.w};
+    const uint32_t qw[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
     const int nsh = 4 * h;
 #pragma unroll
     for (int c = 0; c < 4; c++) {
@@ -194,7 +200,7 @@ __device__ __forceinline__ void pg_dequant_q4(const PgRawQ4 &r, int g, int h, ui
 }
 // Half h of the Q6_K groups of half-block n: h = 0 -> ql[64n .. 64n+31] (q1 / q3), h = 1 -> ql[64n+32 ..] (q2 / q4).
 struct PgRawQ6 {
-    uint32_t ql[8], qh[8];
+    uint32_t ql[8], qh[4];   // qh: words 4h .. 4h+3 of the half-block's 32 bytes, the pair exchanges them when used
     uint32_t sc[2];
     float d;
 };
@@ -202,7 +208,7 @@ __device__ __forceinline__ void pg_load_q6(PgRawQ6 &r, const uint8_t *blk, int n
 #pragma unroll
     for (int i = 0; i < 8; i++) {
         r.ql[i] = pg_ldg_u32_unaligned(blk + 64 * n + 32 * h + 4 * i);
-        r.qh[i] = pg_ldg_u32_unaligned(blk + 128 + 32 * n + 4 * i);
+        if (i < 4) r.qh[i] = pg_ldg_u32_unaligned(blk + 128 + 32 * n + 16 * h + 4 * i);
     }
     r.sc[0] = pg_ldg_u32_unaligned(blk + 192 + 8 * n);
     r.sc[1] = pg_ldg_u32_unaligned(blk + 196 + 8 * n);
@@ -210,6 +216,13 @@ __device__ __forceinline__ void pg_load_q6(PgRawQ6 &r, const uint8_t *blk, int n
 }
 __device__ __forceinline__ void pg_dequant_q6(const PgRawQ6 &r, int g, int h, uint8_t *row_base, int rr) {
     const bool odd = g & 1;
+    uint32_t qh[8];
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const uint32_t other = __shfl_xor_sync(0xffffffffu, r.qh[i], 1);
+        qh[i] = h ? other : r.qh[i];
+        qh[4 + i] = h ? r.qh[i] : other;
+    }
     const uint32_t scw = (odd ? r.sc[1] : r.sc[0]) >> (16 * h);   // this half's two scale bytes
     const float ds0 = __fmul_rn(r.d, (float)(int)(int8_t)(scw & 0xffu)), ds1 = __fmul_rn(r.d, (float)(int)(int8_t)((scw >> 8) & 0xffu));
     // the two high bits of this half's elements sit at bit 2h (even group) or 4 + 2h (odd group) of qh
@@ -222,7 +235,7 @@ __device__ __forceinline__ void pg_dequant_q6(const PgRawQ6 &r, int g, int h, ui
         for (int w = 0; w < 2; w++) {
             const int i = 2 * c + w;
             const uint32_t lo = (odd ? (r.ql[i] >> 4) : r.ql[i]) & 0x0f0f0f0fu;
-            const uint32_t q = lo | (((r.qh[i] >> hs) << 4) & 0x30303030u);
+            const uint32_t q = lo | (((qh[i] >> hs) << 4) & 0x30303030u);
             o[2 * w] = pg_pack_bf16(__fmul_rn(sa, pg_byte_to_f32_m32(q, 0)), __fmul_rn(sa, pg_byte_to_f32_m32(q, 1)));
             o[2 * w + 1] = pg_pack_bf16(__fmul_rn(sa, pg_byte_to_f32_m32(q, 2)), __fmul_rn(sa, pg_byte_to_f32_m32(q, 3)));
         }
@@ -302,11 +315,18 @@ prefill_gemm_kernel(const __grid_constant__ PgJobs jobs, const __grid_constant__
         if (ok) issue_tokens(0);
         if (TYPE == TYPE_Q4_K) {
             PgRawQ4 cur, nxt;
-            pg_load_q4(cur, wr, 0);
+            uint4 hdr = make_uint4(0u, 0u, 0u, 0u);
+            pg_load_q4(cur, wr, 0, h);
             for (int kt = 0; kt < KT && ok; kt++) {
-                if (kt + 1 < KT) pg_load_q4(nxt, wr + (size_t)((kt + 1) >> 2) * BLK, (kt + 1) & 3);
-                pg_dequant_q4(cur, kt & 3, h, brow + (uint32_t)(kt % PG_STAGES) * PG_STAGE_BYTES, rr);
-                ok = stage_tail(kt);
+                const int g = kt & 3;
+                if (kt + 1 < KT) pg_load_q4(nxt, wr + (size_t)((kt + 1) >> 2) * BLK, (kt + 1) & 3, h);
+                if (g == 0) {   // a new block: put the header halves together
+                    const uint32_t ox = __shfl_xor_sync(0xffffffffu, cur.hdr_half.x, 1), oy = __shfl_xor_sync(0xffffffffu, cur.hdr_half.y, 1);
+                    hdr = h ? make_uint4(ox, oy, cur.hdr_half.x, cur.hdr_half.y) : make_uint4(cur.hdr_half.x, cur.hdr_half.y, ox, oy);
+                }
+                const uint4 other = pg_pair_exchange(cur.qm);
+                pg_dequant_q4(hdr, h ? other : cur.qm, h ? cur.qm : other, g, h, brow + (uint32_t)(kt % PG_STAGES) * PG_STAGE_BYTES, rr);
+                ok = __all_sync(0xffffffffu, stage_tail(kt));   // warp-uniform: the shuffles above need the whole warp
                 cur = nxt;
             }
         } else {
@@ -316,7 +336,7 @@ prefill_gemm_kernel(const __grid_constant__ PgJobs jobs, const __grid_constant__
                 // a half block (128 elements) serves two stages: fetch the next half two stages ahead
                 if (!(kt & 1) && kt + 2 < KT) pg_load_q6(nxt, wr + (size_t)((kt + 2) >> 2) * BLK, ((kt + 2) >> 1) & 1, h);
                 pg_dequant_q6(cur, kt & 3, h, brow + (uint32_t)(kt % PG_STAGES) * PG_STAGE_BYTES, rr);
-                ok = stage_tail(kt);
+                ok = __all_sync(0xffffffffu, stage_tail(kt));   // warp-uniform: the shuffles in the dequantisation need the whole warp
                 if (kt & 1) cur = nxt;
             }
         }
