@@ -11,18 +11,38 @@ namespace rnb {
 // crates/rnb-cpu/src/gemm/f32_gemv.rs:215-237,266-275): thread j owns accumulator lane j of
 // the two 8-lane FMA registers, then lanes are folded 8, 4, 2, 1 apart.  Bit-identical
 // logits are what makes the selected expert ids identical.  hidden % 16 == 0.
+// The loads of a batch of 32 steps are issued together (the chain of FMAs is latency-bound on its
+// loads otherwise); the first batch of router weights is fetched before the wait on the previous
+// kernel, which only the hidden state depends on.  Any number of experts per CTA (blockDim / 16).
 RNB_GLOBAL void __launch_bounds__(128)
 router_logits_kernel(const float *__restrict__ w, const float *__restrict__ h, int n_expert,
                      int hidden, float *__restrict__ logits) {
     pdl_launch_dependents();
-    pdl_wait();
+    constexpr int B = 32;   // steps per batch: elements j, j + 16, ... j + 16 * 31
     const int j = threadIdx.x & 15;
     const int e = blockIdx.x * (blockDim.x >> 4) + (threadIdx.x >> 4);
     const bool live = e < n_expert;
     const float *wr = w + (size_t)(live ? e : 0) * hidden;
+    float wv[B];
+    const int full = hidden / (16 * B) * (16 * B);
+    if (full > 0) {
+#pragma unroll
+        for (int u = 0; u < B; u++) wv[u] = __ldg(wr + u * 16 + j);
+    }
+    pdl_wait();
     float acc = 0.0f;
-#pragma unroll 8
-    for (int i = j; i < hidden; i += 16) acc = __fmaf_rn(wr[i], h[i], acc);
+    for (int base = 0; base < full; base += 16 * B) {
+        float hv[B];
+#pragma unroll
+        for (int u = 0; u < B; u++) hv[u] = h[base + u * 16 + j];
+#pragma unroll
+        for (int u = 0; u < B; u++) acc = __fmaf_rn(wv[u], hv[u], acc);
+        if (base + 16 * B < full) {
+#pragma unroll
+            for (int u = 0; u < B; u++) wv[u] = __ldg(wr + base + 16 * B + u * 16 + j);
+        }
+    }
+    for (int i = full + j; i < hidden; i += 16) acc = __fmaf_rn(wr[i], h[i], acc);
     acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 8));
     acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 4));
     acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 2));
