@@ -316,12 +316,20 @@ inline int launch_quantize_q8k(cudaStream_t s, const float *x, size_t cols, size
 
 inline int flash_decode_default_chunks(size_t kv_len, size_t num_kv_heads, int sm_count) {
     if (kv_len == 0) return 1;
+    static const bool per_sm_given = [] {
+        const char *e = getenv("RNB_B200_FD_CTAS_PER_SM");
+        return e && *e;
+    }();
     static const int per_sm = [] {
         const char *e = getenv("RNB_B200_FD_CTAS_PER_SM");
         const int v = (e && *e) ? atoi(e) : 4;
         return v < 1 ? 1 : (v > 16 ? 16 : v);
     }();
     long want = (long)(per_sm * sm_count) / (long)(num_kv_heads ? num_kv_heads : 1);
+    // The merge kernel's cost grows with the chunks per head: with four or more KV heads on this GPU
+    // half an SM count of chunks per head already fills the machine (measured: Llama-3-8B shape at
+    // 4096 and the 4-KV-head MoE shape at 8192 are both fastest at 74 chunks per head).
+    if (!per_sm_given && num_kv_heads >= 4 && want > sm_count / 2) want = sm_count / 2;
     long max_c = (long)((kv_len + 31) / 32);
     if (want > max_c) want = max_c;
     if (want > FD_MAX_CHUNKS) want = FD_MAX_CHUNKS;

@@ -14,9 +14,8 @@ namespace rnb {
 // The loads of a batch of 32 steps are issued together (the chain of FMAs is latency-bound on its
 // loads otherwise); the first batch of router weights is fetched before the wait on the previous
 // kernel, which only the hidden state depends on.  Any number of experts per CTA (blockDim / 16).
-RNB_GLOBAL void __launch_bounds__(128)
-router_logits_kernel(const float *__restrict__ w, const float *__restrict__ h, int n_expert,
-                     int hidden, float *__restrict__ logits) {
+__device__ __forceinline__ void router_logits_body(const float *__restrict__ w, const float *__restrict__ h, int n_expert,
+                                                   int hidden, float *logits) {
     pdl_launch_dependents();
     constexpr int B = 32;   // steps per batch: elements j, j + 16, ... j + 16 * 31
     const int j = threadIdx.x & 15;
@@ -49,6 +48,11 @@ router_logits_kernel(const float *__restrict__ w, const float *__restrict__ h, i
     acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 1));
     if (live && j == 0) logits[e] = acc;
 }
+RNB_GLOBAL void __launch_bounds__(128)
+router_logits_kernel(const float *__restrict__ w, const float *__restrict__ h, int n_expert,
+                     int hidden, float *__restrict__ logits) {
+    router_logits_body(w, h, n_expert, hidden, logits);
+}
 
 // Top-k by logit (descending, ties -> lower expert id), weights = softmax over the selected
 // logits in rank order: crates/rnb-llm/src/engine/models/shared_expert_moe/routing.rs:18-62;
@@ -56,12 +60,12 @@ router_logits_kernel(const float *__restrict__ w, const float *__restrict__ h, i
 // (crates/rnb-backend/cuda/cuda/kernels/quant_batch_and_ops.cuh:4782-4912).
 // One warp per token; n_expert <= 1024, top_k <= 32.  exp is taken in double and rounded once.
 // Returns the id this lane selected (lane r holds rank r; other lanes return 0).
-__device__ __forceinline__ uint32_t moe_route_topk_warp(const float *__restrict__ logits, int n_expert, int top_k,
+__device__ __forceinline__ uint32_t moe_route_topk_warp(const float *logits, int token, int n_expert, int top_k,
                                                         uint32_t *__restrict__ ids_out, float *__restrict__ weights_out) {
     const int lane = threadIdx.x;
-    const float *lg = logits + (size_t)blockIdx.x * n_expert;
-    uint32_t *ids = ids_out + (size_t)blockIdx.x * top_k;
-    float *wts = weights_out + (size_t)blockIdx.x * top_k;
+    const float *lg = logits + (size_t)token * n_expert;
+    uint32_t *ids = ids_out + (size_t)token * top_k;
+    float *wts = weights_out + (size_t)token * top_k;
     const int sel = min(min(top_k, n_expert), 32);
     uint32_t taken = 0;  // bit s <-> expert lane + 32*s
     float my_val = 0.0f;
@@ -71,7 +75,7 @@ __device__ __forceinline__ uint32_t moe_route_topk_warp(const float *__restrict_
         int bi = 0x7fffffff;
         for (int s = 0, e = lane; e < n_expert; s++, e += 32) {
             if (taken & (1u << s)) continue;
-            const float v = lg[e];
+            const float v = __ldcg(lg + e);   // may have been written by other CTAs of the same launch
             if (bi == 0x7fffffff || v > best) {  // ascending e: strict > keeps the lowest id
                 best = v;
                 bi = e;
@@ -105,7 +109,7 @@ moe_route_topk_kernel(const float *__restrict__ logits, int n_expert, int top_k,
                       uint32_t *__restrict__ ids_out, float *__restrict__ weights_out) {
     pdl_launch_dependents();
     pdl_wait();
-    moe_route_topk_warp(logits, n_expert, top_k, ids_out, weights_out);
+    moe_route_topk_warp(logits, (int)blockIdx.x, n_expert, top_k, ids_out, weights_out);
 }
 
 // Fills the per-layer job tables of the expert-gathered matvecs from the routed ids:
@@ -124,15 +128,24 @@ __device__ __forceinline__ void moe_fill_jobs_warp(size_t id, const float *__res
     down_job->parts[e].w = lp.down_base + id * lp.down_stride;
     down_job->parts[e].scale = weights + e;
 }
-// Routing and the job tables in one launch (one token): the warp that selected the experts
-// also points the expert-gathered matvecs at them.
+// Router logits, routing and job tables in one launch (one token): CTAs of one warp compute two
+// experts' logits each; the CTA that finishes last (a counter that it re-arms) selects the experts
+// and points the expert-gathered matvecs at them.
 RNB_GLOBAL void __launch_bounds__(32)
-moe_route_fill_kernel(const float *__restrict__ logits, int n_expert, int top_k, uint32_t *__restrict__ ids_out, float *__restrict__ weights_out,
-                      MoeLayerPtrs lp, GemvJob *__restrict__ gate_up_jobs, GemvJob *__restrict__ down_job) {
-    pdl_launch_dependents();
-    pdl_wait();
-    const uint32_t id = moe_route_topk_warp(logits, n_expert, top_k, ids_out, weights_out);  // lane r: the expert of rank r
+router_route_fill_kernel(const float *__restrict__ w, const float *__restrict__ h, int n_expert, int hidden, float *logits,
+                         int top_k, uint32_t *__restrict__ ids_out, float *__restrict__ weights_out, MoeLayerPtrs lp,
+                         GemvJob *__restrict__ gate_up_jobs, GemvJob *__restrict__ down_job, int *__restrict__ counter) {
+    router_logits_body(w, h, n_expert, hidden, logits);
+    __threadfence();   // this CTA's logits are visible device-wide before the CTA is counted
+    __syncwarp();
+    int last = 0;
+    if (threadIdx.x == 0) last = atomicAdd(counter, 1) == (int)gridDim.x - 1;
+    last = __shfl_sync(0xffffffffu, last, 0);
+    if (!last) return;
+    __threadfence();
+    const uint32_t id = moe_route_topk_warp(logits, 0, n_expert, top_k, ids_out, weights_out);   // one token: its row of ids / weights
     moe_fill_jobs_warp(id, weights_out, top_k, lp, gate_up_jobs, down_job);
+    if (threadIdx.x == 0) *counter = 0;
 }
 
 }  // namespace rnb
