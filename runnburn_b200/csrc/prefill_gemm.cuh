@@ -126,6 +126,54 @@ f32_to_bf16_kernel(const float *__restrict__ x, uint16_t *__restrict__ y, size_t
     *reinterpret_cast<uint4 *>(y + i) = make_uint4(pg_pack_bf16(a.x, a.y), pg_pack_bf16(a.z, a.w), pg_pack_bf16(b.x, b.y), pg_pack_bf16(b.z, b.w));
 }
 
+// Residual add + RMSNorm of a batch of token rows, written straight as the bf16 token matrix of
+// the next matmul: x += t (when t is given; x is updated in place), then (x / rms) * w with the
+// f64 mean square of rnb-cpu's rms_norm_into (crates/rnb-cpu/src/kernels/norm.rs:177-196) in the
+// reduction order of rmsnorm_q8k_kernel, rounded once to bf16.  One CTA per token; hidden % 8 == 0.
+template <int THREADS>
+RNB_GLOBAL void __launch_bounds__(THREADS)
+add_rmsnorm_bf16_kernel(float *__restrict__ x, const float *__restrict__ t, const float *__restrict__ w, float eps, int hidden,
+                        uint16_t *__restrict__ out) {
+    pdl_launch_dependents();
+    pdl_wait();
+    __shared__ double red[THREADS / 32];
+    __shared__ float s_rms;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    float *xs = x + (size_t)blockIdx.x * hidden;
+    double ss = 0.0;
+    if (t) {
+        const float *ts = t + (size_t)blockIdx.x * hidden;
+        for (int i = tid; i < hidden; i += THREADS) {
+            const float v = __fadd_rn(xs[i], ts[i]);
+            xs[i] = v;
+            ss += (double)v * (double)v;
+        }
+    } else {
+        for (int i = tid; i < hidden; i += THREADS) {
+            const double v = (double)xs[i];
+            ss += v * v;
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if (lane == 0) red[warp] = ss;
+    __syncthreads();   // also orders this CTA's writes of xs before the reads below
+    if (tid == 0) {
+        double a = 0.0;
+        for (int i = 0; i < THREADS / 32; i++) a += red[i];
+        s_rms = (float)sqrt(a / (double)hidden + (double)eps);
+    }
+    __syncthreads();
+    const float rms = s_rms;
+    uint16_t *os = out + (size_t)blockIdx.x * hidden;
+    for (int i = tid * 8; i < hidden; i += THREADS * 8) {
+        float v[8];
+#pragma unroll
+        for (int j = 0; j < 8; j++) v[j] = __fmul_rn(__fdiv_rn(xs[i + j], rms), w[i + j]);
+        *reinterpret_cast<uint4 *>(os + i) = make_uint4(pg_pack_bf16(v[0], v[1]), pg_pack_bf16(v[2], v[3]), pg_pack_bf16(v[4], v[5]), pg_pack_bf16(v[6], v[7]));
+    }
+}
+
 // silu(gate) * up (g / (1 + exp(-g)), crates/rnb-cpu/src/kernels/activation.rs:74-89, exp in double and
 // rounded once as in silu_mul_q8k_kernel) written straight as the bf16 token matrix of the down
 // matmul: the f32 value is rounded to bf16 exactly as f32_to_bf16_kernel would round it.
