@@ -101,3 +101,16 @@ def test_compute_fails_loudly_without_a_gpu(lib):
     assert e.value.status == 4 and "no CPU fallback" in str(e.value)
     with pytest.raises(r.RnbError):
         r.Decoder(r.ModelConfig(n_layer=1, hidden=256, n_head=2, n_kv_head=1, n_ff=256, vocab=32, max_ctx=8))
+
+
+def test_split_kv_chunk_rule(lib):
+    """Chunks per KV head of the split-KV decode attention (148 SMs assumed without a device):
+    4 CTAs per SM spread over the KV heads, at most one chunk per 32 positions, and with four or
+    more KV heads at most max(74, kv_len / 128) so that the merge stays short."""
+    f = lib.rnb_b200_flash_decode_default_chunks
+    assert f(4096, 8) == 74          # Llama-3-8B, ctx 4096
+    assert f(8192, 4) == 74          # 4-KV-head MoE shape, ctx 8192 (148 without the cap)
+    assert f(32768, 4) == 148        # 70B two-GPU shard: long chunks keep the full count
+    assert f(32768, 1) == 592        # one KV head per GPU: no cap
+    assert f(100, 8) == 4            # short cache: one chunk per 32 positions
+    assert f(0, 8) == 1
