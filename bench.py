@@ -300,6 +300,68 @@ def prefill_gemm_bench(shape: dict, seq: int, reps: int = 3) -> dict:
             "launches": rows_out}
 
 
+def matvec_shape_bench(shapes=None, min_total_bytes=1 << 30, reps=5) -> list:
+    """BASELINE config 1: each batch-1 matvec shape timed alone.  Every shape gets enough distinct
+    weight copies to exceed 1 GiB (far more than the 126 MB L2), one launch per copy is captured
+    into a CUDA graph, and the graph is replayed `reps` times between two CUDA events on the
+    launching stream.  Bytes are the algorithmic ones: rows * row_bytes + Q8_K activation + f32 out."""
+    import torch
+
+    import runnburn_b200 as r
+    L = r.load()
+    shapes = shapes or [(12, 4096, 4096), (12, 1024, 4096), (12, 14336, 4096), (12, 4096, 14336), (14, 1024, 4096), (14, 4096, 14336), (14, 128256, 4096)]
+    peaks = load_peaks()
+    g = torch.Generator(device="cuda").manual_seed(0)
+    out = []
+    for t, rows, cols in shapes:
+        rb = row_bytes(t, cols)
+        wbytes = rows * rb
+        n = max(2, -(-min_total_bytes // wbytes))
+        blk = 144 if t == 12 else 210
+        w = torch.randint(0, 256, (n, rows, cols // 256, blk), dtype=torch.uint8, device="cuda", generator=g)
+        if t == 12:
+            w[..., 1] = 0x10; w[..., 3] = 0x10      # f16 d, dmin ~ 5e-4
+        else:
+            w[..., 209] = 0x10
+        x = torch.randn(cols, device="cuda", generator=g)
+        xq = torch.empty(int(L.rnb_b200_dev_q8k_bytes(cols)) + 16, dtype=torch.uint8, device="cuda")
+        y = torch.empty(n, rows, device="cuda")
+        st = torch.cuda.Stream()
+        with torch.cuda.stream(st):
+            sp = st.cuda_stream
+            if L.rnb_b200_dev_quantize_q8k(x.data_ptr(), cols, 1, xq.data_ptr(), None, sp) != 0:
+                raise RuntimeError(L.rnb_b200_last_error().decode())
+
+            def run():
+                for i in range(n):
+                    if L.rnb_b200_dev_gemv(t, w[i].data_ptr(), rows, cols, xq.data_ptr(), y[i].data_ptr(), 0, sp) != 0:
+                        raise RuntimeError(L.rnb_b200_last_error().decode())
+            run()
+            st.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=st):
+                run()
+            for _ in range(3):
+                graph.replay()
+            st.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(st)
+            for _ in range(reps):
+                graph.replay()
+            e1.record(st)
+            st.synchronize()
+        us = e0.elapsed_time(e1) * 1000.0 / (reps * n)
+        alg = wbytes + q8k_bytes(cols) + rows * 4
+        gbs = alg / us / 1e3
+        out.append({"type": "Q4_K" if t == 12 else "Q6_K", "rows": rows, "cols": cols, "us": us, "algorithmic_bytes": alg, "gbs": gbs,
+                    "frac": gbs / peaks["hbm_gbs"], "frac_of_8TBs_nominal": gbs / 8000.0, "copies": n})
+        del w, y
+        torch.cuda.empty_cache()
+    if r.ops.dev_error_flag() != 0:
+        raise RuntimeError("device error flag set by a matvec")
+    return out
+
+
 def run_gpu(args, shape, ctx, name, rank, world, local_rank):
     import torch
 

@@ -71,6 +71,11 @@ int rnb_b200_prewarm_q4k_weights(const uint8_t *const *slices, const size_t *len
 /* Residency budget override in bytes (0 = derive from free memory as
  * DeviceResidencyPlan does — crates/rnb-memory/src/device_residency.rs:40-91). */
 int rnb_b200_set_resident_limit(size_t bytes);
+/* inject_qwen35_resident_alloc_ooms_for_test — crates/rnb-backend/cuda/src/runtime/state/
+ * q4k_cache.rs:1040-1053: the next `count` device allocations of the resident cache report
+ * out-of-memory without touching the driver, so the evict-and-retry ladder
+ * (q4k_cache.rs:757-851) can be driven from a test.  Host-side fault injection only. */
+int rnb_b200_inject_resident_alloc_ooms_for_test(size_t count);
 /* host_register.rs:45-190 — pin the page-aligned interior of a host range for async DMA;
  * clear_host_registered_ranges — api/cache_api.rs */
 int rnb_b200_register_host_range(const void *ptr, size_t len);
@@ -309,6 +314,53 @@ int rnb_b200_decoder_attach_peers(rnb_b200_decoder *d, const uint8_t *handles /*
  * (4 = peer timeout).  The context stays usable. */
 int rnb_b200_peer_exchange_timeout_selftest(int *status_out);
 
+/* Shape the decoder was created with. */
+int rnb_b200_decoder_config(const rnb_b200_decoder *d, rnb_b200_model_cfg *out);
+
+/* ---- GGUF container and file loader ------------------------------------------------------------
+ * GGUFFile::parse — crates/rnb-loader/src/gguf/parser.rs:244-404 (magic "GGUF", versions 2 and 3,
+ * little-endian only, u64 counts, KV metadata, tensor infos with dims stored innermost first,
+ * `general.alignment` (default 32, a power of two), data section at the next aligned offset;
+ * limits and messages as the reference's); type ids — gguf/types.rs:5-40.  `open` maps the file
+ * read-only; `parse` reads a buffer the caller keeps alive.  Tensor data is never copied on the
+ * host. */
+typedef struct rnb_b200_gguf rnb_b200_gguf;
+typedef struct {
+    char name[64];
+    uint32_t n_dims, ggml_type;
+    uint64_t dims[4];      /* row-major: outermost first, as the reference normalises them */
+    uint64_t offset;       /* from the start of the data section */
+    uint64_t n_elements;
+    uint64_t n_bytes;      /* 0 when the type's block size is not tabulated */
+    const uint8_t *data;   /* inside the mapped file */
+} rnb_b200_gguf_tensor_info;
+int rnb_b200_gguf_open(const char *path, rnb_b200_gguf **out);
+int rnb_b200_gguf_parse(const void *data, size_t len, rnb_b200_gguf **out);
+void rnb_b200_gguf_close(rnb_b200_gguf *g);
+int rnb_b200_gguf_info(const rnb_b200_gguf *g, uint32_t *version, uint64_t *alignment,
+                       uint64_t *data_start, uint64_t *n_tensors, uint64_t *n_metadata);
+/* Metadata getters (get_u32 / get_f32 / get_string / get_u32_array of arch/mod.rs): a missing key
+ * returns RNB_B200_UNSUPPORTED, a value of another kind RNB_B200_VALIDATION_FAILED. */
+int rnb_b200_gguf_get_u64(const rnb_b200_gguf *g, const char *key, uint64_t *out);
+int rnb_b200_gguf_get_f64(const rnb_b200_gguf *g, const char *key, double *out);
+int rnb_b200_gguf_get_str(const rnb_b200_gguf *g, const char *key, char *buf, size_t cap,
+                          size_t *len_out);
+int rnb_b200_gguf_get_array_u64(const rnb_b200_gguf *g, const char *key, uint64_t *out,
+                                size_t cap, size_t *len_out);
+int rnb_b200_gguf_tensor(const rnb_b200_gguf *g, const char *name, rnb_b200_gguf_tensor_info *out);
+int rnb_b200_gguf_tensor_at(const rnb_b200_gguf *g, size_t index, rnb_b200_gguf_tensor_info *out);
+/* extract_metadata — crates/rnb-loader/src/arch/mod.rs:304-560, for the Llama-style families the
+ * decoder runs: `<arch>.embedding_length`, `.block_count`, `.attention.head_count[_kv]`,
+ * `.feed_forward_length`, `.rope.freq_base` (default 10000), `.attention.layer_norm_rms_epsilon`
+ * (default 1e-5), `.expert_count`, `.expert_used_count`, `.expert_feed_forward_length`;
+ * max_ctx <= 0 takes `<arch>.context_length` (default 4096). */
+int rnb_b200_gguf_model_config(const rnb_b200_gguf *g, int max_ctx, rnb_b200_model_cfg *cfg);
+/* Tensor names of crates/rnb-loader/src/arch/llama.rs:33-155 (`token_embd`, `blk.N.attn_q`, ...,
+ * `output_norm`, `output`; a file without `output.weight` ties the LM head to the embedding)
+ * uploaded from the mapped pages; register_pages != 0 pins the data section first
+ * (rnb_b200_register_host_range). */
+int rnb_b200_decoder_load_gguf(rnb_b200_decoder *d, const rnb_b200_gguf *g, int register_pages);
+
 /* ---- device-pointer tier (no host copies, no synchronisation; for callers that keep
  * activations on the device and for kernel timing).  `stream` is a cudaStream_t or NULL. */
 int rnb_b200_dev_quantize_q8k(const float *x_dev, size_t cols, size_t seq, void *xq_dev,
@@ -347,11 +399,19 @@ int rnb_b200_flash_decode_default_chunks(size_t kv_len, size_t num_kv_heads);
  * Every call on a device uses the same array: calls that overlap on the GPU (different
  * streams, or this entry point from two threads) race on it and must be serialised by the
  * caller.  Nothing in the array needs clearing between calls: each call rewrites every record
- * it later reads. */
+ * it later reads.  Alignment: q_dev on a 16-byte boundary, k_dev and v_dev on 8 bytes (16 bytes
+ * selects the faster tensor-core kernel), out_dev on 4 bytes; anything else is rejected with
+ * RNB_B200_VALIDATION_FAILED rather than left to fault on the device. */
 int rnb_b200_attention_decode_hd128_noalloc(const float *q_dev, const uint16_t *k_dev,
                                             const uint16_t *v_dev, size_t kv_len,
                                             size_t num_heads, size_t num_kv_heads, float scale,
                                             float *out_dev, void *stream);
+/* Companion of the call above, also without a counterpart in the reference and also free of
+ * allocations: waits for `stream`, then reads (and clears) the entry point's own status word on
+ * the current device, a second fixed word beside the scratch array.  0 = every launch since the
+ * last read completed; non-zero = a bounded wait inside a kernel gave up and the outputs written
+ * since then are not to be trusted (the codes are those of rnb_b200_dev_error_flag). */
+int rnb_b200_attention_decode_hd128_noalloc_status(int *status_out, void *stream);
 /* Reads and clears the device error word set by kernels whose bounded waits gave up. */
 int rnb_b200_dev_error_flag(int *flag_out);
 

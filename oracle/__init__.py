@@ -59,6 +59,8 @@ def _declare(L):
     L.orc_dequantize_row.restype = i32
     L.orc_quantize_matrix.argtypes = [i32, vp, sz, sz, vp, i32]
     L.orc_quantize_matrix.restype = i32
+    L.orc_synth_matrix.argtypes = [i32, sz, sz, C.c_uint64, C.c_float, vp, i32]
+    L.orc_synth_matrix.restype = i32
     for n in ("orc_dot_q4k_q8k", "orc_dot_q6k_q8k", "orc_dot_q4k_q8k_lanes", "orc_dot_q6k_q8k_lanes"):
         getattr(L, n).restype = f32
         getattr(L, n).argtypes = [vp, vp, sz]
@@ -150,6 +152,16 @@ def quantize_matrix(ggml_type: int, w, threads: int | None = None) -> np.ndarray
     rows, cols = w.shape
     out = np.zeros(rows * row_bytes(ggml_type, cols), dtype=np.uint8)
     rc = lib().orc_quantize_matrix(ggml_type, _p(w), rows, cols, _p(out), threads or n_threads())
+    assert rc == 0
+    return out
+
+
+def synth_matrix(ggml_type: int, rows: int, cols: int, seed: int, sigma: float = 0.02,
+                 threads: int | None = None) -> np.ndarray:
+    """Seeded N(0, sigma) weights as GGUF blocks, quantised with a plain per-block fit: a fast
+    harness utility for full-width test models (not a restatement of reference code)."""
+    out = np.zeros(rows * row_bytes(ggml_type, cols), dtype=np.uint8)
+    rc = lib().orc_synth_matrix(ggml_type, rows, cols, seed, sigma, _p(out), threads or n_threads())
     assert rc == 0
     return out
 

@@ -496,6 +496,99 @@ int orc_quantize_matrix(int type, const float *x, size_t rows, size_t cols, uint
 }
 
 /* ------------------------------------------------------------------------------------------
+ * Harness utility, not a restatement of anything in the reference: seeded N(0, sigma) weights
+ * quantised block by block with a plain min/max fit (Q4_K), an absmax fit (Q6_K, Q8_0).  It
+ * exists so that tests can build full-width random-init matrices (128 256 x 4096 and the like)
+ * in a second instead of minutes; the blocks are ordinary GGUF blocks that the dequantisers
+ * and dots above read like any other.
+ * ---------------------------------------------------------------------------------------- */
+static inline uint64_t synth_mix64(uint64_t z) {
+    z += 0x9e3779b97f4a7c15ull;
+    z = (z ^ (z >> 30)) * 0xbf58476d1ce4e5b9ull;
+    z = (z ^ (z >> 27)) * 0x94d049bb133111ebull;
+    return z ^ (z >> 31);
+}
+static inline void synth_gauss_pair(uint64_t seed, uint64_t idx, float sigma, float *a, float *b) {
+    uint64_t r = synth_mix64(seed ^ (idx * 0xd1342543de82ef95ull));
+    float u1 = ((float)(uint32_t)(r >> 40) + 1.0f) * (1.0f / 16777217.0f);
+    float u2 = (float)(uint32_t)(r & 0xffffff) * (1.0f / 16777216.0f);
+    float rad = sigma * sqrtf(-2.0f * logf(u1));
+    *a = rad * cosf(6.2831853f * u2);
+    *b = rad * sinf(6.2831853f * u2);
+}
+static void synth_block(int type, uint64_t seed, uint64_t block_index, float sigma, uint8_t *out) {
+    float x[256];
+    for (int i = 0; i < 256; i += 2) synth_gauss_pair(seed, block_index * 128 + (uint64_t)(i / 2), sigma, &x[i], &x[i + 1]);
+    if (type == ORC_TYPE_Q4_K) {
+        float sc[8], mn[8], max_sc = 0.0f, max_mn = 0.0f;
+        for (int j = 0; j < 8; j++) {
+            float lo = 0.0f, hi = x[32 * j];
+            for (int l = 0; l < 32; l++) {
+                if (x[32 * j + l] < lo) lo = x[32 * j + l];
+                if (x[32 * j + l] > hi) hi = x[32 * j + l];
+            }
+            sc[j] = (hi - lo) / 15.0f;
+            mn[j] = -lo;
+            if (sc[j] > max_sc) max_sc = sc[j];
+            if (mn[j] > max_mn) max_mn = mn[j];
+        }
+        uint16_t dh = orc_f32_to_f16(max_sc / 63.0f), mh = orc_f32_to_f16(max_mn / 63.0f);
+        float d = orc_f16_to_f32(dh), dm = orc_f16_to_f32(mh);
+        uint8_t ls[8], lm[8], ys[12] = {0};
+        for (int j = 0; j < 8; j++) {
+            ls[j] = (uint8_t)clampi(d > 0.0f ? nearest_int(sc[j] / d) : 0, 0, 63);
+            lm[j] = (uint8_t)clampi(dm > 0.0f ? nearest_int(mn[j] / dm) : 0, 0, 63);
+        }
+        for (int j = 0; j < 8; j++) {
+            if (j < 4) {
+                ys[j] |= ls[j];
+                ys[j + 4] |= lm[j];
+            } else {
+                ys[j + 4] = (uint8_t)((ls[j] & 0xF) | ((lm[j] & 0xF) << 4));
+                ys[j - 4] |= (uint8_t)((ls[j] >> 4) << 6);
+                ys[j] |= (uint8_t)((lm[j] >> 4) << 6);
+            }
+        }
+        out[0] = (uint8_t)(dh & 0xff);
+        out[1] = (uint8_t)(dh >> 8);
+        out[2] = (uint8_t)(mh & 0xff);
+        out[3] = (uint8_t)(mh >> 8);
+        memcpy(out + 4, ys, 12);
+        for (int g = 0; g < 4; g++)
+            for (int l = 0; l < 32; l++) {
+                int q[2];
+                for (int h = 0; h < 2; h++) {
+                    int j = 2 * g + h;
+                    float ds = d * ls[j], ms = dm * lm[j];
+                    q[h] = ds > 0.0f ? clampi(nearest_int((x[64 * g + 32 * h + l] + ms) / ds), 0, 15) : 0;
+                }
+                out[16 + 32 * g + l] = (uint8_t)(q[0] | (q[1] << 4));
+            }
+    } else if (type == ORC_TYPE_Q6_K) {
+        orc_quantize_row_q6k(x, 256, out);
+    } else {
+        orc_quantize_row_q8_0(x, 256, out);
+    }
+}
+typedef struct {
+    int type;
+    uint64_t seed;
+    float sigma;
+    uint8_t *out;
+} synth_ctx;
+static void synth_blocks(size_t b, size_t e, void *p) {
+    synth_ctx *c = (synth_ctx *)p;
+    size_t bb = orc_row_bytes(c->type, 256);
+    for (size_t i = b; i < e; i++) synth_block(c->type, c->seed, i, c->sigma, c->out + i * bb);
+}
+int orc_synth_matrix(int type, size_t rows, size_t cols, uint64_t seed, float sigma, uint8_t *out, int threads) {
+    if (orc_row_bytes(type, cols) == 0 || cols % 256 != 0) return -1;
+    synth_ctx c = {type, seed, sigma, out};
+    orc_parallel_for(rows * (cols / 256), threads, synth_blocks, &c);
+    return 0;
+}
+
+/* ------------------------------------------------------------------------------------------
  * Integer row dots.  Two statements of each: `_lanes` is portable C that reproduces the
  * AVX2 lane structure (8 f32 accumulators per row, one FMA per block, the same horizontal
  * sum order) and is bit-identical to the intrinsic version, which follows

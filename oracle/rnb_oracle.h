@@ -60,6 +60,9 @@ void orc_quantize_row_q6k(const float *x, size_t n, uint8_t *out);
 void orc_quantize_row_q8_0(const float *x, size_t n, uint8_t *out);
 int orc_quantize_matrix(int ggml_type, const float *x, size_t rows, size_t cols, uint8_t *out,
                         int threads);
+/* harness utility: seeded N(0, sigma) weights quantised with a plain per-block fit (fast) */
+int orc_synth_matrix(int ggml_type, size_t rows, size_t cols, uint64_t seed, float sigma, uint8_t *out,
+                     int threads);
 
 /* ---- row dots ---- */
 float orc_dot_q4k_q8k(const uint8_t *row, const orc_q8k_block *y, size_t nb);

@@ -46,6 +46,11 @@ class QWeight(C.Structure):
     _fields_ = [("type", C.c_uint32), ("data", C.c_void_p), ("len", C.c_size_t)]
 
 
+class GgufTensorInfo(C.Structure):
+    _fields_ = [("name", C.c_char * 64), ("n_dims", C.c_uint32), ("ggml_type", C.c_uint32), ("dims", C.c_uint64 * 4),
+                ("offset", C.c_uint64), ("n_elements", C.c_uint64), ("n_bytes", C.c_uint64), ("data", C.c_void_p)]
+
+
 class LayerWeights(C.Structure):
     _fields_ = [("attn_norm", C.c_void_p), ("ffn_norm", C.c_void_p)] + \
                [(n, QWeight) for n in ("wq", "wk", "wv", "wo", "gate", "up", "down")] + \
@@ -68,6 +73,8 @@ def load() -> C.CDLL:
     sz, vp, i32, u32, f32, u64 = C.c_size_t, C.c_void_p, C.c_int, C.c_uint32, C.c_float, C.c_uint64
     L.rnb_b200_last_error.restype = C.c_char_p
     L.rnb_b200_close.restype = None
+    L.rnb_b200_gguf_close.restype = None
+    L.rnb_b200_gguf_close.argtypes = [C.c_void_p]
     sig = {
         "rnb_b200_open": [],
         "rnb_b200_cuda_memory_info": [vp, vp],
@@ -134,7 +141,21 @@ def load() -> C.CDLL:
         "rnb_b200_dev_flash_decode": [vp, vp, vp, sz, sz, sz, f32, vp, sz, i32, vp, vp],
         "rnb_b200_flash_decode_default_chunks": [sz, sz],
         "rnb_b200_attention_decode_hd128_noalloc": [vp, vp, vp, sz, sz, sz, f32, vp, vp],
+        "rnb_b200_attention_decode_hd128_noalloc_status": [vp, vp],
         "rnb_b200_dev_error_flag": [vp],
+        "rnb_b200_decoder_config": [vp, vp],
+        "rnb_b200_gguf_open": [C.c_char_p, vp],
+        "rnb_b200_gguf_parse": [vp, sz, vp],
+        "rnb_b200_gguf_info": [vp, vp, vp, vp, vp, vp],
+        "rnb_b200_gguf_get_u64": [vp, C.c_char_p, vp],
+        "rnb_b200_gguf_get_f64": [vp, C.c_char_p, vp],
+        "rnb_b200_gguf_get_str": [vp, C.c_char_p, vp, sz, vp],
+        "rnb_b200_gguf_get_array_u64": [vp, C.c_char_p, vp, sz, vp],
+        "rnb_b200_gguf_tensor": [vp, C.c_char_p, vp],
+        "rnb_b200_gguf_tensor_at": [vp, sz, vp],
+        "rnb_b200_gguf_model_config": [vp, i32, vp],
+        "rnb_b200_decoder_load_gguf": [vp, vp, i32],
+        "rnb_b200_inject_resident_alloc_ooms_for_test": [sz],
     }
     for name, args in sig.items():
         fn = getattr(L, name)

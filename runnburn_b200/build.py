@@ -12,7 +12,7 @@ from pathlib import Path
 PKG = Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
 LIB = PKG / "librnb_b200.so"
-SOURCES = ["api.cu", "noalloc.cu"]
+SOURCES = ["api.cu", "noalloc.cu", "gguf.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "-Xcompiler", "-Wall", "-Xcompiler", "-Wno-unused-function",
@@ -39,7 +39,8 @@ def build_library(force: bool = False, verbose: bool = False) -> Path:
     if not force and not _stale():
         return LIB
     srcs = [str(CSRC / s) for s in SOURCES if (CSRC / s).exists()]
-    cmd = [_nvcc(), *NVCC_FLAGS, "-shared", "-o", str(LIB), *srcs, "-ldl"]
+    extra = os.environ.get("RNB_B200_NVCC_FLAGS", "").split()   # development hook, e.g. -DGM_PROFILE
+    cmd = [_nvcc(), *NVCC_FLAGS, *extra, "-shared", "-o", str(LIB), *srcs, "-ldl"]
     if verbose:
         cmd.insert(1, "-Xptxas")
         cmd.insert(2, "-v")

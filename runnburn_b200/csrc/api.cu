@@ -67,6 +67,8 @@ int gemv_kernel_setup() {
     RNB_CU(cudaFuncSetAttribute(gemv_stream_kernel_1, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn));
     RNB_CU(cudaFuncSetAttribute(gemv_pair_q4k_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn));
     RNB_CU(cudaFuncSetAttribute(gemv_ksplit_q6k_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn));
+    RNB_CU(cudaFuncSetAttribute(gemv_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn));
+    RNB_CU(cudaFuncSetAttribute(gemv_mma_kernel_1, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn));
     g_gemv_smem_max = dyn;
     done = true;
     return RNB_B200_OK;
@@ -130,8 +132,11 @@ void State::close() {
     kv_mirrors.clear();
     for (auto &r : registered) cudaHostUnregister(r.first);
     registered.clear();
-    DevBuf *bufs[] = {&in_f32, &xq, &xq2, &out_f32, &mid_a, &mid_b, &mid_c, &jobs, &partials, &misc, &transient};
+    DevBuf *bufs[] = {&in_f32, &xq, &xq2, &out_f32, &mid_a, &mid_b, &mid_c, &jobs, &partials, &misc, &xb};
     for (DevBuf *b : bufs) b->release();
+    for (DevBuf &b : transient_pool) b.release();
+    transient_pool.clear();
+    transient_used = 0;
     pin_in.release();
     pin_out.release();
     pin_jobs.release();
@@ -142,9 +147,25 @@ void State::close() {
     is_open = false;
 }
 
+// Over-budget weights travel through transient buffers that live for one operator call: every
+// transient upload of a call takes the next buffer of a grow-only pool (an operator that needs
+// gate, up and down at once gets three distinct regions), and the pool's cursor returns to the
+// start when the next call takes the state lock.
+int State::transient_upload(const uint8_t *host, size_t len, const uint8_t **dev_out) {
+    if (transient_used >= transient_pool.size()) transient_pool.emplace_back();
+    DevBuf &buf = transient_pool[transient_used];
+    RNB_TRY(buf.ensure(len + 16));
+    RNB_CU(cudaMemcpyAsync(buf.p, host, len, cudaMemcpyHostToDevice, stream));
+    transient_used++;
+    ctr.transient_uploads++;
+    ctr.h2d_bytes += len;
+    *dev_out = buf.as<uint8_t>();
+    return RNB_B200_OK;
+}
+
 // Resident lookup: exact (ptr,len) hit, or a slice of a larger resident range (stacked expert
 // tensors registered once); miss -> budget check, LRU eviction, allocate, upload.  Over-budget
-// weights are uploaded into a transient buffer that the next transient upload overwrites
+// weights are uploaded into a transient buffer of the current call
 // (crates/rnb-backend/cuda/src/runtime/state/q4k_cache.rs:757-851).
 int State::resident_ptr(const uint8_t *host, size_t len, bool pin, const uint8_t **dev_out) {
     ctr.lookups++;
@@ -164,12 +185,7 @@ int State::resident_ptr(const uint8_t *host, size_t len, bool pin, const uint8_t
     ctr.misses++;
     if (len > resident_limit) {
         if (pin) return fail(RNB_B200_OUT_OF_MEMORY, "resident weight of %zu bytes exceeds the residency limit %zu", len, resident_limit);
-        RNB_TRY(transient.ensure(len + 16));
-        RNB_CU(cudaMemcpyAsync(transient.p, host, len, cudaMemcpyHostToDevice, stream));
-        ctr.transient_uploads++;
-        ctr.h2d_bytes += len;
-        *dev_out = transient.as<uint8_t>();
-        return RNB_B200_OK;
+        return transient_upload(host, len, dev_out);
     }
     auto evict_lru = [&]() -> bool {
         auto victim = resident.end();
@@ -186,12 +202,7 @@ int State::resident_ptr(const uint8_t *host, size_t len, bool pin, const uint8_t
         if (!evict_lru()) break;
     if (resident_bytes + len > resident_limit) {
         if (pin) return fail(RNB_B200_OUT_OF_MEMORY, "no room to pin %zu bytes (resident %zu, limit %zu)", len, resident_bytes, resident_limit);
-        RNB_TRY(transient.ensure(len + 16));
-        RNB_CU(cudaMemcpyAsync(transient.p, host, len, cudaMemcpyHostToDevice, stream));
-        ctr.transient_uploads++;
-        ctr.h2d_bytes += len;
-        *dev_out = transient.as<uint8_t>();
-        return RNB_B200_OK;
+        return transient_upload(host, len, dev_out);
     }
     uint8_t *dev = nullptr;
     for (;;) {
@@ -268,7 +279,7 @@ static int finish_to_host(State &st, const void *dev_src, void *host_dst, size_t
 struct Locked {
     std::lock_guard<std::mutex> g;
     State &st;
-    Locked() : g(state_mutex()), st(state()) {}
+    Locked() : g(state_mutex()), st(state()) { st.transient_used = 0; }   // a new call: last call's transient uploads are dead
 };
 
 static const char *type_name(int t) {
@@ -471,6 +482,11 @@ int rnb_b200_set_resident_limit(size_t bytes) {
     }
     return RNB_B200_OK;
 }
+int rnb_b200_inject_resident_alloc_ooms_for_test(size_t count) {
+    Locked L;
+    L.st.fail_next_allocs = (int)std::min<size_t>(count, 1u << 20);
+    return RNB_B200_OK;
+}
 int rnb_b200_register_host_range(const void *ptr, size_t len) {
     if (!ptr || !len) return fail(RNB_B200_VALIDATION_FAILED, "empty host range");
     Locked L;
@@ -638,9 +654,14 @@ int rnb_b200_attention_decode_cached(size_t layer, const float *q, size_t q_len,
             return fail_cuda(e, "cudaMalloc(kv mirror)");
         }
         if (m.rows_have && m.kv_dim == kv_dim) {
-            RNB_CU(cudaMemcpyAsync(nk, m.dk, m.rows_have * kv_dim * 2, cudaMemcpyDeviceToDevice, st.stream));
-            RNB_CU(cudaMemcpyAsync(nv, m.dv, m.rows_have * kv_dim * 2, cudaMemcpyDeviceToDevice, st.stream));
-            RNB_CU(cudaStreamSynchronize(st.stream));
+            cudaError_t ce = cudaMemcpyAsync(nk, m.dk, m.rows_have * kv_dim * 2, cudaMemcpyDeviceToDevice, st.stream);
+            if (ce == cudaSuccess) ce = cudaMemcpyAsync(nv, m.dv, m.rows_have * kv_dim * 2, cudaMemcpyDeviceToDevice, st.stream);
+            if (ce == cudaSuccess) ce = cudaStreamSynchronize(st.stream);
+            if (ce != cudaSuccess) {   // the old mirror stays in place; the new buffers must not leak
+                cudaFree(nk);
+                cudaFree(nv);
+                return fail_cuda(ce, "cudaMemcpyAsync(kv mirror grow)");
+            }
         } else {
             m.rows_have = 0;
         }
@@ -1065,14 +1086,32 @@ int rnb_b200_flash_decode_default_chunks(size_t kv_len, size_t num_kv_heads) {
 int rnb_b200_dev_flash_decode(const float *q_dev, const uint16_t *k_dev, const uint16_t *v_dev, size_t kv_len, size_t num_heads,
                               size_t num_kv_heads, float scale, float *partials_dev, size_t partials_bytes, int n_chunks,
                               float *out_dev, void *stream) {
-    if (num_kv_heads == 0 || num_heads % num_kv_heads != 0) return fail(RNB_B200_VALIDATION_FAILED, "attention: num_heads(%zu) must be a multiple of num_kv_heads(%zu)", num_heads, num_kv_heads);
-    if (n_chunks < 1 || partials_bytes < flash_decode_scratch_bytes(num_heads, n_chunks))
+    if (!q_dev || !k_dev || !v_dev || !partials_dev || !out_dev) return fail(RNB_B200_VALIDATION_FAILED, "null pointer argument");
+    if (num_kv_heads == 0 || num_heads == 0 || num_heads % num_kv_heads != 0) return fail(RNB_B200_VALIDATION_FAILED, "attention: num_heads(%zu) must be a multiple of num_kv_heads(%zu)", num_heads, num_kv_heads);
+    if (kv_len == 0 || kv_len > (size_t)0x7fffffff) return fail(RNB_B200_VALIDATION_FAILED, "attention kv_len must be in 1..2^31-1, got %zu", kv_len);
+    // the merge kernels keep one rescale factor per chunk in a fixed shared-memory array
+    if (n_chunks < 1 || n_chunks > FD_MAX_CHUNKS) return fail(RNB_B200_VALIDATION_FAILED, "flash decode n_chunks must be in 1..%d, got %d", FD_MAX_CHUNKS, n_chunks);
+    if (partials_bytes < flash_decode_scratch_bytes(num_heads, n_chunks))
         return fail(RNB_B200_VALIDATION_FAILED, "flash decode scratch too small: got %zu, expected >= %zu", partials_bytes, flash_decode_scratch_bytes(num_heads, n_chunks));
+    // vector loads: q 16 bytes, K/V 8 bytes (16 selects the tensor-core kernel), f32 records and output
+    if (((uintptr_t)q_dev & 15u) || ((uintptr_t)k_dev & 7u) || ((uintptr_t)v_dev & 7u) || ((uintptr_t)out_dev & 3u) || ((uintptr_t)partials_dev & 15u))
+        return fail(RNB_B200_VALIDATION_FAILED, "attention operands are not aligned: q and the scratch need 16 bytes, k and v 8 bytes, out 4 bytes");
     Locked L;
     RNB_TRY(L.st.open());
     return launch_flash_decode((cudaStream_t)stream, q_dev, k_dev, v_dev, nullptr, (int)kv_len, (int)num_heads, (int)num_kv_heads, scale,
                                partials_dev, n_chunks, out_dev, L.st.dev_error);
 }
+#ifdef GM_PROFILE
+extern "C" int rnb_b200_debug_gm_profile(unsigned long long *out8, int reset) {
+    cudaDeviceSynchronize();
+    if (cudaMemcpyFromSymbol(out8, g_gm_prof, 8 * sizeof(unsigned long long)) != cudaSuccess) return 1;
+    if (reset) {
+        unsigned long long z[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        cudaMemcpyToSymbol(g_gm_prof, z, sizeof(z));
+    }
+    return 0;
+}
+#endif
 int rnb_b200_dev_error_flag(int *flag_out) {
     Locked L;
     RNB_TRY(L.st.open());

@@ -7,6 +7,7 @@
 #include "gemv_stream.cuh"
 #include "gemv_pair.cuh"
 #include "gemv_ksplit.cuh"
+#include "gemv_mma.cuh"
 #include "moe.cuh"
 #include "prefill_gemm.cuh"
 #include "q8k.cuh"
@@ -172,11 +173,111 @@ inline const KsplitTuning &ksplit_tuning() {
     }();
     return t;
 }
+// Integer-MMA kernel (gemv_mma.cuh): every batch-1 Q4_K / Q6_K launch whose operands are 16-byte
+// aligned (Q6_K rows additionally need a multiple of 8 super-blocks, so that every stage starts
+// on a 16-byte boundary).  RNB_B200_MMA=0 turns it off, _MMA_STAGES / _MMA_CTAS set the ring depth
+// and the resident CTAs per SM the persistent grid is sized for.
+struct MmaTuning {
+    int enabled, stages, ctas_per_sm;
+};
+inline const MmaTuning &mma_tuning() {
+    static const MmaTuning t = [] {
+        auto env_int = [](const char *name, int dflt, int lo, int hi) {
+            const char *e = getenv(name);
+            if (!e || !*e) return dflt;
+            const int x = atoi(e);
+            return x < lo ? lo : (x > hi ? hi : x);
+        };
+        MmaTuning v;
+        v.enabled = env_int("RNB_B200_MMA", 1, 0, 1);
+        v.stages = env_int("RNB_B200_MMA_STAGES", 3, 1, GM_MAX_STAGES);
+        v.ctas_per_sm = env_int("RNB_B200_MMA_CTAS", 0, 0, 8);
+        return v;
+    }();
+    return t;
+}
+// Returns 1 when the launch was taken, 0 when the jobs do not qualify, < 0 on error.
+inline int try_launch_gemv_mma(cudaStream_t s, const GemvJob *jobs_host, const GemvJob *jobs_dev, int n_jobs, size_t cols, int *dev_error,
+                               int dynamic_table, bool by_value, const GpTail *tail, bool *tail_done) {
+    const MmaTuning &mt = mma_tuning();
+    if (!mt.enabled || cols % 256 != 0 || n_jobs < 1) return 0;
+    const int nb = (int)(cols / 256);
+    bool any_q6 = false;
+    int tiles = 0;
+    for (int i = 0; i < n_jobs; i++) {
+        const GemvJob &j = jobs_host[i];
+        if ((j.type != TYPE_Q4_K && j.type != TYPE_Q6_K) || j.seq > 1 || j.n_parts < 1 || j.n_parts > GEMV_MAX_PARTS || j.rows < 1) return 0;
+        if (j.type == TYPE_Q6_K) {
+            any_q6 = true;
+            if (nb % GM_CHUNK != 0) return 0;
+        }
+        for (int p = 0; p < j.n_parts; p++) {
+            // device-written tables carry the weight pointers only on the device: expert slices are whole rows
+            // of 16-byte multiples behind an allocation boundary
+            if (!dynamic_table && (((uintptr_t)j.parts[p].w) & 15u)) return 0;
+            if (((uintptr_t)j.parts[p].x) & 15u) return 0;
+        }
+        tiles += (j.rows + GM_ROWS - 1) / GM_ROWS;
+    }
+    // Row-rich Q4_K launches with short rows (gate + up: 28672 x 4096) stay on the two-threads-per-row kernel,
+    // which measured faster there (14.9 us against 25 us): too few tiles per persistent CTA for this kernel's
+    // pipeline to reach steady state.  RNB_B200_MMA_ALL=1 sends them here as well.
+    static const bool all_shapes = [] {
+        const char *e = getenv("RNB_B200_MMA_ALL");
+        return e && *e == '1';
+    }();
+    if (!all_shapes && !any_q6 && !dynamic_table && tiles * GM_ROWS >= pair_tuning().min_rows && pair_tuning().enabled && nb <= 32) return 0;
+    GmParams P;
+    P.cols = (int)cols;
+    P.dynamic_table = dynamic_table;
+    P.n_tiles = tiles;
+    P.row_stride = any_q6 ? 1712u : 1168u;   // 8 blocks of 210 / 144 bytes, padded to an odd number of 16-byte units
+    P.act_off = (uint32_t)GM_ROWS * P.row_stride;
+    P.slot_bytes = (P.act_off + GM_ACT_BYTES + 127u) & ~127u;
+    int n_items = 0;
+    for (int i = 0; i < n_jobs; i++) n_items = std::max(n_items, jobs_host[i].n_parts * ((nb + GM_CHUNK - 1) / GM_CHUNK));
+    P.n_stages = mt.stages;
+    while (P.n_stages > 1 && gm_smem_bytes(P.n_stages, P.slot_bytes) > gemv_smem_max()) P.n_stages--;
+    const size_t smem = gm_smem_bytes(P.n_stages, P.slot_bytes);
+    if (smem > gemv_smem_max()) return 0;
+    const int sm = state().sm_count > 0 ? state().sm_count : 148;
+    int per_sm = mt.ctas_per_sm;
+    if (per_sm == 0) {
+        per_sm = (int)((size_t)227 * 1024 / (smem + 1024));
+        if (per_sm > GM_MIN_CTAS) per_sm = GM_MIN_CTAS;   // the kernels' register budget is set for this many
+        if (per_sm < 1) per_sm = 1;
+    }
+    const int grid = std::min(tiles, per_sm * sm);
+    GpTail t;
+    memset(&t, 0, sizeof(t));
+    if (tail && tail->kind == 1 && !dynamic_table && n_jobs == 2 && jobs_host[0].rows == jobs_host[1].rows && jobs_host[0].rows % 256 == 0 &&
+        jobs_host[0].rows == tail->n) {
+        t = *tail;
+        if (tail_done) *tail_done = true;
+    }
+    if ((by_value || !dynamic_table) && n_jobs <= GS_PACK) {
+        GemvJobPack pack;
+        memset(&pack, 0, sizeof(pack));
+        for (int i = 0; i < n_jobs; i++) pack.j[i] = jobs_host[i];
+        const cudaError_t e = launch_k(gemv_mma_kernel_1, dim3(grid), dim3(GM_THREADS), smem, s, pack, n_jobs, P, dev_error, t);
+        if (e != cudaSuccess) return -fail_cuda(e, "gemv_mma_kernel launch");
+    } else {
+        if (t.kind) return -fail(RNB_B200_VALIDATION_FAILED, "matvec tail needs a by-value job table");
+        const cudaError_t e = launch_k(gemv_mma_kernel, dim3(grid), dim3(GM_THREADS), smem, s, jobs_dev, n_jobs, P, dev_error);
+        if (e != cudaSuccess) return -fail_cuda(e, "gemv_mma_kernel launch");
+    }
+    return 1;
+}
 // Row-rich, all-Q4_K, single-part, 16-byte aligned static tables go to the two-threads-per-row
 // kernel; everything else to the eight-threads-per-row kernel.
 inline int launch_gemv_stream(cudaStream_t s, const GemvJob *jobs_host, const GemvJob *jobs_dev, int n_jobs,
                               size_t cols, int *dev_error, int dynamic_table, bool by_value, const GpTail *tail = nullptr,
                               bool *tail_done = nullptr) {
+    {
+        const int took = try_launch_gemv_mma(s, jobs_host, jobs_dev, n_jobs, cols, dev_error, dynamic_table, by_value, tail, tail_done);
+        if (took < 0) return -took;
+        if (took) return RNB_B200_OK;
+    }
     const KsplitTuning &kt = ksplit_tuning();
     if (kt.enabled && !dynamic_table && n_jobs == 1 && jobs_host[0].type == TYPE_Q6_K && jobs_host[0].n_parts == 1 && jobs_host[0].seq <= 1 && jobs_host[0].epi == GEMV_EPI_NONE &&
         cols % (256 * GK_CHUNK) == 0 && (int)cols >= kt.min_cols && jobs_host[0].rows <= kt.max_rows &&

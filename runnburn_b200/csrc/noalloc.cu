@@ -21,22 +21,33 @@ constexpr int NA_MAX_DEVICES = 64;
 // until the process exits.
 static __device__ __align__(256) float g_na_partials[NA_MAX_HEADS * NA_MAX_CHUNKS * FD_PART_STRIDE];
 
-// In host code the array's name is only a handle; kernels need the device address, which is
+// Status word of this entry point, beside the scratch and just as fixed: a kernel whose bounded
+// wait gave up writes a non-zero code here (the rows it skipped are then wrong).  Read and cleared
+// by rnb_b200_attention_decode_hd128_noalloc_status.
+static __device__ int g_na_status;
+
+// In host code the symbols' names are only handles; kernels need the device addresses, which are
 // looked up once per device (with that device current) and cached here.
-static float *g_na_dev_ptr[NA_MAX_DEVICES];
+struct NaDevice {
+    float *partials = nullptr;
+    int *status = nullptr;
+};
+static NaDevice g_na_dev[NA_MAX_DEVICES];
 static std::mutex g_na_mutex;
 
-static int na_scratch(float **out) {
+static int na_device(NaDevice *out) {
     int dev = -1;
     RNB_CU(cudaGetDevice(&dev));
     if (dev < 0 || dev >= NA_MAX_DEVICES) return fail(RNB_B200_UNSUPPORTED, "no-alloc attention: device ordinal %d not supported", dev);
     std::lock_guard<std::mutex> g(g_na_mutex);
-    if (!g_na_dev_ptr[dev]) {
-        void *p = nullptr;
+    if (!g_na_dev[dev].partials) {
+        void *p = nullptr, *st = nullptr;
         RNB_CU(cudaGetSymbolAddress(&p, g_na_partials));
-        g_na_dev_ptr[dev] = static_cast<float *>(p);
+        RNB_CU(cudaGetSymbolAddress(&st, g_na_status));
+        g_na_dev[dev].status = static_cast<int *>(st);
+        g_na_dev[dev].partials = static_cast<float *>(p);
     }
-    *out = g_na_dev_ptr[dev];
+    *out = g_na_dev[dev];
     return RNB_B200_OK;
 }
 
@@ -53,8 +64,13 @@ extern "C" int rnb_b200_attention_decode_hd128_noalloc(const float *q_dev, const
     if (num_heads > (size_t)NA_MAX_HEADS)
         return fail(RNB_B200_VALIDATION_FAILED, "no-alloc attention supports at most %d query heads, got %zu", NA_MAX_HEADS, num_heads);
     if (kv_len == 0 || kv_len > (size_t)0x7fffffff) return fail(RNB_B200_VALIDATION_FAILED, "attention kv_len must be in 1..2^31-1, got %zu", kv_len);
-    float *partials = nullptr;
-    RNB_TRY(na_scratch(&partials));
+    // the kernels read q with 16-byte loads and K/V with 8-byte (16-byte on the tensor-core path) loads:
+    // a misaligned pointer would raise a device fault instead of an error code
+    if (((uintptr_t)q_dev & 15u) || ((uintptr_t)k_dev & 7u) || ((uintptr_t)v_dev & 7u) || ((uintptr_t)out_dev & 3u))
+        return fail(RNB_B200_VALIDATION_FAILED, "attention operands are not aligned: q needs 16 bytes, k and v 8 bytes, out 4 bytes");
+    NaDevice nd;
+    RNB_TRY(na_device(&nd));
+    float *partials = nd.partials;
     int sm = 148, dev = 0;
     RNB_CU(cudaGetDevice(&dev));
     RNB_CU(cudaDeviceGetAttribute(&sm, cudaDevAttrMultiProcessorCount, dev));
@@ -63,5 +79,17 @@ extern "C" int rnb_b200_attention_decode_hd128_noalloc(const float *q_dev, const
     // Every (head, chunk) record that the merge reads is rewritten by this call's first kernel
     // (empty chunks write max = -inf, sum = 0), so nothing in the array has to start at zero.
     return launch_flash_decode((cudaStream_t)stream, q_dev, k_dev, v_dev, nullptr, (int)kv_len, (int)num_heads, (int)num_kv_heads,
-                               scale, partials, n_chunks, out_dev);
+                               scale, partials, n_chunks, out_dev, nd.status);
+}
+
+extern "C" int rnb_b200_attention_decode_hd128_noalloc_status(int *status_out, void *stream) {
+    if (!status_out) return fail(RNB_B200_VALIDATION_FAILED, "null pointer argument");
+    NaDevice nd;
+    RNB_TRY(na_device(&nd));
+    int v = 0;
+    RNB_CU(cudaMemcpyAsync(&v, nd.status, sizeof(int), cudaMemcpyDeviceToHost, (cudaStream_t)stream));
+    RNB_CU(cudaStreamSynchronize((cudaStream_t)stream));
+    if (v != 0) RNB_CU(cudaMemsetAsync(nd.status, 0, sizeof(int), (cudaStream_t)stream));
+    *status_out = v;
+    return RNB_B200_OK;
 }

@@ -128,7 +128,9 @@ struct State {
     std::map<std::pair<const void *, size_t>, Resident> resident;
     uint64_t epoch = 0;
     rnb_b200_cache_snapshot ctr{};
-    DevBuf in_f32, xq, xq2, out_f32, mid_a, mid_b, mid_c, jobs, partials, misc, transient, xb;
+    DevBuf in_f32, xq, xq2, out_f32, mid_a, mid_b, mid_c, jobs, partials, misc, xb;
+    std::vector<DevBuf> transient_pool;   // over-budget weights of the current call, one buffer per upload
+    size_t transient_used = 0;
     PinnedBuf pin_in, pin_out, pin_jobs;
     int *dev_error = nullptr;
     std::map<size_t, KvMirror> kv_mirrors;
@@ -138,6 +140,7 @@ struct State {
     int open();
     void close();
     int resident_ptr(const uint8_t *host, size_t len, bool pin, const uint8_t **dev_out);
+    int transient_upload(const uint8_t *host, size_t len, const uint8_t **dev_out);
     void evict_all(bool include_pinned);
     int h2d(void *dst, const void *src, size_t n, PinnedBuf &stage, size_t stage_off = 0);
     int check_dev_error();

@@ -86,6 +86,12 @@ def prewarm_q4k_weights(slices) -> int:
     return got.value
 
 
+def inject_resident_alloc_ooms_for_test(count: int) -> None:
+    """The next `count` device allocations of the resident cache report out-of-memory (host-side
+    fault injection, as the reference's test hook of the same name)."""
+    check(load().rnb_b200_inject_resident_alloc_ooms_for_test(count))
+
+
 def register_host_range(a: np.ndarray) -> None:
     check(load().rnb_b200_register_host_range(_p(a), a.nbytes))
 

@@ -87,3 +87,54 @@ def moe_description(seed: int, n_layer=2, hidden=512, n_head=4, n_kv_head=2, voc
                n_ff_expert=n_ff_expert)
     return dict(cfg=cfg, layers=layers, token_embd=quantized(rng, Q4_K, vocab, hidden, 1.0),
                 out_norm=np.ones(hidden, np.float32), output=quantized(rng, Q6_K, vocab, hidden, sigma))
+
+
+def synth(ggml_type: int, rows: int, cols: int, seed: int, sigma: float = 0.02):
+    """(type, blocks) of a seeded N(0, sigma) matrix from the oracle's fast generator."""
+    return ggml_type, orc.synth_matrix(ggml_type, rows, cols, seed, sigma)
+
+
+def llama_description_fast(seed: int, n_layer=2, hidden=4096, n_head=32, n_kv_head=8, n_ff=14336, vocab=128256,
+                           rope_theta=5e5, rms_eps=1e-5, sigma=0.02):
+    """Llama-style stack in the Q4_K_M convention at full width (Llama-3-8B by default) with few
+    layers: weights come from the oracle's fast seeded generator instead of numpy + the
+    reference quantiser, which would take minutes at these sizes."""
+    hd = 128
+    layers = []
+    for l in range(n_layer):
+        b = seed * 1000 + l * 16
+        layers.append(dict(
+            attn_norm=np.ones(hidden, np.float32), ffn_norm=np.ones(hidden, np.float32),
+            wq=synth(Q4_K, n_head * hd, hidden, b + 1, sigma), wk=synth(Q4_K, n_kv_head * hd, hidden, b + 2, sigma),
+            wv=synth(Q6_K, n_kv_head * hd, hidden, b + 3, sigma), wo=synth(Q4_K, hidden, n_head * hd, b + 4, sigma),
+            gate=synth(Q4_K, n_ff, hidden, b + 5, sigma), up=synth(Q4_K, n_ff, hidden, b + 6, sigma),
+            down=synth(Q6_K, hidden, n_ff, b + 7, sigma)))
+    cfg = dict(n_layer=n_layer, hidden=hidden, n_head=n_head, n_kv_head=n_kv_head, head_dim=hd, n_ff=n_ff,
+               vocab=vocab, rope_neox=0, rms_eps=rms_eps, rope_theta=rope_theta, n_expert=0, n_expert_used=0,
+               n_ff_expert=0)
+    return dict(cfg=cfg, layers=layers, token_embd=synth(Q4_K, vocab, hidden, seed * 1000 + 900, 1.0),
+                out_norm=np.ones(hidden, np.float32), output=synth(Q6_K, vocab, hidden, seed * 1000 + 901, sigma))
+
+
+def moe_description_fast(seed: int, n_layer=2, hidden=2048, n_head=32, n_kv_head=4, vocab=32768, n_expert=128,
+                         n_expert_used=8, n_ff_expert=768, rope_theta=1e6, rms_eps=1e-6, sigma=0.02):
+    """Qwen3-30B-A3B-shaped stack (Q6_K attention, Q4_K experts, f32 N(0,1) router, half-split
+    RoPE) at full width with few layers, weights from the oracle's fast generator."""
+    rng = np.random.default_rng(seed)
+    hd = 128
+    layers = []
+    for l in range(n_layer):
+        b = seed * 1000 + l * 16
+        layers.append(dict(
+            attn_norm=np.ones(hidden, np.float32), ffn_norm=np.ones(hidden, np.float32),
+            wq=synth(Q6_K, n_head * hd, hidden, b + 1, sigma), wk=synth(Q6_K, n_kv_head * hd, hidden, b + 2, sigma),
+            wv=synth(Q6_K, n_kv_head * hd, hidden, b + 3, sigma), wo=synth(Q6_K, hidden, n_head * hd, b + 4, sigma),
+            router=rng.standard_normal((n_expert, hidden)).astype(np.float32),
+            gate_exps=synth(Q4_K, n_expert * n_ff_expert, hidden, b + 5, sigma),
+            up_exps=synth(Q4_K, n_expert * n_ff_expert, hidden, b + 6, sigma),
+            down_exps=synth(Q4_K, n_expert * hidden, n_ff_expert, b + 7, sigma)))
+    cfg = dict(n_layer=n_layer, hidden=hidden, n_head=n_head, n_kv_head=n_kv_head, head_dim=hd, n_ff=0, vocab=vocab,
+               rope_neox=1, rms_eps=rms_eps, rope_theta=rope_theta, n_expert=n_expert, n_expert_used=n_expert_used,
+               n_ff_expert=n_ff_expert)
+    return dict(cfg=cfg, layers=layers, token_embd=synth(Q4_K, vocab, hidden, seed * 1000 + 900, 1.0),
+                out_norm=np.ones(hidden, np.float32), output=synth(Q6_K, vocab, hidden, seed * 1000 + 901, sigma))

@@ -114,3 +114,32 @@ def test_split_kv_chunk_rule(lib):
     assert f(32768, 1) == 592        # one KV head per GPU: no cap
     assert f(100, 8) == 4            # short cache: one chunk per 32 positions
     assert f(0, 8) == 1
+
+
+def test_device_pointer_attention_rejects_bad_arguments_before_any_launch(lib):
+    """rnb_b200_dev_flash_decode and the allocation-free entry point validate chunk count,
+    cache length, null pointers and pointer alignment on the host: an out-of-range chunk count
+    would index past the merge kernel's shared array, a misaligned pointer would fault on the
+    device.  No GPU is needed to be refused."""
+    f = lib.rnb_b200_dev_flash_decode
+    err = lambda: lib.rnb_b200_last_error().decode()
+    big = 1 << 40
+    q, k, v, part, out = 0x10000, 0x20000, 0x30000, 0x40000, 0x50000   # never dereferenced: every call is refused
+    assert f(q, k, v, 128, 32, 8, 0.1, part, big, 1025, out, None) == 2 and "n_chunks must be in 1..1024" in err()
+    assert f(q, k, v, 128, 32, 8, 0.1, part, big, 0, out, None) == 2
+    assert f(q, k, v, 0, 32, 8, 0.1, part, big, 4, out, None) == 2 and "kv_len" in err()
+    assert f(q, k, v, 1 << 31, 32, 8, 0.1, part, big, 4, out, None) == 2 and "kv_len" in err()
+    assert f(None, k, v, 128, 32, 8, 0.1, part, big, 4, out, None) == 2 and "null pointer" in err()
+    assert f(q, k, v, 128, 32, 8, 0.1, None, big, 4, out, None) == 2 and "null pointer" in err()
+    assert f(q + 4, k, v, 128, 32, 8, 0.1, part, big, 4, out, None) == 2 and "not aligned" in err()
+    assert f(q, k + 2, v, 128, 32, 8, 0.1, part, big, 4, out, None) == 2 and "not aligned" in err()
+    assert f(q, k, v + 4, 128, 32, 8, 0.1, part, big, 4, out, None) == 2 and "not aligned" in err()
+    assert f(q, k, v, 128, 32, 8, 0.1, part, big, 4, out + 2, None) == 2 and "not aligned" in err()
+    assert f(q, k, v, 128, 32, 8, 0.1, part, 16, 4, out, None) == 2 and "scratch too small" in err()
+    assert f(q, k, v, 128, 33, 8, 0.1, part, big, 4, out, None) == 2 and "multiple of num_kv_heads" in err()
+    g = lib.rnb_b200_attention_decode_hd128_noalloc
+    assert g(q + 8, k, v, 128, 32, 8, 0.1, out, None) == 2 and "not aligned" in err()
+    assert g(q, k + 4, v, 128, 32, 8, 0.1, out, None) == 2 and "not aligned" in err()
+    assert g(q, k, v, 0, 32, 8, 0.1, out, None) == 2 and "kv_len" in err()
+    assert g(q, k, v, 128, 65, 1, 0.1, out, None) == 2 and "at most 64 query heads" in err()
+    assert g(None, k, v, 128, 32, 8, 0.1, out, None) == 2 and "null pointer" in err()

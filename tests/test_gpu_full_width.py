@@ -1,0 +1,126 @@
+"""Parity at the widths the headline configurations are quoted on, with few layers so that the
+CPU oracle stays in seconds: Llama-3-8B width (hidden 4096, 32 / 8 heads, FFN 14336, vocab
+128 256) and Qwen3-30B-A3B width (hidden 2048, 128 experts top-8, expert FFN 768, 32 / 4 heads).
+Weights are seeded N(0, 0.02) blocks from the oracle's fast generator.
+"""
+import numpy as np
+import pytest
+
+import oracle as orc
+from synth import llama_description_fast, max_err_vs_norm, moe_description_fast
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def llama8b_width():
+    return llama_description_fast(seed=3, n_layer=2)
+
+
+def _first_divergence(a, b):
+    return next((i for i, (x, y) in enumerate(zip(a, b)) if x != y), None)
+
+
+def test_llama3_8b_width_64_greedy_ids_identical(llama8b_width):
+    """Prompt fed token by token, then 64 greedy steps: every id equals the oracle's."""
+    import runnburn_b200 as r
+    desc = llama8b_width
+    n_prompt, n_steps = 16, 64
+    dec = r.Decoder(r.ModelConfig(max_ctx=n_prompt + n_steps + 4, **desc["cfg"]))
+    dec.load_description(desc)
+    ref = orc.Model(desc, n_prompt + n_steps + 4)
+    prompt = np.random.default_rng(11).integers(0, desc["cfg"]["vocab"], n_prompt).tolist()
+    pos, tok_g, tok_c = 0, None, None
+    for t in prompt:
+        tok_g = dec.step(t, pos)
+        tok_c = orc.argmax_last(ref.decode(t, pos))
+        pos += 1
+    gpu_ids, cpu_ids, margins, errs = [], [], [], []
+    for _ in range(n_steps):
+        gpu_ids.append(tok_g)
+        cpu_ids.append(tok_c)
+        if tok_g != tok_c:
+            break
+        tok_g, lg = dec.step(tok_g, pos, want_logits=True)
+        lc = ref.decode(tok_c, pos)
+        top2 = np.partition(lc, -2)[-2:]
+        margins.append(float(top2[1] - top2[0]))
+        errs.append(max_err_vs_norm(lg, lc))
+        assert tok_g == orc.argmax_last(lg)
+        tok_c = orc.argmax_last(lc)
+        pos += 1
+    first = _first_divergence(gpu_ids, cpu_ids)
+    assert first is None, f"greedy ids diverge at step {first}: gpu={gpu_ids[first]} cpu={cpu_ids[first]}, " \
+                          f"logit margin of the step before = {margins[first - 1] if first else float('nan'):.3e}"
+    assert len(gpu_ids) == n_steps and max(errs) <= 1e-3
+    dec.close()
+    ref.close()
+
+
+def test_llama3_8b_width_ids_after_tensor_core_prefill(llama8b_width):
+    """The same prompt through rnb_b200_decoder_prefill (bf16 tensor-core matmuls), then 64 greedy
+    steps, against the exact token-by-token path of the same decoder.  The prefill rounds weights
+    and tokens to bf16, so the K/V rows it leaves are not the exact ones; where the two id
+    sequences part, the step's top-2 logit margin has to be within that rounding's reach."""
+    import runnburn_b200 as r
+    desc = llama8b_width
+    n_prompt, n_steps = 48, 64
+    cfg = r.ModelConfig(max_ctx=n_prompt + n_steps + 4, **desc["cfg"])
+    exact, fast = r.Decoder(cfg), r.Decoder(cfg)
+    exact.load_description(desc)
+    fast.load_description(desc)
+    prompt = np.random.default_rng(12).integers(0, desc["cfg"]["vocab"], n_prompt).tolist()
+    tok_e = None
+    for pos, t in enumerate(prompt):
+        tok_e = exact.step(t, pos)
+    tok_f = fast.prefill(prompt, 0)
+    le, lf = exact.read_logits(), fast.read_logits()
+    assert max_err_vs_norm(lf, le) <= 3e-2
+    ids_e, ids_f, margins = [], [], []
+    pos = n_prompt
+    for _ in range(n_steps):
+        ids_e.append(tok_e)
+        ids_f.append(tok_f)
+        if tok_e != tok_f:
+            break
+        tok_e, le = exact.step(tok_e, pos, want_logits=True)
+        tok_f = fast.step(tok_f, pos)
+        top2 = np.partition(le, -2)[-2:]
+        margins.append(float(top2[1] - top2[0]) / float(np.max(np.abs(le))))
+        pos += 1
+    first = _first_divergence(ids_e, ids_f)
+    if first is not None:
+        m = margins[first - 1] if first else 0.0
+        print(f"ids after the bf16 prefill part from the exact path at step {first}; relative top-2 margin there {m:.3e}")
+        assert m <= 3e-2, f"ids diverge at step {first} although the top-2 margin {m:.3e} is beyond bf16 rounding"
+    else:
+        assert len(ids_e) == n_steps
+    exact.close()
+    fast.close()
+
+
+def test_qwen3_30b_a3b_width_expert_ids_and_tokens():
+    """128 experts, top-8, hidden 2048: the routed expert ids of every layer and the greedy
+    token of every step equal the oracle's."""
+    import runnburn_b200 as r
+    desc = moe_description_fast(seed=5, n_layer=2)
+    n_prompt, n_steps = 8, 24
+    dec = r.Decoder(r.ModelConfig(max_ctx=n_prompt + n_steps + 4, **desc["cfg"]))
+    dec.load_description(desc)
+    ref = orc.Model(desc, n_prompt + n_steps + 4)
+    prompt = np.random.default_rng(13).integers(0, desc["cfg"]["vocab"], n_prompt).tolist()
+    pos, tok_g, tok_c = 0, None, None
+    for t in prompt + [None] * n_steps:
+        if t is None:
+            assert tok_g == tok_c, f"greedy ids diverge at position {pos}"
+            t = tok_g
+        tok_g, lg = dec.step(t, pos, want_logits=True)
+        lc = ref.decode(t, pos)
+        tok_c = orc.argmax_last(lc)
+        for layer in range(2):
+            got, want = dec.read_expert_ids(layer), ref.expert_ids(layer)
+            assert len(got) == 8 and np.array_equal(got, want), f"expert ids differ at position {pos}, layer {layer}: {got} vs {want}"
+        assert max_err_vs_norm(lg, lc) <= 1e-3
+        pos += 1
+    dec.close()
+    ref.close()

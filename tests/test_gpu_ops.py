@@ -196,7 +196,9 @@ def test_resident_cache_counters_and_eviction(ops):
 
 # ---- attention ----------------------------------------------------------------------------------
 @pytest.mark.parametrize("heads,kvh,kv_len", [(32, 8, 1), (32, 8, 7), (32, 8, 333), (32, 8, 4096), (32, 4, 1025),
-                                              (64, 8, 2000), (8, 8, 65), (6, 2, 100), (32, 2, 300), (16, 8, 20000), (24, 2, 17)])
+                                              (64, 8, 2000), (8, 8, 65), (6, 2, 100), (32, 2, 300), (16, 8, 20000), (24, 2, 17),
+                                              # the headline configurations' own shapes: MoE at 8192, a 70B 8-GPU shard and the whole 70B at 32768
+                                              (32, 4, 8192), (8, 1, 32768), (64, 8, 32768)])
 def test_attention_decode_hd128(ops, heads, kvh, kv_len):
     rng = np.random.default_rng(heads * 1000 + kv_len)
     q = rng.standard_normal(heads * 128).astype(np.float32)

@@ -287,3 +287,126 @@ def test_glue_formulas(orc):
     assert orc.argmax_last(np.array([1, 5, 5, 2], np.float32)) == 2
     g = orc.silu_mul(np.array([0.0, 1.0, -2.0], np.float32), np.array([3.0, 2.0, 1.0], np.float32))
     assert np.allclose(g, [0.0, 2.0 / (1 + np.exp(-1.0)), -2.0 / (1 + np.exp(2.0))], atol=1e-6)
+
+
+# ---- the reference's own attention / RoPE / RMSNorm fixtures, restated -------------------------
+def _lcg_f32(seed: int, n: int) -> np.ndarray:
+    """The generator of the reference's attention tests (kernels/attention/mod.rs:213-221):
+    a 64-bit LCG whose top 31 bits map to [-1, 1)."""
+    out = np.empty(n, np.float32)
+    s = seed
+    for i in range(n):
+        s = (s * 6364136223846793005 + 1442695040888963407) & 0xFFFFFFFFFFFFFFFF
+        out[i] = np.float32(np.float32(s >> 33) / np.float32(1 << 31)) * np.float32(2.0) - np.float32(1.0)
+    return out
+
+
+def _naive_attention(q, k, v, seq, kv, nh, nkv, hd):
+    """naive_attention of kernels/attention/mod.rs:146-201 (f32 throughout, causal by global position)."""
+    out = np.zeros(seq * nh * hd, np.float32)
+    scale = np.float32(1.0) / np.sqrt(np.float32(hd))
+    for h in range(nh):
+        kvh = h // (nh // nkv)
+        for i in range(seq):
+            qr = q[i * nh * hd + h * hd:][:hd]
+            gp = (kv - seq) + i
+            n_vis = min(gp, kv - 1) + 1
+            sc = np.full(kv, -np.inf, np.float32)
+            for j in range(n_vis):
+                kr = k[j * nkv * hd + kvh * hd:][:hd]
+                dot = np.float32(0.0)
+                for d in range(hd):
+                    dot = np.float32(dot + qr[d] * kr[d])
+                sc[j] = dot * scale
+            p = np.exp((sc - sc.max()).astype(np.float32)).astype(np.float32)
+            p = (p / p.sum(dtype=np.float32)).astype(np.float32)
+            acc = np.zeros(hd, np.float32)
+            for j in range(kv):
+                acc = (acc + p[j] * v[j * nkv * hd + kvh * hd:][:hd]).astype(np.float32)
+            out[i * nh * hd + h * hd:][:hd] = acc
+    return out
+
+
+def test_reference_attention_fixtures(orc):
+    # test_attention_decode_into_matches_tensor (kernels/attention/mod.rs:32-88): sin/cos ramps,
+    # 4 heads over 2 KV heads, head_dim 4, 3 cached rows; f16 cache vs f32 attention within 1e-2
+    nh, nkv, hd, kv = 4, 2, 4, 3
+    q = np.sin(np.arange(nh * hd, dtype=np.float32) * np.float32(0.1)).astype(np.float32)
+    kf = np.cos(np.arange(kv * nkv * hd, dtype=np.float32) * np.float32(0.2)).astype(np.float32)
+    vf = np.sin(np.arange(kv * nkv * hd, dtype=np.float32) * np.float32(0.3)).astype(np.float32)
+    scale = 1.0 / np.sqrt(np.float32(hd))
+    want = orc.attention_prefill(q, kf, vf, 1, kv, nh, nkv, hd, scale)
+    got = orc.attention_decode(q, orc.f32_to_f16_bits(kf), orc.f32_to_f16_bits(vf), nh, nkv, hd, kv, scale)
+    assert np.max(np.abs(got - want)) < 1e-2
+    assert np.max(np.abs(want - _naive_attention(q, kf, vf, 1, kv, nh, nkv, hd))) < 1e-5
+    # test_attention_single_token (:112-127): one query, one key -> the value row itself
+    out = orc.attention_prefill(np.float32([1, 0]), np.float32([1, 0]), np.float32([3, 7]), 1, 1, 1, 1, 2, 1.0 / np.sqrt(2.0))
+    assert abs(out[0] - 3.0) < 1e-4 and abs(out[1] - 7.0) < 1e-4
+    # test_attention_long_seq_matches_naive (:203-266), at a quarter of its sequence length so that
+    # the pure-Python naive loop stays in seconds: LCG seed 42, 4 heads, head_dim 64, causal
+    seq, nh, nkv, hd = 32, 4, 4, 64
+    g = _lcg_f32(42, seq * nh * hd + 2 * seq * nkv * hd)
+    q, k, v = g[:seq * nh * hd], g[seq * nh * hd:][:seq * nkv * hd], g[seq * nh * hd + seq * nkv * hd:]
+    flash = orc.attention_prefill(q, k, v, seq, seq, nh, nkv, hd, 1.0 / np.sqrt(np.float32(hd)))
+    assert np.max(np.abs(flash - _naive_attention(q, k, v, seq, seq, nh, nkv, hd))) < 1e-4
+    # test_attention_decode_flash_matches_legacy (:346-428): LCG seed 12345, 8 heads over 4 KV heads,
+    # head_dim 64, 128 rows; the online form against the 4-pass form: cos >= 0.9999, max abs < 1e-3
+    nh, nkv, hd, kv = 8, 4, 64, 128
+    g = _lcg_f32(12345, nh * hd + 2 * kv * nkv * hd)
+    q, k, v = g[:nh * hd], g[nh * hd:][:kv * nkv * hd], g[nh * hd + kv * nkv * hd:]
+    kb, vb = orc.f32_to_f16_bits(k), orc.f32_to_f16_bits(v)
+    legacy = orc.attention_decode(q, kb, vb, nh, nkv, hd, kv, 1.0 / np.sqrt(np.float32(hd)))
+    flash = orc.attention_decode(q, kb, vb, nh, nkv, hd, kv, 1.0 / np.sqrt(np.float32(hd)), online=True)
+    cos = float(np.dot(legacy.astype(np.float64), flash.astype(np.float64)) /
+                (np.linalg.norm(legacy.astype(np.float64)) * np.linalg.norm(flash.astype(np.float64))))
+    assert cos >= 0.9999 and np.max(np.abs(legacy - flash)) < 1e-3
+    # the f16 conversion the fixtures rely on is IEEE round-to-nearest-even (half::f16::from_f32)
+    assert np.array_equal(kb, k.astype(np.float16).view(np.uint16))
+
+
+def test_reference_rope_fixtures(orc):
+    """kernels/rope.rs:725-790: position 0 is the identity, position 1 rotates, the in-place form
+    equals the tensor form, positions advance per token, and the closed form of the first pairs
+    (pair 0 turns by `pos` radians, pair 1 by pos * theta^(-2/head_dim))."""
+    x = np.float32([1, 2, 3, 4])
+    assert np.max(np.abs(orc.rope(x, 0, 4, 4, 10000.0) - x)) < 1e-5
+    r = orc.rope(np.float32([1, 0, 0, 0]), 1, 4, 4, 10000.0)
+    assert abs(r[0] - 1.0) > 1e-3 or abs(r[1]) > 1e-3
+    assert abs(r[0] - np.cos(np.float32(1.0))) < 1e-5 and abs(r[1] - np.sin(np.float32(1.0))) < 1e-5
+    r = orc.rope(np.float32([1, 0, 0, 1]), 1, 4, 4, 10000.0)
+    a1 = np.float32(0.01)                                      # 1 * 10000^(-2/4)
+    assert abs(r[2] + np.sin(a1)) < 1e-6 and abs(r[3] - np.cos(a1)) < 1e-6
+    # two heads of one token share the angles (test_rope_inplace_matches_tensor, pos 5)
+    r = orc.rope(np.float32([1, 0, 0, 1, 2, 0, 0, 2]), 5, 4, 8, 10000.0)
+    assert np.allclose(r[4:], 2 * r[:4], atol=1e-6)
+    assert abs(r[0] - np.cos(np.float32(5.0))) < 1e-5 and abs(r[1] - np.sin(np.float32(5.0))) < 1e-5
+    # test_rope_per_token_position: token 0 at pos 0 unchanged, token 1 at pos 1 rotated
+    two = np.float32([1, 2, 3, 4, 1, 2, 3, 4])
+    r = orc.rope(two, 0, 4, 4, 10000.0)
+    assert np.max(np.abs(r[:4] - two[:4])) < 1e-5 and (abs(r[4] - 1.0) > 1e-3 or abs(r[5] - 2.0) > 1e-3)
+
+
+def test_reference_rms_norm_fixtures(orc):
+    """kernels/norm.rs:339-415: [1,2,3,4] with unit weights divides by sqrt(7.5 + eps); weighted
+    rows follow (x / rms) * w bit for bit; the f64 reduce stays within 2e-5 of the f32 scalar
+    formula on the 1536-wide pattern rows of the reference's AVX2 test."""
+    x = np.float32([1, 2, 3, 4])
+    got = orc.rms_norm(x, np.ones(4, np.float32), 1e-5)
+    rms = np.sqrt(np.float32(7.5) + np.float32(1e-5))
+    assert abs(got[0] - 1.0 / rms) < 1e-4 and abs(got[1] - 2.0 / rms) < 1e-4
+    w = np.float32([1.0, 0.5, 2.0, 0.25])
+    rms64 = np.float32(np.sqrt(np.float64(7.5) + np.float64(np.float32(1e-5))))
+    assert np.array_equal(orc.rms_norm(x, w, 1e-5).view(np.uint32), ((x / rms64) * w).astype(np.float32).view(np.uint32))
+    hidden, rows = 1536, 3
+    i = np.arange(hidden * rows)
+    inp = (((i * 37 % 251).astype(np.float32) - np.float32(125.0)) / np.float32(31.0)).astype(np.float32)
+    j = np.arange(hidden)
+    wt = (((j * 19 % 127).astype(np.float32) - np.float32(63.0)) / np.float32(97.0)).astype(np.float32)
+    got = orc.rms_norm(inp, wt, 1e-5).reshape(rows, hidden)
+    for s in range(rows):
+        xs = inp[s * hidden:(s + 1) * hidden]
+        acc = np.float32(0.0)
+        for vv in xs:                                           # rms_norm_into_scalar: sequential f32 sum
+            acc = np.float32(acc + vv * vv)
+        rms32 = np.sqrt(np.float32(acc / np.float32(hidden)) + np.float32(1e-5))
+        assert np.max(np.abs(got[s] - (xs / rms32) * wt)) < 2e-5

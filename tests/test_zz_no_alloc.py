@@ -56,4 +56,12 @@ def test_noalloc_attention_matches_regular_entry_point_twice():
     rc = L.rnb_b200_attention_decode_hd128_noalloc(q_dev.data_ptr(), k_dev.data_ptr(), v_dev.data_ptr(), 16, 128, 8, scale,
                                                    out_dev.data_ptr(), None)
     assert rc == 2 and b"at most 64 query heads" in L.rnb_b200_last_error()
+    # a pointer the kernels' vector loads could not take is refused too, not left to fault
+    rc = L.rnb_b200_attention_decode_hd128_noalloc(q_dev.data_ptr() + 4, k_dev.data_ptr(), v_dev.data_ptr(), 16, heads, kvh, scale,
+                                                   out_dev.data_ptr(), None)
+    assert rc == 2 and b"not aligned" in L.rnb_b200_last_error()
+    # the entry point reports its kernels' bounded waits through its own fixed status word
+    status = C.c_int(-1)
+    assert L.rnb_b200_attention_decode_hd128_noalloc_status(C.byref(status), C.c_void_p(stream)) == 0
+    assert status.value == 0
     assert ops.dev_error_flag() == 0
