@@ -216,9 +216,11 @@ def run_reference(args, shape, ctx, name, rank, world):
     value = s.tok_per_s(total / len(layer), min(head))
     cb = {"value": value, "unit": UNIT, "cores": s.threads, "kind": "port", "sample": s.describe()}
     return {"impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": 1000.0 * total / len(layer), "higher_is_better": True,
+            # a step is one decode token: the timed layer sample scaled to the whole stack plus the LM head
+            "warmup": args.warmup, "ms_per_step": 1000.0 / value, "ms_per_layer_sample": 1000.0 * total / len(layer), "higher_is_better": True,
             "scaling": "strong" if args.gpus > 1 else "weak", "vs_baseline": None, "dtype": "int8xint4->int32, f32 accumulate",
-            "data": "synthetic", "config": {"workload": name, "step": "one layer sample on the host CPU", "context": ctx},
+            "data": "synthetic", "config": {"workload": name, "context": ctx, "kv_cache": "f16",
+                                            "timed": "%d repetitions of one layer's decode work on the host CPU, scaled to %d layers + LM head" % (len(layer), shape["n_layer"])},
             "cpu_baseline": cb, "gpu_launches": 0,
             "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
 

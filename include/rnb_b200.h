@@ -218,6 +218,70 @@ typedef struct {
 } rnb_b200_bundle_admission;
 /* evaluate_expert_bundle_admission — sparse_expert_cache.rs:221-245: 1 = admit */
 int rnb_b200_evaluate_expert_bundle_admission(const rnb_b200_bundle_admission *a);
+/* ---- expert-bundle cache bookkeeping (host accounting only) ---------------------------------------
+ * crates/rnb-memory/src/sparse_expert_cache.rs.  Keys are (layer, expert), ordered layer first. */
+/* ExpertBundleReuseHistory — :272-393.  observe() returns the decayed frequency before this
+ * lookup; frequency halves once per `decay_interval` (default = capacity, at least 1) epochs
+ * spent unobserved; over capacity the minimum of (effective frequency, last-seen epoch, key)
+ * goes.  decay_interval 0 on create selects the default. */
+typedef struct rnb_b200_expert_history rnb_b200_expert_history;
+typedef struct {
+    uint64_t capacity, decay_interval, epoch, len;
+} rnb_b200_expert_history_info;
+int rnb_b200_expert_history_create(size_t capacity, uint64_t decay_interval, rnb_b200_expert_history **out);
+void rnb_b200_expert_history_destroy(rnb_b200_expert_history *h);
+uint64_t rnb_b200_expert_history_observe(rnb_b200_expert_history *h, uint32_t layer, uint32_t expert);
+void rnb_b200_expert_history_set_capacity(rnb_b200_expert_history *h, size_t capacity);
+int rnb_b200_expert_history_contains(const rnb_b200_expert_history *h, uint32_t layer, uint32_t expert);
+void rnb_b200_expert_history_get_info(const rnb_b200_expert_history *h, rnb_b200_expert_history_info *out);
+void rnb_b200_expert_history_set_epoch_for_test(rnb_b200_expert_history *h, uint64_t epoch);
+/* SparseExpertCacheBudget over ByteLruPolicy — :505-530, crates/rnb-memory/src/byte_lru.rs:17-116:
+ * byte-budgeted LRU accounting; touch() returns the keys to reclaim as (layer << 32) | expert. */
+typedef struct rnb_b200_expert_budget rnb_b200_expert_budget;
+int rnb_b200_expert_budget_create(uint64_t max_bytes, rnb_b200_expert_budget **out);
+void rnb_b200_expert_budget_destroy(rnb_b200_expert_budget *b);
+int rnb_b200_expert_budget_touch(rnb_b200_expert_budget *b, uint32_t layer, uint32_t expert, uint64_t bytes,
+                                 uint64_t *evicted, size_t cap, size_t *n_evicted);
+int rnb_b200_expert_budget_remove(rnb_b200_expert_budget *b, uint32_t layer, uint32_t expert);
+uint64_t rnb_b200_expert_budget_resident_bytes(const rnb_b200_expert_budget *b);
+/* evaluate_expert_bundle_admission with its whole cost record — :221-270.  The 128-bit fields of
+ * ExpertBundleAdmissionCost come back as (lo, hi) pairs; residency: 0 full, 1 partial, 2 miss. */
+typedef struct {
+    uint64_t gate_bytes, up_bytes, down_bytes;
+    uint32_t gate_resident, up_resident, down_resident, replaces_temp_upload;
+    uint64_t predicted_future_reuses, eviction_reload_bytes;
+} rnb_b200_bundle_candidate;
+typedef struct {
+    uint32_t admit, profitable, residency, reserved;
+    uint64_t missing_admission_bytes, eviction_reload_bytes, predicted_future_reuses;
+    uint64_t predicted_saved_lo, predicted_saved_hi;
+    uint64_t net_saved_lo;
+    int64_t net_saved_hi;
+} rnb_b200_bundle_decision;
+int rnb_b200_evaluate_expert_bundle(const rnb_b200_bundle_candidate *c, rnb_b200_bundle_decision *out);
+/* ExpertBundleCacheStats, ExpertBundleObservationReceipt — :395-500 (saturating counters) */
+typedef struct {
+    uint64_t bundle_lookups, bundle_hits, bundle_partial_hits, bundle_misses, bundle_admissions,
+        bundle_evictions, admitted_bytes, evicted_bytes, h2d_bytes, temp_h2d_bytes;
+} rnb_b200_expert_bundle_stats;
+typedef struct {
+    uint32_t consumed, reserved;
+    rnb_b200_expert_bundle_stats pending_stats;
+} rnb_b200_expert_bundle_receipt;
+void rnb_b200_expert_stats_record_lookup(rnb_b200_expert_bundle_stats *s, int gate_resident, int up_resident, int down_resident);
+void rnb_b200_expert_stats_delta(const rnb_b200_expert_bundle_stats *after, const rnb_b200_expert_bundle_stats *before,
+                                 rnb_b200_expert_bundle_stats *out);
+void rnb_b200_expert_stats_add(rnb_b200_expert_bundle_stats *acc, const rnb_b200_expert_bundle_stats *delta);
+void rnb_b200_expert_receipt_record(rnb_b200_expert_bundle_receipt *r, const rnb_b200_expert_bundle_stats *stats);
+void rnb_b200_expert_receipt_mark_consumed(rnb_b200_expert_bundle_receipt *r);
+void rnb_b200_expert_receipt_clear_stats(rnb_b200_expert_bundle_receipt *r);
+/* qwen35_moe_layer_cache_limit / qwen35_moe_transient_reserve_bytes —
+ * crates/rnb-backend/cuda/src/runtime/state/moe_cache.rs:6-29 */
+uint64_t rnb_b200_qwen35_moe_layer_cache_limit(uint64_t model_moe_bytes, uint64_t free_bytes,
+                                               uint64_t device_resident_limit_bytes, uint64_t requested_bytes,
+                                               uint64_t runtime_headroom_bytes);
+uint64_t rnb_b200_qwen35_moe_transient_reserve_bytes(uint64_t dynamic_reserve_bytes, uint64_t model_moe_bytes,
+                                                     uint64_t resident_moe_bytes, uint64_t min_layer_bytes);
 /* DeviceResidencyPlan::from_snapshot — crates/rnb-memory/src/device_residency.rs:40-91:
  * resident_limit = free - reserve, reserve = clamp(ceil_256MiB(total/16), 512 MiB, 2 GiB) */
 uint64_t rnb_b200_resident_limit_for(uint64_t total_bytes, uint64_t free_bytes);

@@ -43,6 +43,29 @@ const GemvTuning &gemv_tuning() {
     }();
     return t;
 }
+int encode_weight_map(GmTensorMap *out, const uint8_t *w, size_t rows, size_t row_bytes, uint32_t box_bytes) {
+    static_assert(sizeof(GmTensorMap) == sizeof(CUtensorMap) && alignof(GmTensorMap) >= alignof(CUtensorMap), "descriptor size");
+    typedef CUresult (*EncodeTiled)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
+                                    const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+    static EncodeTiled encode = nullptr;
+    if (!encode) {
+        void *fn = nullptr;
+        cudaDriverEntryPointQueryResult q = cudaDriverEntryPointSymbolNotFound;
+        RNB_CU(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q));
+        if (q != cudaDriverEntryPointSuccess || !fn) return fail(RNB_B200_UNSUPPORTED, "the driver has no cuTensorMapEncodeTiled");
+        encode = reinterpret_cast<EncodeTiled>(fn);
+    }
+    if (((uintptr_t)w & 15u) || (row_bytes & 15u) || (box_bytes & 15u) || box_bytes / 8 > 256 || rows == 0)
+        return fail(RNB_B200_VALIDATION_FAILED, "weight matrix cannot be described for tiled copies (alignment or box width)");
+    const cuuint64_t dims[2] = {(cuuint64_t)(row_bytes / 8), (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)row_bytes};
+    const cuuint32_t box[2] = {(cuuint32_t)(box_bytes / 8), (cuuint32_t)GM_ROWS};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = encode(reinterpret_cast<CUtensorMap *>(out), CU_TENSOR_MAP_DATA_TYPE_UINT64, 2, const_cast<uint8_t *>(w), dims, strides, box, estr,
+                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(RNB_B200_CUDA_ERROR, "cuTensorMapEncodeTiled(weights) failed with driver code %d", (int)r);
+    return RNB_B200_OK;
+}
 static size_t g_gemv_smem_max = 0;
 size_t gemv_smem_max() { return g_gemv_smem_max; }
 int gemv_kernel_setup() {

@@ -315,10 +315,20 @@ __device__ __forceinline__ void split_f16x2(float x, float y, uint32_t &hi, uint
 // (8 / group) consecutive queries x the group's heads, query i sees positions
 // 0 .. kv_len - seq_len + i, and the normalised result is written straight to `out`
 // ([seq][head][128]); no chunking, the CTA walks all visible positions.
+// Optional tail of the decode kernel: the CTA that completes a KV head's last chunk (arrival counter,
+// re-armed by that CTA) merges the chunks of the group's query heads and writes the attention
+// output as f32 and / or as Q8_K blocks (two heads = one 256-element block), which saves the merge
+// launch.  counters: one int per KV head, zero before the launch.
+struct FdMerge {
+    int *counters;       // null: no merge here
+    float *out;          // [heads][128] f32, optional
+    uint8_t *xq_out;     // Q8K-dev layout of the heads x 128 vector, optional (needs an even head group)
+};
 template <bool PREFILL>
 __device__ __forceinline__ void fdm_body(const float *__restrict__ q, const uint16_t *__restrict__ k, const uint16_t *__restrict__ v,
                                          const int *__restrict__ kv_len_dev, int kv_len_host, int seq_len, int num_heads, int num_kv_heads,
-                                         float scale, float *__restrict__ partials, float *__restrict__ out, int *__restrict__ err_flag) {
+                                         float scale, float *__restrict__ partials, float *__restrict__ out, int *__restrict__ err_flag,
+                                         const FdMerge merge = FdMerge{nullptr, nullptr, nullptr}) {
     pdl_launch_dependents();
     pdl_wait();
     __shared__ __align__(128) uint8_t s_kv[FDM_KV_BYTES];   // K rows then V rows; merge scratch later
@@ -522,14 +532,76 @@ __device__ __forceinline__ void fdm_body(const float *__restrict__ q, const uint
         // the next head pass overwrites s_kv through the async proxy after these generic reads
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
+    if (PREFILL || !merge.counters) return;
+    // ---- last CTA of this KV head: merge its chunks --------------------------------------------
+    __shared__ int s_last;
+    __threadfence();   // this CTA's records are visible device-wide before it is counted
+    __syncthreads();
+    if (tid == 0) s_last = atomicAdd(&merge.counters[kv_h], 1) == n_chunks - 1;
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    float *s_f = reinterpret_cast<float *>(s_kv);                                   // [warp][n_chunks] rescale factors
+    float *s_o = reinterpret_cast<float *>(s_kv) + (FDM_THREADS / 32) * FD_MAX_CHUNKS;   // [head of the group][128] merged rows
+    static_assert(((FDM_THREADS / 32) * FD_MAX_CHUNKS + 16 * HD) * 4 <= FDM_KV_BYTES, "merge tail scratch must fit the staging area");
+    float *my_f = s_f + warp * FD_MAX_CHUNKS;
+    for (int g0 = 0; g0 < group; g0 += 16) {
+        const int n_here = min(16, group - g0);
+        // warp w merges heads w, w + 4, ... of this slice: lane = output dims 4 lane .. 4 lane + 3
+        for (int hh = warp; hh < n_here; hh += FDM_THREADS / 32) {
+            const int head = kv_h * group + g0 + hh;
+            const float *base = partials + (size_t)head * n_chunks * FD_PART_STRIDE;
+            float m = -INFINITY;
+            for (int c = lane; c < n_chunks; c += 32) m = fmaxf(m, __ldcg(base + (size_t)c * FD_PART_STRIDE + HD));
+            const float M = warp_max(m);
+            float l = 0.f;
+            for (int c = lane; c < n_chunks; c += 32) {
+                const float mc = __ldcg(base + (size_t)c * FD_PART_STRIDE + HD);
+                const float f = mc == -INFINITY ? 0.f : expf(mc - M);
+                my_f[c] = f;
+                l += __ldcg(base + (size_t)c * FD_PART_STRIDE + HD + 1) * f;
+            }
+            const float L = warp_sum(l);
+            __syncwarp();
+            float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 8
+            for (int c = 0; c < n_chunks; c++) {
+                // records are 130 floats apart: 8-byte alignment is all that holds for every chunk
+                const float2 *rp = reinterpret_cast<const float2 *>(base + (size_t)c * FD_PART_STRIDE) + 2 * lane;
+                const float2 r0 = __ldcg(rp), r1 = __ldcg(rp + 1);
+                const float f = my_f[c];
+                a.x += r0.x * f;
+                a.y += r0.y * f;
+                a.z += r1.x * f;
+                a.w += r1.y * f;
+            }
+            const float4 o4 = L > 0.f ? make_float4(a.x / L, a.y / L, a.z / L, a.w / L) : make_float4(0.f, 0.f, 0.f, 0.f);
+            if (merge.out) *(reinterpret_cast<float4 *>(merge.out + (size_t)head * HD) + lane) = o4;
+            *(reinterpret_cast<float4 *>(s_o + hh * HD) + lane) = o4;
+            __syncwarp();
+        }
+        __syncthreads();
+        if (merge.xq_out) {
+            // heads 2b, 2b + 1 of the slice are one Q8_K block; the slice starts at an even head
+            for (int bq = warp; 2 * bq + 1 < n_here; bq += FDM_THREADS / 32) {
+                const float4 v0 = *(reinterpret_cast<const float4 *>(s_o + 2 * bq * HD) + 2 * lane), v1 = *(reinterpret_cast<const float4 *>(s_o + 2 * bq * HD) + 2 * lane + 1);
+                const float vv[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+                Q8kDevView dv = q8k_dev_view(merge.xq_out, num_heads * HD);
+                const int blk = (kv_h * group + g0) / 2 + bq;
+                q8k_quantize_block_warp(vv, lane, dv.qs + blk * 256, dv.d + blk, dv.bsum16 + blk * 16, nullptr);
+            }
+        }
+        __syncthreads();
+    }
+    if (tid == 0) merge.counters[kv_h] = 0;
 }
 
 RNB_GLOBAL void __launch_bounds__(FDM_THREADS, 4)
 flash_decode_mma_kernel(const float *__restrict__ q, const uint16_t *__restrict__ k,
                         const uint16_t *__restrict__ v, const int *__restrict__ kv_len_dev,
                         int kv_len_host, int num_heads, int num_kv_heads, float scale,
-                        float *__restrict__ partials, int *__restrict__ err_flag) {
-    fdm_body<false>(q, k, v, kv_len_dev, kv_len_host, 1, num_heads, num_kv_heads, scale, partials, nullptr, err_flag);
+                        float *__restrict__ partials, int *__restrict__ err_flag, const FdMerge merge) {
+    fdm_body<false>(q, k, v, kv_len_dev, kv_len_host, 1, num_heads, num_kv_heads, scale, partials, nullptr, err_flag, merge);
 }
 // Causal prefill attention on the same machinery: grid (kv heads, ceil(seq / queries per CTA)).
 RNB_GLOBAL void __launch_bounds__(FDM_THREADS, 4)
@@ -627,6 +699,67 @@ flash_decode_reduce_q8k_kernel(const float *__restrict__ partials, int n_chunks,
     s_out[threadIdx.x] = o;
     __syncthreads();
     if (threadIdx.x < 32) {
+        const float4 v0 = *reinterpret_cast<const float4 *>(s_out + lane * 8), v1 = *reinterpret_cast<const float4 *>(s_out + lane * 8 + 4);
+        const float v[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+        Q8kDevView dv = q8k_dev_view(xq_out, num_heads * HD);
+        const int b = blockIdx.x;
+        q8k_quantize_block_warp(v, lane, dv.qs + b * 256, dv.d + b, dv.bsum16 + b * 16, nullptr);
+    }
+}
+
+// Chunk merge fused with the Q8_K quantisation of the attention output (the o_proj input):
+// grid = num_heads / 2, 1024 threads; two heads are exactly one 256-element Q8_K block.
+// Thread (head hs, chunk group g, dim d): the 512 threads of a head first agree on the global max
+// and the per-chunk rescale factors (shared memory), then group g sums dimension d over the chunks
+// g, g + 4, ... and the four groups are added in a fixed order.
+constexpr int FDR_GROUPS = 4;
+RNB_GLOBAL void __launch_bounds__(2 * FDR_GROUPS * HD)
+flash_decode_reduce_q8k_wide_kernel(const float *__restrict__ partials, int n_chunks, int num_heads,
+                               float *__restrict__ out, uint8_t *__restrict__ xq_out) {
+    pdl_launch_dependents();
+    pdl_wait();
+    __shared__ __align__(16) float s_out[2 * HD];
+    __shared__ float s_f[2][FD_MAX_CHUNKS];
+    __shared__ float s_red[2][FDR_GROUPS * 4];
+    __shared__ float s_part[2][FDR_GROUPS][HD];
+    const int tid = threadIdx.x, hs = tid / (FDR_GROUPS * HD), th = tid % (FDR_GROUPS * HD), g = th >> 7, d = th & (HD - 1), wq = th >> 5, lane = tid & 31;
+    const int h = blockIdx.x * 2 + hs;
+    const float *base = partials + (size_t)h * n_chunks * FD_PART_STRIDE;
+    float m = -INFINITY;
+    for (int c = th; c < n_chunks; c += FDR_GROUPS * HD) m = fmaxf(m, base[(size_t)c * FD_PART_STRIDE + HD]);
+    m = warp_max(m);
+    if (lane == 0) s_red[hs][wq] = m;
+    __syncthreads();
+    float M = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < FDR_GROUPS * 4; i++) M = fmaxf(M, s_red[hs][i]);
+    __syncthreads();
+    float l = 0.f;
+    for (int c = th; c < n_chunks; c += FDR_GROUPS * HD) {
+        const float mc = base[(size_t)c * FD_PART_STRIDE + HD];
+        const float f = mc == -INFINITY ? 0.f : expf(mc - M);
+        s_f[hs][c] = f;
+        l += base[(size_t)c * FD_PART_STRIDE + HD + 1] * f;
+    }
+    l = warp_sum(l);
+    if (lane == 0) s_red[hs][wq] = l;
+    __syncthreads();
+    float L = 0.f;
+#pragma unroll
+    for (int i = 0; i < FDR_GROUPS * 4; i++) L += s_red[hs][i];
+    float a = 0.f;
+#pragma unroll 8
+    for (int c = g; c < n_chunks; c += FDR_GROUPS) a += base[(size_t)c * FD_PART_STRIDE + d] * s_f[hs][c];
+    s_part[hs][g][d] = a;
+    __syncthreads();
+    if (g == 0) {
+        const float t = (s_part[hs][0][d] + s_part[hs][1][d]) + (s_part[hs][2][d] + s_part[hs][3][d]);
+        const float o = L > 0.f ? t / L : 0.f;
+        if (out) out[(size_t)h * HD + d] = o;
+        s_out[hs * HD + d] = o;
+    }
+    __syncthreads();
+    if (tid < 32) {
         const float4 v0 = *reinterpret_cast<const float4 *>(s_out + lane * 8), v1 = *reinterpret_cast<const float4 *>(s_out + lane * 8 + 4);
         const float v[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
         Q8kDevView dv = q8k_dev_view(xq_out, num_heads * HD);

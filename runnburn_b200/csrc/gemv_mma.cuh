@@ -10,13 +10,13 @@
 // that remains is the nibble masks, one integer multiply by the sub-block scale per lane sum and
 // the ordered f32 FMA chain - about a third of the instructions of the dp4a forms, same bits.
 //
-// Shape of a CTA: a tile of 16 rows, eight MMA warps and one control warp.  K is cut into
+// Shape of a CTA: a tile of 16 rows, eight MMA warps, a producer warp and a replay warp.  K is cut into
 // stages of eight super-blocks of every row (bulk-async copies onto an mbarrier, a ring of
 // stages); MMA warp w takes block w of the stage for all 16 rows and leaves, per (block, row), the
 // lane sums, the mins products and the block scales as f32 in a double-buffered record area.
-// The control warp issues the copies and replays the records in block order - one FMA per block
-// and accumulator, the only part that has to be sequential - then folds the lanes and runs the
-// epilogue.  CTAs are persistent: they walk tiles blockIdx.x, blockIdx.x + gridDim.x, ... with
+// One lane of the producer warp issues the copies as the MMA warps release stages; the replay warp
+// replays the records in block order - one FMA per block and accumulator, the only part that has to
+// be sequential - then folds the lanes and runs the epilogue.  CTAs are persistent: they walk tiles blockIdx.x, blockIdx.x + gridDim.x, ... with
 // the copy ring running across tile boundaries.
 //
 // Fragment layouts (PTX ISA, mma.m16n8k32 with 8-bit operands; g = lane / 4, t = lane % 4):
@@ -37,23 +37,42 @@ namespace rnb {
 constexpr int GM_ROWS = 16;
 constexpr int GM_CHUNK = 8;                              // super-blocks per stage = MMA warps
 constexpr int GM_MMA_WARPS = 8;
-constexpr int GM_THREADS = 32 * (GM_MMA_WARPS + 1);
-constexpr int GM_MAX_STAGES = 4;
+constexpr int GM_THREADS = 32 * (GM_MMA_WARPS + 2);   // + producer warp + replay warp
+constexpr int GM_MAX_STAGES = 6;
 constexpr uint32_t GM_REC_BYTES = 64;                    // per (block, row): a[8] | m[4] | d | dmin | pad
 constexpr uint32_t GM_PBUF_BYTES = GM_CHUNK * GM_ROWS * GM_REC_BYTES;
 constexpr uint32_t GM_ZERO_BYTES = 320;                  // zeros read by threads that feed no column
-constexpr uint32_t GM_ACT_BYTES = GM_CHUNK * (256 + 32 + 4);   // qs | bsum16 | d of a stage
+constexpr uint32_t GM_ACT_BLOCK_BYTES = 256 + 32 + 4;               // qs | bsum16 | d per super-block of a stage
 constexpr uint32_t GM_POLL_LIMIT = 1u << 21;
 #ifndef GM_MIN_CTAS
 #define GM_MIN_CTAS 2
 #endif
 
+// Tiled-copy descriptors (CUtensorMap, opaque here) of the launch's weight matrices: with them a
+// stage's 16 rows arrive by ONE copy instruction instead of 16, which is what the single issuing
+// lane can sustain at the HBM rate.  Matrix i is described as [rows][row_bytes / 8] 8-byte words with a
+// box of 16 rows x (row stride / 8) words; rows or words past the end read as zeros.
+struct alignas(64) GmTensorMap {
+    unsigned long long opaque[16];
+};
+struct GmTmaps {
+    GmTensorMap m[GS_PACK];
+};
+__device__ __forceinline__ void gm_tma_2d(uint32_t dst, const void *tmap, int x, int y, uint64_t *bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"(dst), "l"(tmap), "r"(x), "r"(y), "r"(smem_u32(bar))
+                 : "memory");
+}
+
 struct GmParams {
     int cols;
+    int chunk;            // super-blocks per stage: GM_CHUNK or 2 * GM_CHUNK (each MMA warp then takes two blocks per stage)
     int n_stages;
     int dynamic_table;
     int n_tiles;
-    uint32_t row_stride;  // bytes of a weight row per stage; row_stride / 16 is odd (ldmatrix reads 8 rows conflict-free)
+    int use_tmap;         // weights arrive through the tiled-copy descriptors (by-value kernel only)
+    uint32_t row_stride;  // bytes of a Q4_K weight row per stage; row_stride / 16 is odd (ldmatrix reads 8 rows conflict-free)
+    uint32_t row_stride6; // the same for Q6_K rows (equal to row_stride unless descriptors are in use)
     uint32_t act_off;
     uint32_t slot_bytes;
 };
@@ -113,6 +132,11 @@ __device__ __forceinline__ void sts_f1(uint32_t addr, float a) {
 __device__ __forceinline__ float4 lds_f4(uint32_t addr) {
     float4 v;
     asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ float2 lds_f2(uint32_t addr) {
+    float2 v;
+    asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(addr));
     return v;
 }
 __device__ __forceinline__ float lds_f1(uint32_t addr) {
@@ -344,15 +368,16 @@ __device__ __forceinline__ bool gm_next(const GemvJob *__restrict__ jobs, int n_
 }
 
 __device__ __forceinline__ void gemv_mma_body(const GemvJob *__restrict__ jobs, int n_jobs, const GmParams &P, int *__restrict__ dev_error,
-                                              const GpTail &tail) {
+                                              const GpTail &tail, const GmTmaps *__restrict__ tmaps) {
     extern __shared__ __align__(128) uint8_t smem[];
-    __shared__ __align__(8) uint64_t full[GM_MAX_STAGES], pfull[2], pempty[2];
+    __shared__ __align__(8) uint64_t full[GM_MAX_STAGES], empty[GM_MAX_STAGES], pfull[2], pempty[2];
     __shared__ int s_abort;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int S = P.n_stages, cols = P.cols, nb = cols >> 8, n_chunks = (nb + GM_CHUNK - 1) / GM_CHUNK;
+    const int S = P.n_stages, cols = P.cols, nb = cols >> 8, CB = P.chunk, n_chunks = (nb + CB - 1) / CB, halves = CB / GM_CHUNK;
     if (blockDim.x != GM_THREADS || S < 1 || S > GM_MAX_STAGES || nb < 1 || (P.row_stride & 15u) || !((P.row_stride >> 4) & 1u) ||
-        P.act_off < (uint32_t)GM_ROWS * P.row_stride || (P.act_off & 15u) || P.act_off + GM_ACT_BYTES > P.slot_bytes || (P.slot_bytes & 127u) ||
-        n_jobs < 1) {
+        (P.row_stride6 & 15u) || !((P.row_stride6 >> 4) & 1u) || (P.use_tmap && !tmaps) ||
+        P.act_off < (uint32_t)GM_ROWS * max(P.row_stride, P.row_stride6) || (P.act_off & 15u) || P.act_off + (uint32_t)CB * GM_ACT_BLOCK_BYTES > P.slot_bytes || (P.slot_bytes & 127u) ||
+        n_jobs < 1 || (CB != GM_CHUNK && CB != 2 * GM_CHUNK)) {
         if (tid == 0) atomicExch(dev_error, DEV_ERR_BAD_JOB);
         return;
     }
@@ -361,7 +386,10 @@ __device__ __forceinline__ void gemv_mma_body(const GemvJob *__restrict__ jobs, 
     const uint32_t smem_base = smem_u32(smem);
     const uint32_t pbuf = smem_base + (uint32_t)S * P.slot_bytes, zeros = pbuf + 2u * GM_PBUF_BYTES;
     if (tid == 0) {
-        for (int s = 0; s < S; s++) mbar_init(&full[s], 1);
+        for (int s = 0; s < S; s++) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], GM_MMA_WARPS);
+        }
         for (int b = 0; b < 2; b++) {
             mbar_init(&pfull[b], GM_MMA_WARPS);
             mbar_init(&pempty[b], 1);
@@ -380,40 +408,43 @@ __device__ __forceinline__ void gemv_mma_body(const GemvJob *__restrict__ jobs, 
 
     if (warp < GM_MMA_WARPS) {
         // ------------------------------ MMA warps ------------------------------
-        pdl_wait();
         int slot = 0;
         uint32_t it = 0;
         bool more = true, failed = false;
         GM_PROF_DECL;
         while (more) {
-            const int nblk = min(GM_CHUNK, nb - cur.chunk * GM_CHUNK);
+            const int nblk = min(CB, nb - cur.chunk * CB);
             const uint32_t slot_base = smem_base + (uint32_t)slot * P.slot_bytes;
-            const uint32_t b = it & 1u;
-            const bool mine = warp < nblk;
-            // the stage has landed, and the record buffer is free once the replay of two items ago is done
+            // the stage has landed
             if (!gm_wait(&full[slot], (it / (uint32_t)S) & 1u, &s_abort)) {
                 failed = true;
                 break;
             }
             GM_PROF_LAP(prof_a);
-            if (it >= 2 && !gm_wait(&pempty[b], ((it >> 1) - 1u) & 1u, &s_abort)) {
-                failed = true;
-                break;
+            for (int h = 0; h < halves; h++) {
+                const uint32_t ri = it * (uint32_t)halves + (uint32_t)h, b = ri & 1u;   // record item and its buffer
+                const int j = h * GM_CHUNK + warp;                                       // this warp's block of the stage
+                // the record buffer is free once the replay of two record items ago is done
+                if (ri >= 2 && !gm_wait(&pempty[b], ((ri >> 1) - 1u) & 1u, &s_abort)) {
+                    failed = true;
+                    break;
+                }
+                GM_PROF_LAP(prof_b);
+                if (j < nblk) {
+                    const uint32_t act_qs = slot_base + P.act_off + (uint32_t)j * 256u;
+                    const uint32_t act_bs = slot_base + P.act_off + (uint32_t)CB * 256u + (uint32_t)j * 32u;
+                    const float yd = lds_f1(slot_base + P.act_off + (uint32_t)CB * 288u + (uint32_t)j * 4u);
+                    const uint32_t rec = pbuf + b * GM_PBUF_BYTES + (uint32_t)warp * GM_ROWS * GM_REC_BYTES;
+                    if (cur.type == TYPE_Q4_K) gm_q4k_block(slot_base, P.row_stride, (uint32_t)j * Q4K_BYTES, act_qs, act_bs, yd, zeros, rec, lane);
+                    else if (j & 1) gm_q6k_block<true>(slot_base, P.row_stride6, (uint32_t)j * Q6K_BYTES, act_qs, act_bs, yd, zeros, rec, lane);
+                    else gm_q6k_block<false>(slot_base, P.row_stride6, (uint32_t)j * Q6K_BYTES, act_qs, act_bs, yd, zeros, rec, lane);
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&pfull[b]);   // this warp's record of the half (if any) is in place
+                GM_PROF_LAP(prof_c);
             }
-            GM_PROF_LAP(prof_b);
-            if (mine) {
-                const uint32_t act_qs = slot_base + P.act_off + (uint32_t)warp * 256u;
-                const uint32_t act_bs = slot_base + P.act_off + GM_CHUNK * 256u + (uint32_t)warp * 32u;
-                const float yd = lds_f1(slot_base + P.act_off + GM_CHUNK * 288u + (uint32_t)warp * 4u);
-                const uint32_t rec = pbuf + b * GM_PBUF_BYTES + (uint32_t)warp * GM_ROWS * GM_REC_BYTES;
-                if (cur.type == TYPE_Q4_K) gm_q4k_block(slot_base, P.row_stride, (uint32_t)warp * Q4K_BYTES, act_qs, act_bs, yd, zeros, rec, lane);
-                else if (warp & 1) gm_q6k_block<true>(slot_base, P.row_stride, (uint32_t)warp * Q6K_BYTES, act_qs, act_bs, yd, zeros, rec, lane);
-                else gm_q6k_block<false>(slot_base, P.row_stride, (uint32_t)warp * Q6K_BYTES, act_qs, act_bs, yd, zeros, rec, lane);
-            }
-            __syncwarp();
-            // the stage's bytes have been consumed by this warp and its record (if any) is in place: one
-            // arrival says both, so a complete record buffer also means the stage can be refilled
-            if (lane == 0) mbar_arrive(&pfull[b]);
+            if (failed) break;
+            if (lane == 0) mbar_arrive(&empty[slot]);   // this warp has consumed the stage's bytes: the producer may refill the slot
             ++it;
             if (++slot == S) slot = 0;
             more = gm_next(jobs, n_jobs, n_chunks, P.n_tiles, tile_step, cur);
@@ -437,93 +468,153 @@ __device__ __forceinline__ void gemv_mma_body(const GemvJob *__restrict__ jobs, 
         return;
     }
 
-    // ------------------------------ control warp ------------------------------
-    // copies of item (tile, part, chunk) into a slot: lanes 0..15 one weight row each, lanes 16..18 the activation slices
-    auto issue = [&](const GmCursor &c, int slot, bool weights, bool act) {
-        const GemvJob &job = jobs[c.jsel];
-        const uint32_t blk = c.type == TYPE_Q4_K ? Q4K_BYTES : Q6K_BYTES;
-        const int nblk = min(GM_CHUNK, nb - c.chunk * GM_CHUNK);
-        const uint32_t wbytes = (uint32_t)nblk * blk, dbytes = ((uint32_t)nblk * 4u + 15u) & ~15u;
-        uint64_t *bar = &full[slot];
-        uint8_t *dst = smem + (size_t)slot * P.slot_bytes;
-        if (weights) {
-            if (lane == 0) mbar_arrive_expect_tx(bar, wbytes * (uint32_t)c.nrows + (uint32_t)nblk * 288u + dbytes);
-            __syncwarp();
-            if (lane < c.nrows) {
-                const uint32_t rb = (uint32_t)nb * blk;
-                bulk_g2s(dst + (uint32_t)lane * P.row_stride, job.parts[c.part].w + (size_t)(c.row0 + lane) * rb + (uint32_t)(c.chunk * GM_CHUNK) * blk, wbytes, bar);
+    if (warp == GM_MMA_WARPS) {
+        // ------------------------------ producer warp: one lane issues every copy ------------------------------
+        if (lane != 0) return;
+        // copies of item (tile, part, chunk) into a slot: one bulk copy per weight row, three for the activation slices
+        auto issue = [&](const GmCursor &c, int slot, bool weights, bool act) {
+            const GemvJob &job = jobs[c.jsel];
+            const uint32_t blk = c.type == TYPE_Q4_K ? Q4K_BYTES : Q6K_BYTES;
+            const int nblk = min(CB, nb - c.chunk * CB);
+            const uint32_t wbytes = (uint32_t)nblk * blk, dbytes = ((uint32_t)nblk * 4u + 15u) & ~15u;
+            uint64_t *bar = &full[slot];
+            uint8_t *dst = smem + (size_t)slot * P.slot_bytes;
+            const uint32_t rs = c.type == TYPE_Q4_K ? P.row_stride : P.row_stride6;
+            if (weights && P.use_tmap) {
+                // one tiled copy: the box is always 16 rows x the whole row stride (zeros past the matrix), and so is its byte count
+                mbar_arrive_expect_tx(bar, (uint32_t)GM_ROWS * rs + (uint32_t)nblk * 288u + dbytes);
+                gm_tma_2d(smem_u32(dst), &tmaps->m[c.jsel], (int)(((uint32_t)(c.chunk * CB) * blk) >> 3), c.row0, bar);
+            } else if (weights) {
+                mbar_arrive_expect_tx(bar, wbytes * (uint32_t)c.nrows + (uint32_t)nblk * 288u + dbytes);
+                const size_t rb = (size_t)nb * blk;
+                const uint8_t *src = job.parts[c.part].w + (size_t)c.row0 * rb + (uint32_t)(c.chunk * CB) * blk;
+                uint8_t *d = dst;
+                for (int r = 0; r < c.nrows; r++, src += rb, d += rs) bulk_g2s(d, src, wbytes, bar);
+            }
+            if (act) {
+                const uint8_t *x = job.parts[c.part].x;
+                const uint32_t b0 = (uint32_t)(c.chunk * CB);
+                bulk_g2s(dst + P.act_off, x + b0 * 256u, (uint32_t)nblk * 256u, bar);
+                bulk_g2s(dst + P.act_off + (uint32_t)CB * 256u, x + cols + b0 * 32u, (uint32_t)nblk * 32u, bar);
+                bulk_g2s(dst + P.act_off + (uint32_t)CB * 288u, x + cols + 32 * nb + b0 * 4u, dbytes, bar);
+            }
+        };
+        GmCursor pc = cur;
+        bool p_more = true, failed = false;
+        uint32_t issued = 0;
+        {
+            GmCursor c2 = cur;
+            bool m2 = true;
+            for (int i = 0; i < S && m2; i++) {
+                issue(c2, i, true, false);
+                m2 = gm_next(jobs, n_jobs, n_chunks, P.n_tiles, tile_step, c2);
+            }
+            pdl_wait();   // weights do not depend on the previous kernel; the activation does
+            for (int i = 0; i < S && p_more; i++) {
+                issue(pc, i, false, true);
+                ++issued;
+                p_more = gm_next(jobs, n_jobs, n_chunks, P.n_tiles, tile_step, pc);
             }
         }
-        if (act) {
-            const uint8_t *x = job.parts[c.part].x;
-            const uint32_t b0 = (uint32_t)(c.chunk * GM_CHUNK);
-            if (lane == 16) bulk_g2s(dst + P.act_off, x + b0 * 256u, (uint32_t)nblk * 256u, bar);
-            if (lane == 17) bulk_g2s(dst + P.act_off + GM_CHUNK * 256u, x + cols + b0 * 32u, (uint32_t)nblk * 32u, bar);
-            if (lane == 18) bulk_g2s(dst + P.act_off + GM_CHUNK * 288u, x + cols + 32 * nb + b0 * 4u, dbytes, bar);
-        }
-    };
-    GmCursor pc = cur;        // producer cursor: the next item to fetch
-    bool p_more = true;
-    uint32_t issued = 0;      // items whose copies have been started
-    {
-        GmCursor c2 = cur;
-        bool m2 = true;
-        for (int i = 0; i < S && m2; i++) {
-            issue(c2, i, true, false);
-            m2 = gm_next(jobs, n_jobs, n_chunks, P.n_tiles, tile_step, c2);
-        }
-        pdl_wait();   // weights do not depend on the previous kernel; activations, residual and outputs do
-        for (int i = 0; i < S && p_more; i++) {
-            issue(pc, i, false, true);
+        int slot = 0;
+        while (p_more) {
+            // item `issued` goes into the slot that item `issued - S` has occupied
+            if (!gm_wait(&empty[slot], ((issued / (uint32_t)S) - 1u) & 1u, &s_abort)) {
+                failed = true;
+                break;
+            }
+            issue(pc, slot, true, true);
             ++issued;
+            if (++slot == S) slot = 0;
             p_more = gm_next(jobs, n_jobs, n_chunks, P.n_tiles, tile_step, pc);
         }
+        if (failed) {
+            s_abort = 1;
+            atomicExch(dev_error, DEV_ERR_MBAR_TIMEOUT);
+        }
+        // Every copy this lane started must land before the CTA's shared memory goes away: the consumers
+        // wait for each of them in the normal course; after a failure wait here (bounded) for the last S.
+        if (failed || s_abort) {
+            const uint32_t first = issued > (uint32_t)S ? issued - (uint32_t)S : 0u;
+            for (uint32_t n = first; n < issued; n++) {
+                bool landed = false;
+                for (uint32_t k = 0; k < (1u << 18) && !landed; k++) landed = mbar_try_wait(&full[n % (uint32_t)S], (n / (uint32_t)S) & 1u);
+            }
+        }
+        return;
     }
+
+    // ------------------------------ replay warp ------------------------------
+    pdl_wait();
+    // thread (row r = lane / 2, half hq = lane % 2) carries accumulator lanes 4hq..4hq+3 and mins lanes 2hq, 2hq+1
     const int r = lane >> 1, hq = lane & 1;
-    float acc[4] = {0.f, 0.f, 0.f, 0.f}, accm[4] = {0.f, 0.f, 0.f, 0.f}, acc_total = 0.f;
+    float acc[4] = {0.f, 0.f, 0.f, 0.f}, accm[2] = {0.f, 0.f}, acc_total = 0.f;
     const uint32_t ra = (uint32_t)r * GM_REC_BYTES + gm_rec_unit(r, hq), rd = (uint32_t)r * GM_REC_BYTES + gm_rec_unit(r, 3);
-    const uint32_t rm = (uint32_t)(lane & 15) * GM_REC_BYTES + gm_rec_unit(lane & 15, 2), rdm = (uint32_t)(lane & 15) * GM_REC_BYTES + gm_rec_unit(lane & 15, 3) + 4u;
-    int slot = 0;
+    const uint32_t rm = (uint32_t)r * GM_REC_BYTES + gm_rec_unit(r, 2) + 8u * (uint32_t)hq;
     uint32_t it = 0;
     bool more = true, failed = false;
     GM_PROF_DECL;
+    float res_pref = 0.f;
     while (more) {
-        const int nblk = min(GM_CHUNK, nb - cur.chunk * GM_CHUNK);
-        const uint32_t b = it & 1u;
-        if (!gm_wait(&pfull[b], (it >> 1) & 1u, &s_abort)) {
-            failed = true;
-            break;
-        }
-        GM_PROF_LAP(prof_a);
-        // every MMA warp has also released the stage (it arrives there first): refill it
-        if (p_more) {
-            issue(pc, slot, true, true);
-            ++issued;
-            p_more = gm_next(jobs, n_jobs, n_chunks, P.n_tiles, tile_step, pc);
-        }
-        GM_PROF_LAP(prof_b);
-        const uint32_t recs = pbuf + b * GM_PBUF_BYTES;
+        const int nblk_stage = min(CB, nb - cur.chunk * CB);
         const bool q4 = cur.type == TYPE_Q4_K;
-#pragma unroll 4
-        for (int j = 0; j < nblk; j++) {
-            const uint32_t rj = recs + (uint32_t)j * GM_ROWS * GM_REC_BYTES;
-            const float4 s = lds_f4(rj + ra);
-            const float d = lds_f1(rj + rd);
-            acc[0] = __fmaf_rn(d, s.x, acc[0]);
-            acc[1] = __fmaf_rn(d, s.y, acc[1]);
-            acc[2] = __fmaf_rn(d, s.z, acc[2]);
-            acc[3] = __fmaf_rn(d, s.w, acc[3]);
-            if (q4 && lane < 16) {
-                const float4 m = lds_f4(rj + rm);
-                const float dm = lds_f1(rj + rdm);
-                accm[0] = __fmaf_rn(dm, m.x, accm[0]);
-                accm[1] = __fmaf_rn(dm, m.y, accm[1]);
-                accm[2] = __fmaf_rn(dm, m.z, accm[2]);
-                accm[3] = __fmaf_rn(dm, m.w, accm[3]);
-            }
+        if (cur.chunk == 0 && cur.part == 0) {
+            // the residual of this tile's rows is fetched now and used when the tile is done
+            const GemvJob &tj = jobs[cur.jsel];
+            res_pref = (r < cur.nrows && hq == 0 && tj.residual) ? tj.residual[(size_t)cur.row0 + r] : 0.f;
         }
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&pempty[b]);
+        for (int h = 0; h < halves; h++) {
+            const uint32_t ri = it * (uint32_t)halves + (uint32_t)h, b = ri & 1u;
+            const int nblk = max(0, min(GM_CHUNK, nblk_stage - h * GM_CHUNK));
+            if (!gm_wait(&pfull[b], (ri >> 1) & 1u, &s_abort)) {
+                failed = true;
+                break;
+            }
+            GM_PROF_LAP(prof_a);
+            const uint32_t recs = pbuf + b * GM_PBUF_BYTES;
+            if (nblk == GM_CHUNK) {
+                // all records first, then the ordered chains: the loads overlap instead of alternating with the FMAs
+                float4 sv[GM_CHUNK];
+                float2 mv[GM_CHUNK], dv[GM_CHUNK];
+#pragma unroll
+                for (int j = 0; j < GM_CHUNK; j++) {
+                    const uint32_t rj = recs + (uint32_t)j * GM_ROWS * GM_REC_BYTES;
+                    sv[j] = lds_f4(rj + ra);
+                    dv[j] = lds_f2(rj + rd);
+                    if (q4) mv[j] = lds_f2(rj + rm);
+                }
+#pragma unroll
+                for (int j = 0; j < GM_CHUNK; j++) {
+                    acc[0] = __fmaf_rn(dv[j].x, sv[j].x, acc[0]);
+                    acc[1] = __fmaf_rn(dv[j].x, sv[j].y, acc[1]);
+                    acc[2] = __fmaf_rn(dv[j].x, sv[j].z, acc[2]);
+                    acc[3] = __fmaf_rn(dv[j].x, sv[j].w, acc[3]);
+                    if (q4) {
+                        accm[0] = __fmaf_rn(dv[j].y, mv[j].x, accm[0]);
+                        accm[1] = __fmaf_rn(dv[j].y, mv[j].y, accm[1]);
+                    }
+                }
+            } else {
+                for (int j = 0; j < nblk; j++) {
+                    const uint32_t rj = recs + (uint32_t)j * GM_ROWS * GM_REC_BYTES;
+                    const float4 s = lds_f4(rj + ra);
+                    const float2 d = lds_f2(rj + rd);
+                    acc[0] = __fmaf_rn(d.x, s.x, acc[0]);
+                    acc[1] = __fmaf_rn(d.x, s.y, acc[1]);
+                    acc[2] = __fmaf_rn(d.x, s.z, acc[2]);
+                    acc[3] = __fmaf_rn(d.x, s.w, acc[3]);
+                    if (q4) {
+                        const float2 m = lds_f2(rj + rm);
+                        accm[0] = __fmaf_rn(d.y, m.x, accm[0]);
+                        accm[1] = __fmaf_rn(d.y, m.y, accm[1]);
+                    }
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&pempty[b]);
+            GM_PROF_LAP(prof_b);
+        }
+        if (failed) break;
         if (cur.chunk == n_chunks - 1) {
             // fold: (l + l4) -> (+2) -> (+1); mins (a0 + a2) + (a1 + a3)
             const float v0 = __fadd_rn(acc[0], __shfl_xor_sync(0xffffffffu, acc[0], 1));
@@ -531,19 +622,21 @@ __device__ __forceinline__ void gemv_mma_body(const GemvJob *__restrict__ jobs, 
             const float v2 = __fadd_rn(acc[2], __shfl_xor_sync(0xffffffffu, acc[2], 1));
             const float v3 = __fadd_rn(acc[3], __shfl_xor_sync(0xffffffffu, acc[3], 1));
             float dot = __fadd_rn(__fadd_rn(v0, v2), __fadd_rn(v1, v3));
-            const float ms = __fadd_rn(__fadd_rn(accm[0], accm[2]), __fadd_rn(accm[1], accm[3]));   // row `lane` (lanes 0..15)
-            const float msr = __shfl_sync(0xffffffffu, ms, r);
-            if (q4) dot = __fadd_rn(dot, msr);
+            // mins: (m0 + m2) + (m1 + m3); the pair of threads of a row holds (m0, m1) and (m2, m3)
+            const float m02 = __fadd_rn(accm[0], __shfl_xor_sync(0xffffffffu, accm[0], 1));
+            const float m13 = __fadd_rn(accm[1], __shfl_xor_sync(0xffffffffu, accm[1], 1));
+            if (q4) dot = __fadd_rn(dot, __fadd_rn(m02, m13));
             const GemvJob &job = jobs[cur.jsel];
             if (job.parts[cur.part].scale) dot = __fmul_rn(dot, __ldg(job.parts[cur.part].scale));
             acc_total = cur.n_parts == 1 ? dot : __fadd_rn(acc_total, dot);
 #pragma unroll
-            for (int k = 0; k < 4; k++) acc[k] = 0.f, accm[k] = 0.f;
+            for (int k = 0; k < 4; k++) acc[k] = 0.f;
+            accm[0] = accm[1] = 0.f;
             if (cur.part == cur.n_parts - 1) {
                 const bool live = r < cur.nrows && hq == 0;
                 const size_t o = (size_t)cur.row0 + r;
                 float val = acc_total;
-                if (live && job.residual) val = __fadd_rn(job.residual[o], acc_total);
+                if (live && job.residual) val = __fadd_rn(res_pref, acc_total);
                 acc_total = 0.f;
                 const int epi = job.epi;
                 if (epi == GEMV_EPI_NONE) {
@@ -570,7 +663,6 @@ __device__ __forceinline__ void gemv_mma_body(const GemvJob *__restrict__ jobs, 
             }
         }
         ++it;
-        if (++slot == S) slot = 0;
         more = gm_next(jobs, n_jobs, n_chunks, P.n_tiles, tile_step, cur);
         GM_PROF_LAP(prof_c);
 #ifdef GM_PROFILE
@@ -585,16 +677,9 @@ __device__ __forceinline__ void gemv_mma_body(const GemvJob *__restrict__ jobs, 
         atomicAdd(&g_gm_prof[7], (unsigned long long)prof_n);
     }
 #endif
-    if (failed) {
-        if (lane == 0) {
-            s_abort = 1;
-            atomicExch(dev_error, DEV_ERR_MBAR_TIMEOUT);
-        }
-        // let the copies that are still in flight land before the CTA's shared memory goes away
-        for (uint32_t n = it; n < issued; n++) {
-            bool landed = false;
-            for (uint32_t k = 0; k < (1u << 18) && !landed; k++) landed = mbar_try_wait(&full[n % (uint32_t)S], (n / (uint32_t)S) & 1u);
-        }
+    if (failed && lane == 0) {
+        s_abort = 1;
+        atomicExch(dev_error, DEV_ERR_MBAR_TIMEOUT);
     }
 }
 
@@ -602,12 +687,12 @@ RNB_GLOBAL void __launch_bounds__(GM_THREADS, GM_MIN_CTAS)
 gemv_mma_kernel(const GemvJob *__restrict__ jobs, int n_jobs, const GmParams P, int *__restrict__ dev_error) {
     GpTail none;
     none.kind = 0;
-    gemv_mma_body(jobs, n_jobs, P, dev_error, none);
+    gemv_mma_body(jobs, n_jobs, P, dev_error, none, nullptr);
 }
 RNB_GLOBAL void __launch_bounds__(GM_THREADS, GM_MIN_CTAS)
 gemv_mma_kernel_1(const __grid_constant__ GemvJobPack jobs, int n_jobs, const GmParams P, int *__restrict__ dev_error,
-                  const __grid_constant__ GpTail tail) {
-    gemv_mma_body(jobs.j, n_jobs, P, dev_error, tail);
+                  const __grid_constant__ GpTail tail, const __grid_constant__ GmTmaps tmaps) {
+    gemv_mma_body(jobs.j, n_jobs, P, dev_error, tail, &tmaps);
 }
 
 }  // namespace rnb

@@ -177,8 +177,11 @@ inline const KsplitTuning &ksplit_tuning() {
 // aligned (Q6_K rows additionally need a multiple of 8 super-blocks, so that every stage starts
 // on a 16-byte boundary).  RNB_B200_MMA=0 turns it off, _MMA_STAGES / _MMA_CTAS set the ring depth
 // and the resident CTAs per SM the persistent grid is sized for.
+// Descriptor of a weight matrix for the integer-MMA matvec's tiled copies: [rows][row_bytes / 8] 8-byte
+// words, boxes of 16 rows x box_bytes / 8 words, no swizzle, zeros outside the matrix.
+int encode_weight_map(GmTensorMap *out, const uint8_t *w, size_t rows, size_t row_bytes, uint32_t box_bytes);
 struct MmaTuning {
-    int enabled, stages, ctas_per_sm;
+    int enabled, stages, ctas_per_sm, chunk16, tmap;
 };
 inline const MmaTuning &mma_tuning() {
     static const MmaTuning t = [] {
@@ -192,6 +195,8 @@ inline const MmaTuning &mma_tuning() {
         v.enabled = env_int("RNB_B200_MMA", 1, 0, 1);
         v.stages = env_int("RNB_B200_MMA_STAGES", 3, 1, GM_MAX_STAGES);
         v.ctas_per_sm = env_int("RNB_B200_MMA_CTAS", 0, 0, 8);
+        v.chunk16 = env_int("RNB_B200_MMA_CHUNK16", 1, 0, 1);
+        v.tmap = env_int("RNB_B200_MMA_TMAP", 1, 0, 1);
         return v;
     }();
     return t;
@@ -231,13 +236,39 @@ inline int try_launch_gemv_mma(cudaStream_t s, const GemvJob *jobs_host, const G
     P.cols = (int)cols;
     P.dynamic_table = dynamic_table;
     P.n_tiles = tiles;
-    P.row_stride = any_q6 ? 1712u : 1168u;   // 8 blocks of 210 / 144 bytes, padded to an odd number of 16-byte units
-    P.act_off = (uint32_t)GM_ROWS * P.row_stride;
-    P.slot_bytes = (P.act_off + GM_ACT_BYTES + 127u) & ~127u;
+    // Stage geometry: 8 super-blocks per row when a Q6_K matrix is in the launch (8 x 210 bytes is its shortest
+    // 16-byte multiple), else 16 (half as many copies to issue per byte); rows padded to an odd number of
+    // 16-byte units so that ldmatrix reads eight rows without bank conflicts.
+    // With tiled-copy descriptors (static single-part jobs that travel by value) a stage costs one copy
+    // instruction whatever its width: 8 blocks per stage, each type at its own row pitch, a deeper ring.
+    bool all_q6 = true, single_part = true;
+    for (int i = 0; i < n_jobs; i++) {
+        all_q6 = all_q6 && jobs_host[i].type == TYPE_Q6_K;
+        single_part = single_part && jobs_host[i].n_parts == 1;
+    }
+    const bool by_val = (by_value || !dynamic_table) && n_jobs <= GS_PACK;
+    P.use_tmap = (mt.tmap && by_val && !dynamic_table && single_part) ? 1 : 0;
+    if (P.use_tmap) {
+        P.chunk = GM_CHUNK;
+        P.row_stride = 1168u;
+        P.row_stride6 = any_q6 ? 1712u : 1168u;   // no Q6_K job: the slot is sized for Q4_K rows alone
+        P.act_off = (uint32_t)GM_ROWS * P.row_stride6;
+    } else {
+        P.chunk = (any_q6 || nb < 2 * GM_CHUNK || mt.chunk16 == 0) ? GM_CHUNK : 2 * GM_CHUNK;
+        P.row_stride = any_q6 ? 1712u : (P.chunk == GM_CHUNK ? 1168u : 2320u);
+        P.row_stride6 = P.row_stride;
+        P.act_off = (uint32_t)GM_ROWS * P.row_stride;
+    }
+    (void)all_q6;
+    P.slot_bytes = (P.act_off + (uint32_t)P.chunk * GM_ACT_BLOCK_BYTES + 127u) & ~127u;
     int n_items = 0;
-    for (int i = 0; i < n_jobs; i++) n_items = std::max(n_items, jobs_host[i].n_parts * ((nb + GM_CHUNK - 1) / GM_CHUNK));
-    P.n_stages = mt.stages;
+    for (int i = 0; i < n_jobs; i++) n_items = std::max(n_items, jobs_host[i].n_parts * ((nb + P.chunk - 1) / P.chunk));
+    P.n_stages = P.use_tmap ? std::max(mt.stages, 4) : mt.stages;
     while (P.n_stages > 1 && gm_smem_bytes(P.n_stages, P.slot_bytes) > gemv_smem_max()) P.n_stages--;
+    // two CTAs per SM (the kernels' register budget) matter more than a deeper ring
+    const size_t per_cta_for_two = ((size_t)228 * 1024 - 2 * 1024) / 2;
+    if (mt.ctas_per_sm != 1)
+        while (P.n_stages > 2 && gm_smem_bytes(P.n_stages, P.slot_bytes) > per_cta_for_two) P.n_stages--;
     const size_t smem = gm_smem_bytes(P.n_stages, P.slot_bytes);
     if (smem > gemv_smem_max()) return 0;
     const int sm = state().sm_count > 0 ? state().sm_count : 148;
@@ -259,7 +290,15 @@ inline int try_launch_gemv_mma(cudaStream_t s, const GemvJob *jobs_host, const G
         GemvJobPack pack;
         memset(&pack, 0, sizeof(pack));
         for (int i = 0; i < n_jobs; i++) pack.j[i] = jobs_host[i];
-        const cudaError_t e = launch_k(gemv_mma_kernel_1, dim3(grid), dim3(GM_THREADS), smem, s, pack, n_jobs, P, dev_error, t);
+        GmTmaps tm;
+        memset(&tm, 0, sizeof(tm));
+        if (P.use_tmap)
+            for (int i = 0; i < n_jobs; i++) {
+                const GemvJob &j = jobs_host[i];
+                const int rc = encode_weight_map(&tm.m[i], j.parts[0].w, (size_t)j.rows, row_bytes_of(j.type, cols), j.type == TYPE_Q4_K ? P.row_stride : P.row_stride6);
+                if (rc != RNB_B200_OK) return -rc;
+            }
+        const cudaError_t e = launch_k(gemv_mma_kernel_1, dim3(grid), dim3(GM_THREADS), smem, s, pack, n_jobs, P, dev_error, t, tm);
         if (e != cudaSuccess) return -fail_cuda(e, "gemv_mma_kernel launch");
     } else {
         if (t.kind) return -fail(RNB_B200_VALIDATION_FAILED, "matvec tail needs a by-value job table");
@@ -454,14 +493,24 @@ inline bool flash_decode_force_simt() {
     }();
     return v;
 }
+// `merge` (optional): let the tensor-core kernel's last CTA per KV head merge the chunks; *merged tells the
+// caller whether that happened (it does not on the CUDA-core fallback) or a merge launch is still needed.
 inline int launch_flash_decode_partials(cudaStream_t s, const float *q, const uint16_t *k, const uint16_t *v,
                                         const int *kv_len_dev, int kv_len_host, int num_heads, int num_kv_heads,
-                                        float scale, float *partials, int n_chunks, int *dev_error) {
+                                        float scale, float *partials, int n_chunks, int *dev_error, const FdMerge *merge = nullptr,
+                                        bool *merged = nullptr) {
     const bool aligned = (((uintptr_t)k | (uintptr_t)v) & 15) == 0;
-    if (aligned && !flash_decode_force_simt())
+    if (merged) *merged = false;
+    if (aligned && !flash_decode_force_simt()) {
+        FdMerge m{nullptr, nullptr, nullptr};
+        const int group = num_kv_heads ? num_heads / num_kv_heads : 0;
+        if (merge && merge->counters && n_chunks <= FD_MAX_CHUNKS && (!merge->xq_out || group % 2 == 0)) {
+            m = *merge;
+            if (merged) *merged = true;
+        }
         RNB_CU(launch_k(flash_decode_mma_kernel, dim3(num_kv_heads, n_chunks), dim3(FDM_THREADS), 0, s, q, k, v, kv_len_dev,
-                        kv_len_host, num_heads, num_kv_heads, scale, partials, dev_error));
-    else
+                        kv_len_host, num_heads, num_kv_heads, scale, partials, dev_error, m));
+    } else
         RNB_CU(launch_k(flash_decode_partials_kernel, dim3(num_kv_heads, n_chunks), dim3(FD_THREADS), 0, s, q, k, v,
                         kv_len_dev, kv_len_host, num_heads, num_kv_heads, scale, partials));
     return RNB_B200_OK;

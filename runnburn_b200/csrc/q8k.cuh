@@ -156,6 +156,50 @@ rmsnorm_q8k_kernel(const float *__restrict__ x, const float *__restrict__ w, flo
     }
 }
 
+// The same for one token, spread over hidden / 256 CTAs: every CTA sums the squares of the whole
+// vector (same order in every CTA, so all agree on the rms to the bit) and then normalises and
+// quantises its own 256-element block.  One CTA doing all blocks in turn spends most of its time
+// in dependent latency; this form is a single round of loads, one reduction and one block.
+RNB_GLOBAL void __launch_bounds__(128)
+rmsnorm_q8k_blocks_kernel(const float *__restrict__ x, const float *__restrict__ w, float eps, int hidden,
+                          float *__restrict__ h_out, uint8_t *__restrict__ xq_out) {
+    pdl_launch_dependents();
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, b = blockIdx.x;
+    // the norm weights do not depend on the previous kernel
+    const float4 w0 = __ldg(reinterpret_cast<const float4 *>(w + b * 256 + lane * 8)), w1 = __ldg(reinterpret_cast<const float4 *>(w + b * 256 + lane * 8 + 4));
+    pdl_wait();
+    __shared__ double red[4];
+    double ss = 0.0;
+    for (int i = tid * 4; i < hidden; i += 128 * 4) {
+        const float4 v = *reinterpret_cast<const float4 *>(x + i);
+        ss += (double)v.x * (double)v.x;
+        ss += (double)v.y * (double)v.y;
+        ss += (double)v.z * (double)v.z;
+        ss += (double)v.w * (double)v.w;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if (lane == 0) red[warp] = ss;
+    __syncthreads();
+    if (warp != 0) return;
+    const double total = ((red[0] + red[1]) + red[2]) + red[3];
+    const float rms = (float)sqrt(total / (double)hidden + (double)eps);
+    const float4 a = *reinterpret_cast<const float4 *>(x + b * 256 + lane * 8), c = *reinterpret_cast<const float4 *>(x + b * 256 + lane * 8 + 4);
+    const float xv[8] = {a.x, a.y, a.z, a.w, c.x, c.y, c.z, c.w}, wv[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+    float v[8];
+#pragma unroll
+    for (int j = 0; j < 8; j++) v[j] = __fmul_rn(__fdiv_rn(xv[j], rms), wv[j]);
+    if (h_out) {
+        float *ho = h_out + b * 256 + lane * 8;
+        *reinterpret_cast<float4 *>(ho) = make_float4(v[0], v[1], v[2], v[3]);
+        *reinterpret_cast<float4 *>(ho + 4) = make_float4(v[4], v[5], v[6], v[7]);
+    }
+    if (xq_out) {
+        Q8kDevView dv = q8k_dev_view(xq_out, hidden);
+        q8k_quantize_block_warp(v, lane, dv.qs + b * 256, dv.d + b, dv.bsum16 + b * 16, nullptr);
+    }
+}
+
 // act = silu(gate) * up with g / (1 + exp(-g)) (crates/rnb-cpu/src/kernels/activation.rs:74-89),
 // fused with Q8_K quantisation.  exp is evaluated in double and rounded once so that the
 // value fed to the quantiser is the correctly rounded one.
