@@ -380,6 +380,12 @@ int rnb_b200_peer_exchange_timeout_selftest(int *status_out);
 
 /* Shape the decoder was created with. */
 int rnb_b200_decoder_config(const rnb_b200_decoder *d, rnb_b200_model_cfg *out);
+/* Longest context (positions, 0..4096) that decode steps serve with the reference-order attention
+ * kernel, whose output is bit-identical to rnb-cpu's four-pass decode attention
+ * (crates/rnb-cpu/src/kernels/attention/decode_flash.rs:91-212); longer contexts use the chunked
+ * tensor-core kernel (same result to ~1e-6).  0 turns the reference-order kernel off.  Default:
+ * environment RNB_B200_EXACT_ATTN_MAX, else 1024.  Only before the first step. */
+int rnb_b200_decoder_set_exact_attention_max(rnb_b200_decoder *d, int max_positions);
 
 /* ---- GGUF container and file loader ------------------------------------------------------------
  * GGUFFile::parse — crates/rnb-loader/src/gguf/parser.rs:244-404 (magic "GGUF", versions 2 and 3,
@@ -422,7 +428,7 @@ int rnb_b200_gguf_model_config(const rnb_b200_gguf *g, int max_ctx, rnb_b200_mod
 /* Tensor names of crates/rnb-loader/src/arch/llama.rs:33-155 (`token_embd`, `blk.N.attn_q`, ...,
  * `output_norm`, `output`; a file without `output.weight` ties the LM head to the embedding)
  * uploaded from the mapped pages; register_pages != 0 pins the data section first
- * (rnb_b200_register_host_range). */
+ * (rnb_b200_register_host_range) where the mapping can be pinned: best effort. */
 int rnb_b200_decoder_load_gguf(rnb_b200_decoder *d, const rnb_b200_gguf *g, int register_pages);
 
 /* ---- device-pointer tier (no host copies, no synchronisation; for callers that keep

@@ -144,6 +144,7 @@ def load() -> C.CDLL:
         "rnb_b200_attention_decode_hd128_noalloc_status": [vp, vp],
         "rnb_b200_dev_error_flag": [vp],
         "rnb_b200_decoder_config": [vp, vp],
+        "rnb_b200_decoder_set_exact_attention_max": [vp, C.c_int],
         "rnb_b200_gguf_open": [C.c_char_p, vp],
         "rnb_b200_gguf_parse": [vp, sz, vp],
         "rnb_b200_gguf_info": [vp, vp, vp, vp, vp, vp],

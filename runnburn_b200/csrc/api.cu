@@ -629,8 +629,8 @@ static int attention_run(State &st, const uint16_t *k_dev, const uint16_t *v_dev
     const int n_chunks = flash_decode_default_chunks(kv_len, kv_heads, st.sm_count);
     RNB_TRY(st.partials.ensure(flash_decode_scratch_bytes(heads, n_chunks)));
     RNB_TRY(st.out_f32.ensure(heads * HD * sizeof(float)));
-    RNB_TRY(launch_flash_decode(st.stream, st.in_f32.as<float>(), k_dev, v_dev, nullptr, (int)kv_len, (int)heads,
-                                (int)kv_heads, scale, st.partials.as<float>(), n_chunks, st.out_f32.as<float>(), st.dev_error));
+    RNB_TRY(launch_attention_decode(st.stream, st.in_f32.as<float>(), k_dev, v_dev, (int)kv_len, (int)heads, (int)kv_heads, scale,
+                                    st.partials.as<float>(), n_chunks, st.out_f32.as<float>(), st.dev_error));
     return finish_to_host(st, st.out_f32.p, out, heads * HD * sizeof(float));
 }
 
@@ -1121,8 +1121,8 @@ int rnb_b200_dev_flash_decode(const float *q_dev, const uint16_t *k_dev, const u
         return fail(RNB_B200_VALIDATION_FAILED, "attention operands are not aligned: q and the scratch need 16 bytes, k and v 8 bytes, out 4 bytes");
     Locked L;
     RNB_TRY(L.st.open());
-    return launch_flash_decode((cudaStream_t)stream, q_dev, k_dev, v_dev, nullptr, (int)kv_len, (int)num_heads, (int)num_kv_heads, scale,
-                               partials_dev, n_chunks, out_dev, L.st.dev_error);
+    return launch_attention_decode((cudaStream_t)stream, q_dev, k_dev, v_dev, (int)kv_len, (int)num_heads, (int)num_kv_heads, scale, partials_dev,
+                                   n_chunks, out_dev, L.st.dev_error);
 }
 #ifdef GM_PROFILE
 extern "C" int rnb_b200_debug_gm_profile(unsigned long long *out8, int reset) {

@@ -768,4 +768,180 @@ flash_decode_reduce_q8k_wide_kernel(const float *__restrict__ partials, int n_ch
     }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Reference-order decode attention: the same floating-point operations in the same order as
+// rnb-cpu's four-pass decode kernel (crates/rnb-cpu/src/kernels/attention/decode_flash.rs:91-212
+// with the f32·f16 helpers of x86_helpers.rs:11-80), so the result is bit-identical to the CPU's:
+//   score_j = hsum(16 lanes, each 8 sequential mul-then-add steps over dims 16i + lane) * scale
+//   m = max_j score_j;  p_j = expf(score_j - m);  sum = ((p_0 + p_1) + p_2) + ...  (f32, in order)
+//   w_j = p_j * (1 / sum);  out_d = ((v_0d * w_0) + v_1d * w_1) + ...              (mul, then add)
+// The chunked tensor-core kernel above reassociates all three sums; its result differs in the last
+// bits, which the Q8_K rounding of the o_proj input can amplify.  This kernel is the one used for
+// short contexts, where the in-order sums cost less than a microsecond.
+//
+// expf is the C library's on the reference's platform: glibc's single-precision routine evaluates
+// 2^(k/32) * P(r) in binary64 (a 32-entry table of 2^(i/32) and a cubic in r) and rounds once to
+// f32.  The same evaluation here agrees with it on every input up to the binary64 rounding of
+// intermediate steps, which is 2^29 times finer than an f32 ulp.
+// ---------------------------------------------------------------------------------------------
+__device__ __constant__ unsigned long long c_exp2_tab32[32] = {   // bits(2^(i/32)) - (i << 47)
+    0x3ff0000000000000ull, 0x3fefd9b0d3158574ull, 0x3fefb5586cf9890full, 0x3fef9301d0125b51ull,
+    0x3fef72b83c7d517bull, 0x3fef54873168b9aaull, 0x3fef387a6e756238ull, 0x3fef1e9df51fdee1ull,
+    0x3fef06fe0a31b715ull, 0x3feef1a7373aa9cbull, 0x3feedea64c123422ull, 0x3feece086061892dull,
+    0x3feebfdad5362a27ull, 0x3feeb42b569d4f82ull, 0x3feeab07dd485429ull, 0x3feea47eb03a5585ull,
+    0x3feea09e667f3bcdull, 0x3fee9f75e8ec5f74ull, 0x3feea11473eb0187ull, 0x3feea589994cce13ull,
+    0x3feeace5422aa0dbull, 0x3feeb737b0cdc5e5ull, 0x3feec49182a3f090ull, 0x3feed503b23e255dull,
+    0x3feee89f995ad3adull, 0x3feeff76f2fb5e47ull, 0x3fef199bdd85529cull, 0x3fef3720dcef9069ull,
+    0x3fef5818dcfba487ull, 0x3fef7c97337b9b5full, 0x3fefa4afa2a490daull, 0x3fefd0765b6e4540ull,
+};
+// `tab` is a shared-memory copy of c_exp2_tab32 (the index differs per thread)
+__device__ __forceinline__ float expf_libm(float x, const unsigned long long *tab) {
+    if (x != x) return x;
+    if (x < -0x1.9fe368p6f) return 0.0f;            // below the smallest subnormal
+    if (x > 0x1.62e42ep6f) return INFINITY;
+    const double z = __dmul_rn(0x1.71547652b82fep+5, (double)x);   // x * 32 / ln 2
+    double kd = __dadd_rn(z, 0x1.8p52);                           // round to nearest integer
+    const unsigned long long ki = (unsigned long long)__double_as_longlong(kd);
+    kd = __dsub_rn(kd, 0x1.8p52);
+    const double r = __dsub_rn(z, kd);
+    const double s = __longlong_as_double((long long)(tab[ki & 31] + (ki << 47)));
+    const double p = __dadd_rn(__dmul_rn(0x1.c6af84b912394p-20, r), 0x1.ebfce50fac4f3p-13);
+    const double r2 = __dmul_rn(r, r);
+    double y = __dadd_rn(__dmul_rn(0x1.62e42ff0c52d6p-6, r), 1.0);
+    y = __dadd_rn(__dmul_rn(p, r2), y);
+    return __double2float_rn(__dmul_rn(y, s));
+}
+
+constexpr int AX_THREADS = 512;       // two heads per CTA, 256 threads (16 half-warps) each
+constexpr int AX_MAX_LEN = 4096;      // 2 heads * 4 bytes * 4096 positions = 32 KB of scores (no opt-in needed)
+// grid = ceil(num_heads / 2); dynamic shared memory = 2 * max_len floats.  Writes `out`
+// ([num_heads][128] f32) and/or the Q8_K blocks of the output (`xq_out`, needs an even head
+// count: two heads are one 256-element block).  A context longer than max_len raises the
+// error flag and writes nothing.
+RNB_GLOBAL void __launch_bounds__(AX_THREADS)
+attention_decode_exact_kernel(const float *__restrict__ q, const uint16_t *__restrict__ k, const uint16_t *__restrict__ v,
+                              const int *__restrict__ kv_len_dev, int kv_len_host, int max_len, int num_heads, int num_kv_heads,
+                              float scale, float *__restrict__ out, uint8_t *__restrict__ xq_out, int *__restrict__ err_flag) {
+    pdl_launch_dependents();
+    pdl_wait();
+    extern __shared__ __align__(16) float s_score[];   // [2][max_len]
+    __shared__ unsigned long long s_tab[32];
+    __shared__ float s_red[2][8];
+    __shared__ float s_inv[2];
+    __shared__ __align__(16) float s_o[2 * HD];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int kv_len = kv_len_dev ? *kv_len_dev + kv_len_host : kv_len_host;
+    if (kv_len < 1 || kv_len > max_len) {
+        if (tid == 0 && err_flag) atomicExch(err_flag, DEV_ERR_BAD_JOB);
+        return;
+    }
+    if (tid < 32) s_tab[tid] = c_exp2_tab32[tid];
+    const int hs = warp >> 3, th = tid & 255;             // head slot, thread within the head
+    const int h = blockIdx.x * 2 + hs;
+    const bool live = h < num_heads;
+    const int group = num_heads / num_kv_heads;
+    const size_t kv_dim = (size_t)num_kv_heads * HD;
+    const size_t head_off = (size_t)(live ? h / group : 0) * HD;
+    float *sc = s_score + (size_t)hs * max_len;
+
+    // pass 1: scores.  Half-warp (16 lanes) per position, lane l owns dims 16 i + l.
+    if (live) {
+        const int l16 = lane & 15, hw = (th >> 4);        // 16 half-warps per head
+        // the two halves of a warp run different trip counts: shuffles name the own half only
+        const unsigned hmask = (lane & 16) ? 0xffff0000u : 0x0000ffffu;
+        float qr[8];
+#pragma unroll
+        for (int i = 0; i < 8; i++) qr[i] = q[(size_t)h * HD + 16 * i + l16];
+        for (int j0 = hw; j0 < kv_len; j0 += 32) {        // two positions in flight per half-warp
+            const int j1 = j0 + 16;
+            const uint16_t *r0 = k + (size_t)j0 * kv_dim + head_off + l16;
+            const uint16_t *r1 = k + (size_t)(j1 < kv_len ? j1 : j0) * kv_dim + head_off + l16;
+            uint16_t a[8], b[8];
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                a[i] = r0[16 * i];
+                b[i] = r1[16 * i];
+            }
+            float acc0 = 0.0f, acc1 = 0.0f;
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                acc0 = __fadd_rn(acc0, __fmul_rn(qr[i], __half2float(__ushort_as_half(a[i]))));
+                acc1 = __fadd_rn(acc1, __fmul_rn(qr[i], __half2float(__ushort_as_half(b[i]))));
+            }
+            // lanes l and l + 8 are the reference's two accumulators; then lo + hi, movehdup, movehl
+#pragma unroll
+            for (int o = 8; o >= 4; o >>= 1) {
+                acc0 = __fadd_rn(acc0, __shfl_xor_sync(hmask, acc0, o));
+                acc1 = __fadd_rn(acc1, __shfl_xor_sync(hmask, acc1, o));
+            }
+            acc0 = __fadd_rn(acc0, __shfl_xor_sync(hmask, acc0, 1));
+            acc1 = __fadd_rn(acc1, __shfl_xor_sync(hmask, acc1, 1));
+            acc0 = __fadd_rn(acc0, __shfl_xor_sync(hmask, acc0, 2));
+            acc1 = __fadd_rn(acc1, __shfl_xor_sync(hmask, acc1, 2));
+            if (l16 == 0) {
+                sc[j0] = __fmul_rn(acc0, scale);
+                if (j1 < kv_len) sc[j1] = __fmul_rn(acc1, scale);
+            }
+        }
+    }
+    __syncthreads();
+    // pass 2: max
+    float m = -INFINITY;
+    if (live)
+        for (int j = th; j < kv_len; j += 256) m = fmaxf(m, sc[j]);
+    m = warp_max(m);
+    if (lane == 0) s_red[hs][warp & 7] = m;
+    __syncthreads();
+    float M = s_red[hs][0];
+#pragma unroll
+    for (int i = 1; i < 8; i++) M = fmaxf(M, s_red[hs][i]);
+    // pass 3: exponentials in parallel, their sum in position order by one thread per head
+    if (live)
+        for (int j = th; j < kv_len; j += 256) sc[j] = expf_libm(__fsub_rn(sc[j], M), s_tab);
+    __syncthreads();
+    if (live && th == 0) {
+        float sum = 0.0f;
+        int j = 0;
+        for (; j + 4 <= kv_len; j += 4) {
+            const float4 p = *reinterpret_cast<const float4 *>(sc + j);
+            sum = __fadd_rn(__fadd_rn(__fadd_rn(__fadd_rn(sum, p.x), p.y), p.z), p.w);
+        }
+        for (; j < kv_len; j++) sum = __fadd_rn(sum, sc[j]);
+        s_inv[hs] = sum > 0.0f ? __fdiv_rn(1.0f, sum) : 0.0f;
+    }
+    __syncthreads();
+    // pass 4: weights in parallel, then one thread per output dim walks the positions in order
+    if (live) {
+        const float inv = s_inv[hs];
+        for (int j = th; j < kv_len; j += 256) sc[j] = __fmul_rn(sc[j], inv);
+    }
+    __syncthreads();
+    if (th < HD) {
+        float o = 0.0f;
+        if (live) {
+            const uint16_t *vp = v + head_off + th;
+            int j = 0;
+            for (; j + 8 <= kv_len; j += 8) {
+                uint16_t x[8];
+#pragma unroll
+                for (int u = 0; u < 8; u++) x[u] = vp[(size_t)(j + u) * kv_dim];
+#pragma unroll
+                for (int u = 0; u < 8; u++) o = __fadd_rn(o, __fmul_rn(__half2float(__ushort_as_half(x[u])), sc[j + u]));
+            }
+            for (; j < kv_len; j++) o = __fadd_rn(o, __fmul_rn(__half2float(__ushort_as_half(vp[(size_t)j * kv_dim])), sc[j]));
+            if (out) out[(size_t)h * HD + th] = o;
+        }
+        s_o[hs * HD + th] = o;
+    }
+    if (!xq_out) return;
+    __syncthreads();
+    if (tid < 32) {
+        const float4 v0 = *reinterpret_cast<const float4 *>(s_o + lane * 8), v1 = *reinterpret_cast<const float4 *>(s_o + lane * 8 + 4);
+        const float vals[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+        Q8kDevView dv = q8k_dev_view(xq_out, num_heads * HD);
+        const int b = blockIdx.x;
+        q8k_quantize_block_warp(vals, lane, dv.qs + b * 256, dv.d + b, dv.bsum16 + b * 16, nullptr);
+    }
+}
+
 }  // namespace rnb

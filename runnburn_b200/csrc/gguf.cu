@@ -468,14 +468,16 @@ int rnb_b200_gguf_model_config(const rnb_b200_gguf *g, int max_ctx, rnb_b200_mod
 
 // Points the decoder at the file's tensors (names of arch/llama.rs:33-155; the expert stacks of the
 // MoE families are `ffn_gate_inp`, `ffn_{gate,up,down}_exps`).  With register_pages the mapped
-// tensor-data section is pinned first so the uploads run as asynchronous DMA from the page cache.
+// tensor-data section is pinned first, where the mapping allows it, so the uploads run as
+// asynchronous DMA from the page cache.
 int rnb_b200_decoder_load_gguf(rnb_b200_decoder *d, const rnb_b200_gguf *g, int register_pages) {
     if (!d || !g) return fail(RNB_B200_VALIDATION_FAILED, "null pointer argument");
     rnb_b200_model_cfg c;
     RNB_TRY(rnb_b200_decoder_config(d, &c));
     if (register_pages && g->data_start < g->len) {
-        const int rc = rnb_b200_register_host_range(g->data + g->data_start, g->len - g->data_start);
-        if (rc != RNB_B200_OK) return rc;
+        // best effort: some file systems' read-only mappings cannot be pinned (the driver answers
+        // "invalid argument"); the uploads then run as staged pageable copies, same bytes
+        if (rnb_b200_register_host_range(g->data + g->data_start, g->len - g->data_start) != RNB_B200_OK) cudaGetLastError();
     }
     auto quant = [&](const std::string &name, rnb_b200_qweight *out, bool required) -> int {
         const Tensor *t = g->tensor(name);

@@ -527,6 +527,38 @@ inline int launch_flash_decode(cudaStream_t s, const float *q, const uint16_t *k
     return RNB_B200_OK;
 }
 
+// Longest context the reference-order attention kernel serves (RNB_B200_EXACT_ATTN_MAX, default
+// 1024, 0 turns it off): up to there decode attention is bit-identical to rnb-cpu's; beyond it the
+// chunked tensor-core kernel takes over, whose sums are reassociated.
+inline int exact_attention_max() {
+    static const int v = [] {
+        const char *e = getenv("RNB_B200_EXACT_ATTN_MAX");
+        long n = e && *e ? strtol(e, nullptr, 10) : 1024;
+        if (n < 0) n = 0;
+        if (n > AX_MAX_LEN) n = AX_MAX_LEN;
+        return (int)((n + 3) & ~3L);
+    }();
+    return v;
+}
+// kv_len = (*kv_len_dev if given) + kv_len_host must not exceed max_len (the kernel raises the error flag otherwise)
+inline int launch_attention_decode_exact(cudaStream_t s, const float *q, const uint16_t *k, const uint16_t *v, const int *kv_len_dev,
+                                         int kv_len_host, int max_len, int num_heads, int num_kv_heads, float scale, float *out,
+                                         uint8_t *xq_out, int *dev_error) {
+    if (max_len < 4 || max_len > AX_MAX_LEN || max_len % 4) return fail(RNB_B200_VALIDATION_FAILED, "exact attention: max_len %d must be a multiple of 4 in 4..%d", max_len, AX_MAX_LEN);
+    if (xq_out && num_heads % 2) return fail(RNB_B200_VALIDATION_FAILED, "exact attention: Q8_K output needs an even head count");
+    RNB_CU(launch_k(attention_decode_exact_kernel, dim3((num_heads + 1) / 2), dim3(AX_THREADS), (size_t)max_len * 2 * sizeof(float), s, q, k, v,
+                    kv_len_dev, kv_len_host, max_len, num_heads, num_kv_heads, scale, out, xq_out, dev_error));
+    return RNB_B200_OK;
+}
+// Decode attention with the context length known on the host: reference-order kernel for short
+// contexts, chunked kernel + merge otherwise.
+inline int launch_attention_decode(cudaStream_t s, const float *q, const uint16_t *k, const uint16_t *v, int kv_len, int num_heads,
+                                   int num_kv_heads, float scale, float *partials, int n_chunks, float *out, int *dev_error) {
+    if (kv_len <= exact_attention_max())
+        return launch_attention_decode_exact(s, q, k, v, nullptr, kv_len, (kv_len + 3) & ~3, num_heads, num_kv_heads, scale, out, nullptr, dev_error);
+    return launch_flash_decode(s, q, k, v, nullptr, kv_len, num_heads, num_kv_heads, scale, partials, n_chunks, out, dev_error);
+}
+
 // Tensor-core prefill matmul: converts the f32 token rows to bf16 (scratch `xb`, seq*cols
 // elements) and runs the tcgen05 kernel.  y is [seq][rows] f32.
 int prefill_gemm_setup();   // raises the kernels' dynamic shared-memory limit once

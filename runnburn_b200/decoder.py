@@ -88,6 +88,11 @@ class Decoder:
         check(load().rnb_b200_decoder_set_globals(self._h, _qw(desc["token_embd"], keep), _fp(desc["out_norm"], keep),
                                                   _qw(desc["output"], keep)))
 
+    def set_exact_attention_max(self, max_positions: int) -> None:
+        """Contexts up to `max_positions` use the reference-order attention kernel (bit-identical to
+        the CPU's); 0 turns it off.  Only before the first step."""
+        check(load().rnb_b200_decoder_set_exact_attention_max(self._h, int(max_positions)))
+
     def fill_synthetic(self, seed: int = 0, sigma: float = 0.02) -> None:
         check(load().rnb_b200_decoder_fill_synthetic(self._h, seed, sigma))
 

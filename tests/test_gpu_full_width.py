@@ -22,11 +22,11 @@ def _first_divergence(a, b):
 
 
 def test_llama3_8b_width_64_greedy_ids_identical(llama8b_width):
-    """Prompt fed token by token, then 64 greedy steps against the oracle: ids identical wherever
-    the CPU's top-2 margin is not a near-tie, logits within tolerance throughout (the bar and its
-    reason are stated beside _greedy in test_gpu_decoder.py)."""
+    """Prompt fed token by token, then 64 greedy steps against the oracle: every logit vector, the
+    ids and the K/V rows are bit-identical (contexts this short run the reference-order attention
+    kernel, so the whole step repeats the CPU's arithmetic)."""
     import runnburn_b200 as r
-    from test_gpu_decoder import _assert_ids, _greedy
+    from test_gpu_decoder import _assert_identical, _greedy
     desc = llama8b_width
     n_prompt, n_steps = 16, 64
     dec = r.Decoder(r.ModelConfig(max_ctx=n_prompt + n_steps + 4, **desc["cfg"]))
@@ -34,9 +34,33 @@ def test_llama3_8b_width_64_greedy_ids_identical(llama8b_width):
     ref = orc.Model(desc, n_prompt + n_steps + 4)
     prompt = np.random.default_rng(11).integers(0, desc["cfg"]["vocab"], n_prompt).tolist()
     gpu_ids, cpu_ids, margins, errs = _greedy(dec, ref, prompt, n_steps)
-    _assert_ids(gpu_ids, cpu_ids, margins, errs)
+    _assert_identical(gpu_ids, cpu_ids, errs)
     assert len(gpu_ids) == n_steps
-    print("8B width: %d of %d ids identical, largest logit error %.2e of scale" % (sum(g == c for g, c in zip(gpu_ids, cpu_ids)), n_steps, max(errs)))
+    for layer in range(2):
+        kg, vg = dec.read_kv(layer, n_prompt + n_steps)
+        kc, vc = ref.kv_cache(layer, n_prompt + n_steps)
+        assert np.array_equal(kg, kc) and np.array_equal(vg, vc)
+    dec.close()
+    ref.close()
+
+
+def test_llama3_8b_width_chunked_attention_kernel(llama8b_width):
+    """The same stack with the reference-order attention kernel off, i.e. the kernel that serves
+    long contexts: its ~1e-6 attention differences pass through Q8_K rounding, and at this width
+    (4096-wide matvecs, weights N(0, 0.02)) one flipped quant step moves a logit by ~4e-4 of the
+    logit scale and is amplified by the next layer's quantisers.  Bar: ids identical wherever the
+    CPU's top-2 margin exceeds the near-tie threshold, logits within 5e-2 of their scale."""
+    import runnburn_b200 as r
+    from test_gpu_decoder import _assert_ids, _greedy
+    desc = llama8b_width
+    n_prompt, n_steps = 16, 32
+    dec = r.Decoder(r.ModelConfig(max_ctx=n_prompt + n_steps + 4, **desc["cfg"]))
+    dec.set_exact_attention_max(0)
+    dec.load_description(desc)
+    ref = orc.Model(desc, n_prompt + n_steps + 4)
+    prompt = np.random.default_rng(11).integers(0, desc["cfg"]["vocab"], n_prompt).tolist()
+    gpu_ids, cpu_ids, margins, errs = _greedy(dec, ref, prompt, n_steps)
+    _assert_ids(gpu_ids, cpu_ids, margins, errs, logit_tol=5e-2)
     dec.close()
     ref.close()
 
@@ -59,7 +83,7 @@ def test_llama3_8b_width_ids_after_tensor_core_prefill(llama8b_width):
         tok_e = exact.step(t, pos)
     tok_f = fast.prefill(prompt, 0)
     le, lf = exact.read_logits(), fast.read_logits()
-    assert max_err_vs_norm(lf, le) <= 3e-2
+    assert max_err_vs_norm(lf, le) <= 5e-2          # bf16 weights and tokens through 4096- and 14336-wide sums, two layers
     ids_e, ids_f, margins = [], [], []
     pos = n_prompt
     for _ in range(n_steps):
@@ -84,8 +108,8 @@ def test_llama3_8b_width_ids_after_tensor_core_prefill(llama8b_width):
 
 
 def test_qwen3_30b_a3b_width_expert_ids_and_tokens():
-    """128 experts, top-8, hidden 2048: the routed expert ids of every layer and the greedy
-    token of every step equal the oracle's."""
+    """128 experts, top-8, hidden 2048: the routed expert ids of every layer, the greedy token and
+    the whole logit vector of every step are bit-identical to the oracle's."""
     import runnburn_b200 as r
     desc = moe_description_fast(seed=5, n_layer=2)
     n_prompt, n_steps = 8, 24
@@ -100,13 +124,11 @@ def test_qwen3_30b_a3b_width_expert_ids_and_tokens():
         tok_g, lg = dec.step(t, pos, want_logits=True)
         lc = ref.decode(t, pos)
         tok_c = orc.argmax_last(lc)
-        top2 = np.partition(lc, -2)[-2:]
-        if tok_g != tok_c:
-            assert float(top2[1] - top2[0]) <= 1e-2 * float(np.max(np.abs(lc))), f"greedy ids differ at position {pos} without a near-tie"
+        assert tok_g == tok_c, f"greedy ids differ at position {pos}"
         for layer in range(2):
             got, want = dec.read_expert_ids(layer), ref.expert_ids(layer)
             assert len(got) == 8 and np.array_equal(got, want), f"expert ids differ at position {pos}, layer {layer}: {got} vs {want}"
-        assert max_err_vs_norm(lg, lc) <= 5e-3
+        assert np.array_equal(lg, lc), f"logits are not bit-identical at position {pos}: {max_err_vs_norm(lg, lc):.2e} of scale"
         pos += 1
     dec.close()
     ref.close()
