@@ -39,6 +39,7 @@ WORKLOADS = {
     "tiny-llama-ctx256": (dict(n_layer=2, hidden=512, n_head=4, n_kv_head=2, n_ff=1024, vocab=2048), 256),
 }
 DRAM_TRAFFIC_OVER_ALGORITHMIC = 574.6 / 570.6
+REPEATS = 5
 METRIC = "decode_tok_per_s_batch1"
 UNIT = "tok/s"
 
@@ -302,6 +303,35 @@ def prefill_gemm_bench(shape: dict, seq: int, reps: int = 3) -> dict:
             "launches": rows_out}
 
 
+def moe_decode_bench(args) -> dict:
+    """Secondary measurement (BASELINE config 2): batch-1 decode of the Qwen3-30B-A3B-shaped MoE stack
+    (48 layers, 128 experts, top-8, context 8192) with device-resident token ids, CUDA events on the
+    decoder's stream; median of REPEATS timed regions."""
+    import runnburn_b200 as r
+    name = "qwen3-30b-a3b-moe-ctx8192"
+    shape, ctx = WORKLOADS[name]
+    K, W = min(args.steps, 32), 3
+    dec = r.Decoder(r.ModelConfig(max_ctx=ctx + (REPEATS + 1) * K + W + 8, **shape))
+    dec.fill_synthetic(seed=0, sigma=0.02)
+    dec.fill_kv_synthetic(ctx, seed=0)
+    st = dec.stats()
+    dec.step(1, ctx)
+    dec.time_steps(ctx + 1, W)
+    pos, all_ms = ctx + 1 + W, []
+    for _ in range(REPEATS):
+        all_ms.append(dec.time_steps(pos, K))
+        pos += K
+    dec.close()
+    ms = float(np.median(all_ms))
+    alg = algorithmic_bytes_per_token(shape, ctx)
+    peaks = load_peaks()
+    gbs = alg["total"] / (ms / K / 1000.0) / 1e9
+    return {"workload": name, "value": K / (ms / 1000.0), "unit": UNIT, "ms_per_step": ms / K, "steps": K, "repeats": REPEATS,
+            "launches_per_step": int(st["launches_per_step"]), "algorithmic_bytes_per_token": alg,
+            "whole_step_hbm": {"achieved_gbs": gbs, "peak_gbs": peaks["hbm_gbs"], "frac": gbs / peaks["hbm_gbs"]},
+            "what": "router matvec + top-8 + the 8 selected experts' gate/up/down streamed per layer, expert ids chosen on the device"}
+
+
 def matvec_shape_bench(shapes=None, min_total_bytes=1 << 30, reps=5) -> list:
     """BASELINE config 1: each batch-1 matvec shape timed alone.  Every shape gets enough distinct
     weight copies to exceed 1 GiB (far more than the 126 MB L2), one launch per copy is captured
@@ -382,7 +412,8 @@ def run_gpu(args, shape, ctx, name, rank, world, local_rank):
         dist.barrier()
     ops.open()
     K, W = args.steps, args.warmup
-    max_ctx = ctx + 2 * (K + W) + 8
+    R = REPEATS                                   # the timed region runs R times; the median is reported
+    max_ctx = ctx + (R + 1) * K + 2 * max(W, 3) + 8
     cfg = r.ModelConfig(max_ctx=max_ctx, world_size=world, rank=rank, **shape)
     dec = r.Decoder(cfg)
     transport = os.environ.get("RNB_B200_TRANSPORT", "nccl")   # "nccl": ncclAllGather (measured faster); "peer": own peer-memory exchange kernels
@@ -411,28 +442,65 @@ def run_gpu(args, shape, ctx, name, rank, world, local_rank):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
-    # -- device-resident: token ids never leave the GPU; CUDA events on the decoder's stream
-    tok = dec.step(1, ctx)                       # seeds the device-side token with a real argmax
-    dec.time_steps(ctx + 1, max(W, 3))           # warm-up
+    def drive(d, sync, reduce_max):
+        """The measured sequence on decoder `d`: K device-chained steps timed R times with CUDA events
+        on the decoder's stream (token ids never leave the GPU), then K steps through the host-facing
+        call (token id H2D, next id D2H, a sync per step) under a wall clock.  Returns the R step
+        timings in ms, the end-to-end seconds and every token id the host-facing steps returned."""
+        tok = d.step(1, ctx)                       # seeds the device-side token with a real argmax
+        d.time_steps(ctx + 1, max(W, 3))           # warm-up
+        pos = ctx + 1 + max(W, 3)
+        all_ms = []
+        for _ in range(R):
+            sync()
+            all_ms.append(reduce_max(d.time_steps(pos, K)))
+            pos += K
+        ids = []
+        for i in range(max(W, 3)):
+            tok = d.step(tok, pos + i)
+            ids.append(int(tok))
+        sync()
+        t0 = time.perf_counter()
+        for i in range(K):
+            tok = d.step(tok, pos + max(W, 3) + i)
+            ids.append(int(tok))
+        sync()
+        return all_ms, reduce_max(time.perf_counter() - t0), ids
+
     barrier()
     clocks = ClockSampler(local_rank)
     if rank == 0:
         clocks.start()
-    ms = dec.time_steps(ctx + 1 + max(W, 3), K)
-    barrier()
-    ms = max_over_ranks(ms)
-
-    # -- end to end through the host-facing call: token id H2D, next token id D2H, sync per step
-    pos0 = ctx + 1 + max(W, 3) + K
-    for i in range(max(W, 3)):
-        tok = dec.step(tok, pos0 + i)
-    barrier()
-    t0 = time.perf_counter()
-    for i in range(K):
-        tok = dec.step(tok, pos0 + max(W, 3) + i)
-    barrier()
-    e2e_s = max_over_ranks(time.perf_counter() - t0)
+    all_ms, e2e_s, ids = drive(dec, barrier, max_over_ranks)
     clk = clocks.stop() if rank == 0 else None
+    ms = float(np.median(all_ms))
+
+    # -- N > 1: the same model unsharded on rank 0's GPU (the synthetic fill gives a row shard the bytes
+    # the whole matrix has there), driven through the same sequence: its ids must equal the sharded run's,
+    # and its timing is the 1-GPU base that the N-GPU figure scales from
+    shard = None
+    if world > 1:
+        mine = [None] * world
+        dist.all_gather_object(mine, ids)
+        shard = {"ranks_agree": all(m == mine[0] for m in mine)}
+        if rank == 0 and not args.no_scaling_base:
+            try:
+                base = r.Decoder(r.ModelConfig(max_ctx=max_ctx, world_size=1, rank=0, **shape))
+                base.fill_synthetic(seed=0, sigma=0.02)
+                base.fill_kv_synthetic(ctx, seed=0)
+
+                def base_sync():
+                    base.sync()
+                b_ms, b_e2e, b_ids = drive(base, base_sync, float)
+                base.close()
+                bm = float(np.median(b_ms))
+                shard["ids_equal"] = b_ids == ids
+                shard["n_ids"] = len(ids)
+                shard["base"] = {"workload": name, "n_gpus": 1, "value": K / (bm / 1000.0), "unit": UNIT, "ms_per_step": bm / K,
+                                 "e2e": K / b_e2e, "what": "the same model unsharded on one GPU of this box, same steps"}
+            except Exception as e:   # the base must not lose the headline line
+                shard["base_error"] = str(e)[:200]
+        barrier()
 
     # -- dominant kernel: every matvec launch of a step, timed alone over the model's own weights
     mv = dec.time_matvecs(iters=max(3, min(K, 16))) if shape.get("n_expert", 0) == 0 else None
@@ -446,7 +514,8 @@ def run_gpu(args, shape, ctx, name, rank, world, local_rank):
     value = K / (ms / 1000.0)
     out = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": max(W, 3),
-        "ms_per_step": ms / K, "higher_is_better": True, "scaling": "strong" if world > 1 else "weak",
+        "ms_per_step": ms / K, "repeats": R, "ms_per_step_all": [m / K for m in all_ms], "timing": "median of %d timed regions of %d steps each, max over ranks per region" % (R, K),
+        "higher_is_better": True, "scaling": "strong" if world > 1 else "weak",
         "vs_baseline": None, "dtype": "int8xint4->int32, f32 accumulate", "data": "synthetic",
         "config": {"workload": name, "context": ctx, "kv_cache": "f16", "weights": ("random-init N(0,0.02): attention and LM head Q6_K, f32 router, experts Q4_K, generated on device" if shape.get("n_expert", 0) else "random-init N(0,0.02), Q4_K_M layout (attn_v/ffn_down/output Q6_K), generated on device"),
                    "parallelism": (f"row-sharded x{world}, all-gather by " + ("ncclAllGather" if transport == "nccl" else "peer-memory stores over NVLink (own kernel)")) if world > 1 else "single GPU",
@@ -458,11 +527,16 @@ def run_gpu(args, shape, ctx, name, rank, world, local_rank):
         "whole_step_hbm": {"achieved_gbs": alg["total"] / world / (ms / K / 1000.0) / 1e9, "peak_gbs": peaks["hbm_gbs"],
                            "frac": alg["total"] / world / (ms / K / 1000.0) / 1e9 / peaks["hbm_gbs"]},
     }
+    if shard is not None:
+        out["shard_ids_equal"] = bool(shard.get("ids_equal", False)) and shard["ranks_agree"]
+        out["shard_check"] = {k: v for k, v in shard.items() if k != "base"}
+        if "base" in shard:
+            out["scaling_base"] = shard["base"]
     if mv:
         per_launch_bytes = mv["bytes_per_iter"] / mv["launches_per_iter"]
         per_launch_s = mv["ms"] / 1000.0 / (mv["iters"] * mv["launches_per_iter"])
         ach = per_launch_bytes / per_launch_s / 1e9
-        out["roofline"] = {"kernel": "gemv_stream_kernel", "bound": "hbm", "achieved": ach, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+        out["roofline"] = {"kernel": "gemv_mma_kernel_1 (q/k/v, o, down, LM head: integer tensor-core matvec) and gemv_pair_q4k_kernel (gate/up)", "bound": "hbm", "achieved": ach, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                            "frac": ach / peaks["hbm_gbs"], "frac_of_8TBs_nominal": ach / 8000.0, "peak_source": peaks["source"],
                            # DRAM read+write bytes per launch: the ncu capture of the five matvec shapes gave
                            # 574.6 MB of traffic for 570.6 MB of algorithmic bytes (summary under profiles/)
@@ -499,6 +573,9 @@ def main():
     ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-prefill", action="store_true", help="skip the secondary prefill-matmul measurement")
+    ap.add_argument("--no-per-shape", action="store_true", help="skip the per-shape matvec table of the roofline block")
+    ap.add_argument("--no-moe", action="store_true", help="skip the secondary MoE decode measurement")
+    ap.add_argument("--no-scaling-base", action="store_true", help="N > 1: skip the unsharded 1-GPU run of the same model")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -523,6 +600,23 @@ def main():
             out["prefill_gemm"] = prefill_gemm_bench(shape, 2048)
         except Exception as e:   # a secondary figure must not lose the headline line
             out["prefill_gemm"] = {"error": str(e)[:200]}
+    if world == 1 and "roofline" in out and not args.no_per_shape:
+        # BASELINE config 1: the layer's and the LM head's matvec shapes each timed alone
+        try:
+            ps = matvec_shape_bench([(12, 4096, 4096), (12, 14336, 4096), (12, 4096, 14336), (14, 1024, 4096), (14, 4096, 14336), (14, 128256, 4096)]
+                                    if shape.get("hidden") == 4096 else None)
+            out["roofline"]["per_shape"] = ps
+            out["roofline"]["per_shape_mean_frac"] = float(np.mean([p_["frac"] for p_ in ps]))
+            out["roofline"]["per_shape_how"] = ("each shape alone: enough distinct weight copies to exceed 1 GiB, one launch per copy in a CUDA graph, "
+                                                "graph replayed between two CUDA events on the launching stream; algorithmic bytes = rows * row_bytes + Q8_K activation + f32 out")
+        except Exception as e:
+            out["roofline"]["per_shape"] = {"error": str(e)[:200]}
+    if world == 1 and args.workload is None and not args.no_moe:
+        # BASELINE config 2 as a secondary figure of the default line: Qwen3-30B-A3B-shaped MoE decode
+        try:
+            out["moe"] = moe_decode_bench(args)
+        except Exception as e:
+            out["moe"] = {"error": str(e)[:200]}
     if world == 1 and not args.no_cpu_baseline:
         s, layer, head = cpu_baseline(shape, ctx, reps=5, warmup=1, min_seconds=10.0)   # about 10 s of CPU work
         out["cpu_baseline"] = {"value": s.tok_per_s(min(layer), min(head)), "unit": UNIT, "cores": s.threads, "kind": "port",

@@ -320,15 +320,17 @@ __device__ __forceinline__ void split_f16x2(float x, float y, uint32_t &hi, uint
 // output as f32 and / or as Q8_K blocks (two heads = one 256-element block), which saves the merge
 // launch.  counters: one int per KV head, zero before the launch.
 struct FdMerge {
-    int *counters;       // null: no merge here
+    int *counters;       // null: no counter-based merge
     float *out;          // [heads][128] f32, optional
     uint8_t *xq_out;     // Q8K-dev layout of the heads x 128 vector, optional (needs an even head group)
+    int cluster;         // > 0: the launch is one thread-block cluster of this many chunks per KV head; the
+                         // cluster's CTA b merges heads 2b, 2b + 1 of the group after a cluster barrier
 };
 template <bool PREFILL>
 __device__ __forceinline__ void fdm_body(const float *__restrict__ q, const uint16_t *__restrict__ k, const uint16_t *__restrict__ v,
                                          const int *__restrict__ kv_len_dev, int kv_len_host, int seq_len, int num_heads, int num_kv_heads,
                                          float scale, float *__restrict__ partials, float *__restrict__ out, int *__restrict__ err_flag,
-                                         const FdMerge merge = FdMerge{nullptr, nullptr, nullptr}) {
+                                         const FdMerge merge = FdMerge{nullptr, nullptr, nullptr, 0}) {
     pdl_launch_dependents();
     pdl_wait();
     __shared__ __align__(128) uint8_t s_kv[FDM_KV_BYTES];   // K rows then V rows; merge scratch later
@@ -531,6 +533,45 @@ __device__ __forceinline__ void fdm_body(const float *__restrict__ q, const uint
         }
         // the next head pass overwrites s_kv through the async proxy after these generic reads
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (!PREFILL && merge.cluster > 0) {
+        // ---- all chunks of this KV head are one cluster: barrier, then CTA b merges the group's heads 2b, 2b + 1 ----
+        __threadfence();
+        asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+        const int hA = 2 * chunk;                       // first head of this CTA's pair within the group
+        if (hA >= group) return;
+        float *s_o = reinterpret_cast<float *>(s_kv);   // [2][128] merged rows
+        __syncthreads();
+#pragma unroll
+        for (int e = 0; e < 2; e++) {
+            float o_val = 0.f;
+            const int head = kv_h * group + hA + e;
+            if (hA + e < group) {
+                const float *base = partials + (size_t)head * n_chunks * FD_PART_STRIDE;
+                float M = -INFINITY;
+                for (int c = 0; c < n_chunks; c++) M = fmaxf(M, __ldcg(base + (size_t)c * FD_PART_STRIDE + HD));
+                float a = 0.f, L = 0.f;
+#pragma unroll 4
+                for (int c = 0; c < n_chunks; c++) {
+                    const float mc = __ldcg(base + (size_t)c * FD_PART_STRIDE + HD);
+                    const float f = mc == -INFINITY ? 0.f : expf(mc - M);
+                    L += __ldcg(base + (size_t)c * FD_PART_STRIDE + HD + 1) * f;
+                    a += __ldcg(base + (size_t)c * FD_PART_STRIDE + tid) * f;
+                }
+                o_val = L > 0.f ? a / L : 0.f;
+                if (merge.out) merge.out[(size_t)head * HD + tid] = o_val;
+            }
+            s_o[e * HD + tid] = o_val;
+        }
+        __syncthreads();
+        if (merge.xq_out && warp == 0) {
+            const float4 v0 = *(reinterpret_cast<const float4 *>(s_o) + 2 * lane), v1 = *(reinterpret_cast<const float4 *>(s_o) + 2 * lane + 1);
+            const float vv[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+            Q8kDevView dv = q8k_dev_view(merge.xq_out, num_heads * HD);
+            const int blk = (kv_h * group) / 2 + chunk;
+            q8k_quantize_block_warp(vv, lane, dv.qs + blk * 256, dv.d + blk, dv.bsum16 + blk * 16, nullptr);
+        }
+        return;
     }
     if (PREFILL || !merge.counters) return;
     // ---- last CTA of this KV head: merge its chunks --------------------------------------------
@@ -812,19 +853,46 @@ __device__ __forceinline__ float expf_libm(float x, const unsigned long long *ta
     return __double2float_rn(__dmul_rn(y, s));
 }
 
-constexpr int AX_THREADS = 512;       // two heads per CTA, 256 threads (16 half-warps) each
-constexpr int AX_MAX_LEN = 4096;      // 2 heads * 4 bytes * 4096 positions = 32 KB of scores (no opt-in needed)
-// grid = ceil(num_heads / 2); dynamic shared memory = 2 * max_len floats.  Writes `out`
+constexpr int AX_THREADS = 512;       // two heads per CTA
+constexpr int AX_MAX_LEN = 4096;      // scores of both heads: 2 * 4 bytes * 4096 positions = 32 KB
+constexpr int AX_STAGE_BYTES = 32768; // staged K or V rows: 128 positions of one KV head, or 64 of two
+constexpr int AX_STAGE_VECS = AX_STAGE_BYTES / 16 / AX_THREADS;   // 16-byte loads per thread per tile
+inline size_t ax_smem_bytes(int max_len) { return (size_t)AX_STAGE_BYTES + (size_t)max_len * 2 * sizeof(float); }
+
+// One tile of K or V rows into registers (16-byte loads, all in flight together), then into the
+// staging buffer.  `shared_kv`: both heads of the CTA read the same KV head, the tile is 128
+// positions of it; otherwise 64 positions of each head's KV head (slot = head).
+struct AxTile {
+    uint4 r[AX_STAGE_VECS];
+};
+__device__ __forceinline__ void ax_fetch(AxTile &t, const uint16_t *__restrict__ base, size_t kv_dim, size_t off0, size_t off1, bool shared_kv,
+                                         int pos0, int kv_len, int tid) {
+#pragma unroll
+    for (int i = 0; i < AX_STAGE_VECS; i++) {
+        const int idx = tid + AX_THREADS * i;
+        const int slot = shared_kv ? 0 : idx >> 10, p = shared_kv ? idx >> 4 : (idx & 1023) >> 4, seg = idx & 15;
+        t.r[i] = make_uint4(0, 0, 0, 0);
+        if (pos0 + p < kv_len) t.r[i] = *reinterpret_cast<const uint4 *>(base + (size_t)(pos0 + p) * kv_dim + (slot ? off1 : off0) + seg * 8);
+    }
+}
+__device__ __forceinline__ void ax_store(const AxTile &t, uint16_t *stage, int tid) {
+#pragma unroll
+    for (int i = 0; i < AX_STAGE_VECS; i++) *reinterpret_cast<uint4 *>(stage + (size_t)(tid + AX_THREADS * i) * 8) = t.r[i];
+}
+
+// grid = ceil(num_heads / 2); dynamic shared memory = ax_smem_bytes(max_len).  Writes `out`
 // ([num_heads][128] f32) and/or the Q8_K blocks of the output (`xq_out`, needs an even head
-// count: two heads are one 256-element block).  A context longer than max_len raises the
-// error flag and writes nothing.
+// count: two heads are one 256-element block).  K and V must be 16-byte aligned.  A context
+// longer than max_len raises the error flag and writes nothing.
 RNB_GLOBAL void __launch_bounds__(AX_THREADS)
 attention_decode_exact_kernel(const float *__restrict__ q, const uint16_t *__restrict__ k, const uint16_t *__restrict__ v,
                               const int *__restrict__ kv_len_dev, int kv_len_host, int max_len, int num_heads, int num_kv_heads,
                               float scale, float *__restrict__ out, uint8_t *__restrict__ xq_out, int *__restrict__ err_flag) {
     pdl_launch_dependents();
     pdl_wait();
-    extern __shared__ __align__(16) float s_score[];   // [2][max_len]
+    extern __shared__ __align__(16) uint8_t s_dyn[];
+    uint16_t *stage = reinterpret_cast<uint16_t *>(s_dyn);                    // [slot][position][128]
+    float *s_score = reinterpret_cast<float *>(s_dyn + AX_STAGE_BYTES);       // [2][max_len]
     __shared__ unsigned long long s_tab[32];
     __shared__ float s_red[2][8];
     __shared__ float s_inv[2];
@@ -836,59 +904,77 @@ attention_decode_exact_kernel(const float *__restrict__ q, const uint16_t *__res
         return;
     }
     if (tid < 32) s_tab[tid] = c_exp2_tab32[tid];
-    const int hs = warp >> 3, th = tid & 255;             // head slot, thread within the head
-    const int h = blockIdx.x * 2 + hs;
-    const bool live = h < num_heads;
     const int group = num_heads / num_kv_heads;
     const size_t kv_dim = (size_t)num_kv_heads * HD;
-    const size_t head_off = (size_t)(live ? h / group : 0) * HD;
-    float *sc = s_score + (size_t)hs * max_len;
+    const int h0 = blockIdx.x * 2, h1 = min(h0 + 1, num_heads - 1);           // an odd head count repeats the last head
+    const size_t off0 = (size_t)(h0 / group) * HD, off1 = (size_t)(h1 / group) * HD;
+    const bool shared_kv = off0 == off1;
+    const int tile_pos = shared_kv ? 128 : 64;
+    const int n_tiles = (kv_len + tile_pos - 1) / tile_pos;
 
     // pass 1: scores.  Half-warp (16 lanes) per position, lane l owns dims 16 i + l.
-    if (live) {
-        const int l16 = lane & 15, hw = (th >> 4);        // 16 half-warps per head
-        // the two halves of a warp run different trip counts: shuffles name the own half only
+    {
+        const int l16 = lane & 15, hw = tid >> 4;                             // 32 half-warps
+        // the two halves of a warp can run different trip counts: shuffles name the own half only
         const unsigned hmask = (lane & 16) ? 0xffff0000u : 0x0000ffffu;
-        float qr[8];
+        // shared KV head: every half-warp serves both heads of its positions; else 16 half-warps per head
+        const int slot = shared_kv ? 0 : hw >> 4, p_first = shared_kv ? hw : hw & 15, p_step = shared_kv ? 32 : 16;
+        const int ha = shared_kv ? h0 : (slot ? h1 : h0), hb = shared_kv ? h1 : ha;
+        float qa[8], qb[8];
 #pragma unroll
-        for (int i = 0; i < 8; i++) qr[i] = q[(size_t)h * HD + 16 * i + l16];
-        for (int j0 = hw; j0 < kv_len; j0 += 32) {        // two positions in flight per half-warp
-            const int j1 = j0 + 16;
-            const uint16_t *r0 = k + (size_t)j0 * kv_dim + head_off + l16;
-            const uint16_t *r1 = k + (size_t)(j1 < kv_len ? j1 : j0) * kv_dim + head_off + l16;
-            uint16_t a[8], b[8];
+        for (int i = 0; i < 8; i++) {
+            qa[i] = q[(size_t)ha * HD + 16 * i + l16];
+            qb[i] = q[(size_t)hb * HD + 16 * i + l16];
+        }
+        AxTile t;
+        ax_fetch(t, k, kv_dim, off0, off1, shared_kv, 0, kv_len, tid);
+        for (int ti = 0; ti < n_tiles; ti++) {
+            const int pos0 = ti * tile_pos, n_here = min(tile_pos, kv_len - pos0);
+            __syncthreads();
+            ax_store(t, stage, tid);
+            __syncthreads();
+            if (ti + 1 < n_tiles) ax_fetch(t, k, kv_dim, off0, off1, shared_kv, pos0 + tile_pos, kv_len, tid);
+            for (int p = p_first; p < n_here; p += p_step) {
+                const uint16_t *row = stage + ((size_t)slot * 64 + p) * HD + l16;
+                float acc0 = 0.0f, acc1 = 0.0f;
 #pragma unroll
-            for (int i = 0; i < 8; i++) {
-                a[i] = r0[16 * i];
-                b[i] = r1[16 * i];
-            }
-            float acc0 = 0.0f, acc1 = 0.0f;
+                for (int i = 0; i < 8; i++) {
+                    const float kf = __half2float(__ushort_as_half(row[16 * i]));
+                    acc0 = __fadd_rn(acc0, __fmul_rn(qa[i], kf));
+                    acc1 = __fadd_rn(acc1, __fmul_rn(qb[i], kf));
+                }
+                // lanes l and l + 8 are the reference's two accumulators; then lo + hi, movehdup, movehl
 #pragma unroll
-            for (int i = 0; i < 8; i++) {
-                acc0 = __fadd_rn(acc0, __fmul_rn(qr[i], __half2float(__ushort_as_half(a[i]))));
-                acc1 = __fadd_rn(acc1, __fmul_rn(qr[i], __half2float(__ushort_as_half(b[i]))));
-            }
-            // lanes l and l + 8 are the reference's two accumulators; then lo + hi, movehdup, movehl
-#pragma unroll
-            for (int o = 8; o >= 4; o >>= 1) {
-                acc0 = __fadd_rn(acc0, __shfl_xor_sync(hmask, acc0, o));
-                acc1 = __fadd_rn(acc1, __shfl_xor_sync(hmask, acc1, o));
-            }
-            acc0 = __fadd_rn(acc0, __shfl_xor_sync(hmask, acc0, 1));
-            acc1 = __fadd_rn(acc1, __shfl_xor_sync(hmask, acc1, 1));
-            acc0 = __fadd_rn(acc0, __shfl_xor_sync(hmask, acc0, 2));
-            acc1 = __fadd_rn(acc1, __shfl_xor_sync(hmask, acc1, 2));
-            if (l16 == 0) {
-                sc[j0] = __fmul_rn(acc0, scale);
-                if (j1 < kv_len) sc[j1] = __fmul_rn(acc1, scale);
+                for (int o = 8; o >= 4; o >>= 1) {
+                    acc0 = __fadd_rn(acc0, __shfl_xor_sync(hmask, acc0, o));
+                    acc1 = __fadd_rn(acc1, __shfl_xor_sync(hmask, acc1, o));
+                }
+                acc0 = __fadd_rn(acc0, __shfl_xor_sync(hmask, acc0, 1));
+                acc1 = __fadd_rn(acc1, __shfl_xor_sync(hmask, acc1, 1));
+                acc0 = __fadd_rn(acc0, __shfl_xor_sync(hmask, acc0, 2));
+                acc1 = __fadd_rn(acc1, __shfl_xor_sync(hmask, acc1, 2));
+                if (l16 == 0) {
+                    if (shared_kv) {
+                        s_score[pos0 + p] = __fmul_rn(acc0, scale);
+                        s_score[max_len + pos0 + p] = __fmul_rn(acc1, scale);
+                    } else {
+                        s_score[(size_t)slot * max_len + pos0 + p] = __fmul_rn(acc0, scale);
+                    }
+                }
             }
         }
     }
     __syncthreads();
+    const int hs = warp >> 3, th = tid & 255;                                 // head slot, thread within the head
+    const int h = h0 + hs;
+    const bool live = h < num_heads;
+    float *sc = s_score + (size_t)hs * max_len;
+    // V rows of the first tile travel while the softmax runs
+    AxTile tv;
+    ax_fetch(tv, v, kv_dim, off0, off1, shared_kv, 0, kv_len, tid);
     // pass 2: max
     float m = -INFINITY;
-    if (live)
-        for (int j = th; j < kv_len; j += 256) m = fmaxf(m, sc[j]);
+    for (int j = th; j < kv_len; j += 256) m = fmaxf(m, sc[j]);
     m = warp_max(m);
     if (lane == 0) s_red[hs][warp & 7] = m;
     __syncthreads();
@@ -896,42 +982,55 @@ attention_decode_exact_kernel(const float *__restrict__ q, const uint16_t *__res
 #pragma unroll
     for (int i = 1; i < 8; i++) M = fmaxf(M, s_red[hs][i]);
     // pass 3: exponentials in parallel, their sum in position order by one thread per head
-    if (live)
-        for (int j = th; j < kv_len; j += 256) sc[j] = expf_libm(__fsub_rn(sc[j], M), s_tab);
+    for (int j = th; j < kv_len; j += 256) sc[j] = expf_libm(__fsub_rn(sc[j], M), s_tab);
     __syncthreads();
-    if (live && th == 0) {
+    if (th == 0) {
         float sum = 0.0f;
         int j = 0;
-        for (; j + 4 <= kv_len; j += 4) {
-            const float4 p = *reinterpret_cast<const float4 *>(sc + j);
-            sum = __fadd_rn(__fadd_rn(__fadd_rn(__fadd_rn(sum, p.x), p.y), p.z), p.w);
+        for (; j + 32 <= kv_len; j += 32) {
+            float4 p[8];
+#pragma unroll
+            for (int u = 0; u < 8; u++) p[u] = *reinterpret_cast<const float4 *>(sc + j + 4 * u);
+#pragma unroll
+            for (int u = 0; u < 8; u++) sum = __fadd_rn(__fadd_rn(__fadd_rn(__fadd_rn(sum, p[u].x), p[u].y), p[u].z), p[u].w);
         }
         for (; j < kv_len; j++) sum = __fadd_rn(sum, sc[j]);
         s_inv[hs] = sum > 0.0f ? __fdiv_rn(1.0f, sum) : 0.0f;
     }
     __syncthreads();
     // pass 4: weights in parallel, then one thread per output dim walks the positions in order
-    if (live) {
+    {
         const float inv = s_inv[hs];
         for (int j = th; j < kv_len; j += 256) sc[j] = __fmul_rn(sc[j], inv);
     }
-    __syncthreads();
-    if (th < HD) {
-        float o = 0.0f;
-        if (live) {
-            const uint16_t *vp = v + head_off + th;
-            int j = 0;
-            for (; j + 8 <= kv_len; j += 8) {
-                uint16_t x[8];
+    float o = 0.0f;
+    const int v_slot = shared_kv ? 0 : hs;
+    for (int ti = 0; ti < n_tiles; ti++) {
+        const int pos0 = ti * tile_pos, n_here = min(tile_pos, kv_len - pos0);
+        __syncthreads();                                                      // weights written / previous tile consumed
+        ax_store(tv, stage, tid);
+        __syncthreads();
+        if (ti + 1 < n_tiles) ax_fetch(tv, v, kv_dim, off0, off1, shared_kv, pos0 + tile_pos, kv_len, tid);
+        if (th < HD) {
+            const uint16_t *col = stage + (size_t)v_slot * 64 * HD + th;
+            const float *w = sc + pos0;
+            int p = 0;
+            for (; p + 8 <= n_here; p += 8) {
+                float x[8], wt[8];
 #pragma unroll
-                for (int u = 0; u < 8; u++) x[u] = vp[(size_t)(j + u) * kv_dim];
+                for (int u = 0; u < 8; u++) {
+                    x[u] = __half2float(__ushort_as_half(col[(size_t)(p + u) * HD]));
+                    wt[u] = w[p + u];
+                }
 #pragma unroll
-                for (int u = 0; u < 8; u++) o = __fadd_rn(o, __fmul_rn(__half2float(__ushort_as_half(x[u])), sc[j + u]));
+                for (int u = 0; u < 8; u++) o = __fadd_rn(o, __fmul_rn(x[u], wt[u]));
             }
-            for (; j < kv_len; j++) o = __fadd_rn(o, __fmul_rn(__half2float(__ushort_as_half(vp[(size_t)j * kv_dim])), sc[j]));
-            if (out) out[(size_t)h * HD + th] = o;
+            for (; p < n_here; p++) o = __fadd_rn(o, __fmul_rn(__half2float(__ushort_as_half(col[(size_t)p * HD])), w[p]));
         }
-        s_o[hs * HD + th] = o;
+    }
+    if (th < HD) {
+        if (live && out) out[(size_t)h * HD + th] = o;
+        s_o[hs * HD + th] = live ? o : 0.0f;
     }
     if (!xq_out) return;
     __syncthreads();

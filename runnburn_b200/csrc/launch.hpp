@@ -47,6 +47,28 @@ inline cudaError_t launch_k(void (*kernel)(KArgs...), dim3 grid, dim3 block, siz
     return e;
 }
 
+// The same launch as one thread-block cluster per grid column: cluster dimensions (1, cluster_y, 1).
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_k_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, unsigned cluster_y, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = cluster_y;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = use_pdl() ? 2 : 1;
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+    if (e == cudaSuccess) launch_count()++;
+    return e;
+}
+
 constexpr size_t GEMV_SMEM_LIMIT = 200 * 1024;
 
 // Rows per tile: tiles are whole rows, their byte size must be a multiple of 16 for the bulk
@@ -484,6 +506,36 @@ inline int flash_decode_default_chunks(size_t kv_len, size_t num_kv_heads, int s
 inline size_t flash_decode_scratch_bytes(size_t num_heads, int n_chunks) {
     return num_heads * (size_t)n_chunks * FD_PART_STRIDE * sizeof(float);
 }
+// Chunks per KV head when the attention kernel is launched as thread-block clusters that merge their
+// own chunks (RNB_B200_ATTN_CLUSTER = 2..16; sixteen needs the non-portable cluster size opt-in), 0 if
+// off or not schedulable.  Off by default: a cluster is at most 16 CTAs per KV head, and the Llama-3-8B
+// shape at context 4096 wants about 74 (measured 2.52 ms per token with clusters of 16 against 2.24 ms
+// with 74 chunks and a merge launch).
+inline int flash_decode_cluster_size() {
+    static const int v = [] {
+        const char *e = getenv("RNB_B200_ATTN_CLUSTER");
+        const int want = e && *e ? atoi(e) : 0;
+        if (want < 2) return 0;
+        if (cudaFuncSetAttribute(flash_decode_mma_kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) != cudaSuccess) cudaGetLastError();
+        for (int c = want > 16 ? 16 : want; c >= 2; c /= 2) {
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = dim3(1, c);
+            cfg.blockDim = dim3(FDM_THREADS);
+            cudaLaunchAttribute attr[1];
+            attr[0].id = cudaLaunchAttributeClusterDimension;
+            attr[0].val.clusterDim.x = 1;
+            attr[0].val.clusterDim.y = c;
+            attr[0].val.clusterDim.z = 1;
+            cfg.attrs = attr;
+            cfg.numAttrs = 1;
+            int n = 0;
+            if (cudaOccupancyMaxActiveClusters(&n, flash_decode_mma_kernel, &cfg) == cudaSuccess && n > 0) return c;
+            cudaGetLastError();
+        }
+        return 0;
+    }();
+    return v;
+}
 // Partial records of every (head, chunk).  f16 caches on 16-byte boundaries take the
 // tensor-core kernel (its bulk copies need that alignment); anything else the CUDA-core one.
 inline bool flash_decode_force_simt() {
@@ -502,8 +554,17 @@ inline int launch_flash_decode_partials(cudaStream_t s, const float *q, const ui
     const bool aligned = (((uintptr_t)k | (uintptr_t)v) & 15) == 0;
     if (merged) *merged = false;
     if (aligned && !flash_decode_force_simt()) {
-        FdMerge m{nullptr, nullptr, nullptr};
+        FdMerge m{nullptr, nullptr, nullptr, 0};
         const int group = num_kv_heads ? num_heads / num_kv_heads : 0;
+        if (merge && merge->cluster > 0 && merge->cluster == n_chunks && 2 * n_chunks >= group && (!merge->xq_out || group % 2 == 0)) {
+            // one cluster per KV head: its CTAs merge the chunks after a cluster barrier, no merge launch
+            m = *merge;
+            m.counters = nullptr;
+            if (merged) *merged = true;
+            RNB_CU(launch_k_cluster(flash_decode_mma_kernel, dim3(num_kv_heads, n_chunks), dim3(FDM_THREADS), 0, s, (unsigned)n_chunks, q, k, v, kv_len_dev,
+                                    kv_len_host, num_heads, num_kv_heads, scale, partials, dev_error, m));
+            return RNB_B200_OK;
+        }
         if (merge && merge->counters && n_chunks <= FD_MAX_CHUNKS && (!merge->xq_out || group % 2 == 0)) {
             m = *merge;
             if (merged) *merged = true;
@@ -528,17 +589,26 @@ inline int launch_flash_decode(cudaStream_t s, const float *q, const uint16_t *k
 }
 
 // Longest context the reference-order attention kernel serves (RNB_B200_EXACT_ATTN_MAX, default
-// 1024, 0 turns it off): up to there decode attention is bit-identical to rnb-cpu's; beyond it the
+// 512, at most 4096, 0 turns it off): up to there decode attention is bit-identical to rnb-cpu's; beyond it the
 // chunked tensor-core kernel takes over, whose sums are reassociated.
 inline int exact_attention_max() {
     static const int v = [] {
         const char *e = getenv("RNB_B200_EXACT_ATTN_MAX");
-        long n = e && *e ? strtol(e, nullptr, 10) : 1024;
+        long n = e && *e ? strtol(e, nullptr, 10) : 512;
         if (n < 0) n = 0;
         if (n > AX_MAX_LEN) n = AX_MAX_LEN;
         return (int)((n + 3) & ~3L);
     }();
     return v;
+}
+// raises the kernel's dynamic shared-memory limit once (not a stream operation: call it before a capture)
+inline int attention_exact_setup() {
+    static bool done = false;
+    if (!done) {
+        RNB_CU(cudaFuncSetAttribute(attention_decode_exact_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ax_smem_bytes(AX_MAX_LEN)));
+        done = true;
+    }
+    return RNB_B200_OK;
 }
 // kv_len = (*kv_len_dev if given) + kv_len_host must not exceed max_len (the kernel raises the error flag otherwise)
 inline int launch_attention_decode_exact(cudaStream_t s, const float *q, const uint16_t *k, const uint16_t *v, const int *kv_len_dev,
@@ -546,7 +616,9 @@ inline int launch_attention_decode_exact(cudaStream_t s, const float *q, const u
                                          uint8_t *xq_out, int *dev_error) {
     if (max_len < 4 || max_len > AX_MAX_LEN || max_len % 4) return fail(RNB_B200_VALIDATION_FAILED, "exact attention: max_len %d must be a multiple of 4 in 4..%d", max_len, AX_MAX_LEN);
     if (xq_out && num_heads % 2) return fail(RNB_B200_VALIDATION_FAILED, "exact attention: Q8_K output needs an even head count");
-    RNB_CU(launch_k(attention_decode_exact_kernel, dim3((num_heads + 1) / 2), dim3(AX_THREADS), (size_t)max_len * 2 * sizeof(float), s, q, k, v,
+    if (((uintptr_t)k | (uintptr_t)v) & 15u) return fail(RNB_B200_VALIDATION_FAILED, "exact attention: K and V must be 16-byte aligned");
+    RNB_TRY(attention_exact_setup());
+    RNB_CU(launch_k(attention_decode_exact_kernel, dim3((num_heads + 1) / 2), dim3(AX_THREADS), ax_smem_bytes(max_len), s, q, k, v,
                     kv_len_dev, kv_len_host, max_len, num_heads, num_kv_heads, scale, out, xq_out, dev_error));
     return RNB_B200_OK;
 }
@@ -554,7 +626,7 @@ inline int launch_attention_decode_exact(cudaStream_t s, const float *q, const u
 // contexts, chunked kernel + merge otherwise.
 inline int launch_attention_decode(cudaStream_t s, const float *q, const uint16_t *k, const uint16_t *v, int kv_len, int num_heads,
                                    int num_kv_heads, float scale, float *partials, int n_chunks, float *out, int *dev_error) {
-    if (kv_len <= exact_attention_max())
+    if (kv_len <= exact_attention_max() && ((((uintptr_t)k | (uintptr_t)v) & 15u) == 0))
         return launch_attention_decode_exact(s, q, k, v, nullptr, kv_len, (kv_len + 3) & ~3, num_heads, num_kv_heads, scale, out, nullptr, dev_error);
     return launch_flash_decode(s, q, k, v, nullptr, kv_len, num_heads, num_kv_heads, scale, partials, n_chunks, out, dev_error);
 }

@@ -22,7 +22,7 @@ def _run(desc, prompt, n_steps, max_ctx, exact_attention=True):
 
 # Two parity statements, one per attention kernel.
 #
-# Contexts up to the decoder's exact-attention limit (default 1024 positions) run the
+# Contexts up to the decoder's exact-attention limit (default 512 positions) run the
 # reference-order attention kernel; with it every operation of a decode step repeats the CPU's
 # arithmetic in the CPU's order, and the test demands IDENTICAL bits: logits, K/V rows, ids.
 #

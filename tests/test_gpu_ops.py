@@ -197,7 +197,7 @@ def test_resident_cache_counters_and_eviction(ops):
 # ---- attention ----------------------------------------------------------------------------------
 @pytest.mark.parametrize("heads,kvh,kv_len", [(32, 8, 1), (32, 8, 7), (32, 8, 333), (32, 8, 4096), (32, 4, 1025),
                                               (64, 8, 2000), (8, 8, 65), (6, 2, 100), (32, 2, 300), (16, 8, 20000), (24, 2, 17),
-                                              (5, 5, 9), (7, 1, 1000), (32, 8, 1023), (32, 8, 1024), (3, 1, 2),
+                                              (5, 5, 9), (7, 1, 500), (32, 8, 511), (32, 8, 512), (3, 1, 2),
                                               # the headline configurations' own shapes: MoE at 8192, a 70B 8-GPU shard and the whole 70B at 32768
                                               (32, 4, 8192), (8, 1, 32768), (64, 8, 32768)])
 def test_attention_decode_hd128(ops, heads, kvh, kv_len):
@@ -208,7 +208,7 @@ def test_attention_decode_hd128(ops, heads, kvh, kv_len):
     scale = 1.0 / np.sqrt(128.0)
     ref = orc.attention_decode(q, k, v, heads, kvh, 128, kv_len, scale)
     got = ops.attention_decode_hd128(q, k, v, kv_len, heads, kvh, scale)
-    if kv_len <= 1024:
+    if kv_len <= 512:
         # the reference-order kernel serves these: same operations in the same order as the CPU
         assert np.array_equal(got, ref), f"not bit-identical: {np.max(np.abs(got - ref)):.3e}"
     elif kv_len <= 4096:
@@ -233,7 +233,10 @@ def test_attention_decode_cached_appends_only_new_rows(ops):
         q = rng.standard_normal(heads * 128).astype(np.float32)
         got = ops.attention_decode_cached(3, q, k, v, kv_len, heads, kvh, 128, scale)
         ref = orc.attention_decode(q, k, v, heads, kvh, 128, kv_len, scale)
-        assert np.array_equal(got, ref)
+        if kv_len <= 512:
+            assert np.array_equal(got, ref)
+        else:
+            assert max_rel_err(got, ref) <= TOL
     moved = ops.cuda_cache_snapshot()["h2d_bytes"] - before
     assert moved == 2 * 600 * kvh * 128 * 2 + 6 * heads * 128 * 4   # each KV row crossed PCIe once
     ops.clear_decode_attention_kv_cache()
