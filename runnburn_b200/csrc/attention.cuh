@@ -657,7 +657,7 @@ prefill_attention_mma_kernel(const float *__restrict__ q, const uint16_t *__rest
 // sharded onto one GPU of eight has hundreds of chunks: a serial walk would take tens of us.
 RNB_GLOBAL void __launch_bounds__(4 * HD)
 flash_decode_reduce_kernel(const float *__restrict__ partials, int n_chunks,
-                           float *__restrict__ out) {
+                           float *__restrict__ out, const PeerOut po = PeerOut{}) {
     pdl_launch_dependents();
     pdl_wait();
     __shared__ float s_f[FD_MAX_CHUNKS];
@@ -695,7 +695,17 @@ flash_decode_reduce_kernel(const float *__restrict__ partials, int n_chunks,
     __syncthreads();
     if (g == 0) {
         const float t = (s_part[0][d] + s_part[1][d]) + (s_part[2][d] + s_part[3][d]);
-        out[(size_t)h * HD + d] = L > 0.f ? t / L : 0.f;
+        const float o = L > 0.f ? t / L : 0.f;
+        out[(size_t)h * HD + d] = o;
+        if (po.peers) {
+            // sharded decode: the head's row also goes straight into every peer's gathered buffer
+            peer_store(po, (size_t)h * HD + d, o);
+            __threadfence_system();
+        }
+    }
+    if (po.peers) {
+        __syncthreads();
+        if (tid == 0) peer_arrive(po);
     }
 }
 

@@ -134,6 +134,67 @@ __device__ __forceinline__ float warp_max(float v) {
     return v;
 }
 
+// ---- multi-GPU: a producer's epilogue stores its slice of a gathered f32 buffer straight into
+// every peer's copy (plain peer stores over NVLink; the buffers sit at the same offset of each
+// rank's IPC-mapped arena), and the consumer waits for the other ranks' slices in its prologue.
+// Flags: one int per (exchange, source rank) on every GPU, raised to the step's sequence number
+// by the producer's last CTA after all of its CTAs' stores are visible system-wide.
+struct PeerOut {
+    char *const *peers;    // device array [world] of arena bases, own included; null: off
+    int world, rank;
+    size_t buf_off;        // byte offset of the gathered buffer in an arena
+    int count;             // f32 elements per rank slice
+    size_t flag_off;       // byte offset of this exchange's flag row (ints indexed by source rank)
+    const int *seq_ptr;    // device scalar: sequence number of this step
+    int *arrivals;         // local counter of CTAs done, zero between launches
+    int n_arrive;          // CTAs that will call peer_arrive
+};
+struct PeerWait {
+    const int *flags;      // this GPU's flag row of the exchange; null: off
+    int world, rank;
+    const int *seq_ptr;
+    int *err;
+};
+// element `idx` of this rank's slice into every other rank's buffer (the own copy is the caller's)
+__device__ __forceinline__ void peer_store(const PeerOut &po, size_t idx, float v) {
+    for (int p = 1; p < po.world; p++) {
+        const int r = (po.rank + p) % po.world;
+        reinterpret_cast<float *>(po.peers[r] + po.buf_off)[(size_t)po.rank * po.count + idx] = v;
+    }
+}
+// Once per CTA, by ONE thread, after every storing thread of the CTA has run
+// __threadfence_system() and the CTA (or warp) has synchronised.
+__device__ __forceinline__ void peer_arrive(const PeerOut &po) {
+    const int before = atomicAdd(po.arrivals, 1);
+    if (before != po.n_arrive - 1) return;
+    *po.arrivals = 0;
+    __threadfence_system();   // the other CTAs' stores, observed through the counter, before the flags
+    const int seq = *po.seq_ptr;
+    for (int p = 1; p < po.world; p++) {
+        const int r = (po.rank + p) % po.world;
+        int *theirs = reinterpret_cast<int *>(po.peers[r] + po.flag_off) + po.rank;
+        asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(theirs), "r"(seq) : "memory");
+    }
+}
+// All threads of the CTA call it (it synchronises the CTA): thread t < world waits, bounded, for
+// rank t's flag.  After a timeout the error word is set and later waits return at once.
+__device__ __forceinline__ void peer_wait(const PeerWait &w) {
+    if (!w.flags) return;
+    const int t = threadIdx.x;
+    if (t < w.world && t != w.rank && *reinterpret_cast<volatile int *>(w.err) == 0) {
+        const int seq = *w.seq_ptr;
+        bool ok = false;
+        for (uint32_t i = 0; i < (1u << 21) && !ok; i++) {
+            int v;
+            asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(w.flags + t) : "memory");
+            ok = v >= seq;
+            if (!ok && i > 32) __nanosleep(i > 2048 ? 512 : 64);
+        }
+        if (!ok) atomicExch(w.err, DEV_ERR_PEER_TIMEOUT);
+    }
+    __syncthreads();
+}
+
 #endif  // __CUDACC__
 
 }  // namespace rnb

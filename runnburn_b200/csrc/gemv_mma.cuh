@@ -640,7 +640,10 @@ __device__ __forceinline__ void gemv_mma_body(const GemvJob *__restrict__ jobs, 
                 acc_total = 0.f;
                 const int epi = job.epi;
                 if (epi == GEMV_EPI_NONE) {
-                    if (live) job.y[o] = val;
+                    if (live) {
+                        job.y[o] = val;
+                        if (tail.kind == 2) peer_store(tail.peer, o, val);
+                    }
                 } else {
                     // q/k/v: adjacent-pair RoPE and/or the f16 KV append on the rows just produced; rows 2i and
                     // 2i+1 sit two lanes apart
@@ -681,12 +684,19 @@ __device__ __forceinline__ void gemv_mma_body(const GemvJob *__restrict__ jobs, 
         s_abort = 1;
         atomicExch(dev_error, DEV_ERR_MBAR_TIMEOUT);
     }
+    if (tail.kind == 2 && !failed) {
+        // every CTA of the grid arrives once, with or without tiles; the last raises the peers' flags
+        __threadfence_system();
+        __syncwarp();
+        if (lane == 0) peer_arrive(tail.peer);
+    }
 }
 
 RNB_GLOBAL void __launch_bounds__(GM_THREADS, GM_MIN_CTAS)
 gemv_mma_kernel(const GemvJob *__restrict__ jobs, int n_jobs, const GmParams P, int *__restrict__ dev_error) {
     GpTail none;
     none.kind = 0;
+    none.peer.peers = nullptr;
     gemv_mma_body(jobs, n_jobs, P, dev_error, none, nullptr);
 }
 RNB_GLOBAL void __launch_bounds__(GM_THREADS, GM_MIN_CTAS)

@@ -34,11 +34,12 @@ struct GpParams {
 // the work of silu_mul_q8k_kernel, spread over the blocks as they finish, without a launch.
 // counters[block] is zero before the launch and re-armed by the block's last CTA.
 struct GpTail {
-    int kind;            // 0 = none, 1 = SiLU * up + Q8_K
+    int kind;            // 0 = none, 1 = SiLU * up + Q8_K, 2 = peer publish (integer-MMA kernel, one plain job)
     int n;               // length of the gate / up vectors (multiple of 256)
     const float *gate, *up;
     uint8_t *xq_out;     // Q8K-dev layout of the n-vector
     int *counters;       // n / 256 ints
+    PeerOut peer;        // kind 2: where the finished rows also go
 };
 
 struct Q4kPairAcc {

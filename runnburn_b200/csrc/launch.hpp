@@ -308,6 +308,12 @@ inline int try_launch_gemv_mma(cudaStream_t s, const GemvJob *jobs_host, const G
         t = *tail;
         if (tail_done) *tail_done = true;
     }
+    // kind 2: the rows of a single plain job also go to every peer's gathered buffer (sharded decode)
+    if (tail && tail->kind == 2 && !dynamic_table && n_jobs == 1 && jobs_host[0].epi == GEMV_EPI_NONE && n_jobs <= GS_PACK) {
+        t = *tail;
+        t.peer.n_arrive = grid;
+        if (tail_done) *tail_done = true;
+    }
     if ((by_value || !dynamic_table) && n_jobs <= GS_PACK) {
         GemvJobPack pack;
         memset(&pack, 0, sizeof(pack));
@@ -584,7 +590,7 @@ inline int launch_flash_decode(cudaStream_t s, const float *q, const uint16_t *k
     RNB_TRY(launch_flash_decode_partials(s, q, k, v, kv_len_dev, kv_len_host, num_heads, num_kv_heads, scale, partials,
                                          n_chunks, dev_error));
     RNB_CU(launch_k(flash_decode_reduce_kernel, dim3(num_heads), dim3(4 * HD), 0, s,
-                    (const float *)partials, n_chunks, out));
+                    (const float *)partials, n_chunks, out, PeerOut{}));
     return RNB_B200_OK;
 }
 

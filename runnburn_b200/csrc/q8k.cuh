@@ -162,12 +162,13 @@ rmsnorm_q8k_kernel(const float *__restrict__ x, const float *__restrict__ w, flo
 // in dependent latency; this form is a single round of loads, one reduction and one block.
 RNB_GLOBAL void __launch_bounds__(128)
 rmsnorm_q8k_blocks_kernel(const float *__restrict__ x, const float *__restrict__ w, float eps, int hidden,
-                          float *__restrict__ h_out, uint8_t *__restrict__ xq_out) {
+                          float *__restrict__ h_out, uint8_t *__restrict__ xq_out, const PeerWait pw = PeerWait{}) {
     pdl_launch_dependents();
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, b = blockIdx.x;
     // the norm weights do not depend on the previous kernel
     const float4 w0 = __ldg(reinterpret_cast<const float4 *>(w + b * 256 + lane * 8)), w1 = __ldg(reinterpret_cast<const float4 *>(w + b * 256 + lane * 8 + 4));
     pdl_wait();
+    peer_wait(pw);   // sharded decode: the other ranks' slices of x arrive by peer stores
     __shared__ double red[4];
     double ss = 0.0;
     for (int i = tid * 4; i < hidden; i += 128 * 4) {

@@ -41,24 +41,37 @@ WORKER = textwrap.dedent("""
     ref = orc.Model(desc, 64)
     rng = np.random.default_rng(0)
     prompt = rng.integers(0, 2048, 8).tolist()
-    pos, tg, tc = 0, None, None
-    for t in prompt:
+    exact = os.environ.get("RNB_B200_EXACT_ATTN_MAX", "512") != "0"
+    pos, tc = 0, None
+    got, want, margins = [], [], []
+    for i in range(len(prompt) + 24):
+        t = prompt[i] if i < len(prompt) else tc          # both sides consume the oracle's token
         tg = dec.step(t, pos)
-        tc = orc.argmax_last(ref.decode(t, pos))
-        pos += 1
-    got, want = [], []
-    for _ in range(24):
+        lc = ref.decode(t, pos)
+        tc = orc.argmax_last(lc)
+        top2 = np.partition(lc, -2)[-2:]
         got.append(tg); want.append(tc)
-        tg = dec.step(tg, pos)
-        tc = orc.argmax_last(ref.decode(tc, pos))
+        margins.append(float(top2[1] - top2[0]) / float(np.max(np.abs(lc))))
         pos += 1
-    assert got == want, (rank, got, want)
+    if exact:
+        # contexts this short run the reference-order attention kernel: the sharded step is bit-identical
+        assert got == want, (rank, got, want)
+    else:
+        # chunked attention kernel: ids may part from the oracle's only at near-ties of its logits
+        bad = [(i, g, w, m) for i, (g, w, m) in enumerate(zip(got, want, margins)) if g != w and m > 1e-2]
+        assert not bad and sum(g != w for g, w in zip(got, want)) <= 2, (rank, bad, got, want)
+    every = [None] * world
+    dist.all_gather_object(every, got)
+    assert all(e == every[0] for e in every), "ranks disagree on the greedy ids"
     # each rank holds its own KV heads only
     k, v = dec.read_kv(0, pos)
     kc, vc = ref.kv_cache(0, pos)
     kv_l = desc["cfg"]["n_kv_head"] // world * 128
     kc = kc.reshape(pos, -1)[:, rank * kv_l:(rank + 1) * kv_l]
-    assert np.mean(k.reshape(pos, -1) == kc) > 0.999
+    if exact:
+        assert np.array_equal(k.reshape(pos, -1), kc)
+    else:
+        assert np.mean(k.reshape(pos, -1) == kc) > 0.995
     dec.close(); ref.close()
     dist.barrier()
     dist.destroy_process_group()
@@ -67,7 +80,10 @@ WORKER = textwrap.dedent("""
 """)
 
 
-@pytest.mark.parametrize("transport", ["peer", "peer-ll", "nccl"])
+# fused: producers store their slices into the peers' buffers, consumers wait in their prologue (no
+# exchange launches); fused-chunked: the same with the reference-order attention kernel off, so the
+# chunk-merge kernel publishes too; peer / peer-ll: separate exchange kernels; nccl: ncclAllGather
+@pytest.mark.parametrize("transport", ["fused", "fused-chunked", "peer", "peer-ll", "nccl"])
 def test_two_gpu_row_sharded_greedy_ids(tmp_path, transport):
     import torch
     if torch.cuda.device_count() < 2:
@@ -75,7 +91,9 @@ def test_two_gpu_row_sharded_greedy_ids(tmp_path, transport):
     script = tmp_path / "worker.py"
     script.write_text(WORKER % (str(ROOT), str(ROOT / "tests")))
     env = dict(os.environ, MASTER_ADDR="127.0.0.1", RNB_TEST_TRANSPORT="nccl" if transport == "nccl" else "peer",
-               RNB_B200_PEER_LL="1" if transport == "peer-ll" else "0")
+               RNB_B200_PEER_LL="1" if transport == "peer-ll" else "0",
+               RNB_B200_PEER_FUSED="1" if transport.startswith("fused") else "0",
+               RNB_B200_EXACT_ATTN_MAX="0" if transport == "fused-chunked" else "512")
     r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
                         "--master-addr", "127.0.0.1", "--master-port", "29741", str(script)],
                        capture_output=True, text=True, env=env, timeout=600)
