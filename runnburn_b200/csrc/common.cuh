@@ -168,12 +168,14 @@ __device__ __forceinline__ void peer_arrive(const PeerOut &po) {
     const int before = atomicAdd(po.arrivals, 1);
     if (before != po.n_arrive - 1) return;
     *po.arrivals = 0;
-    __threadfence_system();   // the other CTAs' stores, observed through the counter, before the flags
+    // one system-scope fence orders the other CTAs' stores (observed through the counter) before all
+    // the flags; a release store per peer would each wait for the previous flag's round trip
+    __threadfence_system();
     const int seq = *po.seq_ptr;
     for (int p = 1; p < po.world; p++) {
         const int r = (po.rank + p) % po.world;
         int *theirs = reinterpret_cast<int *>(po.peers[r] + po.flag_off) + po.rank;
-        asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(theirs), "r"(seq) : "memory");
+        asm volatile("st.relaxed.sys.global.s32 [%0], %1;" ::"l"(theirs), "r"(seq) : "memory");
     }
 }
 // All threads of the CTA call it (it synchronises the CTA): thread t < world waits, bounded, for
