@@ -286,6 +286,89 @@ uint64_t rnb_b200_qwen35_moe_transient_reserve_bytes(uint64_t dynamic_reserve_by
  * resident_limit = free - reserve, reserve = clamp(ceil_256MiB(total/16), 512 MiB, 2 GiB) */
 uint64_t rnb_b200_resident_limit_for(uint64_t total_bytes, uint64_t free_bytes);
 
+/* ---- the rest of the operator boundary ---------------------------------------------------------
+ * add_f32_inplace(dst, src) — api/dense_api.rs:1389 (same messages: shape mismatch, u32 overflow) */
+int rnb_b200_add_f32_inplace(float *dst, size_t dst_len, const float *src, size_t src_len);
+/* upload_device_tensor_f32(desc, input) -> DeviceTensorId, download_device_tensor_f32(id),
+ * download_device_tensor_f32_row(id, row), release_device_tensor(id) -> bool —
+ * api/sequence_api.rs:4-56; DeviceTensorDesc{rows, cols, dtype f32, role} and DeviceTensorId{backend,
+ * raw} of crates/rnb-backend/api/src/lib.rs:132-203: `id` is the raw handle, `role` the
+ * DeviceTensorRole discriminant (kept, not interpreted).  device_tensor_ptr exposes the device
+ * address for calls that take `*_dev` arguments. */
+int rnb_b200_upload_device_tensor_f32(size_t rows, size_t cols, uint32_t role, const float *data, size_t len, uint64_t *id_out);
+int rnb_b200_download_device_tensor_f32(uint64_t id, float *out, size_t out_len);
+int rnb_b200_download_device_tensor_f32_row(uint64_t id, size_t row, float *out, size_t out_len);
+int rnb_b200_release_device_tensor(uint64_t id, int *released);
+int rnb_b200_device_tensor_ptr(uint64_t id, uint64_t *dev_ptr, size_t *rows, size_t *cols);
+/* acquire_decode_{hidden,norm_buf,k,v,k_f16,v_f16,attn_out}_carrier(bytes) -> u64,
+ * upload_to_decode_hidden_carrier(host, dev), download_from_decode_hidden_carrier(dev, host),
+ * sync_decode_stream() — api/dense_api.rs:1176-1330,2428.  One entry point with the carrier kind;
+ * uploads and downloads are asynchronous on the decode stream as the reference's are (the host buffer
+ * stays the caller's until rnb_b200_sync_decode_stream). */
+enum {
+    RNB_B200_CARRIER_HIDDEN = 0, RNB_B200_CARRIER_NORM_BUF = 1, RNB_B200_CARRIER_K = 2, RNB_B200_CARRIER_V = 3,
+    RNB_B200_CARRIER_K_F16 = 4, RNB_B200_CARRIER_V_F16 = 5, RNB_B200_CARRIER_ATTN_OUT = 6, RNB_B200_CARRIER_KINDS = 7
+};
+int rnb_b200_acquire_decode_carrier(uint32_t kind, size_t bytes, uint64_t *dev_out);
+int rnb_b200_upload_to_decode_carrier(const void *host, size_t bytes, uint64_t dev);
+int rnb_b200_download_from_decode_carrier(uint64_t dev, void *host, size_t bytes);
+int rnb_b200_sync_decode_stream(void);
+/* attention_decode_cached_to_device(layer_index, q, k, v, kv_len, num_heads, num_kv_heads, head_dim,
+ * scale, output_dev_target, last_token_k_dev: Option<u64>, last_token_v_dev, q_dev_override) —
+ * api/attention_api.rs:1776: the result stays at `output_dev` (f32 [heads][128]) and the call does
+ * not synchronise; 0 stands for None.  With last-token device rows the newest K/V row is copied
+ * device to device into the layer's mirror instead of uploaded. */
+int rnb_b200_attention_decode_cached_to_device(size_t layer, const float *q, size_t q_len, const uint16_t *k, const uint16_t *v, size_t kv_elems,
+                                               size_t kv_len, size_t heads, size_t kv_heads, size_t head_dim, float scale, uint64_t output_dev,
+                                               uint64_t last_token_k_dev, uint64_t last_token_v_dev, uint64_t q_dev_override);
+/* dense_q4k_attention_qkv_rope_hd128_prefill(.., seq_len, ..) — api/dense_api.rs:1075: input
+ * [seq][n_embd], q_rope [seq][q_rows], k_bits / v_bits [seq][kv_rows]; token s sits at position
+ * pos_start + s. */
+int rnb_b200_dense_attention_qkv_rope_hd128_prefill(const uint8_t *q_w, size_t q_w_len, uint32_t q_type, const uint8_t *k_w, size_t k_w_len,
+                                                    uint32_t k_type, const uint8_t *v_w, size_t v_w_len, uint32_t v_type, size_t q_rows,
+                                                    size_t kv_rows, size_t n_embd, size_t num_heads, size_t num_kv_heads, float rope_theta,
+                                                    size_t pos_start, size_t seq_len, const float *input, size_t input_len, float *q_rope,
+                                                    uint16_t *k_bits, uint16_t *v_bits);
+/* qwen35_sparse_experts_into / qwen35_sparse_experts_add_residual_into(gate, up, down, route_weights,
+ * layer_idx: Option<usize>, selected_expert_ids, receipt: &mut ExpertBundleObservationReceipt,
+ * down_quant, n_ff, n_embd, input, output | residual) — api/qwen_moe_api.rs:1918,2163.  layer_idx < 0
+ * is None.  Every selected bundle is looked up (full / partial / miss), observed in the reuse history
+ * and, on a miss, put to the admission test of sparse_expert_cache.rs:221-270; the stats delta of the
+ * call is recorded in `receipt` (may be null). */
+int rnb_b200_qwen35_sparse_experts_into(const uint8_t *const *gate, const uint8_t *const *up, const uint8_t *const *down, size_t gate_slice_len,
+                                        size_t down_slice_len, const float *route_weights, size_t n_selected, int64_t layer_idx,
+                                        const size_t *selected_expert_ids, rnb_b200_expert_bundle_receipt *receipt, uint32_t down_quant,
+                                        size_t n_ff, size_t n_embd, const float *input, float *output, size_t output_len);
+int rnb_b200_qwen35_sparse_experts_add_residual_into(const uint8_t *const *gate, const uint8_t *const *up, const uint8_t *const *down,
+                                                     size_t gate_slice_len, size_t down_slice_len, const float *route_weights, size_t n_selected,
+                                                     int64_t layer_idx, const size_t *selected_expert_ids, rnb_b200_expert_bundle_receipt *receipt,
+                                                     uint32_t down_quant, size_t n_ff, size_t n_embd, const float *input, float *residual_inout,
+                                                     size_t residual_len);
+/* running totals of the accounting above (ExpertBundleCacheStats) */
+int rnb_b200_qwen35_expert_cache_stats(rnb_b200_expert_bundle_stats *out);
+/* qwen35_configure_moe_layer_cache(model_moe_bytes, runtime_headroom_bytes, min_layer_bytes) -> usize
+ * — api/qwen_moe_api.rs:1483: the byte limit chosen for resident expert layers */
+int rnb_b200_qwen35_configure_moe_layer_cache(size_t model_moe_bytes, size_t runtime_headroom_bytes, size_t min_layer_bytes, size_t *limit_out);
+/* qwen35_admit_expert_misses_async — api/qwen_moe_api.rs:2082: uploads the given weight slices into
+ * the residency cache on the stream without synchronising and without evicting anything */
+int rnb_b200_qwen35_admit_expert_misses_async(const uint8_t *const *slices, const size_t *lens, size_t n, size_t *n_admitted);
+/* qwen35_prefill_device_topk_route_slots(router_w, n_expert, hidden_dim, norm_all, seq_len,
+ * n_expert_used) -> (ids, weights, token_ids) — api/qwen_moe_api.rs:1521: router matvec on the
+ * device, then the softmax top-k of moe_route_topk_f32; slot s * n_expert_used + j belongs to token s */
+int rnb_b200_qwen35_prefill_device_topk_route_slots(const float *router_w, size_t n_expert, size_t hidden_dim, const float *norm_all, size_t seq_len,
+                                                    size_t n_expert_used, uint32_t *ids_out, float *weights_out, uint32_t *token_ids_out);
+/* cuda_weight_residency_counters() -> CudaWeightResidencyCounters — api/cache_api.rs:97,
+ * runtime/types.rs:68-82.  This library keeps weights as raw GGUF quant bytes only, so the expanded
+ * f16 / f32 and packed fields are always 0. */
+typedef struct {
+    uint64_t expanded_diag_bytes, native_f32_bytes, packed_q8dot_bytes, raw_quant_bytes, transient_quant_upload_bytes;
+    uint64_t q4_expanded_f16_bytes, q4_expanded_f32_bytes, q6_expanded_f16_bytes, q6_expanded_f32_bytes;
+    uint64_t q4_raw_quant_bytes, q6_raw_quant_bytes, q4_transient_quant_upload_bytes, q6_transient_quant_upload_bytes;
+} rnb_b200_weight_residency_counters;
+int rnb_b200_cuda_weight_residency_counters(rnb_b200_weight_residency_counters *out);
+/* prewarm_quant_resident_weights — api/quant_api.rs:977 (any quant type; same cache as prewarm_q4k_weights) */
+int rnb_b200_prewarm_quant_resident_weights(const uint8_t *const *slices, const size_t *lens, size_t n, size_t *n_resident);
+
 /* ---- token-level decoder: the device-resident chain ------------------------------------------
  * The reference drives one operator call (and usually one stream sync) per projection; its
  * "carrier" variants (api/dense_api.rs:1176-1311, 2098-2400) were moving toward keeping

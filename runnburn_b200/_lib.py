@@ -113,6 +113,27 @@ def load() -> C.CDLL:
         "rnb_b200_rope_f32_inplace": [vp, sz, sz, sz, sz, f32, i32],
         "rnb_b200_activation_mul_f32_inplace": [vp, vp, sz],
         "rnb_b200_evaluate_expert_bundle_admission": [vp],
+        "rnb_b200_add_f32_inplace": [vp, sz, vp, sz],
+        "rnb_b200_upload_device_tensor_f32": [sz, sz, u32, vp, sz, vp],
+        "rnb_b200_download_device_tensor_f32": [u64, vp, sz],
+        "rnb_b200_download_device_tensor_f32_row": [u64, sz, vp, sz],
+        "rnb_b200_release_device_tensor": [u64, vp],
+        "rnb_b200_device_tensor_ptr": [u64, vp, vp, vp],
+        "rnb_b200_acquire_decode_carrier": [u32, sz, vp],
+        "rnb_b200_upload_to_decode_carrier": [vp, sz, u64],
+        "rnb_b200_download_from_decode_carrier": [u64, vp, sz],
+        "rnb_b200_sync_decode_stream": [],
+        "rnb_b200_attention_decode_cached_to_device": [sz, vp, sz, vp, vp, sz, sz, sz, sz, sz, f32, u64, u64, u64, u64],
+        "rnb_b200_dense_attention_qkv_rope_hd128_prefill": [
+            vp, sz, u32, vp, sz, u32, vp, sz, u32, sz, sz, sz, sz, sz, f32, sz, sz, vp, sz, vp, vp, vp],
+        "rnb_b200_qwen35_sparse_experts_into": [vp, vp, vp, sz, sz, vp, sz, C.c_int64, vp, vp, u32, sz, sz, vp, vp, sz],
+        "rnb_b200_qwen35_sparse_experts_add_residual_into": [vp, vp, vp, sz, sz, vp, sz, C.c_int64, vp, vp, u32, sz, sz, vp, vp, sz],
+        "rnb_b200_qwen35_expert_cache_stats": [vp],
+        "rnb_b200_qwen35_configure_moe_layer_cache": [sz, sz, sz, vp],
+        "rnb_b200_qwen35_admit_expert_misses_async": [vp, vp, sz, vp],
+        "rnb_b200_qwen35_prefill_device_topk_route_slots": [vp, sz, sz, vp, sz, sz, vp, vp, vp],
+        "rnb_b200_cuda_weight_residency_counters": [vp],
+        "rnb_b200_prewarm_quant_resident_weights": [vp, vp, sz, vp],
         "rnb_b200_decoder_create": [vp, vp],
         "rnb_b200_decoder_set_layer": [vp, i32, vp],
         "rnb_b200_decoder_set_globals": [vp, QWeight, vp, QWeight],

@@ -417,6 +417,12 @@ using namespace rnb;
 // =============================================================================================
 // extern "C"
 // =============================================================================================
+namespace rnb {
+// defined with the rest of the boundary (boundary.inc): brings a layer's device KV mirror up to kv_len rows
+static int kv_mirror_sync(State &st, size_t layer, const uint16_t *k, const uint16_t *v, size_t kv_len, size_t kv_dim, const uint16_t *last_k_dev,
+                          const uint16_t *last_v_dev);
+}  // namespace rnb
+
 extern "C" {
 
 const char *rnb_b200_last_error(void) { return g_last_error.c_str(); }
@@ -661,50 +667,8 @@ int rnb_b200_attention_decode_cached(size_t layer, const float *q, size_t q_len,
     State &st = L.st;
     RNB_TRY(st.open());
     RNB_CU(cudaSetDevice(st.device));
+    RNB_TRY(kv_mirror_sync(st, layer, k, v, kv_len, kv_heads * HD, nullptr, nullptr));
     KvMirror &m = st.kv_mirrors[layer];
-    const size_t kv_dim = kv_heads * HD;
-    const bool same = m.host_k == k && m.host_v == v && m.kv_dim == kv_dim && m.rows_have <= kv_len;
-    if (!same) m.rows_have = 0;
-    if (m.rows_cap < kv_len || m.kv_dim != kv_dim) {
-        // grow geometrically; old rows are re-uploaded from the host copy (the cache is
-        // append-only and re-uploadable: runtime/attention.rs:3973-3990)
-        size_t cap = std::max<size_t>(kv_len, m.rows_cap * 2);
-        cap = std::max<size_t>(cap, 256);
-        uint16_t *nk = nullptr, *nv = nullptr;
-        RNB_CU(cudaMalloc((void **)&nk, cap * kv_dim * 2));
-        cudaError_t e = cudaMalloc((void **)&nv, cap * kv_dim * 2);
-        if (e != cudaSuccess) {
-            cudaFree(nk);
-            return fail_cuda(e, "cudaMalloc(kv mirror)");
-        }
-        if (m.rows_have && m.kv_dim == kv_dim) {
-            cudaError_t ce = cudaMemcpyAsync(nk, m.dk, m.rows_have * kv_dim * 2, cudaMemcpyDeviceToDevice, st.stream);
-            if (ce == cudaSuccess) ce = cudaMemcpyAsync(nv, m.dv, m.rows_have * kv_dim * 2, cudaMemcpyDeviceToDevice, st.stream);
-            if (ce == cudaSuccess) ce = cudaStreamSynchronize(st.stream);
-            if (ce != cudaSuccess) {   // the old mirror stays in place; the new buffers must not leak
-                cudaFree(nk);
-                cudaFree(nv);
-                return fail_cuda(ce, "cudaMemcpyAsync(kv mirror grow)");
-            }
-        } else {
-            m.rows_have = 0;
-        }
-        cudaFree(m.dk);
-        cudaFree(m.dv);
-        m.dk = nk;
-        m.dv = nv;
-        m.rows_cap = cap;
-        m.kv_dim = kv_dim;
-    }
-    m.host_k = k;
-    m.host_v = v;
-    if (kv_len > m.rows_have) {
-        const size_t off = m.rows_have * kv_dim, n = (kv_len - m.rows_have) * kv_dim * 2;
-        RNB_CU(cudaMemcpyAsync(m.dk + off, k + off, n, cudaMemcpyHostToDevice, st.stream));
-        RNB_CU(cudaMemcpyAsync(m.dv + off, v + off, n, cudaMemcpyHostToDevice, st.stream));
-        st.ctr.h2d_bytes += 2 * n;
-        m.rows_have = kv_len;
-    }
     return attention_run(st, m.dk, m.dv, q, kv_len, heads, kv_heads, scale, out);
 }
 
@@ -1149,4 +1113,5 @@ int rnb_b200_dev_error_flag(int *flag_out) {
 
 }  // extern "C"
 
+#include "boundary.inc"
 #include "decoder.inc"

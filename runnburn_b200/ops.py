@@ -317,3 +317,181 @@ def dev_error_flag() -> int:
     f = C.c_int()
     check(load().rnb_b200_dev_error_flag(C.byref(f)))
     return f.value
+
+
+# ---- the rest of the operator boundary --------------------------------------------------------
+def add_f32_inplace(dst: np.ndarray, src) -> None:
+    """add_f32_inplace — crates/rnb-backend/cuda/src/runtime/api/dense_api.rs:1389"""
+    assert dst.dtype == np.float32 and dst.flags["C_CONTIGUOUS"]
+    src = _f32(src).ravel()
+    check(load().rnb_b200_add_f32_inplace(_p(dst), dst.size, _p(src), src.size))
+
+
+class DeviceTensor:
+    """upload_device_tensor_f32 / download_device_tensor_f32[_row] / release_device_tensor —
+    api/sequence_api.rs:4-56"""
+
+    def __init__(self, data, role: int = 0):
+        a = _f32(data)
+        a2 = a.reshape(1, -1) if a.ndim == 1 else a
+        self.rows, self.cols = a2.shape
+        ident = C.c_uint64()
+        check(load().rnb_b200_upload_device_tensor_f32(self.rows, self.cols, role, _p(a2), a2.size, C.byref(ident)))
+        self.id = ident.value
+
+    @property
+    def ptr(self) -> int:
+        p = C.c_uint64()
+        check(load().rnb_b200_device_tensor_ptr(self.id, C.byref(p), None, None))
+        return p.value
+
+    def download(self) -> np.ndarray:
+        out = np.empty((self.rows, self.cols), np.float32)
+        check(load().rnb_b200_download_device_tensor_f32(self.id, _p(out), out.size))
+        return out
+
+    def download_row(self, row: int) -> np.ndarray:
+        out = np.empty(self.cols, np.float32)
+        check(load().rnb_b200_download_device_tensor_f32_row(self.id, row, _p(out), out.size))
+        return out
+
+    def release(self) -> bool:
+        r = C.c_int()
+        check(load().rnb_b200_release_device_tensor(self.id, C.byref(r)))
+        return bool(r.value)
+
+
+CARRIER_HIDDEN, CARRIER_NORM_BUF, CARRIER_K, CARRIER_V, CARRIER_K_F16, CARRIER_V_F16, CARRIER_ATTN_OUT = range(7)
+
+
+def acquire_decode_carrier(kind: int, nbytes: int) -> int:
+    """acquire_decode_*_carrier — api/dense_api.rs:1176-1290"""
+    p = C.c_uint64()
+    check(load().rnb_b200_acquire_decode_carrier(kind, nbytes, C.byref(p)))
+    return p.value
+
+
+def upload_to_decode_carrier(host: np.ndarray, dev: int) -> None:
+    check(load().rnb_b200_upload_to_decode_carrier(_p(host), host.nbytes, dev))
+
+
+def download_from_decode_carrier(dev: int, host: np.ndarray) -> None:
+    check(load().rnb_b200_download_from_decode_carrier(dev, _p(host), host.nbytes))
+
+
+def sync_decode_stream() -> None:
+    check(load().rnb_b200_sync_decode_stream())
+
+
+def attention_decode_cached_to_device(layer_index: int, q, k, v, kv_len, num_heads, num_kv_heads, head_dim, scale, output_dev: int,
+                                      last_token_k_dev: int = 0, last_token_v_dev: int = 0, q_dev_override: int = 0) -> None:
+    """attention_decode_cached_to_device — api/attention_api.rs:1776 (0 stands for None)"""
+    assert k.dtype == np.uint16 and v.dtype == np.uint16
+    qa = _f32(q).ravel() if q is not None else None
+    check(load().rnb_b200_attention_decode_cached_to_device(layer_index, _p(qa) if qa is not None else None, qa.size if qa is not None else 0,
+                                                            _p(k), _p(v), min(k.size, v.size), kv_len, num_heads, num_kv_heads, head_dim, scale,
+                                                            output_dev, last_token_k_dev, last_token_v_dev, q_dev_override))
+
+
+def dense_attention_qkv_rope_hd128_prefill(q_w, k_w, v_w, q_rows, kv_rows, n_embd, num_heads, num_kv_heads, rope_theta, pos_start, seq_len, x):
+    """dense_q4k_attention_qkv_rope_hd128_prefill — api/dense_api.rs:1075; weights are (type, bytes) pairs"""
+    (qt, qw), (kt, kw), (vt, vw) = [(t, _u8(w)) for t, w in (q_w, k_w, v_w)]
+    x = _f32(x).ravel()
+    q = np.empty(seq_len * q_rows, np.float32)
+    kb = np.empty(seq_len * kv_rows, np.uint16)
+    vb = np.empty(seq_len * kv_rows, np.uint16)
+    check(load().rnb_b200_dense_attention_qkv_rope_hd128_prefill(_p(qw), qw.size, qt, _p(kw), kw.size, kt, _p(vw), vw.size, vt, q_rows, kv_rows,
+                                                                 n_embd, num_heads, num_kv_heads, rope_theta, pos_start, seq_len, _p(x), x.size,
+                                                                 _p(q), _p(kb), _p(vb)))
+    return q, kb, vb
+
+
+class ExpertStats(C.Structure):
+    _fields_ = [(n, C.c_uint64) for n in ("bundle_lookups", "bundle_hits", "bundle_partial_hits", "bundle_misses", "bundle_admissions",
+                                          "bundle_evictions", "admitted_bytes", "evicted_bytes", "h2d_bytes", "temp_h2d_bytes")]
+
+    def as_dict(self) -> dict:
+        return {n: int(getattr(self, n)) for n, _ in self._fields_}
+
+
+class ExpertReceipt(C.Structure):
+    _fields_ = [("consumed", C.c_uint32), ("reserved", C.c_uint32), ("pending_stats", ExpertStats)]
+
+
+def _expert_ptrs(gate, up, down):
+    n = len(gate)
+    keep = [_u8(a) for a in list(gate) + list(up) + list(down)]
+    arr = C.c_void_p * n
+    return keep, arr(*[a.ctypes.data for a in keep[:n]]), arr(*[a.ctypes.data for a in keep[n:2 * n]]), arr(*[a.ctypes.data for a in keep[2 * n:]])
+
+
+def qwen35_sparse_experts_into(gate, up, down, route_weights, layer_idx, selected_expert_ids, receipt, down_quant, n_ff, n_embd, x,
+                               residual=None) -> np.ndarray:
+    """qwen35_sparse_experts_into / _add_residual_into — api/qwen_moe_api.rs:1918,2163.  layer_idx None -> -1."""
+    n = len(gate)
+    keep, g, u, d = _expert_ptrs(gate, up, down)
+    rw, x = _f32(route_weights).ravel(), _f32(x).ravel()
+    ids = (C.c_size_t * n)(*[int(i) for i in selected_expert_ids]) if selected_expert_ids is not None else None
+    li = -1 if layer_idx is None else int(layer_idx)
+    rc = C.byref(receipt) if receipt is not None else None
+    if residual is None:
+        out = np.empty(n_embd, np.float32)
+        check(load().rnb_b200_qwen35_sparse_experts_into(g, u, d, keep[0].size, keep[2 * n].size, _p(rw), n, li, ids, rc, down_quant, n_ff, n_embd,
+                                                         _p(x), _p(out), out.size))
+        return out
+    out = _f32(residual).ravel().copy()
+    check(load().rnb_b200_qwen35_sparse_experts_add_residual_into(g, u, d, keep[0].size, keep[2 * n].size, _p(rw), n, li, ids, rc, down_quant, n_ff,
+                                                                  n_embd, _p(x), _p(out), out.size))
+    return out
+
+
+def qwen35_expert_cache_stats() -> dict:
+    s = ExpertStats()
+    check(load().rnb_b200_qwen35_expert_cache_stats(C.byref(s)))
+    return s.as_dict()
+
+
+def qwen35_configure_moe_layer_cache(model_moe_bytes: int, runtime_headroom_bytes: int, min_layer_bytes: int) -> int:
+    out = C.c_size_t()
+    check(load().rnb_b200_qwen35_configure_moe_layer_cache(model_moe_bytes, runtime_headroom_bytes, min_layer_bytes, C.byref(out)))
+    return out.value
+
+
+def qwen35_admit_expert_misses_async(slices) -> int:
+    keep = [_u8(a) for a in slices]
+    n = len(keep)
+    ptrs = (C.c_void_p * n)(*[a.ctypes.data for a in keep])
+    lens = (C.c_size_t * n)(*[a.size for a in keep])
+    out = C.c_size_t()
+    check(load().rnb_b200_qwen35_admit_expert_misses_async(ptrs, lens, n, C.byref(out)))
+    return out.value
+
+
+def qwen35_prefill_device_topk_route_slots(router_w, norm_all, n_expert_used: int):
+    w, h = _f32(router_w), _f32(norm_all)
+    n_expert, hidden = w.shape
+    seq = h.size // hidden
+    ids = np.empty(seq * n_expert_used, np.uint32)
+    wts = np.empty(seq * n_expert_used, np.float32)
+    toks = np.empty(seq * n_expert_used, np.uint32)
+    check(load().rnb_b200_qwen35_prefill_device_topk_route_slots(_p(w), n_expert, hidden, _p(h), seq, n_expert_used, _p(ids), _p(wts), _p(toks)))
+    return ids, wts, toks
+
+
+def cuda_weight_residency_counters() -> dict:
+    names = ("expanded_diag_bytes", "native_f32_bytes", "packed_q8dot_bytes", "raw_quant_bytes", "transient_quant_upload_bytes",
+             "q4_expanded_f16_bytes", "q4_expanded_f32_bytes", "q6_expanded_f16_bytes", "q6_expanded_f32_bytes", "q4_raw_quant_bytes",
+             "q6_raw_quant_bytes", "q4_transient_quant_upload_bytes", "q6_transient_quant_upload_bytes")
+    buf = (C.c_uint64 * len(names))()
+    check(load().rnb_b200_cuda_weight_residency_counters(buf))
+    return dict(zip(names, [int(v) for v in buf]))
+
+
+def prewarm_quant_resident_weights(slices) -> int:
+    keep = [_u8(a) for a in slices]
+    n = len(keep)
+    ptrs = (C.c_void_p * n)(*[a.ctypes.data for a in keep])
+    lens = (C.c_size_t * n)(*[a.size for a in keep])
+    out = C.c_size_t()
+    check(load().rnb_b200_prewarm_quant_resident_weights(ptrs, lens, n, C.byref(out)))
+    return out.value

@@ -1,0 +1,197 @@
+"""The rest of the reference's operator boundary through the C ABI: device tensors, decode carriers,
+cached decode attention with the output left on the device, the batched q/k/v + RoPE call, the MoE
+entry points that carry layer index / expert ids / receipt through the expert-bundle accounting, and
+the residency reports.  Results are compared with the oracle (bit for bit where the path is exact)."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+import oracle as orc
+from synth import max_rel_err
+
+pytestmark = pytest.mark.gpu
+Q4_K, Q6_K = 12, 14
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from runnburn_b200 import ops as o
+    o.open()
+    return o
+
+
+def quantized(rng, t, rows, cols):
+    return orc.quantize_matrix(t, rng.standard_normal((rows, cols)).astype(np.float32) * 0.05)
+
+
+def test_add_f32_inplace_and_its_messages(ops):
+    import runnburn_b200 as r
+    rng = np.random.default_rng(1)
+    a, b = rng.standard_normal(5000).astype(np.float32), rng.standard_normal(5000).astype(np.float32)
+    want = a + b
+    ops.add_f32_inplace(a, b)
+    assert np.array_equal(a, want)
+    with pytest.raises(r.RnbError, match="CUDA add shape mismatch: dst=4 src=3"):
+        ops.add_f32_inplace(np.zeros(4, np.float32), np.zeros(3, np.float32))
+    ops.add_f32_inplace(np.zeros(0, np.float32), np.zeros(0, np.float32))   # empty: nothing to do
+
+
+def test_device_tensor_round_trip_rows_and_release(ops):
+    import runnburn_b200 as r
+    data = np.arange(3 * 700, dtype=np.float32).reshape(3, 700)
+    t = ops.DeviceTensor(data, role=2)
+    assert t.ptr != 0
+    assert np.array_equal(t.download(), data)
+    assert np.array_equal(t.download_row(2), data[2])
+    with pytest.raises(r.RnbError, match="out of range"):
+        t.download_row(3)
+    assert t.release() is True
+    assert t.release() is False           # Ok(false): already gone
+    with pytest.raises(r.RnbError, match="unknown device tensor id"):
+        t.download()
+
+
+def test_decode_carriers_hold_their_bytes_across_calls(ops):
+    h = ops.acquire_decode_carrier(ops.CARRIER_HIDDEN, 4096 * 4)
+    n = ops.acquire_decode_carrier(ops.CARRIER_NORM_BUF, 4096 * 4)
+    assert h != 0 and n != 0 and h != n
+    assert ops.acquire_decode_carrier(ops.CARRIER_HIDDEN, 1024) == h      # no regrowth for a smaller request
+    x = np.linspace(-3, 3, 4096, dtype=np.float32)
+    ops.upload_to_decode_carrier(x, h)
+    back = np.zeros_like(x)
+    ops.download_from_decode_carrier(h, back)
+    ops.sync_decode_stream()
+    assert np.array_equal(back, x)
+    import runnburn_b200 as r
+    with pytest.raises(r.RnbError):
+        ops.acquire_decode_carrier(99, 16)
+
+
+def test_attention_decode_cached_to_device_with_device_side_last_row(ops):
+    rng = np.random.default_rng(2)
+    heads, kvh, cap = 8, 2, 64
+    kv_dim = kvh * 128
+    k = orc.f32_to_f16_bits(rng.standard_normal(cap * kv_dim))
+    v = orc.f32_to_f16_bits(rng.standard_normal(cap * kv_dim))
+    scale = float(1.0 / np.sqrt(128.0))
+    ops.clear_decode_attention_kv_cache()
+    out_dev = ops.acquire_decode_carrier(ops.CARRIER_ATTN_OUT, heads * 128 * 4)
+    out = np.zeros(heads * 128, np.float32)
+    # host rows up to 40, output read back from the device buffer
+    q = rng.standard_normal(heads * 128).astype(np.float32)
+    ops.attention_decode_cached_to_device(5, q, k, v, 40, heads, kvh, 128, scale, out_dev)
+    ops.download_from_decode_carrier(out_dev, out)
+    ops.sync_decode_stream()
+    assert np.array_equal(out, orc.attention_decode(q, k, v, heads, kvh, 128, 40, scale))
+    # row 40 arrives from device buffers (the host arrays hold something else there), q from the device too
+    k_new = orc.f32_to_f16_bits(rng.standard_normal(kv_dim))
+    v_new = orc.f32_to_f16_bits(rng.standard_normal(kv_dim))
+    kd = ops.acquire_decode_carrier(ops.CARRIER_K_F16, kv_dim * 2)
+    vd = ops.acquire_decode_carrier(ops.CARRIER_V_F16, kv_dim * 2)
+    ops.upload_to_decode_carrier(k_new, kd)
+    ops.upload_to_decode_carrier(v_new, vd)
+    q2 = rng.standard_normal(heads * 128).astype(np.float32)
+    qt = ops.DeviceTensor(q2)
+    before = ops.cuda_cache_snapshot()["h2d_bytes"]
+    ops.attention_decode_cached_to_device(5, None, k, v, 41, heads, kvh, 128, scale, out_dev, kd, vd, qt.ptr)
+    ops.download_from_decode_carrier(out_dev, out)
+    ops.sync_decode_stream()
+    assert ops.cuda_cache_snapshot()["h2d_bytes"] == before          # nothing crossed PCIe for this step
+    k_ref, v_ref = k.copy(), v.copy()
+    k_ref[40 * kv_dim:41 * kv_dim] = k_new
+    v_ref[40 * kv_dim:41 * kv_dim] = v_new
+    assert np.array_equal(out, orc.attention_decode(q2, k_ref, v_ref, heads, kvh, 128, 41, scale))
+    qt.release()
+    ops.clear_decode_attention_kv_cache()
+
+
+def test_qkv_rope_prefill_equals_the_oracle_token_by_token(ops):
+    rng = np.random.default_rng(3)
+    n_embd, heads, kvh, pos0, seq = 512, 4, 2, 9, 5
+    wq, wk, wv = quantized(rng, Q4_K, heads * 128, n_embd), quantized(rng, Q4_K, kvh * 128, n_embd), quantized(rng, Q6_K, kvh * 128, n_embd)
+    x = rng.standard_normal((seq, n_embd)).astype(np.float32)
+    q, kb, vb = ops.dense_attention_qkv_rope_hd128_prefill((Q4_K, wq), (Q4_K, wk), (Q6_K, wv), heads * 128, kvh * 128, n_embd, heads, kvh, 5e5, pos0, seq, x)
+    for s in range(seq):
+        q_ref = orc.rope(orc.gemv(Q4_K, wq, x[s], heads * 128, n_embd), pos0 + s, 128, heads * 128, 5e5)
+        k_ref = orc.rope(orc.gemv(Q4_K, wk, x[s], kvh * 128, n_embd), pos0 + s, 128, kvh * 128, 5e5)
+        v_ref = orc.gemv(Q6_K, wv, x[s], kvh * 128, n_embd)
+        assert np.array_equal(q[s * heads * 128:(s + 1) * heads * 128], q_ref)
+        assert np.array_equal(kb[s * kvh * 128:(s + 1) * kvh * 128], orc.f32_to_f16_bits(k_ref))
+        assert np.array_equal(vb[s * kvh * 128:(s + 1) * kvh * 128], orc.f32_to_f16_bits(v_ref))
+
+
+def test_sparse_experts_into_miss_path_accounting_and_receipt(ops):
+    """A layer that is NOT registered: the first call sees full misses (observed once, so admission does not
+    pay yet under the reference's rule), later calls see history and residency; the receipt carries the
+    call's stats delta; the result equals the oracle's."""
+    rng = np.random.default_rng(4)
+    n_embd, n_ff, n_expert, k = 512, 256, 6, 2
+    gate_all, up_all = quantized(rng, Q4_K, n_expert * n_ff, n_embd), quantized(rng, Q4_K, n_expert * n_ff, n_embd)
+    down_all = quantized(rng, Q4_K, n_expert * n_embd, n_ff)
+    gs, ds = n_ff * orc.row_bytes(Q4_K, n_embd), n_embd * orc.row_bytes(Q4_K, n_ff)
+    x = rng.standard_normal(n_embd).astype(np.float32)
+    ids = [4, 1]
+    rw = np.array([0.7, 0.3], np.float32)
+    gate = [gate_all[e * gs:(e + 1) * gs] for e in ids]
+    up = [up_all[e * gs:(e + 1) * gs] for e in ids]
+    down = [down_all[e * ds:(e + 1) * ds] for e in ids]
+    ref = orc.moe_experts(gate, up, down, rw, Q4_K, n_ff, n_embd, x)
+    ops.reset_state_for_engine_init()
+    before = ops.qwen35_expert_cache_stats()
+    receipt = ops.ExpertReceipt()
+    got = ops.qwen35_sparse_experts_into(gate, up, down, rw, 3, ids, receipt, Q4_K, n_ff, n_embd, x)
+    assert max_rel_err(got, ref) <= 2e-3
+    d = receipt.pending_stats.as_dict()
+    assert receipt.consumed == 0 and d["bundle_lookups"] == k and d["bundle_misses"] == k and d["bundle_hits"] == 0
+    assert d["h2d_bytes"] + d["temp_h2d_bytes"] == k * (2 * gs + ds)
+    after = ops.qwen35_expert_cache_stats()
+    assert after["bundle_lookups"] - before["bundle_lookups"] == k
+    # the compute call made the slices resident (there was room): the same bundles are hits now
+    receipt2 = ops.ExpertReceipt()
+    res = rng.standard_normal(n_embd).astype(np.float32)
+    got2 = ops.qwen35_sparse_experts_into(gate, up, down, rw, 3, ids, receipt2, Q4_K, n_ff, n_embd, x, residual=res)
+    d2 = receipt2.pending_stats.as_dict()
+    assert d2["bundle_hits"] == k and d2["bundle_misses"] == 0 and d2["h2d_bytes"] == 0 and d2["temp_h2d_bytes"] == 0
+    assert np.array_equal(got2, res + got)                     # residual + experts, f32
+    # no layer index: no history, still accounted
+    got3 = ops.qwen35_sparse_experts_into(gate, up, down, rw, None, None, None, Q4_K, n_ff, n_embd, x)
+    assert np.array_equal(got3, got)
+    import runnburn_b200 as r
+    with pytest.raises(r.RnbError, match="needs the selected expert ids"):
+        ops.qwen35_sparse_experts_into(gate, up, down, rw, 3, None, None, Q4_K, n_ff, n_embd, x)
+    ops.reset_state_for_engine_init()
+
+
+def test_admit_misses_async_configure_cache_and_residency_counters(ops):
+    rng = np.random.default_rng(5)
+    ops.reset_state_for_engine_init()
+    a, b = quantized(rng, Q4_K, 256, 512), quantized(rng, Q6_K, 128, 512)
+    c0 = ops.cuda_weight_residency_counters()
+    assert ops.qwen35_admit_expert_misses_async([a, b]) == 2
+    assert ops.qwen35_admit_expert_misses_async([a, b]) == 0          # already resident
+    ops.sync_decode_stream()
+    c1 = ops.cuda_weight_residency_counters()
+    assert c1["raw_quant_bytes"] - c0["raw_quant_bytes"] == a.size + b.size
+    assert c1["q4_expanded_f16_bytes"] == 0 and c1["native_f32_bytes"] == 0
+    assert ops.prewarm_quant_resident_weights([a, b]) == 2
+    free_b, total_b = ops.cuda_memory_info()
+    lim = ops.qwen35_configure_moe_layer_cache(10 << 20, 1 << 30, 1 << 20)
+    assert lim == 10 << 20                                            # the model's expert bytes fit beside the head-room
+    assert ops.qwen35_configure_moe_layer_cache(10 << 20, total_b, 1 << 20) == 0   # head-room swallows everything
+    assert ops.qwen35_configure_moe_layer_cache(1 << 10, 0, 1 << 20) == 0          # less than one layer: nothing kept
+    ops.reset_state_for_engine_init()
+
+
+def test_prefill_route_slots_equal_the_oracle_router(ops):
+    rng = np.random.default_rng(6)
+    n_expert, hidden, seq, k = 16, 512, 7, 4
+    w = rng.standard_normal((n_expert, hidden)).astype(np.float32)
+    h = rng.standard_normal((seq, hidden)).astype(np.float32)
+    ids, wts, toks = ops.qwen35_prefill_device_topk_route_slots(w, h, k)
+    for s in range(seq):
+        lg = orc.gemv_f32(w, h[s])
+        ri, rw = orc.moe_route_topk(lg, k)
+        assert np.array_equal(ids[s * k:(s + 1) * k], np.asarray(ri, np.uint32))
+        assert np.array_equal(wts[s * k:(s + 1) * k], np.asarray(rw, np.float32))
+        assert np.all(toks[s * k:(s + 1) * k] == s)
