@@ -143,3 +143,28 @@ def test_device_pointer_attention_rejects_bad_arguments_before_any_launch(lib):
     assert g(q, k, v, 0, 32, 8, 0.1, out, None) == 2 and "kv_len" in err()
     assert g(q, k, v, 128, 65, 1, 0.1, out, None) == 2 and "at most 64 query heads" in err()
     assert g(None, k, v, 128, 32, 8, 0.1, out, None) == 2 and "null pointer" in err()
+
+
+def test_static_archive_defines_every_declared_symbol_and_links_into_a_c_program(tmp_path):
+    """The form a Rust build.rs links: `nvcc -lib` archive + the CUDA runtime.  A plain C program that
+    binds the header links against it and runs (it only asks for the last error string: no GPU needed)."""
+    from runnburn_b200 import build
+    archive = build.build_static_library()
+    header = re.sub(r"/\*.*?\*/", "", (ROOT / "include" / "rnb_b200.h").read_text(), flags=re.S)
+    declared = sorted(set(re.findall(r"\b(rnb_b200_[a-z0-9_]+)\s*\(", header)))
+    have = set(re.findall(r" T (rnb_b200_[a-z0-9_]+)", subprocess.run(["nm", "-g", "--defined-only", str(archive)], capture_output=True, text=True,
+                                                                       check=True).stdout))
+    missing = [s for s in declared if s not in have]
+    assert not missing, f"declared but not defined in the archive: {missing}"
+    src = tmp_path / "main.c"
+    src.write_text('#include <stdio.h>\n#include "rnb_b200.h"\nint main(void) { const char *e = rnb_b200_last_error(); '
+                   'int rc = rnb_b200_q4k_gemv(0, 0, 3, 100, 0, 0, 0, 0); printf("%d|%s|%s\\n", rc, e ? "ok" : "null", rnb_b200_last_error()); return 0; }\n')
+    exe = tmp_path / "main"
+    cuda_lib = "/usr/local/cuda/lib64"
+    r = subprocess.run(["gcc", "-I", str(ROOT / "include"), str(src), str(archive), "-L", cuda_lib, "-Wl,-rpath," + cuda_lib, "-lcudart", "-ldl",
+                        "-lstdc++", "-lm", "-lpthread", "-lrt", "-o", str(exe)], capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr[-3000:]
+    out = subprocess.run([str(exe)], capture_output=True, text=True, timeout=60)
+    assert out.returncode == 0, out.stderr[-2000:]
+    rc, first, msg = out.stdout.strip().split("|", 2)
+    assert int(rc) != 0 and "256" in msg          # the reference's shape message: cols must be divisible by 256

@@ -91,3 +91,75 @@ def test_reference_arm_under_torchrun_prints_once():
     assert r.returncode == 0, r.stderr[-3000:]
     lines = [l for l in r.stdout.splitlines() if l.startswith("{")]
     assert len(lines) == 1 and '"impl": "reference"' in lines[0]
+
+
+LEAVER = textwrap.dedent("""
+    import os, sys, time
+    sys.path.insert(0, %r)
+    import torch, torch.distributed as dist
+    from datetime import timedelta
+    from runnburn_b200.shard import PeerLeft, StepGuard
+    dist.init_process_group("gloo", timeout=timedelta(seconds=20))
+    rank, world = dist.get_rank(), dist.get_world_size()
+    store = dist.distributed_c10d._get_default_store()
+    guard = StepGuard(store, rank, world)
+    dist.barrier()
+    done = 0
+    try:
+        for step in range(6):
+            if rank == 1 and step == 3:
+                # leaves BETWEEN steps: nothing of its own in flight, says so, exits cleanly
+                guard.leave("planned exit after step 2")
+                sys.stdout.write("rank 1 left\\n"); sys.stdout.flush()
+                os._exit(0)
+            if rank == 0 and step == 3:
+                time.sleep(1.0)                      # the note has time to land
+            guard.step(step)
+            t = torch.ones(4) * (rank + 1)
+            dist.all_reduce(t)                       # the step's exchange: needs every rank
+            assert float(t[0]) == 3.0
+            done += 1
+    except PeerLeft as e:
+        sys.stdout.write("rank %%d saw rank %%d leave after %%d steps: %%s\\n" %% (rank, e.rank, done, e)); sys.stdout.flush()
+        os._exit(0)                                  # no collective was started with the rank missing
+    sys.stdout.write("rank %%d finished %%d steps\\n" %% (rank, done)); sys.stdout.flush()
+""")
+
+
+def test_cpu_rank_leaves_between_steps_and_the_other_learns_on_the_host(tmp_path):
+    """World size 2 on CPU (gloo).  Rank 1 leaves between steps 2 and 3; rank 0 must learn of it from the
+    store BEFORE starting step 3's exchange, i.e. end cleanly after exactly 3 steps without a hung or
+    timed-out collective."""
+    script = tmp_path / "leaver.py"
+    script.write_text(LEAVER % (str(ROOT),))
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", OMP_NUM_THREADS="1")
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+                        "--master-addr", "127.0.0.1", "--master-port", "29733", str(script)],
+                       capture_output=True, text=True, env=env, timeout=120)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-4000:]
+    assert "rank 1 left" in r.stdout
+    assert "rank 0 saw rank 1 leave after 3 steps" in r.stdout, r.stdout[-2000:]
+
+
+def test_step_guard_flags_a_rank_whose_beat_went_stale():
+    from runnburn_b200.shard import PeerLeft, StepGuard
+
+    class FakeStore(dict):
+        def set(self, k, v):
+            self[k] = v.encode()
+
+        def get(self, k):
+            return self[k]
+
+        def check(self, keys):
+            return all(k in self for k in keys)
+
+    st = FakeStore()
+    a, b = StepGuard(st, 0, 2, max_lag=1, stale_after=0.0), StepGuard(st, 1, 2)
+    for step in range(3):
+        b.step(step)
+        a.step(step)
+    a.step(3)                    # rank 1 is one step behind: tolerated
+    with pytest.raises(PeerLeft) as e:
+        a.check(4)               # two behind and its beat has not moved since it was last read
+    assert e.value.rank == 1
