@@ -91,6 +91,15 @@ int rnb_b200_quantize_q8k(const float *input, size_t n, void *blocks_out);
 /* q4k_gemv / q4k_gemv_into — api/quant_api.rs:183-218,220 */
 int rnb_b200_q4k_gemv(const uint8_t *weights, size_t weights_len, size_t rows, size_t cols,
                       const float *input, size_t input_len, float *output, size_t output_len);
+/* Q5_K (GGML type 13, 176-byte blocks) beside the Q4_K_M set: the CPU's dispatch
+ * (crates/rnb-cpu/src/gemm/quant_gemv.rs:94-101, QuantGemvType::Q5K -> dot_q5k_q8k_avx2,
+ * crates/rnb-cpu/src/gemm/avx2_dot.rs:698-789), bit-exact; `down_quant` 13 of
+ * rnb_b200_dense_q4k_silu_ffn_batch takes the same kernel.  _batch: input [seq][cols], output
+ * seq-major. */
+int rnb_b200_q5k_gemv(const uint8_t *weights, size_t weights_len, size_t rows, size_t cols,
+                      const float *input, size_t input_len, float *output, size_t output_len);
+int rnb_b200_q5k_gemv_batch(const uint8_t *weights, size_t weights_len, size_t rows, size_t cols,
+                            const float *input, size_t input_len, float *output, size_t output_len);
 /* q6k_gemv — api/quant_api.rs:2071-2106 */
 int rnb_b200_q6k_gemv(const uint8_t *weights, size_t weights_len, size_t rows, size_t cols,
                       const float *input, size_t input_len, float *output, size_t output_len);

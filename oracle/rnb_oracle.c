@@ -195,6 +195,30 @@ void orc_dequantize_q4k_block(const uint8_t *block, float *out) {
     }
 }
 
+/* Q5_K: crates/rnb-cpu/src/quantize/dequant.rs:729-770; block = d f16 | dmin f16 | scales[12] |
+ * qh[32] | qs[128] (crates/rnb-cpu/src/quantize/blocks.rs:90-98, 176 bytes) */
+void orc_dequantize_q5k_block(const uint8_t *block, float *out) {
+    float d = orc_f16_to_f32(rd_u16(block));
+    float dmin = orc_f16_to_f32(rd_u16(block + 2));
+    const uint8_t *scales = block + 4, *qh = block + 16, *ql = block + 48;
+    int is = 0;
+    uint8_t u1 = 1, u2 = 2;
+    for (int grp = 0; grp < 4; grp++) {
+        uint8_t sc1, m1, sc2, m2;
+        get_scale_min_k4(is, scales, &sc1, &m1);
+        get_scale_min_k4(is + 1, scales, &sc2, &m2);
+        float d1 = d * (float)sc1, mm1 = dmin * (float)m1;
+        float d2 = d * (float)sc2, mm2 = dmin * (float)m2;
+        for (int l = 0; l < 32; l++)
+            out[64 * grp + l] = d1 * (float)((ql[32 * grp + l] & 0xF) + ((qh[l] & u1) ? 16 : 0)) - mm1;
+        for (int l = 0; l < 32; l++)
+            out[64 * grp + 32 + l] = d2 * (float)((ql[32 * grp + l] >> 4) + ((qh[l] & u2) ? 16 : 0)) - mm2;
+        is += 2;
+        u1 = (uint8_t)(u1 << 2);
+        u2 = (uint8_t)(u2 << 2);
+    }
+}
+
 void orc_dequantize_q6k_block(const uint8_t *block, float *out) {
     const uint8_t *ql = block, *qh = block + 128;
     const int8_t *sc = (const int8_t *)(block + 192);
@@ -225,6 +249,7 @@ void orc_dequantize_q8_0_block(const uint8_t *block, float *out) {
 size_t orc_row_bytes(int t, size_t cols) {
     switch (t) {
     case ORC_TYPE_Q4_K: return cols / 256 * ORC_Q4K_BYTES;
+    case ORC_TYPE_Q5_K: return cols / 256 * ORC_Q5K_BYTES;
     case ORC_TYPE_Q6_K: return cols / 256 * ORC_Q6K_BYTES;
     case ORC_TYPE_Q8_0: return cols / 32 * ORC_Q8_0_BYTES;
     default: return 0;
@@ -236,6 +261,10 @@ int orc_dequantize_row(int t, const uint8_t *row, size_t cols, float *out) {
     case ORC_TYPE_Q4_K:
         for (size_t b = 0; b < cols / 256; b++)
             orc_dequantize_q4k_block(row + b * ORC_Q4K_BYTES, out + b * 256);
+        return 0;
+    case ORC_TYPE_Q5_K:
+        for (size_t b = 0; b < cols / 256; b++)
+            orc_dequantize_q5k_block(row + b * ORC_Q5K_BYTES, out + b * 256);
         return 0;
     case ORC_TYPE_Q6_K:
         for (size_t b = 0; b < cols / 256; b++)
@@ -452,6 +481,62 @@ void orc_quantize_row_q6k(const float *input, size_t n, uint8_t *output) {
 }
 
 /* Harness-only Q8_0 quantiser (GGML convention: d = amax/127, q = round(x/d)). */
+/* Q5_K quantiser: harness utility (the reference ships none).  Per 32-element sub-block a
+ * min/max fit on 0..31, super-scales fitted to 6 bits, validated through the reference's
+ * dequantiser (round trip). */
+void orc_quantize_row_q5k(const float *input, size_t n, uint8_t *output) {
+    for (size_t b = 0; b < n / 256; b++) {
+        const float *x = input + b * 256;
+        uint8_t *blk = output + b * ORC_Q5K_BYTES;
+        float sc[8], mn[8], max_sc = 0.f, max_mn = 0.f;
+        for (int j = 0; j < 8; j++) {
+            float lo = 0.f, hi = x[32 * j];
+            for (int l = 0; l < 32; l++) {
+                if (x[32 * j + l] < lo) lo = x[32 * j + l];
+                if (x[32 * j + l] > hi) hi = x[32 * j + l];
+            }
+            sc[j] = (hi - lo) / 31.f;
+            mn[j] = -lo;
+            if (sc[j] > max_sc) max_sc = sc[j];
+            if (mn[j] > max_mn) max_mn = mn[j];
+        }
+        uint16_t dh = orc_f32_to_f16(max_sc / 63.f), mh = orc_f32_to_f16(max_mn / 63.f);
+        float d = orc_f16_to_f32(dh), dm = orc_f16_to_f32(mh);
+        uint8_t ls[8], lm[8];
+        for (int j = 0; j < 8; j++) {
+            ls[j] = (uint8_t)clampi(d > 0.f ? nearest_int(sc[j] / d) : 0, 0, 63);
+            lm[j] = (uint8_t)clampi(dm > 0.f ? nearest_int(mn[j] / dm) : 0, 0, 63);
+        }
+        memset(blk, 0, ORC_Q5K_BYTES);
+        blk[0] = (uint8_t)(dh & 0xff);
+        blk[1] = (uint8_t)(dh >> 8);
+        blk[2] = (uint8_t)(mh & 0xff);
+        blk[3] = (uint8_t)(mh >> 8);
+        uint8_t *ys = blk + 4;
+        for (int j = 0; j < 8; j++) {
+            if (j < 4) {
+                ys[j] = ls[j];
+                ys[j + 4] = lm[j];
+            } else {
+                ys[j + 4] = (uint8_t)((ls[j] & 0xF) | ((lm[j] & 0xF) << 4));
+                ys[j - 4] |= (uint8_t)((ls[j] >> 4) << 6);
+                ys[j] |= (uint8_t)((lm[j] >> 4) << 6);
+            }
+        }
+        uint8_t *qh = blk + 16, *ql = blk + 48;
+        for (int j = 0; j < 8; j++) {
+            float dd = d * (float)ls[j], mm = dm * (float)lm[j];
+            for (int l = 0; l < 32; l++) {
+                int q = dd > 0.f ? clampi(nearest_int((x[32 * j + l] + mm) / dd), 0, 31) : 0;
+                int grp = j / 2;
+                if (j & 1) ql[32 * grp + l] |= (uint8_t)((q & 0xF) << 4);
+                else ql[32 * grp + l] |= (uint8_t)(q & 0xF);
+                if (q & 16) qh[l] |= (uint8_t)(1u << j);
+            }
+        }
+    }
+}
+
 void orc_quantize_row_q8_0(const float *input, size_t n, uint8_t *output) {
     size_t nb = n / 32;
     for (size_t i = 0; i < nb; i++) {
@@ -482,6 +567,7 @@ static void quant_rows(size_t b, size_t e, void *p) {
         const float *x = c->x + r * c->cols;
         uint8_t *o = c->out + r * rb;
         if (c->type == ORC_TYPE_Q4_K) orc_quantize_row_q4k(x, c->cols, o);
+        else if (c->type == ORC_TYPE_Q5_K) orc_quantize_row_q5k(x, c->cols, o);
         else if (c->type == ORC_TYPE_Q6_K) orc_quantize_row_q6k(x, c->cols, o);
         else orc_quantize_row_q8_0(x, c->cols, o);
     }
@@ -564,6 +650,8 @@ static void synth_block(int type, uint64_t seed, uint64_t block_index, float sig
                 }
                 out[16 + 32 * g + l] = (uint8_t)(q[0] | (q[1] << 4));
             }
+    } else if (type == ORC_TYPE_Q5_K) {
+        orc_quantize_row_q5k(x, 256, out);
     } else if (type == ORC_TYPE_Q6_K) {
         orc_quantize_row_q6k(x, 256, out);
     } else {
@@ -655,6 +743,48 @@ float orc_dot_q4k_q8k_lanes(const uint8_t *row, const orc_q8k_block *y, size_t n
     }
     float m0 = acc_m[0] + acc_m[2], m1 = acc_m[1] + acc_m[3];
     return hsum8(acc) + (m0 + m1);
+}
+
+/* Q5_K x Q8_K: crates/rnb-cpu/src/gemm/avx2_dot.rs:698-789.  Eight f32 accumulator lanes as for
+ * Q4_K (lane l = bytes 4l..4l+3 of every 32-byte group, one FMA per block); the fifth bit comes from
+ * the qh plane (bit j of qh[i] belongs to element i of sub-block j); the mins term is ONE scalar:
+ * summs += dmin * (sum_j mins_j * bsum32_j), a multiply and an add per block, added to the folded
+ * lanes at the end. */
+float orc_dot_q5k_q8k(const uint8_t *row, const orc_q8k_block *y, size_t nb) {
+    float acc[8] = {0}, summs = 0.0f;
+    for (size_t i = 0; i < nb; i++) {
+        const uint8_t *block = row + i * ORC_Q5K_BYTES;
+        float d = y[i].d * orc_f16_to_f32(rd_u16(block));
+        float dmin = -y[i].d * orc_f16_to_f32(rd_u16(block + 2));
+        uint32_t utmp[4];
+        unpack_q4k_scales(block + 4, utmp);
+        uint8_t sc[8], mn[8];
+        memcpy(sc, &utmp[0], 8);
+        memcpy(mn, &utmp[2], 8);
+        int32_t msum = 0;
+        for (int j = 0; j < 8; j++) msum += (int32_t)mn[j] * (int32_t)(int16_t)(y[i].bsums[2 * j] + y[i].bsums[2 * j + 1]);
+        volatile float mprod = dmin * (float)msum;   /* a rounded product, then a rounded sum: no contraction */
+        summs = summs + mprod;
+        const uint8_t *qh = block + 16, *q5 = block + 48;
+        const int8_t *q8 = y[i].qs;
+        int32_t sumi[8] = {0};
+        for (int j = 0; j < 4; j++) {
+            for (int l = 0; l < 8; l++) {
+                int32_t lo = 0, hi = 0;
+                for (int b = 0; b < 4; b++) {
+                    int e = 4 * l + b;
+                    uint8_t q = q5[32 * j + e];
+                    int v0 = (q & 0xF) + (((qh[e] >> (2 * j)) & 1) << 4);
+                    int v1 = (q >> 4) + (((qh[e] >> (2 * j + 1)) & 1) << 4);
+                    lo += v0 * q8[64 * j + e];
+                    hi += v1 * q8[64 * j + 32 + e];
+                }
+                sumi[l] += (int32_t)sc[2 * j] * lo + (int32_t)sc[2 * j + 1] * hi;
+            }
+        }
+        for (int l = 0; l < 8; l++) acc[l] = fmaf(d, (float)sumi[l], acc[l]);
+    }
+    return hsum8(acc) + summs;
 }
 
 float orc_dot_q6k_q8k_lanes(const uint8_t *row, const orc_q8k_block *y, size_t nb) {
@@ -874,6 +1004,7 @@ static void gemv_rows(size_t b, size_t e, void *p) {
         for (size_t s = 0; s < c->seq_len; s++) {
             float v;
             if (c->type == ORC_TYPE_Q4_K) v = orc_dot_q4k_q8k(row, c->xq + s * c->nb, c->nb);
+            else if (c->type == ORC_TYPE_Q5_K) v = orc_dot_q5k_q8k(row, c->xq + s * c->nb, c->nb);
             else if (c->type == ORC_TYPE_Q6_K) v = orc_dot_q6k_q8k(row, c->xq + s * c->nb, c->nb);
             else v = orc_dot_q8_0_row(row, c->x + s * c->cols, c->cols / 32);
             c->out[s * c->rows + r] = v;

@@ -13,6 +13,7 @@ HEADER = PKG.parent / "include" / "rnb_b200.h"
 
 OK, UNSUPPORTED, VALIDATION_FAILED, OUT_OF_MEMORY, CUDA_ERROR, DEVICE_FAULT_FLAG = range(6)
 TYPE_Q8_0, TYPE_Q4_K, TYPE_Q6_K = 8, 12, 14
+TYPE_Q5_K = 13
 
 
 class RnbError(RuntimeError):
@@ -89,6 +90,8 @@ def load() -> C.CDLL:
         "rnb_b200_quantize_q8k": [vp, sz, vp],
         "rnb_b200_q4k_gemv": [vp, sz, sz, sz, vp, sz, vp, sz],
         "rnb_b200_q6k_gemv": [vp, sz, sz, sz, vp, sz, vp, sz],
+        "rnb_b200_q5k_gemv": [vp, sz, sz, sz, vp, sz, vp, sz],
+        "rnb_b200_q5k_gemv_batch": [vp, sz, sz, sz, vp, sz, vp, sz],
         "rnb_b200_q8_0_gemv": [vp, sz, sz, sz, vp, sz, vp, sz],
         "rnb_b200_q4k_gemv_with_device_input": [vp, sz, sz, sz, u64, vp, sz],
         "rnb_b200_q6k_gemv_with_device_input": [vp, sz, sz, sz, u64, vp, sz],

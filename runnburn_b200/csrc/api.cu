@@ -307,7 +307,7 @@ struct Locked {
 };
 
 static const char *type_name(int t) {
-    return t == TYPE_Q4_K ? "Q4_K" : t == TYPE_Q6_K ? "Q6_K" : t == TYPE_Q8_0 ? "Q8_0" : "?";
+    return t == TYPE_Q4_K ? "Q4_K" : t == TYPE_Q5_K ? "Q5_K" : t == TYPE_Q6_K ? "Q6_K" : t == TYPE_Q8_0 ? "Q8_0" : "?";
 }
 
 // Shape checks with the reference's wording (api/quant_api.rs:189-206).
@@ -355,9 +355,15 @@ static int gemv_host(int type, const uint8_t *weights, size_t weights_len, size_
         x_stride = q8k_dev_bytes(cols);
     }
     RNB_TRY(st.out_f32.ensure(rows * seq * sizeof(float) + 16));
-    GemvJob job = make_job(type, w_dev, act, st.out_f32.as<float>(), nullptr, rows, cols, 0, st.sm_count,
-                           (int)seq, x_stride);
-    RNB_TRY(launch_gemv_one(st.stream, job, cols, st.dev_error));
+    if (type == TYPE_Q5_K) {
+        // its own warp-per-row kernel (exact; seq-major output like the others)
+        RNB_CU(launch_k(gemv_q5k_kernel, dim3((unsigned)((rows + G5_WARPS - 1) / G5_WARPS)), dim3(G5_WARPS * 32), 0, st.stream, w_dev,
+                        (const uint8_t *)act, x_stride, st.out_f32.as<float>(), (int)rows, (int)cols, (int)seq));
+    } else {
+        GemvJob job = make_job(type, w_dev, act, st.out_f32.as<float>(), nullptr, rows, cols, 0, st.sm_count,
+                               (int)seq, x_stride);
+        RNB_TRY(launch_gemv_one(st.stream, job, cols, st.dev_error));
+    }
     if (argmax_idx) {
         RNB_TRY(st.misc.ensure(16));
         RNB_CU(launch_k(argmax_last_kernel, dim3(1), dim3(1024), 0, st.stream, (const float *)st.out_f32.p,
@@ -566,6 +572,13 @@ int rnb_b200_quantize_q8k(const float *input, size_t n, void *blocks_out) {
 
 int rnb_b200_q4k_gemv(const uint8_t *w, size_t wl, size_t rows, size_t cols, const float *in, size_t il, float *out, size_t ol) {
     return gemv_host(TYPE_Q4_K, w, wl, rows, cols, in, il, 0, 1, out, ol, nullptr, nullptr);
+}
+int rnb_b200_q5k_gemv(const uint8_t *w, size_t wl, size_t rows, size_t cols, const float *in, size_t il, float *out, size_t ol) {
+    return gemv_host(TYPE_Q5_K, w, wl, rows, cols, in, il, 0, 1, out, ol, nullptr, nullptr);
+}
+int rnb_b200_q5k_gemv_batch(const uint8_t *w, size_t wl, size_t rows, size_t cols, const float *in, size_t il, float *out, size_t ol) {
+    if (cols == 0 || il % cols != 0) return fail(RNB_B200_VALIDATION_FAILED, "Q5_K input length mismatch: got %zu, not a multiple of cols %zu", il, cols);
+    return prefill_gemm_host(TYPE_Q5_K, w, wl, rows, cols, in, il / cols, out, ol);
 }
 int rnb_b200_q6k_gemv(const uint8_t *w, size_t wl, size_t rows, size_t cols, const float *in, size_t il, float *out, size_t ol) {
     return gemv_host(TYPE_Q6_K, w, wl, rows, cols, in, il, 0, 1, out, ol, nullptr, nullptr);
@@ -860,7 +873,8 @@ int rnb_b200_dense_attention_qkv_rope_hd128_decode(const uint8_t *q_w, size_t q_
 int rnb_b200_dense_q4k_silu_ffn_batch(const uint8_t *gate, size_t gate_len, const uint8_t *up, size_t up_len, const uint8_t *down,
                                       size_t down_len, uint32_t down_quant, size_t n_ff, size_t n_embd, size_t seq_len,
                                       const float *input, float *output) {
-    if (down_quant != TYPE_Q4_K && down_quant != TYPE_Q6_K) return fail(RNB_B200_UNSUPPORTED, "dense FFN: down quant %u not supported", down_quant);
+    if (down_quant != TYPE_Q4_K && down_quant != TYPE_Q5_K && down_quant != TYPE_Q6_K)
+        return fail(RNB_B200_UNSUPPORTED, "dense FFN: down quant %u not supported", down_quant);
     if (seq_len == 0) return fail(RNB_B200_VALIDATION_FAILED, "dense FFN: seq_len must be non-zero");
     RNB_TRY(validate_gemv(TYPE_Q4_K, gate_len, n_ff, n_embd, n_embd * seq_len, seq_len, n_ff * seq_len, true));
     RNB_TRY(validate_gemv(TYPE_Q4_K, up_len, n_ff, n_embd, n_embd * seq_len, seq_len, n_ff * seq_len, true));
@@ -891,8 +905,13 @@ int rnb_b200_dense_q4k_silu_ffn_batch(const uint8_t *gate, size_t gate_len, cons
     RNB_CU(launch_k(silu_mul_q8k_kernel, dim3((unsigned)((n_ff / 256 * seq_len + 3) / 4)), dim3(128), 0, st.stream,
                     (const float *)st.mid_a.p, (const float *)st.mid_b.p, (int)n_ff, (int)seq_len, (float *)nullptr, st.xq2.as<uint8_t>()));
     RNB_TRY(st.out_f32.ensure(n_embd * seq_len * 4));
-    GemvJob dj = make_job((int)down_quant, dd, st.xq2.p, st.out_f32.as<float>(), nullptr, n_embd, n_ff, 0, st.sm_count, (int)seq_len, q8k_dev_bytes(n_ff));
-    RNB_TRY(launch_gemv_one(st.stream, dj, n_ff, st.dev_error));
+    if (down_quant == TYPE_Q5_K) {
+        RNB_CU(launch_k(gemv_q5k_kernel, dim3((unsigned)((n_embd + G5_WARPS - 1) / G5_WARPS)), dim3(G5_WARPS * 32), 0, st.stream, dd,
+                        (const uint8_t *)st.xq2.p, q8k_dev_bytes(n_ff), st.out_f32.as<float>(), (int)n_embd, (int)n_ff, (int)seq_len));
+    } else {
+        GemvJob dj = make_job((int)down_quant, dd, st.xq2.p, st.out_f32.as<float>(), nullptr, n_embd, n_ff, 0, st.sm_count, (int)seq_len, q8k_dev_bytes(n_ff));
+        RNB_TRY(launch_gemv_one(st.stream, dj, n_ff, st.dev_error));
+    }
     return finish_to_host(st, st.out_f32.p, output, n_embd * seq_len * 4);
 }
 

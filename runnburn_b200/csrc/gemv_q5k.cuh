@@ -1,0 +1,99 @@
+// Q5_K x Q8_K matvec, bit-exact with rnb-cpu's AVX2 dot
+// (crates/rnb-cpu/src/gemm/avx2_dot.rs:698-789): eight f32 accumulator lanes per row (lane l sums
+// bytes 4l..4l+3 of every 32-byte group), one FMA per block in block order, the fold 4-2-1 at
+// the end, and the mins term kept as ONE scalar that takes a rounded product and a rounded sum
+// per block.  Block layout (176 bytes): d f16 | dmin f16 | scales[12] | qh[32] | qs[128]
+// (crates/rnb-cpu/src/quantize/blocks.rs:90-98); bit j of qh[i] is the fifth bit of element i of
+// sub-block j.
+//
+// One warp per row: its four 8-lane groups take four consecutive blocks at a time; integer lane
+// sums are exact in any order, the f32 chain is then replayed in block order with the four
+// blocks' values fetched by shuffle (every group carries the same accumulators).  Weights are
+// read straight from global memory with 4-byte loads: this kernel serves the formats beside the
+// Q4_K_M set and is built for parity first; it does not stage through shared memory.
+#pragma once
+#include "common.cuh"
+
+namespace rnb {
+
+constexpr int TYPE_Q5_K = 13;
+constexpr int Q5K_BYTES = 176;
+constexpr int G5_WARPS = 4;
+
+// xq: Q8K-dev layout of the activation (qs[cols] | bsum16[cols/16] | d[cols/256]); seq tokens, xq_stride bytes apart
+RNB_GLOBAL void __launch_bounds__(G5_WARPS * 32)
+gemv_q5k_kernel(const uint8_t *__restrict__ w, const uint8_t *__restrict__ xq, size_t xq_stride, float *__restrict__ y, int rows, int cols, int seq) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int row = blockIdx.x * G5_WARPS + warp;
+    if (row >= rows) return;
+    const int nb = cols >> 8, l = lane & 7, g = lane >> 3;
+    const uint8_t *wrow = w + (size_t)row * nb * Q5K_BYTES;
+    for (int s = 0; s < seq; s++) {
+        const uint8_t *x = xq + (size_t)s * xq_stride;
+        const int8_t *qs = reinterpret_cast<const int8_t *>(x);
+        const int16_t *bsum16 = reinterpret_cast<const int16_t *>(x + cols);
+        const float *xd = reinterpret_cast<const float *>(x + cols + 32 * nb);
+        float acc = 0.f, summs = 0.f;
+        for (int b0 = 0; b0 < nb; b0 += 4) {
+            const int b = b0 + g;
+            int sumi = 0;
+            float dd = 0.f, mprod = 0.f;
+            if (b < nb) {
+                const uint8_t *blk = wrow + (size_t)b * Q5K_BYTES;
+                const uint32_t hdr = *reinterpret_cast<const uint32_t *>(blk);
+                const float yd = xd[b];
+                dd = __fmul_rn(yd, __half2float(__ushort_as_half((unsigned short)(hdr & 0xffffu))));
+                const float dmin = __fmul_rn(-yd, __half2float(__ushort_as_half((unsigned short)(hdr >> 16))));
+                // 6-bit scales and mins of the eight sub-blocks (the reference's unpack of the 12 packed bytes)
+                uint32_t u0 = *reinterpret_cast<const uint32_t *>(blk + 4), u1 = *reinterpret_cast<const uint32_t *>(blk + 8),
+                         u2 = *reinterpret_cast<const uint32_t *>(blk + 12);
+                const uint32_t u3 = ((u2 >> 4) & 0x0f0f0f0fu) | (((u1 >> 6) & 0x03030303u) << 4);
+                const uint32_t ua = u1 & 0x3f3f3f3fu;
+                u1 = (u2 & 0x0f0f0f0fu) | (((u0 >> 6) & 0x03030303u) << 4);
+                u2 = ua;
+                u0 &= 0x3f3f3f3fu;
+                // scales: bytes of (u0, u1); mins: bytes of (u2, u3)
+                int msum = 0;
+#pragma unroll
+                for (int j = 0; j < 8; j++) {
+                    const int mn = (int)(((j < 4 ? u2 : u3) >> (8 * (j & 3))) & 0xffu);
+                    const int bs = (int)(short)(bsum16[b * 16 + 2 * j] + bsum16[b * 16 + 2 * j + 1]);   // 16-bit wrap as the AVX2 hadd
+                    msum += mn * bs;
+                }
+                mprod = __fmul_rn(dmin, (float)msum);
+                const uint32_t qh = *reinterpret_cast<const uint32_t *>(blk + 16 + 4 * l);
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    const uint32_t ql = *reinterpret_cast<const uint32_t *>(blk + 48 + 32 * j + 4 * l);
+                    const int v0 = (int)((ql & 0x0f0f0f0fu) | (((qh >> (2 * j)) & 0x01010101u) << 4));
+                    const int v1 = (int)(((ql >> 4) & 0x0f0f0f0fu) | (((qh >> (2 * j + 1)) & 0x01010101u) << 4));
+                    const int a0 = *reinterpret_cast<const int *>(qs + b * 256 + 64 * j + 4 * l);
+                    const int a1 = *reinterpret_cast<const int *>(qs + b * 256 + 64 * j + 32 + 4 * l);
+                    const int sc0 = (int)(((j < 2 ? u0 : u1) >> (8 * ((2 * j) & 3))) & 0xffu);
+                    const int sc1 = (int)(((j < 2 ? u0 : u1) >> (8 * ((2 * j + 1) & 3))) & 0xffu);
+                    sumi += sc0 * __dp4a(v0, a0, 0) + sc1 * __dp4a(v1, a1, 0);   // weights 0..31: positive as signed bytes
+                }
+            }
+            // the four blocks' FMAs in block order; every group ends up with the same eight lanes
+#pragma unroll
+            for (int gg = 0; gg < 4; gg++) {
+                const int si = __shfl_sync(0xffffffffu, sumi, l + 8 * gg);
+                const float di = __shfl_sync(0xffffffffu, dd, l + 8 * gg);
+                const float mi = __shfl_sync(0xffffffffu, mprod, l + 8 * gg);
+                if (b0 + gg < nb) {
+                    acc = __fmaf_rn(di, (float)si, acc);
+                    summs = __fadd_rn(summs, mi);
+                }
+            }
+        }
+        // fold: (l + l4) -> (+2) -> (+1), then the scalar mins term
+        float r = __fadd_rn(__shfl_sync(0xffffffffu, acc, (l + 4) & 7), acc);   // lanes 0..3: a[l+4] + a[l]
+        r = __fadd_rn(r, __shfl_sync(0xffffffffu, r, (l + 2) & 7));            // lanes 0, 1: (r0 + r2), (r1 + r3)
+        r = __fadd_rn(r, __shfl_sync(0xffffffffu, r, (l + 1) & 7));            // lane 0: s0 + s1
+        if (lane == 0) y[(size_t)s * rows + row] = __fadd_rn(r, summs);
+    }
+}
+
+}  // namespace rnb

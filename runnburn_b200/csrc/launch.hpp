@@ -8,6 +8,7 @@
 #include "gemv_pair.cuh"
 #include "gemv_ksplit.cuh"
 #include "gemv_mma.cuh"
+#include "gemv_q5k.cuh"
 #include "moe.cuh"
 #include "prefill_gemm.cuh"
 #include "q8k.cuh"

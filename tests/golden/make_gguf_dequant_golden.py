@@ -41,6 +41,12 @@ def main():
     x = rng.standard_normal((16, 64)).astype(np.float32)
     out["q8_0_quant_in"] = x
     out["q8_0_quant_bytes"] = quants.quantize(x, T.Q8_0)
+    # drawn after everything else so that the earlier vectors keep their bytes
+    q5 = rng.integers(0, 256, size=(n, 176), dtype=np.uint8)
+    q5[:, 0:2] = f16_bits(rng, n).view(np.uint8).reshape(n, 2)
+    q5[:, 2:4] = f16_bits(rng, n).view(np.uint8).reshape(n, 2)
+    out["q5k_bytes"] = q5
+    out["q5k_f32"] = quants.dequantize(q5, T.Q5_K).astype(np.float32)
     np.savez_compressed(Path(__file__).with_name("gguf_dequant.npz"), **out)
     print({k: v.shape for k, v in out.items()})
 

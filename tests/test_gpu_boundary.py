@@ -21,6 +21,14 @@ def ops():
     return o
 
 
+@pytest.fixture(autouse=True)
+def _fresh_weight_cache(ops):
+    """The resident cache is keyed by host address (weights are borrowed, immutable mmap pages in the
+    reference's contract); numpy reuses freed addresses, so every test starts from an empty cache."""
+    ops.reset_state_for_engine_init()
+    yield
+
+
 def quantized(rng, t, rows, cols):
     return orc.quantize_matrix(t, rng.standard_normal((rows, cols)).astype(np.float32) * 0.05)
 
@@ -195,3 +203,48 @@ def test_prefill_route_slots_equal_the_oracle_router(ops):
         assert np.array_equal(ids[s * k:(s + 1) * k], np.asarray(ri, np.uint32))
         assert np.array_equal(wts[s * k:(s + 1) * k], np.asarray(rw, np.float32))
         assert np.all(toks[s * k:(s + 1) * k] == s)
+
+
+Q5_K = 13
+
+
+@pytest.mark.parametrize("rows,cols", [(1, 256), (5, 512), (130, 1024), (1024, 4096), (4096, 14336), (33, 768)])
+def test_q5k_matvec_bit_exact(ops, rows, cols):
+    """Q5_K x Q8_K (crates/rnb-cpu/src/gemm/avx2_dot.rs:698-789): the device result equals the oracle's bit for
+    bit, on quantised N(0, 0.05) weights and on random block bytes (all scale / high-bit patterns)."""
+    rng = np.random.default_rng(rows * 7 + cols)
+    x = rng.standard_normal(cols).astype(np.float32)
+    w = orc.quantize_matrix(Q5_K, (rng.standard_normal((rows, cols)) * 0.05).astype(np.float32))
+    assert np.array_equal(ops.q5k_gemv(w, rows, cols, x).view(np.uint32), orc.gemv(Q5_K, w, x, rows, cols).view(np.uint32))
+    ops.clear_q4k_cache()        # `raw` may land on a freed array's address
+    raw = rng.integers(0, 256, size=(rows, cols // 256, 176), dtype=np.uint8)
+    raw[..., 1] = 0x10
+    raw[..., 3] = 0x10
+    raw = raw.reshape(-1)
+    assert np.array_equal(ops.q5k_gemv(raw, rows, cols, x).view(np.uint32), orc.gemv(Q5_K, raw, x, rows, cols).view(np.uint32))
+
+
+def test_q5k_batch_and_ffn_down_quant_13(ops):
+    import runnburn_b200 as r
+    rng = np.random.default_rng(77)
+    rows, cols, seq = 96, 1024, 3
+    w = orc.quantize_matrix(Q5_K, (rng.standard_normal((rows, cols)) * 0.05).astype(np.float32))
+    x = rng.standard_normal((seq, cols)).astype(np.float32)
+    got = ops.q5k_gemv_batch(w, rows, cols, x)
+    want = orc.gemv(Q5_K, w, x, rows, cols, seq_len=seq)
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+    # dense FFN with a Q5_K down matrix (ggml type id 13 of dense_q4k_silu_ffn_batch)
+    n_embd, n_ff = 512, 1024
+    g = orc.quantize_matrix(Q4_K, (rng.standard_normal((n_ff, n_embd)) * 0.05).astype(np.float32))
+    u = orc.quantize_matrix(Q4_K, (rng.standard_normal((n_ff, n_embd)) * 0.05).astype(np.float32))
+    d = orc.quantize_matrix(Q5_K, (rng.standard_normal((n_embd, n_ff)) * 0.05).astype(np.float32))
+    xs = rng.standard_normal((2, n_embd)).astype(np.float32)
+    out = ops.dense_q4k_silu_ffn_batch(g, u, d, Q5_K, n_ff, n_embd, 2, xs)
+    for s in range(2):
+        act = orc.silu_mul(orc.gemv(Q4_K, g, xs[s], n_ff, n_embd), orc.gemv(Q4_K, u, xs[s], n_ff, n_embd))
+        ref = orc.gemv(Q5_K, d, act, n_embd, n_ff)
+        assert np.array_equal(out[s * n_embd:(s + 1) * n_embd].view(np.uint32), ref.view(np.uint32))
+    with pytest.raises(r.RnbError, match="Q5_K cols must be divisible by 256"):
+        ops.q5k_gemv(np.zeros(176, np.uint8), 1, 100, np.zeros(100, np.float32))
+    with pytest.raises(r.RnbError, match="Q5_K weight byte mismatch"):
+        ops.q5k_gemv(np.zeros(100, np.uint8), 1, 256, np.zeros(256, np.float32))

@@ -108,7 +108,7 @@ def test_dequant_zero_blocks_and_q8_0_known(orc):
 
 def test_dequant_matches_gguf_package(orc):
     g = np.load(GOLD / "gguf_dequant.npz")
-    for name, t, cols in (("q4k", orc.TYPE_Q4_K, 256), ("q6k", orc.TYPE_Q6_K, 256),
+    for name, t, cols in (("q4k", orc.TYPE_Q4_K, 256), ("q5k", orc.TYPE_Q5_K, 256), ("q6k", orc.TYPE_Q6_K, 256),
                           ("q8_0", orc.TYPE_Q8_0, 32)):
         raw, want = g[f"{name}_bytes"], g[f"{name}_f32"]
         got = orc.dequantize_matrix(t, raw.ravel(), raw.shape[0], cols)
@@ -410,3 +410,34 @@ def test_reference_rms_norm_fixtures(orc):
             acc = np.float32(acc + vv * vv)
         rms32 = np.sqrt(np.float32(acc / np.float32(hidden)) + np.float32(1e-5))
         assert np.max(np.abs(got[s] - (xs / rms32) * wt)) < 2e-5
+
+
+def test_q5k_block_size_zero_block_and_dot_against_dequantised_q8k(orc):
+    """Q5_K (crates/rnb-cpu/src/quantize/blocks.rs:90-98: 176 bytes; dequant.rs test_dequant_q5_k_zero).
+    The integer dot equals the scalar dot over the dequantised weights and the dequantised Q8_K
+    activation to f32 rounding (the bound the reference uses for its int-dot tests), and the harness
+    quantiser round-trips through the reference's dequantiser."""
+    assert orc.row_bytes(orc.TYPE_Q5_K, 256) == 176
+    assert np.all(orc.dequantize_matrix(orc.TYPE_Q5_K, np.zeros(176, np.uint8), 1, 256) == 0.0)
+    rng = np.random.default_rng(55)
+    rows, cols = 6, 1024
+    w = (rng.standard_normal((rows, cols)) * 0.05).astype(np.float32)
+    q = orc.quantize_matrix(orc.TYPE_Q5_K, w)
+    back = orc.dequantize_matrix(orc.TYPE_Q5_K, q, rows, cols)
+    assert _cos(w.ravel(), back.ravel()) >= 0.999
+    x = rng.standard_normal(cols).astype(np.float32)
+    xq = orc.quantize_q8k(x)
+    blocks = xq.view(np.uint8).reshape(-1, 292)
+    xd = np.concatenate([blocks[b, :4].view(np.float32)[0] * blocks[b, 4:260].view(np.int8).astype(np.float32) for b in range(cols // 256)])
+    got = orc.gemv(orc.TYPE_Q5_K, q, x, rows, cols)
+    want = back.astype(np.float64) @ xd.astype(np.float64)
+    assert np.max(np.abs(got - want) / np.maximum(np.abs(want), 1e-3)) < 1e-4
+    # random blocks (all bit patterns of scales and high bits) as well
+    raw = rng.integers(0, 256, size=(rows, cols // 256, 176), dtype=np.uint8)
+    raw[..., 1] = 0x10
+    raw[..., 3] = 0x10
+    raw = raw.reshape(-1)
+    back = orc.dequantize_matrix(orc.TYPE_Q5_K, raw, rows, cols)
+    got = orc.gemv(orc.TYPE_Q5_K, raw, x, rows, cols)
+    want = back.astype(np.float64) @ xd.astype(np.float64)
+    assert np.max(np.abs(got - want)) < 1e-4 * np.max(np.abs(want))
