@@ -92,6 +92,7 @@ int gemv_kernel_setup() {
     RNB_CU(cudaFuncSetAttribute(gemv_ksplit_q6k_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn));
     RNB_CU(cudaFuncSetAttribute(gemv_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn));
     RNB_CU(cudaFuncSetAttribute(gemv_mma_kernel_1, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn));
+    RNB_CU(cudaFuncSetAttribute(gemv_mma_kernel_1_peer, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn));
     RNB_TRY(attention_exact_setup());
     g_gemv_smem_max = dyn;
     done = true;

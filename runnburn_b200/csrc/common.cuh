@@ -181,8 +181,11 @@ __device__ __forceinline__ void peer_arrive(const PeerOut &po) {
 }
 // All threads of the CTA call it (it synchronises the CTA): thread t < world waits, bounded, for
 // rank t's flag.  After a timeout the error word is set and later waits return at once.
+static __device__ __noinline__ void peer_wait_slow(const PeerWait &w);
 __device__ __forceinline__ void peer_wait(const PeerWait &w) {
-    if (!w.flags) return;
+    if (w.flags) peer_wait_slow(w);   // out of line: single-GPU launches pay one test
+}
+static __device__ __noinline__ void peer_wait_slow(const PeerWait &w) {
     const int t = threadIdx.x;
     if (t < w.world && t != w.rank && *reinterpret_cast<volatile int *>(w.err) == 0) {
         const int seq = *w.seq_ptr;

@@ -367,6 +367,9 @@ __device__ __forceinline__ bool gm_next(const GemvJob *__restrict__ jobs, int n_
     return gm_locate(jobs, n_jobs, c);
 }
 
+// PEER: the instantiation whose epilogue also stores the rows into the peers' buffers (sharded decode);
+// the single-GPU instantiation carries none of that code.
+template <bool PEER>
 __device__ __forceinline__ void gemv_mma_body(const GemvJob *__restrict__ jobs, int n_jobs, const GmParams &P, int *__restrict__ dev_error,
                                               const GpTail &tail, const GmTmaps *__restrict__ tmaps) {
     extern __shared__ __align__(128) uint8_t smem[];
@@ -642,7 +645,7 @@ __device__ __forceinline__ void gemv_mma_body(const GemvJob *__restrict__ jobs, 
                 if (epi == GEMV_EPI_NONE) {
                     if (live) {
                         job.y[o] = val;
-                        if (tail.kind == 2) peer_store(tail.peer, o, val);
+                        if (PEER && tail.kind == 2) peer_store(tail.peer, o, val);
                     }
                 } else {
                     // q/k/v: adjacent-pair RoPE and/or the f16 KV append on the rows just produced; rows 2i and
@@ -684,7 +687,7 @@ __device__ __forceinline__ void gemv_mma_body(const GemvJob *__restrict__ jobs, 
         s_abort = 1;
         atomicExch(dev_error, DEV_ERR_MBAR_TIMEOUT);
     }
-    if (tail.kind == 2 && !failed) {
+    if (PEER && tail.kind == 2 && !failed) {
         // every CTA of the grid arrives once, with or without tiles; the last raises the peers' flags
         __threadfence_system();
         __syncwarp();
@@ -697,12 +700,17 @@ gemv_mma_kernel(const GemvJob *__restrict__ jobs, int n_jobs, const GmParams P, 
     GpTail none;
     none.kind = 0;
     none.peer.peers = nullptr;
-    gemv_mma_body(jobs, n_jobs, P, dev_error, none, nullptr);
+    gemv_mma_body<false>(jobs, n_jobs, P, dev_error, none, nullptr);
 }
 RNB_GLOBAL void __launch_bounds__(GM_THREADS, GM_MIN_CTAS)
 gemv_mma_kernel_1(const __grid_constant__ GemvJobPack jobs, int n_jobs, const GmParams P, int *__restrict__ dev_error,
                   const __grid_constant__ GpTail tail, const __grid_constant__ GmTmaps tmaps) {
-    gemv_mma_body(jobs.j, n_jobs, P, dev_error, tail, &tmaps);
+    gemv_mma_body<false>(jobs.j, n_jobs, P, dev_error, tail, &tmaps);
+}
+RNB_GLOBAL void __launch_bounds__(GM_THREADS, GM_MIN_CTAS)
+gemv_mma_kernel_1_peer(const __grid_constant__ GemvJobPack jobs, int n_jobs, const GmParams P, int *__restrict__ dev_error,
+                       const __grid_constant__ GpTail tail, const __grid_constant__ GmTmaps tmaps) {
+    gemv_mma_body<true>(jobs.j, n_jobs, P, dev_error, tail, &tmaps);
 }
 
 }  // namespace rnb

@@ -327,7 +327,8 @@ inline int try_launch_gemv_mma(cudaStream_t s, const GemvJob *jobs_host, const G
                 const int rc = encode_weight_map(&tm.m[i], j.parts[0].w, (size_t)j.rows, row_bytes_of(j.type, cols), j.type == TYPE_Q4_K ? P.row_stride : P.row_stride6);
                 if (rc != RNB_B200_OK) return -rc;
             }
-        const cudaError_t e = launch_k(gemv_mma_kernel_1, dim3(grid), dim3(GM_THREADS), smem, s, pack, n_jobs, P, dev_error, t, tm);
+        const cudaError_t e = t.kind == 2 ? launch_k(gemv_mma_kernel_1_peer, dim3(grid), dim3(GM_THREADS), smem, s, pack, n_jobs, P, dev_error, t, tm)
+                                          : launch_k(gemv_mma_kernel_1, dim3(grid), dim3(GM_THREADS), smem, s, pack, n_jobs, P, dev_error, t, tm);
         if (e != cudaSuccess) return -fail_cuda(e, "gemv_mma_kernel launch");
     } else {
         if (t.kind) return -fail(RNB_B200_VALIDATION_FAILED, "matvec tail needs a by-value job table");
