@@ -416,7 +416,7 @@ def run_gpu(args, shape, ctx, name, rank, world, local_rank):
     max_ctx = ctx + (R + 1) * K + 2 * max(W, 3) + 8
     cfg = r.ModelConfig(max_ctx=max_ctx, world_size=world, rank=rank, **shape)
     dec = r.Decoder(cfg)
-    transport = os.environ.get("RNB_B200_TRANSPORT", "nccl")   # "nccl": ncclAllGather (measured faster); "peer": own peer-memory exchange kernels
+    transport = os.environ.get("RNB_B200_TRANSPORT", "peer")   # "peer": producers store their slices into the peers' buffers (measured faster at 4 GPUs, equal at 2); "nccl": ncclAllGather
     if world > 1 and transport == "nccl":
         ids = [nccl_unique_id() if rank == 0 else None]
         dist.broadcast_object_list(ids, src=0)
@@ -533,7 +533,7 @@ def run_gpu(args, shape, ctx, name, rank, world, local_rank):
         "higher_is_better": True, "scaling": "strong" if world > 1 else "weak",
         "vs_baseline": None, "dtype": "int8xint4->int32, f32 accumulate", "data": "synthetic",
         "config": {"workload": name, "context": ctx, "kv_cache": "f16", "weights": ("random-init N(0,0.02): attention and LM head Q6_K, f32 router, experts Q4_K, generated on device" if shape.get("n_expert", 0) else "random-init N(0,0.02), Q4_K_M layout (attn_v/ffn_down/output Q6_K), generated on device"),
-                   "parallelism": (f"row-sharded x{world}, all-gather by " + ("ncclAllGather" if transport == "nccl" else "peer-memory stores over NVLink (own kernel)")) if world > 1 else "single GPU",
+                   "parallelism": (f"row-sharded x{world}, all-gather by " + ("ncclAllGather" if transport == "nccl" else "peer-memory stores over NVLink from the producing kernels' epilogues, consumers wait on arrival flags (no exchange launch)")) if world > 1 else "single GPU",
                    "l2": "each step streams its whole weight set and KV cache (GBs), far more than the 126 MB L2: no flush needed",
                    "algorithmic_bytes_per_token": alg},
         "e2e": {"value": K / e2e_s, "unit": UNIT, "h2d_bytes_per_step": 8, "d2h_bytes_per_step": 8},
