@@ -416,7 +416,9 @@ def run_gpu(args, shape, ctx, name, rank, world, local_rank):
     max_ctx = ctx + (R + 1) * K + 2 * max(W, 3) + 8
     cfg = r.ModelConfig(max_ctx=max_ctx, world_size=world, rank=rank, **shape)
     dec = r.Decoder(cfg)
-    transport = os.environ.get("RNB_B200_TRANSPORT", "peer")   # "peer": producers store their slices into the peers' buffers (measured faster at 4 GPUs, equal at 2); "nccl": ncclAllGather
+    # "peer": producers store their slices into the peers' buffers (measured: 11.3 against 12.1 ms per token at 4 GPUs);
+    # "nccl": ncclAllGather (13.0 against 13.8 ms at 2 GPUs, where one peer makes the gather a single copy)
+    transport = os.environ.get("RNB_B200_TRANSPORT", "nccl" if world == 2 else "peer")
     if world > 1 and transport == "nccl":
         ids = [nccl_unique_id() if rank == 0 else None]
         dist.broadcast_object_list(ids, src=0)
