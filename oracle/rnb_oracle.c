@@ -1283,8 +1283,7 @@ void orc_attention_prefill_f16kv(const float *q, const uint16_t *k, const uint16
  * MoE routing: top-k by logit (descending; ties → lower expert id), weights = softmax over
  * the k selected logits in rank order.
  * crates/rnb-llm/src/engine/models/shared_expert_moe/routing.rs:18-62
- * The exponential is evaluated in double and rounded once, so that the device path (which
- * does the same) can match the weights bit for bit.
+ * The exponential is f32::exp, i.e. libm's expf, as in the reference.
  * ---------------------------------------------------------------------------------------- */
 size_t orc_moe_route_topk(const float *logits, size_t n_expert, size_t top_k, uint32_t *ids,
                           float *weights) {
@@ -1313,7 +1312,7 @@ size_t orc_moe_route_topk(const float *logits, size_t n_expert, size_t top_k, ui
     }
     float mx = best_vals[0], sum = 0.0f;
     for (size_t r = 0; r < sel; r++) {
-        float w = (float)exp((double)(best_vals[r] - mx));
+        float w = expf(best_vals[r] - mx);   /* f32::exp, routing.rs:50 */
         ids[r] = (uint32_t)best_ids[r];
         weights[r] = w;
         sum += w;

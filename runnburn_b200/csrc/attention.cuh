@@ -835,34 +835,6 @@ flash_decode_reduce_q8k_wide_kernel(const float *__restrict__ partials, int n_ch
 // f32.  The same evaluation here agrees with it on every input up to the binary64 rounding of
 // intermediate steps, which is 2^29 times finer than an f32 ulp.
 // ---------------------------------------------------------------------------------------------
-__device__ __constant__ unsigned long long c_exp2_tab32[32] = {   // bits(2^(i/32)) - (i << 47)
-    0x3ff0000000000000ull, 0x3fefd9b0d3158574ull, 0x3fefb5586cf9890full, 0x3fef9301d0125b51ull,
-    0x3fef72b83c7d517bull, 0x3fef54873168b9aaull, 0x3fef387a6e756238ull, 0x3fef1e9df51fdee1ull,
-    0x3fef06fe0a31b715ull, 0x3feef1a7373aa9cbull, 0x3feedea64c123422ull, 0x3feece086061892dull,
-    0x3feebfdad5362a27ull, 0x3feeb42b569d4f82ull, 0x3feeab07dd485429ull, 0x3feea47eb03a5585ull,
-    0x3feea09e667f3bcdull, 0x3fee9f75e8ec5f74ull, 0x3feea11473eb0187ull, 0x3feea589994cce13ull,
-    0x3feeace5422aa0dbull, 0x3feeb737b0cdc5e5ull, 0x3feec49182a3f090ull, 0x3feed503b23e255dull,
-    0x3feee89f995ad3adull, 0x3feeff76f2fb5e47ull, 0x3fef199bdd85529cull, 0x3fef3720dcef9069ull,
-    0x3fef5818dcfba487ull, 0x3fef7c97337b9b5full, 0x3fefa4afa2a490daull, 0x3fefd0765b6e4540ull,
-};
-// `tab` is a shared-memory copy of c_exp2_tab32 (the index differs per thread)
-__device__ __forceinline__ float expf_libm(float x, const unsigned long long *tab) {
-    if (x != x) return x;
-    if (x < -0x1.9fe368p6f) return 0.0f;            // below the smallest subnormal
-    if (x > 0x1.62e42ep6f) return INFINITY;
-    const double z = __dmul_rn(0x1.71547652b82fep+5, (double)x);   // x * 32 / ln 2
-    double kd = __dadd_rn(z, 0x1.8p52);                           // round to nearest integer
-    const unsigned long long ki = (unsigned long long)__double_as_longlong(kd);
-    kd = __dsub_rn(kd, 0x1.8p52);
-    const double r = __dsub_rn(z, kd);
-    const double s = __longlong_as_double((long long)(tab[ki & 31] + (ki << 47)));
-    const double p = __dadd_rn(__dmul_rn(0x1.c6af84b912394p-20, r), 0x1.ebfce50fac4f3p-13);
-    const double r2 = __dmul_rn(r, r);
-    double y = __dadd_rn(__dmul_rn(0x1.62e42ff0c52d6p-6, r), 1.0);
-    y = __dadd_rn(__dmul_rn(p, r2), y);
-    return __double2float_rn(__dmul_rn(y, s));
-}
-
 constexpr int AX_THREADS = 512;       // two heads per CTA
 constexpr int AX_MAX_LEN = 4096;      // scores of both heads: 2 * 4 bytes * 4096 positions = 32 KB
 constexpr int AX_STAGE_BYTES = 32768; // staged K or V rows: 128 positions of one KV head, or 64 of two
@@ -992,7 +964,7 @@ attention_decode_exact_kernel(const float *__restrict__ q, const uint16_t *__res
 #pragma unroll
     for (int i = 1; i < 8; i++) M = fmaxf(M, s_red[hs][i]);
     // pass 3: exponentials in parallel, their sum in position order by one thread per head
-    for (int j = th; j < kv_len; j += 256) sc[j] = expf_libm(__fsub_rn(sc[j], M), s_tab);
+    for (int j = th; j < kv_len; j += 256) sc[j] = expf_libm_smem(__fsub_rn(sc[j], M), s_tab);
     __syncthreads();
     if (th == 0) {
         float sum = 0.0f;

@@ -135,6 +135,50 @@ __device__ __forceinline__ float warp_max(float v) {
     return v;
 }
 
+// ---- expf as the C library of the reference's platform evaluates it --------------------------------
+// rnb-cpu calls f32::exp (libm's expf) in softmax, SiLU and the MoE routing weights.  glibc's
+// single-precision routine computes 2^(k/32) * P(r) in binary64 (a 32-entry table of 2^(i/32) and a
+// cubic in r) and rounds once to f32; it is NOT the correctly rounded exponential in about one input
+// in a thousand, so a device exp rounded from double differs from it there by one ulp.  The same
+// evaluation here agrees with libm on every input up to the binary64 rounding of intermediate steps,
+// which is 2^29 times finer than an f32 ulp (checked against the host libm on 262 million inputs).
+// (global memory, not the constant bank: the index differs per thread, and two cache lines serve a warp)
+static __device__ const unsigned long long c_exp2_tab32[32] = {   // bits(2^(i/32)) - (i << 47)
+    0x3ff0000000000000ull, 0x3fefd9b0d3158574ull, 0x3fefb5586cf9890full, 0x3fef9301d0125b51ull,
+    0x3fef72b83c7d517bull, 0x3fef54873168b9aaull, 0x3fef387a6e756238ull, 0x3fef1e9df51fdee1ull,
+    0x3fef06fe0a31b715ull, 0x3feef1a7373aa9cbull, 0x3feedea64c123422ull, 0x3feece086061892dull,
+    0x3feebfdad5362a27ull, 0x3feeb42b569d4f82ull, 0x3feeab07dd485429ull, 0x3feea47eb03a5585ull,
+    0x3feea09e667f3bcdull, 0x3fee9f75e8ec5f74ull, 0x3feea11473eb0187ull, 0x3feea589994cce13ull,
+    0x3feeace5422aa0dbull, 0x3feeb737b0cdc5e5ull, 0x3feec49182a3f090ull, 0x3feed503b23e255dull,
+    0x3feee89f995ad3adull, 0x3feeff76f2fb5e47ull, 0x3fef199bdd85529cull, 0x3fef3720dcef9069ull,
+    0x3fef5818dcfba487ull, 0x3fef7c97337b9b5full, 0x3fefa4afa2a490daull, 0x3fefd0765b6e4540ull,
+};
+// LOAD(i) returns table entry i: from global memory (expf_libm) or from a shared-memory copy where a whole CTA
+// evaluates at once (expf_libm_smem).
+template <class Load>
+__device__ __forceinline__ float expf_libm_with(float x, Load load) {
+    if (x != x) return x;
+    if (x < -0x1.9fe368p6f) return 0.0f;            // below the smallest subnormal
+    if (x > 0x1.62e42ep6f) return INFINITY;
+    const double z = __dmul_rn(0x1.71547652b82fep+5, (double)x);   // x * 32 / ln 2
+    double kd = __dadd_rn(z, 0x1.8p52);                           // round to nearest integer
+    const unsigned long long ki = (unsigned long long)__double_as_longlong(kd);
+    kd = __dsub_rn(kd, 0x1.8p52);
+    const double r = __dsub_rn(z, kd);
+    const double s = __longlong_as_double((long long)(load((int)(ki & 31)) + (ki << 47)));
+    const double p = __dadd_rn(__dmul_rn(0x1.c6af84b912394p-20, r), 0x1.ebfce50fac4f3p-13);
+    const double r2 = __dmul_rn(r, r);
+    double y = __dadd_rn(__dmul_rn(0x1.62e42ff0c52d6p-6, r), 1.0);
+    y = __dadd_rn(__dmul_rn(p, r2), y);
+    return __double2float_rn(__dmul_rn(y, s));
+}
+__device__ __forceinline__ float expf_libm(float x) {
+    return expf_libm_with(x, [](int i) { return __ldg(c_exp2_tab32 + i); });
+}
+__device__ __forceinline__ float expf_libm_smem(float x, const unsigned long long *tab) {
+    return expf_libm_with(x, [tab](int i) { return tab[i]; });
+}
+
 // ---- multi-GPU: a producer's epilogue stores its slice of a gathered f32 buffer straight into
 // every peer's copy (plain peer stores over NVLink; the buffers sit at the same offset of each
 // rank's IPC-mapped arena), and the consumer waits for the other ranks' slices in its prologue.

@@ -327,7 +327,7 @@ static __device__ __noinline__ void gm_silu_tail(const GpTail &tail, int blk, in
     float v[8];
 #pragma unroll
     for (int k = 0; k < 8; k++) {
-        const float e = (float)exp((double)(-gv[k]));   // exp in double, rounded once (as silu_mul_q8k_kernel)
+        const float e = expf_libm(-gv[k]);   // libm's expf (as silu_mul_q8k_kernel)
         v[k] = __fmul_rn(__fdiv_rn(gv[k], __fadd_rn(1.0f, e)), uv[k]);
     }
     Q8kDevView dv = q8k_dev_view(tail.xq_out, tail.n);

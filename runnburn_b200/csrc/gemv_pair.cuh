@@ -199,7 +199,7 @@ gemv_pair_q4k_kernel(const __grid_constant__ GemvJobPack jobs, int n_jobs, const
         float v[8];
 #pragma unroll
         for (int j = 0; j < 8; j++) {
-            const float e = (float)exp((double)(-gv[j]));   // as silu_mul_q8k_kernel: exp in double, rounded once
+            const float e = expf_libm(-gv[j]);   // as silu_mul_q8k_kernel: libm's expf
             v[j] = __fmul_rn(__fdiv_rn(gv[j], __fadd_rn(1.0f, e)), uv[j]);
         }
         Q8kDevView dv = q8k_dev_view(tail.xq_out, tail.n);

@@ -58,7 +58,7 @@ router_logits_kernel(const float *__restrict__ w, const float *__restrict__ h, i
 // logits in rank order: crates/rnb-llm/src/engine/models/shared_expert_moe/routing.rs:18-62;
 // same contract as the reference's rnb_moe_route_topk_f32
 // (crates/rnb-backend/cuda/cuda/kernels/quant_batch_and_ops.cuh:4782-4912).
-// One warp per token; n_expert <= 1024, top_k <= 32.  exp is taken in double and rounded once.
+// One warp per token; n_expert <= 1024, top_k <= 32.  exp is libm's expf (expf_libm), as the CPU's routing.
 // Returns the id this lane selected (lane r holds rank r; other lanes return 0).
 __device__ __forceinline__ uint32_t moe_route_topk_warp(const float *logits, int token, int n_expert, int top_k,
                                                         uint32_t *__restrict__ ids_out, float *__restrict__ weights_out) {
@@ -98,7 +98,7 @@ __device__ __forceinline__ uint32_t moe_route_topk_warp(const float *logits, int
         }
     }
     const float mx = __shfl_sync(0xffffffffu, my_val, 0);
-    float w = lane < sel ? (float)exp((double)__fsub_rn(my_val, mx)) : 0.0f;
+    float w = lane < sel ? expf_libm(__fsub_rn(my_val, mx)) : 0.0f;   // libm's expf, as the CPU's .exp()
     float sum = 0.0f;
     for (int r = 0; r < sel; r++) sum = __fadd_rn(sum, __shfl_sync(0xffffffffu, w, r));
     if (lane < sel) wts[lane] = sum != 0.0f ? __fdiv_rn(w, sum) : w;

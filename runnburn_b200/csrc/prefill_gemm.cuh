@@ -174,8 +174,8 @@ add_rmsnorm_bf16_kernel(float *__restrict__ x, const float *__restrict__ t, cons
     }
 }
 
-// silu(gate) * up (g / (1 + exp(-g)), crates/rnb-cpu/src/kernels/activation.rs:74-89, exp in double and
-// rounded once as in silu_mul_q8k_kernel) written straight as the bf16 token matrix of the down
+// silu(gate) * up (g / (1 + exp(-g)), crates/rnb-cpu/src/kernels/activation.rs:74-89, libm's expf as in
+// silu_mul_q8k_kernel) written straight as the bf16 token matrix of the down
 // matmul: the f32 value is rounded to bf16 exactly as f32_to_bf16_kernel would round it.
 RNB_GLOBAL void __launch_bounds__(256)
 silu_mul_bf16_kernel(const float *__restrict__ gate, const float *__restrict__ up, uint16_t *__restrict__ y, size_t n) {
@@ -189,7 +189,7 @@ silu_mul_bf16_kernel(const float *__restrict__ gate, const float *__restrict__ u
     float v[8];
 #pragma unroll
     for (int j = 0; j < 8; j++) {
-        const float e = (float)exp((double)(-gv[j]));
+        const float e = expf_libm(-gv[j]);
         v[j] = __fmul_rn(__fdiv_rn(gv[j], __fadd_rn(1.0f, e)), uv[j]);
     }
     *reinterpret_cast<uint4 *>(y + i) = make_uint4(pg_pack_bf16(v[0], v[1]), pg_pack_bf16(v[2], v[3]), pg_pack_bf16(v[4], v[5]), pg_pack_bf16(v[6], v[7]));

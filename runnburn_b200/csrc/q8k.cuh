@@ -202,8 +202,8 @@ rmsnorm_q8k_blocks_kernel(const float *__restrict__ x, const float *__restrict__
 }
 
 // act = silu(gate) * up with g / (1 + exp(-g)) (crates/rnb-cpu/src/kernels/activation.rs:74-89),
-// fused with Q8_K quantisation.  exp is evaluated in double and rounded once so that the
-// value fed to the quantiser is the correctly rounded one.
+// fused with Q8_K quantisation.  exp is libm's expf evaluated as the C library does (expf_libm),
+// so the value fed to the quantiser has the CPU's bits.
 RNB_GLOBAL void __launch_bounds__(128)
 silu_mul_q8k_kernel(const float *__restrict__ gate, const float *__restrict__ up, int n, int seq,
                     float *__restrict__ act_out, uint8_t *__restrict__ xq_out) {
@@ -219,7 +219,7 @@ silu_mul_q8k_kernel(const float *__restrict__ gate, const float *__restrict__ up
 #pragma unroll
     for (int j = 0; j < 8; j++) {
         const float g = gate[off + j];
-        const float e = (float)exp((double)(-g));
+        const float e = expf_libm(-g);   // libm's expf, as the CPU's (-g).exp()
         v[j] = __fmul_rn(__fdiv_rn(g, __fadd_rn(1.0f, e)), up[off + j]);
     }
     if (act_out) {

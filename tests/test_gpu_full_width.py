@@ -44,6 +44,29 @@ def test_llama3_8b_width_64_greedy_ids_identical(llama8b_width):
     ref.close()
 
 
+def test_llama3_8b_full_depth_32_layers_bit_identical():
+    """The whole Llama-3-8B shape (32 layers, hidden 4096, 32 / 8 heads, FFN 14336, vocab 128 256; 4.9 GB of
+    seeded Q4_K_M-layout weights): an 8-token prompt and 24 greedy steps, every logit vector, every id and
+    the last layer's K/V rows bit-identical to the oracle's model loop."""
+    import runnburn_b200 as r
+    from test_gpu_decoder import _assert_identical, _greedy
+    desc = llama_description_fast(seed=7, n_layer=32)
+    n_prompt, n_steps = 8, 24
+    dec = r.Decoder(r.ModelConfig(max_ctx=n_prompt + n_steps + 4, **desc["cfg"]))
+    dec.load_description(desc)
+    ref = orc.Model(desc, n_prompt + n_steps + 4)
+    prompt = np.random.default_rng(17).integers(0, desc["cfg"]["vocab"], n_prompt).tolist()
+    gpu_ids, cpu_ids, margins, errs = _greedy(dec, ref, prompt, n_steps)
+    _assert_identical(gpu_ids, cpu_ids, errs)
+    assert len(set(gpu_ids)) > 1                     # not a degenerate run
+    for layer in (0, 15, 31):
+        kg, vg = dec.read_kv(layer, n_prompt + n_steps)
+        kc, vc = ref.kv_cache(layer, n_prompt + n_steps)
+        assert np.array_equal(kg, kc) and np.array_equal(vg, vc)
+    dec.close()
+    ref.close()
+
+
 def test_llama3_8b_width_chunked_attention_kernel(llama8b_width):
     """The same stack with the reference-order attention kernel off, i.e. the kernel that serves
     long contexts: its ~1e-6 attention differences pass through Q8_K rounding, and at this width
