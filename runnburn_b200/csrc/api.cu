@@ -192,6 +192,10 @@ int State::transient_upload(const uint8_t *host, size_t len, const uint8_t **dev
 // tensors registered once); miss -> budget check, LRU eviction, allocate, upload.  Over-budget
 // weights are uploaded into a transient buffer of the current call
 // (crates/rnb-backend/cuda/src/runtime/state/q4k_cache.rs:757-851).
+// Weight slices that the calling thread's current operation must NOT admit into the residency cache (an expert
+// bundle that failed the admission test): a miss on one of them is staged for the call only.
+thread_local std::vector<std::pair<const uint8_t *, size_t>> tl_stage_only;
+
 int State::resident_ptr(const uint8_t *host, size_t len, bool pin, const uint8_t **dev_out) {
     ctr.lookups++;
     epoch++;
@@ -208,6 +212,8 @@ int State::resident_ptr(const uint8_t *host, size_t len, bool pin, const uint8_t
         }
     }
     ctr.misses++;
+    for (const auto &so : tl_stage_only)
+        if (so.first == host && so.second == len) return transient_upload(host, len, dev_out);
     if (len > resident_limit) {
         if (pin) return fail(RNB_B200_OUT_OF_MEMORY, "resident weight of %zu bytes exceeds the residency limit %zu", len, resident_limit);
         return transient_upload(host, len, dev_out);

@@ -130,14 +130,17 @@ def test_qkv_rope_prefill_equals_the_oracle_token_by_token(ops):
 
 
 def test_sparse_experts_into_miss_path_accounting_and_receipt(ops):
-    """A layer that is NOT registered: the first call sees full misses (observed once, so admission does not
-    pay yet under the reference's rule), later calls see history and residency; the receipt carries the
-    call's stats delta; the result equals the oracle's."""
+    """A layer that is NOT registered.  First sighting of a bundle: full miss, reuse history says 0, and under
+    the reference's rule (saved = missing x (reuses + 1) must EXCEED missing + reload) admission does not pay,
+    so the bytes are staged for the call only.  Second sighting: still a miss, history says 1, admitted.
+    Third: full hit, nothing crosses PCIe.  Every call's receipt carries its own stats delta and the result
+    equals the oracle's."""
     rng = np.random.default_rng(4)
     n_embd, n_ff, n_expert, k = 512, 256, 6, 2
     gate_all, up_all = quantized(rng, Q4_K, n_expert * n_ff, n_embd), quantized(rng, Q4_K, n_expert * n_ff, n_embd)
     down_all = quantized(rng, Q4_K, n_expert * n_embd, n_ff)
     gs, ds = n_ff * orc.row_bytes(Q4_K, n_embd), n_embd * orc.row_bytes(Q4_K, n_ff)
+    bundle = 2 * gs + ds
     x = rng.standard_normal(n_embd).astype(np.float32)
     ids = [4, 1]
     rw = np.array([0.7, 0.3], np.float32)
@@ -145,30 +148,37 @@ def test_sparse_experts_into_miss_path_accounting_and_receipt(ops):
     up = [up_all[e * gs:(e + 1) * gs] for e in ids]
     down = [down_all[e * ds:(e + 1) * ds] for e in ids]
     ref = orc.moe_experts(gate, up, down, rw, Q4_K, n_ff, n_embd, x)
-    ops.reset_state_for_engine_init()
     before = ops.qwen35_expert_cache_stats()
-    receipt = ops.ExpertReceipt()
-    got = ops.qwen35_sparse_experts_into(gate, up, down, rw, 3, ids, receipt, Q4_K, n_ff, n_embd, x)
+    snap0 = ops.cuda_cache_snapshot()
+    r1 = ops.ExpertReceipt()
+    got = ops.qwen35_sparse_experts_into(gate, up, down, rw, 3, ids, r1, Q4_K, n_ff, n_embd, x)
     assert max_rel_err(got, ref) <= 2e-3
-    d = receipt.pending_stats.as_dict()
-    assert receipt.consumed == 0 and d["bundle_lookups"] == k and d["bundle_misses"] == k and d["bundle_hits"] == 0
-    assert d["h2d_bytes"] + d["temp_h2d_bytes"] == k * (2 * gs + ds)
-    after = ops.qwen35_expert_cache_stats()
-    assert after["bundle_lookups"] - before["bundle_lookups"] == k
-    # the compute call made the slices resident (there was room): the same bundles are hits now
-    receipt2 = ops.ExpertReceipt()
+    d1 = r1.pending_stats.as_dict()
+    assert r1.consumed == 0 and d1["bundle_lookups"] == k and d1["bundle_misses"] == k and d1["bundle_hits"] == 0
+    assert d1["bundle_admissions"] == 0 and d1["temp_h2d_bytes"] == k * bundle and d1["h2d_bytes"] == 0
+    snap1 = ops.cuda_cache_snapshot()
+    assert snap1["resident_bytes"] == snap0["resident_bytes"] and snap1["transient_uploads"] - snap0["transient_uploads"] == 3 * k
+    r2 = ops.ExpertReceipt()
     res = rng.standard_normal(n_embd).astype(np.float32)
-    got2 = ops.qwen35_sparse_experts_into(gate, up, down, rw, 3, ids, receipt2, Q4_K, n_ff, n_embd, x, residual=res)
-    d2 = receipt2.pending_stats.as_dict()
-    assert d2["bundle_hits"] == k and d2["bundle_misses"] == 0 and d2["h2d_bytes"] == 0 and d2["temp_h2d_bytes"] == 0
+    got2 = ops.qwen35_sparse_experts_into(gate, up, down, rw, 3, ids, r2, Q4_K, n_ff, n_embd, x, residual=res)
+    d2 = r2.pending_stats.as_dict()
+    assert d2["bundle_misses"] == k and d2["bundle_admissions"] == k and d2["admitted_bytes"] == k * bundle and d2["temp_h2d_bytes"] == 0
     assert np.array_equal(got2, res + got)                     # residual + experts, f32
-    # no layer index: no history, still accounted
-    got3 = ops.qwen35_sparse_experts_into(gate, up, down, rw, None, None, None, Q4_K, n_ff, n_embd, x)
-    assert np.array_equal(got3, got)
+    assert ops.cuda_cache_snapshot()["resident_bytes"] - snap1["resident_bytes"] == k * bundle
+    r3 = ops.ExpertReceipt()
+    h2d = ops.cuda_cache_snapshot()["upload_bytes"]
+    got3 = ops.qwen35_sparse_experts_into(gate, up, down, rw, 3, ids, r3, Q4_K, n_ff, n_embd, x)
+    d3 = r3.pending_stats.as_dict()
+    assert d3["bundle_hits"] == k and d3["bundle_misses"] == 0 and d3["h2d_bytes"] == 0 and d3["temp_h2d_bytes"] == 0
+    assert ops.cuda_cache_snapshot()["upload_bytes"] == h2d and np.array_equal(got3, got)
+    after = ops.qwen35_expert_cache_stats()
+    assert after["bundle_lookups"] - before["bundle_lookups"] == 3 * k
+    # no layer index: no history is kept, the lookups are still accounted
+    got4 = ops.qwen35_sparse_experts_into(gate, up, down, rw, None, None, None, Q4_K, n_ff, n_embd, x)
+    assert np.array_equal(got4, got)
     import runnburn_b200 as r
     with pytest.raises(r.RnbError, match="needs the selected expert ids"):
         ops.qwen35_sparse_experts_into(gate, up, down, rw, 3, None, None, Q4_K, n_ff, n_embd, x)
-    ops.reset_state_for_engine_init()
 
 
 def test_admit_misses_async_configure_cache_and_residency_counters(ops):
