@@ -38,7 +38,7 @@ WORKLOADS = {
                                        n_ff_expert=768, rope_neox=1), 8192),
     "tiny-llama-ctx256": (dict(n_layer=2, hidden=512, n_head=4, n_kv_head=2, n_ff=1024, vocab=2048), 256),
 }
-DRAM_TRAFFIC_OVER_ALGORITHMIC = 574.6 / 570.6
+DRAM_TRAFFIC_OVER_ALGORITHMIC = 459.77 / 456.19   # ncu, gemv_mma_kernel_1: LM head + q/k/v + o launches (profiles/gemv_mma_kernel_llama3-8b-2layers-ctx4096.md)
 REPEATS = 5
 METRIC = "decode_tok_per_s_batch1"
 UNIT = "tok/s"
@@ -555,10 +555,10 @@ def run_gpu(args, shape, ctx, name, rank, world, local_rank):
         ach = per_launch_bytes / per_launch_s / 1e9
         out["roofline"] = {"kernel": "gemv_mma_kernel_1 (q/k/v, o, down, LM head: integer tensor-core matvec) and gemv_pair_q4k_kernel (gate/up)", "bound": "hbm", "achieved": ach, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                            "frac": ach / peaks["hbm_gbs"], "frac_of_8TBs_nominal": ach / 8000.0, "peak_source": peaks["source"],
-                           # DRAM read+write bytes per launch: the ncu capture of the five matvec shapes gave
-                           # 574.6 MB of traffic for 570.6 MB of algorithmic bytes (summary under profiles/)
+                           # DRAM read+write bytes per launch: the ncu capture of three matvec launches (LM head, q/k/v, o)
+                           # gave 459.8 MB of traffic for 456.2 MB of algorithmic bytes (summary under profiles/)
                            "traffic": per_launch_bytes * DRAM_TRAFFIC_OVER_ALGORITHMIC,
-                           "traffic_source": "ncu dram__bytes_read.sum+dram__bytes_write.sum of the five layer shapes, scaled by algorithmic bytes",
+                           "traffic_source": "ncu dram__bytes_read.sum+dram__bytes_write.sum of three launches of gemv_mma_kernel_1 (LM head, q/k/v, o), scaled by algorithmic bytes",
                            "launches_per_step": mv["launches_per_iter"],
                            "algorithmic_bytes_per_launch": per_launch_bytes, "avg_launch_us": per_launch_s * 1e6,
                            "how": "CUDA events around all matvec launches of a step on the decoder stream, model's own weights"}
