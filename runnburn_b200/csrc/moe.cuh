@@ -11,34 +11,39 @@ namespace rnb {
 // crates/rnb-cpu/src/gemm/f32_gemv.rs:215-237,266-275): thread j owns accumulator lane j of
 // the two 8-lane FMA registers, then lanes are folded 8, 4, 2, 1 apart.  Bit-identical
 // logits are what makes the selected expert ids identical.  hidden % 16 == 0.
-// The loads of a batch of 32 steps are issued together (the chain of FMAs is latency-bound on its
-// loads otherwise); the first batch of router weights is fetched before the wait on the previous
-// kernel, which only the hidden state depends on.  Any number of experts per CTA (blockDim / 16).
+// The loads of a batch of steps are issued together (the chain of FMAs is latency-bound on its
+// loads otherwise).  Any number of experts per CTA (blockDim / 16).
 __device__ __forceinline__ void router_logits_body(const float *__restrict__ w, const float *__restrict__ h, int n_expert,
                                                    int hidden, float *logits) {
     pdl_launch_dependents();
-    constexpr int B = 32;   // steps per batch: elements j, j + 16, ... j + 16 * 31
+    // WB steps of router weights per batch (elements j, j + 16, ...) are in registers before they are needed: the
+    // first batch is fetched before the wait on the previous kernel (a 2048-wide row is one batch, so nothing of the
+    // row is left to fetch after the wait); the hidden state follows in sub-batches of HB steps.
+    constexpr int WB = 128, HB = 64;
     const int j = threadIdx.x & 15;
     const int e = blockIdx.x * (blockDim.x >> 4) + (threadIdx.x >> 4);
     const bool live = e < n_expert;
     const float *wr = w + (size_t)(live ? e : 0) * hidden;
-    float wv[B];
-    const int full = hidden / (16 * B) * (16 * B);
+    float wv[WB];
+    const int full = hidden / (16 * WB) * (16 * WB);
     if (full > 0) {
 #pragma unroll
-        for (int u = 0; u < B; u++) wv[u] = __ldg(wr + u * 16 + j);
+        for (int u = 0; u < WB; u++) wv[u] = __ldg(wr + u * 16 + j);
     }
     pdl_wait();
     float acc = 0.0f;
-    for (int base = 0; base < full; base += 16 * B) {
-        float hv[B];
+    for (int base = 0; base < full; base += 16 * WB) {
 #pragma unroll
-        for (int u = 0; u < B; u++) hv[u] = h[base + u * 16 + j];
+        for (int sub = 0; sub < WB / HB; sub++) {
+            float hv[HB];
 #pragma unroll
-        for (int u = 0; u < B; u++) acc = __fmaf_rn(wv[u], hv[u], acc);
-        if (base + 16 * B < full) {
+            for (int u = 0; u < HB; u++) hv[u] = h[base + (sub * HB + u) * 16 + j];
 #pragma unroll
-            for (int u = 0; u < B; u++) wv[u] = __ldg(wr + base + 16 * B + u * 16 + j);
+            for (int u = 0; u < HB; u++) acc = __fmaf_rn(wv[sub * HB + u], hv[u], acc);
+        }
+        if (base + 16 * WB < full) {
+#pragma unroll
+            for (int u = 0; u < WB; u++) wv[u] = __ldg(wr + base + 16 * WB + u * 16 + j);
         }
     }
     for (int i = full + j; i < hidden; i += 16) acc = __fmaf_rn(wr[i], h[i], acc);
