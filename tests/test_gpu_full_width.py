@@ -30,6 +30,7 @@ def test_llama3_8b_width_64_greedy_ids_identical(llama8b_width):
     desc = llama8b_width
     n_prompt, n_steps = 16, 64
     dec = r.Decoder(r.ModelConfig(max_ctx=n_prompt + n_steps + 4, **desc["cfg"]))
+    dec.set_exact_attention_max(512)
     dec.load_description(desc)
     ref = orc.Model(desc, n_prompt + n_steps + 4)
     prompt = np.random.default_rng(11).integers(0, desc["cfg"]["vocab"], n_prompt).tolist()
@@ -53,6 +54,7 @@ def test_llama3_8b_full_depth_32_layers_bit_identical():
     desc = llama_description_fast(seed=7, n_layer=32)
     n_prompt, n_steps = 8, 24
     dec = r.Decoder(r.ModelConfig(max_ctx=n_prompt + n_steps + 4, **desc["cfg"]))
+    dec.set_exact_attention_max(512)
     dec.load_description(desc)
     ref = orc.Model(desc, n_prompt + n_steps + 4)
     prompt = np.random.default_rng(17).integers(0, desc["cfg"]["vocab"], n_prompt).tolist()
@@ -137,6 +139,7 @@ def test_qwen3_30b_a3b_width_expert_ids_and_tokens():
     desc = moe_description_fast(seed=5, n_layer=2)
     n_prompt, n_steps = 8, 24
     dec = r.Decoder(r.ModelConfig(max_ctx=n_prompt + n_steps + 4, **desc["cfg"]))
+    dec.set_exact_attention_max(512)
     dec.load_description(desc)
     ref = orc.Model(desc, n_prompt + n_steps + 4)
     prompt = np.random.default_rng(13).integers(0, desc["cfg"]["vocab"], n_prompt).tolist()
