@@ -96,6 +96,12 @@ int rnb_b200_q4k_gemv(const uint8_t *weights, size_t weights_len, size_t rows, s
  * crates/rnb-cpu/src/gemm/avx2_dot.rs:698-789), bit-exact; `down_quant` 13 of
  * rnb_b200_dense_q4k_silu_ffn_batch takes the same kernel.  _batch: input [seq][cols], output
  * seq-major. */
+/* Q2_K (GGML type 10, 84-byte blocks): QuantGemvType::Q2K -> dot_q2k_q8k_avx2
+ * (crates/rnb-cpu/src/gemm/avx2_dot.rs:169-245), bit-exact */
+int rnb_b200_q2k_gemv(const uint8_t *weights, size_t weights_len, size_t rows, size_t cols,
+                      const float *input, size_t input_len, float *output, size_t output_len);
+int rnb_b200_q2k_gemv_batch(const uint8_t *weights, size_t weights_len, size_t rows, size_t cols,
+                            const float *input, size_t input_len, float *output, size_t output_len);
 int rnb_b200_q5k_gemv(const uint8_t *weights, size_t weights_len, size_t rows, size_t cols,
                       const float *input, size_t input_len, float *output, size_t output_len);
 int rnb_b200_q5k_gemv_batch(const uint8_t *weights, size_t weights_len, size_t rows, size_t cols,

@@ -195,6 +195,22 @@ void orc_dequantize_q4k_block(const uint8_t *block, float *out) {
     }
 }
 
+/* Q2_K: crates/rnb-cpu/src/quantize/dequant.rs:66-86; block = scales[16] (low nibble scale, high
+ * nibble min) | qs[64] | d f16 | dmin f16 (crates/rnb-cpu/src/quantize/blocks.rs:63-69, 84 bytes).
+ * Each 128-element half interleaves four 32-element groups in its 32 bytes, two bits apiece. */
+void orc_dequantize_q2k_block(const uint8_t *block, float *out) {
+    float d = orc_f16_to_f32(rd_u16(block + 80));
+    float dmin = orc_f16_to_f32(rd_u16(block + 82));
+    const uint8_t *qs = block + 16;
+    for (int j = 0; j < 16; j++) {
+        uint8_t sc = block[j];
+        float scale = d * (float)(sc & 0x0F), mn = dmin * (float)(sc >> 4);
+        int half = j / 8, group = j % 8;
+        int q_base = half * 32 + (group % 2) * 16, shift = (group / 2) * 2;
+        for (int l = 0; l < 16; l++) out[j * 16 + l] = (float)((qs[q_base + l] >> shift) & 3) * scale - mn;
+    }
+}
+
 /* Q5_K: crates/rnb-cpu/src/quantize/dequant.rs:729-770; block = d f16 | dmin f16 | scales[12] |
  * qh[32] | qs[128] (crates/rnb-cpu/src/quantize/blocks.rs:90-98, 176 bytes) */
 void orc_dequantize_q5k_block(const uint8_t *block, float *out) {
@@ -248,6 +264,7 @@ void orc_dequantize_q8_0_block(const uint8_t *block, float *out) {
 
 size_t orc_row_bytes(int t, size_t cols) {
     switch (t) {
+    case ORC_TYPE_Q2_K: return cols / 256 * ORC_Q2K_BYTES;
     case ORC_TYPE_Q4_K: return cols / 256 * ORC_Q4K_BYTES;
     case ORC_TYPE_Q5_K: return cols / 256 * ORC_Q5K_BYTES;
     case ORC_TYPE_Q6_K: return cols / 256 * ORC_Q6K_BYTES;
@@ -261,6 +278,10 @@ int orc_dequantize_row(int t, const uint8_t *row, size_t cols, float *out) {
     case ORC_TYPE_Q4_K:
         for (size_t b = 0; b < cols / 256; b++)
             orc_dequantize_q4k_block(row + b * ORC_Q4K_BYTES, out + b * 256);
+        return 0;
+    case ORC_TYPE_Q2_K:
+        for (size_t b = 0; b < cols / 256; b++)
+            orc_dequantize_q2k_block(row + b * ORC_Q2K_BYTES, out + b * 256);
         return 0;
     case ORC_TYPE_Q5_K:
         for (size_t b = 0; b < cols / 256; b++)
@@ -481,6 +502,47 @@ void orc_quantize_row_q6k(const float *input, size_t n, uint8_t *output) {
 }
 
 /* Harness-only Q8_0 quantiser (GGML convention: d = amax/127, q = round(x/d)). */
+/* Q2_K quantiser: harness utility (the reference ships none): per 16-element sub-block a min/max fit
+ * on 0..3, 4-bit scales and mins against the block's largest; validated through the reference's
+ * dequantiser (round trip). */
+void orc_quantize_row_q2k(const float *input, size_t n, uint8_t *output) {
+    for (size_t b = 0; b < n / 256; b++) {
+        const float *x = input + b * 256;
+        uint8_t *blk = output + b * ORC_Q2K_BYTES;
+        float sc[16], mn[16], max_sc = 0.f, max_mn = 0.f;
+        for (int j = 0; j < 16; j++) {
+            float lo = 0.f, hi = x[16 * j];
+            for (int l = 0; l < 16; l++) {
+                if (x[16 * j + l] < lo) lo = x[16 * j + l];
+                if (x[16 * j + l] > hi) hi = x[16 * j + l];
+            }
+            sc[j] = (hi - lo) / 3.f;
+            mn[j] = -lo;
+            if (sc[j] > max_sc) max_sc = sc[j];
+            if (mn[j] > max_mn) max_mn = mn[j];
+        }
+        uint16_t dh = orc_f32_to_f16(max_sc / 15.f), mh = orc_f32_to_f16(max_mn / 15.f);
+        float d = orc_f16_to_f32(dh), dm = orc_f16_to_f32(mh);
+        memset(blk, 0, ORC_Q2K_BYTES);
+        blk[80] = (uint8_t)(dh & 0xff);
+        blk[81] = (uint8_t)(dh >> 8);
+        blk[82] = (uint8_t)(mh & 0xff);
+        blk[83] = (uint8_t)(mh >> 8);
+        for (int j = 0; j < 16; j++) {
+            int ls = clampi(d > 0.f ? nearest_int(sc[j] / d) : 0, 0, 15);
+            int lm = clampi(dm > 0.f ? nearest_int(mn[j] / dm) : 0, 0, 15);
+            blk[j] = (uint8_t)(ls | (lm << 4));
+            float dd = d * (float)ls, mm = dm * (float)lm;
+            int half = j / 8, group = j % 8;
+            int q_base = half * 32 + (group % 2) * 16, shift = (group / 2) * 2;
+            for (int l = 0; l < 16; l++) {
+                int q = dd > 0.f ? clampi(nearest_int((x[16 * j + l] + mm) / dd), 0, 3) : 0;
+                blk[16 + q_base + l] |= (uint8_t)(q << shift);
+            }
+        }
+    }
+}
+
 /* Q5_K quantiser: harness utility (the reference ships none).  Per 32-element sub-block a
  * min/max fit on 0..31, super-scales fitted to 6 bits, validated through the reference's
  * dequantiser (round trip). */
@@ -567,6 +629,7 @@ static void quant_rows(size_t b, size_t e, void *p) {
         const float *x = c->x + r * c->cols;
         uint8_t *o = c->out + r * rb;
         if (c->type == ORC_TYPE_Q4_K) orc_quantize_row_q4k(x, c->cols, o);
+        else if (c->type == ORC_TYPE_Q2_K) orc_quantize_row_q2k(x, c->cols, o);
         else if (c->type == ORC_TYPE_Q5_K) orc_quantize_row_q5k(x, c->cols, o);
         else if (c->type == ORC_TYPE_Q6_K) orc_quantize_row_q6k(x, c->cols, o);
         else orc_quantize_row_q8_0(x, c->cols, o);
@@ -650,6 +713,8 @@ static void synth_block(int type, uint64_t seed, uint64_t block_index, float sig
                 }
                 out[16 + 32 * g + l] = (uint8_t)(q[0] | (q[1] << 4));
             }
+    } else if (type == ORC_TYPE_Q2_K) {
+        orc_quantize_row_q2k(x, 256, out);
     } else if (type == ORC_TYPE_Q5_K) {
         orc_quantize_row_q5k(x, 256, out);
     } else if (type == ORC_TYPE_Q6_K) {
@@ -743,6 +808,34 @@ float orc_dot_q4k_q8k_lanes(const uint8_t *row, const orc_q8k_block *y, size_t n
     }
     float m0 = acc_m[0] + acc_m[2], m1 = acc_m[1] + acc_m[3];
     return hsum8(acc) + (m0 + m1);
+}
+
+/* Q2_K x Q8_K: crates/rnb-cpu/src/gemm/avx2_dot.rs:169-245.  Eight f32 accumulator lanes; per block first
+ * the mins term (lane l: mins[2l] * bsums[2l] + mins[2l+1] * bsums[2l+1], one FMA with dmin), then the
+ * quants (lane l = bytes 4l..4l+3 of each 32-byte chunk; chunk k of half h is the 2-bit plane k, its
+ * scale is sub-block 8h + 2k for lanes 0..3 and 8h + 2k + 1 for lanes 4..7), one FMA with d. */
+float orc_dot_q2k_q8k(const uint8_t *row, const orc_q8k_block *y, size_t nb) {
+    float acc[8] = {0};
+    for (size_t i = 0; i < nb; i++) {
+        const uint8_t *block = row + i * ORC_Q2K_BYTES;
+        const uint8_t *q2 = block + 16;
+        float d = y[i].d * orc_f16_to_f32(rd_u16(block + 80));
+        float dmin = -y[i].d * orc_f16_to_f32(rd_u16(block + 82));
+        for (int l = 0; l < 8; l++) {
+            int32_t prod = (int32_t)(block[2 * l] >> 4) * (int32_t)y[i].bsums[2 * l] + (int32_t)(block[2 * l + 1] >> 4) * (int32_t)y[i].bsums[2 * l + 1];
+            acc[l] = fmaf(dmin, (float)prod, acc[l]);
+        }
+        int32_t sumi[8] = {0};
+        for (int h = 0; h < 2; h++)
+            for (int k = 0; k < 4; k++)
+                for (int l = 0; l < 8; l++) {
+                    int32_t p = 0;
+                    for (int b = 0; b < 4; b++) p += (int32_t)((q2[32 * h + 4 * l + b] >> (2 * k)) & 3) * (int32_t)y[i].qs[128 * h + 32 * k + 4 * l + b];
+                    sumi[l] += (int32_t)(block[8 * h + 2 * k + (l >= 4)] & 0x0F) * p;
+                }
+        for (int l = 0; l < 8; l++) acc[l] = fmaf(d, (float)sumi[l], acc[l]);
+    }
+    return hsum8(acc);
 }
 
 /* Q5_K x Q8_K: crates/rnb-cpu/src/gemm/avx2_dot.rs:698-789.  Eight f32 accumulator lanes as for
@@ -1004,6 +1097,7 @@ static void gemv_rows(size_t b, size_t e, void *p) {
         for (size_t s = 0; s < c->seq_len; s++) {
             float v;
             if (c->type == ORC_TYPE_Q4_K) v = orc_dot_q4k_q8k(row, c->xq + s * c->nb, c->nb);
+            else if (c->type == ORC_TYPE_Q2_K) v = orc_dot_q2k_q8k(row, c->xq + s * c->nb, c->nb);
             else if (c->type == ORC_TYPE_Q5_K) v = orc_dot_q5k_q8k(row, c->xq + s * c->nb, c->nb);
             else if (c->type == ORC_TYPE_Q6_K) v = orc_dot_q6k_q8k(row, c->xq + s * c->nb, c->nb);
             else v = orc_dot_q8_0_row(row, c->x + s * c->cols, c->cols / 32);

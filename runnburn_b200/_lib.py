@@ -91,6 +91,8 @@ def load() -> C.CDLL:
         "rnb_b200_q4k_gemv": [vp, sz, sz, sz, vp, sz, vp, sz],
         "rnb_b200_q6k_gemv": [vp, sz, sz, sz, vp, sz, vp, sz],
         "rnb_b200_q5k_gemv": [vp, sz, sz, sz, vp, sz, vp, sz],
+        "rnb_b200_q2k_gemv": [vp, sz, sz, sz, vp, sz, vp, sz],
+        "rnb_b200_q2k_gemv_batch": [vp, sz, sz, sz, vp, sz, vp, sz],
         "rnb_b200_q5k_gemv_batch": [vp, sz, sz, sz, vp, sz, vp, sz],
         "rnb_b200_q8_0_gemv": [vp, sz, sz, sz, vp, sz, vp, sz],
         "rnb_b200_q4k_gemv_with_device_input": [vp, sz, sz, sz, u64, vp, sz],

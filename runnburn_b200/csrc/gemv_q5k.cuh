@@ -1,4 +1,4 @@
-// Q5_K x Q8_K matvec, bit-exact with rnb-cpu's AVX2 dot
+// Q5_K x Q8_K (and, below, Q2_K x Q8_K) matvec, bit-exact with rnb-cpu's AVX2 dots
 // (crates/rnb-cpu/src/gemm/avx2_dot.rs:698-789): eight f32 accumulator lanes per row (lane l sums
 // bytes 4l..4l+3 of every 32-byte group), one FMA per block in block order, the fold 4-2-1 at
 // the end, and the mins term kept as ONE scalar that takes a rounded product and a rounded sum
@@ -93,6 +93,73 @@ gemv_q5k_kernel(const uint8_t *__restrict__ w, const uint8_t *__restrict__ xq, s
         r = __fadd_rn(r, __shfl_sync(0xffffffffu, r, (l + 2) & 7));            // lanes 0, 1: (r0 + r2), (r1 + r3)
         r = __fadd_rn(r, __shfl_sync(0xffffffffu, r, (l + 1) & 7));            // lane 0: s0 + s1
         if (lane == 0) y[(size_t)s * rows + row] = __fadd_rn(r, summs);
+    }
+}
+
+// Q2_K x Q8_K, bit-exact with crates/rnb-cpu/src/gemm/avx2_dot.rs:169-245.  Block (84 bytes): scales[16]
+// (low nibble scale, high nibble min) | qs[64] | d f16 | dmin f16 (crates/rnb-cpu/src/quantize/blocks.rs:63-69).
+// Eight accumulator lanes; per block first the mins term (lane l: min[2l] * bsum[2l] + min[2l+1] * bsum[2l+1],
+// one FMA with dmin), then the quants (lane l = bytes 4l..4l+3 of each 32-byte chunk; chunk k of half h is the
+// 2-bit plane k and takes sub-block scale 8h + 2k for lanes 0..3, 8h + 2k + 1 for lanes 4..7), one FMA with d.
+// Same warp-per-row scheme as the Q5_K kernel above.
+constexpr int TYPE_Q2_K = 10;
+constexpr int Q2K_BYTES = 84;
+RNB_GLOBAL void __launch_bounds__(G5_WARPS * 32)
+gemv_q2k_kernel(const uint8_t *__restrict__ w, const uint8_t *__restrict__ xq, size_t xq_stride, float *__restrict__ y, int rows, int cols, int seq) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int row = blockIdx.x * G5_WARPS + warp;
+    if (row >= rows) return;
+    const int nb = cols >> 8, l = lane & 7, g = lane >> 3;
+    const uint8_t *wrow = w + (size_t)row * nb * Q2K_BYTES;
+    for (int s = 0; s < seq; s++) {
+        const uint8_t *x = xq + (size_t)s * xq_stride;
+        const int8_t *qs = reinterpret_cast<const int8_t *>(x);
+        const int16_t *bsum16 = reinterpret_cast<const int16_t *>(x + cols);
+        const float *xd = reinterpret_cast<const float *>(x + cols + 32 * nb);
+        float acc = 0.f;
+        for (int b0 = 0; b0 < nb; b0 += 4) {
+            const int b = b0 + g;
+            int sumi = 0, prod = 0;
+            float dd = 0.f, dmin = 0.f;
+            if (b < nb) {
+                const uint8_t *blk = wrow + (size_t)b * Q2K_BYTES;
+                const uint32_t tail = *reinterpret_cast<const uint32_t *>(blk + 80);
+                const float yd = xd[b];
+                dd = __fmul_rn(yd, __half2float(__ushort_as_half((unsigned short)(tail & 0xffffu))));
+                dmin = __fmul_rn(-yd, __half2float(__ushort_as_half((unsigned short)(tail >> 16))));
+                const uint32_t sc_lo = *reinterpret_cast<const uint32_t *>(blk + ((2 * l) & ~3));   // holds scales bytes 2l, 2l + 1
+                const int m0 = (int)((sc_lo >> (8 * ((2 * l) & 3) + 4)) & 0xfu), m1 = (int)((sc_lo >> (8 * ((2 * l + 1) & 3) + 4)) & 0xfu);
+                prod = m0 * (int)bsum16[b * 16 + 2 * l] + m1 * (int)bsum16[b * 16 + 2 * l + 1];
+#pragma unroll
+                for (int h = 0; h < 2; h++) {
+                    const uint32_t q2 = *reinterpret_cast<const uint32_t *>(blk + 16 + 32 * h + 4 * l);
+                    const uint32_t scw = *reinterpret_cast<const uint32_t *>(blk + 8 * h), scw2 = *reinterpret_cast<const uint32_t *>(blk + 8 * h + 4);
+#pragma unroll
+                    for (int k = 0; k < 4; k++) {
+                        const int v = (int)((q2 >> (2 * k)) & 0x03030303u);
+                        const int a = *reinterpret_cast<const int *>(qs + b * 256 + 128 * h + 32 * k + 4 * l);
+                        const int si = 2 * k + (l >= 4);                                        // sub-block within the half
+                        const int sc = (int)(((si < 4 ? scw : scw2) >> (8 * (si & 3))) & 0xfu);
+                        sumi += sc * __dp4a(v, a, 0);
+                    }
+                }
+            }
+#pragma unroll
+            for (int gg = 0; gg < 4; gg++) {
+                const int pi = __shfl_sync(0xffffffffu, prod, l + 8 * gg), si = __shfl_sync(0xffffffffu, sumi, l + 8 * gg);
+                const float di = __shfl_sync(0xffffffffu, dd, l + 8 * gg), mi = __shfl_sync(0xffffffffu, dmin, l + 8 * gg);
+                if (b0 + gg < nb) {
+                    acc = __fmaf_rn(mi, (float)pi, acc);
+                    acc = __fmaf_rn(di, (float)si, acc);
+                }
+            }
+        }
+        float r = __fadd_rn(__shfl_sync(0xffffffffu, acc, (l + 4) & 7), acc);
+        r = __fadd_rn(r, __shfl_sync(0xffffffffu, r, (l + 2) & 7));
+        r = __fadd_rn(r, __shfl_sync(0xffffffffu, r, (l + 1) & 7));
+        if (lane == 0) y[(size_t)s * rows + row] = r;
     }
 }
 

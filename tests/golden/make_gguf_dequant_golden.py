@@ -47,6 +47,11 @@ def main():
     q5[:, 2:4] = f16_bits(rng, n).view(np.uint8).reshape(n, 2)
     out["q5k_bytes"] = q5
     out["q5k_f32"] = quants.dequantize(q5, T.Q5_K).astype(np.float32)
+    q2 = rng.integers(0, 256, size=(n, 84), dtype=np.uint8)
+    q2[:, 80:82] = f16_bits(rng, n).view(np.uint8).reshape(n, 2)
+    q2[:, 82:84] = f16_bits(rng, n).view(np.uint8).reshape(n, 2)
+    out["q2k_bytes"] = q2
+    out["q2k_f32"] = quants.dequantize(q2, T.Q2_K).astype(np.float32)
     np.savez_compressed(Path(__file__).with_name("gguf_dequant.npz"), **out)
     print({k: v.shape for k, v in out.items()})
 

@@ -258,3 +258,25 @@ def test_q5k_batch_and_ffn_down_quant_13(ops):
         ops.q5k_gemv(np.zeros(176, np.uint8), 1, 100, np.zeros(100, np.float32))
     with pytest.raises(r.RnbError, match="Q5_K weight byte mismatch"):
         ops.q5k_gemv(np.zeros(100, np.uint8), 1, 256, np.zeros(256, np.float32))
+
+
+Q2_K = 10
+
+
+@pytest.mark.parametrize("rows,cols", [(1, 256), (5, 512), (33, 768), (130, 1024), (1024, 4096), (2048, 768)])
+def test_q2k_matvec_bit_exact(ops, rows, cols):
+    """Q2_K x Q8_K (crates/rnb-cpu/src/gemm/avx2_dot.rs:169-245): bit for bit the oracle's, on fitted weights
+    and on random block bytes; the batched form likewise."""
+    rng = np.random.default_rng(rows * 11 + cols)
+    x = rng.standard_normal(cols).astype(np.float32)
+    w = orc.quantize_matrix(Q2_K, (rng.standard_normal((rows, cols)) * 0.05).astype(np.float32))
+    assert np.array_equal(ops.q2k_gemv(w, rows, cols, x).view(np.uint32), orc.gemv(Q2_K, w, x, rows, cols).view(np.uint32))
+    ops.clear_q4k_cache()
+    raw = rng.integers(0, 256, size=(rows, cols // 256, 84), dtype=np.uint8)
+    raw[..., 81] = 0x10
+    raw[..., 83] = 0x10
+    raw = raw.reshape(-1)
+    assert np.array_equal(ops.q2k_gemv(raw, rows, cols, x).view(np.uint32), orc.gemv(Q2_K, raw, x, rows, cols).view(np.uint32))
+    xs = rng.standard_normal((2, cols)).astype(np.float32)
+    got = ops.q2k_gemv_batch(raw, rows, cols, xs)
+    assert np.array_equal(got.view(np.uint32), orc.gemv(Q2_K, raw, xs, rows, cols, seq_len=2).view(np.uint32))
