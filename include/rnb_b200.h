@@ -102,6 +102,12 @@ int rnb_b200_q2k_gemv(const uint8_t *weights, size_t weights_len, size_t rows, s
                       const float *input, size_t input_len, float *output, size_t output_len);
 int rnb_b200_q2k_gemv_batch(const uint8_t *weights, size_t weights_len, size_t rows, size_t cols,
                             const float *input, size_t input_len, float *output, size_t output_len);
+/* Q3_K (GGML type 11, 110-byte blocks, 2-byte aligned): QuantGemvType::Q3K -> dot_q3k_q8k_avx2
+ * (crates/rnb-cpu/src/gemm/avx2_dot.rs:247-378), bit-exact */
+int rnb_b200_q3k_gemv(const uint8_t *weights, size_t weights_len, size_t rows, size_t cols,
+                      const float *input, size_t input_len, float *output, size_t output_len);
+int rnb_b200_q3k_gemv_batch(const uint8_t *weights, size_t weights_len, size_t rows, size_t cols,
+                            const float *input, size_t input_len, float *output, size_t output_len);
 int rnb_b200_q5k_gemv(const uint8_t *weights, size_t weights_len, size_t rows, size_t cols,
                       const float *input, size_t input_len, float *output, size_t output_len);
 int rnb_b200_q5k_gemv_batch(const uint8_t *weights, size_t weights_len, size_t rows, size_t cols,

@@ -17,6 +17,7 @@ _LIB_PATH = _HERE / "librnb_oracle.so"
 
 TYPE_Q8_0 = 8
 TYPE_Q2_K = 10
+TYPE_Q3_K = 11
 TYPE_Q4_K = 12
 TYPE_Q5_K = 13
 TYPE_Q6_K = 14
@@ -63,7 +64,7 @@ def _declare(L):
     L.orc_quantize_matrix.restype = i32
     L.orc_synth_matrix.argtypes = [i32, sz, sz, C.c_uint64, C.c_float, vp, i32]
     L.orc_synth_matrix.restype = i32
-    for n in ("orc_dot_q2k_q8k", "orc_dot_q4k_q8k", "orc_dot_q5k_q8k", "orc_dot_q6k_q8k", "orc_dot_q4k_q8k_lanes", "orc_dot_q6k_q8k_lanes"):
+    for n in ("orc_dot_q2k_q8k", "orc_dot_q3k_q8k", "orc_dot_q4k_q8k", "orc_dot_q5k_q8k", "orc_dot_q6k_q8k", "orc_dot_q4k_q8k_lanes", "orc_dot_q6k_q8k_lanes"):
         getattr(L, n).restype = f32
         getattr(L, n).argtypes = [vp, vp, sz]
     L.orc_dot_q8_0_row.restype = f32
@@ -181,7 +182,7 @@ def dequantize_matrix(ggml_type: int, data, rows: int, cols: int) -> np.ndarray:
 # ---- dots / GEMV ---------------------------------------------------------------------------
 def dot_row(ggml_type: int, row, xq: np.ndarray, lanes: bool = False) -> float:
     row = _u8(row)
-    name = {TYPE_Q2_K: "orc_dot_q2k_q8k", TYPE_Q4_K: "orc_dot_q4k_q8k", TYPE_Q5_K: "orc_dot_q5k_q8k", TYPE_Q6_K: "orc_dot_q6k_q8k"}[ggml_type]
+    name = {TYPE_Q2_K: "orc_dot_q2k_q8k", TYPE_Q3_K: "orc_dot_q3k_q8k", TYPE_Q4_K: "orc_dot_q4k_q8k", TYPE_Q5_K: "orc_dot_q5k_q8k", TYPE_Q6_K: "orc_dot_q6k_q8k"}[ggml_type]
     if lanes:
         name += "_lanes"
     return float(getattr(lib(), name)(_p(row), _p(xq), xq.size))

@@ -211,6 +211,48 @@ void orc_dequantize_q2k_block(const uint8_t *block, float *out) {
     }
 }
 
+/* Q3_K: crates/rnb-cpu/src/quantize/dequant.rs:237-297; block = hmask[32] | qs[64] | scales[12] | d f16
+ * (crates/rnb-cpu/src/quantize/blocks.rs:72-78, 110 bytes).  16 six-bit scales (bias 32); element =
+ * 2 low bits minus 4 where its hmask bit is CLEAR. */
+static void q3k_scales(const uint8_t *sb, int8_t scales[16]) {
+    const uint32_t kmask1 = 0x03030303u, kmask2 = 0x0f0f0f0fu;
+    uint32_t aux[4];
+    aux[0] = rd_u32(sb);
+    aux[1] = rd_u32(sb + 4);
+    aux[2] = rd_u32(sb + 8);
+    uint32_t tmp = aux[2];
+    aux[2] = ((aux[0] >> 4) & kmask2) | (((tmp >> 4) & kmask1) << 4);
+    aux[3] = ((aux[1] >> 4) & kmask2) | (((tmp >> 6) & kmask1) << 4);
+    aux[0] = (aux[0] & kmask2) | (((tmp >> 0) & kmask1) << 4);
+    aux[1] = (aux[1] & kmask2) | (((tmp >> 2) & kmask1) << 4);
+    for (int i = 0; i < 4; i++)
+        for (int j = 0; j < 4; j++) scales[i * 4 + j] = (int8_t)((aux[i] >> (8 * j)) & 0xff);
+}
+void orc_dequantize_q3k_block(const uint8_t *block, float *out) {
+    float d_all = orc_f16_to_f32(rd_u16(block + 108));
+    int8_t scales[16];
+    q3k_scales(block + 96, scales);
+    const uint8_t *hm = block, *q = block + 32;
+    int is = 0, y_idx = 0, q_off = 0;
+    uint8_t m = 1;
+    for (int half = 0; half < 2; half++) {
+        int shift = 0;
+        for (int k = 0; k < 4; k++) {
+            for (int part = 0; part < 2; part++) {
+                float dl = d_all * ((float)scales[is++] - 32.0f);
+                for (int l = 0; l < 16; l++) {
+                    int qv = (q[q_off + l + 16 * part] >> shift) & 3;
+                    int hv = (hm[l + 16 * part] & m) ? 0 : 4;
+                    out[y_idx++] = dl * (float)(qv - hv);
+                }
+            }
+            shift += 2;
+            m = (uint8_t)(m << 1);
+        }
+        q_off += 32;
+    }
+}
+
 /* Q5_K: crates/rnb-cpu/src/quantize/dequant.rs:729-770; block = d f16 | dmin f16 | scales[12] |
  * qh[32] | qs[128] (crates/rnb-cpu/src/quantize/blocks.rs:90-98, 176 bytes) */
 void orc_dequantize_q5k_block(const uint8_t *block, float *out) {
@@ -265,6 +307,7 @@ void orc_dequantize_q8_0_block(const uint8_t *block, float *out) {
 size_t orc_row_bytes(int t, size_t cols) {
     switch (t) {
     case ORC_TYPE_Q2_K: return cols / 256 * ORC_Q2K_BYTES;
+    case ORC_TYPE_Q3_K: return cols / 256 * ORC_Q3K_BYTES;
     case ORC_TYPE_Q4_K: return cols / 256 * ORC_Q4K_BYTES;
     case ORC_TYPE_Q5_K: return cols / 256 * ORC_Q5K_BYTES;
     case ORC_TYPE_Q6_K: return cols / 256 * ORC_Q6K_BYTES;
@@ -282,6 +325,10 @@ int orc_dequantize_row(int t, const uint8_t *row, size_t cols, float *out) {
     case ORC_TYPE_Q2_K:
         for (size_t b = 0; b < cols / 256; b++)
             orc_dequantize_q2k_block(row + b * ORC_Q2K_BYTES, out + b * 256);
+        return 0;
+    case ORC_TYPE_Q3_K:
+        for (size_t b = 0; b < cols / 256; b++)
+            orc_dequantize_q3k_block(row + b * ORC_Q3K_BYTES, out + b * 256);
         return 0;
     case ORC_TYPE_Q5_K:
         for (size_t b = 0; b < cols / 256; b++)
@@ -543,6 +590,57 @@ void orc_quantize_row_q2k(const float *input, size_t n, uint8_t *output) {
     }
 }
 
+/* Q3_K quantiser: harness utility (the reference ships none): per 16-element sub-block a symmetric
+ * fit on -4..3, six-bit scales (bias 32) against the block's largest; validated through the reference's
+ * dequantiser (round trip). */
+void orc_quantize_row_q3k(const float *input, size_t n, uint8_t *output) {
+    for (size_t b = 0; b < n / 256; b++) {
+        const float *x = input + b * 256;
+        uint8_t *blk = output + b * ORC_Q3K_BYTES;
+        float sc[16], max_sc = 0.f;
+        for (int j = 0; j < 16; j++) {
+            float amax = 0.f;
+            for (int l = 0; l < 16; l++) {
+                float a = fabsf(x[16 * j + l]);
+                if (a > amax) amax = a;
+            }
+            sc[j] = amax / 4.f;
+            if (sc[j] > max_sc) max_sc = sc[j];
+        }
+        uint16_t dh = orc_f32_to_f16(max_sc / 31.f);
+        float d = orc_f16_to_f32(dh);
+        memset(blk, 0, ORC_Q3K_BYTES);
+        blk[108] = (uint8_t)(dh & 0xff);
+        blk[109] = (uint8_t)(dh >> 8);
+        int ls[16];
+        for (int j = 0; j < 16; j++) ls[j] = clampi(d > 0.f ? nearest_int(sc[j] / d) : 0, 0, 31) + 32;   /* stored biased, 32..63 */
+        /* 6-bit packing: low nibbles of scales 0..7 in bytes 0..7 (low), of 8..15 in their high nibbles;
+         * the two top bits of scale j in byte 8 + j % 4 at bit pair j / 4 */
+        uint8_t *sb = blk + 96;
+        for (int j = 0; j < 16; j++) {
+            int lo = ls[j] & 0xF, hi = ls[j] >> 4;
+            if (j < 8) sb[j] |= (uint8_t)lo;
+            else sb[j - 8] |= (uint8_t)(lo << 4);
+            sb[8 + j % 4] |= (uint8_t)(hi << (2 * (j / 4)));
+        }
+        uint8_t *hm = blk, *q = blk + 32;
+        /* element order of the dequantiser: half, plane k, part (16 elements) */
+        int y_idx = 0, is = 0;
+        for (int half = 0; half < 2; half++)
+            for (int k = 0; k < 4; k++)
+                for (int part = 0; part < 2; part++) {
+                    float dl = d * (float)(ls[is++] - 32);
+                    for (int l = 0; l < 16; l++) {
+                        int v = dl != 0.f ? clampi(nearest_int(x[y_idx] / dl), -4, 3) : 0;
+                        y_idx++;
+                        int qv = v & 3;                       /* two low bits of v + 4 */
+                        if (v >= 0) hm[l + 16 * part] |= (uint8_t)(1u << (4 * half + k));
+                        q[32 * half + l + 16 * part] |= (uint8_t)(qv << (2 * k));
+                    }
+                }
+    }
+}
+
 /* Q5_K quantiser: harness utility (the reference ships none).  Per 32-element sub-block a
  * min/max fit on 0..31, super-scales fitted to 6 bits, validated through the reference's
  * dequantiser (round trip). */
@@ -630,6 +728,7 @@ static void quant_rows(size_t b, size_t e, void *p) {
         uint8_t *o = c->out + r * rb;
         if (c->type == ORC_TYPE_Q4_K) orc_quantize_row_q4k(x, c->cols, o);
         else if (c->type == ORC_TYPE_Q2_K) orc_quantize_row_q2k(x, c->cols, o);
+        else if (c->type == ORC_TYPE_Q3_K) orc_quantize_row_q3k(x, c->cols, o);
         else if (c->type == ORC_TYPE_Q5_K) orc_quantize_row_q5k(x, c->cols, o);
         else if (c->type == ORC_TYPE_Q6_K) orc_quantize_row_q6k(x, c->cols, o);
         else orc_quantize_row_q8_0(x, c->cols, o);
@@ -715,6 +814,8 @@ static void synth_block(int type, uint64_t seed, uint64_t block_index, float sig
             }
     } else if (type == ORC_TYPE_Q2_K) {
         orc_quantize_row_q2k(x, 256, out);
+    } else if (type == ORC_TYPE_Q3_K) {
+        orc_quantize_row_q3k(x, 256, out);
     } else if (type == ORC_TYPE_Q5_K) {
         orc_quantize_row_q5k(x, 256, out);
     } else if (type == ORC_TYPE_Q6_K) {
@@ -832,6 +933,34 @@ float orc_dot_q2k_q8k(const uint8_t *row, const orc_q8k_block *y, size_t nb) {
                     int32_t p = 0;
                     for (int b = 0; b < 4; b++) p += (int32_t)((q2[32 * h + 4 * l + b] >> (2 * k)) & 3) * (int32_t)y[i].qs[128 * h + 32 * k + 4 * l + b];
                     sumi[l] += (int32_t)(block[8 * h + 2 * k + (l >= 4)] & 0x0F) * p;
+                }
+        for (int l = 0; l < 8; l++) acc[l] = fmaf(d, (float)sumi[l], acc[l]);
+    }
+    return hsum8(acc);
+}
+
+/* Q3_K x Q8_K: crates/rnb-cpu/src/gemm/avx2_dot.rs:247-378.  Eight f32 accumulator lanes, one FMA per
+ * block; lane l = bytes 4l..4l+3 of each 32-byte chunk; chunk k of half h is the 2-bit plane k minus 4
+ * where hmask bit 4h + k is clear, and takes scale 8h + 2k (lanes 0..3) or 8h + 2k + 1 (lanes 4..7). */
+float orc_dot_q3k_q8k(const uint8_t *row, const orc_q8k_block *y, size_t nb) {
+    float acc[8] = {0};
+    for (size_t i = 0; i < nb; i++) {
+        const uint8_t *block = row + i * ORC_Q3K_BYTES;
+        const uint8_t *hm = block, *q3 = block + 32;
+        float d = y[i].d * orc_f16_to_f32(rd_u16(block + 108));
+        int8_t scales[16];
+        q3k_scales(block + 96, scales);
+        int32_t sumi[8] = {0};
+        for (int h = 0; h < 2; h++)
+            for (int k = 0; k < 4; k++)
+                for (int l = 0; l < 8; l++) {
+                    int32_t p = 0;
+                    for (int b = 0; b < 4; b++) {
+                        int e = 4 * l + b;
+                        int v = ((q3[32 * h + e] >> (2 * k)) & 3) - (((hm[e] >> (4 * h + k)) & 1) ? 0 : 4);
+                        p += v * (int32_t)y[i].qs[128 * h + 32 * k + e];
+                    }
+                    sumi[l] += ((int32_t)scales[8 * h + 2 * k + (l >= 4)] - 32) * p;
                 }
         for (int l = 0; l < 8; l++) acc[l] = fmaf(d, (float)sumi[l], acc[l]);
     }
@@ -1098,6 +1227,7 @@ static void gemv_rows(size_t b, size_t e, void *p) {
             float v;
             if (c->type == ORC_TYPE_Q4_K) v = orc_dot_q4k_q8k(row, c->xq + s * c->nb, c->nb);
             else if (c->type == ORC_TYPE_Q2_K) v = orc_dot_q2k_q8k(row, c->xq + s * c->nb, c->nb);
+            else if (c->type == ORC_TYPE_Q3_K) v = orc_dot_q3k_q8k(row, c->xq + s * c->nb, c->nb);
             else if (c->type == ORC_TYPE_Q5_K) v = orc_dot_q5k_q8k(row, c->xq + s * c->nb, c->nb);
             else if (c->type == ORC_TYPE_Q6_K) v = orc_dot_q6k_q8k(row, c->xq + s * c->nb, c->nb);
             else v = orc_dot_q8_0_row(row, c->x + s * c->cols, c->cols / 32);

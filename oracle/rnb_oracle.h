@@ -24,6 +24,7 @@ extern "C" {
 
 #define ORC_QK_K 256
 #define ORC_Q2K_BYTES 84
+#define ORC_Q3K_BYTES 110
 #define ORC_Q4K_BYTES 144
 #define ORC_Q5K_BYTES 176
 #define ORC_Q6K_BYTES 210
@@ -33,6 +34,7 @@ extern "C" {
 /* GGML type ids as the reference passes them (`down_quant: u32`). */
 #define ORC_TYPE_Q8_0 8
 #define ORC_TYPE_Q2_K 10
+#define ORC_TYPE_Q3_K 11
 #define ORC_TYPE_Q4_K 12
 #define ORC_TYPE_Q5_K 13
 #define ORC_TYPE_Q6_K 14
@@ -55,6 +57,7 @@ void orc_quantize_q8k(const float *x, size_t n, orc_q8k_block *out);
 /* ---- dequantisation of one block / of a row of blocks ---- */
 void orc_dequantize_q4k_block(const uint8_t *block, float *out256);
 void orc_dequantize_q2k_block(const uint8_t *block, float *out256);
+void orc_dequantize_q3k_block(const uint8_t *block, float *out256);
 void orc_dequantize_q5k_block(const uint8_t *block, float *out256);
 void orc_dequantize_q6k_block(const uint8_t *block, float *out256);
 void orc_dequantize_q8_0_block(const uint8_t *block, float *out32);
@@ -63,6 +66,7 @@ int orc_dequantize_row(int ggml_type, const uint8_t *row, size_t cols, float *ou
 /* ---- weight quantisers (harness utilities for building synthetic models) ---- */
 void orc_quantize_row_q4k(const float *x, size_t n, uint8_t *out);
 void orc_quantize_row_q2k(const float *x, size_t n, uint8_t *out);   /* harness utility */
+void orc_quantize_row_q3k(const float *x, size_t n, uint8_t *out);   /* harness utility */
 void orc_quantize_row_q5k(const float *x, size_t n, uint8_t *out);   /* harness utility */
 void orc_quantize_row_q6k(const float *x, size_t n, uint8_t *out);
 void orc_quantize_row_q8_0(const float *x, size_t n, uint8_t *out);
@@ -75,6 +79,7 @@ int orc_synth_matrix(int ggml_type, size_t rows, size_t cols, uint64_t seed, flo
 /* ---- row dots ---- */
 float orc_dot_q4k_q8k(const uint8_t *row, const orc_q8k_block *y, size_t nb);
 float orc_dot_q2k_q8k(const uint8_t *row, const orc_q8k_block *y, size_t nb);
+float orc_dot_q3k_q8k(const uint8_t *row, const orc_q8k_block *y, size_t nb);
 float orc_dot_q5k_q8k(const uint8_t *row, const orc_q8k_block *y, size_t nb);
 float orc_dot_q6k_q8k(const uint8_t *row, const orc_q8k_block *y, size_t nb);
 float orc_dot_q4k_q8k_lanes(const uint8_t *row, const orc_q8k_block *y, size_t nb);

@@ -92,6 +92,8 @@ def load() -> C.CDLL:
         "rnb_b200_q6k_gemv": [vp, sz, sz, sz, vp, sz, vp, sz],
         "rnb_b200_q5k_gemv": [vp, sz, sz, sz, vp, sz, vp, sz],
         "rnb_b200_q2k_gemv": [vp, sz, sz, sz, vp, sz, vp, sz],
+        "rnb_b200_q3k_gemv": [vp, sz, sz, sz, vp, sz, vp, sz],
+        "rnb_b200_q3k_gemv_batch": [vp, sz, sz, sz, vp, sz, vp, sz],
         "rnb_b200_q2k_gemv_batch": [vp, sz, sz, sz, vp, sz, vp, sz],
         "rnb_b200_q5k_gemv_batch": [vp, sz, sz, sz, vp, sz, vp, sz],
         "rnb_b200_q8_0_gemv": [vp, sz, sz, sz, vp, sz, vp, sz],

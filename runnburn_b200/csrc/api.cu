@@ -314,7 +314,7 @@ struct Locked {
 };
 
 static const char *type_name(int t) {
-    return t == TYPE_Q2_K ? "Q2_K" : t == TYPE_Q4_K ? "Q4_K" : t == TYPE_Q5_K ? "Q5_K" : t == TYPE_Q6_K ? "Q6_K" : t == TYPE_Q8_0 ? "Q8_0" : "?";
+    return t == TYPE_Q2_K ? "Q2_K" : t == TYPE_Q3_K ? "Q3_K" : t == TYPE_Q4_K ? "Q4_K" : t == TYPE_Q5_K ? "Q5_K" : t == TYPE_Q6_K ? "Q6_K" : t == TYPE_Q8_0 ? "Q8_0" : "?";
 }
 
 // Shape checks with the reference's wording (api/quant_api.rs:189-206).
@@ -362,7 +362,10 @@ static int gemv_host(int type, const uint8_t *weights, size_t weights_len, size_
         x_stride = q8k_dev_bytes(cols);
     }
     RNB_TRY(st.out_f32.ensure(rows * seq * sizeof(float) + 16));
-    if (type == TYPE_Q2_K) {
+    if (type == TYPE_Q3_K) {
+        RNB_CU(launch_k(gemv_q3k_kernel, dim3((unsigned)((rows + G5_WARPS - 1) / G5_WARPS)), dim3(G5_WARPS * 32), 0, st.stream, w_dev,
+                        (const uint8_t *)act, x_stride, st.out_f32.as<float>(), (int)rows, (int)cols, (int)seq));
+    } else if (type == TYPE_Q2_K) {
         RNB_CU(launch_k(gemv_q2k_kernel, dim3((unsigned)((rows + G5_WARPS - 1) / G5_WARPS)), dim3(G5_WARPS * 32), 0, st.stream, w_dev,
                         (const uint8_t *)act, x_stride, st.out_f32.as<float>(), (int)rows, (int)cols, (int)seq));
     } else if (type == TYPE_Q5_K) {
@@ -589,6 +592,13 @@ int rnb_b200_q2k_gemv(const uint8_t *w, size_t wl, size_t rows, size_t cols, con
 int rnb_b200_q2k_gemv_batch(const uint8_t *w, size_t wl, size_t rows, size_t cols, const float *in, size_t il, float *out, size_t ol) {
     if (cols == 0 || il % cols != 0) return fail(RNB_B200_VALIDATION_FAILED, "Q2_K input length mismatch: got %zu, not a multiple of cols %zu", il, cols);
     return prefill_gemm_host(TYPE_Q2_K, w, wl, rows, cols, in, il / cols, out, ol);
+}
+int rnb_b200_q3k_gemv(const uint8_t *w, size_t wl, size_t rows, size_t cols, const float *in, size_t il, float *out, size_t ol) {
+    return gemv_host(TYPE_Q3_K, w, wl, rows, cols, in, il, 0, 1, out, ol, nullptr, nullptr);
+}
+int rnb_b200_q3k_gemv_batch(const uint8_t *w, size_t wl, size_t rows, size_t cols, const float *in, size_t il, float *out, size_t ol) {
+    if (cols == 0 || il % cols != 0) return fail(RNB_B200_VALIDATION_FAILED, "Q3_K input length mismatch: got %zu, not a multiple of cols %zu", il, cols);
+    return prefill_gemm_host(TYPE_Q3_K, w, wl, rows, cols, in, il / cols, out, ol);
 }
 int rnb_b200_q5k_gemv(const uint8_t *w, size_t wl, size_t rows, size_t cols, const float *in, size_t il, float *out, size_t ol) {
     return gemv_host(TYPE_Q5_K, w, wl, rows, cols, in, il, 0, 1, out, ol, nullptr, nullptr);

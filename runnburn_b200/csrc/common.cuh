@@ -37,6 +37,7 @@ __host__ __device__ inline size_t row_bytes_of(int type, size_t cols) {
     case TYPE_Q6_K: return cols / 256 * Q6K_BYTES;
     case TYPE_Q8_0: return cols / 32 * Q8_0_BYTES;
     case 10: return cols / 256 * 84;    // Q2_K (gemv_q5k.cuh)
+    case 11: return cols / 256 * 110;   // Q3_K (gemv_q5k.cuh)
     case 13: return cols / 256 * 176;   // Q5_K (gemv_q5k.cuh)
     default: return 0;
     }

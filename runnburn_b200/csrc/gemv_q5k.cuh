@@ -163,4 +163,71 @@ gemv_q2k_kernel(const uint8_t *__restrict__ w, const uint8_t *__restrict__ xq, s
     }
 }
 
+// Q3_K x Q8_K, bit-exact with crates/rnb-cpu/src/gemm/avx2_dot.rs:247-378.  Block (110 bytes, so only 2-byte
+// aligned): hmask[32] | qs[64] | scales[12] | d f16 (crates/rnb-cpu/src/quantize/blocks.rs:72-78).  Sixteen
+// six-bit scales with bias 32; an element is its two low bits minus 4 where its hmask bit (4h + k for plane k of
+// half h) is clear.  Eight lanes, one FMA per block; lane / scale assignment as for Q2_K.
+constexpr int TYPE_Q3_K = 11;
+constexpr int Q3K_BYTES = 110;
+__device__ __forceinline__ uint32_t ld32_a2(const uint8_t *p) {   // 4 bytes from a 2-byte aligned address
+    const unsigned short *h = reinterpret_cast<const unsigned short *>(p);
+    return (uint32_t)h[0] | ((uint32_t)h[1] << 16);
+}
+RNB_GLOBAL void __launch_bounds__(G5_WARPS * 32)
+gemv_q3k_kernel(const uint8_t *__restrict__ w, const uint8_t *__restrict__ xq, size_t xq_stride, float *__restrict__ y, int rows, int cols, int seq) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int row = blockIdx.x * G5_WARPS + warp;
+    if (row >= rows) return;
+    const int nb = cols >> 8, l = lane & 7, g = lane >> 3;
+    const uint8_t *wrow = w + (size_t)row * nb * Q3K_BYTES;
+    for (int s = 0; s < seq; s++) {
+        const uint8_t *x = xq + (size_t)s * xq_stride;
+        const int8_t *qs = reinterpret_cast<const int8_t *>(x);
+        const float *xd = reinterpret_cast<const float *>(x + cols + 32 * nb);
+        float acc = 0.f;
+        for (int b0 = 0; b0 < nb; b0 += 4) {
+            const int b = b0 + g;
+            int sumi = 0;
+            float dd = 0.f;
+            if (b < nb) {
+                const uint8_t *blk = wrow + (size_t)b * Q3K_BYTES;
+                dd = __fmul_rn(xd[b], __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short *>(blk + 108))));
+                // the 16 scales as bytes of aux[0..3] (the reference's unpack of the 12 packed bytes), still biased by 32
+                const uint32_t a0 = ld32_a2(blk + 96), a1 = ld32_a2(blk + 100), a2 = ld32_a2(blk + 104);
+                uint32_t aux[4];
+                aux[0] = (a0 & 0x0f0f0f0fu) | (((a2 >> 0) & 0x03030303u) << 4);
+                aux[1] = (a1 & 0x0f0f0f0fu) | (((a2 >> 2) & 0x03030303u) << 4);
+                aux[2] = ((a0 >> 4) & 0x0f0f0f0fu) | (((a2 >> 4) & 0x03030303u) << 4);
+                aux[3] = ((a1 >> 4) & 0x0f0f0f0fu) | (((a2 >> 6) & 0x03030303u) << 4);
+                const uint32_t nhm = ~ld32_a2(blk + 4 * l);   // set where 4 is subtracted
+#pragma unroll
+                for (int h = 0; h < 2; h++) {
+                    const uint32_t q3 = ld32_a2(blk + 32 + 32 * h + 4 * l);
+#pragma unroll
+                    for (int k = 0; k < 4; k++) {
+                        const int lo = (int)((q3 >> (2 * k)) & 0x03030303u);
+                        const int hi = (int)(((nhm >> (4 * h + k)) & 0x01010101u) << 2);
+                        const int a = *reinterpret_cast<const int *>(qs + b * 256 + 128 * h + 32 * k + 4 * l);
+                        const int si = 8 * h + 2 * k + (l >= 4);
+                        const int sc = (int)((aux[si >> 2] >> (8 * (si & 3))) & 0xffu) - 32;
+                        sumi += sc * (__dp4a(lo, a, 0) - __dp4a(hi, a, 0));
+                    }
+                }
+            }
+#pragma unroll
+            for (int gg = 0; gg < 4; gg++) {
+                const int si = __shfl_sync(0xffffffffu, sumi, l + 8 * gg);
+                const float di = __shfl_sync(0xffffffffu, dd, l + 8 * gg);
+                if (b0 + gg < nb) acc = __fmaf_rn(di, (float)si, acc);
+            }
+        }
+        float r = __fadd_rn(__shfl_sync(0xffffffffu, acc, (l + 4) & 7), acc);
+        r = __fadd_rn(r, __shfl_sync(0xffffffffu, r, (l + 2) & 7));
+        r = __fadd_rn(r, __shfl_sync(0xffffffffu, r, (l + 1) & 7));
+        if (lane == 0) y[(size_t)s * rows + row] = r;
+    }
+}
+
 }  // namespace rnb

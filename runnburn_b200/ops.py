@@ -134,6 +134,16 @@ def q2k_gemv_batch(weights, rows: int, cols: int, x) -> np.ndarray:
     return _gemv(load().rnb_b200_q2k_gemv_batch, weights, rows, cols, x, seq=x.size // cols)
 
 
+def q3k_gemv(weights, rows: int, cols: int, x) -> np.ndarray:
+    """Q3_K matvec (QuantGemvType::Q3K, crates/rnb-cpu/src/gemm/quant_gemv.rs:94-101)"""
+    return _gemv(load().rnb_b200_q3k_gemv, weights, rows, cols, x)
+
+
+def q3k_gemv_batch(weights, rows: int, cols: int, x) -> np.ndarray:
+    x = _f32(x)
+    return _gemv(load().rnb_b200_q3k_gemv_batch, weights, rows, cols, x, seq=x.size // cols)
+
+
 def q5k_gemv(weights, rows: int, cols: int, x) -> np.ndarray:
     """Q5_K matvec (QuantGemvType::Q5K, crates/rnb-cpu/src/gemm/quant_gemv.rs:94-101)"""
     return _gemv(load().rnb_b200_q5k_gemv, weights, rows, cols, x)

@@ -52,6 +52,10 @@ def main():
     q2[:, 82:84] = f16_bits(rng, n).view(np.uint8).reshape(n, 2)
     out["q2k_bytes"] = q2
     out["q2k_f32"] = quants.dequantize(q2, T.Q2_K).astype(np.float32)
+    q3 = rng.integers(0, 256, size=(n, 110), dtype=np.uint8)
+    q3[:, 108:110] = f16_bits(rng, n).view(np.uint8).reshape(n, 2)
+    out["q3k_bytes"] = q3
+    out["q3k_f32"] = quants.dequantize(q3, T.Q3_K).astype(np.float32)
     np.savez_compressed(Path(__file__).with_name("gguf_dequant.npz"), **out)
     print({k: v.shape for k, v in out.items()})
 

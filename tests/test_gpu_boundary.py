@@ -280,3 +280,24 @@ def test_q2k_matvec_bit_exact(ops, rows, cols):
     xs = rng.standard_normal((2, cols)).astype(np.float32)
     got = ops.q2k_gemv_batch(raw, rows, cols, xs)
     assert np.array_equal(got.view(np.uint32), orc.gemv(Q2_K, raw, xs, rows, cols, seq_len=2).view(np.uint32))
+
+
+Q3_K = 11
+
+
+@pytest.mark.parametrize("rows,cols", [(1, 256), (5, 512), (33, 768), (130, 1024), (1024, 4096), (2048, 768)])
+def test_q3k_matvec_bit_exact(ops, rows, cols):
+    """Q3_K x Q8_K (crates/rnb-cpu/src/gemm/avx2_dot.rs:247-378): bit for bit the oracle's, on fitted weights and
+    on random block bytes (odd block indices sit on 2-byte boundaries); the batched form likewise."""
+    rng = np.random.default_rng(rows * 13 + cols)
+    x = rng.standard_normal(cols).astype(np.float32)
+    w = orc.quantize_matrix(Q3_K, (rng.standard_normal((rows, cols)) * 0.05).astype(np.float32))
+    assert np.array_equal(ops.q3k_gemv(w, rows, cols, x).view(np.uint32), orc.gemv(Q3_K, w, x, rows, cols).view(np.uint32))
+    ops.clear_q4k_cache()
+    raw = rng.integers(0, 256, size=(rows, cols // 256, 110), dtype=np.uint8)
+    raw[..., 109] = 0x10
+    raw = raw.reshape(-1)
+    assert np.array_equal(ops.q3k_gemv(raw, rows, cols, x).view(np.uint32), orc.gemv(Q3_K, raw, x, rows, cols).view(np.uint32))
+    xs = rng.standard_normal((2, cols)).astype(np.float32)
+    got = ops.q3k_gemv_batch(raw, rows, cols, xs)
+    assert np.array_equal(got.view(np.uint32), orc.gemv(Q3_K, raw, xs, rows, cols, seq_len=2).view(np.uint32))

@@ -108,7 +108,7 @@ def test_dequant_zero_blocks_and_q8_0_known(orc):
 
 def test_dequant_matches_gguf_package(orc):
     g = np.load(GOLD / "gguf_dequant.npz")
-    for name, t, cols in (("q2k", orc.TYPE_Q2_K, 256), ("q4k", orc.TYPE_Q4_K, 256), ("q5k", orc.TYPE_Q5_K, 256), ("q6k", orc.TYPE_Q6_K, 256),
+    for name, t, cols in (("q2k", orc.TYPE_Q2_K, 256), ("q3k", orc.TYPE_Q3_K, 256), ("q4k", orc.TYPE_Q4_K, 256), ("q5k", orc.TYPE_Q5_K, 256), ("q6k", orc.TYPE_Q6_K, 256),
                           ("q8_0", orc.TYPE_Q8_0, 32)):
         raw, want = g[f"{name}_bytes"], g[f"{name}_f32"]
         got = orc.dequantize_matrix(t, raw.ravel(), raw.shape[0], cols)
@@ -465,3 +465,25 @@ def test_q2k_block_size_and_dot_against_dequantised_q8k(orc):
         want = back.astype(np.float64) @ xd.astype(np.float64)
         assert np.max(np.abs(got - want)) < 1e-4 * np.max(np.abs(want))
     assert _cos(w.ravel(), orc.dequantize_matrix(orc.TYPE_Q2_K, q, rows, cols).ravel()) >= 0.9
+
+
+def test_q3k_block_size_and_dot_against_dequantised_q8k(orc):
+    """Q3_K (crates/rnb-cpu/src/quantize/blocks.rs:72-78: 110 bytes, 2-byte aligned only).  The integer dot
+    (crates/rnb-cpu/src/gemm/avx2_dot.rs:247-378) equals the scalar dot over the dequantised weights and the
+    dequantised Q8_K activation to f32 rounding, on fitted weights and on random block bytes."""
+    assert orc.row_bytes(orc.TYPE_Q3_K, 256) == 110
+    rng = np.random.default_rng(33)
+    rows, cols = 6, 1024
+    x = rng.standard_normal(cols).astype(np.float32)
+    blocks = orc.quantize_q8k(x).view(np.uint8).reshape(-1, 292)
+    xd = np.concatenate([blocks[b, :4].view(np.float32)[0] * blocks[b, 4:260].view(np.int8).astype(np.float32) for b in range(cols // 256)])
+    w = (rng.standard_normal((rows, cols)) * 0.05).astype(np.float32)
+    q = orc.quantize_matrix(orc.TYPE_Q3_K, w)
+    raw = rng.integers(0, 256, size=(rows, cols // 256, 110), dtype=np.uint8)
+    raw[..., 109] = 0x10
+    for data in (q, raw.reshape(-1)):
+        back = orc.dequantize_matrix(orc.TYPE_Q3_K, data, rows, cols)
+        got = orc.gemv(orc.TYPE_Q3_K, data, x, rows, cols)
+        want = back.astype(np.float64) @ xd.astype(np.float64)
+        assert np.max(np.abs(got - want)) < 1e-4 * np.max(np.abs(want))
+    assert _cos(w.ravel(), orc.dequantize_matrix(orc.TYPE_Q3_K, q, rows, cols).ravel()) >= 0.97
