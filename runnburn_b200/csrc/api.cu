@@ -437,6 +437,9 @@ using namespace rnb;
 // extern "C"
 // =============================================================================================
 namespace rnb {
+// defined with the rest of the boundary (boundary.inc): frees device tensors, decode carriers and the expert
+// history; `all` = library close (false: engine re-init keeps handles a caller may still hold)
+static void boundary_release(bool all);
 // defined with the rest of the boundary (boundary.inc): brings a layer's device KV mirror up to kv_len rows
 static int kv_mirror_sync(State &st, size_t layer, const uint16_t *k, const uint16_t *v, size_t kv_len, size_t kv_dim, const uint16_t *last_k_dev,
                           const uint16_t *last_v_dev);
@@ -452,6 +455,11 @@ int rnb_b200_open(void) {
 }
 void rnb_b200_close(void) {
     Locked L;
+    if (L.st.is_open) {
+        cudaSetDevice(L.st.device);
+        cudaStreamSynchronize(L.st.stream);
+        boundary_release(true);
+    }
     L.st.close();
 }
 int rnb_b200_cuda_memory_info(size_t *free_bytes, size_t *total_bytes) {
@@ -499,6 +507,7 @@ int rnb_b200_reset_state_for_engine_init(void) {
     }
     L.st.kv_mirrors.clear();
     memset(&L.st.ctr, 0, sizeof(L.st.ctr));
+    boundary_release(false);
     return RNB_B200_OK;
 }
 int rnb_b200_prewarm_q4k_weights(const uint8_t *const *slices, const size_t *lens, size_t n, size_t *n_resident) {
