@@ -89,6 +89,7 @@ int gemv_kernel_setup() {
     RNB_CU(cudaFuncSetAttribute(gemv_stream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn));
     RNB_CU(cudaFuncSetAttribute(gemv_stream_kernel_1, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn));
     RNB_CU(cudaFuncSetAttribute(gemv_pair_q4k_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn));
+    RNB_CU(cudaFuncSetAttribute(gemv_pair_q4k_dyn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn));
     RNB_CU(cudaFuncSetAttribute(gemv_ksplit_q6k_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn));
     RNB_CU(cudaFuncSetAttribute(gemv_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn));
     RNB_CU(cudaFuncSetAttribute(gemv_mma_kernel_1, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn));

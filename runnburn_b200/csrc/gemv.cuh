@@ -44,6 +44,13 @@ struct GemvJob {
     const float *epi_rope;    // [pos][cos 64 | sin 64]
     const int *epi_pos;       // device scalar: position of this token
     uint16_t *epi_cache;      // K or V cache of the layer
+    // Expert-gathered form (two-threads-per-row kernel): `rows` are virtual rows, dyn_rows per selected expert;
+    // virtual row v reads row ids[v / dyn_rows] * dyn_rows + v % dyn_rows of the stacked expert tensor parts[0].w
+    // against the activation parts[0].x + (v / dyn_rows) * dyn_x_stride.  The ids are written by an earlier
+    // kernel of the same stream.  null = plain rows.
+    const uint32_t *dyn_ids;
+    int dyn_rows;
+    uint32_t dyn_x_stride;
 };
 constexpr int GEMV_EPI_NONE = 0, GEMV_EPI_ROPE_F32 = 1, GEMV_EPI_ROPE_F16_CACHE = 2, GEMV_EPI_F16_CACHE = 3;
 

@@ -34,12 +34,17 @@ struct GpParams {
 // the work of silu_mul_q8k_kernel, spread over the blocks as they finish, without a launch.
 // counters[block] is zero before the launch and re-armed by the block's last CTA.
 struct GpTail {
-    int kind;            // 0 = none, 1 = SiLU * up + Q8_K, 2 = peer publish (integer-MMA kernel, one plain job)
-    int n;               // length of the gate / up vectors (multiple of 256)
-    const float *gate, *up;
+    int kind;            // 0 = none, 1 = SiLU * up + Q8_K, 2 = peer publish (integer-MMA kernel, one plain job),
+                         // 3 = ordered sum of the selected experts' rows (expert-gathered down projection)
+    int n;               // length of the gate / up vectors (multiple of 256); kind 3: rows per expert
+    const float *gate, *up;   // kind 3: gate = the experts' raw rows [k][n], up = the k route weights
     uint8_t *xq_out;     // Q8K-dev layout of the n-vector
-    int *counters;       // n / 256 ints
+    int *counters;       // n / 256 ints; kind 3: n / 16
     PeerOut peer;        // kind 2: where the finished rows also go
+    int vec_n;           // kind 1: the n elements are n / vec_n vectors, each quantised on its own (0 = one vector)
+    int sum_k;           // kind 3: experts per token
+    float *sum_out;      // kind 3: out[row] = residual[row] + sum over experts in order of weight * row
+    const float *sum_res;
 };
 
 struct Q4kPairAcc {
@@ -88,9 +93,10 @@ __device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
 }
 
 // grid = tiles of 16 rows, 32 threads.  Operands must be 16-byte aligned (the host checks).
-RNB_GLOBAL void __launch_bounds__(32)
-gemv_pair_q4k_kernel(const __grid_constant__ GemvJobPack jobs, int n_jobs, const GpParams P, int *__restrict__ dev_error,
-                     const __grid_constant__ GpTail tail) {
+// DYN: the expert-gathered instantiation (virtual rows, ids read after the wait on the previous kernel, tails 1 with
+// per-expert vectors and 3); the dense instantiation carries none of that code.
+template <bool DYN>
+__device__ __forceinline__ void gemv_pair_body(const GemvJobPack &jobs, int n_jobs, const GpParams &P, int *__restrict__ dev_error, const GpTail &tail) {
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ __align__(8) uint64_t full[GP_MAX_STAGES];
     const int lane = threadIdx.x, r = lane >> 1, h = lane & 1;
@@ -110,7 +116,7 @@ gemv_pair_q4k_kernel(const __grid_constant__ GemvJobPack jobs, int n_jobs, const
     pdl_launch_dependents();
     const uint32_t rb = (uint32_t)nb * Q4K_BYTES;
     const int n_chunks = (nb + CB - 1) / CB;
-    const uint8_t *w = job.parts[0].w, *x = job.parts[0].x;
+    const uint8_t *w = job.parts[0].w + (size_t)row0 * rb, *x = job.parts[0].x;   // w: first row of this tile
     // every row's first thread fetches that row's chunk; lane 1 fetches the activation slice
     auto issue_w = [&](int c, int slot_idx) {
         if (h != 0) return;
@@ -118,7 +124,7 @@ gemv_pair_q4k_kernel(const __grid_constant__ GemvJobPack jobs, int n_jobs, const
         if (r < nrows) {
             const uint32_t bytes = (uint32_t)min(CB, nb - c * CB) * Q4K_BYTES;
             mbar_arrive_expect_tx(bar, bytes);
-            bulk_g2s(smem + (uint32_t)slot_idx * P.slot_bytes + (uint32_t)r * P.row_stride, w + (size_t)(row0 + r) * rb + (uint32_t)(c * CB) * Q4K_BYTES,
+            bulk_g2s(smem + (uint32_t)slot_idx * P.slot_bytes + (uint32_t)r * P.row_stride, w + (size_t)r * rb + (uint32_t)(c * CB) * Q4K_BYTES,
                      bytes, bar);
         } else {
             mbar_arrive(bar);
@@ -141,8 +147,16 @@ gemv_pair_q4k_kernel(const __grid_constant__ GemvJobPack jobs, int n_jobs, const
         mbar_fence_init();
     }
     __syncwarp();
+    if (DYN) {
+        // the ids come from an earlier kernel: nothing can be fetched before the wait
+        pdl_wait();
+        const int e = row0 / job.dyn_rows;
+        const uint32_t id = __ldcg(job.dyn_ids + e);
+        w = job.parts[0].w + ((size_t)id * (size_t)job.dyn_rows + (size_t)(row0 - e * job.dyn_rows)) * rb;
+        x += (size_t)e * job.dyn_x_stride;
+    }
     for (int i = 0; i < S && i < n_chunks; i++) issue_w(i, i);
-    pdl_wait();   // the weights do not depend on the previous kernel; the activation does
+    if (!DYN) pdl_wait();   // the weights do not depend on the previous kernel; the activation does
     for (int i = 0; i < S && i < n_chunks; i++) issue_a(i, i);
     const uint32_t row_off = (uint32_t)(r < nrows ? r : 0) * P.row_stride + 0u;   // dead rows read row 0 and do not store
     Q4kPairAcc A = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f}};
@@ -202,10 +216,48 @@ gemv_pair_q4k_kernel(const __grid_constant__ GemvJobPack jobs, int n_jobs, const
             const float e = expf_libm(-gv[j]);   // as silu_mul_q8k_kernel: libm's expf
             v[j] = __fmul_rn(__fdiv_rn(gv[j], __fadd_rn(1.0f, e)), uv[j]);
         }
-        Q8kDevView dv = q8k_dev_view(tail.xq_out, tail.n);
-        q8k_quantize_block_warp(v, lane, dv.qs + blk * 256, dv.d + blk, dv.bsum16 + blk * 16, nullptr);
+        int vb = blk, vn = tail.n;
+        uint8_t *xq = tail.xq_out;
+        if (DYN && tail.vec_n) {
+            // one Q8_K vector per expert
+            vn = tail.vec_n;
+            const int vec = blk / (vn >> 8);
+            vb = blk - vec * (vn >> 8);
+            xq += (size_t)vec * q8k_dev_bytes((size_t)vn);
+        }
+        Q8kDevView dv = q8k_dev_view(xq, vn);
+        q8k_quantize_block_warp(v, lane, dv.qs + vb * 256, dv.d + vb, dv.bsum16 + vb * 16, nullptr);
         if (lane == 0) tail.counters[blk] = 0;
     }
+    if (DYN && tail.kind == 3) {
+        // the tile that completes its 16 rows over all experts folds them in selection order:
+        // out = residual + ((0 + w0 * r0) + w1 * r1 + ...), the order of the multi-part matvec
+        const int e = row0 / tail.n, lrow0 = row0 - e * tail.n, ctr = lrow0 >> 4;
+        __threadfence();
+        __syncwarp();
+        int last = 0;
+        if (lane == 0) last = atomicAdd(&tail.counters[ctr], 1) == tail.sum_k - 1;
+        last = __shfl_sync(0xffffffffu, last, 0);
+        if (!last) return;
+        __threadfence();
+        if (lane < GP_ROWS && lrow0 + lane < tail.n) {
+            const size_t o = (size_t)lrow0 + lane;
+            float acc = 0.f;
+            for (int k = 0; k < tail.sum_k; k++) acc = __fadd_rn(acc, __fmul_rn(__ldcg(tail.gate + (size_t)k * tail.n + o), __ldcg(tail.up + k)));
+            tail.sum_out[o] = tail.sum_res ? __fadd_rn(__ldcg(tail.sum_res + o), acc) : acc;
+        }
+        if (lane == 0) tail.counters[ctr] = 0;
+    }
+}
+RNB_GLOBAL void __launch_bounds__(32)
+gemv_pair_q4k_kernel(const __grid_constant__ GemvJobPack jobs, int n_jobs, const GpParams P, int *__restrict__ dev_error,
+                     const __grid_constant__ GpTail tail) {
+    gemv_pair_body<false>(jobs, n_jobs, P, dev_error, tail);
+}
+RNB_GLOBAL void __launch_bounds__(32)
+gemv_pair_q4k_dyn_kernel(const __grid_constant__ GemvJobPack jobs, int n_jobs, const GpParams P, int *__restrict__ dev_error,
+                         const __grid_constant__ GpTail tail) {
+    gemv_pair_body<true>(jobs, n_jobs, P, dev_error, tail);
 }
 
 }  // namespace rnb

@@ -339,9 +339,11 @@ inline int try_launch_gemv_mma(cudaStream_t s, const GemvJob *jobs_host, const G
 }
 // Row-rich, all-Q4_K, single-part, 16-byte aligned static tables go to the two-threads-per-row
 // kernel; everything else to the eight-threads-per-row kernel.
+inline int launch_gemv_pair_dyn(cudaStream_t s, const GemvJob *jobs_host, int n_jobs, size_t cols, int *dev_error, const GpTail *tail, bool *tail_done);
 inline int launch_gemv_stream(cudaStream_t s, const GemvJob *jobs_host, const GemvJob *jobs_dev, int n_jobs,
                               size_t cols, int *dev_error, int dynamic_table, bool by_value, const GpTail *tail = nullptr,
                               bool *tail_done = nullptr) {
+    if (n_jobs >= 1 && jobs_host[0].dyn_ids) return launch_gemv_pair_dyn(s, jobs_host, n_jobs, cols, dev_error, tail, tail_done);
     {
         const int took = try_launch_gemv_mma(s, jobs_host, jobs_dev, n_jobs, cols, dev_error, dynamic_table, by_value, tail, tail_done);
         if (took < 0) return -took;
@@ -396,6 +398,58 @@ inline int launch_gemv_stream(cudaStream_t s, const GemvJob *jobs_host, const Ge
         if (tail_done) *tail_done = true;
     }
     RNB_CU(launch_k(gemv_pair_q4k_kernel, dim3(tiles), dim3(32), smem, s, pack, n_jobs, P, dev_error, t));
+    return RNB_B200_OK;
+}
+
+// Expert-gathered jobs (GemvJob::dyn_ids): static tables by value, the two-threads-per-row kernel's expert form.
+// Tunables: RNB_B200_MOE_CHUNK (super-blocks per stage, default min(4, row)), RNB_B200_MOE_STAGES (default 3).
+inline int launch_gemv_pair_dyn(cudaStream_t s, const GemvJob *jobs_host, int n_jobs, size_t cols, int *dev_error, const GpTail *tail, bool *tail_done) {
+    if (n_jobs > GS_PACK || cols % 256 != 0) return fail(RNB_B200_VALIDATION_FAILED, "expert-gathered matvec: at most %d jobs, cols a multiple of 256", GS_PACK);
+    GemvJobPack pack;
+    memset(&pack, 0, sizeof(pack));
+    int tiles = 0;
+    for (int i = 0; i < n_jobs; i++) {
+        const GemvJob &j = jobs_host[i];
+        if (!j.dyn_ids || j.type != TYPE_Q4_K || j.n_parts != 1 || j.seq > 1 || j.epi != GEMV_EPI_NONE || j.dyn_rows < GP_ROWS || j.dyn_rows % GP_ROWS || j.rows % j.dyn_rows ||
+            ((((uintptr_t)j.parts[0].w | (uintptr_t)j.parts[0].x) | (uintptr_t)j.dyn_x_stride) & 15u))
+            return fail(RNB_B200_VALIDATION_FAILED, "expert-gathered matvec: Q4_K, one part, 16-byte aligned operands, whole tiles per expert");
+        pack.j[i] = j;
+        pack.j[i].rows_per_tile = GP_ROWS;
+        pack.j[i].tile0 = tiles;
+        tiles += j.rows / GP_ROWS;
+    }
+    static const int env_chunk = [] {
+        const char *e = getenv("RNB_B200_MOE_CHUNK");
+        return (e && *e) ? atoi(e) : 4;
+    }();
+    static const int env_stages = [] {
+        const char *e = getenv("RNB_B200_MOE_STAGES");
+        return (e && *e) ? atoi(e) : 3;
+    }();
+    const int nb = (int)(cols / 256);
+    GpParams P;
+    P.cols = (int)cols;
+    P.chunk = std::max(1, std::min(std::min(env_chunk, GP_MAX_CHUNK), nb));
+    const int n_chunks = (nb + P.chunk - 1) / P.chunk;
+    P.n_stages = std::max(1, std::min(std::min(env_stages, GP_MAX_STAGES), n_chunks));
+    P.row_stride = (uint32_t)P.chunk * Q4K_BYTES;
+    while ((P.row_stride & 127u) != 32u && (P.row_stride & 127u) != 96u) P.row_stride += 16u;
+    P.act_off = ((uint32_t)GP_ROWS * P.row_stride + 127u) & ~127u;
+    P.slot_bytes = (P.act_off + (uint32_t)P.chunk * 288u + 32u + 127u) & ~127u;
+    const size_t smem = (size_t)P.n_stages * P.slot_bytes;
+    if (smem > gemv_smem_max()) return fail(RNB_B200_VALIDATION_FAILED, "expert-gathered matvec: stage ring of %zu bytes", smem);
+    GpTail t;
+    memset(&t, 0, sizeof(t));
+    if (tail && tail->kind == 1 && n_jobs == 2 && jobs_host[0].rows == jobs_host[1].rows && jobs_host[0].rows % 256 == 0 && jobs_host[0].rows == tail->n &&
+        (tail->vec_n == 0 || (tail->vec_n % 256 == 0 && tail->n % tail->vec_n == 0))) {
+        t = *tail;
+        if (tail_done) *tail_done = true;
+    }
+    if (tail && tail->kind == 3 && n_jobs == 1 && tail->n == jobs_host[0].dyn_rows && tail->sum_k * tail->n == jobs_host[0].rows && tail->gate == jobs_host[0].y) {
+        t = *tail;
+        if (tail_done) *tail_done = true;
+    }
+    RNB_CU(launch_k(gemv_pair_q4k_dyn_kernel, dim3(tiles), dim3(32), smem, s, pack, n_jobs, P, dev_error, t));
     return RNB_B200_OK;
 }
 

@@ -75,15 +75,35 @@ __device__ __forceinline__ uint32_t moe_route_topk_warp(const float *logits, int
     uint32_t taken = 0;  // bit s <-> expert lane + 32*s
     float my_val = 0.0f;
     uint32_t my_id = 0;
+    // up to 256 experts: the lane's logits are read once and kept in registers (every round of the selection would
+    // otherwise wait on the L2 again)
+    constexpr int RC = 8;
+    const bool cached = n_expert <= 32 * RC;
+    float cv[RC];
+    if (cached) {
+#pragma unroll
+        for (int s = 0; s < RC; s++) cv[s] = lane + 32 * s < n_expert ? __ldcg(lg + lane + 32 * s) : 0.0f;
+    }
     for (int r = 0; r < sel; r++) {
         float best = -INFINITY;
         int bi = 0x7fffffff;
-        for (int s = 0, e = lane; e < n_expert; s++, e += 32) {
-            if (taken & (1u << s)) continue;
-            const float v = __ldcg(lg + e);   // may have been written by other CTAs of the same launch
-            if (bi == 0x7fffffff || v > best) {  // ascending e: strict > keeps the lowest id
-                best = v;
-                bi = e;
+        if (cached) {
+#pragma unroll
+            for (int s = 0; s < RC; s++) {
+                const int e = lane + 32 * s;
+                if (e < n_expert && !(taken & (1u << s)) && (bi == 0x7fffffff || cv[s] > best)) {
+                    best = cv[s];
+                    bi = e;
+                }
+            }
+        } else {
+            for (int s = 0, e = lane; e < n_expert; s++, e += 32) {
+                if (taken & (1u << s)) continue;
+                const float v = __ldcg(lg + e);   // may have been written by other CTAs of the same launch
+                if (bi == 0x7fffffff || v > best) {  // ascending e: strict > keeps the lowest id
+                    best = v;
+                    bi = e;
+                }
             }
         }
 #pragma unroll
