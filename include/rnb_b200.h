@@ -165,6 +165,18 @@ int rnb_b200_attention_decode_cached(size_t layer_index, const float *q, size_t 
                                      const uint16_t *k, const uint16_t *v, size_t kv_elems,
                                      size_t kv_len, size_t num_heads, size_t num_kv_heads,
                                      size_t head_dim, float scale, float *out, size_t out_len);
+/* attention_decode_cached_window(layer_index, q, k, v, kv_len, window_start, window_len, num_heads,
+ * num_kv_heads, head_dim, scale) — api/attention_api.rs:2105-2163: sliding-window decode; attention
+ * over positions [window_start, window_start + window_len) of the mirrored cache.  With
+ * window_start + window_len == kv_len the result equals the CPU routine's with
+ * sliding_window = window_len (crates/rnb-cpu/src/kernels/attention/decode_flash.rs:139-146: masked
+ * positions score -inf and contribute exact zeros).  An empty or out-of-range window is
+ * RNB_B200_VALIDATION_FAILED. */
+int rnb_b200_attention_decode_cached_window(size_t layer_index, const float *q, size_t q_len,
+                                            const uint16_t *k, const uint16_t *v, size_t kv_elems,
+                                            size_t kv_len, size_t window_start, size_t window_len,
+                                            size_t num_heads, size_t num_kv_heads, size_t head_dim,
+                                            float scale, float *out, size_t out_len);
 /* clear_decode_attention_kv_cache — api/cache_api.rs:136 */
 int rnb_b200_clear_decode_attention_kv_cache(void);
 /* attention_prefill_flash_hd128 — api/attention_api.rs:661-700: causal, query i sees keys

@@ -78,6 +78,7 @@ def _declare(L):
     L.orc_row_bytes.restype = sz
     L.orc_row_bytes.argtypes = [i32, sz]
     L.orc_attention_decode.argtypes = [vp, vp, vp, vp, sz, sz, sz, sz, f32]
+    L.orc_attention_decode_window.argtypes = [vp, vp, vp, vp, sz, sz, sz, sz, f32, sz]
     L.orc_attention_decode_online.argtypes = [vp, vp, vp, vp, sz, sz, sz, sz, f32]
     L.orc_attention_decode_mt.argtypes = [vp, vp, vp, vp, sz, sz, sz, sz, f32, i32]
     L.orc_attention_prefill.argtypes = [vp, vp, vp, vp, sz, sz, sz, sz, sz, f32]
@@ -224,6 +225,16 @@ def attention_decode(q, k_bits, v_bits, num_heads, num_kv_heads, head_dim, kv_le
         return out
     fn = lib().orc_attention_decode_online if online else lib().orc_attention_decode
     fn(_p(q), _p(k), _p(v), _p(out), num_heads, num_kv_heads, head_dim, kv_len, scale)
+    return out
+
+
+def attention_decode_window(q, k_bits, v_bits, num_heads, num_kv_heads, head_dim, kv_len, scale, window: int) -> np.ndarray:
+    """The CPU routine with sliding_window = Some(window): every position walked, masked ones with weight zero."""
+    q = _f32(q).ravel()
+    k = np.ascontiguousarray(k_bits, dtype=np.uint16)
+    v = np.ascontiguousarray(v_bits, dtype=np.uint16)
+    out = np.empty(num_heads * head_dim, dtype=np.float32)
+    lib().orc_attention_decode_window(_p(q), _p(k), _p(v), _p(out), num_heads, num_kv_heads, head_dim, kv_len, scale, window)
     return out
 
 

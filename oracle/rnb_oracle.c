@@ -1344,6 +1344,7 @@ typedef struct {
     float *out;
     size_t num_heads, num_kv_heads, head_dim, kv_len;
     float scale;
+    size_t window;   /* sliding window (0 = none): position j is masked when j + window <= kv_len - 1 */
 } attn_ctx;
 static void attn_heads(size_t hb, size_t he, void *p) {
     attn_ctx *c = (attn_ctx *)p;
@@ -1353,8 +1354,14 @@ static void attn_heads(size_t hb, size_t he, void *p) {
     for (size_t h = hb; h < he; h++) {
         size_t kv_h = h / group;
         const float *qh = c->q + h * head_dim;
-        for (size_t j = 0; j < kv_len; j++)
+        for (size_t j = 0; j < kv_len; j++) {
+            /* decode_flash.rs:139-146: a masked position scores -inf (its weight is exp(-inf) = 0) */
+            if (c->window && j + c->window <= kv_len - 1) {
+                scores[j] = -INFINITY;
+                continue;
+            }
             scores[j] = dot_f32_f16(qh, c->k + j * kv_dim + kv_h * head_dim, head_dim) * c->scale;
+        }
         float max_score = -INFINITY;
         for (size_t j = 0; j < kv_len; j++)
             if (scores[j] > max_score) max_score = scores[j];
@@ -1374,14 +1381,23 @@ static void attn_heads(size_t hb, size_t he, void *p) {
 void orc_attention_decode(const float *q, const uint16_t *k, const uint16_t *v, float *out,
                           size_t num_heads, size_t num_kv_heads, size_t head_dim, size_t kv_len,
                           float scale) {
-    attn_ctx c = {q, k, v, out, num_heads, num_kv_heads, head_dim, kv_len, scale};
+    attn_ctx c = {q, k, v, out, num_heads, num_kv_heads, head_dim, kv_len, scale, 0};
+    attn_heads(0, num_heads, &c);
+}
+/* attention_decode_into_with_scale_window_and_softcap with sliding_window = Some(window), softcap = None
+ * (crates/rnb-cpu/src/kernels/attention/decode_flash.rs:91-212): every position is walked, the masked ones
+ * with weight zero. */
+void orc_attention_decode_window(const float *q, const uint16_t *k, const uint16_t *v, float *out,
+                                 size_t num_heads, size_t num_kv_heads, size_t head_dim, size_t kv_len,
+                                 float scale, size_t window) {
+    attn_ctx c = {q, k, v, out, num_heads, num_kv_heads, head_dim, kv_len, scale, window};
     attn_heads(0, num_heads, &c);
 }
 /* Heads are independent; the reference runs them in parallel on its thread pool. */
 void orc_attention_decode_mt(const float *q, const uint16_t *k, const uint16_t *v, float *out,
                              size_t num_heads, size_t num_kv_heads, size_t head_dim, size_t kv_len,
                              float scale, int threads) {
-    attn_ctx c = {q, k, v, out, num_heads, num_kv_heads, head_dim, kv_len, scale};
+    attn_ctx c = {q, k, v, out, num_heads, num_kv_heads, head_dim, kv_len, scale, 0};
     if (threads <= 1) {
         attn_heads(0, num_heads, &c);
         return;

@@ -98,6 +98,9 @@ size_t orc_row_bytes(int ggml_type, size_t cols);
 void orc_attention_decode(const float *q, const uint16_t *k, const uint16_t *v, float *out,
                           size_t num_heads, size_t num_kv_heads, size_t head_dim, size_t kv_len,
                           float scale);
+void orc_attention_decode_window(const float *q, const uint16_t *k, const uint16_t *v, float *out,
+                                 size_t num_heads, size_t num_kv_heads, size_t head_dim, size_t kv_len,
+                                 float scale, size_t window);
 void orc_attention_decode_mt(const float *q, const uint16_t *k, const uint16_t *v, float *out,
                              size_t num_heads, size_t num_kv_heads, size_t head_dim, size_t kv_len,
                              float scale, int threads);

@@ -106,6 +106,7 @@ def load() -> C.CDLL:
         "rnb_b200_q6k_bf16_gemm_batch": [vp, sz, sz, sz, vp, sz, vp, sz],
         "rnb_b200_attention_decode_hd128": [vp, sz, vp, vp, sz, sz, sz, sz, f32, vp, sz],
         "rnb_b200_attention_decode_cached": [sz, vp, sz, vp, vp, sz, sz, sz, sz, sz, f32, vp, sz],
+        "rnb_b200_attention_decode_cached_window": [sz, vp, sz, vp, vp, sz, sz, sz, sz, sz, sz, sz, f32, vp, sz],
         "rnb_b200_clear_decode_attention_kv_cache": [],
         "rnb_b200_attention_prefill_flash_hd128": [vp, vp, vp, sz, sz, sz, sz, f32, vp],
         "rnb_b200_attention_prefill_flash_hd128_f16kv": [vp, vp, vp, sz, sz, sz, sz, f32, vp],

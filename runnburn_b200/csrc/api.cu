@@ -722,6 +722,24 @@ int rnb_b200_attention_decode_cached(size_t layer, const float *q, size_t q_len,
     return attention_run(st, m.dk, m.dv, q, kv_len, heads, kv_heads, scale, out);
 }
 
+int rnb_b200_attention_decode_cached_window(size_t layer, const float *q, size_t q_len, const uint16_t *k, const uint16_t *v,
+                                            size_t kv_elems, size_t kv_len, size_t window_start, size_t window_len, size_t heads,
+                                            size_t kv_heads, size_t head_dim, float scale, float *out, size_t out_len) {
+    RNB_TRY(validate_attn(q_len, kv_elems, kv_len, heads, kv_heads, head_dim, out_len));
+    if (!q || !k || !v || !out) return fail(RNB_B200_VALIDATION_FAILED, "null pointer argument");
+    if (window_len == 0 || window_start > kv_len || window_len > kv_len - window_start)
+        return fail(RNB_B200_VALIDATION_FAILED, "cached window decode attention invalid window: kv_len=%zu start=%zu len=%zu", kv_len, window_start, window_len);
+    Locked L;
+    State &st = L.st;
+    RNB_TRY(st.open());
+    RNB_CU(cudaSetDevice(st.device));
+    // the mirror holds every position (the next call may widen the window); attention runs over the window's rows only
+    RNB_TRY(kv_mirror_sync(st, layer, k, v, kv_len, kv_heads * HD, nullptr, nullptr));
+    KvMirror &m = st.kv_mirrors[layer];
+    const size_t off = window_start * kv_heads * HD;
+    return attention_run(st, m.dk + off, m.dv + off, q, window_len, heads, kv_heads, scale, out);
+}
+
 int rnb_b200_clear_decode_attention_kv_cache(void) {
     Locked L;
     if (!L.st.is_open) return RNB_B200_OK;

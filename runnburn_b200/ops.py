@@ -225,6 +225,20 @@ def attention_decode_cached(layer_index: int, q, k, v, kv_len: int, num_heads: i
     return out
 
 
+def attention_decode_cached_window(layer_index: int, q, k, v, kv_len: int, window_start: int, window_len: int,
+                                   num_heads: int, num_kv_heads: int, head_dim: int, scale: float) -> np.ndarray:
+    """attention_decode_cached_window — api/attention_api.rs:2105: sliding-window decode over positions
+    [window_start, window_start + window_len) of the mirrored cache; an empty or out-of-range window raises."""
+    q = _f32(q).ravel()
+    assert k.dtype == np.uint16 and v.dtype == np.uint16 and k.flags["C_CONTIGUOUS"] and v.flags["C_CONTIGUOUS"], \
+        "the KV mirror is keyed by the host buffers' addresses: pass the cache arrays themselves"
+    out = np.empty(num_heads * head_dim, dtype=np.float32)
+    check(load().rnb_b200_attention_decode_cached_window(layer_index, _p(q), q.size, _p(k), _p(v), min(k.size, v.size), kv_len,
+                                                         window_start, window_len, num_heads, num_kv_heads, head_dim, scale,
+                                                         _p(out), out.size))
+    return out
+
+
 def clear_decode_attention_kv_cache() -> None:
     check(load().rnb_b200_clear_decode_attention_kv_cache())
 

@@ -242,6 +242,35 @@ def test_attention_decode_cached_appends_only_new_rows(ops):
     ops.clear_decode_attention_kv_cache()
 
 
+def test_attention_decode_cached_window(ops):
+    # sliding-window decode over the mirrored cache: equal to the CPU routine with sliding_window = window_len when the
+    # window ends at kv_len (bit for bit up to 512 positions), and attention over the range for any other start
+    rng = np.random.default_rng(22)
+    heads, kvh, cap = 8, 2, 1500
+    k = orc.f32_to_f16_bits(rng.standard_normal(cap * kvh * 128))
+    v = orc.f32_to_f16_bits(rng.standard_normal(cap * kvh * 128))
+    scale = 1.0 / np.sqrt(128.0)
+    ops.clear_decode_attention_kv_cache()
+    for kv_len, window in ((1, 1), (40, 8), (300, 300), (700, 512), (701, 33), (1500, 1024)):
+        q = rng.standard_normal(heads * 128).astype(np.float32)
+        got = ops.attention_decode_cached_window(4, q, k, v, kv_len, kv_len - window, window, heads, kvh, 128, scale)
+        ref = orc.attention_decode_window(q, k, v, heads, kvh, 128, kv_len, scale, window)
+        if window <= 512:
+            assert np.array_equal(got, ref), (kv_len, window)
+        else:
+            assert max_rel_err(got, ref) <= TOL and np.max(np.abs(got - ref)) < 1e-4
+    # a window in the middle of the cache: attention over those rows alone
+    q = rng.standard_normal(heads * 128).astype(np.float32)
+    got = ops.attention_decode_cached_window(4, q, k, v, 1500, 100, 200, heads, kvh, 128, scale)
+    lo, hi = 100 * kvh * 128, 300 * kvh * 128
+    assert np.array_equal(got, orc.attention_decode(q, k[lo:hi], v[lo:hi], heads, kvh, 128, 200, scale))
+    import runnburn_b200 as r
+    for start, length in ((0, 0), (1501, 1), (1400, 101)):
+        with pytest.raises(r.RnbError):
+            ops.attention_decode_cached_window(4, q, k, v, 1500, start, length, heads, kvh, 128, scale)
+    ops.clear_decode_attention_kv_cache()
+
+
 def test_attention_prefill_causal(ops):
     rng = np.random.default_rng(8)
     heads, kvh, seq, kv_len = 8, 2, 37, 50

@@ -487,3 +487,19 @@ def test_q3k_block_size_and_dot_against_dequantised_q8k(orc):
         want = back.astype(np.float64) @ xd.astype(np.float64)
         assert np.max(np.abs(got - want)) < 1e-4 * np.max(np.abs(want))
     assert _cos(w.ravel(), orc.dequantize_matrix(orc.TYPE_Q3_K, q, rows, cols).ravel()) >= 0.97
+
+
+def test_sliding_window_equals_attention_over_the_last_rows(orc):
+    # the literal routine (every position walked, masked ones scoring -inf) equals plain attention over the
+    # window's rows bit for bit: the masked weights are exact zeros
+    rng = np.random.default_rng(31)
+    heads, kvh, kv_len = 4, 2, 90
+    k = orc.f32_to_f16_bits(rng.standard_normal(kv_len * kvh * 128))
+    v = orc.f32_to_f16_bits(rng.standard_normal(kv_len * kvh * 128))
+    q = rng.standard_normal(heads * 128).astype(np.float32)
+    scale = 1.0 / np.sqrt(128.0)
+    for window in (1, 7, 64, 90, 200):
+        w = min(window, kv_len)
+        lo = (kv_len - w) * kvh * 128
+        full = orc.attention_decode_window(q, k, v, heads, kvh, 128, kv_len, scale, window)
+        assert np.array_equal(full, orc.attention_decode(q, k[lo:], v[lo:], heads, kvh, 128, w, scale))
