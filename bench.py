@@ -36,6 +36,9 @@ WORKLOADS = {
     # BASELINE config 4: Qwen3-30B-A3B shape, 128 experts top-8 (Q4_K), attention in Q6_K
     "qwen3-30b-a3b-moe-ctx8192": (dict(n_layer=48, hidden=2048, n_head=32, n_kv_head=4, n_ff=0, vocab=128256, n_expert=128, n_expert_used=8,
                                        n_ff_expert=768, rope_neox=1), 8192),
+    # eight layers of the MoE shapes + its LM head: the capture-sized case for ncu (about 3 GB resident, 0.6 GB streamed per token)
+    "qwen3-30b-a3b-moe-8layers-ctx8192": (dict(n_layer=8, hidden=2048, n_head=32, n_kv_head=4, n_ff=0, vocab=128256, n_expert=128, n_expert_used=8,
+                                               n_ff_expert=768, rope_neox=1), 8192),
     "tiny-llama-ctx256": (dict(n_layer=2, hidden=512, n_head=4, n_kv_head=2, n_ff=1024, vocab=2048), 256),
 }
 DRAM_TRAFFIC_OVER_ALGORITHMIC = 459.77 / 456.19   # ncu, gemv_mma_kernel_1: LM head + q/k/v + o launches (profiles/gemv_mma_kernel_llama3-8b-2layers-ctx4096.md)

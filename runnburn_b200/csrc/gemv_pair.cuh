@@ -27,6 +27,8 @@ struct GpParams {
     uint32_t row_stride;  // 16-byte multiple, = 32 or 96 mod 128: the 16-byte loads of a quarter-warp hit 8 bank groups
     uint32_t act_off;     // activation slice inside a stage: qs | bsum16 | d
     uint32_t slot_bytes;
+    int rows_per_tile;    // expert-gathered form only: 4, 8 or 16 rows per one-warp CTA (the other lanes idle).
+                          // The dense form is 16.
 };
 
 // Optional tail for a gate + up launch: the CTA that completes a 256-row block of both vectors
@@ -39,7 +41,7 @@ struct GpTail {
     int n;               // length of the gate / up vectors (multiple of 256); kind 3: rows per expert
     const float *gate, *up;   // kind 3: gate = the experts' raw rows [k][n], up = the k route weights
     uint8_t *xq_out;     // Q8K-dev layout of the n-vector
-    int *counters;       // n / 256 ints; kind 3: n / 16
+    int *counters;       // n / 256 ints; kind 3: n / rows per tile
     PeerOut peer;        // kind 2: where the finished rows also go
     int vec_n;           // kind 1: the n elements are n / vec_n vectors, each quantised on its own (0 = one vector)
     int sum_k;           // kind 3: experts per token
@@ -105,11 +107,12 @@ __device__ __forceinline__ void gemv_pair_body(const GemvJobPack &jobs, int n_jo
     for (int i = 1; i < n_jobs; i++)
         if (tile >= jobs.j[i].tile0) jsel = i;
     const GemvJob &job = jobs.j[jsel];
-    const int row0 = (tile - job.tile0) * GP_ROWS, nrows = min(GP_ROWS, job.rows - row0);
+    const int RPT = DYN ? P.rows_per_tile : GP_ROWS;
+    const int row0 = (tile - job.tile0) * RPT, nrows = min(RPT, job.rows - row0);
     const int cols = P.cols, nb = cols >> 8, CB = P.chunk, S = P.n_stages;
     if (nrows <= 0 || job.n_parts != 1 || job.type != TYPE_Q4_K || nb < 1 || CB < 1 || CB > GP_MAX_CHUNK || S < 1 || S > GP_MAX_STAGES ||
         blockDim.x != 32 || (P.row_stride & 15u) || (uint32_t)CB * Q4K_BYTES > P.row_stride || (P.act_off & 15u) ||
-        (uint32_t)GP_ROWS * P.row_stride > P.act_off || P.act_off + (uint32_t)CB * 288u + 32u > P.slot_bytes) {
+        RPT < 1 || RPT > GP_ROWS || (uint32_t)RPT * P.row_stride > P.act_off || P.act_off + (uint32_t)CB * 288u + 32u > P.slot_bytes) {
         if (lane == 0) atomicExch(dev_error, DEV_ERR_BAD_JOB);
         return;
     }
@@ -202,7 +205,7 @@ __device__ __forceinline__ void gemv_pair_body(const GemvJobPack &jobs, int n_jo
         __threadfence();   // this tile's 16 results are visible device-wide before the tile is counted
         __syncwarp();
         int last = 0;
-        if (lane == 0) last = atomicAdd(&tail.counters[blk], 1) == n_jobs * (256 / GP_ROWS) - 1;
+        if (lane == 0) last = atomicAdd(&tail.counters[blk], 1) == n_jobs * (256 / RPT) - 1;
         last = __shfl_sync(0xffffffffu, last, 0);
         if (!last) return;
         __threadfence();
@@ -232,7 +235,7 @@ __device__ __forceinline__ void gemv_pair_body(const GemvJobPack &jobs, int n_jo
     if (DYN && tail.kind == 3) {
         // the tile that completes its 16 rows over all experts folds them in selection order:
         // out = residual + ((0 + w0 * r0) + w1 * r1 + ...), the order of the multi-part matvec
-        const int e = row0 / tail.n, lrow0 = row0 - e * tail.n, ctr = lrow0 >> 4;
+        const int e = row0 / tail.n, lrow0 = row0 - e * tail.n, ctr = lrow0 / RPT;
         __threadfence();
         __syncwarp();
         int last = 0;
@@ -240,7 +243,7 @@ __device__ __forceinline__ void gemv_pair_body(const GemvJobPack &jobs, int n_jo
         last = __shfl_sync(0xffffffffu, last, 0);
         if (!last) return;
         __threadfence();
-        if (lane < GP_ROWS && lrow0 + lane < tail.n) {
+        if (lane < RPT && lrow0 + lane < tail.n) {
             const size_t o = (size_t)lrow0 + lane;
             float acc = 0.f;
             for (int k = 0; k < tail.sum_k; k++) acc = __fadd_rn(acc, __fmul_rn(__ldcg(tail.gate + (size_t)k * tail.n + o), __ldcg(tail.up + k)));

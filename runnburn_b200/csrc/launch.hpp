@@ -386,6 +386,7 @@ inline int launch_gemv_stream(cudaStream_t s, const GemvJob *jobs_host, const Ge
     P.n_stages = n_chunks < pt.stages ? n_chunks : pt.stages;
     P.row_stride = (uint32_t)P.chunk * Q4K_BYTES;
     while ((P.row_stride & 127u) != 32u && (P.row_stride & 127u) != 96u) P.row_stride += 16u;
+    P.rows_per_tile = GP_ROWS;
     P.act_off = ((uint32_t)GP_ROWS * P.row_stride + 127u) & ~127u;
     P.slot_bytes = (P.act_off + (uint32_t)P.chunk * 288u + 32u + 127u) & ~127u;
     const size_t smem = (size_t)P.n_stages * P.slot_bytes;
@@ -401,6 +402,17 @@ inline int launch_gemv_stream(cudaStream_t s, const GemvJob *jobs_host, const Ge
     return RNB_B200_OK;
 }
 
+// Rows per one-warp CTA of the expert-gathered matvec (RNB_B200_MOE_ROWS = 4, 8 or 16; the tail counters of the
+// callers are sized for 4).  Measured on the 48-layer MoE shape: 16 rows 2.996 ms per token, 8 rows 3.033, 4 rows 3.124 -
+// more, shorter warps do not pay although each warp is latency-bound.
+inline int moe_rows_per_tile() {
+    static const int v = [] {
+        const char *e = getenv("RNB_B200_MOE_ROWS");
+        const int x = (e && *e) ? atoi(e) : 16;
+        return (x == 4 || x == 8 || x == 16) ? x : 16;
+    }();
+    return v;
+}
 // Expert-gathered jobs (GemvJob::dyn_ids): static tables by value, the two-threads-per-row kernel's expert form.
 // Tunables: RNB_B200_MOE_CHUNK (super-blocks per stage, default min(4, row)), RNB_B200_MOE_STAGES (default 3).
 inline int launch_gemv_pair_dyn(cudaStream_t s, const GemvJob *jobs_host, int n_jobs, size_t cols, int *dev_error, const GpTail *tail, bool *tail_done) {
@@ -408,15 +420,16 @@ inline int launch_gemv_pair_dyn(cudaStream_t s, const GemvJob *jobs_host, int n_
     GemvJobPack pack;
     memset(&pack, 0, sizeof(pack));
     int tiles = 0;
+    const int rpt = moe_rows_per_tile();
     for (int i = 0; i < n_jobs; i++) {
         const GemvJob &j = jobs_host[i];
-        if (!j.dyn_ids || j.type != TYPE_Q4_K || j.n_parts != 1 || j.seq > 1 || j.epi != GEMV_EPI_NONE || j.dyn_rows < GP_ROWS || j.dyn_rows % GP_ROWS || j.rows % j.dyn_rows ||
+        if (!j.dyn_ids || j.type != TYPE_Q4_K || j.n_parts != 1 || j.seq > 1 || j.epi != GEMV_EPI_NONE || j.dyn_rows < rpt || j.dyn_rows % rpt || j.rows % j.dyn_rows ||
             ((((uintptr_t)j.parts[0].w | (uintptr_t)j.parts[0].x) | (uintptr_t)j.dyn_x_stride) & 15u))
             return fail(RNB_B200_VALIDATION_FAILED, "expert-gathered matvec: Q4_K, one part, 16-byte aligned operands, whole tiles per expert");
         pack.j[i] = j;
-        pack.j[i].rows_per_tile = GP_ROWS;
+        pack.j[i].rows_per_tile = rpt;
         pack.j[i].tile0 = tiles;
-        tiles += j.rows / GP_ROWS;
+        tiles += j.rows / rpt;
     }
     static const int env_chunk = [] {
         const char *e = getenv("RNB_B200_MOE_CHUNK");
@@ -434,7 +447,8 @@ inline int launch_gemv_pair_dyn(cudaStream_t s, const GemvJob *jobs_host, int n_
     P.n_stages = std::max(1, std::min(std::min(env_stages, GP_MAX_STAGES), n_chunks));
     P.row_stride = (uint32_t)P.chunk * Q4K_BYTES;
     while ((P.row_stride & 127u) != 32u && (P.row_stride & 127u) != 96u) P.row_stride += 16u;
-    P.act_off = ((uint32_t)GP_ROWS * P.row_stride + 127u) & ~127u;
+    P.rows_per_tile = rpt;
+    P.act_off = ((uint32_t)rpt * P.row_stride + 127u) & ~127u;
     P.slot_bytes = (P.act_off + (uint32_t)P.chunk * 288u + 32u + 127u) & ~127u;
     const size_t smem = (size_t)P.n_stages * P.slot_bytes;
     if (smem > gemv_smem_max()) return fail(RNB_B200_VALIDATION_FAILED, "expert-gathered matvec: stage ring of %zu bytes", smem);
