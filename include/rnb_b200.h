@@ -158,6 +158,17 @@ int rnb_b200_attention_decode_hd128(const float *q, size_t q_len, const uint16_t
                                     const uint16_t *v, size_t kv_elems, size_t kv_len,
                                     size_t num_heads, size_t num_kv_heads, float scale,
                                     float *out, size_t out_len);
+/* attention_decode_hd256 / attention_decode_hd512 — api/attention_api.rs:1906-1941,1980-2015: the
+ * same call for head_dim 256 and 512 (q f32[heads*D]; k, v f16 bits [kv_len][kv_heads][D]).  fp32
+ * split-KV on CUDA cores: within 1e-3 of the CPU routine, not tuned. */
+int rnb_b200_attention_decode_hd256(const float *q, size_t q_len, const uint16_t *k,
+                                    const uint16_t *v, size_t kv_elems, size_t kv_len,
+                                    size_t num_heads, size_t num_kv_heads, float scale,
+                                    float *out, size_t out_len);
+int rnb_b200_attention_decode_hd512(const float *q, size_t q_len, const uint16_t *k,
+                                    const uint16_t *v, size_t kv_elems, size_t kv_len,
+                                    size_t num_heads, size_t num_kv_heads, float scale,
+                                    float *out, size_t out_len);
 /* attention_decode_cached — api/attention_api.rs:2055-2102 (runtime/attention.rs:3913-4291):
  * per-layer device KV mirror keyed by the host K/V base addresses; only rows the mirror does
  * not hold yet are uploaded. */

@@ -105,6 +105,8 @@ def load() -> C.CDLL:
         "rnb_b200_q4k_bf16_gemm_batch": [vp, sz, sz, sz, vp, sz, vp, sz],
         "rnb_b200_q6k_bf16_gemm_batch": [vp, sz, sz, sz, vp, sz, vp, sz],
         "rnb_b200_attention_decode_hd128": [vp, sz, vp, vp, sz, sz, sz, sz, f32, vp, sz],
+        "rnb_b200_attention_decode_hd256": [vp, sz, vp, vp, sz, sz, sz, sz, f32, vp, sz],
+        "rnb_b200_attention_decode_hd512": [vp, sz, vp, vp, sz, sz, sz, sz, f32, vp, sz],
         "rnb_b200_attention_decode_cached": [sz, vp, sz, vp, vp, sz, sz, sz, sz, sz, f32, vp, sz],
         "rnb_b200_attention_decode_cached_window": [sz, vp, sz, vp, vp, sz, sz, sz, sz, sz, sz, sz, f32, vp, sz],
         "rnb_b200_clear_decode_attention_kv_cache": [],

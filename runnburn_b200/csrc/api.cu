@@ -6,6 +6,7 @@
 
 #include "launch.hpp"
 #include "prefill.cuh"
+#include "attention_wide.cuh"
 
 namespace rnb {
 
@@ -706,6 +707,54 @@ int rnb_b200_attention_decode_hd128(const float *q, size_t q_len, const uint16_t
     RNB_CU(cudaMemcpyAsync(st.mid_b.p, v, bytes, cudaMemcpyHostToDevice, st.stream));
     st.ctr.h2d_bytes += 2 * bytes;
     return attention_run(st, st.mid_a.as<uint16_t>(), st.mid_b.as<uint16_t>(), q, kv_len, heads, kv_heads, scale, out);
+}
+
+// head_dim 256 / 512: split-KV on CUDA cores (attention_wide.cuh)
+static int attention_decode_wide(const size_t HD_, const float *q, size_t q_len, const uint16_t *k, const uint16_t *v, size_t kv_elems, size_t kv_len, size_t heads,
+                                 size_t kv_heads, float scale, float *out, size_t out_len) {
+    if (kv_heads == 0 || heads == 0 || heads % kv_heads != 0)
+        return fail(RNB_B200_VALIDATION_FAILED, "attention: num_heads(%zu) must be a multiple of num_kv_heads(%zu)", heads, kv_heads);
+    if (q_len != heads * HD_) return fail(RNB_B200_VALIDATION_FAILED, "decode attention q len mismatch: got %zu, expected %zu", q_len, heads * HD_);
+    if (kv_elems < kv_len * kv_heads * HD_)
+        return fail(RNB_B200_VALIDATION_FAILED, "decode attention k/v len mismatch: got %zu, expected >= %zu", kv_elems, kv_len * kv_heads * HD_);
+    if (out_len < heads * HD_) return fail(RNB_B200_VALIDATION_FAILED, "attention output too small: got %zu, expected >= %zu", out_len, heads * HD_);
+    if (kv_len == 0) return fail(RNB_B200_VALIDATION_FAILED, "attention kv_len must be non-zero");
+    if (kv_len > (size_t)1 << 30) return fail(RNB_B200_VALIDATION_FAILED, "attention kv_len too large");
+    if (!q || !k || !v || !out) return fail(RNB_B200_VALIDATION_FAILED, "null pointer argument");
+    Locked L;
+    State &st = L.st;
+    RNB_TRY(st.open());
+    RNB_CU(cudaSetDevice(st.device));
+    const size_t bytes = kv_len * kv_heads * HD_ * sizeof(uint16_t), qb = heads * HD_ * sizeof(float);
+    RNB_TRY(st.mid_a.ensure(bytes));
+    RNB_TRY(st.mid_b.ensure(bytes));
+    RNB_CU(cudaMemcpyAsync(st.mid_a.p, k, bytes, cudaMemcpyHostToDevice, st.stream));
+    RNB_CU(cudaMemcpyAsync(st.mid_b.p, v, bytes, cudaMemcpyHostToDevice, st.stream));
+    st.ctr.h2d_bytes += 2 * bytes;
+    RNB_TRY(st.in_f32.ensure(qb));
+    RNB_TRY(st.h2d(st.in_f32.p, q, qb, st.pin_in));
+    const int n_chunks = attention_wide_chunks(kv_len, heads, st.sm_count);
+    RNB_TRY(st.partials.ensure(attention_wide_scratch_bytes(heads, n_chunks, HD_)));
+    RNB_TRY(st.out_f32.ensure(qb));
+    const dim3 grid((unsigned)heads, (unsigned)n_chunks);
+    const float *qd = st.in_f32.as<float>(), *pd = st.partials.as<float>();
+    const uint16_t *kd = st.mid_a.as<uint16_t>(), *vd = st.mid_b.as<uint16_t>();
+    if (HD_ == 256) {
+        RNB_CU(launch_k(attention_wide_partials_kernel<256>, grid, dim3(AW_THREADS), 0, st.stream, qd, kd, vd, (int)kv_len, (int)heads, (int)kv_heads, scale, st.partials.as<float>()));
+        RNB_CU(launch_k(attention_wide_merge_kernel<256>, dim3((unsigned)heads), dim3(128), 0, st.stream, pd, n_chunks, st.out_f32.as<float>()));
+    } else {
+        RNB_CU(launch_k(attention_wide_partials_kernel<512>, grid, dim3(AW_THREADS), 0, st.stream, qd, kd, vd, (int)kv_len, (int)heads, (int)kv_heads, scale, st.partials.as<float>()));
+        RNB_CU(launch_k(attention_wide_merge_kernel<512>, dim3((unsigned)heads), dim3(256), 0, st.stream, pd, n_chunks, st.out_f32.as<float>()));
+    }
+    return finish_to_host(st, st.out_f32.p, out, qb);
+}
+int rnb_b200_attention_decode_hd256(const float *q, size_t q_len, const uint16_t *k, const uint16_t *v, size_t kv_elems, size_t kv_len, size_t heads,
+                                    size_t kv_heads, float scale, float *out, size_t out_len) {
+    return attention_decode_wide(256, q, q_len, k, v, kv_elems, kv_len, heads, kv_heads, scale, out, out_len);
+}
+int rnb_b200_attention_decode_hd512(const float *q, size_t q_len, const uint16_t *k, const uint16_t *v, size_t kv_elems, size_t kv_len, size_t heads,
+                                    size_t kv_heads, float scale, float *out, size_t out_len) {
+    return attention_decode_wide(512, q, q_len, k, v, kv_elems, kv_len, heads, kv_heads, scale, out, out_len);
 }
 
 int rnb_b200_attention_decode_cached(size_t layer, const float *q, size_t q_len, const uint16_t *k, const uint16_t *v,

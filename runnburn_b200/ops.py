@@ -214,6 +214,23 @@ def attention_decode_hd128(q, k, v, kv_len: int, num_heads: int, num_kv_heads: i
     return out
 
 
+def _attention_decode_wide(fn, head_dim: int, q, k, v, kv_len: int, num_heads: int, num_kv_heads: int, scale: float) -> np.ndarray:
+    q, k, v = _f32(q).ravel(), _u16(k).ravel(), _u16(v).ravel()
+    out = np.empty(num_heads * head_dim, dtype=np.float32)
+    check(fn(_p(q), q.size, _p(k), _p(v), min(k.size, v.size), kv_len, num_heads, num_kv_heads, scale, _p(out), out.size))
+    return out
+
+
+def attention_decode_hd256(q, k, v, kv_len: int, num_heads: int, num_kv_heads: int, scale: float) -> np.ndarray:
+    """attention_decode_hd256 — api/attention_api.rs:1906"""
+    return _attention_decode_wide(load().rnb_b200_attention_decode_hd256, 256, q, k, v, kv_len, num_heads, num_kv_heads, scale)
+
+
+def attention_decode_hd512(q, k, v, kv_len: int, num_heads: int, num_kv_heads: int, scale: float) -> np.ndarray:
+    """attention_decode_hd512 — api/attention_api.rs:1980"""
+    return _attention_decode_wide(load().rnb_b200_attention_decode_hd512, 512, q, k, v, kv_len, num_heads, num_kv_heads, scale)
+
+
 def attention_decode_cached(layer_index: int, q, k, v, kv_len: int, num_heads: int, num_kv_heads: int,
                             head_dim: int, scale: float) -> np.ndarray:
     q = _f32(q).ravel()

@@ -242,6 +242,27 @@ def test_attention_decode_cached_appends_only_new_rows(ops):
     ops.clear_decode_attention_kv_cache()
 
 
+@pytest.mark.parametrize("head_dim", [256, 512])
+def test_attention_decode_wide_heads(ops, head_dim):
+    # head_dim 256 / 512 (attention_decode_hd256 / _hd512): fp32 split-KV against the CPU routine, the bounds of the
+    # long-context hd128 path
+    rng = np.random.default_rng(23 + head_dim)
+    fn = ops.attention_decode_hd256 if head_dim == 256 else ops.attention_decode_hd512
+    scale = 1.0 / np.sqrt(float(head_dim))
+    for heads, kvh, kv_len in ((8, 2, 1), (8, 2, 37), (4, 4, 300), (16, 2, 2051), (1, 1, 5000)):
+        q = rng.standard_normal(heads * head_dim).astype(np.float32)
+        k = orc.f32_to_f16_bits(rng.standard_normal(kv_len * kvh * head_dim))
+        v = orc.f32_to_f16_bits(rng.standard_normal(kv_len * kvh * head_dim))
+        got = fn(q, k, v, kv_len, heads, kvh, scale)
+        ref = orc.attention_decode(q, k, v, heads, kvh, head_dim, kv_len, scale)
+        assert max_err_vs_norm(got, ref) <= TOL / 10 and np.max(np.abs(got - ref)) < 1e-4, (heads, kvh, kv_len)
+    import runnburn_b200 as r
+    with pytest.raises(r.RnbError):
+        fn(q[:-1], k, v, kv_len, heads, kvh, scale)
+    with pytest.raises(r.RnbError):
+        fn(q, k, v, 0, heads, kvh, scale)
+
+
 def test_attention_decode_cached_window(ops):
     # sliding-window decode over the mirrored cache: equal to the CPU routine with sliding_window = window_len when the
     # window ends at kv_len (bit for bit up to 512 positions), and attention over the range for any other start
