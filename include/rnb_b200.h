@@ -131,6 +131,13 @@ int rnb_b200_q6k_gemv_with_device_input(const uint8_t *weights, size_t weights_l
 int rnb_b200_q6k_gemv_argmax(const uint8_t *weights, size_t weights_len, size_t rows, size_t cols,
                              const float *input, size_t input_len, uint32_t *index_out,
                              float *value_out);
+/* q8_0_gemv_argmax -> (u32, f32) and q8_0_gemv_batch — api/quant_api.rs:733,807: the Q8_0 LM head
+ * and the batched Q8_0 matvec (input [seq][cols], output [seq][rows]); same tie rule. */
+int rnb_b200_q8_0_gemv_argmax(const uint8_t *weights, size_t weights_len, size_t rows, size_t cols,
+                              const float *input, size_t input_len, uint32_t *index_out,
+                              float *value_out);
+int rnb_b200_q8_0_gemv_batch(const uint8_t *weights, size_t weights_len, size_t rows, size_t cols,
+                             const float *input, size_t input_len, float *output, size_t output_len);
 /* q4k_gemv_batch / q6k_gemv_batch — api/quant_api.rs:2283,3919: input [seq][cols], output
  * seq-major [seq][rows]. */
 int rnb_b200_q4k_gemv_batch(const uint8_t *weights, size_t weights_len, size_t rows, size_t cols,
@@ -150,6 +157,15 @@ int rnb_b200_q4k_bf16_gemm_batch(const uint8_t *weights, size_t weights_len, siz
 int rnb_b200_q6k_bf16_gemm_batch(const uint8_t *weights, size_t weights_len, size_t rows, size_t cols,
                                  const float *input, size_t input_len, float *output,
                                  size_t output_len);
+
+/* quant_embedding_gather(quant, weights, rows, cols, token_ids) — api/quant_api.rs:1827-1905:
+ * out [n_tokens][cols] f32 = the dequantised rows token_ids[i] of a quantised embedding table
+ * (bit-identical to the CPU dequantisers).  quant: RNB_B200_TYPE_Q8_0 / Q4_K / Q6_K, cols a multiple
+ * of 256; other types RNB_B200_UNSUPPORTED; an id >= rows RNB_B200_VALIDATION_FAILED; no tokens:
+ * nothing written. */
+int rnb_b200_quant_embedding_gather(uint32_t quant, const uint8_t *weights, size_t weights_len,
+                                    size_t rows, size_t cols, const uint32_t *token_ids,
+                                    size_t n_tokens, float *out, size_t out_len);
 
 /* ---- attention ---------------------------------------------------------------------------- */
 /* attention_decode_hd128 — api/attention_api.rs:1943-1978.  q f32[heads*128]; k, v f16 bits

@@ -100,11 +100,14 @@ def load() -> C.CDLL:
         "rnb_b200_q4k_gemv_with_device_input": [vp, sz, sz, sz, u64, vp, sz],
         "rnb_b200_q6k_gemv_with_device_input": [vp, sz, sz, sz, u64, vp, sz],
         "rnb_b200_q6k_gemv_argmax": [vp, sz, sz, sz, vp, sz, vp, vp],
+        "rnb_b200_q8_0_gemv_argmax": [vp, sz, sz, sz, vp, sz, vp, vp],
+        "rnb_b200_q8_0_gemv_batch": [vp, sz, sz, sz, vp, sz, vp, sz],
         "rnb_b200_q4k_gemv_batch": [vp, sz, sz, sz, vp, sz, vp, sz],
         "rnb_b200_q6k_gemv_batch": [vp, sz, sz, sz, vp, sz, vp, sz],
         "rnb_b200_q4k_bf16_gemm_batch": [vp, sz, sz, sz, vp, sz, vp, sz],
         "rnb_b200_q6k_bf16_gemm_batch": [vp, sz, sz, sz, vp, sz, vp, sz],
         "rnb_b200_attention_decode_hd128": [vp, sz, vp, vp, sz, sz, sz, sz, f32, vp, sz],
+        "rnb_b200_quant_embedding_gather": [u32, vp, sz, sz, sz, vp, sz, vp, sz],
         "rnb_b200_attention_decode_hd256": [vp, sz, vp, vp, sz, sz, sz, sz, f32, vp, sz],
         "rnb_b200_attention_decode_hd512": [vp, sz, vp, vp, sz, sz, sz, sz, f32, vp, sz],
         "rnb_b200_attention_decode_cached": [sz, vp, sz, vp, vp, sz, sz, sz, sz, sz, f32, vp, sz],

@@ -636,6 +636,14 @@ int rnb_b200_q6k_gemv_argmax(const uint8_t *w, size_t wl, size_t rows, size_t co
     if (!idx) return fail(RNB_B200_VALIDATION_FAILED, "null index output");
     return gemv_host(TYPE_Q6_K, w, wl, rows, cols, in, il, 0, 1, nullptr, 0, idx, val);
 }
+int rnb_b200_q8_0_gemv_argmax(const uint8_t *w, size_t wl, size_t rows, size_t cols, const float *in, size_t il, uint32_t *idx, float *val) {
+    if (!idx) return fail(RNB_B200_VALIDATION_FAILED, "null index output");
+    return gemv_host(TYPE_Q8_0, w, wl, rows, cols, in, il, 0, 1, nullptr, 0, idx, val);
+}
+int rnb_b200_q8_0_gemv_batch(const uint8_t *w, size_t wl, size_t rows, size_t cols, const float *in, size_t il, float *out, size_t ol) {
+    if (cols == 0 || il % cols != 0) return fail(RNB_B200_VALIDATION_FAILED, "Q8_0 batch input length %zu is not a multiple of cols %zu", il, cols);
+    return prefill_gemm_host(TYPE_Q8_0, w, wl, rows, cols, in, il / cols, out, ol);
+}
 int rnb_b200_q4k_gemv_batch(const uint8_t *w, size_t wl, size_t rows, size_t cols, const float *in, size_t il, float *out, size_t ol) {
     if (cols == 0 || il % cols != 0) return fail(RNB_B200_VALIDATION_FAILED, "Q4_K batch input length %zu is not a multiple of cols %zu", il, cols);
     return prefill_gemm_host(TYPE_Q4_K, w, wl, rows, cols, in, il / cols, out, ol);

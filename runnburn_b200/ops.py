@@ -183,6 +183,20 @@ def q6k_gemv_argmax(weights, rows: int, cols: int, x) -> tuple[int, float]:
     return idx.value, val.value
 
 
+def q8_0_gemv_argmax(weights, rows: int, cols: int, x) -> tuple[int, float]:
+    """q8_0_gemv_argmax — api/quant_api.rs:733"""
+    w, x = _u8(weights), _f32(x).ravel()
+    idx, val = C.c_uint32(), C.c_float()
+    check(load().rnb_b200_q8_0_gemv_argmax(_p(w), w.size, rows, cols, _p(x), x.size, C.byref(idx), C.byref(val)))
+    return idx.value, val.value
+
+
+def q8_0_gemv_batch(weights, rows: int, cols: int, x) -> np.ndarray:
+    """q8_0_gemv_batch — api/quant_api.rs:807: input [seq][cols], output [seq][rows]"""
+    x = _f32(x).ravel()
+    return _gemv(load().rnb_b200_q8_0_gemv_batch, weights, rows, cols, x, seq=max(1, x.size // max(cols, 1)))
+
+
 def q4k_gemv_batch(weights, rows: int, cols: int, x) -> np.ndarray:
     x = _f32(x).ravel()
     return _gemv(load().rnb_b200_q4k_gemv_batch, weights, rows, cols, x, seq=max(1, x.size // max(cols, 1)))
@@ -211,6 +225,16 @@ def attention_decode_hd128(q, k, v, kv_len: int, num_heads: int, num_kv_heads: i
     out = np.empty(num_heads * 128, dtype=np.float32)
     check(load().rnb_b200_attention_decode_hd128(_p(q), q.size, _p(k), _p(v), min(k.size, v.size), kv_len,
                                                  num_heads, num_kv_heads, scale, _p(out), out.size))
+    return out
+
+
+def quant_embedding_gather(quant: int, weights, rows: int, cols: int, token_ids) -> np.ndarray:
+    """quant_embedding_gather — api/quant_api.rs:1827: f32 [n_tokens][cols] rows of a quantised embedding table"""
+    w = _u8(weights)
+    ids = np.ascontiguousarray(token_ids, dtype=np.uint32).ravel()
+    out = np.empty((ids.size, cols), dtype=np.float32)
+    check(load().rnb_b200_quant_embedding_gather(quant, _p(w), w.size, rows, cols, _p(ids) if ids.size else None, ids.size,
+                                                 _p(out) if ids.size else None, out.size))
     return out
 
 

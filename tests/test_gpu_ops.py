@@ -168,6 +168,25 @@ def test_q6k_gemv_argmax_tie_rule(ops):
     assert idx == max(i for i in range(rows) if y[i] == y.max())
 
 
+def test_q8_0_gemv_argmax_and_batch(ops):
+    # the Q8_0 LM-head form (argmax with the sampler's tie rule) and the batched Q8_0 matvec: same bits as the
+    # single-token call
+    rng = np.random.default_rng(12)
+    rows, cols, seq = 500, 256, 4
+    w = random_blocks(rng, Q8_0, rows, cols).reshape(rows, -1)
+    x = rng.standard_normal((seq, cols)).astype(np.float32)
+    y0 = orc.gemv(Q8_0, w.ravel(), x[0], rows, cols)
+    w[400] = w[int(np.argmax(y0))]       # the maximum twice: the later row wins
+    w[77] = w[400]
+    y = ops.q8_0_gemv(w.ravel(), rows, cols, x[0])
+    assert bits_equal(y, orc.gemv(Q8_0, w.ravel(), x[0], rows, cols))
+    idx, val = ops.q8_0_gemv_argmax(w.ravel(), rows, cols, x[0])
+    assert idx == orc.argmax_last(y) and val == y[idx] and idx == max(i for i in range(rows) if y[i] == y.max())
+    got = ops.q8_0_gemv_batch(w.ravel(), rows, cols, x)
+    for s in range(seq):
+        assert np.array_equal(got[s * rows:(s + 1) * rows], ops.q8_0_gemv(w.ravel(), rows, cols, x[s]))
+
+
 def test_resident_cache_counters_and_eviction(ops):
     ops.reset_state_for_engine_init()
     rng = np.random.default_rng(1)
@@ -240,6 +259,25 @@ def test_attention_decode_cached_appends_only_new_rows(ops):
     moved = ops.cuda_cache_snapshot()["h2d_bytes"] - before
     assert moved == 2 * 600 * kvh * 128 * 2 + 6 * heads * 128 * 4   # each KV row crossed PCIe once
     ops.clear_decode_attention_kv_cache()
+
+
+@pytest.mark.parametrize("ggml_type", [Q4_K, Q6_K, Q8_0])
+def test_quant_embedding_gather_bit_exact(ops, ggml_type):
+    # quant_embedding_gather: the selected rows of a quantised table, dequantised on the device, equal the CPU
+    # dequantiser's bit for bit; ragged cases: no tokens, repeated ids, the last row, an id out of range
+    rng = np.random.default_rng(40 + ggml_type)
+    rows, cols = 300, 512
+    _, w = quantized(rng, ggml_type, rows, cols)
+    table = orc.dequantize_matrix(ggml_type, w, rows, cols)
+    ids = np.array([0, 299, 17, 17, 255, 1], dtype=np.uint32)
+    got = ops.quant_embedding_gather(ggml_type, w, rows, cols, ids)
+    assert got.shape == (6, cols) and np.array_equal(got, table[ids])
+    assert ops.quant_embedding_gather(ggml_type, w, rows, cols, []).shape == (0, cols)
+    import runnburn_b200 as r
+    with pytest.raises(r.RnbError, match="out of range"):
+        ops.quant_embedding_gather(ggml_type, w, rows, cols, [300])
+    with pytest.raises(r.RnbError, match="byte mismatch"):
+        ops.quant_embedding_gather(ggml_type, w[:-1], rows, cols, [0])
 
 
 @pytest.mark.parametrize("head_dim", [256, 512])
