@@ -146,6 +146,17 @@ int rnb_b200_q4k_gemv_batch(const uint8_t *weights, size_t weights_len, size_t r
 int rnb_b200_q6k_gemv_batch(const uint8_t *weights, size_t weights_len, size_t rows, size_t cols,
                             const float *input, size_t input_len, float *output,
                             size_t output_len);
+/* q4k_f16_qkv_gemm_batch(q_weights, k_weights, v_weights, q_rows, kv_rows, cols, input) ->
+ * (q, k, v) — api/quant_api.rs:2405-2463: the three Q4_K projections of a token batch behind one
+ * token matrix; here one tcgen05 launch (bf16 x bf16, f32 accumulate).  Outputs [seq][q_rows],
+ * [seq][kv_rows], [seq][kv_rows]. */
+int rnb_b200_q4k_bf16_qkv_gemm_batch(const uint8_t *q_weights, size_t q_weights_len,
+                                     const uint8_t *k_weights, size_t k_weights_len,
+                                     const uint8_t *v_weights, size_t v_weights_len, size_t q_rows,
+                                     size_t kv_rows, size_t cols, const float *input,
+                                     size_t input_len, float *q_out, size_t q_out_len,
+                                     float *k_out, size_t k_out_len, float *v_out,
+                                     size_t v_out_len);
 /* q4k_f16_gemm_batch — api/quant_api.rs:2364 (runtime/gemv.rs:2335-2421: dequant -> f16 +
  * cublasGemmEx with f32 accumulation).  Here: weights dequantised tile-wise to bf16 inside a
  * tcgen05 kernel, tokens rounded to bf16, f32 accumulators in tensor memory.  Same argument

@@ -431,6 +431,44 @@ static int prefill_tc_host(int type, const uint8_t *w, size_t wl, size_t rows, s
     return st.check_dev_error();
 }
 
+// q / k / v of a token batch in one tensor-core launch (the reference's q4k_f16_qkv_gemm_batch)
+static int prefill_tc_qkv_host(const uint8_t *qw, size_t qwl, const uint8_t *kw, size_t kwl, const uint8_t *vw, size_t vwl, size_t q_rows, size_t kv_rows,
+                               size_t cols, const float *in, size_t il, float *q_out, size_t q_len, float *k_out, size_t k_len, float *v_out, size_t v_len) {
+    if (cols == 0 || cols % 256 != 0) return fail(RNB_B200_VALIDATION_FAILED, "Q4_K QKV GEMM cols must be divisible by 256, got %zu", cols);
+    if (il == 0 || il % cols != 0) return fail(RNB_B200_VALIDATION_FAILED, "Q4_K QKV GEMM batch input length %zu is not divisible by cols %zu", il, cols);
+    const size_t seq = il / cols, rb = cols / 256 * Q4K_BYTES;
+    if (qwl != q_rows * rb) return fail(RNB_B200_VALIDATION_FAILED, "Q4_K QKV GEMM q weight byte mismatch: got %zu, expected %zu", qwl, q_rows * rb);
+    if (kwl != kv_rows * rb || vwl != kv_rows * rb)
+        return fail(RNB_B200_VALIDATION_FAILED, "Q4_K QKV GEMM k/v weight byte mismatch: k=%zu v=%zu expected %zu", kwl, vwl, kv_rows * rb);
+    if (q_rows == 0 || kv_rows == 0) return fail(RNB_B200_VALIDATION_FAILED, "Q4_K QKV GEMM needs rows");
+    if (q_len < seq * q_rows || k_len < seq * kv_rows || v_len < seq * kv_rows) return fail(RNB_B200_VALIDATION_FAILED, "Q4_K QKV GEMM output too small");
+    if (!qw || !kw || !vw || !in || !q_out || !k_out || !v_out) return fail(RNB_B200_VALIDATION_FAILED, "null pointer argument");
+    Locked L;
+    State &st = L.st;
+    RNB_TRY(st.open());
+    RNB_CU(cudaSetDevice(st.device));
+    const uint8_t *w_dev[3] = {nullptr, nullptr, nullptr};
+    RNB_TRY(st.resident_ptr(qw, qwl, false, &w_dev[0]));
+    RNB_TRY(st.resident_ptr(kw, kwl, false, &w_dev[1]));
+    RNB_TRY(st.resident_ptr(vw, vwl, false, &w_dev[2]));
+    RNB_TRY(st.in_f32.ensure(il * sizeof(float)));
+    RNB_TRY(st.h2d(st.in_f32.p, in, il * sizeof(float), st.pin_in));
+    RNB_TRY(st.xb.ensure(il * 2));
+    const size_t qn = seq * q_rows, kn = seq * kv_rows;
+    const size_t qn_pad = (qn + 3) & ~(size_t)3, kn_pad = (kn + 3) & ~(size_t)3;   // 16-byte aligned outputs
+    RNB_TRY(st.out_f32.ensure((qn_pad + 2 * kn_pad) * sizeof(float) + 16));
+    float *y[3] = {st.out_f32.as<float>(), st.out_f32.as<float>() + qn_pad, st.out_f32.as<float>() + qn_pad + kn_pad};
+    const int types[3] = {TYPE_Q4_K, TYPE_Q4_K, TYPE_Q4_K};
+    const size_t rows[3] = {q_rows, kv_rows, kv_rows};
+    RNB_TRY(launch_prefill_gemm_multi(st.stream, 3, types, w_dev, rows, y, cols, st.in_f32.as<float>(), seq, st.xb.as<uint16_t>(), st.dev_error));
+    RNB_CU(cudaMemcpyAsync(q_out, y[0], qn * sizeof(float), cudaMemcpyDeviceToHost, st.stream));
+    RNB_CU(cudaMemcpyAsync(k_out, y[1], kn * sizeof(float), cudaMemcpyDeviceToHost, st.stream));
+    RNB_CU(cudaMemcpyAsync(v_out, y[2], kn * sizeof(float), cudaMemcpyDeviceToHost, st.stream));
+    RNB_CU(cudaStreamSynchronize(st.stream));
+    st.ctr.d2h_bytes += (qn + 2 * kn) * sizeof(float);
+    return st.check_dev_error();
+}
+
 }  // namespace rnb
 
 using namespace rnb;
@@ -657,6 +695,11 @@ int rnb_b200_q4k_bf16_gemm_batch(const uint8_t *w, size_t wl, size_t rows, size_
 }
 int rnb_b200_q6k_bf16_gemm_batch(const uint8_t *w, size_t wl, size_t rows, size_t cols, const float *in, size_t il, float *out, size_t ol) {
     return prefill_tc_host(TYPE_Q6_K, w, wl, rows, cols, in, il, out, ol);
+}
+int rnb_b200_q4k_bf16_qkv_gemm_batch(const uint8_t *qw, size_t qwl, const uint8_t *kw, size_t kwl, const uint8_t *vw, size_t vwl, size_t q_rows,
+                                     size_t kv_rows, size_t cols, const float *in, size_t il, float *q_out, size_t q_len, float *k_out, size_t k_len,
+                                     float *v_out, size_t v_len) {
+    return prefill_tc_qkv_host(qw, qwl, kw, kwl, vw, vwl, q_rows, kv_rows, cols, in, il, q_out, q_len, k_out, k_len, v_out, v_len);
 }
 int rnb_b200_dev_prefill_gemm(int type, const uint8_t *w_dev, size_t rows, size_t cols, const float *x_dev, size_t seq, uint16_t *xb_dev,
                               float *y_dev, void *stream) {

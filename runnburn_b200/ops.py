@@ -207,6 +207,19 @@ def q6k_gemv_batch(weights, rows: int, cols: int, x) -> np.ndarray:
     return _gemv(load().rnb_b200_q6k_gemv_batch, weights, rows, cols, x, seq=max(1, x.size // max(cols, 1)))
 
 
+def q4k_bf16_qkv_gemm_batch(q_weights, k_weights, v_weights, q_rows: int, kv_rows: int, cols: int, x):
+    """q4k_f16_qkv_gemm_batch — api/quant_api.rs:2405: (q [seq][q_rows], k [seq][kv_rows], v [seq][kv_rows]) of a
+    token batch, the three Q4_K projections in one tensor-core launch."""
+    qw, kw, vw, x = _u8(q_weights), _u8(k_weights), _u8(v_weights), _f32(x).ravel()
+    seq = x.size // max(cols, 1)
+    q = np.empty(seq * q_rows, dtype=np.float32)
+    k = np.empty(seq * kv_rows, dtype=np.float32)
+    v = np.empty(seq * kv_rows, dtype=np.float32)
+    check(load().rnb_b200_q4k_bf16_qkv_gemm_batch(_p(qw), qw.size, _p(kw), kw.size, _p(vw), vw.size, q_rows, kv_rows, cols, _p(x), x.size,
+                                                  _p(q), q.size, _p(k), k.size, _p(v), v.size))
+    return q, k, v
+
+
 def q4k_bf16_gemm_batch(weights, rows: int, cols: int, x) -> np.ndarray:
     """Tensor-core prefill matmul (reference: q4k_f16_gemm_batch, api/quant_api.rs:2364): bf16
     weights x bf16 tokens, f32 accumulate, output [seq][rows]."""

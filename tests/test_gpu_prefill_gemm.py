@@ -61,6 +61,24 @@ def test_bf16_gemm_uniform_quant_blocks_config1_shape(ops):
     assert max_err_vs_norm(got, ref) <= TOL / 10
 
 
+def test_bf16_qkv_gemm_batch_equals_the_single_matrix_calls(ops):
+    # q4k_f16_qkv_gemm_batch: three Q4_K projections of one token batch; each output equals the single-matrix call's
+    # (same kernel, same tiles) and so inherits its bound against the oracle
+    rng = np.random.default_rng(17)
+    q_rows, kv_rows, cols, seq = 512, 130, 1024, 45
+    ws = [quantized(rng, Q4_K, r, cols)[1] for r in (q_rows, kv_rows, kv_rows)]
+    x = rng.standard_normal((seq, cols)).astype(np.float32)
+    q, k, v = ops.q4k_bf16_qkv_gemm_batch(ws[0], ws[1], ws[2], q_rows, kv_rows, cols, x)
+    for got, w, rows in ((q, ws[0], q_rows), (k, ws[1], kv_rows), (v, ws[2], kv_rows)):
+        assert np.array_equal(got, ops.q4k_bf16_gemm_batch(w, rows, cols, x))
+        wd = orc.dequantize_matrix(Q4_K, w, rows, cols).reshape(rows, cols)
+        ref = bf16_round(x).astype(np.float64) @ bf16_round(wd).astype(np.float64).T
+        assert max_err_vs_norm(got.reshape(seq, rows), ref) <= TOL / 10
+    import runnburn_b200 as r
+    with pytest.raises(r.RnbError, match="byte mismatch"):
+        ops.q4k_bf16_qkv_gemm_batch(ws[0], ws[1][:-1], ws[2], q_rows, kv_rows, cols, x)
+
+
 def test_bf16_gemm_three_matrices_one_launch(ops):
     """q/k/v style: three matrices (mixed Q4_K / Q6_K, different row counts) behind one token tile."""
     import ctypes as C
