@@ -228,6 +228,16 @@ int rnb_b200_attention_prefill_flash_hd128(const float *q, const float *k, const
 int rnb_b200_attention_prefill_flash_hd128_f16kv(const float *q, const uint16_t *k, const uint16_t *v,
                                                  size_t seq_len, size_t kv_len, size_t num_heads,
                                                  size_t num_kv_heads, float scale, float *out);
+/* dense_q4k_attention_qkv(q_weights, k_weights, v_weights, q_rows, kv_rows, n_embd, input, q, k, v)
+ * — api/dense_api.rs:916-986: the three projections of one token in one launch, no RoPE; each
+ * output equals the single-matrix matvec's bit for bit.  A GGML type id per matrix (Q4_K_M keeps
+ * attn_v in Q6_K). */
+int rnb_b200_dense_attention_qkv(const uint8_t *q_w, size_t q_w_len, uint32_t q_type,
+                                 const uint8_t *k_w, size_t k_w_len, uint32_t k_type,
+                                 const uint8_t *v_w, size_t v_w_len, uint32_t v_type, size_t q_rows,
+                                 size_t kv_rows, size_t n_embd, const float *input,
+                                 size_t input_len, float *q, size_t q_len, float *k, size_t k_len,
+                                 float *v, size_t v_len);
 /* dense_q4k_attention_qkv_rope_hd128_decode — api/dense_api.rs:988-1074: q/k/v matvec,
  * adjacent-pair RoPE on q and k at position pos_start, K/V rounded to f16.  Weight types are
  * given per matrix (the reference's name says Q4_K; Q4_K_M files carry Q6_K in attn_v). */

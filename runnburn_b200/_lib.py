@@ -101,6 +101,7 @@ def load() -> C.CDLL:
         "rnb_b200_q6k_gemv_with_device_input": [vp, sz, sz, sz, u64, vp, sz],
         "rnb_b200_q6k_gemv_argmax": [vp, sz, sz, sz, vp, sz, vp, vp],
         "rnb_b200_q4k_bf16_qkv_gemm_batch": [vp, sz, vp, sz, vp, sz, sz, sz, sz, vp, sz, vp, sz, vp, sz, vp, sz],
+        "rnb_b200_dense_attention_qkv": [vp, sz, u32, vp, sz, u32, vp, sz, u32, sz, sz, sz, vp, sz, vp, sz, vp, sz, vp, sz],
         "rnb_b200_q8_0_gemv_argmax": [vp, sz, sz, sz, vp, sz, vp, vp],
         "rnb_b200_q8_0_gemv_batch": [vp, sz, sz, sz, vp, sz, vp, sz],
         "rnb_b200_q4k_gemv_batch": [vp, sz, sz, sz, vp, sz, vp, sz],

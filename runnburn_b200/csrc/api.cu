@@ -1025,6 +1025,49 @@ int rnb_b200_dense_attention_qkv_rope_hd128_decode(const uint8_t *q_w, size_t q_
     return RNB_B200_OK;
 }
 
+int rnb_b200_dense_attention_qkv(const uint8_t *q_w, size_t q_w_len, uint32_t q_type, const uint8_t *k_w, size_t k_w_len, uint32_t k_type,
+                                 const uint8_t *v_w, size_t v_w_len, uint32_t v_type, size_t q_rows, size_t kv_rows, size_t n_embd, const float *input,
+                                 size_t input_len, float *q, size_t q_len, float *k, size_t k_len, float *v, size_t v_len) {
+    if (input_len != n_embd) return fail(RNB_B200_VALIDATION_FAILED, "dense QKV input length mismatch: got %zu, expected %zu", input_len, n_embd);
+    if (n_embd == 0 || n_embd % 256 != 0) return fail(RNB_B200_VALIDATION_FAILED, "dense QKV cols must be divisible by 256, got %zu", n_embd);
+    if (q_len < q_rows || k_len < kv_rows || v_len < kv_rows)
+        return fail(RNB_B200_VALIDATION_FAILED, "dense QKV output length mismatch: q=%zu k=%zu v=%zu expected q>=%zu k/v>=%zu", q_len, k_len, v_len, q_rows, kv_rows);
+    const uint32_t types[3] = {q_type, k_type, v_type};
+    const size_t lens[3] = {q_w_len, k_w_len, v_w_len}, rows[3] = {q_rows, kv_rows, kv_rows};
+    for (int i = 0; i < 3; i++) {
+        if (types[i] != TYPE_Q4_K && types[i] != TYPE_Q6_K) return fail(RNB_B200_UNSUPPORTED, "dense QKV: weight type %u not supported", types[i]);
+        RNB_TRY(validate_gemv((int)types[i], lens[i], rows[i], n_embd, n_embd, 1, rows[i], true));
+    }
+    if (!q_w || !k_w || !v_w || !input || !q || !k || !v) return fail(RNB_B200_VALIDATION_FAILED, "null pointer argument");
+    Locked L;
+    State &st = L.st;
+    RNB_TRY(st.open());
+    RNB_CU(cudaSetDevice(st.device));
+    const uint8_t *wd[3];
+    const uint8_t *wh[3] = {q_w, k_w, v_w};
+    for (int i = 0; i < 3; i++) RNB_TRY(st.resident_ptr(wh[i], lens[i], false, &wd[i]));
+    RNB_TRY(st.in_f32.ensure(n_embd * 4));
+    RNB_TRY(st.h2d(st.in_f32.p, input, n_embd * 4, st.pin_in));
+    RNB_TRY(st.xq.ensure(q8k_dev_bytes(n_embd)));
+    RNB_TRY(launch_quantize_q8k(st.stream, st.in_f32.as<float>(), n_embd, 1, st.xq.as<uint8_t>(), nullptr));
+    const size_t out_floats = q_rows + 2 * kv_rows;
+    RNB_TRY(st.out_f32.ensure(out_floats * 4));
+    float *qd = st.out_f32.as<float>(), *kd = qd + q_rows, *vd = kd + kv_rows;
+    GemvJob jobs[3];
+    float *outs[3] = {qd, kd, vd};
+    for (int i = 0; i < 3; i++) jobs[i] = make_job((int)types[i], wd[i], st.xq.p, outs[i], nullptr, rows[i], n_embd, 0, st.sm_count);
+    gemv_finalize_group(jobs, 3, n_embd, st.sm_count);
+    RNB_TRY(st.jobs.ensure(sizeof(jobs)));
+    RNB_TRY(st.h2d(st.jobs.p, jobs, sizeof(jobs), st.pin_jobs));
+    RNB_TRY(launch_gemv_jobs(st.stream, jobs, st.jobs.as<GemvJob>(), 3, n_embd, st.dev_error));
+    std::vector<float> tmp(out_floats);
+    RNB_TRY(finish_to_host(st, st.out_f32.p, tmp.data(), out_floats * 4));
+    memcpy(q, tmp.data(), q_rows * 4);
+    memcpy(k, tmp.data() + q_rows, kv_rows * 4);
+    memcpy(v, tmp.data() + q_rows + kv_rows, kv_rows * 4);
+    return RNB_B200_OK;
+}
+
 int rnb_b200_dense_q4k_silu_ffn_batch(const uint8_t *gate, size_t gate_len, const uint8_t *up, size_t up_len, const uint8_t *down,
                                       size_t down_len, uint32_t down_quant, size_t n_ff, size_t n_embd, size_t seq_len,
                                       const float *input, float *output) {

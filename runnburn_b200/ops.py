@@ -330,6 +330,15 @@ def dense_attention_qkv_rope_hd128_decode(q_w, k_w, v_w, q_rows, kv_rows, n_embd
     return q, kb, vb
 
 
+def dense_attention_qkv(q_w, k_w, v_w, q_rows, kv_rows, n_embd, x, q_type=TYPE_Q4_K, k_type=TYPE_Q4_K, v_type=TYPE_Q4_K):
+    """dense_q4k_attention_qkv — api/dense_api.rs:916: q, k, v of one token in one launch, no RoPE"""
+    qw, kw, vw, x = _u8(q_w), _u8(k_w), _u8(v_w), _f32(x).ravel()
+    q, k, v = np.empty(q_rows, np.float32), np.empty(kv_rows, np.float32), np.empty(kv_rows, np.float32)
+    check(load().rnb_b200_dense_attention_qkv(_p(qw), qw.size, q_type, _p(kw), kw.size, k_type, _p(vw), vw.size, v_type, q_rows, kv_rows, n_embd,
+                                              _p(x), x.size, _p(q), q.size, _p(k), k.size, _p(v), v.size))
+    return q, k, v
+
+
 def dense_q4k_silu_ffn_batch(gate, up, down, down_quant, n_ff, n_embd, seq_len, x) -> np.ndarray:
     g, u, d, x = _u8(gate), _u8(up), _u8(down), _f32(x).ravel()
     out = np.empty(seq_len * n_embd, np.float32)

@@ -402,6 +402,24 @@ def test_fused_qkv_rope_decode(ops):
     assert np.array_equal(vb, orc.f32_to_f16_bits(ops.q6k_gemv(wv, kvh * 128, n_embd, x)))
 
 
+def test_dense_attention_qkv_without_rope(ops):
+    # dense_q4k_attention_qkv: the three projections of one token in one launch, bit-identical to the CPU matvecs;
+    # ragged row counts, mixed Q4_K / Q6_K, and the reference's length checks
+    rng = np.random.default_rng(16)
+    n_embd, q_rows, kv_rows = 768, 520, 130
+    tq, wq = quantized(rng, Q4_K, q_rows, n_embd)
+    tk, wk = quantized(rng, Q4_K, kv_rows, n_embd)
+    tv, wv = quantized(rng, Q6_K, kv_rows, n_embd)
+    x = rng.standard_normal(n_embd).astype(np.float32)
+    q, k, v = ops.dense_attention_qkv(wq, wk, wv, q_rows, kv_rows, n_embd, x, tq, tk, tv)
+    assert bits_equal(q, orc.gemv(Q4_K, wq, x, q_rows, n_embd))
+    assert bits_equal(k, orc.gemv(Q4_K, wk, x, kv_rows, n_embd))
+    assert bits_equal(v, orc.gemv(Q6_K, wv, x, kv_rows, n_embd))
+    import runnburn_b200 as r
+    with pytest.raises(r.RnbError, match="input length mismatch"):
+        ops.dense_attention_qkv(wq, wk, wv, q_rows, kv_rows, n_embd, x[:-1], tq, tk, tv)
+
+
 def test_dense_silu_ffn(ops):
     rng = np.random.default_rng(9)
     n_embd, n_ff, seq = 512, 1024, 3
