@@ -266,6 +266,23 @@ int rnb_b200_moe_route_topk_f32(const float *logits, size_t logits_len,
  * gemv_f32 (crates/rnb-cpu/src/gemm/f32_gemv.rs:215-237), bit-exact. */
 int rnb_b200_router_logits_f32(const float *router_w, size_t n_expert, size_t hidden,
                                const float *h, float *logits_out);
+/* qwen35_expert(gate, up, down, down_quant, n_ff, n_embd, input) — api/qwen_moe_api.rs:1566: one
+ * expert's FFN, down(silu(gate x) * (up x)). */
+int rnb_b200_qwen35_expert(const uint8_t *gate, size_t gate_len, const uint8_t *up, size_t up_len,
+                           const uint8_t *down, size_t down_len, uint32_t down_quant, size_t n_ff,
+                           size_t n_embd, const float *input, size_t input_len, float *output,
+                           size_t output_len);
+/* qwen35_sparse_experts_by_token(gate, up, down, route_weights, token_ids, token_count, down_quant,
+ * n_ff, n_embd, input) — api/qwen_moe_api.rs:2477: a batch of tokens; slot s applies its expert to
+ * token token_ids[s] with weight route_weights[s]; output [token_count][n_embd], a token's slots
+ * summed in slot order, zero for a token without slots (and for no slots at all). */
+int rnb_b200_qwen35_sparse_experts_by_token(const uint8_t *const *gate, const uint8_t *const *up,
+                                            const uint8_t *const *down, size_t gate_slice_len,
+                                            size_t down_slice_len, const float *route_weights,
+                                            const uint32_t *token_ids, size_t n_slots,
+                                            size_t token_count, uint32_t down_quant, size_t n_ff,
+                                            size_t n_embd, const float *input, size_t input_len,
+                                            float *output, size_t output_len);
 /* qwen35_sparse_experts — api/qwen_moe_api.rs:1712-1803: out = sum_e w_e * Down_e(silu(Gate_e
  * x) * (Up_e x)) over the routed experts, summed in selection order.  gate/up are Q4_K,
  * down is `down_quant`. */

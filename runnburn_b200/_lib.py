@@ -122,6 +122,8 @@ def load() -> C.CDLL:
         "rnb_b200_dense_q4k_silu_ffn_batch": [vp, sz, vp, sz, vp, sz, u32, sz, sz, sz, vp, vp],
         "rnb_b200_moe_route_topk_f32": [vp, sz, vp, sz, sz, sz, i32, i32, f32, f32, vp, vp, vp],
         "rnb_b200_router_logits_f32": [vp, sz, sz, vp, vp],
+        "rnb_b200_qwen35_expert": [vp, sz, vp, sz, vp, sz, u32, sz, sz, vp, sz, vp, sz],
+        "rnb_b200_qwen35_sparse_experts_by_token": [vp, vp, vp, sz, sz, vp, vp, sz, sz, u32, sz, sz, vp, sz, vp, sz],
         "rnb_b200_qwen35_sparse_experts": [vp, vp, vp, sz, sz, vp, sz, u32, sz, sz, vp, vp],
         "rnb_b200_qwen35_register_moe_layer": [vp, sz, vp, sz, vp, sz, u32, sz, sz, vp],
         "rnb_b200_rms_norm_rows_f32": [vp, vp, sz, sz, f32, vp],

@@ -382,6 +382,35 @@ def qwen35_sparse_experts(gate, up, down, route_weights, down_quant, n_ff, n_emb
     return out
 
 
+def qwen35_expert(gate, up, down, down_quant, n_ff, n_embd, x) -> np.ndarray:
+    """qwen35_expert — api/qwen_moe_api.rs:1566: one expert's FFN"""
+    g, u, d, x = _u8(gate), _u8(up), _u8(down), _f32(x).ravel()
+    out = np.empty(n_embd, np.float32)
+    check(load().rnb_b200_qwen35_expert(_p(g), g.size, _p(u), u.size, _p(d), d.size, down_quant, n_ff, n_embd, _p(x), x.size, _p(out), out.size))
+    return out
+
+
+def qwen35_sparse_experts_by_token(gate, up, down, route_weights, token_ids, token_count, down_quant, n_ff, n_embd, x) -> np.ndarray:
+    """qwen35_sparse_experts_by_token — api/qwen_moe_api.rs:2477: output [token_count][n_embd]"""
+    n = len(gate)
+    rw, x = _f32(route_weights).ravel(), _f32(x).ravel()
+    ids = np.ascontiguousarray(token_ids, dtype=np.uint32).ravel()
+    assert len(up) == n and len(down) == n and rw.size == n and ids.size == n, "Qwen35 token-batch sparse expert length mismatch"
+    out = np.empty((token_count, n_embd), np.float32)
+    if n == 0:
+        check(load().rnb_b200_qwen35_sparse_experts_by_token(None, None, None, 0, 0, None, None, 0, token_count, down_quant, n_ff, n_embd,
+                                                             _p(x) if x.size else None, x.size, _p(out) if out.size else None, out.size))
+        return out
+    keep = [_u8(a) for a in list(gate) + list(up) + list(down)]
+    arr = C.c_void_p * n
+    g = arr(*[a.ctypes.data for a in keep[:n]])
+    u = arr(*[a.ctypes.data for a in keep[n:2 * n]])
+    d = arr(*[a.ctypes.data for a in keep[2 * n:]])
+    check(load().rnb_b200_qwen35_sparse_experts_by_token(g, u, d, keep[0].size, keep[2 * n].size, _p(rw), _p(ids), n, token_count, down_quant, n_ff,
+                                                         n_embd, _p(x), x.size, _p(out), out.size))
+    return out
+
+
 def qwen35_register_moe_layer(gate_all, up_all, down_all, down_quant, n_ff, n_embd) -> bool:
     g, u, d = _u8(gate_all), _u8(up_all), _u8(down_all)
     fitted = C.c_int()

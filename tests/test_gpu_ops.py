@@ -463,6 +463,45 @@ def test_router_logits_bit_exact(ops):
         assert np.array_equal(ops.router_logits_f32(w, h).view(np.uint32), orc.gemv_f32(w, h).view(np.uint32))
 
 
+def test_single_expert_and_token_batch_experts(ops):
+    # qwen35_expert (one expert, no route weight) and qwen35_sparse_experts_by_token (slots -> tokens): both equal the
+    # decode call's results bit for bit; a token without slots is zero; the reference's length checks
+    rng = np.random.default_rng(19)
+    n_embd, n_ff, n_expert, tokens = 512, 256, 5, 4
+    gs, ds = n_ff * orc.row_bytes(Q4_K, n_embd), n_embd * orc.row_bytes(Q6_K, n_ff)
+    _, gate_all = quantized(rng, Q4_K, n_expert * n_ff, n_embd)
+    _, up_all = quantized(rng, Q4_K, n_expert * n_ff, n_embd)
+    _, down_all = quantized(rng, Q6_K, n_expert * n_embd, n_ff)
+    sl = lambda a, e, n: a[e * n:(e + 1) * n]
+    x = rng.standard_normal((tokens, n_embd)).astype(np.float32)
+    one = ops.qwen35_expert(sl(gate_all, 2, gs), sl(up_all, 2, gs), sl(down_all, 2, ds), Q6_K, n_ff, n_embd, x[0])
+    ref = orc.moe_experts([sl(gate_all, 2, gs)], [sl(up_all, 2, gs)], [sl(down_all, 2, ds)], np.float32([1.0]), Q6_K, n_ff, n_embd, x[0])
+    assert max_rel_err(one, ref) <= 2 * TOL
+    assert np.array_equal(one, ops.qwen35_sparse_experts([sl(gate_all, 2, gs)], [sl(up_all, 2, gs)], [sl(down_all, 2, ds)], np.float32([1.0]), Q6_K,
+                                                         n_ff, n_embd, x[0]))
+    # slots: token 0 <- experts 1, 3; token 1 <- none; token 2 <- expert 4; token 3 <- experts 0, 2, 4 (interleaved order)
+    slot_expert = [1, 0, 4, 3, 2, 4]
+    slot_token = [0, 3, 2, 0, 3, 3]
+    rw = rng.random(len(slot_expert)).astype(np.float32)
+    gate = [sl(gate_all, e, gs) for e in slot_expert]
+    up = [sl(up_all, e, gs) for e in slot_expert]
+    down = [sl(down_all, e, ds) for e in slot_expert]
+    got = ops.qwen35_sparse_experts_by_token(gate, up, down, rw, slot_token, tokens, Q6_K, n_ff, n_embd, x)
+    assert got.shape == (tokens, n_embd) and not got[1].any()
+    for t in (0, 2, 3):
+        mine = [s for s in range(len(slot_token)) if slot_token[s] == t]
+        ref_t = orc.moe_experts([gate[s] for s in mine], [up[s] for s in mine], [down[s] for s in mine], rw[mine], Q6_K, n_ff, n_embd, x[t])
+        assert max_rel_err(got[t], ref_t) <= 2 * TOL
+        assert np.array_equal(got[t], ops.qwen35_sparse_experts([gate[s] for s in mine], [up[s] for s in mine], [down[s] for s in mine], rw[mine], Q6_K,
+                                                                n_ff, n_embd, x[t]))
+    assert not ops.qwen35_sparse_experts_by_token([], [], [], [], [], tokens, Q6_K, n_ff, n_embd, x).any()
+    import runnburn_b200 as r
+    with pytest.raises(r.RnbError, match="token id out of range"):
+        ops.qwen35_sparse_experts_by_token(gate, up, down, rw, [0, 3, 2, 0, 3, 4], tokens, Q6_K, n_ff, n_embd, x)
+    with pytest.raises(r.RnbError, match="input length mismatch"):
+        ops.qwen35_expert(gate[0], up[0], down[0], Q6_K, n_ff, n_embd, x[0][:-1])
+
+
 def test_sparse_experts(ops):
     rng = np.random.default_rng(14)
     n_embd, n_ff, n_expert, k = 512, 256, 12, 4
