@@ -68,8 +68,8 @@ def llama_description(seed: int, n_layer=2, hidden=512, n_head=4, n_kv_head=2, n
 
 
 def moe_description(seed: int, n_layer=2, hidden=512, n_head=4, n_kv_head=2, vocab=1024, n_expert=16,
-                    n_expert_used=4, n_ff_expert=256, rope_theta=1e6, rms_eps=1e-6, sigma=0.02):
-    """Qwen3-MoE-shaped stack: Q6_K attention, Q4_K experts, f32 N(0,1) router, half-split RoPE."""
+                    n_expert_used=4, n_ff_expert=256, rope_theta=1e6, rms_eps=1e-6, sigma=0.02, down_type=Q4_K):
+    """Qwen3-MoE-shaped stack: Q6_K attention, Q4_K experts (down experts: down_type), f32 N(0,1) router, half-split RoPE."""
     rng = np.random.default_rng(seed)
     hd = 128
     layers = []
@@ -81,7 +81,7 @@ def moe_description(seed: int, n_layer=2, hidden=512, n_head=4, n_kv_head=2, voc
             router=rng.standard_normal((n_expert, hidden)).astype(np.float32),
             gate_exps=quantized(rng, Q4_K, n_expert * n_ff_expert, hidden, sigma),
             up_exps=quantized(rng, Q4_K, n_expert * n_ff_expert, hidden, sigma),
-            down_exps=quantized(rng, Q4_K, n_expert * hidden, n_ff_expert, sigma)))
+            down_exps=quantized(rng, down_type, n_expert * hidden, n_ff_expert, sigma)))
     cfg = dict(n_layer=n_layer, hidden=hidden, n_head=n_head, n_kv_head=n_kv_head, head_dim=hd, n_ff=0, vocab=vocab,
                rope_neox=1, rms_eps=rms_eps, rope_theta=rope_theta, n_expert=n_expert, n_expert_used=n_expert_used,
                n_ff_expert=n_ff_expert)

@@ -134,13 +134,14 @@ def test_llama_first_layer_kv_bits_and_embedding_exact():
     ref.close()
 
 
-@pytest.mark.parametrize("static_tables", ["1", "0"])
-def test_moe_decoder_expert_ids_and_tokens(static_tables, monkeypatch):
+@pytest.mark.parametrize("static_tables,down_type", [("1", 12), ("0", 12), ("1", 14)])
+def test_moe_decoder_expert_ids_and_tokens(static_tables, down_type, monkeypatch):
     # "1": the expert matvecs read the routed ids on the device from static tables over the stacked expert tensors
-    # (SiLU and the ordered expert sum in their tails); "0": the job tables the router rewrites every token
+    # (SiLU and the ordered expert sum in their tails); "0": the job tables the router rewrites every token;
+    # Q6_K down experts (type 14): gate + up static, down from the table
     monkeypatch.setenv("RNB_B200_MOE_STATIC", static_tables)
     desc = moe_description(seed=1, n_layer=2, hidden=512, n_head=4, n_kv_head=2, vocab=1024, n_expert=16,
-                           n_expert_used=4, n_ff_expert=256)
+                           n_expert_used=4, n_ff_expert=256, down_type=down_type)
     rng = np.random.default_rng(1)
     prompt = rng.integers(0, 1024, 8).tolist()
     dec, ref = _run(desc, prompt, 16, 64)
