@@ -278,8 +278,16 @@ def prefill_gemm_bench(shape: dict, seq: int, reps: int = 3) -> dict:
         rws = (C.c_size_t * n)(*[r_ for _, r_, _ in grp])
         yp = (C.c_void_p * n)(*[y.data_ptr() for y in ys])
 
+        # gate + up run as the prefill driver runs them: one launch whose epilogue writes silu(gate) * up as bf16
+        fused = n == 2 and grp[0] == grp[1]
+        act = torch.empty(seq, grp[0][1], dtype=torch.bfloat16, device="cuda") if fused else None
+
         def run():
-            rc = L.rnb_b200_dev_prefill_gemm_multi(n, types, wp, rws, yp, cols, x.data_ptr(), seq, xb.data_ptr(), stream)
+            if fused:
+                rc = L.rnb_b200_dev_prefill_gemm_silu(grp[0][0], ws[0].data_ptr(), ws[1].data_ptr(), grp[0][1], cols, x.data_ptr(), seq, xb.data_ptr(),
+                                                      act.data_ptr(), stream)
+            else:
+                rc = L.rnb_b200_dev_prefill_gemm_multi(n, types, wp, rws, yp, cols, x.data_ptr(), seq, xb.data_ptr(), stream)
             if rc != 0:
                 raise RuntimeError(L.rnb_b200_last_error().decode())
         for _ in range(3):
@@ -295,8 +303,9 @@ def prefill_gemm_bench(shape: dict, seq: int, reps: int = 3) -> dict:
         fl = sum(2.0 * r_ * cols * seq for _, r_, _ in grp)
         flops_total += fl
         ms_total += ms
-        rows_out.append({"matrices": ["%s %dx%d" % ("Q4_K" if t == 12 else "Q6_K", r_, c_) for t, r_, c_ in grp], "ms": ms, "tflops": fl / ms / 1e9})
-        del ws, ys, x, xb
+        rows_out.append({"matrices": ["%s %dx%d" % ("Q4_K" if t == 12 else "Q6_K", r_, c_) for t, r_, c_ in grp], "ms": ms, "tflops": fl / ms / 1e9,
+                         **({"epilogue": "silu(gate) * up -> bf16"} if fused else {})})
+        del ws, ys, x, xb, act
     if r.ops.dev_error_flag() != 0:
         raise RuntimeError("device error flag set by the prefill matmul")
     tf = flops_total / ms_total / 1e9

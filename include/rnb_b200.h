@@ -630,6 +630,12 @@ int rnb_b200_dev_prefill_gemm(int type, const uint8_t *w_dev, size_t rows, size_
 int rnb_b200_dev_prefill_gemm_multi(int n, const int *types, const uint8_t *const *w_dev,
                                     const size_t *rows, float *const *y_dev, size_t cols,
                                     const float *x_dev, size_t seq, uint16_t *xb_dev, void *stream);
+/* gate + up of a token batch with silu(gate) * up computed in the matmul's epilogue: act_dev bf16
+ * [seq][rows] (the token matrix of the down matmul); gate and up share the GGML type; act_dev must
+ * not alias xb_dev. */
+int rnb_b200_dev_prefill_gemm_silu(int type, const uint8_t *gate_dev, const uint8_t *up_dev,
+                                   size_t rows, size_t cols, const float *x_dev, size_t seq,
+                                   uint16_t *xb_dev, uint16_t *act_dev, void *stream);
 int rnb_b200_dev_flash_decode(const float *q_dev, const uint16_t *k_dev, const uint16_t *v_dev,
                               size_t kv_len, size_t num_heads, size_t num_kv_heads, float scale,
                               float *partials_dev, size_t partials_bytes, int n_chunks,

@@ -176,6 +176,7 @@ def load() -> C.CDLL:
         "rnb_b200_dev_gemv": [u32, vp, sz, sz, vp, vp, i32, vp],
         "rnb_b200_dev_prefill_gemm": [i32, vp, sz, sz, vp, sz, vp, vp, vp],
         "rnb_b200_dev_prefill_gemm_multi": [i32, vp, vp, vp, vp, sz, vp, sz, vp, vp],
+        "rnb_b200_dev_prefill_gemm_silu": [i32, vp, vp, sz, sz, vp, sz, vp, vp, vp],
         "rnb_b200_dev_flash_decode": [vp, vp, vp, sz, sz, sz, f32, vp, sz, i32, vp, vp],
         "rnb_b200_flash_decode_default_chunks": [sz, sz],
         "rnb_b200_attention_decode_hd128_noalloc": [vp, vp, vp, sz, sz, sz, f32, vp, vp],

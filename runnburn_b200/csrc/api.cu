@@ -718,6 +718,14 @@ int rnb_b200_dev_prefill_gemm_multi(int n, const int *types, const uint8_t *cons
     return launch_prefill_gemm_multi((cudaStream_t)stream, n, types, w_dev, rows, y_dev, cols, x_dev, seq, xb_dev, L.st.dev_error);
 }
 
+int rnb_b200_dev_prefill_gemm_silu(int type, const uint8_t *gate_dev, const uint8_t *up_dev, size_t rows, size_t cols, const float *x_dev, size_t seq,
+                                   uint16_t *xb_dev, uint16_t *act_dev, void *stream) {
+    if (!gate_dev || !up_dev || !x_dev || !xb_dev || !act_dev) return fail(RNB_B200_VALIDATION_FAILED, "null pointer argument");
+    Locked L;
+    RNB_TRY(L.st.open());
+    return launch_prefill_gemm_silu((cudaStream_t)stream, type, gate_dev, up_dev, rows, cols, x_dev, seq, xb_dev, act_dev, L.st.dev_error);
+}
+
 // ---- attention --------------------------------------------------------------------------------
 static int validate_attn(size_t q_len, size_t kv_elems, size_t kv_len, size_t heads, size_t kv_heads, size_t head_dim, size_t out_len) {
     if (head_dim != 128) return fail(RNB_B200_UNSUPPORTED, "decode attention supports head_dim 128 only, got %zu", head_dim);

@@ -766,6 +766,34 @@ inline int launch_prefill_gemm_multi(cudaStream_t s, int n, const int *types, co
     RNB_CU(launch_k(prefill_gemm_kernel, grid, dim3(PG_THREADS), PG_SMEM, s, jobs, tmap, (int)seq, (int)cols, dev_error));
     return RNB_B200_OK;
 }
+// gate + up of a token batch with silu(gate) * up in the epilogue: act [seq][rows] bf16, ready to be the token matrix of
+// the down matmul.  `act` must not alias `xb` (other CTAs are still reading tokens when the first tiles finish).
+inline int launch_prefill_gemm_silu(cudaStream_t s, int type, const uint8_t *gate, const uint8_t *up, size_t rows, size_t cols, const float *x, size_t seq,
+                                    uint16_t *xb, uint16_t *act, int *dev_error) {
+    if (type != TYPE_Q4_K && type != TYPE_Q6_K) return fail(RNB_B200_UNSUPPORTED, "tensor-core prefill matmul supports Q4_K and Q6_K weights");
+    if (cols == 0 || cols % 256 != 0) return fail(RNB_B200_VALIDATION_FAILED, "cols(%zu) must be a non-zero multiple of 256", cols);
+    if (seq == 0 || rows == 0) return fail(RNB_B200_VALIDATION_FAILED, "prefill matmul needs tokens and rows");
+    if (!gate || !up || !xb || !act || act == xb) return fail(RNB_B200_VALIDATION_FAILED, "prefill gate+up: null or aliased operands");
+    if (((uintptr_t)x & 15u) || ((uintptr_t)xb & 15u) || ((uintptr_t)act & 1u) || (((uintptr_t)gate | (uintptr_t)up) & (type == TYPE_Q4_K ? 15u : 1u)))
+        return fail(RNB_B200_VALIDATION_FAILED, "prefill matmul operands are not aligned");
+    PgJobs jobs;
+    memset(&jobs, 0, sizeof(jobs));
+    jobs.n = 1;
+    jobs.j[0].w = gate;
+    jobs.j[0].w2 = up;
+    jobs.j[0].yb = act;
+    jobs.j[0].rows = (int)rows;
+    jobs.j[0].type = type;
+    const int tiles = (int)((rows + PG_ROWS / 2 - 1) / (PG_ROWS / 2));
+    RNB_TRY(prefill_gemm_setup());
+    const size_t ne = seq * cols;
+    if (x) RNB_CU(launch_k(f32_to_bf16_kernel, dim3((unsigned)((ne / 8 + 255) / 256)), dim3(256), 0, s, x, xb, ne));
+    PgTensorMap tmap;
+    RNB_TRY(encode_token_map(&tmap, xb, seq, cols));
+    const dim3 grid((unsigned)tiles, (unsigned)((seq + PG_TOK - 1) / PG_TOK));
+    RNB_CU(launch_k(prefill_gemm_kernel, grid, dim3(PG_THREADS), PG_SMEM, s, jobs, tmap, (int)seq, (int)cols, dev_error));
+    return RNB_B200_OK;
+}
 inline int launch_prefill_gemm(cudaStream_t s, int type, const uint8_t *w, size_t rows, size_t cols, const float *x, size_t seq,
                                uint16_t *xb, float *y, int *dev_error) {
     return launch_prefill_gemm_multi(s, 1, &type, &w, &rows, &y, cols, x, seq, xb, dev_error);

@@ -214,6 +214,10 @@ struct PgJob {
     const uint8_t *w;
     float *y;     // [seq][rows]
     int rows, type, tile0, pad;
+    // gate + up form (w2 != null): a tile is 64 rows of w (gate) on TMEM lanes 0-63 and the same 64 rows of w2 (up) on
+    // lanes 64-127; the epilogue writes silu(gate) * up as bf16 [seq][rows] to yb - the token matrix of the down matmul
+    const uint8_t *w2;
+    uint16_t *yb;
 };
 struct PgJobs {
     PgJob j[PG_MAX_JOBS];
@@ -312,7 +316,8 @@ prefill_gemm_kernel(const __grid_constant__ PgJobs jobs, const __grid_constant__
     const uint8_t *__restrict__ w = job.w;
     float *__restrict__ y = job.y;
     const uint32_t BLK = TYPE == TYPE_Q4_K ? Q4K_BYTES : Q6K_BYTES;
-    const int n0 = ((int)blockIdx.x - job.tile0) * PG_ROWS, m0 = blockIdx.y * PG_TOK;
+    const bool pair = job.w2 != nullptr;
+    const int n0 = ((int)blockIdx.x - job.tile0) * (pair ? PG_ROWS / 2 : PG_ROWS), m0 = blockIdx.y * PG_TOK;
     const int nb = cols >> 8, KT = cols / PG_K;
     if (tid == 0) {
         for (int s = 0; s < PG_STAGES; s++) {
@@ -336,7 +341,9 @@ prefill_gemm_kernel(const __grid_constant__ PgJobs jobs, const __grid_constant__
     if (warp < 8) {
         const int row = tid >> 1, h = tid & 1, rr = row & 7;
         const size_t rb = (size_t)nb * BLK;
-        const uint8_t *wr = w + (size_t)min(n0 + row, rows - 1) * rb;   // rows past the end repeat the last one (never stored)
+        // rows past the end repeat the last one (never stored)
+        const uint8_t *wr = pair ? (row < PG_ROWS / 2 ? w : job.w2) + (size_t)min(n0 + (row & (PG_ROWS / 2 - 1)), rows - 1) * rb
+                                 : w + (size_t)min(n0 + row, rows - 1) * rb;
         uint8_t *const brow = smem + PG_A_BYTES + (row >> 3) * 1024 + rr * 128;
         // token tile of stage kt: thread 0 announces the bytes and issues the two copies
         auto issue_tokens = [&](int kt) {
@@ -424,7 +431,38 @@ prefill_gemm_kernel(const __grid_constant__ PgJobs jobs, const __grid_constant__
             for (int s = 0; s < PG_STAGES; s++) mbar_wait_bounded(&full[s], 0u);
         }
         pg_fence_after();
-        if (fin) {
+        if (pair) {
+            // gate rows sit on lanes 0-63 (lane quarters 0, 1), the same rows of up on lanes 64-127 (quarters 2, 3): the
+            // eight warps put their 32 rows x 32 tokens into shared memory (the operand stages are free by now), then
+            // each computes silu(gate) * up for 16 of the 32 tokens of its row.  Every warp takes part in every
+            // barrier, whatever its own wait returned.
+            float *ex = reinterpret_cast<float *>(smem);
+            const int q = warp & 3, nh = warp >> 2, qp = q & 1;
+            const int row = n0 + qp * 32 + lane, t_lo = (q >> 1) * 16;
+#pragma unroll 1
+            for (int cc = 0; cc < 256 / 32; cc++) {
+                // two exchange buffers in turn: the barrier of the next pass also covers the reads of this one
+                float *buf = ex + (size_t)(cc & 1) * (8 * 32 * 33);
+                float *mine = buf + (size_t)warp * (32 * 33);
+                const float *gsrc = buf + (size_t)(nh * 4 + qp) * (32 * 33), *usrc = buf + (size_t)(nh * 4 + qp + 2) * (32 * 33);
+                uint32_t v[32];
+                if (fin) pg_tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(nh * 256 + cc * 32), v);
+#pragma unroll
+                for (int i = 0; i < 32; i++) mine[lane * 33 + i] = fin ? __uint_as_float(v[i]) : 0.f;
+                asm volatile("bar.sync 1, 256;" ::: "memory");
+                const int tok0 = m0 + nh * 256 + cc * 32 + t_lo;
+                if (fin && row < rows) {
+                    uint16_t *dst = job.yb + (size_t)tok0 * rows + row;
+#pragma unroll
+                    for (int i = 0; i < 16; i++) {
+                        const float g = gsrc[lane * 33 + t_lo + i], u = usrc[lane * 33 + t_lo + i];
+                        // fast exponential and division: their 2^-21 relative error disappears in the bf16 rounding below
+                        const float a = __fdividef(g, 1.0f + __expf(-g)) * u;
+                        if (tok0 + i < seq) dst[(size_t)i * rows] = (uint16_t)(pg_pack_bf16(a, 0.f) & 0xffffu);
+                    }
+                }
+            }
+        } else if (fin) {
             const int q = warp & 3, nh = warp >> 2;
             const int row = n0 + q * 32 + lane;
 #pragma unroll 1

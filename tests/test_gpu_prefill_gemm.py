@@ -109,6 +109,37 @@ def test_bf16_gemm_three_matrices_one_launch(ops):
         assert max_err_vs_norm(y.cpu().numpy(), ref) <= TOL / 10
 
 
+@pytest.mark.parametrize("t,rows,cols,seq", [(Q4_K, 256, 512, 70), (Q4_K, 1000, 1024, 600), (Q6_K, 192, 1024, 33), (Q4_K, 14336, 4096, 512)])
+def test_bf16_gate_up_silu_epilogue(ops, t, rows, cols, seq):
+    """gate + up in one launch (64 rows of each per tile) with silu(gate) * up written as bf16 by the epilogue: equal to
+    the two single-matrix products pushed through the same formula, up to the bf16 rounding of the result; ragged
+    row and token counts."""
+    import torch
+
+    import runnburn_b200 as r
+    L = r.load()
+    rng = np.random.default_rng(rows + seq)
+    wg = quantized(rng, t, rows, cols)[1] if rows < 4096 else random_blocks(rng, t, rows, cols)
+    wu = quantized(rng, t, rows, cols)[1] if rows < 4096 else random_blocks(rng, t, rows, cols)
+    x = (rng.standard_normal((seq, cols)) * (1.0 if rows < 4096 else 0.05)).astype(np.float32)
+    fn = ops.q4k_bf16_gemm_batch if t == Q4_K else ops.q6k_bf16_gemm_batch
+    g = fn(wg, rows, cols, x).reshape(seq, rows).astype(np.float64)
+    u = fn(wu, rows, cols, x).reshape(seq, rows).astype(np.float64)
+    ref = g / (1.0 + np.exp(-g)) * u
+    gt, ut = torch.from_numpy(np.ascontiguousarray(wg)).cuda(), torch.from_numpy(np.ascontiguousarray(wu)).cuda()
+    xt = torch.from_numpy(x).cuda()
+    xb = torch.empty(seq * cols, dtype=torch.int16, device="cuda")
+    act = torch.zeros(seq, rows, dtype=torch.bfloat16, device="cuda")
+    rc = L.rnb_b200_dev_prefill_gemm_silu(t, gt.data_ptr(), ut.data_ptr(), rows, cols, xt.data_ptr(), seq, xb.data_ptr(), act.data_ptr(),
+                                          torch.cuda.current_stream().cuda_stream)
+    assert rc == 0, L.rnb_b200_last_error()
+    torch.cuda.synchronize()
+    assert ops.dev_error_flag() == 0
+    got = act.float().cpu().numpy().astype(np.float64)
+    # one bf16 rounding of the result (2^-9 relative) on top of the f32 evaluation
+    assert np.max(np.abs(got - ref) / np.maximum(np.abs(ref), 1e-3 * np.max(np.abs(ref)))) <= 2.0 ** -8
+
+
 def test_bf16_gemm_rejects_bad_shapes(ops):
     import runnburn_b200 as r
     w = np.zeros(144, np.uint8)
