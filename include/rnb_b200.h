@@ -540,7 +540,9 @@ int rnb_b200_decoder_attach_nccl(rnb_b200_decoder *d, const uint8_t id[128]);
  * prefill.rs:1104-1166): all matmuls on the tcgen05 kernel (bf16 x bf16 -> f32), RoPE + f16 KV
  * append for every position, causal attention over the cache, then the last token's logits ->
  * greedy token.  Leaves the decoder ready to decode at position pos0+n.  ms_out (optional):
- * device time between two events on the decoder's stream.  Single GPU, dense stacks. */
+ * device time between two events on the decoder's stream.  The tensor-core path serves single-GPU
+ * dense stacks in Q4_K / Q6_K; MoE stacks, sharded decoders (every rank calls) and other weight
+ * types take the prompt token by token through the decode step (ms_out: host wall time). */
 int rnb_b200_decoder_prefill(rnb_b200_decoder *d, const uint32_t *tokens, int n, int pos0,
                              uint32_t *next_token, float *ms_out);
 /* Logits of the last step or prefill (this rank's vocab slice), for tests. */

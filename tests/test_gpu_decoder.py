@@ -163,6 +163,29 @@ def test_moe_decoder_expert_ids_and_tokens(static_tables, down_type, monkeypatch
     ref.close()
 
 
+def test_prefill_of_a_moe_stack_goes_token_by_token():
+    # the tensor-core prefill serves dense stacks; a MoE stack takes its prompt through the decode step: same next token
+    # and the same KV rows as decoding the prompt
+    import runnburn_b200 as r
+    desc = moe_description(seed=3, n_layer=2, hidden=512, n_head=4, n_kv_head=2, vocab=1024, n_expert=16, n_expert_used=4, n_ff_expert=256)
+    prompt = np.random.default_rng(3).integers(0, 1024, 9).tolist()
+    a = r.Decoder(r.ModelConfig(max_ctx=32, **desc["cfg"]))
+    a.load_description(desc)
+    b = r.Decoder(r.ModelConfig(max_ctx=32, **desc["cfg"]))
+    b.load_description(desc)
+    nxt, ms = a.prefill(prompt, 0, timed=True)
+    for pos, t in enumerate(prompt):
+        want = b.step(t, pos)
+    assert nxt == want and ms > 0.0
+    for layer in range(2):
+        ka, va = a.read_kv(layer, len(prompt))
+        kb, vb = b.read_kv(layer, len(prompt))
+        assert np.array_equal(ka, kb) and np.array_equal(va, vb)
+    assert a.step(nxt, len(prompt)) == b.step(want, len(prompt))
+    a.close()
+    b.close()
+
+
 def test_step_dev_chain_matches_host_steps():
     desc = llama_description(seed=2, n_layer=2, hidden=256, n_head=2, n_kv_head=1, n_ff=512, vocab=512)
     import runnburn_b200 as r
