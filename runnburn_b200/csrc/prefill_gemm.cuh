@@ -256,12 +256,22 @@ struct PgRawQ6 {
     uint32_t sc[2];
     float d;
 };
-__device__ __forceinline__ void pg_load_q6(PgRawQ6 &r, const uint8_t *blk, int n, int h) {
+// N consecutive words from a 2-byte aligned address: N + 1 aligned words, funnel-shifted (no branch; the extra word
+// lies inside the block for the ql and qh ranges this is used for).
+template <int N>
+__device__ __forceinline__ void pg_ldg_words_unaligned(const uint8_t *p, uint32_t *out) {
+    const uintptr_t a = reinterpret_cast<uintptr_t>(p);
+    const uint32_t *w = reinterpret_cast<const uint32_t *>(a & ~(uintptr_t)3);
+    const uint32_t sh = (uint32_t)(a & 3) * 8;
+    uint32_t v[N + 1];
 #pragma unroll
-    for (int i = 0; i < 8; i++) {
-        r.ql[i] = pg_ldg_u32_unaligned(blk + 64 * n + 32 * h + 4 * i);
-        if (i < 4) r.qh[i] = pg_ldg_u32_unaligned(blk + 128 + 32 * n + 16 * h + 4 * i);
-    }
+    for (int i = 0; i <= N; i++) v[i] = __ldg(w + i);
+#pragma unroll
+    for (int i = 0; i < N; i++) out[i] = __funnelshift_r(v[i], v[i + 1], sh);
+}
+__device__ __forceinline__ void pg_load_q6(PgRawQ6 &r, const uint8_t *blk, int n, int h) {
+    pg_ldg_words_unaligned<8>(blk + 64 * n + 32 * h, r.ql);
+    pg_ldg_words_unaligned<4>(blk + 128 + 32 * n + 16 * h, r.qh);
     r.sc[0] = pg_ldg_u32_unaligned(blk + 192 + 8 * n);
     r.sc[1] = pg_ldg_u32_unaligned(blk + 196 + 8 * n);
     r.d = f16_bits_to_f32(*reinterpret_cast<const uint16_t *>(blk + 208));
