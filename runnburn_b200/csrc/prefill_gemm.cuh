@@ -106,15 +106,7 @@ __device__ __forceinline__ uint4 pg_pair_exchange(const uint4 &mine) {
 }
 // Q6_K: group g of a block = elements 64g..64g+63 = for half n = g/2 the pair (q1,q2) if g even,
 // (q3,q4) if g odd, l = 0..31 each; y = (d*sc)*(q-32): dequant.rs:780-807.  Blocks are 210 bytes,
-// so rows are only 2-byte aligned: bytes are fetched as aligned words and funnel-shifted.
-__device__ __forceinline__ uint32_t pg_ldg_u32_unaligned(const uint8_t *p) {
-    const uintptr_t a = reinterpret_cast<uintptr_t>(p);
-    const uint32_t *w = reinterpret_cast<const uint32_t *>(a & ~(uintptr_t)3);
-    const uint32_t sh = (uint32_t)(a & 3) * 8;
-    const uint32_t w0 = __ldg(w);
-    if (sh == 0) return w0;
-    return __funnelshift_r(w0, __ldg(w + 1), sh);
-}
+// so rows are only 2-byte aligned: bytes are fetched as aligned 16-byte windows and shifted into place (pg_ldg_window).
 // f32 -> bf16 rows (activation), padded to a multiple of 8 columns by construction (cols % 256 == 0)
 RNB_GLOBAL void __launch_bounds__(256)
 f32_to_bf16_kernel(const float *__restrict__ x, uint16_t *__restrict__ y, size_t n) {
@@ -256,25 +248,47 @@ struct PgRawQ6 {
     uint32_t sc[2];
     float d;
 };
-// N consecutive words from a 2-byte aligned address: N + 1 aligned words, funnel-shifted (no branch; the extra word
-// lies inside the block for the ql and qh ranges this is used for).
-template <int N>
-__device__ __forceinline__ void pg_ldg_words_unaligned(const uint8_t *p, uint32_t *out) {
+// NW consecutive words from a 2-byte aligned address out of NV aligned 16-byte loads (4 NV >= NW + 4): the words of the
+// loaded window are shifted by whole words with two levels of selects, then funnel-shifted by the odd half-word.  The
+// threads of a warp read rows that lie kilobytes apart, so every load instruction costs 32 cache-line accesses
+// whatever its width: seven 16-byte loads per half block instead of eighteen 4-byte ones is what lifts the Q6_K
+// producer off the load pipe.  An aligned 16-byte load that contains one byte of the tensor cannot leave its page.
+template <int NW, int NV>
+__device__ __forceinline__ void pg_ldg_window(const uint8_t *p, uint32_t *out, uint32_t *raw = nullptr) {
+    static_assert(4 * NV >= NW + 4, "window too small");
     const uintptr_t a = reinterpret_cast<uintptr_t>(p);
-    const uint32_t *w = reinterpret_cast<const uint32_t *>(a & ~(uintptr_t)3);
-    const uint32_t sh = (uint32_t)(a & 3) * 8;
-    uint32_t v[N + 1];
+    const uint8_t *base = reinterpret_cast<const uint8_t *>(a & ~(uintptr_t)15);
+    const uint32_t off = (uint32_t)(a & 15), k = off >> 2, sh = (off & 3u) * 8u;
+    uint32_t v[4 * NV];
 #pragma unroll
-    for (int i = 0; i <= N; i++) v[i] = __ldg(w + i);
+    for (int j = 0; j < NV; j++) {
+        const uint4 t = ldg_nc_u4(base + 16 * j);
+        v[4 * j] = t.x, v[4 * j + 1] = t.y, v[4 * j + 2] = t.z, v[4 * j + 3] = t.w;
+    }
+    if (raw) {
 #pragma unroll
-    for (int i = 0; i < N; i++) out[i] = __funnelshift_r(v[i], v[i + 1], sh);
+        for (int i = 0; i < 4 * NV; i++) raw[i] = v[i];
+    }
+    uint32_t s1[NW + 2], s2[NW + 1];
+#pragma unroll
+    for (int i = 0; i < NW + 2; i++) s1[i] = (k & 2u) ? v[i + 2] : v[i];
+#pragma unroll
+    for (int i = 0; i < NW + 1; i++) s2[i] = (k & 1u) ? s1[i + 1] : s1[i];
+#pragma unroll
+    for (int i = 0; i < NW; i++) out[i] = __funnelshift_r(s2[i], s2[i + 1], sh);
 }
 __device__ __forceinline__ void pg_load_q6(PgRawQ6 &r, const uint8_t *blk, int n, int h) {
-    pg_ldg_words_unaligned<8>(blk + 64 * n + 32 * h, r.ql);
-    pg_ldg_words_unaligned<4>(blk + 128 + 32 * n + 16 * h, r.qh);
-    r.sc[0] = pg_ldg_u32_unaligned(blk + 192 + 8 * n);
-    r.sc[1] = pg_ldg_u32_unaligned(blk + 196 + 8 * n);
-    r.d = f16_bits_to_f32(*reinterpret_cast<const uint16_t *>(blk + 208));
+    pg_ldg_window<8, 3>(blk + 64 * n + 32 * h, r.ql);
+    pg_ldg_window<4, 2>(blk + 128 + 32 * n + 16 * h, r.qh);
+    // scales (16 bytes at 192) and d (2 bytes at 208): one 18-byte window = two aligned 16-byte loads
+    uint32_t sc4[4], raw[8];
+    pg_ldg_window<4, 2>(blk + 192, sc4, raw);
+    r.sc[0] = n ? sc4[2] : sc4[0];
+    r.sc[1] = n ? sc4[3] : sc4[1];
+    // d sits 16 bytes after the window's first byte: in the second 16-byte load, at the same offset
+    const uint32_t dpos = (uint32_t)(reinterpret_cast<uintptr_t>(blk + 192) & 15u), dk = dpos >> 2;
+    const uint32_t dlo = (dk & 2u) ? ((dk & 1u) ? raw[7] : raw[6]) : ((dk & 1u) ? raw[5] : raw[4]);
+    r.d = f16_bits_to_f32((dlo >> ((dpos & 2u) * 8u)) & 0xffffu);
 }
 __device__ __forceinline__ void pg_dequant_q6(const PgRawQ6 &r, int g, int h, uint8_t *row_base, int rr) {
     const bool odd = g & 1;
